@@ -1,0 +1,338 @@
+"""Benchmark of the quantised GEMV hot path on B200: Q4_K decode sweep, Llama-7B layer shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass over the sweep: y = x W^T for the four Q4_K weight shapes 4096x4096, 11008x4096,
+4096x11008 and 32000x4096 at batch M = 1 and M = 8 (eight launches). Weights are seeded N(0, 0.02)
+values quantised to Q4_K, activations N(0, 1). Each launch reads a different copy of its weight from
+a rotating pool several times the size of L2, so every weight byte comes from HBM.
+
+The line printed (rank 0) carries:
+  value      algorithmic GB/s of the whole job with inputs resident in HBM (CUDA events, max over ranks)
+  e2e        the same metric through the C ABI with host buffers: pinned-host x copied in and y copied
+             out inside every timed call
+  roofline   achieved GB/s of the GEMV kernel against the measured HBM copy peak
+  cpu_baseline  the CPU port of the reference's host arithmetic (oracle/), one thread, one step
+With --gpus N > 1 every weight is split by output rows over the ranks and each launch is followed by
+an NCCL all-gather of the output slices (strong scaling: the job is the same at every N).
+With --impl reference the CPU port runs the sweep on all host threads instead (the reference's own
+backend for these operators is its scalar host loop; it has no JVM here to run in).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # [N out, K in]
+BATCHES = [1, 8]
+TYPE = "Q4_K"
+BYTES_PER_WEIGHT = 144.0 / 256.0
+POOL_COPIES = 4  # distinct copies of every weight; 4 x 134 MB = 537 MB, about 4x the 126 MB L2
+METRIC = "q4k_gemv_sweep_GBps"
+
+
+def algorithmic_bytes(n, k, m):
+    """Quantised weights once + FP32 x + FP32 y."""
+    return n * k * BYTES_PER_WEIGHT + 4.0 * m * k + 4.0 * m * n
+
+
+def step_bytes():
+    return sum(algorithmic_bytes(n, k, m) for n, k in SHAPES for m in BATCHES)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_weights(torch, device, rank, world):
+    """Seeded N(0, 0.02) weights quantised to Q4_K on the GPU; each rank uploads its row shard."""
+    from jitnn_b200 import Tensor, synth
+    pools = []
+    for si, (n, k) in enumerate(SHAPES):
+        copies = []
+        for c in range(POOL_COPIES):
+            g = torch.Generator(device=device).manual_seed(1234 + 17 * si + c)
+            wf = torch.randn(n, k, generator=g, device=device) * 0.02
+            raw = synth.quantize_q4_k(wf).cpu().numpy()
+            del wf
+            lo, hi = rank * n // world, (rank + 1) * n // world
+            copies.append(Tensor.quantized(TYPE, raw, n, k, device=device.index, rows=(lo, hi)) if world > 1
+                          else Tensor.quantized(TYPE, raw, n, k, device=device.index))
+            if c == 0 and si == 0:
+                first_raw = raw[:64].copy()
+        pools.append(copies)
+    return pools, first_raw
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import jitnn_b200
+    from jitnn_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run for N > 1" % (args.gpus, world))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback for the product path"
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    L = jitnn_b200.load()
+    stream = torch.cuda.current_stream(device)
+    sp = ctypes.c_void_p(stream.cuda_stream)
+
+    pools, first_raw = make_weights(torch, device, rank, world)
+    g = torch.Generator(device=device).manual_seed(99)
+    xs = {(k, m): torch.randn(m, k, generator=g, device=device) for _, k in SHAPES for m in BATCHES}
+    ys = {}
+    gathered = {}
+    for n, k in SHAPES:
+        for m in BATCHES:
+            ys[(n, k, m)] = torch.empty(m, n // world, device=device)
+            if world > 1:
+                gathered[(n, k, m)] = torch.empty(world, m, n // world, device=device)
+
+    def step(i):
+        for si, (n, k) in enumerate(SHAPES):
+            for mi, m in enumerate(BATCHES):
+                w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
+                y = ys[(n, k, m)]
+                _lib.check(L.jq_linear_f32(w._handle(), xs[(k, m)].data_ptr(), m, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[(n, k, m)], y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # correctness guard: the first rows of the first weight against the CPU oracle (not timed)
+    if rank == 0 and world == 1:
+        from oracle import oracle
+        xh = xs[(4096, 1)].cpu().numpy()
+        yh = jitnn_b200.Gguf.linear(xs[(4096, 1)], pools[0][0], None).cpu().numpy()
+        ref = oracle.linear(TYPE, first_raw, xh, None)
+        rel = float(np.abs(yh[:, :64] - ref).max() / np.abs(ref).max())
+        assert rel <= 1e-3, "GEMV differs from the oracle: %g" % rel
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = L.jq_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        step(args.warmup + i)
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = L.jq_launch_count() - launches0
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms / args.steps
+    value = step_bytes() / (ms_per_step * 1e-3) / 1e9
+
+    # per-shape kernel times (device-resident, same rotation), for the roofline breakdown
+    per_shape = {}
+    if world == 1:
+        for si, (n, k) in enumerate(SHAPES):
+            for m in BATCHES:
+                reps = 40
+                for r in range(4):
+                    _lib.check(L.jq_linear_f32(pools[si][r % POOL_COPIES]._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), 1, sp))
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize(device)
+                a.record(stream)
+                for r in range(reps):
+                    _lib.check(L.jq_linear_f32(pools[si][r % POOL_COPIES]._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), 1, sp))
+                b.record(stream)
+                torch.cuda.synchronize(device)
+                us = a.elapsed_time(b) * 1e3 / reps
+                per_shape["%dx%d_m%d" % (n, k, m)] = {"us": round(us, 3), "GBps": round(algorithmic_bytes(n, k, m) / us / 1e3, 1)}
+
+    # end to end through the C ABI with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if world == 1:
+        hx = {key: torch.randn(key[1], key[0], generator=torch.Generator().manual_seed(5)).pin_memory() for key in xs}
+        hy = {key: torch.empty(key[2], key[0]).pin_memory() for key in ys}
+
+        def host_step(i):
+            for si, (n, k) in enumerate(SHAPES):
+                for mi, m in enumerate(BATCHES):
+                    w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
+                    _lib.check(L.jq_linear_f32(w._handle(), hx[(k, m)].data_ptr(), m, None, hy[(n, k, m)].data_ptr(), _lib.JQ_MEM_HOST, None))
+
+        for i in range(args.warmup):
+            host_step(i)
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            host_step(args.warmup + i)
+        torch.cuda.synchronize(device)
+        dt = (time.perf_counter() - t0) / args.steps
+        e2e = {"value": round(step_bytes() / dt / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": int(sum(4 * m * k for _, k in SHAPES for m in BATCHES)),
+               "d2h_bytes_per_step": int(sum(4 * m * n for n, _ in SHAPES for m in BATCHES)),
+               "ms_per_step": round(dt * 1e3, 4)}
+
+    cpu = cpu_baseline_leg(threads=1, fraction=1, steps=2) if (rank == 0 and world == 1 and not args.no_cpu) else None
+
+    if rank == 0:
+        peak, which = measured_peaks()
+        n_launch = len(SHAPES) * len(BATCHES)
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; 8 launches per step",
+                       "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32",
+                       "l2": "every launch reads a different copy from a pool of %d copies per shape (%.0f MB > 126 MB L2)"
+                             % (POOL_COPIES, POOL_COPIES * sum(n * k for n, k in SHAPES) * BYTES_PER_WEIGHT / 1e6),
+                       "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + NCCL all-gather per launch" % world},
+            "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s", "frac": round(value / world / peak, 4),
+                         "traffic": None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
+                         "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
+                         "per_shape": per_shape},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_leg(threads, fraction, steps=1, warmup=0):
+    """Times the CPU port of the reference's host loops on the sweep (rows [0, N/fraction) of every shape)."""
+    import numpy as np
+    import torch
+    from jitnn_b200 import synth
+    from oracle import oracle
+    work = []
+    total_bytes = 0.0
+    for si, (n, k) in enumerate(SHAPES):
+        rows = max(1, n // fraction)
+        g = torch.Generator().manual_seed(1234 + 17 * si)
+        raw = synth.quantize_q4_k(torch.randn(rows, k, generator=g) * 0.02).numpy()
+        for m in BATCHES:
+            x = torch.randn(m, k, generator=g).numpy()
+            work.append((raw, x, rows))
+            total_bytes += algorithmic_bytes(rows, k, m)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        for raw, x, rows in work:
+            oracle.linear(TYPE, raw, x, None, n=rows, threads=threads)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    dt = sum(times) / len(times)
+    return {"value": round(total_bytes / dt / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "%d step(s) of the sweep on rows [0, N/%d) of every shape, %.2f s per step" % (steps, fraction, dt),
+            "seconds_per_step": round(dt, 3)}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path: its scalar host loops (ops/Gguf.java:187-205),
+    restated in C (oracle/) because no JVM exists here, on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    fraction = max(1, 8 // threads)
+    cpu = cpu_baseline_leg(threads=threads, fraction=fraction, steps=args.steps, warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(cpu["seconds_per_step"] * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; rows [0, N/%d) of each" % fraction,
+                   "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32"},
+        "cpu_baseline": cpu, "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,161 @@
+/*
+ * jitnn_b200 — C ABI of the B200 (sm_100a) quantised linear operator for GGUF block formats.
+ *
+ * This is the boundary a jitNN backend binds through the Panama FFM API (java.lang.foreign), in the
+ * style of the reference's own native binding jitnn-core/.../cpu/Blas.java:85-104,177-201: plain C
+ * symbols, scalars and pointers only, no callbacks, no structs by value. Every function returns
+ * JQ_OK (0) or a negative JQ_ERR_* code; the message of the last failure on the calling thread is
+ * available from jq_last_error(). Nothing here aborts the process or throws.
+ *
+ * Citations name the reference interface each entry point stands in for; paths are relative to
+ * jitnn-core/src/main/java/ai/beestream/jitnn/ unless they start with another module's name.
+ */
+#ifndef JITNN_B200_H
+#define JITNN_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define JQ_API __attribute__((visibility("default")))
+#else
+#define JQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+#define JQ_OK 0
+#define JQ_ERR_INVALID (-1)     /* shape, type, alignment or handle misuse (Java: IllegalArgumentException) */
+#define JQ_ERR_OOM (-2)         /* device or pinned-host allocation failed */
+#define JQ_ERR_CUDA (-3)        /* a CUDA runtime call or kernel launch failed (Java: JitnnException) */
+#define JQ_ERR_NCCL (-4)        /* reserved for collective failures reported by the host side */
+#define JQ_ERR_TIMEOUT (-5)     /* a bounded device-side wait gave up */
+#define JQ_ERR_UNSUPPORTED (-6) /* the format has no kernel for this operation */
+
+/* ---- weight element types: ggml type ids (jitnn-gguf/.../gguf/GgmlType.java:27-51) ---------- */
+#define JQ_TYPE_Q4_0 2
+#define JQ_TYPE_Q4_1 3
+#define JQ_TYPE_Q5_0 6
+#define JQ_TYPE_Q5_1 7
+#define JQ_TYPE_Q8_0 8
+#define JQ_TYPE_Q2_K 10
+#define JQ_TYPE_Q3_K 11
+#define JQ_TYPE_Q4_K 12
+#define JQ_TYPE_Q5_K 13
+#define JQ_TYPE_Q6_K 14
+
+/* ---- where a data pointer lives ------------------------------------------------------------ */
+#define JQ_MEM_HOST 0   /* host memory (pageable or pinned); the call copies in, computes, copies out and
+                           returns when y is complete */
+#define JQ_MEM_DEVICE 1 /* device memory of the weight's GPU; the call only enqueues work on `stream` */
+
+/* ---- device layouts of an uploaded weight --------------------------------------------------- */
+#define JQ_LAYOUT_AUTO 0 /* the library's layout for the format: Q4_K and Q5_K blocks stay verbatim (their
+                            144/176-byte blocks are 16-byte multiples); Q8_0, Q4_0, Q4_1 and Q6_K are split
+                            into a 16-byte aligned plane of quants and a plane of fp16 scales */
+
+typedef struct jq_weight jq_weight; /* opaque; immutable after upload, safe to share between threads */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+JQ_API int jq_version(void);
+
+/* Message of the last error on the calling thread ("" if none). The pointer stays valid until the
+ * next failing call on the same thread. (Java side: the message of the exception to throw.) */
+JQ_API const char* jq_last_error(void);
+
+/* Values per block and bytes per block of a format, 0 for an unknown type (DType.java:75-98). */
+JQ_API int jq_block_values(int type);
+JQ_API int jq_block_bytes(int type);
+
+/* Number of CUDA devices visible to the process. */
+JQ_API int jq_device_count(int* count);
+
+/*
+ * Uploads the raw blocks of a [n, k] weight (row r occupies bytes [r*k/QK*B, (r+1)*k/QK*B), exactly
+ * as a GGUF file stores it) to `device`. Stands in for Tensor.quantized(DType, byte[], dims...)
+ * (Tensor.java:249-278) plus the first-use upload of a persistent tensor
+ * (engine/PlanCompiler.java:209,240). Validates k % QK == 0 and nbytes == n*k/QK*B as
+ * Tensor.persistent does. The blocks are copied during the call; the caller's buffer (for example a
+ * memory-mapped GGUF region, jitnn-gguf/.../GgufFile.java:382-402) is not retained.
+ */
+JQ_API int jq_weight_upload(int device, int type, const void* host_blocks, int64_t nbytes, int64_t n, int64_t k,
+                     int layout, jq_weight** out);
+
+/*
+ * As jq_weight_upload for the output rows [row_begin, row_end) only: the shard one GPU holds when a
+ * linear is split by output rows. `host_blocks`/`nbytes` still describe the whole [n, k] weight. The
+ * resulting handle is a [row_end - row_begin, k] weight. (No counterpart in the reference, which
+ * never shards a linear; the collective that completes it mirrors dist/Collective.java:64-65.)
+ */
+JQ_API int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t nbytes, int64_t n, int64_t k,
+                          int64_t row_begin, int64_t row_end, int layout, jq_weight** out);
+
+/* Releases the device memory of a weight (Tensor.release/close, Tensor.java:362-370). NULL is a no-op. */
+JQ_API int jq_weight_free(jq_weight* w);
+
+/* info[0..7] = n, k, type, layout, device, bytes held on the device, QK, block bytes. */
+JQ_API int jq_weight_info(const jq_weight* w, int64_t info[8]);
+
+/* Copies the weight back to the host in its original GGUF block bytes (n*k/QK*B of them): undoes any
+ * device repacking. For tests and for saving what was loaded. */
+JQ_API int jq_weight_download(const jq_weight* w, void* host_blocks, int64_t nbytes);
+
+/*
+ * dst[n*k] = dequantised weight in float32, bit-exact with the reference's per-element decode
+ * (kernels/GgufKernels.java:85-223 `value`; Q8_0: ops/Quant.java:137-144). Stands in for
+ * Gguf.dequantize / Quant.dequantize (ops/Gguf.java:68-73, ops/Quant.java:52-60).
+ */
+JQ_API int jq_dequantize(const jq_weight* w, float* dst, int dst_mem, void* stream);
+
+/*
+ * y[m, n] = x[m, k] * W^T (+ bias[n]), float32 activations and outputs, FP32 accumulation; the
+ * activations are never quantised. Stands in for Gguf.linear(x, w, bias) (ops/Gguf.java:76-98) and
+ * Quant.linear / F.linearQ8 (ops/Quant.java:66-80): any m >= 0 (leading axes of x flattened by the
+ * caller as ops/Gguf.java:86-93 does), bias may be NULL. Rows are dispatched like the reference
+ * dispatches them (ops/Gguf.java:90): m <= 16 to the fused dequantise-GEMV kernels, larger m in
+ * groups of 16 rows through the same kernels unless the tensor-core prefill path is selected with
+ * jq_set_option. `mem` says where x, bias and y live (all three alike); with JQ_MEM_DEVICE they must
+ * be 16-byte aligned and `stream` is the CUDA stream (cudaStream_t, NULL = default stream).
+ */
+JQ_API int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, int mem,
+                  void* stream);
+
+/*
+ * Prefill form: x is bfloat16 [m, k] (raw 16-bit patterns), y float32 [m, n]; dequantised weights are
+ * rounded to bfloat16 and multiplied on the tensor cores with FP32 accumulation. Semantics of the
+ * reference's prefill composition dequantize + matmul (ops/Gguf.java:94-95,
+ * ops/MatMul.java:597-625) at bfloat16 operand precision.
+ */
+JQ_API int jq_linear_bf16(const jq_weight* w, const uint16_t* x_bf16, int64_t m, const float* bias, float* y, int mem,
+                   void* stream);
+
+/*
+ * blocks_out[count/32*34] = Q8_0 blocks of x[count] (count % 32 == 0), following the reference's host
+ * quantiser ops/Quant.java:102-118 (F.quantizeQ8): d = (float)(max|x| / 127.0) stored as fp16, q =
+ * x / d rounded half away from zero using the unrounded float d, clamped to [-127, 127].
+ */
+JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blocks_out, int mem, void* stream);
+
+/*
+ * Named integer options, the counterpart of the reference's jitnn.* configuration keys
+ * (JitnnConfig.java:423-424 for this path). Known names:
+ *   "prefill_min_rows"  rows of x from which jq_linear_f32 rounds x to bfloat16 and uses the
+ *                       tensor-core prefill kernel (default 0 = never: FP32 results for every m).
+ */
+JQ_API int jq_set_option(const char* name, int64_t value);
+JQ_API int jq_get_option(const char* name, int64_t* value);
+
+/* Pinned host memory for activations and results (faster and truly asynchronous copies). */
+JQ_API int jq_host_alloc(void** ptr, int64_t nbytes);
+JQ_API int jq_host_free(void* ptr);
+
+/* Number of kernels this library has launched from the calling process since load (all threads). */
+JQ_API int64_t jq_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* JITNN_B200_H */

@@ -1,0 +1,78 @@
+"""ctypes binding of ``libjitnn_b200.so`` (the C ABI declared in ``include/jitnn_b200.h``).
+
+The library is the product: there is no Python or CPU fallback. ``load()`` raises if the shared
+object has not been built (``python -m jitnn_b200.build``).
+"""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libjitnn_b200.so")
+
+JQ_OK = 0
+JQ_ERR_INVALID, JQ_ERR_OOM, JQ_ERR_CUDA, JQ_ERR_NCCL, JQ_ERR_TIMEOUT, JQ_ERR_UNSUPPORTED = -1, -2, -3, -4, -5, -6
+JQ_MEM_HOST, JQ_MEM_DEVICE = 0, 1
+JQ_LAYOUT_AUTO = 0
+
+c_i64, c_int, vp = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
+
+# name -> (restype, argtypes); every symbol the header declares
+SIGNATURES = {
+    "jq_version": (c_int, []),
+    "jq_last_error": (ctypes.c_char_p, []),
+    "jq_block_values": (c_int, [c_int]),
+    "jq_block_bytes": (c_int, [c_int]),
+    "jq_device_count": (c_int, [ctypes.POINTER(c_int)]),
+    "jq_weight_upload": (c_int, [c_int, c_int, vp, c_i64, c_i64, c_i64, c_int, ctypes.POINTER(vp)]),
+    "jq_weight_upload_rows": (c_int, [c_int, c_int, vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_int, ctypes.POINTER(vp)]),
+    "jq_weight_free": (c_int, [vp]),
+    "jq_weight_info": (c_int, [vp, ctypes.POINTER(c_i64)]),
+    "jq_weight_download": (c_int, [vp, vp, c_i64]),
+    "jq_dequantize": (c_int, [vp, vp, c_int, vp]),
+    "jq_linear_f32": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
+    "jq_linear_bf16": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
+    "jq_quantize_q8_0": (c_int, [c_int, vp, c_i64, vp, c_int, vp]),
+    "jq_set_option": (c_int, [ctypes.c_char_p, c_i64]),
+    "jq_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_i64)]),
+    "jq_host_alloc": (c_int, [ctypes.POINTER(vp), c_i64]),
+    "jq_host_free": (c_int, [vp]),
+    "jq_launch_count": (c_i64, []),
+}
+
+_lib = None
+
+
+class JitnnError(RuntimeError):
+    """A runtime failure inside the library (the reference wraps these in JitnnException)."""
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("libjitnn_b200.so is not built: run `python -m jitnn_b200.build` (needs nvcc); there is no fallback path")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return load().jq_last_error().decode("utf-8", "replace")
+
+
+def check(rc):
+    """Maps a status code to the exception the reference's Java API would throw."""
+    if rc == JQ_OK:
+        return
+    msg = last_error()
+    if rc in (JQ_ERR_INVALID, JQ_ERR_UNSUPPORTED):
+        raise ValueError(msg)  # IllegalArgumentException
+    if rc == JQ_ERR_OOM:
+        raise MemoryError(msg)
+    if rc == JQ_ERR_TIMEOUT:
+        raise TimeoutError(msg)
+    raise JitnnError(msg)

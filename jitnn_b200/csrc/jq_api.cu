@@ -1,0 +1,506 @@
+// The C ABI (include/jitnn_b200.h): argument validation, weight upload, dispatch, host staging.
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "jq_common.cuh"
+
+namespace jq {
+
+std::atomic<int64_t> g_launches{0};
+static thread_local std::string t_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    t_error = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    int code = e == cudaErrorMemoryAllocation ? JQ_ERR_OOM : JQ_ERR_CUDA;
+    return fail(code, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+int check_launch(const char* kernel) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return fail(JQ_ERR_CUDA, "launch of %s failed: %s", kernel, cudaGetErrorString(e));
+    }
+    return JQ_OK;
+}
+
+// Makes `device` current for the scope and restores the caller's device afterwards.
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) {
+            prev = -1;
+        }
+        if (prev != device) {
+            ok = cudaSetDevice(device) == cudaSuccess;
+        } else {
+            prev = -1;
+        }
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) {
+            cudaSetDevice(prev);
+        }
+    }
+};
+
+// Per-thread, per-device staging for calls whose data lives on the host: a device buffer that grows on
+// demand and a private stream, so that concurrent callers never share scratch.
+struct Staging {
+    uint8_t* dev = nullptr;
+    size_t bytes = 0;
+    cudaStream_t stream = nullptr;
+};
+
+static thread_local std::vector<Staging> t_staging;
+
+static int staging_for(int device, size_t bytes, Staging** out) {
+    if ((size_t)device >= t_staging.size()) {
+        t_staging.resize(device + 1);
+    }
+    Staging& st = t_staging[device];
+    if (st.stream == nullptr) {
+        JQ_CUDA(cudaStreamCreateWithFlags(&st.stream, cudaStreamNonBlocking));
+    }
+    if (st.bytes < bytes) {
+        if (st.dev != nullptr) {
+            JQ_CUDA(cudaStreamSynchronize(st.stream));
+            JQ_CUDA(cudaFree(st.dev));
+            st.dev = nullptr;
+            st.bytes = 0;
+        }
+        size_t want = bytes + bytes / 4 + 4096;
+        JQ_CUDA(cudaMalloc(&st.dev, want));
+        st.bytes = want;
+    }
+    *out = &st;
+    return JQ_OK;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static int check_weight(const jq_weight* w, const char* who) {
+    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC) {
+        return fail(JQ_ERR_INVALID, "%s: not a live weight handle", who);
+    }
+    return JQ_OK;
+}
+
+static View view_of(const jq_weight* w) { return View{w->q, w->aux, w->n, w->k, w->type}; }
+
+static const char* type_name(int type) {
+    switch (type) {
+        case JQ_TYPE_Q8_0: return "Q8_0";
+        case JQ_TYPE_Q4_0: return "Q4_0";
+        case JQ_TYPE_Q4_1: return "Q4_1";
+        case JQ_TYPE_Q4_K: return "Q4_K";
+        case JQ_TYPE_Q5_K: return "Q5_K";
+        case JQ_TYPE_Q6_K: return "Q6_K";
+        case JQ_TYPE_Q5_0: return "Q5_0";
+        case JQ_TYPE_Q5_1: return "Q5_1";
+        case JQ_TYPE_Q2_K: return "Q2_K";
+        case JQ_TYPE_Q3_K: return "Q3_K";
+        default: return "?";
+    }
+}
+
+// ---- options ------------------------------------------------------------------------------------
+static std::atomic<int64_t> g_prefill_min_rows{0};
+
+// ---- linear on device pointers --------------------------------------------------------------------
+static int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
+    View v = view_of(w);
+    for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        int rows = (int)(m - m0 < 16 ? m - m0 : 16);
+        int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
+        if (rc != JQ_OK) {
+            return rc;
+        }
+    }
+    return JQ_OK;
+}
+
+}  // namespace jq
+
+using namespace jq;
+
+extern "C" {
+
+int jq_version(void) { return 100; }
+
+const char* jq_last_error(void) { return t_error.c_str(); }
+
+int jq_block_values(int type) { return block_values(type); }
+
+int jq_block_bytes(int type) { return block_bytes(type); }
+
+int jq_device_count(int* count) {
+    if (count == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_device_count: null result pointer");
+    }
+    JQ_CUDA(cudaGetDeviceCount(count));
+    return JQ_OK;
+}
+
+int64_t jq_launch_count(void) { return g_launches.load(); }
+
+int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t nbytes, int64_t n, int64_t k, int64_t row_begin,
+                          int64_t row_end, int layout, jq_weight** out) {
+    if (out == nullptr) {
+        return fail(JQ_ERR_INVALID, "weight upload: null result pointer");
+    }
+    *out = nullptr;
+    int qk = block_values(type), bb = block_bytes(type);
+    if (qk == 0) {
+        return fail(JQ_ERR_INVALID, "weight upload: type id %d is not a GGUF block format this library loads", type);
+    }
+    if (n < 0 || k < 0 || k % qk != 0) {
+        return fail(JQ_ERR_INVALID, "%s weight of shape [%lld, %lld]: last axis not a multiple of its block of %d", type_name(type),
+                    (long long)n, (long long)k, qk);
+    }
+    if (n * k >= ((int64_t)1 << 31)) {
+        return fail(JQ_ERR_INVALID, "%s weight of shape [%lld, %lld]: more than 2^31-1 elements", type_name(type), (long long)n, (long long)k);
+    }
+    int64_t row_bytes = k / qk * bb;
+    if (nbytes != n * row_bytes) {
+        return fail(JQ_ERR_INVALID, "%s tensor of shape [%lld, %lld] needs %lld bytes, got %lld", type_name(type), (long long)n, (long long)k,
+                    (long long)(n * row_bytes), (long long)nbytes);
+    }
+    if (row_begin < 0 || row_end < row_begin || row_end > n) {
+        return fail(JQ_ERR_INVALID, "weight upload: rows [%lld, %lld) outside [0, %lld)", (long long)row_begin, (long long)row_end, (long long)n);
+    }
+    if (layout != JQ_LAYOUT_AUTO) {
+        return fail(JQ_ERR_INVALID, "weight upload: unknown layout %d", layout);
+    }
+    if (host_blocks == nullptr && nbytes > 0) {
+        return fail(JQ_ERR_INVALID, "weight upload: null blocks");
+    }
+    int count = 0;
+    JQ_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) {
+        return fail(JQ_ERR_INVALID, "weight upload: device %d of %d", device, count);
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail(JQ_ERR_CUDA, "weight upload: cannot select device %d", device);
+    }
+    int64_t rows = row_end - row_begin;
+    int64_t blocks = rows * (k / qk);
+    const uint8_t* src = (const uint8_t*)host_blocks + row_begin * row_bytes;
+    int64_t src_bytes = rows * row_bytes;
+
+    jq_weight* w = new (std::nothrow) jq_weight();
+    if (w == nullptr) {
+        return fail(JQ_ERR_OOM, "weight upload: out of host memory");
+    }
+    w->magic = JQ_WEIGHT_MAGIC;
+    w->device = device;
+    w->type = type;
+    w->layout = layout;
+    w->n = rows;
+    w->k = k;
+    w->q_bytes = blocks * plane_q_bytes(type);
+    w->aux_bytes = blocks * plane_aux_bytes(type);
+    w->q = nullptr;
+    w->aux = nullptr;
+
+    int rc = JQ_OK;
+    uint8_t* tmp = nullptr;
+    cudaError_t e = cudaMalloc(&w->q, (size_t)(w->q_bytes > 0 ? w->q_bytes : 16));
+    if (e == cudaSuccess && w->aux_bytes > 0) {
+        e = cudaMalloc(&w->aux, (size_t)w->aux_bytes);
+    }
+    if (e != cudaSuccess) {
+        rc = cuda_fail(e, "cudaMalloc(weight)");
+    }
+    if (rc == JQ_OK && src_bytes > 0) {
+        if (plane_aux_bytes(type) == 0) {
+            e = cudaMemcpy(w->q, src, (size_t)src_bytes, cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) {
+                rc = cuda_fail(e, "cudaMemcpy(weight)");
+            }
+        } else {
+            e = cudaMalloc(&tmp, (size_t)src_bytes);
+            if (e == cudaSuccess) {
+                e = cudaMemcpy(tmp, src, (size_t)src_bytes, cudaMemcpyHostToDevice);
+            }
+            if (e != cudaSuccess) {
+                rc = cuda_fail(e, "staging the verbatim blocks");
+            } else {
+                rc = launch_repack(type, tmp, w->q, w->aux, blocks, nullptr);
+                if (rc == JQ_OK) {
+                    e = cudaDeviceSynchronize();
+                    if (e != cudaSuccess) {
+                        rc = cuda_fail(e, "repack");
+                    }
+                }
+            }
+        }
+    }
+    if (tmp != nullptr) {
+        cudaFree(tmp);
+    }
+    if (rc != JQ_OK) {
+        cudaFree(w->q);
+        cudaFree(w->aux);
+        w->magic = 0;
+        delete w;
+        return rc;
+    }
+    *out = w;
+    return JQ_OK;
+}
+
+int jq_weight_upload(int device, int type, const void* host_blocks, int64_t nbytes, int64_t n, int64_t k, int layout, jq_weight** out) {
+    return jq_weight_upload_rows(device, type, host_blocks, nbytes, n, k, 0, n < 0 ? 0 : n, layout, out);
+}
+
+int jq_weight_free(jq_weight* w) {
+    if (w == nullptr) {
+        return JQ_OK;
+    }
+    int rc = check_weight(w, "jq_weight_free");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    DeviceGuard guard(w->device);
+    cudaFree(w->q);
+    cudaFree(w->aux);
+    w->magic = 0;
+    delete w;
+    return JQ_OK;
+}
+
+int jq_weight_info(const jq_weight* w, int64_t info[8]) {
+    int rc = check_weight(w, "jq_weight_info");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (info == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_weight_info: null result pointer");
+    }
+    info[0] = w->n;
+    info[1] = w->k;
+    info[2] = w->type;
+    info[3] = w->layout;
+    info[4] = w->device;
+    info[5] = w->q_bytes + w->aux_bytes;
+    info[6] = block_values(w->type);
+    info[7] = block_bytes(w->type);
+    return JQ_OK;
+}
+
+int jq_weight_download(const jq_weight* w, void* host_blocks, int64_t nbytes) {
+    int rc = check_weight(w, "jq_weight_download");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    int64_t blocks = w->n * (w->k / block_values(w->type));
+    int64_t want = blocks * block_bytes(w->type);
+    if (nbytes != want || (host_blocks == nullptr && want > 0)) {
+        return fail(JQ_ERR_INVALID, "jq_weight_download: needs a buffer of %lld bytes, got %lld", (long long)want, (long long)nbytes);
+    }
+    if (want == 0) {
+        return JQ_OK;
+    }
+    DeviceGuard guard(w->device);
+    if (plane_aux_bytes(w->type) == 0) {
+        JQ_CUDA(cudaMemcpy(host_blocks, w->q, (size_t)want, cudaMemcpyDeviceToHost));
+        return JQ_OK;
+    }
+    uint8_t* tmp = nullptr;
+    JQ_CUDA(cudaMalloc(&tmp, (size_t)want));
+    rc = launch_unpack(w->type, w->q, w->aux, tmp, blocks, nullptr);
+    if (rc == JQ_OK) {
+        cudaError_t e = cudaMemcpy(host_blocks, tmp, (size_t)want, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) {
+            rc = cuda_fail(e, "cudaMemcpy(download)");
+        }
+    }
+    cudaFree(tmp);
+    return rc;
+}
+
+int jq_dequantize(const jq_weight* w, float* dst, int dst_mem, void* stream) {
+    int rc = check_weight(w, "jq_dequantize");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    int64_t count = w->n * w->k;
+    if (count == 0) {
+        return JQ_OK;
+    }
+    if (dst == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_dequantize: null destination");
+    }
+    DeviceGuard guard(w->device);
+    if (dst_mem == JQ_MEM_DEVICE) {
+        if (((uintptr_t)dst & 15) != 0) {
+            return fail(JQ_ERR_INVALID, "jq_dequantize: device destination must be 16-byte aligned");
+        }
+        return launch_dequantize(view_of(w), dst, (cudaStream_t)stream);
+    }
+    if (dst_mem != JQ_MEM_HOST) {
+        return fail(JQ_ERR_INVALID, "jq_dequantize: unknown memory kind %d", dst_mem);
+    }
+    Staging* st;
+    rc = staging_for(w->device, (size_t)count * 4, &st);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    rc = launch_dequantize(view_of(w), (float*)st->dev, st->stream);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    JQ_CUDA(cudaMemcpyAsync(dst, st->dev, (size_t)count * 4, cudaMemcpyDeviceToHost, st->stream));
+    JQ_CUDA(cudaStreamSynchronize(st->stream));
+    return JQ_OK;
+}
+
+int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, int mem, void* stream) {
+    int rc = check_weight(w, "jq_linear_f32");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (!has_linear_kernel(w->type)) {
+        return fail(JQ_ERR_UNSUPPORTED, "%s linear: the format is dequantise-only", type_name(w->type));
+    }
+    if (m < 0) {
+        return fail(JQ_ERR_INVALID, "%s linear: input of %lld rows and weight [%lld, %lld]", type_name(w->type), (long long)m, (long long)w->n,
+                    (long long)w->k);
+    }
+    if (m == 0 || w->n == 0) {
+        return JQ_OK;
+    }
+    if (x == nullptr || y == nullptr) {
+        return fail(JQ_ERR_INVALID, "%s linear: null input or output", type_name(w->type));
+    }
+    DeviceGuard guard(w->device);
+    if (mem == JQ_MEM_DEVICE) {
+        if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+            return fail(JQ_ERR_INVALID, "%s linear: device pointers must be 16-byte aligned", type_name(w->type));
+        }
+        return linear_device(w, x, m, bias, y, (cudaStream_t)stream);
+    }
+    if (mem != JQ_MEM_HOST) {
+        return fail(JQ_ERR_INVALID, "%s linear: unknown memory kind %d", type_name(w->type), mem);
+    }
+    size_t xb = align256((size_t)m * w->k * 4), bb = align256((size_t)w->n * 4), yb = align256((size_t)m * w->n * 4);
+    Staging* st;
+    rc = staging_for(w->device, xb + bb + yb, &st);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    float* dx = (float*)st->dev;
+    float* db = (float*)(st->dev + xb);
+    float* dy = (float*)(st->dev + xb + bb);
+    JQ_CUDA(cudaMemcpyAsync(dx, x, (size_t)m * w->k * 4, cudaMemcpyHostToDevice, st->stream));
+    if (bias != nullptr) {
+        JQ_CUDA(cudaMemcpyAsync(db, bias, (size_t)w->n * 4, cudaMemcpyHostToDevice, st->stream));
+    }
+    rc = linear_device(w, dx, m, bias != nullptr ? db : nullptr, dy, st->stream);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    JQ_CUDA(cudaMemcpyAsync(y, dy, (size_t)m * w->n * 4, cudaMemcpyDeviceToHost, st->stream));
+    JQ_CUDA(cudaStreamSynchronize(st->stream));
+    return JQ_OK;
+}
+
+int jq_linear_bf16(const jq_weight* w, const uint16_t*, int64_t, const float*, float*, int, void*) {
+    int rc = check_weight(w, "jq_linear_bf16");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    return fail(JQ_ERR_UNSUPPORTED, "jq_linear_bf16: the tensor-core prefill kernel is not built into this library");
+}
+
+int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blocks_out, int mem, void* stream) {
+    if (count < 0 || count % 32 != 0) {
+        return fail(JQ_ERR_INVALID, "Q8_0 needs a last axis that is a multiple of 32, got %lld values", (long long)count);
+    }
+    if (count == 0) {
+        return JQ_OK;
+    }
+    if (x == nullptr || blocks_out == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_quantize_q8_0: null input or output");
+    }
+    int devices = 0;
+    JQ_CUDA(cudaGetDeviceCount(&devices));
+    if (device < 0 || device >= devices) {
+        return fail(JQ_ERR_INVALID, "jq_quantize_q8_0: device %d of %d", device, devices);
+    }
+    DeviceGuard guard(device);
+    int64_t blocks = count / 32;
+    if (mem == JQ_MEM_DEVICE) {
+        return launch_quantize_q8_0(x, blocks, (uint8_t*)blocks_out, (cudaStream_t)stream);
+    }
+    if (mem != JQ_MEM_HOST) {
+        return fail(JQ_ERR_INVALID, "jq_quantize_q8_0: unknown memory kind %d", mem);
+    }
+    size_t xb = align256((size_t)count * 4), ob = (size_t)blocks * 34;
+    Staging* st;
+    int rc = staging_for(device, xb + ob, &st);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    JQ_CUDA(cudaMemcpyAsync(st->dev, x, (size_t)count * 4, cudaMemcpyHostToDevice, st->stream));
+    rc = launch_quantize_q8_0((const float*)st->dev, blocks, st->dev + xb, st->stream);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    JQ_CUDA(cudaMemcpyAsync(blocks_out, st->dev + xb, ob, cudaMemcpyDeviceToHost, st->stream));
+    JQ_CUDA(cudaStreamSynchronize(st->stream));
+    return JQ_OK;
+}
+
+int jq_set_option(const char* name, int64_t value) {
+    if (name != nullptr && strcmp(name, "prefill_min_rows") == 0) {
+        if (value < 0) {
+            return fail(JQ_ERR_INVALID, "option prefill_min_rows: %lld is negative", (long long)value);
+        }
+        g_prefill_min_rows.store(value);
+        return JQ_OK;
+    }
+    return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);
+}
+
+int jq_get_option(const char* name, int64_t* value) {
+    if (name != nullptr && value != nullptr && strcmp(name, "prefill_min_rows") == 0) {
+        *value = g_prefill_min_rows.load();
+        return JQ_OK;
+    }
+    return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);
+}
+
+int jq_host_alloc(void** ptr, int64_t nbytes) {
+    if (ptr == nullptr || nbytes < 0) {
+        return fail(JQ_ERR_INVALID, "jq_host_alloc: bad arguments");
+    }
+    *ptr = nullptr;
+    cudaError_t e = cudaMallocHost(ptr, (size_t)(nbytes > 0 ? nbytes : 1));
+    if (e != cudaSuccess) {
+        return fail(JQ_ERR_OOM, "jq_host_alloc(%lld): %s", (long long)nbytes, cudaGetErrorString(e));
+    }
+    return JQ_OK;
+}
+
+int jq_host_free(void* ptr) {
+    if (ptr != nullptr) {
+        JQ_CUDA(cudaFreeHost(ptr));
+    }
+    return JQ_OK;
+}
+
+}  // extern "C"

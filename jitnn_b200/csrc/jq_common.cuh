@@ -1,0 +1,117 @@
+// Shared declarations of the library: error reporting, the weight handle, launch bookkeeping.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/jitnn_b200.h"
+
+namespace jq {
+
+// ---- error reporting (thread-local message behind jq_last_error) ------------------------------
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define JQ_CUDA(call)                                   \
+    do {                                                \
+        cudaError_t e_ = (call);                        \
+        if (e_ != cudaSuccess) {                        \
+            return ::jq::cuda_fail(e_, #call);          \
+        }                                               \
+    } while (0)
+
+extern std::atomic<int64_t> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Checks the launch that was just issued.
+int check_launch(const char* kernel);
+
+// ---- block geometry (DType.java:75-98 of the reference) ---------------------------------------
+inline int block_values(int type) {
+    switch (type) {
+        case JQ_TYPE_Q8_0: case JQ_TYPE_Q4_0: case JQ_TYPE_Q4_1: case JQ_TYPE_Q5_0: case JQ_TYPE_Q5_1: return 32;
+        case JQ_TYPE_Q4_K: case JQ_TYPE_Q5_K: case JQ_TYPE_Q6_K: case JQ_TYPE_Q2_K: case JQ_TYPE_Q3_K: return 256;
+        default: return 0;
+    }
+}
+
+inline int block_bytes(int type) {
+    switch (type) {
+        case JQ_TYPE_Q8_0: return 34;
+        case JQ_TYPE_Q4_0: return 18;
+        case JQ_TYPE_Q4_1: return 20;
+        case JQ_TYPE_Q4_K: return 144;
+        case JQ_TYPE_Q5_K: return 176;
+        case JQ_TYPE_Q6_K: return 210;
+        case JQ_TYPE_Q5_0: return 22;
+        case JQ_TYPE_Q5_1: return 24;
+        case JQ_TYPE_Q2_K: return 84;
+        case JQ_TYPE_Q3_K: return 110;
+        default: return 0;
+    }
+}
+
+// Bytes per block of the quant plane and of the scale plane in the device layout. Formats whose
+// blocks are 16-byte multiples (Q4_K, Q5_K) and the dequantise-only formats stay verbatim (aux = 0).
+inline int plane_q_bytes(int type) {
+    switch (type) {
+        case JQ_TYPE_Q8_0: return 32;
+        case JQ_TYPE_Q4_0: return 16;
+        case JQ_TYPE_Q4_1: return 16;
+        case JQ_TYPE_Q6_K: return 208;
+        default: return block_bytes(type);
+    }
+}
+
+inline int plane_aux_bytes(int type) {
+    switch (type) {
+        case JQ_TYPE_Q8_0: return 2;
+        case JQ_TYPE_Q4_0: return 2;
+        case JQ_TYPE_Q4_1: return 4;
+        case JQ_TYPE_Q6_K: return 2;
+        default: return 0;
+    }
+}
+
+inline bool has_linear_kernel(int type) {
+    return type == JQ_TYPE_Q8_0 || type == JQ_TYPE_Q4_0 || type == JQ_TYPE_Q4_1 || type == JQ_TYPE_Q4_K ||
+           type == JQ_TYPE_Q5_K || type == JQ_TYPE_Q6_K;
+}
+
+// What the kernels see of a weight.
+struct View {
+    const uint8_t* q;    // quant plane (or verbatim blocks), 256-byte aligned
+    const uint8_t* aux;  // scale plane, or nullptr
+    int64_t n;           // output rows
+    int64_t k;           // input features
+    int type;
+};
+
+// ---- kernel launchers (one translation unit each) ----------------------------------------------
+int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, cudaStream_t s);
+int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, cudaStream_t s);
+int launch_dequantize(const View& v, float* dst, cudaStream_t s);
+int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
+int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
+
+}  // namespace jq
+
+// The opaque handle of the C ABI.
+struct jq_weight {
+    uint32_t magic;
+    int device;
+    int type;
+    int layout;
+    int64_t n;
+    int64_t k;
+    uint8_t* q;
+    uint8_t* aux;
+    int64_t q_bytes;
+    int64_t aux_bytes;
+};
+
+#define JQ_WEIGHT_MAGIC 0x4a515754u
