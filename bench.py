@@ -326,7 +326,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    ap.add_argument("--only", default=None, metavar="NxKxM",
+                    help="restrict the sweep to one shape and batch, e.g. 32000x4096x1 (a small case for profiler captures)")
     args = ap.parse_args()
+    if args.only:
+        n, k, m = (int(v) for v in args.only.lower().split("x"))
+        SHAPES[:] = [(n, k)]
+        BATCHES[:] = [m]
+        args.no_cpu = True
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)

@@ -97,6 +97,11 @@ int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verba
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
 int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
+// Tensor-core GEMV for Q4_K; *handled = false leaves the call to the generic kernel.
+int launch_gemv_q4k_mma(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
+
+// Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
+extern std::atomic<int64_t> g_opt_gemv_generic;
 
 }  // namespace jq
 

@@ -92,6 +92,13 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
     if (v.n == 0) {
         return JQ_OK;
     }
+    if (v.type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+        bool handled = false;
+        int rc = launch_gemv_q4k_mma(v, x, rows, bias, y, s, &handled);
+        if (rc != JQ_OK || handled) {
+            return rc;
+        }
+    }
     switch (v.type) {
         case JQ_TYPE_Q8_0: return by_rows<JQ_TYPE_Q8_0>(v, x, rows, bias, y, s);
         case JQ_TYPE_Q4_0: return by_rows<JQ_TYPE_Q4_0>(v, x, rows, bias, y, s);
