@@ -173,8 +173,9 @@ def run_ours(args):
     # correctness guard: the first rows of the first weight against the CPU oracle (not timed)
     if rank == 0 and world == 1:
         from oracle import oracle
-        xh = xs[(4096, 1)].cpu().numpy()
-        yh = jitnn_b200.Gguf.linear(xs[(4096, 1)], pools[0][0], None).cpu().numpy()
+        x0 = xs[(SHAPES[0][1], BATCHES[0])]
+        xh = x0.cpu().numpy()
+        yh = jitnn_b200.Gguf.linear(x0, pools[0][0], None).cpu().numpy()
         ref = oracle.linear(TYPE, first_raw, xh, None)
         rel = float(np.abs(yh[:, :64] - ref).max() / np.abs(ref).max())
         assert rel <= 1e-3, "GEMV differs from the oracle: %g" % rel

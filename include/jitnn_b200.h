@@ -143,6 +143,8 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  * (JitnnConfig.java:423-424 for this path). Known names:
  *   "prefill_min_rows"  rows of x from which jq_linear_f32 rounds x to bfloat16 and uses the
  *                       tensor-core prefill kernel (default 0 = never: FP32 results for every m).
+ *   "gemv_generic"      non-zero: every decode GEMV runs on the generic CUDA-core kernel (for comparisons).
+ *   "gemv_q4k_fp16"     non-zero: Q4_K keeps the fp16 tensor-core GEMV also for m <= 4 (for comparisons).
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);

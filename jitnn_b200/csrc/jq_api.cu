@@ -118,6 +118,7 @@ static const char* type_name(int type) {
 // ---- options ------------------------------------------------------------------------------------
 static std::atomic<int64_t> g_prefill_min_rows{0};
 std::atomic<int64_t> g_opt_gemv_generic{0};
+std::atomic<int64_t> g_opt_q4k_fp16{0};
 
 // ---- linear on device pointers --------------------------------------------------------------------
 static int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
@@ -218,9 +219,17 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
 
     int rc = JQ_OK;
     uint8_t* tmp = nullptr;
-    cudaError_t e = cudaMalloc(&w->q, (size_t)(w->q_bytes > 0 ? w->q_bytes : 16));
+    // PAD_ROWS rows of zeros follow each plane, so that 16-row tiles may read past the last row
+    const int64_t pad_q = (int64_t)PAD_ROWS * (k / qk) * plane_q_bytes(type), pad_aux = (int64_t)PAD_ROWS * (k / qk) * plane_aux_bytes(type);
+    cudaError_t e = cudaMalloc(&w->q, (size_t)(w->q_bytes + pad_q + 16));
+    if (e == cudaSuccess) {
+        e = cudaMemset(w->q + w->q_bytes, 0, (size_t)(pad_q + 16));
+    }
     if (e == cudaSuccess && w->aux_bytes > 0) {
-        e = cudaMalloc(&w->aux, (size_t)w->aux_bytes);
+        e = cudaMalloc(&w->aux, (size_t)(w->aux_bytes + pad_aux));
+        if (e == cudaSuccess) {
+            e = cudaMemset(w->aux + w->aux_bytes, 0, (size_t)pad_aux);
+        }
     }
     if (e != cudaSuccess) {
         rc = cuda_fail(e, "cudaMalloc(weight)");
@@ -478,6 +487,10 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_gemv_generic.store(value != 0);
         return JQ_OK;
     }
+    if (name != nullptr && strcmp(name, "gemv_q4k_fp16") == 0) {
+        g_opt_q4k_fp16.store(value != 0);
+        return JQ_OK;
+    }
     return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);
 }
 
@@ -488,6 +501,10 @@ int jq_get_option(const char* name, int64_t* value) {
     }
     if (name != nullptr && value != nullptr && strcmp(name, "gemv_generic") == 0) {
         *value = g_opt_gemv_generic.load();
+        return JQ_OK;
+    }
+    if (name != nullptr && value != nullptr && strcmp(name, "gemv_q4k_fp16") == 0) {
+        *value = g_opt_q4k_fp16.load();
         return JQ_OK;
     }
     return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);

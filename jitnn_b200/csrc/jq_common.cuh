@@ -100,8 +100,16 @@ int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStrea
 // Tensor-core GEMV for Q4_K; *handled = false leaves the call to the generic kernel.
 int launch_gemv_q4k_mma(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
 
+// Integer tensor-core GEMV for Q4_K, rows <= 4; needs the 16 padding rows every uploaded weight has.
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
+
+// Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
+constexpr int PAD_ROWS = 16;
+
 // Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_generic;
+// Option "gemv_q4k_fp16": non-zero keeps Q4_K on the fp16 tensor-core kernel for every row count.
+extern std::atomic<int64_t> g_opt_q4k_fp16;
 
 }  // namespace jq
 

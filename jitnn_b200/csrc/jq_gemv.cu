@@ -94,6 +94,12 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
     }
     if (v.type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
         bool handled = false;
+        if (rows <= 4 && g_opt_q4k_fp16.load(std::memory_order_relaxed) == 0) {
+            int rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, &handled);
+            if (rc != JQ_OK || handled) {
+                return rc;
+            }
+        }
         int rc = launch_gemv_q4k_mma(v, x, rows, bias, y, s, &handled);
         if (rc != JQ_OK || handled) {
             return rc;

@@ -19,7 +19,9 @@
 // Work split: a CTA (8 warps) owns 16 output rows at a time and walks the tiles blockIdx.x,
 // blockIdx.x + gridDim.x, ...; warp p takes the super-blocks b = p (mod 8) of those rows. Lane (g, t)
 // (g = lane / 4, t = lane % 4) loads for rows g and g + 8 the 16-byte header and the 32 bytes of nibbles
-// of group t (sub-blocks 2t and 2t+1) with 128-bit loads, one super-block ahead of the arithmetic.
+// of group t (sub-blocks 2t and 2t+1). The weights travel HBM -> shared memory with 16-byte cp.async
+// copies into a private ring of STAGES super-block slots per warp, so each warp keeps STAGES - 1
+// super-blocks (2304 bytes each) in flight without holding registers for them.
 // The activations are converted once per CTA into MMA B-fragment order in shared memory.
 #include <cuda_fp16.h>
 
@@ -32,6 +34,17 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int FRAGS = 17;  // 16 MMAs of quants + 1 MMA of mins per super-block
+constexpr int SLOT_BYTES = 16 * 144;      // one super-block of 16 rows
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(const uint8_t* p) { return *reinterpret_cast<const uint4*>(p); }
 
 __device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 __device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
@@ -42,14 +55,24 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) { return h2u(__floats2half2_rn(lo, hi)); }
+// The first MMA of an accumulator chain: C = 0 (the zero register), so no accumulator needs clearing.
+__device__ __forceinline__ void mma16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 
-// What one lane holds of one super-block of two rows: header and its group's nibbles.
-struct Raw {
-    uint4 h0, h1;    // headers of rows g and g + 8
-    uint4 a0, a1;    // row g: bytes [32t, 32t+32) of qs
-    uint4 b0, b1;    // row g + 8
-};
+// (a & b) | c in one logic instruction.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Two nibbles (selected by mask) placed in the mantissas of a pair of fp16 1024.0: (1024 + q, 1024 + q').
+__device__ __forceinline__ __half2 magic_pair(uint32_t v, uint32_t mask) { return u2h(and_or(v, mask, 0x64006400u)); }
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) { return h2u(__floats2half2_rn(lo, hi)); }
 
 // Per row: fp16 pairs used by the conversion of this lane's two sub-blocks, and d / dmin.
 struct RowScales {
@@ -59,16 +82,35 @@ struct RowScales {
     float d, dmin;
 };
 
-__device__ __forceinline__ RowScales decode_scales(const uint4& h, int t) {
-    // 12 packed bytes: bytes 0-3 low 6 bits sc[0..3], bytes 4-7 low 6 bits m[0..3]; bytes 8-11 low/high
-    // nibbles sc[4..7]/m[4..7] whose top two bits sit in the top two bits of bytes 0-3 / 4-7.
-    uint32_t sc = t < 2 ? (h.y & 0x3f3f3f3fu) : ((h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u));
-    uint32_t mn = t < 2 ? (h.z & 0x3f3f3f3fu) : (((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u));
+// Lane constants of the 6-bit scale unpacking. The 12 packed bytes (three words y, z, w of the header):
+// bytes 0-3 hold sc[0..3] in their low 6 bits, bytes 4-7 hold m[0..3]; bytes 8-11 hold the low nibbles of
+// sc[4..7] (low half) and m[4..7] (high half), whose top two bits are the top two bits of bytes 0-3 / 4-7.
+// Lanes t < 2 need sub-blocks 0..3, lanes t >= 2 sub-blocks 4..7; both cases are written as
+// ((y >> sh) & ma) | (w & mb) so that no lane takes a branch.
+struct LaneConsts {
+    uint32_t sh, ma, mb;            // shift and masks, see above
+    uint32_t sel_lo, sel_hi, sel_m; // byte_perm selectors building fp16 1024+value pairs
+};
+
+__device__ __forceinline__ LaneConsts lane_consts(int t) {
+    LaneConsts c;
+    c.sh = t < 2 ? 0u : 2u;
+    c.ma = t < 2 ? 0x3f3f3f3fu : 0x30303030u;
+    c.mb = t < 2 ? 0u : 0x0f0f0f0fu;
     const uint32_t bi = (2u * (uint32_t)t) & 3u;
+    c.sel_lo = (4u << 12) | (bi << 8) | (4u << 4) | bi;
+    c.sel_hi = (4u << 12) | ((bi + 1) << 8) | (4u << 4) | (bi + 1);
+    c.sel_m = (4u << 12) | ((bi + 1) << 8) | (4u << 4) | bi;
+    return c;
+}
+
+__device__ __forceinline__ RowScales decode_scales(const uint4& h, const LaneConsts& c) {
+    const uint32_t sc = and_or(h.y >> c.sh, c.ma, h.w & c.mb);
+    const uint32_t mn = and_or(h.z >> c.sh, c.ma, (h.w >> 4) & c.mb);
     const uint32_t magic = 0x64646464u;  // byte 0x64 = high byte of fp16 1024.0
-    uint32_t lo = __byte_perm(sc, magic, (4u << 12) | (bi << 8) | (4u << 4) | bi);
-    uint32_t hi = __byte_perm(sc, magic, (4u << 12) | ((bi + 1) << 8) | (4u << 4) | (bi + 1));
-    uint32_t mm = __byte_perm(mn, magic, (4u << 12) | ((bi + 1) << 8) | (4u << 4) | bi);
+    const uint32_t lo = __byte_perm(sc, magic, c.sel_lo);
+    const uint32_t hi = __byte_perm(sc, magic, c.sel_hi);
+    const uint32_t mm = __byte_perm(mn, magic, c.sel_m);
     RowScales r;
     const __half2 k1024 = u2h(0x64006400u), kneg1024 = u2h(0xE400E400u), k16th = u2h(0x2C002C00u), kneg64 = u2h(0xD400D400u);
     r.s_lo = __hsub2(u2h(lo), k1024);
@@ -93,8 +135,8 @@ __host__ __device__ constexpr size_t frag_bytes_per_block() {
     return (size_t)FRAGS * Cfg<MT>::NG * Cfg<MT>::NCOL * 4 * 8;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(THREADS, 2) gemv_q4k_mma_kernel(View v, const float* __restrict__ x, int rows,
+template <int MT, int STAGES>
+__global__ void __launch_bounds__(THREADS, MT <= 2 ? 3 : 2) gemv_q4k_mma_kernel(View v, const float* __restrict__ x, int rows,
                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles) {
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, MP = C::MP;
@@ -110,30 +152,48 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_mma_kernel(View v, const 
     const int64_t n = v.n;
     const int64_t row_bytes = (int64_t)KB * 144;
 
-    auto load_raw = [&](Raw& r, int tile, int b) {
-        int64_t r0 = (int64_t)tile * 16 + g, r1 = r0 + 8;
-        r0 = r0 < n ? r0 : n - 1;
-        r1 = r1 < n ? r1 : n - 1;
-        const uint8_t* p0 = v.q + r0 * row_bytes + (int64_t)b * 144;
-        const uint8_t* p1 = v.q + r1 * row_bytes + (int64_t)b * 144;
-        r.h0 = ld16(p0);
-        r.h1 = ld16(p1);
-        r.a0 = ld16(p0 + 16 + 32 * t);
-        r.a1 = ld16(p0 + 32 + 32 * t);
-        r.b0 = ld16(p1 + 16 + 32 * t);
-        r.b1 = ld16(p1 + 32 + 32 * t);
+    const LaneConsts lc = lane_consts(t);
+    uint8_t* ring = reinterpret_cast<uint8_t*>(scale_s + MT + (4 - MT % 4) % 4) + (size_t)warp * STAGES * SLOT_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+
+    // This warp's steps: super-blocks b = warp, warp + 8, ... of every tile of the CTA, in order.
+    const int nb_w = warp < KB ? (KB - warp + WARPS - 1) / WARPS : 0;
+    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int steps = nb_w * my_tiles;
+
+    // Requests step s into ring slot s % STAGES: lane (g, t) copies its 32 bytes of nibbles of rows g and
+    // g + 8, lanes t = 0 / t = 1 also the 16-byte header of row g / g + 8. Rows past n repeat row n - 1.
+    int iss_tile = blockIdx.x, iss_j = 0;  // tile and block counter of the next step to request
+    auto issue = [&](int s) {
+        if (s < steps) {
+            int64_t r0 = (int64_t)iss_tile * 16 + g, r1 = r0 + 8;
+            r0 = r0 < n ? r0 : n - 1;
+            r1 = r1 < n ? r1 : n - 1;
+            const uint32_t boff = (uint32_t)(warp + WARPS * iss_j) * 144u;
+            const uint8_t* p0 = v.q + r0 * row_bytes + boff;
+            const uint8_t* p1 = v.q + r1 * row_bytes + boff;
+            const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
+            const uint32_t d0 = slot + (uint32_t)g * 144u, d1 = d0 + 8u * 144u;
+            const uint32_t lo = 16u + 32u * (uint32_t)t;
+            cp_async16(d0 + lo, p0 + lo);
+            cp_async16(d0 + lo + 16, p0 + lo + 16);
+            cp_async16(d1 + lo, p1 + lo);
+            cp_async16(d1 + lo + 16, p1 + lo + 16);
+            if (t < 2) {
+                cp_async16(t == 0 ? d0 : d1, t == 0 ? p0 : p1);
+            }
+            if (++iss_j == nb_w) {
+                iss_j = 0;
+                iss_tile += gridDim.x;
+            }
+        }
+        cp_async_commit();
     };
 
     // The first weights are requested before the activations are prepared: they do not depend on x.
-    int tile = blockIdx.x, b = warp;
-    // advance (tile, b) to this warp's first valid step
-    auto valid = [&]() { return tile < tiles; };
-    if (b >= KB) {
-        tile = tiles;  // a warp without super-blocks only helps with the activations and the reduction
-    }
-    Raw cur;
-    if (valid()) {
-        load_raw(cur, tile, b);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        issue(s);
     }
 
     // ---- activations -> B fragments in shared memory ------------------------------------------------------
@@ -222,81 +282,76 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_mma_kernel(View v, const 
     for (int i = 0; i < NG; i++) {
         acc[i][0] = acc[i][1] = 0.0f;
     }
+    // Lanes whose column g is not stored (g >= NCOL) read another lane's fragment: their accumulator columns
+    // belong to activation rows that do not exist and are never written out.
+    const uint2* fb_lane = xf + (size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t;
+
+    auto compute = [&](const uint8_t* slot, int b) {
+        const uint8_t* q0 = slot + g * 144;
+        const uint8_t* q1 = q0 + 8 * 144;
+        const uint4 h0 = lds16(q0), h1 = lds16(q1);
+        const uint4 qa0 = lds16(q0 + 16 + 32 * t), qa1 = lds16(q0 + 32 + 32 * t);
+        const uint4 qb0 = lds16(q1 + 16 + 32 * t), qb1 = lds16(q1 + 32 + 32 * t);
+        const RowScales s0 = decode_scales(h0, lc), s1 = decode_scales(h1, lc);
+        // CH independent accumulator chains per column group keep the tensor pipe from waiting on itself
+        constexpr int CH = NG == 1 ? 4 : 2;
+        float D[NG][CH][4], E[NG][4];
+        const uint2* fb = fb_lane + (size_t)b * (FRAGS * NG * NCOL * 4);
+        const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+        const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const uint32_t va = wa[w], vb = wb[w], va8 = va >> 8, vb8 = vb >> 8;
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                // hf = 0: low nibbles, sub-block 2t; hf = 1: high nibbles, sub-block 2t + 1.
+                // Elements 4w + {0, 2} come from va, 4w + {1, 3} from va >> 8.
+                const uint32_t mask = hf == 0 ? 0x000F000Fu : 0x00F000F0u;
+                const __half2 sa = hf == 0 ? s0.s_lo : s0.s_hi, ca = hf == 0 ? s0.c_lo : s0.c_hi;
+                const __half2 sb = hf == 0 ? s1.s_lo : s1.s_hi, cb = hf == 0 ? s1.c_lo : s1.c_hi;
+                const uint32_t a0 = h2u(__hfma2(magic_pair(va, mask), sa, ca));
+                const uint32_t a2 = h2u(__hfma2(magic_pair(va8, mask), sa, ca));
+                const uint32_t a1 = h2u(__hfma2(magic_pair(vb, mask), sb, cb));
+                const uint32_t a3 = h2u(__hfma2(magic_pair(vb8, mask), sb, cb));
+                const int f = 2 * w + hf;
+#pragma unroll
+                for (int i = 0; i < NG; i++) {
+                    const uint2 bf = fb[(f * NG + i) * NCOL * 4];
+                    if (f < CH) {
+                        mma16816_first(D[i][f % CH], a0, a1, a2, a3, bf.x, bf.y);
+                    } else {
+                        mma16816(D[i][f % CH], a0, a1, a2, a3, bf.x, bf.y);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            const uint2 bf = fb[(16 * NG + i) * NCOL * 4];
+            mma16816_first(E[i], s0.mins, s1.mins, 0u, 0u, bf.x, bf.y);
+            float d01, d23;
+            if (CH == 4) {
+                d01 = ((D[i][0][0] + D[i][1][0]) + (D[i][2][0] + D[i][3][0])) + ((D[i][0][1] + D[i][1][1]) + (D[i][2][1] + D[i][3][1]));
+                d23 = ((D[i][0][2] + D[i][1][2]) + (D[i][2][2] + D[i][3][2])) + ((D[i][0][3] + D[i][1][3]) + (D[i][2][3] + D[i][3][3]));
+            } else {
+                d01 = (D[i][0][0] + D[i][1][0]) + (D[i][0][1] + D[i][1][1]);
+                d23 = (D[i][0][2] + D[i][1][2]) + (D[i][0][3] + D[i][1][3]);
+            }
+            acc[i][0] += s0.d * d01 - s0.dmin * (E[i][0] + E[i][1]);
+            acc[i][1] += s1.d * d23 - s1.dmin * (E[i][2] + E[i][3]);
+        }
+    };
+
     int parity = 0;
+    int step = 0;
     for (int my_tile = blockIdx.x; my_tile < tiles; my_tile += gridDim.x) {
-        // every warp takes part in every tile's reduction, with or without super-blocks of its own
-        while (valid() && tile == my_tile) {
-            // prefetch the next step of this warp
-            int nt = tile, nb = b + WARPS;
-            if (nb >= KB) {
-                nb = warp;
-                nt = tile + gridDim.x;
-            }
-            Raw nxt;
-            const bool more = nt < tiles;
-            if (more) {
-                load_raw(nxt, nt, nb);
-            }
-
-            RowScales s0 = decode_scales(cur.h0, t), s1 = decode_scales(cur.h1, t);
-            float D[NG][4], E[NG][4];
-#pragma unroll
-            for (int i = 0; i < NG; i++) {
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    D[i][c] = 0.0f;
-                    E[i][c] = 0.0f;
-                }
-            }
-            const uint2* fb = xf + ((size_t)b * FRAGS * NG) * NCOL * 4 + (size_t)g * 4 + t;
-            const uint32_t wa[8] = {cur.a0.x, cur.a0.y, cur.a0.z, cur.a0.w, cur.a1.x, cur.a1.y, cur.a1.z, cur.a1.w};
-            const uint32_t wb[8] = {cur.b0.x, cur.b0.y, cur.b0.z, cur.b0.w, cur.b1.x, cur.b1.y, cur.b1.z, cur.b1.w};
-#pragma unroll
-            for (int w = 0; w < 8; w++) {
-                const uint32_t va = wa[w], vb = wb[w], va8 = va >> 8, vb8 = vb >> 8;
-                // low nibbles: sub-block 2t, elements 4w + {0, 2} and 4w + {1, 3}
-                uint32_t a0 = h2u(__hfma2(u2h((va & 0x000F000Fu) | 0x64006400u), s0.s_lo, s0.c_lo));
-                uint32_t a2 = h2u(__hfma2(u2h((va8 & 0x000F000Fu) | 0x64006400u), s0.s_lo, s0.c_lo));
-                uint32_t a1 = h2u(__hfma2(u2h((vb & 0x000F000Fu) | 0x64006400u), s1.s_lo, s1.c_lo));
-                uint32_t a3 = h2u(__hfma2(u2h((vb8 & 0x000F000Fu) | 0x64006400u), s1.s_lo, s1.c_lo));
-#pragma unroll
-                for (int i = 0; i < NG; i++) {
-                    uint2 bf = make_uint2(0u, 0u);
-                    if (NCOL == 8 || g < NCOL) {
-                        bf = fb[((size_t)(2 * w) * NG + i) * NCOL * 4];
-                    }
-                    mma16816(D[i], a0, a1, a2, a3, bf.x, bf.y);
-                }
-                // high nibbles: sub-block 2t + 1
-                a0 = h2u(__hfma2(u2h((va & 0x00F000F0u) | 0x64006400u), s0.s_hi, s0.c_hi));
-                a2 = h2u(__hfma2(u2h((va8 & 0x00F000F0u) | 0x64006400u), s0.s_hi, s0.c_hi));
-                a1 = h2u(__hfma2(u2h((vb & 0x00F000F0u) | 0x64006400u), s1.s_hi, s1.c_hi));
-                a3 = h2u(__hfma2(u2h((vb8 & 0x00F000F0u) | 0x64006400u), s1.s_hi, s1.c_hi));
-#pragma unroll
-                for (int i = 0; i < NG; i++) {
-                    uint2 bf = make_uint2(0u, 0u);
-                    if (NCOL == 8 || g < NCOL) {
-                        bf = fb[((size_t)(2 * w + 1) * NG + i) * NCOL * 4];
-                    }
-                    mma16816(D[i], a0, a1, a2, a3, bf.x, bf.y);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < NG; i++) {
-                uint2 bf = make_uint2(0u, 0u);
-                if (NCOL == 8 || g < NCOL) {
-                    bf = fb[((size_t)16 * NG + i) * NCOL * 4];
-                }
-                mma16816(E[i], s0.mins, s1.mins, 0u, 0u, bf.x, bf.y);
-                acc[i][0] += s0.d * (D[i][0] + D[i][1]) - s0.dmin * (E[i][0] + E[i][1]);
-                acc[i][1] += s1.d * (D[i][2] + D[i][3]) - s1.dmin * (E[i][2] + E[i][3]);
-            }
-
-            tile = nt;
-            b = nb;
-            if (more) {
-                cur = nxt;
-            }
+        for (int b = warp; b < KB; b += WARPS) {
+            __syncwarp();                 // every lane is done reading the slot that is requested next
+            issue(step + STAGES - 1);
+            cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+            __syncwarp();                 // ... and so have the other lanes'
+            compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, b);
+            step++;
         }
         // ---- reduce the 8 warps' partial sums of this tile in a fixed order ---------------------------------
         float* rd = red + (size_t)parity * WARPS * 16 * MP;
@@ -334,30 +389,46 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT>
-int run_q4k(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+template <int MT, int STAGES>
+size_t smem_bytes(int KB) {
     using C = Cfg<MT>;
-    const int KB = (int)(v.k / 256);
-    size_t smem = (size_t)KB * frag_bytes_per_block<MT>() + (size_t)(2 * WARPS * 16 * C::MP + WARPS * MT + MT) * sizeof(float);
-    if (smem > 200 * 1024) {
-        *handled = false;  // the activations do not fit in shared memory in fragment form
-        return JQ_OK;
-    }
+    return (size_t)KB * frag_bytes_per_block<MT>() + (size_t)(2 * WARPS * 16 * C::MP + WARPS * MT + (MT + 3) / 4 * 4) * sizeof(float) +
+           (size_t)WARPS * STAGES * SLOT_BYTES;
+}
+
+template <int MT, int STAGES>
+int launch_q4k(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s) {
+    const size_t smem = smem_bytes<MT, STAGES>((int)(v.k / 256));
     // the opt-in for more than 48 KB of dynamic shared memory is per device
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_mma_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_mma_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16);
-    int per_sm = smem > 100 * 1024 ? 1 : 2;
-    int grid = tiles < sm_count() * per_sm ? tiles : sm_count() * per_sm;
-    gemv_q4k_mma_kernel<MT><<<grid, THREADS, smem, s>>>(v, x, rows, bias, y, tiles);
+    const int per_sm = smem > SMEM_MAX / 2 - 1024 ? 1 : (MT <= 2 && smem <= SMEM_MAX / 3 - 1024 ? 3 : 2);
+    const int grid = tiles < sm_count() * per_sm ? tiles : sm_count() * per_sm;
+    gemv_q4k_mma_kernel<MT, STAGES><<<grid, THREADS, smem, s>>>(v, x, rows, bias, y, tiles);
     count_launch();
-    *handled = true;
     return check_launch("gemv_q4k_mma_kernel");
+}
+
+template <int MT>
+int run_q4k(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+    const int KB = (int)(v.k / 256);
+    const size_t half = SMEM_MAX / 2 - 1024;  // two CTAs per SM (1 KB each is reserved by the system)
+    *handled = true;
+    if (MT <= 2 && smem_bytes<MT, 2>(KB) <= SMEM_MAX / 3 - 1024) return launch_q4k<MT, 2>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 4>(KB) <= half) return launch_q4k<MT, 4>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 3>(KB) <= half) return launch_q4k<MT, 3>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 4>(KB) <= SMEM_MAX) return launch_q4k<MT, 4>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 2>(KB) <= SMEM_MAX) return launch_q4k<MT, 2>(v, x, rows, bias, y, s);
+    *handled = false;  // the activations do not fit in shared memory in fragment form
+    return JQ_OK;
 }
 
 }  // namespace

@@ -1,0 +1,454 @@
+// Decode GEMV for Q4_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 4.
+//
+// The 4-bit quants never become floating point. Per row of x the activations are scaled by a power of
+// two and rounded to 22-bit fixed point, X = rint(x / s * 2^21), then split into three signed base-256
+// digits X = d2 * 65536 + d1 * 256 + d0 that occupy three columns of the B operand of
+// mma.sync.m16n8k32 (u8 x s8 -> s32). Four nibbles are widened to four bytes with one AND (one more
+// shift for the high nibbles) and go straight into the A operand, so one MMA multiplies one 32-element
+// sub-block of 16 weight rows with all digit columns exactly. The sub-block sums are combined with the
+// 6-bit scales in integer arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to
+// float once per super-block and scaled by fp16 d. The "min" part, dmin * sum_sub m_sub * sum(x over the
+// sub-block), uses one m16n8k16 MMA whose A operand is the eight packed 6-bit mins and whose B operand
+// holds the digit sums of each sub-block. Everything up to the per-super-block float conversion is exact,
+// and x keeps 22 bits relative to its largest magnitude, so results match an FP32-accumulating kernel.
+// The summation order depends on k only: a row shard of a weight gives bitwise the same outputs.
+//
+// Work split as in the fp16 kernel: a CTA of 8 warps owns 16 rows at a time (tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ...), warp p takes super-blocks b = p (mod 8). Weights stream HBM -> shared
+// memory through a per-warp ring of cp.async slots; consecutive lanes copy consecutive 16-byte chunks, so
+// every 32-byte sector is requested once. The weight buffer is padded by 16 rows, which lets the last
+// tile read past n without a bounds check.
+#include "jq_formats.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int ROW_PITCH = 160;              // bytes per row in a ring slot: 144 padded, conflict-free 8-byte reads
+constexpr int SLOT_BYTES = 16 * ROW_PITCH;  // one super-block of 16 rows
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// D = A(16x32 u8) * B(32x8 s8), accumulators start at zero.
+__device__ __forceinline__ void imma_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// D = A(16x16 u8) * B(16x8 s8), accumulators start at zero.
+__device__ __forceinline__ void imma_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int MT>
+struct Cfg {
+    static constexpr int COLS = 3 * MT;               // digit columns: column 3m + i is digit i of activation row m
+    static constexpr int NG = (COLS + 7) / 8;         // MMA column groups for the quants
+    static constexpr int NCOL = NG == 1 ? COLS : 8;   // columns stored per group
+    static constexpr int MCOLS = 2 * COLS;            // mins: column 2c + p is part p (low 7 bits / rest) of the sums of digit column c
+    static constexpr int NGM = (MCOLS + 7) / 8;
+    static constexpr int NCOLM = NGM == 1 ? MCOLS : 8;
+    static constexpr int SLOTS = 2 * NG + NGM;        // float partial sums per lane and row
+    // bytes of activation image per super-block
+    static constexpr size_t XD = (size_t)8 * NG * NCOL * 4 * 8;   // 8 sub-blocks x groups x columns x 4 lanes x 8 bytes
+    static constexpr size_t XM = (size_t)NGM * NCOLM * 4 * 4;     // groups x columns x 4 lanes x 4 bytes
+};
+
+template <int MT, int STAGES>
+__global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const float* __restrict__ x, int rows,
+                                                                const float* __restrict__ bias, float* __restrict__ y, int tiles) {
+    using C = Cfg<MT>;
+    constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int KB = (int)(v.k >> 8);
+    uint2* xd = reinterpret_cast<uint2*>(smem_raw);                                   // [KB][8][NG][NCOL][4]
+    uint32_t* xm = reinterpret_cast<uint32_t*>(smem_raw + (size_t)KB * C::XD);        // [KB][NGM][NCOLM][4]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KB * (C::XD + C::XM));   // [2][WARPS][16][MT]
+    float* amax_s = red + 2 * WARPS * 16 * MT;                                        // [WARPS][MT]
+    float* scale_s = amax_s + WARPS * MT;                                             // [MT] (+ padding to 4)
+    uint8_t* ring = reinterpret_cast<uint8_t*>(scale_s + 4) + (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n = v.n;
+    const int64_t row_bytes = (int64_t)KB * 144;
+
+    // ---- weight stream: chunk c = lane + 32 i of the 144 chunks (16 rows x 9) of a super-block -------------
+    uint32_t src_off[5], dst_off[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) {
+        const int c = lane + 32 * i, r = c / 9, ch = c % 9;
+        src_off[i] = (uint32_t)(r * (int)row_bytes + ch * 16);
+        dst_off[i] = (uint32_t)(r * ROW_PITCH + ch * 16);
+    }
+    const int nb_w = warp < KB ? (KB - warp + WARPS - 1) / WARPS : 0;
+    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int steps = nb_w * my_tiles;
+    int iss_tile = blockIdx.x, iss_j = 0;
+    auto issue = [&](int s) {
+        if (s < steps) {
+            const uint8_t* base = v.q + (int64_t)iss_tile * 16 * row_bytes + (uint32_t)(warp + WARPS * iss_j) * 144u;
+            const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                cp_async16(slot + dst_off[i], base + src_off[i]);
+            }
+            if (lane < 16) {
+                cp_async16(slot + dst_off[4], base + src_off[4]);
+            }
+            if (++iss_j == nb_w) {
+                iss_j = 0;
+                iss_tile += gridDim.x;
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        issue(s);  // the first weights are on their way while the activations are prepared
+    }
+
+    // ---- activations -> digit fragments in shared memory -------------------------------------------------------
+    {
+        const int octs = (int)(v.k >> 3);  // groups of 8 consecutive activations
+        float am[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            am[m] = 0.0f;
+        }
+        for (int q = tid; q < 2 * octs; q += THREADS) {
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                if (m < rows) {
+                    const float4 xv = __ldg(reinterpret_cast<const float4*>(x + (int64_t)m * v.k) + q);
+                    am[m] = fmaxf(am[m], fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w))));
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                am[m] = fmaxf(am[m], __shfl_xor_sync(0xffffffffu, am[m], o));
+            }
+            if (lane == 0) {
+                amax_s[warp * MT + m] = am[m];
+            }
+        }
+        __syncthreads();
+        if (tid < MT) {
+            float a = 0.0f;
+            for (int w = 0; w < WARPS; w++) {
+                a = fmaxf(a, amax_s[w * MT + tid]);
+            }
+            // s = 2^floor(log2(amax)): the largest |x| / s lies in [1, 2)
+            uint32_t e = __float_as_uint(a) & 0x7f800000u;
+            e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s a normal float
+            scale_s[tid] = __uint_as_float(e);
+        }
+        __syncthreads();
+        // thread -> one octet (8 activations, the k-slots of one lane in one sub-block MMA) of one activation row
+        for (int q = tid; q < octs; q += THREADS) {
+            const int blk = q >> 5, o = q & 31;  // 32 octets per super-block
+            const int sub = o >> 2, tt = o & 3;  // sub-block and lane slot: elements 32 sub + 8 tt + 0..7
+            // element order inside the block: sub-block 2j + hf covers elements 64 j + 32 hf + l
+            uint2* frag = xd + ((size_t)(blk * 8 + sub) * NG) * NCOL * 4 + tt;
+            uint32_t* fmin = xm + ((size_t)blk * NGM) * NCOLM * 4 + (sub >> 2);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                int X[8];
+                if (m < rows) {
+                    const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * v.k) + 2 * q;
+                    const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
+                    // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
+                    const float inv = __uint_as_float(0x7f000000u - __float_as_uint(scale_s[m]) + (21u << 23));
+                    X[0] = __float2int_rn(lo.x * inv); X[1] = __float2int_rn(lo.y * inv);
+                    X[2] = __float2int_rn(lo.z * inv); X[3] = __float2int_rn(lo.w * inv);
+                    X[4] = __float2int_rn(hi.x * inv); X[5] = __float2int_rn(hi.y * inv);
+                    X[6] = __float2int_rn(hi.z * inv); X[7] = __float2int_rn(hi.w * inv);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        X[i] = 0;
+                    }
+                }
+#pragma unroll
+                for (int dgt = 0; dgt < 3; dgt++) {
+                    uint32_t w0 = 0, w1 = 0;
+                    int sum = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
+                        X[i] = (X[i] - d) >> 8;
+                        sum += d;
+                        if (i < 4) {
+                            w0 |= (uint32_t)(d & 0xff) << (8 * i);
+                        } else {
+                            w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
+                        }
+                    }
+                    const int col = 3 * m + dgt;
+                    frag[((size_t)(col >> 3) * NCOL + (col & 7)) * 4] = make_uint2(w0, w1);
+                    // digit sum of the whole sub-block: the 4 octets of a sub-block sit in 4 consecutive lanes
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    if (tt == 0) {
+                        const int lo7 = sum & 127, hi = (sum - lo7) >> 7;  // sum = 128 hi + lo7, both fit a signed byte
+#pragma unroll
+                        for (int p = 0; p < 2; p++) {
+                            const int mc = 2 * col + p;
+                            uint8_t* dst = reinterpret_cast<uint8_t*>(fmin + ((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 4) + (sub & 3);
+                            *dst = (uint8_t)(p == 0 ? lo7 : hi);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- main loop ----------------------------------------------------------------------------------------------
+    // Lanes whose column is not stored read another lane's fragment; their results get weight zero below.
+    const uint2* xd_lane = xd + (size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t;
+    const uint32_t* xm_lane = xm + (size_t)(NCOLM == 8 ? g : g % NCOLM) * 4 + (t & 1);
+    float acc[NG][2][2];   // [group][row g / g + 8][column 2t / 2t + 1], in units of 2^-21 * 256^digit
+    float accm[NGM][2];    // mins, [group][row]
+#pragma unroll
+    for (int i = 0; i < NG; i++) {
+        acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NGM; i++) {
+        accm[i][0] = accm[i][1] = 0.0f;
+    }
+
+    auto compute = [&](const uint8_t* slot, int b) {
+        const uint8_t* q0 = slot + g * ROW_PITCH;
+        const uint8_t* q1 = q0 + 8 * ROW_PITCH;
+        const uint4 h0 = *reinterpret_cast<const uint4*>(q0), h1 = *reinterpret_cast<const uint4*>(q1);
+        // 6-bit scales and mins of the 8 sub-blocks as packed bytes: [0..3] and [4..7]
+        const uint32_t sc0a = h0.y & 0x3f3f3f3fu, sc0b = and_or(h0.y >> 2, 0x30303030u, h0.w & 0x0f0f0f0fu);
+        const uint32_t sc1a = h1.y & 0x3f3f3f3fu, sc1b = and_or(h1.y >> 2, 0x30303030u, h1.w & 0x0f0f0f0fu);
+        const uint32_t mn0 = t == 0 ? (h0.z & 0x3f3f3f3fu) : (t == 1 ? and_or(h0.z >> 2, 0x30303030u, (h0.w >> 4) & 0x0f0f0f0fu) : 0u);
+        const uint32_t mn1 = t == 0 ? (h1.z & 0x3f3f3f3fu) : (t == 1 ? and_or(h1.z >> 2, 0x30303030u, (h1.w >> 4) & 0x0f0f0f0fu) : 0u);
+        int I[NG][4];
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            I[i][0] = I[i][1] = I[i][2] = I[i][3] = 0;
+        }
+        const uint2* fb = xd_lane + (size_t)b * (8 * NG * NCOL * 4);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // this lane's 8 bytes of group j for rows g and g + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
+            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + 16 + 32 * j + 8 * t);
+            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + 16 + 32 * j + 8 * t);
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const int sub = 2 * j + hf;
+                const uint32_t a0 = (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
+                const uint32_t a2 = (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
+                const uint32_t a1 = (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
+                const uint32_t a3 = (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
+                const int s0 = (int)__byte_perm(sub < 4 ? sc0a : sc0b, 0u, 0x4440u + (sub & 3));
+                const int s1 = (int)__byte_perm(sub < 4 ? sc1a : sc1b, 0u, 0x4440u + (sub & 3));
+#pragma unroll
+                for (int i = 0; i < NG; i++) {
+                    const uint2 bf = fb[(sub * NG + i) * NCOL * 4];
+                    int D[4];
+                    imma_k32(D, a0, a1, a2, a3, bf.x, bf.y);
+                    I[i][0] += s0 * D[0];
+                    I[i][1] += s0 * D[1];
+                    I[i][2] += s1 * D[2];
+                    I[i][3] += s1 * D[3];
+                }
+            }
+        }
+        const float d0 = half_bits_to_float(h0.x), d1 = half_bits_to_float(h1.x);
+        const float dm0 = half_bits_to_float(h0.x >> 16), dm1 = half_bits_to_float(h1.x >> 16);
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            acc[i][0][0] = fmaf(d0, (float)I[i][0], acc[i][0][0]);
+            acc[i][0][1] = fmaf(d0, (float)I[i][1], acc[i][0][1]);
+            acc[i][1][0] = fmaf(d1, (float)I[i][2], acc[i][1][0]);
+            acc[i][1][1] = fmaf(d1, (float)I[i][3], acc[i][1][1]);
+        }
+        const uint32_t* fm = xm_lane + (size_t)b * (NGM * NCOLM * 4);
+#pragma unroll
+        for (int i = 0; i < NGM; i++) {
+            int E[4];
+            imma_k16(E, mn0, mn1, fm[i * NCOLM * 4]);
+            accm[i][0] = fmaf(dm0, (float)(E[1] * 128 + E[0]), accm[i][0]);
+            accm[i][1] = fmaf(dm1, (float)(E[3] * 128 + E[2]), accm[i][1]);
+        }
+    };
+
+    // digit weights of this lane's accumulator columns (0 for columns that hold no activation row)
+    float wq[NG][2], wm[NGM];
+    int mq[NG][2], mmn[NGM];
+#pragma unroll
+    for (int i = 0; i < NG; i++) {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int col = 8 * i + 2 * t + c;
+            mq[i][c] = col < C::COLS ? col / 3 : -1;
+            wq[i][c] = col < C::COLS ? __uint_as_float((uint32_t)(127 - 21 + 8 * (col % 3)) << 23) : 0.0f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NGM; i++) {
+        const int col = 4 * i + t;  // digit column whose two parts this lane holds
+        mmn[i] = col < C::COLS ? col / 3 : -1;
+        wm[i] = col < C::COLS ? __uint_as_float((uint32_t)(127 - 21 + 8 * (col % 3)) << 23) : 0.0f;
+    }
+
+    int parity = 0;
+    int step = 0;
+    for (int my_tile = blockIdx.x; my_tile < tiles; my_tile += gridDim.x) {
+        for (int b = warp; b < KB; b += WARPS) {
+            __syncwarp();                 // every lane is done reading the slot that is requested next
+            issue(step + STAGES - 1);
+            cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+            __syncwarp();                 // ... and so have the other lanes'
+            compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, b);
+            step++;
+        }
+        // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
+        float* rd = red + (size_t)parity * WARPS * 16 * MT;
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    if (mq[i][c] == m) {
+                        p0 = fmaf(acc[i][0][c], wq[i][c], p0);
+                        p1 = fmaf(acc[i][1][c], wq[i][c], p1);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NGM; i++) {
+                if (mmn[i] == m) {
+                    p0 = fmaf(-accm[i][0], wm[i], p0);
+                    p1 = fmaf(-accm[i][1], wm[i], p1);
+                }
+            }
+            p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+            p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+            p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+            p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+            if (t == 0) {
+                rd[(warp * 16 + g) * MT + m] = p0;
+                rd[(warp * 16 + g + 8) * MT + m] = p1;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < NGM; i++) {
+            accm[i][0] = accm[i][1] = 0.0f;
+        }
+        __syncthreads();
+        // ---- the 8 warps' partial sums in a fixed order ------------------------------------------------------------------
+        for (int o = tid; o < 16 * MT; o += THREADS) {
+            const int r = o / MT, m = o % MT;
+            const int64_t row = (int64_t)my_tile * 16 + r;
+            if (m < rows && row < n) {
+                const float* p = rd + r * MT + m;
+                const float s = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
+                                ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
+                y[(int64_t)m * n + row] = s * scale_s[m] + (bias != nullptr ? bias[row] : 0.0f);
+            }
+        }
+        parity ^= 1;
+    }
+}
+
+int g_sms = 0;
+int sm_count() {
+    if (g_sms == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+            g_sms = sms;
+        } else {
+            g_sms = 148;
+        }
+    }
+    return g_sms;
+}
+
+template <int MT, int STAGES>
+size_t smem_bytes(int KB) {
+    using C = Cfg<MT>;
+    return (size_t)KB * (C::XD + C::XM) + (size_t)(2 * WARPS * 16 * MT + WARPS * MT + 4) * sizeof(float) + (size_t)WARPS * STAGES * SLOT_BYTES;
+}
+
+template <int MT, int STAGES>
+int launch(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s) {
+    const size_t smem = smem_bytes<MT, STAGES>((int)(v.k / 256));
+    static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
+    int dev = 0;
+    JQ_CUDA(cudaGetDevice(&dev));
+    if ((configured.load() >> (dev & 63) & 1) == 0) {
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        configured.fetch_or((uint64_t)1 << (dev & 63));
+    }
+    const int tiles = (int)((v.n + 15) / 16);
+    const int per_sm = smem > SMEM_MAX / 2 - 1024 ? 1 : 2;
+    const int grid = tiles < sm_count() * per_sm ? tiles : sm_count() * per_sm;
+    gemv_q4k_i8_kernel<MT, STAGES><<<grid, THREADS, smem, s>>>(v, x, rows, bias, y, tiles);
+    count_launch();
+    return check_launch("gemv_q4k_i8_kernel");
+}
+
+template <int MT>
+int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+    const int KB = (int)(v.k / 256);
+    const size_t half = SMEM_MAX / 2 - 1024;  // two CTAs per SM
+    *handled = true;
+    if (smem_bytes<MT, 4>(KB) <= half) return launch<MT, 4>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 3>(KB) <= half) return launch<MT, 3>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 4>(KB) <= SMEM_MAX) return launch<MT, 4>(v, x, rows, bias, y, s);
+    if (smem_bytes<MT, 2>(KB) <= SMEM_MAX) return launch<MT, 2>(v, x, rows, bias, y, s);
+    *handled = false;  // the activation image does not fit in shared memory
+    return JQ_OK;
+}
+
+}  // namespace
+
+// Q4_K with rows in [1, 4] on a weight whose buffer is padded by 16 rows. *handled = false leaves the call
+// to another kernel.
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+    *handled = false;
+    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 4 || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
+        return JQ_OK;
+    }
+    if (rows == 1) return run<1>(v, x, rows, bias, y, s, handled);
+    if (rows == 2) return run<2>(v, x, rows, bias, y, s, handled);
+    return run<4>(v, x, rows, bias, y, s, handled);
+}
+
+}  // namespace jq
