@@ -88,6 +88,45 @@ static int staging_for(int device, size_t bytes, Staging** out) {
     return JQ_OK;
 }
 
+// ---- per (device, stream) scratch ------------------------------------------------------------------
+struct Scratch {
+    int device;
+    cudaStream_t stream;
+    uint8_t* buf;
+    size_t bytes;
+};
+static std::mutex g_scratch_mu;
+static std::vector<Scratch> g_scratch;
+
+int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out) {
+    int dev = 0;
+    JQ_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    Scratch* hit = nullptr;
+    for (Scratch& sc : g_scratch) {
+        if (sc.device == dev && sc.stream == s) {
+            hit = &sc;
+            break;
+        }
+    }
+    if (hit == nullptr) {
+        g_scratch.push_back(Scratch{dev, s, nullptr, 0});
+        hit = &g_scratch.back();
+    }
+    if (hit->bytes < bytes) {
+        if (hit->buf != nullptr) {
+            JQ_CUDA(cudaFree(hit->buf));  // waits for the device, so no kernel still reads the old buffer
+            hit->buf = nullptr;
+            hit->bytes = 0;
+        }
+        const size_t want = bytes < ((size_t)1 << 20) ? ((size_t)1 << 20) : bytes + bytes / 2;
+        JQ_CUDA(cudaMalloc(&hit->buf, want));
+        hit->bytes = want;
+    }
+    *out = hit->buf;
+    return JQ_OK;
+}
+
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 static int check_weight(const jq_weight* w, const char* who) {

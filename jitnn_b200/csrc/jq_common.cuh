@@ -101,7 +101,12 @@ int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStrea
 int launch_gemv_q4k_mma(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
 
 // Integer tensor-core GEMV for Q4_K, rows <= 4; needs the 16 padding rows every uploaded weight has.
-int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
+size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
+
+// Scratch memory of at least `bytes` on the current device, private to work enqueued on `s` (one buffer per
+// device and stream, grown on demand and kept until the library is unloaded).
+int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out);
 
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;

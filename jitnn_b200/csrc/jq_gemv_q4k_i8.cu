@@ -1,23 +1,29 @@
 // Decode GEMV for Q4_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 4.
 //
-// The 4-bit quants never become floating point. Per row of x the activations are scaled by a power of
-// two and rounded to 22-bit fixed point, X = rint(x / s * 2^21), then split into three signed base-256
-// digits X = d2 * 65536 + d1 * 256 + d0 that occupy three columns of the B operand of
-// mma.sync.m16n8k32 (u8 x s8 -> s32). Four nibbles are widened to four bytes with one AND (one more
-// shift for the high nibbles) and go straight into the A operand, so one MMA multiplies one 32-element
-// sub-block of 16 weight rows with all digit columns exactly. The sub-block sums are combined with the
-// 6-bit scales in integer arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to
-// float once per super-block and scaled by fp16 d. The "min" part, dmin * sum_sub m_sub * sum(x over the
-// sub-block), uses one m16n8k16 MMA whose A operand is the eight packed 6-bit mins and whose B operand
-// holds the digit sums of each sub-block. Everything up to the per-super-block float conversion is exact,
-// and x keeps 22 bits relative to its largest magnitude, so results match an FP32-accumulating kernel.
-// The summation order depends on k only: a row shard of a weight gives bitwise the same outputs.
+// The 4-bit quants never become floating point. A small first kernel turns the activations into an
+// "activation image" in a scratch buffer: per 256-element super-block of k and per row of x, the values
+// are scaled by a power of two s (from the block's largest magnitude), rounded to 22-bit fixed point,
+// X = rint(x / s * 2^21), and split into three signed base-256 digits X = d2 * 65536 + d1 * 256 + d0.
+// The digits are laid out as B fragments of mma.sync.m16n8k32 (u8 x s8 -> s32): column 3m + i holds digit
+// i of activation row m. The GEMV kernel widens four nibbles to four bytes with one AND (one more shift for
+// the high nibbles) and feeds them as the A operand, so one MMA multiplies one 32-element sub-block of 16
+// weight rows with every digit column exactly. Sub-block results are combined with the 6-bit scales in
+// integer arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to float once per
+// super-block and scaled by fp16 d and the column weight s * 2^(8i - 21). The "min" part of Q4_K,
+// dmin * sum_sub m_sub * sum(x over the sub-block), uses one m16n8k16 MMA whose A operand is the eight
+// packed 6-bit mins and whose B operand holds the digit sums of every sub-block. Everything up to the
+// per-super-block float conversion is exact and x keeps 22 bits relative to the largest magnitude of its
+// super-block, so results match an FP32-accumulating kernel. The summation order depends on k only: a row
+// shard of a weight gives bitwise the same outputs as the whole weight.
 //
-// Work split as in the fp16 kernel: a CTA of 8 warps owns 16 rows at a time (tiles blockIdx.x,
-// blockIdx.x + gridDim.x, ...), warp p takes super-blocks b = p (mod 8). Weights stream HBM -> shared
-// memory through a per-warp ring of cp.async slots; consecutive lanes copy consecutive 16-byte chunks, so
-// every 32-byte sector is requested once. The weight buffer is padded by 16 rows, which lets the last
-// tile read past n without a bounds check.
+// Work split: a CTA of 8 warps owns 16 output rows at a time (tiles blockIdx.x, blockIdx.x + gridDim.x,
+// ...), warp p takes super-blocks b = p (mod 8). Weights stream HBM -> shared memory through a per-warp
+// ring of cp.async slots; consecutive lanes copy consecutive 16-byte chunks, so every 32-byte sector is
+// requested once, and the slot layout is swizzled so that the 8-byte fragment reads are conflict free.
+// The weight buffer is padded by 16 rows, which lets the last tile read past n without a bounds check.
+// The GEMV kernel is launched with programmatic stream serialization: it requests its first weights while
+// the activation kernel is still running and waits for it (griddepcontrol.wait) only before copying the
+// image into shared memory.
 #include "jq_formats.cuh"
 
 namespace jq {
@@ -26,8 +32,8 @@ namespace {
 
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
-constexpr int ROW_PITCH = 160;              // bytes per row in a ring slot: 144 padded, conflict-free 8-byte reads
-constexpr int SLOT_BYTES = 16 * ROW_PITCH;  // one super-block of 16 rows
+constexpr int SLOT_BYTES = 16 * 144;        // one super-block of 16 rows: 16 x 128 bytes of nibbles, then 16 headers
+constexpr int SLOT_HEADERS = 16 * 128;
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
@@ -67,25 +73,119 @@ struct Cfg {
     static constexpr int MCOLS = 2 * COLS;            // mins: column 2c + p is part p (low 7 bits / rest) of the sums of digit column c
     static constexpr int NGM = (MCOLS + 7) / 8;
     static constexpr int NCOLM = NGM == 1 ? MCOLS : 8;
-    static constexpr int SLOTS = 2 * NG + NGM;        // float partial sums per lane and row
-    // bytes of activation image per super-block
+    // bytes of activation image per super-block: digit fragments, digit-sum fragments, column weights
     static constexpr size_t XD = (size_t)8 * NG * NCOL * 4 * 8;   // 8 sub-blocks x groups x columns x 4 lanes x 8 bytes
-    static constexpr size_t XM = (size_t)NGM * NCOLM * 4 * 4;     // groups x columns x 4 lanes x 4 bytes
+    static constexpr size_t XM = (size_t)NGM * NCOLM * 2 * 4;     // groups x columns x 2 lanes x 4 bytes
+    static constexpr size_t TAB = (size_t)NG * 8 * 4;             // one float per digit column
+    static constexpr size_t PB = XD + XM + TAB;
 };
 
-template <int MT, int STAGES>
-__global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const float* __restrict__ x, int rows,
-                                                                const float* __restrict__ bias, float* __restrict__ y, int tiles) {
+// ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
+// One warp per super-block of k; lane = octet (sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of that sub-block MMA).
+constexpr int PREP_WARPS = 4;
+
+template <int MT>
+__global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
+                                                                             uint8_t* __restrict__ image) {
+    using C = Cfg<MT>;
+    constexpr int NG = C::NG, NCOL = C::NCOL, NCOLM = C::NCOLM;
+    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    if (b >= (int)(k >> 8)) {
+        return;
+    }
+    const int sub = lane >> 2, tt = lane & 3;
+    uint8_t* img = image + (size_t)b * C::PB;
+    uint2* xd = reinterpret_cast<uint2*>(img);
+    uint32_t* xm = reinterpret_cast<uint32_t*>(img + C::XD);
+    float* tab = reinterpret_cast<float*>(img + C::XD + C::XM);
+    if (lane >= C::COLS && lane < NG * 8) {
+        tab[lane] = 0.0f;  // columns that hold no activation row
+    }
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        float xv[8];
+        if (m < rows) {
+            const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
+            const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
+            xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
+            xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                xv[i] = 0.0f;
+            }
+        }
+        float am = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            am = fmaxf(am, fabsf(xv[i]));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        }
+        // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
+        uint32_t e = __float_as_uint(am) & 0x7f800000u;
+        e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
+        // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
+        const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
+        int X[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            X[i] = __float2int_rn(xv[i] * inv);
+        }
+#pragma unroll
+        for (int dgt = 0; dgt < 3; dgt++) {
+            uint32_t w0 = 0, w1 = 0;
+            int sum = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
+                X[i] = (X[i] - d) >> 8;
+                sum += d;
+                if (i < 4) {
+                    w0 |= (uint32_t)(d & 0xff) << (8 * i);
+                } else {
+                    w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
+                }
+            }
+            const int col = 3 * m + dgt;
+            xd[(((size_t)sub * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt] = make_uint2(w0, w1);
+            // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            const int lo7 = sum & 127, hi = (sum - lo7) >> 7;
+#pragma unroll
+            for (int p = 0; p < 2; p++) {
+                // bytes of sub-blocks 4q .. 4q+3 packed into one word, in lanes 0 (q = 0) and 16 (q = 1)
+                uint32_t byte = (uint32_t)(p == 0 ? lo7 : hi) & 0xffu;
+                uint32_t word = byte | (__shfl_down_sync(0xffffffffu, byte, 4) << 8) | (__shfl_down_sync(0xffffffffu, byte, 8) << 16) |
+                                (__shfl_down_sync(0xffffffffu, byte, 12) << 24);
+                const int mc = 2 * col + p;
+                if ((lane & 15) == 0) {
+                    xm[((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 2 + (lane >> 4)] = word;
+                }
+            }
+            if (lane == 0) {
+                tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
+            }
+        }
+    }
+}
+
+// ---- the GEMV ---------------------------------------------------------------------------------------------------
+template <int MT, int STAGES, int OCC>
+__global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
+                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles) {
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int KB = (int)(v.k >> 8);
-    uint2* xd = reinterpret_cast<uint2*>(smem_raw);                                   // [KB][8][NG][NCOL][4]
-    uint32_t* xm = reinterpret_cast<uint32_t*>(smem_raw + (size_t)KB * C::XD);        // [KB][NGM][NCOLM][4]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KB * (C::XD + C::XM));   // [2][WARPS][16][MT]
-    float* amax_s = red + 2 * WARPS * 16 * MT;                                        // [WARPS][MT]
-    float* scale_s = amax_s + WARPS * MT;                                             // [MT] (+ padding to 4)
-    uint8_t* ring = reinterpret_cast<uint8_t*>(scale_s + 4) + (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
+    uint8_t* img = smem_raw;                                                         // [KB][PB]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KB * C::PB);            // [2][WARPS][16][MT]
+    uint8_t* ring = reinterpret_cast<uint8_t*>(red + 2 * WARPS * 16 * MT) + (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -94,12 +194,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
     const int64_t row_bytes = (int64_t)KB * 144;
 
     // ---- weight stream: chunk c = lane + 32 i of the 144 chunks (16 rows x 9) of a super-block -------------
+    // Slot layout: row r's 128 bytes of nibbles at r * 128 with its four 32-byte segments permuted by r & 3
+    // (segment p sits at position p ^ (r & 3)), the 16 headers behind them.
     uint32_t src_off[5], dst_off[5];
 #pragma unroll
     for (int i = 0; i < 5; i++) {
         const int c = lane + 32 * i, r = c / 9, ch = c % 9;
         src_off[i] = (uint32_t)(r * (int)row_bytes + ch * 16);
-        dst_off[i] = (uint32_t)(r * ROW_PITCH + ch * 16);
+        dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
+                             : (uint32_t)(r * 128 + ((((ch - 1) >> 1) ^ (r & 3)) << 5) + ((ch - 1) & 1) * 16);
     }
     const int nb_w = warp < KB ? (KB - warp + WARPS - 1) / WARPS : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -125,113 +228,33 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        issue(s);  // the first weights are on their way while the activations are prepared
+        issue(s);  // the first weights are on their way before the activation image is complete
     }
 
-    // ---- activations -> digit fragments in shared memory -------------------------------------------------------
+    // ---- activation image: wait for the kernel that writes it, then copy it into shared memory -----------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     {
-        const int octs = (int)(v.k >> 3);  // groups of 8 consecutive activations
-        float am[MT];
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-            am[m] = 0.0f;
+        const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+        const int chunks = (int)((size_t)KB * C::PB / 16);
+        for (int c = tid; c < chunks; c += THREADS) {
+            cp_async16(img_s + (uint32_t)c * 16u, image + (size_t)c * 16);
         }
-        for (int q = tid; q < 2 * octs; q += THREADS) {
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                if (m < rows) {
-                    const float4 xv = __ldg(reinterpret_cast<const float4*>(x + (int64_t)m * v.k) + q);
-                    am[m] = fmaxf(am[m], fmaxf(fmaxf(fabsf(xv.x), fabsf(xv.y)), fmaxf(fabsf(xv.z), fabsf(xv.w))));
-                }
-            }
-        }
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                am[m] = fmaxf(am[m], __shfl_xor_sync(0xffffffffu, am[m], o));
-            }
-            if (lane == 0) {
-                amax_s[warp * MT + m] = am[m];
-            }
-        }
-        __syncthreads();
-        if (tid < MT) {
-            float a = 0.0f;
-            for (int w = 0; w < WARPS; w++) {
-                a = fmaxf(a, amax_s[w * MT + tid]);
-            }
-            // s = 2^floor(log2(amax)): the largest |x| / s lies in [1, 2)
-            uint32_t e = __float_as_uint(a) & 0x7f800000u;
-            e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s a normal float
-            scale_s[tid] = __uint_as_float(e);
-        }
-        __syncthreads();
-        // thread -> one octet (8 activations, the k-slots of one lane in one sub-block MMA) of one activation row
-        for (int q = tid; q < octs; q += THREADS) {
-            const int blk = q >> 5, o = q & 31;  // 32 octets per super-block
-            const int sub = o >> 2, tt = o & 3;  // sub-block and lane slot: elements 32 sub + 8 tt + 0..7
-            // element order inside the block: sub-block 2j + hf covers elements 64 j + 32 hf + l
-            uint2* frag = xd + ((size_t)(blk * 8 + sub) * NG) * NCOL * 4 + tt;
-            uint32_t* fmin = xm + ((size_t)blk * NGM) * NCOLM * 4 + (sub >> 2);
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                int X[8];
-                if (m < rows) {
-                    const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * v.k) + 2 * q;
-                    const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
-                    // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
-                    const float inv = __uint_as_float(0x7f000000u - __float_as_uint(scale_s[m]) + (21u << 23));
-                    X[0] = __float2int_rn(lo.x * inv); X[1] = __float2int_rn(lo.y * inv);
-                    X[2] = __float2int_rn(lo.z * inv); X[3] = __float2int_rn(lo.w * inv);
-                    X[4] = __float2int_rn(hi.x * inv); X[5] = __float2int_rn(hi.y * inv);
-                    X[6] = __float2int_rn(hi.z * inv); X[7] = __float2int_rn(hi.w * inv);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        X[i] = 0;
-                    }
-                }
-#pragma unroll
-                for (int dgt = 0; dgt < 3; dgt++) {
-                    uint32_t w0 = 0, w1 = 0;
-                    int sum = 0;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
-                        X[i] = (X[i] - d) >> 8;
-                        sum += d;
-                        if (i < 4) {
-                            w0 |= (uint32_t)(d & 0xff) << (8 * i);
-                        } else {
-                            w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
-                        }
-                    }
-                    const int col = 3 * m + dgt;
-                    frag[((size_t)(col >> 3) * NCOL + (col & 7)) * 4] = make_uint2(w0, w1);
-                    // digit sum of the whole sub-block: the 4 octets of a sub-block sit in 4 consecutive lanes
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    if (tt == 0) {
-                        const int lo7 = sum & 127, hi = (sum - lo7) >> 7;  // sum = 128 hi + lo7, both fit a signed byte
-#pragma unroll
-                        for (int p = 0; p < 2; p++) {
-                            const int mc = 2 * col + p;
-                            uint8_t* dst = reinterpret_cast<uint8_t*>(fmin + ((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 4) + (sub & 3);
-                            *dst = (uint8_t)(p == 0 ? lo7 : hi);
-                        }
-                    }
-                }
-            }
-        }
+        cp_async_commit();
+        cp_async_wait<0>();
         __syncthreads();
     }
 
     // ---- main loop ----------------------------------------------------------------------------------------------
-    // Lanes whose column is not stored read another lane's fragment; their results get weight zero below.
-    const uint2* xd_lane = xd + (size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t;
-    const uint32_t* xm_lane = xm + (size_t)(NCOLM == 8 ? g : g % NCOLM) * 4 + (t & 1);
-    float acc[NG][2][2];   // [group][row g / g + 8][column 2t / 2t + 1], in units of 2^-21 * 256^digit
+    // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
+    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 8;
+    const uint8_t* xm_lane = img + C::XD + ((size_t)(NCOLM == 8 ? g : g % NCOLM) * 2 + (t & 1)) * 4;
+    const uint8_t* tab_lane = img + C::XD + C::XM;
+    uint32_t qoff[4];  // this lane's 8 bytes of group j inside a row of the slot
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        qoff[j] = (uint32_t)(((j ^ (g & 3)) << 5) + 8 * t);
+    }
+    float acc[NG][2][2];   // [group][row g / g + 8][column 2t / 2t + 1]
     float accm[NGM][2];    // mins, [group][row]
 #pragma unroll
     for (int i = 0; i < NG; i++) {
@@ -243,9 +266,10 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
     }
 
     auto compute = [&](const uint8_t* slot, int b) {
-        const uint8_t* q0 = slot + g * ROW_PITCH;
-        const uint8_t* q1 = q0 + 8 * ROW_PITCH;
-        const uint4 h0 = *reinterpret_cast<const uint4*>(q0), h1 = *reinterpret_cast<const uint4*>(q1);
+        const uint8_t* q0 = slot + g * 128;
+        const uint8_t* q1 = q0 + 8 * 128;
+        const uint4 h0 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + g * 16);
+        const uint4 h1 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + (g + 8) * 16);
         // 6-bit scales and mins of the 8 sub-blocks as packed bytes: [0..3] and [4..7]
         const uint32_t sc0a = h0.y & 0x3f3f3f3fu, sc0b = and_or(h0.y >> 2, 0x30303030u, h0.w & 0x0f0f0f0fu);
         const uint32_t sc1a = h1.y & 0x3f3f3f3fu, sc1b = and_or(h1.y >> 2, 0x30303030u, h1.w & 0x0f0f0f0fu);
@@ -256,12 +280,12 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
         for (int i = 0; i < NG; i++) {
             I[i][0] = I[i][1] = I[i][2] = I[i][3] = 0;
         }
-        const uint2* fb = xd_lane + (size_t)b * (8 * NG * NCOL * 4);
+        const uint8_t* blk = xd_lane + (size_t)b * C::PB;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             // this lane's 8 bytes of group j for rows g and g + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
-            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + 16 + 32 * j + 8 * t);
-            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + 16 + 32 * j + 8 * t);
+            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + qoff[j]);
+            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + qoff[j]);
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
                 const int sub = 2 * j + hf;
@@ -273,7 +297,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
                 const int s1 = (int)__byte_perm(sub < 4 ? sc1a : sc1b, 0u, 0x4440u + (sub & 3));
 #pragma unroll
                 for (int i = 0; i < NG; i++) {
-                    const uint2 bf = fb[(sub * NG + i) * NCOL * 4];
+                    const uint2 bf = *reinterpret_cast<const uint2*>(blk + (size_t)((sub * NG + i) * NCOL) * 32);
                     int D[4];
                     imma_k32(D, a0, a1, a2, a3, bf.x, bf.y);
                     I[i][0] += s0 * D[0];
@@ -285,25 +309,27 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
         }
         const float d0 = half_bits_to_float(h0.x), d1 = half_bits_to_float(h1.x);
         const float dm0 = half_bits_to_float(h0.x >> 16), dm1 = half_bits_to_float(h1.x >> 16);
+        const uint8_t* tb = tab_lane + (size_t)b * C::PB;
 #pragma unroll
         for (int i = 0; i < NG; i++) {
-            acc[i][0][0] = fmaf(d0, (float)I[i][0], acc[i][0][0]);
-            acc[i][0][1] = fmaf(d0, (float)I[i][1], acc[i][0][1]);
-            acc[i][1][0] = fmaf(d1, (float)I[i][2], acc[i][1][0]);
-            acc[i][1][1] = fmaf(d1, (float)I[i][3], acc[i][1][1]);
+            const float2 w = *reinterpret_cast<const float2*>(tb + (8 * i + 2 * t) * 4);  // weights of columns 2t, 2t+1
+            acc[i][0][0] = fmaf(d0 * w.x, (float)I[i][0], acc[i][0][0]);
+            acc[i][0][1] = fmaf(d0 * w.y, (float)I[i][1], acc[i][0][1]);
+            acc[i][1][0] = fmaf(d1 * w.x, (float)I[i][2], acc[i][1][0]);
+            acc[i][1][1] = fmaf(d1 * w.y, (float)I[i][3], acc[i][1][1]);
         }
-        const uint32_t* fm = xm_lane + (size_t)b * (NGM * NCOLM * 4);
+        const uint8_t* fm = xm_lane + (size_t)b * C::PB;
 #pragma unroll
         for (int i = 0; i < NGM; i++) {
             int E[4];
-            imma_k16(E, mn0, mn1, fm[i * NCOLM * 4]);
-            accm[i][0] = fmaf(dm0, (float)(E[1] * 128 + E[0]), accm[i][0]);
-            accm[i][1] = fmaf(dm1, (float)(E[3] * 128 + E[2]), accm[i][1]);
+            imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)i * NCOLM * 8));
+            const float w = *reinterpret_cast<const float*>(tb + ((4 * i + t) & (8 * NG - 1)) * 4);  // weight of digit column 4i + t
+            accm[i][0] = fmaf(dm0 * w, (float)(E[1] * 128 + E[0]), accm[i][0]);
+            accm[i][1] = fmaf(dm1 * w, (float)(E[3] * 128 + E[2]), accm[i][1]);
         }
     };
 
-    // digit weights of this lane's accumulator columns (0 for columns that hold no activation row)
-    float wq[NG][2], wm[NGM];
+    // activation row each accumulator column of this lane belongs to (-1: none)
     int mq[NG][2], mmn[NGM];
 #pragma unroll
     for (int i = 0; i < NG; i++) {
@@ -311,14 +337,12 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
         for (int c = 0; c < 2; c++) {
             const int col = 8 * i + 2 * t + c;
             mq[i][c] = col < C::COLS ? col / 3 : -1;
-            wq[i][c] = col < C::COLS ? __uint_as_float((uint32_t)(127 - 21 + 8 * (col % 3)) << 23) : 0.0f;
         }
     }
 #pragma unroll
     for (int i = 0; i < NGM; i++) {
-        const int col = 4 * i + t;  // digit column whose two parts this lane holds
+        const int col = 4 * i + t;  // digit column whose two sum parts this lane holds
         mmn[i] = col < C::COLS ? col / 3 : -1;
-        wm[i] = col < C::COLS ? __uint_as_float((uint32_t)(127 - 21 + 8 * (col % 3)) << 23) : 0.0f;
     }
 
     int parity = 0;
@@ -342,16 +366,16 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
 #pragma unroll
                 for (int c = 0; c < 2; c++) {
                     if (mq[i][c] == m) {
-                        p0 = fmaf(acc[i][0][c], wq[i][c], p0);
-                        p1 = fmaf(acc[i][1][c], wq[i][c], p1);
+                        p0 += acc[i][0][c];
+                        p1 += acc[i][1][c];
                     }
                 }
             }
 #pragma unroll
             for (int i = 0; i < NGM; i++) {
                 if (mmn[i] == m) {
-                    p0 = fmaf(-accm[i][0], wm[i], p0);
-                    p1 = fmaf(-accm[i][1], wm[i], p1);
+                    p0 -= accm[i][0];
+                    p1 -= accm[i][1];
                 }
             }
             p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
@@ -380,7 +404,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemv_q4k_i8_kernel(View v, const f
                 const float* p = rd + r * MT + m;
                 const float s = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
                                 ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
-                y[(int64_t)m * n + row] = s * scale_s[m] + (bias != nullptr ? bias[row] : 0.0f);
+                y[(int64_t)m * n + row] = s + (bias != nullptr ? bias[row] : 0.0f);
             }
         }
         parity ^= 1;
@@ -402,53 +426,89 @@ int sm_count() {
 
 template <int MT, int STAGES>
 size_t smem_bytes(int KB) {
-    using C = Cfg<MT>;
-    return (size_t)KB * (C::XD + C::XM) + (size_t)(2 * WARPS * 16 * MT + WARPS * MT + 4) * sizeof(float) + (size_t)WARPS * STAGES * SLOT_BYTES;
+    return (size_t)KB * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (size_t)WARPS * STAGES * SLOT_BYTES;
 }
 
-template <int MT, int STAGES>
-int launch(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s) {
+template <int MT, int STAGES, int OCC>
+int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s) {
     const size_t smem = smem_bytes<MT, STAGES>((int)(v.k / 256));
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16);
-    const int per_sm = smem > SMEM_MAX / 2 - 1024 ? 1 : 2;
-    const int grid = tiles < sm_count() * per_sm ? tiles : sm_count() * per_sm;
-    gemv_q4k_i8_kernel<MT, STAGES><<<grid, THREADS, smem, s>>>(v, x, rows, bias, y, tiles);
+    const int grid = tiles < sm_count() * OCC ? tiles : sm_count() * OCC;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the activation kernel runs
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles));
     count_launch();
-    return check_launch("gemv_q4k_i8_kernel");
+    return JQ_OK;
 }
 
 template <int MT>
-int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     const int KB = (int)(v.k / 256);
-    const size_t half = SMEM_MAX / 2 - 1024;  // two CTAs per SM
+    const size_t third = SMEM_MAX / 3 - 1024, half = SMEM_MAX / 2 - 1024;  // per-CTA budgets for 3 and 2 CTAs per SM
+    int pick = 0;
+    if (smem_bytes<MT, 3>(KB) <= third) pick = 33;
+    else if (smem_bytes<MT, 4>(KB) <= half) pick = 42;
+    else if (smem_bytes<MT, 3>(KB) <= half) pick = 32;
+    else if (smem_bytes<MT, 4>(KB) <= SMEM_MAX) pick = 41;
+    else if (smem_bytes<MT, 2>(KB) <= SMEM_MAX) pick = 21;
+    if (pick == 0) {
+        *handled = false;  // the activation image does not fit in shared memory
+        return JQ_OK;
+    }
     *handled = true;
-    if (smem_bytes<MT, 4>(KB) <= half) return launch<MT, 4>(v, x, rows, bias, y, s);
-    if (smem_bytes<MT, 3>(KB) <= half) return launch<MT, 3>(v, x, rows, bias, y, s);
-    if (smem_bytes<MT, 4>(KB) <= SMEM_MAX) return launch<MT, 4>(v, x, rows, bias, y, s);
-    if (smem_bytes<MT, 2>(KB) <= SMEM_MAX) return launch<MT, 2>(v, x, rows, bias, y, s);
-    *handled = false;  // the activation image does not fit in shared memory
-    return JQ_OK;
+    q4k_activation_image_kernel<MT><<<(KB + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+    count_launch();
+    int rc = check_launch("q4k_activation_image_kernel");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    switch (pick) {
+        case 33: return launch<MT, 3, 3>(v, image, rows, bias, y, s);
+        case 42: return launch<MT, 4, 2>(v, image, rows, bias, y, s);
+        case 32: return launch<MT, 3, 2>(v, image, rows, bias, y, s);
+        case 41: return launch<MT, 4, 1>(v, image, rows, bias, y, s);
+        default: return launch<MT, 2, 1>(v, image, rows, bias, y, s);
+    }
 }
 
 }  // namespace
 
-// Q4_K with rows in [1, 4] on a weight whose buffer is padded by 16 rows. *handled = false leaves the call
-// to another kernel.
-int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled) {
+// Bytes of scratch (activation image) a Q4_K GEMV of `rows` activation rows over k inputs needs; 0 if the
+// shape is not handled by the integer kernel.
+size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
+    if (rows < 1 || rows > 4 || k <= 0) {
+        return 0;
+    }
+    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : Cfg<4>::PB);
+    return (size_t)(k / 256) * pb;
+}
+
+// Q4_K with rows in [1, 4] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
+// gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
+// *handled = false leaves the call to another kernel.
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     *handled = false;
-    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 4 || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
+    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 4 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
         return JQ_OK;
     }
-    if (rows == 1) return run<1>(v, x, rows, bias, y, s, handled);
-    if (rows == 2) return run<2>(v, x, rows, bias, y, s, handled);
-    return run<4>(v, x, rows, bias, y, s, handled);
+    if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
+    return run<4>(v, x, rows, bias, y, s, image, handled);
 }
 
 }  // namespace jq
