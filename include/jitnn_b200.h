@@ -115,7 +115,7 @@ JQ_API int jq_dequantize(const jq_weight* w, float* dst, int dst_mem, void* stre
  * Quant.linear / F.linearQ8 (ops/Quant.java:66-80): any m >= 0 (leading axes of x flattened by the
  * caller as ops/Gguf.java:86-93 does), bias may be NULL. Rows are dispatched like the reference
  * dispatches them (ops/Gguf.java:90): m <= 16 to the fused dequantise-GEMV kernels, larger m in
- * groups of 16 rows through the same kernels unless the tensor-core prefill path is selected with
+ * groups of up to 16 rows through the same kernels unless the tensor-core prefill path is selected with
  * jq_set_option. `mem` says where x, bias and y live (all three alike); with JQ_MEM_DEVICE they must
  * be 16-byte aligned and `stream` is the CUDA stream (cudaStream_t, NULL = default stream).
  */
@@ -144,7 +144,6 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "prefill_min_rows"  rows of x from which jq_linear_f32 rounds x to bfloat16 and uses the
  *                       tensor-core prefill kernel (default 0 = never: FP32 results for every m).
  *   "gemv_generic"      non-zero: every decode GEMV runs on the generic CUDA-core kernel (for comparisons).
- *   "gemv_q4k_fp16"     non-zero: Q4_K keeps the fp16 tensor-core GEMV also for m <= 4 (for comparisons).
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);

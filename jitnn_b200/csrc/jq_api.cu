@@ -157,13 +157,14 @@ static const char* type_name(int type) {
 // ---- options ------------------------------------------------------------------------------------
 static std::atomic<int64_t> g_prefill_min_rows{0};
 std::atomic<int64_t> g_opt_gemv_generic{0};
-std::atomic<int64_t> g_opt_q4k_fp16{0};
 
 // ---- linear on device pointers --------------------------------------------------------------------
 static int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
     View v = view_of(w);
-    for (int64_t m0 = 0; m0 < m; m0 += 16) {
-        int rows = (int)(m - m0 < 16 ? m - m0 : 16);
+    // Q4_K's integer tensor-core kernel takes up to 8 activation rows per pass, the other kernels 16.
+    const int64_t group = (w->type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load() == 0) ? 8 : 16;
+    for (int64_t m0 = 0; m0 < m; m0 += group) {
+        int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
         if (rc != JQ_OK) {
             return rc;
@@ -526,10 +527,6 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_gemv_generic.store(value != 0);
         return JQ_OK;
     }
-    if (name != nullptr && strcmp(name, "gemv_q4k_fp16") == 0) {
-        g_opt_q4k_fp16.store(value != 0);
-        return JQ_OK;
-    }
     return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);
 }
 
@@ -540,10 +537,6 @@ int jq_get_option(const char* name, int64_t* value) {
     }
     if (name != nullptr && value != nullptr && strcmp(name, "gemv_generic") == 0) {
         *value = g_opt_gemv_generic.load();
-        return JQ_OK;
-    }
-    if (name != nullptr && value != nullptr && strcmp(name, "gemv_q4k_fp16") == 0) {
-        *value = g_opt_q4k_fp16.load();
         return JQ_OK;
     }
     return fail(JQ_ERR_INVALID, "unknown option '%s'", name == nullptr ? "(null)" : name);

@@ -97,10 +97,7 @@ int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verba
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
 int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
-// Tensor-core GEMV for Q4_K; *handled = false leaves the call to the generic kernel.
-int launch_gemv_q4k_mma(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool* handled);
-
-// Integer tensor-core GEMV for Q4_K, rows <= 4; needs the 16 padding rows every uploaded weight has.
+// Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 
@@ -113,8 +110,6 @@ constexpr int PAD_ROWS = 16;
 
 // Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_generic;
-// Option "gemv_q4k_fp16": non-zero keeps Q4_K on the fp16 tensor-core kernel for every row count.
-extern std::atomic<int64_t> g_opt_q4k_fp16;
 
 }  // namespace jq
 

@@ -92,20 +92,14 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
     if (v.n == 0) {
         return JQ_OK;
     }
-    if (v.type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+    if (v.type == JQ_TYPE_Q4_K && rows <= 8 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
         bool handled = false;
-        if (rows <= 4 && g_opt_q4k_fp16.load(std::memory_order_relaxed) == 0) {
-            const size_t need = gemv_q4k_i8_scratch_bytes(v.k, rows);
-            uint8_t* image = nullptr;
-            int rc = need > 0 ? scratch_for(s, need, &image) : JQ_OK;
-            if (rc == JQ_OK) {
-                rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, image, &handled);
-            }
-            if (rc != JQ_OK || handled) {
-                return rc;
-            }
+        const size_t need = gemv_q4k_i8_scratch_bytes(v.k, rows);
+        uint8_t* image = nullptr;
+        int rc = need > 0 ? scratch_for(s, need, &image) : JQ_OK;
+        if (rc == JQ_OK) {
+            rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, image, &handled);
         }
-        int rc = launch_gemv_q4k_mma(v, x, rows, bias, y, s, &handled);
         if (rc != JQ_OK || handled) {
             return rc;
         }

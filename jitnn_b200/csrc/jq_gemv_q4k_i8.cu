@@ -1,4 +1,4 @@
-// Decode GEMV for Q4_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 4.
+// Decode GEMV for Q4_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 8.
 //
 // The 4-bit quants never become floating point. A small first kernel turns the activations into an
 // "activation image" in a scratch buffer: per 256-element super-block of k and per row of x, the values
@@ -178,14 +178,20 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
 // ---- the GEMV ---------------------------------------------------------------------------------------------------
 template <int MT, int STAGES, int OCC>
 __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
-                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles) {
+                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles,
+                                                                  int KS, int max_tiles) {
+    // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
+    // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int KB = (int)(v.k >> 8);
-    uint8_t* img = smem_raw;                                                         // [KB][PB]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KB * C::PB);            // [2][WARPS][16][MT]
-    uint8_t* ring = reinterpret_cast<uint8_t*>(red + 2 * WARPS * 16 * MT) + (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
+    const int nslices = (KB + KS - 1) / KS;
+    uint8_t* img = smem_raw;                                                         // [KS][PB]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][WARPS][16][MT]
+    float* carry = red + 2 * WARPS * 16 * MT;                                        // [max_tiles][16][MT], only if nslices > 1
+    uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) +
+                    (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -204,13 +210,24 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
                              : (uint32_t)(r * 128 + ((((ch - 1) >> 1) ^ (r & 3)) << 5) + ((ch - 1) & 1) * 16);
     }
-    const int nb_w = warp < KB ? (KB - warp + WARPS - 1) / WARPS : 0;
+    // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + 8 i.
+    auto blocks_of = [&](int sl) {  // number of super-blocks this warp has in slice sl
+        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
+        return warp < len ? (len - warp + WARPS - 1) / WARPS : 0;
+    };
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int steps = nb_w * my_tiles;
-    int iss_tile = blockIdx.x, iss_j = 0;
+    int steps = 0;
+    for (int sl = 0; sl < nslices; sl++) {
+        steps += blocks_of(sl) * my_tiles;
+    }
+    int iss_sl = 0, iss_ti = 0, iss_j = 0;
+    while (iss_sl < nslices && blocks_of(iss_sl) == 0) {
+        iss_sl++;
+    }
     auto issue = [&](int s) {
         if (s < steps) {
-            const uint8_t* base = v.q + (int64_t)iss_tile * 16 * row_bytes + (uint32_t)(warp + WARPS * iss_j) * 144u;
+            const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
+            const uint8_t* base = v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)(iss_sl * KS + warp + WARPS * iss_j) * 144u;
             const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -219,9 +236,14 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
             if (lane < 16) {
                 cp_async16(slot + dst_off[4], base + src_off[4]);
             }
-            if (++iss_j == nb_w) {
+            if (++iss_j == blocks_of(iss_sl)) {
                 iss_j = 0;
-                iss_tile += gridDim.x;
+                if (++iss_ti == my_tiles) {
+                    iss_ti = 0;
+                    do {
+                        iss_sl++;
+                    } while (iss_sl < nslices && blocks_of(iss_sl) == 0);
+                }
             }
         }
         cp_async_commit();
@@ -231,18 +253,9 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         issue(s);  // the first weights are on their way before the activation image is complete
     }
 
-    // ---- activation image: wait for the kernel that writes it, then copy it into shared memory -----------------
+    // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    {
-        const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
-        const int chunks = (int)((size_t)KB * C::PB / 16);
-        for (int c = tid; c < chunks; c += THREADS) {
-            cp_async16(img_s + (uint32_t)c * 16u, image + (size_t)c * 16);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-    }
+    const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
 
     // ---- main loop ----------------------------------------------------------------------------------------------
     // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
@@ -265,7 +278,7 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         accm[i][0] = accm[i][1] = 0.0f;
     }
 
-    auto compute = [&](const uint8_t* slot, int b) {
+    auto compute = [&](const uint8_t* slot, int b) {  // b = super-block index inside the resident slice
         const uint8_t* q0 = slot + g * 128;
         const uint8_t* q1 = q0 + 8 * 128;
         const uint4 h0 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + g * 16);
@@ -323,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         for (int i = 0; i < NGM; i++) {
             int E[4];
             imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)i * NCOLM * 8));
-            const float w = *reinterpret_cast<const float*>(tb + ((4 * i + t) & (8 * NG - 1)) * 4);  // weight of digit column 4i + t
+            const float w = *reinterpret_cast<const float*>(tb + (4 * i + t) * 4);  // weight of digit column 4i + t
             accm[i][0] = fmaf(dm0 * w, (float)(E[1] * 128 + E[0]), accm[i][0]);
             accm[i][1] = fmaf(dm1 * w, (float)(E[3] * 128 + E[2]), accm[i][1]);
         }
@@ -347,67 +360,90 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
 
     int parity = 0;
     int step = 0;
-    for (int my_tile = blockIdx.x; my_tile < tiles; my_tile += gridDim.x) {
-        for (int b = warp; b < KB; b += WARPS) {
-            __syncwarp();                 // every lane is done reading the slot that is requested next
-            issue(step + STAGES - 1);
-            cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
-            __syncwarp();                 // ... and so have the other lanes'
-            compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, b);
-            step++;
+    for (int sl = 0; sl < nslices; sl++) {
+        // ---- bring this slice of the activation image into shared memory ---------------------------------------------
+        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
+        if (sl > 0) {
+            __syncthreads();  // every warp is done with the previous slice
         }
-        // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
-        float* rd = red + (size_t)parity * WARPS * 16 * MT;
+        {
+            const uint8_t* src = image + (size_t)sl * KS * C::PB;
+            const int chunks = (int)((size_t)len * C::PB / 16);
+            for (int c = tid; c < chunks; c += THREADS) {
+                cp_async16(img_s + (uint32_t)c * 16u, src + (size_t)c * 16);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+        }
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
+            for (int b = warp; b < len; b += WARPS) {
+                __syncwarp();                 // every lane is done reading the slot that is requested next
+                issue(step + STAGES - 1);
+                cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+                __syncwarp();                 // ... and so have the other lanes'
+                compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, b);
+                step++;
+            }
+            // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
+            float* rd = red + (size_t)parity * WARPS * 16 * MT;
 #pragma unroll
-        for (int m = 0; m < MT; m++) {
-            float p0 = 0.0f, p1 = 0.0f;
+            for (int m = 0; m < MT; m++) {
+                float p0 = 0.0f, p1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NG; i++) {
+                for (int i = 0; i < NG; i++) {
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    if (mq[i][c] == m) {
-                        p0 += acc[i][0][c];
-                        p1 += acc[i][1][c];
+                    for (int c = 0; c < 2; c++) {
+                        if (mq[i][c] == m) {
+                            p0 += acc[i][0][c];
+                            p1 += acc[i][1][c];
+                        }
                     }
                 }
+#pragma unroll
+                for (int i = 0; i < NGM; i++) {
+                    if (mmn[i] == m) {
+                        p0 -= accm[i][0];
+                        p1 -= accm[i][1];
+                    }
+                }
+                p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+                p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+                p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+                p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+                if (t == 0) {
+                    rd[(warp * 16 + g) * MT + m] = p0;
+                    rd[(warp * 16 + g + 8) * MT + m] = p1;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
             }
 #pragma unroll
             for (int i = 0; i < NGM; i++) {
-                if (mmn[i] == m) {
-                    p0 -= accm[i][0];
-                    p1 -= accm[i][1];
+                accm[i][0] = accm[i][1] = 0.0f;
+            }
+            __syncthreads();
+            // ---- the 8 warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
+            for (int o = tid; o < 16 * MT; o += THREADS) {
+                const int r = o / MT, m = o % MT;
+                const int64_t row = (int64_t)my_tile * 16 + r;
+                const float* p = rd + r * MT + m;
+                float sum = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
+                            ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
+                if (sl > 0) {
+                    sum += carry[(size_t)ti * 16 * MT + o];
+                }
+                if (sl + 1 < nslices) {
+                    carry[(size_t)ti * 16 * MT + o] = sum;
+                } else if (m < rows && row < n) {
+                    y[(int64_t)m * n + row] = sum + (bias != nullptr ? bias[row] : 0.0f);
                 }
             }
-            p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
-            p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
-            p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
-            p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
-            if (t == 0) {
-                rd[(warp * 16 + g) * MT + m] = p0;
-                rd[(warp * 16 + g + 8) * MT + m] = p1;
-            }
+            parity ^= 1;
         }
-#pragma unroll
-        for (int i = 0; i < NG; i++) {
-            acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < NGM; i++) {
-            accm[i][0] = accm[i][1] = 0.0f;
-        }
-        __syncthreads();
-        // ---- the 8 warps' partial sums in a fixed order ------------------------------------------------------------------
-        for (int o = tid; o < 16 * MT; o += THREADS) {
-            const int r = o / MT, m = o % MT;
-            const int64_t row = (int64_t)my_tile * 16 + r;
-            if (m < rows && row < n) {
-                const float* p = rd + r * MT + m;
-                const float s = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
-                                ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
-                y[(int64_t)m * n + row] = s + (bias != nullptr ? bias[row] : 0.0f);
-            }
-        }
-        parity ^= 1;
     }
 }
 
@@ -424,14 +460,8 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT, int STAGES>
-size_t smem_bytes(int KB) {
-    return (size_t)KB * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (size_t)WARPS * STAGES * SLOT_BYTES;
-}
-
 template <int MT, int STAGES, int OCC>
-int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s) {
-    const size_t smem = smem_bytes<MT, STAGES>((int)(v.k / 256));
+int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
@@ -440,7 +470,6 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16);
-    const int grid = tiles < sm_count() * OCC ? tiles : sm_count() * OCC;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(THREADS);
@@ -451,23 +480,56 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
+}
+
+// Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
+template <int MT>
+size_t smem_bytes(int KS, int stages, bool sliced, int max_tiles) {
+    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+           (size_t)WARPS * stages * SLOT_BYTES;
 }
 
 template <int MT>
 int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     const int KB = (int)(v.k / 256);
-    const size_t third = SMEM_MAX / 3 - 1024, half = SMEM_MAX / 2 - 1024;  // per-CTA budgets for 3 and 2 CTAs per SM
-    int pick = 0;
-    if (smem_bytes<MT, 3>(KB) <= third) pick = 33;
-    else if (smem_bytes<MT, 4>(KB) <= half) pick = 42;
-    else if (smem_bytes<MT, 3>(KB) <= half) pick = 32;
-    else if (smem_bytes<MT, 4>(KB) <= SMEM_MAX) pick = 41;
-    else if (smem_bytes<MT, 2>(KB) <= SMEM_MAX) pick = 21;
-    if (pick == 0) {
-        *handled = false;  // the activation image does not fit in shared memory
+    const int tiles = (int)((v.n + 15) / 16);
+    // Candidate shapes, best first: (CTAs per SM, ring stages). The slice length KS is a function of MT and k only (so
+    // that the summation order never depends on n): the whole k if its image fits beside the ring, else a multiple of 8.
+    const int occ_of[3] = {3, 2, 2}, st_of[3] = {3, 4, 3};
+    const size_t fixed = (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + 8 * 1024;  // reduction buffer + room for carried sums
+    int pick = -1, KS = KB;
+    for (int c = 0; c < 3 && pick < 0; c++) {
+        const size_t budget = SMEM_MAX / occ_of[c] - 1024;
+        if ((size_t)KB * Cfg<MT>::PB + fixed + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
+            pick = c;
+        }
+    }
+    int stages = pick >= 0 ? st_of[pick] : 0;
+    if (pick < 0) {
+        // slices: two CTAs per SM, three ring stages, or two if a slice of 8 super-blocks needs the room
+        pick = 2;
+        for (stages = 3; stages >= 2; stages--) {
+            const size_t budget = SMEM_MAX / 2 - 1024 - fixed - (size_t)WARPS * stages * SLOT_BYTES;
+            KS = (int)(budget / Cfg<MT>::PB) / 8 * 8;
+            if (KS >= 8) {
+                break;
+            }
+        }
+        if (KS < 8) {
+            *handled = false;
+            return JQ_OK;
+        }
+    }
+    const int occ = occ_of[pick];
+    const int grid = tiles < sm_count() * occ ? tiles : sm_count() * occ;
+    const int max_tiles = (tiles + grid - 1) / grid;
+    const bool sliced = KS < KB;
+    const size_t smem = smem_bytes<MT>(KS, stages, sliced, max_tiles);
+    if (smem > SMEM_MAX / occ - 1024) {
+        *handled = false;  // more tiles per CTA than the carried sums have room for
         return JQ_OK;
     }
     *handled = true;
@@ -477,13 +539,10 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
     if (rc != JQ_OK) {
         return rc;
     }
-    switch (pick) {
-        case 33: return launch<MT, 3, 3>(v, image, rows, bias, y, s);
-        case 42: return launch<MT, 4, 2>(v, image, rows, bias, y, s);
-        case 32: return launch<MT, 3, 2>(v, image, rows, bias, y, s);
-        case 41: return launch<MT, 4, 1>(v, image, rows, bias, y, s);
-        default: return launch<MT, 2, 1>(v, image, rows, bias, y, s);
-    }
+    if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    if (stages == 3) return launch<MT, 3, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    return launch<MT, 2, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
 }
 
 }  // namespace
@@ -491,24 +550,25 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
 // Bytes of scratch (activation image) a Q4_K GEMV of `rows` activation rows over k inputs needs; 0 if the
 // shape is not handled by the integer kernel.
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
-    if (rows < 1 || rows > 4 || k <= 0) {
+    if (rows < 1 || rows > 8 || k <= 0) {
         return 0;
     }
-    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : Cfg<4>::PB);
+    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : (rows <= 4 ? Cfg<4>::PB : Cfg<8>::PB));
     return (size_t)(k / 256) * pb;
 }
 
-// Q4_K with rows in [1, 4] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
+// Q4_K with rows in [1, 8] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
 // gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
 // *handled = false leaves the call to another kernel.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     *handled = false;
-    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 4 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
+    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
         return JQ_OK;
     }
     if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
     if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
-    return run<4>(v, x, rows, bias, y, s, image, handled);
+    if (rows <= 4) return run<4>(v, x, rows, bias, y, s, image, handled);
+    return run<8>(v, x, rows, bias, y, s, image, handled);
 }
 
 }  // namespace jq
