@@ -148,6 +148,25 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);
 
+/*
+ * y[m, n] = x[m, k] * W^T (+ bias[n]) for a Q4_K weight, 1 <= m <= 8, device pointers only (16-byte aligned),
+ * enqueued on `stream`: the same kernels and the same results as jq_linear_f32, but the call allocates no
+ * memory. It has no counterpart in the reference. jq_linear_f32 keeps its intermediate "activation image" in a
+ * buffer it allocates with cudaMalloc when a stream first needs one; this entry point is for callers that
+ * cannot have that happen: a process that has already given all device memory to its own pools (the allocation
+ * would fail), or a latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives
+ * in a 1 MiB array that is part of the library itself, so every GPU that loads the library holds that 1 MiB
+ * until the process exits. Limits: the image, (k / 256) * 848 bytes for one row, 1696 for two, 4352 for three or
+ * four and 6624 for five to eight rows, must fit 1 MiB (for example k <= 40448 at eight rows); anything larger, any
+ * other format and any other row count is refused with JQ_ERR_INVALID or JQ_ERR_UNSUPPORTED and a message.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call before starting any stream capture. All calls share the one array, which keeps
+ * whatever the last call left in it; every call rewrites the part it reads, nothing has to start at zero.
+ * Two calls that overlap on the GPU (different streams, or different host threads without ordering) race on it:
+ * serialise them.
+ */
+JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, void* stream);
+
 /* Pinned host memory for activations and results (faster and truly asynchronous copies). */
 JQ_API int jq_host_alloc(void** ptr, int64_t nbytes);
 JQ_API int jq_host_free(void* ptr);
