@@ -61,7 +61,7 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons every 50 ms from its creation until stop()."""
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -69,7 +69,7 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -80,9 +80,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 7:
-                self.rows.append(parts)
+                self.rows.append((time.time(), parts))
 
-    def stop(self):
+    def stop(self, t0, t1):
+        """Summary over the samples taken in [t0, t1] (the timed region); if the region was too short to
+        catch one, over the samples of the whole run under load, and `window` says so."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -90,18 +92,24 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        inside = [r for ts, r in self.rows if t0 <= ts <= t1 + 0.05]
+        window = "timed region"
+        if not inside:
+            inside = [r for ts, r in self.rows]
+            window = "whole run (timed region shorter than the sampling period)"
+        sm, mx, power, reasons = [], [], [], set()
+        for r in inside:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                power.append(float(r[2]))
             except ValueError:
                 continue
             for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def make_weights(torch, device, rank, world):
@@ -124,6 +132,15 @@ def make_weights(torch, device, rank, world):
     return pools, first_raw
 
 
+def launches_per_step(L, step, side, torch, device):
+    """Kernels one eager step launches (the graph replays exactly these)."""
+    with torch.cuda.stream(side):
+        before = L.jq_launch_count()
+        step(0)
+        torch.cuda.synchronize(device)
+        return L.jq_launch_count() - before
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -142,8 +159,6 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     L = jitnn_b200.load()
-    stream = torch.cuda.current_stream(device)
-    sp = ctypes.c_void_p(stream.cuda_stream)
 
     pools, first_raw = make_weights(torch, device, rank, world)
     g = torch.Generator(device=device).manual_seed(99)
@@ -157,6 +172,7 @@ def run_ours(args):
                 gathered[(n, k, m)] = torch.empty(world, m, n // world, device=device)
 
     def step(i):
+        sp = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         for si, (n, k) in enumerate(SHAPES):
             for mi, m in enumerate(BATCHES):
                 w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
@@ -180,44 +196,87 @@ def run_ours(args):
         rel = float(np.abs(yh[:, :64] - ref).max() / np.abs(ref).max())
         assert rel <= 1e-3, "GEMV differs from the oracle: %g" % rel
 
-    for i in range(args.warmup):
-        step(i)
+    # The weight rotation repeats every `period` steps. On one GPU that many steps are captured into a CUDA graph
+    # (the launches of a step are a few microseconds each, less than the host needs to issue them) and the graph
+    # is replayed; with several ranks the steps are issued eagerly because each launch is followed by a collective.
+    period = POOL_COPIES // len(BATCHES) if POOL_COPIES % len(BATCHES) == 0 else POOL_COPIES
+    use_graph = world == 1 and not args.eager
+    side = torch.cuda.Stream(device)
+    graph = None
+    with torch.cuda.stream(side):
+        for i in range(args.warmup):
+            step(i)
+        torch.cuda.synchronize(device)
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(period):
+                    step(i)
+            for _ in range(3):
+                graph.replay()
     barrier()
+    timed_steps = args.steps if not use_graph else max(period, args.steps // period * period)
     sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        time.sleep(0.2)
+    t_start = time.time()
     launches0 = L.jq_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for i in range(args.steps):
-        step(args.warmup + i)
-    e1.record(stream)
+    with torch.cuda.stream(side):
+        e0.record(side)
+        if use_graph:
+            for _ in range(timed_steps // period):
+                graph.replay()
+        else:
+            for i in range(timed_steps):
+                step(args.warmup + i)
+        e1.record(side)
     barrier()
+    t_end = time.time()
     ms = e0.elapsed_time(e1)
-    launches = L.jq_launch_count() - launches0
+    # kernels of this library that ran in the timed region: counted at launch, or launches per captured step x replays
+    launches = (L.jq_launch_count() - launches0) if not use_graph else timed_steps * launches_per_step(L, step, side, torch, device)
     if world > 1:
         t = torch.tensor([ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    clocks = sampler.stop() if sampler else None
-    ms_per_step = ms / args.steps
+    clocks = sampler.stop(t_start, t_end) if sampler else None
+    ms_per_step = ms / timed_steps
+    args.steps = timed_steps
     value = step_bytes() / (ms_per_step * 1e-3) / 1e9
+    stream = torch.cuda.current_stream(device)
+    sp = ctypes.c_void_p(stream.cuda_stream)
 
-    # per-shape kernel times (device-resident, same rotation), for the roofline breakdown
+    # per-shape kernel times (device-resident, same rotation, graph replay), for the roofline breakdown
     per_shape = {}
     if world == 1:
-        for si, (n, k) in enumerate(SHAPES):
-            for m in BATCHES:
-                reps = 40
-                for r in range(4):
-                    _lib.check(L.jq_linear_f32(pools[si][r % POOL_COPIES]._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), 1, sp))
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize(device)
-                a.record(stream)
-                for r in range(reps):
-                    _lib.check(L.jq_linear_f32(pools[si][r % POOL_COPIES]._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), 1, sp))
-                b.record(stream)
-                torch.cuda.synchronize(device)
-                us = a.elapsed_time(b) * 1e3 / reps
-                per_shape["%dx%d_m%d" % (n, k, m)] = {"us": round(us, 3), "GBps": round(algorithmic_bytes(n, k, m) / us / 1e3, 1)}
+        with torch.cuda.stream(side):
+            sps = ctypes.c_void_p(side.cuda_stream)
+            for si, (n, k) in enumerate(SHAPES):
+                for m in BATCHES:
+                    def rot():
+                        for r in range(POOL_COPIES):
+                            _lib.check(L.jq_linear_f32(pools[si][r]._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), 1, sps))
+                    rot()
+                    torch.cuda.synchronize(device)
+                    reps = 10
+                    if use_graph:
+                        gs = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(gs, stream=side):
+                            rot()
+                        gs.replay()
+                    a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(device)
+                    a.record(side)
+                    for r in range(reps):
+                        if use_graph:
+                            gs.replay()
+                        else:
+                            rot()
+                    b2.record(side)
+                    torch.cuda.synchronize(device)
+                    us = a.elapsed_time(b2) * 1e3 / (reps * POOL_COPIES)
+                    per_shape["%dx%d_m%d" % (n, k, m)] = {"us": round(us, 3), "GBps": round(algorithmic_bytes(n, k, m) / us / 1e3, 1)}
 
     # end to end through the C ABI with host buffers (pinned), copies inside the timed region
     e2e = None
@@ -257,6 +316,7 @@ def run_ours(args):
                        "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32",
                        "l2": "every launch reads a different copy from a pool of %d copies per shape (%.0f MB > 126 MB L2)"
                              % (POOL_COPIES, POOL_COPIES * sum(n * k for n, k in SHAPES) * BYTES_PER_WEIGHT / 1e6),
+                       "launch": ("CUDA graph of %d steps, replayed" % period) if use_graph else "eager launches through the C ABI",
                        "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + NCCL all-gather per launch" % world},
             "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s", "frac": round(value / world / peak, 4),
                          "traffic": None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
@@ -306,7 +366,13 @@ def run_reference(args):
         return
     from oracle import oracle
     threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
-    fraction = max(1, 8 // threads)
+    # size the per-step sample so that the whole run stays within about two minutes: time rows [0, N/64) once,
+    # then take the largest power-of-two share of the rows that fits
+    probe = cpu_baseline_leg(threads=threads, fraction=64, steps=1, warmup=0)
+    total_steps = args.steps + min(args.warmup, 1)
+    fraction = 1
+    while fraction < 64 and probe["seconds_per_step"] * 64 / fraction * total_steps > 120.0:
+        fraction *= 2
     cpu = cpu_baseline_leg(threads=threads, fraction=fraction, steps=args.steps, warmup=min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
@@ -323,10 +389,11 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    ap.add_argument("--eager", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default=None, metavar="NxKxM",
                     help="restrict the sweep to one shape and batch, e.g. 32000x4096x1 (a small case for profiler captures)")
     args = ap.parse_args()

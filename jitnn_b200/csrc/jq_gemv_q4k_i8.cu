@@ -83,7 +83,8 @@ struct Cfg {
 };
 
 // ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
-// One warp per super-block of k; lane = octet (sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of that sub-block MMA).
+// One warp per (super-block of k, activation row); lane = octet: sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of
+// that sub-block's MMA. The kernel is tiny and latency bound, so the work is spread over as many warps as possible.
 constexpr int PREP_WARPS = 4;
 
 template <int MT>
@@ -93,86 +94,81 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
     constexpr int NG = C::NG, NCOL = C::NCOL, NCOLM = C::NCOLM;
     asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
     const int lane = threadIdx.x & 31;
-    const int b = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    const int b = pair / MT, m = pair % MT;
     if (b >= (int)(k >> 8)) {
         return;
     }
     const int sub = lane >> 2, tt = lane & 3;
     uint8_t* img = image + (size_t)b * C::PB;
     uint2* xd = reinterpret_cast<uint2*>(img);
-    uint32_t* xm = reinterpret_cast<uint32_t*>(img + C::XD);
+    uint8_t* xm = img + C::XD;
     float* tab = reinterpret_cast<float*>(img + C::XD + C::XM);
-    if (lane >= C::COLS && lane < NG * 8) {
+    if (m == 0 && lane >= C::COLS && lane < NG * 8) {
         tab[lane] = 0.0f;  // columns that hold no activation row
     }
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-        float xv[8];
-        if (m < rows) {
-            const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
-            const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
-            xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
-            xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                xv[i] = 0.0f;
-            }
-        }
-        float am = 0.0f;
+    float xv[8];
+    if (m < rows) {
+        const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
+        const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
+        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
+        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
+    } else {
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            am = fmaxf(am, fabsf(xv[i]));
+            xv[i] = 0.0f;
         }
+    }
+    float am = 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        }
-        // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
-        uint32_t e = __float_as_uint(am) & 0x7f800000u;
-        e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
-        // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
-        const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
-        int X[8];
+    for (int i = 0; i < 8; i++) {
+        am = fmaxf(am, fabsf(xv[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    }
+    // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
+    uint32_t e = __float_as_uint(am) & 0x7f800000u;
+    e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
+    // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
+    const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
+    int X[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        X[i] = __float2int_rn(xv[i] * inv);
+    }
+#pragma unroll
+    for (int dgt = 0; dgt < 3; dgt++) {
+        uint32_t w0 = 0, w1 = 0;
+        int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            X[i] = __float2int_rn(xv[i] * inv);
-        }
-#pragma unroll
-        for (int dgt = 0; dgt < 3; dgt++) {
-            uint32_t w0 = 0, w1 = 0;
-            int sum = 0;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
-                X[i] = (X[i] - d) >> 8;
-                sum += d;
-                if (i < 4) {
-                    w0 |= (uint32_t)(d & 0xff) << (8 * i);
-                } else {
-                    w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
-                }
+            const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
+            X[i] = (X[i] - d) >> 8;
+            sum += d;
+            if (i < 4) {
+                w0 |= (uint32_t)(d & 0xff) << (8 * i);
+            } else {
+                w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
             }
-            const int col = 3 * m + dgt;
-            xd[(((size_t)sub * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt] = make_uint2(w0, w1);
-            // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        }
+        const int col = 3 * m + dgt;
+        xd[(((size_t)sub * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt] = make_uint2(w0, w1);
+        // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte;
+        // byte (sub % 4) of the word of lane slot sub / 4, in mins column 2 col + part
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (tt == 0) {
             const int lo7 = sum & 127, hi = (sum - lo7) >> 7;
 #pragma unroll
             for (int p = 0; p < 2; p++) {
-                // bytes of sub-blocks 4q .. 4q+3 packed into one word, in lanes 0 (q = 0) and 16 (q = 1)
-                uint32_t byte = (uint32_t)(p == 0 ? lo7 : hi) & 0xffu;
-                uint32_t word = byte | (__shfl_down_sync(0xffffffffu, byte, 4) << 8) | (__shfl_down_sync(0xffffffffu, byte, 8) << 16) |
-                                (__shfl_down_sync(0xffffffffu, byte, 12) << 24);
                 const int mc = 2 * col + p;
-                if ((lane & 15) == 0) {
-                    xm[((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 2 + (lane >> 4)] = word;
-                }
+                xm[(((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 2 + (sub >> 2)) * 4 + (sub & 3)] = (uint8_t)(p == 0 ? lo7 : hi);
             }
-            if (lane == 0) {
-                tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
-            }
+        }
+        if (lane == 0) {
+            tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
         }
     }
 }
@@ -535,7 +531,7 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         return JQ_OK;
     }
     *handled = true;
-    q4k_activation_image_kernel<MT><<<(KB + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+    q4k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
     count_launch();
     int rc = check_launch("q4k_activation_image_kernel");
     if (rc != JQ_OK) {
