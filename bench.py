@@ -39,6 +39,8 @@ TYPE = "Q4_K"
 BYTES_PER_WEIGHT = 144.0 / 256.0
 POOL_COPIES = 4  # distinct copies of every weight; 4 x 134 MB = 537 MB, about 4x the 126 MB L2
 METRIC = "q4k_gemv_sweep_GBps"
+# dram__bytes_read.sum + dram__bytes_write.sum of one step under ncu (profiles/gemv_q4k_i8_sweep.md), per linear
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 269903616 // 8
 
 
 def algorithmic_bytes(n, k, m):
@@ -319,7 +321,7 @@ def run_ours(args):
                        "launch": ("CUDA graph of %d steps, replayed" % period) if use_graph else "eager launches through the C ABI",
                        "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + NCCL all-gather per launch" % world},
             "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s", "frac": round(value / world / peak, 4),
-                         "traffic": None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
