@@ -148,7 +148,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     import jitnn_b200
-    from jitnn_b200 import _lib
+    from jitnn_b200 import _lib, sharded
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -166,12 +166,9 @@ def run_ours(args):
     g = torch.Generator(device=device).manual_seed(99)
     xs = {(k, m): torch.randn(m, k, generator=g, device=device) for _, k in SHAPES for m in BATCHES}
     ys = {}
-    gathered = {}
     for n, k in SHAPES:
         for m in BATCHES:
             ys[(n, k, m)] = torch.empty(m, n // world, device=device)
-            if world > 1:
-                gathered[(n, k, m)] = torch.empty(world, m, n // world, device=device)
 
     def step(i):
         sp = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
@@ -181,7 +178,7 @@ def run_ours(args):
                 y = ys[(n, k, m)]
                 _lib.check(L.jq_linear_f32(w._handle(), xs[(k, m)].data_ptr(), m, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
                 if world > 1:
-                    dist.all_gather_into_tensor(gathered[(n, k, m)], y)
+                    sharded.gather_rows(y, n)  # y [m, n] complete on every rank
 
     def barrier():
         if world > 1:
