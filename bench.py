@@ -195,11 +195,11 @@ def run_ours(args):
         rel = float(np.abs(yh[:, :64] - ref).max() / np.abs(ref).max())
         assert rel <= 1e-3, "GEMV differs from the oracle: %g" % rel
 
-    # The weight rotation repeats every `period` steps. On one GPU that many steps are captured into a CUDA graph
-    # (the launches of a step are a few microseconds each, less than the host needs to issue them) and the graph
-    # is replayed; with several ranks the steps are issued eagerly because each launch is followed by a collective.
+    # The weight rotation repeats every `period` steps. That many steps are captured into a CUDA graph (the launches of
+    # a step are a few microseconds each, less than the host needs to issue them) and the graph is replayed; with
+    # several ranks the NCCL all-gathers are part of each rank's graph.
     period = POOL_COPIES // len(BATCHES) if POOL_COPIES % len(BATCHES) == 0 else POOL_COPIES
-    use_graph = world == 1 and not args.eager
+    use_graph = not args.eager
     side = torch.cuda.Stream(device)
     graph = None
     with torch.cuda.stream(side):

@@ -124,12 +124,21 @@ JQ_API int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const fl
 
 /*
  * Prefill form: x is bfloat16 [m, k] (raw 16-bit patterns), y float32 [m, n]; dequantised weights are
- * rounded to bfloat16 and multiplied on the tensor cores with FP32 accumulation. Semantics of the
+ * rounded to bfloat16 and multiplied on the tensor cores (tcgen05) with FP32 accumulation. Semantics of the
  * reference's prefill composition dequantize + matmul (ops/Gguf.java:94-95,
- * ops/MatMul.java:597-625) at bfloat16 operand precision.
+ * ops/MatMul.java:597-625) at bfloat16 operand precision. k must be a multiple of 64; any m works, the
+ * kernel is built for m >= 128.
  */
 JQ_API int jq_linear_bf16(const jq_weight* w, const uint16_t* x_bf16, int64_t m, const float* bias, float* y, int mem,
                    void* stream);
+
+/*
+ * Waits for the work enqueued on `device` and reports, then clears, the status word of its kernels: 0, or the code of
+ * the first bounded device-side wait that gave up (the prefill kernel's barrier waits are bounded instead of being
+ * able to hang). Calls with host memory check this themselves and return JQ_ERR_TIMEOUT; callers that enqueue with
+ * device memory can poll it at a synchronisation point of their own. (No counterpart in the reference.)
+ */
+JQ_API int jq_device_status(int device, int* status);
 
 /*
  * blocks_out[count/32*34] = Q8_0 blocks of x[count] (count % 32 == 0), following the reference's host

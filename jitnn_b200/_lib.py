@@ -32,6 +32,7 @@ SIGNATURES = {
     "jq_linear_f32": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
     "jq_linear_bf16": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
     "jq_linear_q4k_f32_noalloc": (c_int, [vp, vp, c_i64, vp, vp, vp]),
+    "jq_device_status": (c_int, [c_int, ctypes.POINTER(c_int)]),
     "jq_quantize_q8_0": (c_int, [c_int, vp, c_i64, vp, c_int, vp]),
     "jq_set_option": (c_int, [ctypes.c_char_p, c_i64]),
     "jq_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_i64)]),

@@ -161,6 +161,19 @@ std::atomic<int64_t> g_opt_gemv_generic{0};
 // ---- linear on device pointers --------------------------------------------------------------------
 static int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
     View v = view_of(w);
+    const int64_t min_rows = g_prefill_min_rows.load();
+    if (min_rows > 0 && m >= min_rows && prefill_supported(v)) {
+        // the caller opted in to bfloat16 operand precision for large row counts: round x, then the tensor-core kernel
+        uint8_t* xb = nullptr;
+        int rc = scratch_for(s, (size_t)m * w->k * 2, &xb);
+        if (rc == JQ_OK) {
+            rc = launch_f32_to_bf16(x, (uint16_t*)xb, m * w->k, s);
+        }
+        if (rc == JQ_OK) {
+            rc = launch_prefill_bf16(v, (const uint16_t*)xb, m, bias, y, s);
+        }
+        return rc;
+    }
     // Q4_K's integer tensor-core kernel takes up to 8 activation rows per pass, the other kernels 16.
     const int64_t group = (w->type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load() == 0) ? 8 : 16;
     for (int64_t m0 = 0; m0 < m; m0 += group) {
@@ -468,12 +481,74 @@ int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bi
     return JQ_OK;
 }
 
-int jq_linear_bf16(const jq_weight* w, const uint16_t*, int64_t, const float*, float*, int, void*) {
+int jq_linear_bf16(const jq_weight* w, const uint16_t* x, int64_t m, const float* bias, float* y, int mem, void* stream) {
     int rc = check_weight(w, "jq_linear_bf16");
     if (rc != JQ_OK) {
         return rc;
     }
-    return fail(JQ_ERR_UNSUPPORTED, "jq_linear_bf16: the tensor-core prefill kernel is not built into this library");
+    if (!has_linear_kernel(w->type)) {
+        return fail(JQ_ERR_UNSUPPORTED, "%s linear: the format is dequantise-only", type_name(w->type));
+    }
+    if (m < 0 || m >= ((int64_t)1 << 31)) {
+        return fail(JQ_ERR_INVALID, "%s linear: input of %lld rows and weight [%lld, %lld]", type_name(w->type), (long long)m, (long long)w->n,
+                    (long long)w->k);
+    }
+    if (m == 0 || w->n == 0) {
+        return JQ_OK;
+    }
+    if (x == nullptr || y == nullptr) {
+        return fail(JQ_ERR_INVALID, "%s linear: null input or output", type_name(w->type));
+    }
+    DeviceGuard guard(w->device);
+    View v = view_of(w);
+    if (mem == JQ_MEM_DEVICE) {
+        if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+            return fail(JQ_ERR_INVALID, "%s linear: device pointers must be 16-byte aligned", type_name(w->type));
+        }
+        return launch_prefill_bf16(v, x, m, bias, y, (cudaStream_t)stream);
+    }
+    if (mem != JQ_MEM_HOST) {
+        return fail(JQ_ERR_INVALID, "%s linear: unknown memory kind %d", type_name(w->type), mem);
+    }
+    size_t xb = align256((size_t)m * w->k * 2), bb = align256((size_t)w->n * 4), yb = align256((size_t)m * w->n * 4);
+    Staging* st;
+    rc = staging_for(w->device, xb + bb + yb, &st);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    uint16_t* dx = (uint16_t*)st->dev;
+    float* db = (float*)(st->dev + xb);
+    float* dy = (float*)(st->dev + xb + bb);
+    JQ_CUDA(cudaMemcpyAsync(dx, x, (size_t)m * w->k * 2, cudaMemcpyHostToDevice, st->stream));
+    if (bias != nullptr) {
+        JQ_CUDA(cudaMemcpyAsync(db, bias, (size_t)w->n * 4, cudaMemcpyHostToDevice, st->stream));
+    }
+    rc = launch_prefill_bf16(v, dx, m, bias != nullptr ? db : nullptr, dy, st->stream);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    JQ_CUDA(cudaMemcpyAsync(y, dy, (size_t)m * w->n * 4, cudaMemcpyDeviceToHost, st->stream));
+    JQ_CUDA(cudaStreamSynchronize(st->stream));
+    int status = 0;
+    rc = prefill_status(&status);
+    if (rc == JQ_OK && status != 0) {
+        rc = fail(JQ_ERR_TIMEOUT, "prefill kernel: a bounded wait gave up (code %d)", status);
+    }
+    return rc;
+}
+
+int jq_device_status(int device, int* status) {
+    if (status == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_device_status: null result pointer");
+    }
+    int count = 0;
+    JQ_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) {
+        return fail(JQ_ERR_INVALID, "jq_device_status: device %d of %d", device, count);
+    }
+    DeviceGuard guard(device);
+    JQ_CUDA(cudaDeviceSynchronize());
+    return prefill_status(status);
 }
 
 int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blocks_out, int mem, void* stream) {

@@ -108,6 +108,12 @@ int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out);
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;
 
+// Tensor-core prefill (jq_prefill.cu).
+bool prefill_supported(const View& v);
+int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const float* bias, float* y, cudaStream_t s);
+int launch_f32_to_bf16(const float* x, uint16_t* out, int64_t count, cudaStream_t s);
+int prefill_status(int* status);
+
 // Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_generic;
 

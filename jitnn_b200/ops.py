@@ -215,6 +215,47 @@ class Gguf:
     def dequantize(w, out=None):
         return _dequantize(w, out)
 
+    @staticmethod
+    def linearBf16(x, w, bias=None):
+        """Prefill form: x bfloat16 [..., K] (a torch CUDA tensor, or a numpy uint16 array of bfloat16 bit patterns),
+        y float32 [..., N]; dequantised weights rounded to bfloat16, tensor-core product, FP32 accumulation."""
+        L = _lib.load()
+        if not isinstance(w, Tensor):
+            raise ValueError("Gguf.linearBf16: weight is not a quantised tensor")
+        n, k = w.shape()
+        if _is_torch(x):
+            import torch
+            if x.dtype != torch.bfloat16:
+                raise ValueError("needs a BF16 tensor, got %s" % x.dtype)
+            if x.dim() == 0 or x.shape[-1] != k:
+                raise ValueError("%s linear: input %s and weight %s" % (w.dtype().name, list(x.shape), list(w.shape())))
+            xc = x.contiguous()
+            m = xc.numel() // k if k else 0
+            y = torch.empty(list(x.shape[:-1]) + [n], dtype=torch.float32, device=x.device)
+            b = None if bias is None else bias.contiguous()
+            with torch.cuda.device(x.device):
+                check(L.jq_linear_bf16(w._handle(), xc.data_ptr(), m, None if b is None else b.data_ptr(), y.data_ptr(), JQ_MEM_DEVICE, _stream_of(x)))
+            return y
+        x = np.asarray(x)
+        if x.dtype != np.uint16:
+            raise ValueError("needs bfloat16 bit patterns as uint16, got %s" % x.dtype)
+        if x.ndim == 0 or x.shape[-1] != k:
+            raise ValueError("%s linear: input %s and weight %s" % (w.dtype().name, list(x.shape), list(w.shape())))
+        xc = np.ascontiguousarray(x)
+        m = xc.size // k if k else 0
+        y = np.empty(x.shape[:-1] + (n,), dtype=np.float32)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        check(L.jq_linear_bf16(w._handle(), xc.ctypes.data, m, None if b is None else b.ctypes.data, y.ctypes.data, JQ_MEM_HOST, None))
+        return y
+
+
+def device_status(device=0):
+    """Waits for the device and returns (then clears) the status word of the library's kernels: 0 when no bounded
+    device-side wait ever gave up."""
+    st = ctypes.c_int(-1)
+    check(_lib.load().jq_device_status(device, ctypes.byref(st)))
+    return st.value
+
 
 class Quant:
     """ops/Quant.java of the reference: the Q8_0 operators."""
