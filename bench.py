@@ -213,11 +213,10 @@ def run_ours(args):
                     step(i)
             for _ in range(3):
                 graph.replay()
-    barrier()
     timed_steps = args.steps if not use_graph else max(period, args.steps // period * period)
     sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        time.sleep(0.2)
+    time.sleep(0.2)  # lets the sampler take its first readings; every rank waits, then all start together
+    barrier()
     t_start = time.time()
     launches0 = L.jq_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -302,6 +301,7 @@ def run_ours(args):
                "d2h_bytes_per_step": int(sum(4 * m * n for n, _ in SHAPES for m in BATCHES)),
                "ms_per_step": round(dt * 1e3, 4)}
 
+    prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
     cpu = cpu_baseline_leg(threads=1, fraction=1, steps=2) if (rank == 0 and world == 1 and not args.no_cpu) else None
 
     if rank == 0:
@@ -321,11 +321,56 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing NCCL down under captured graphs: everything measured is printed, all ranks are in step
+        graph = None
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+
+
+PREFILL_SHAPES = [("Q4_K", 4096, 4096), ("Q4_K", 11008, 4096), ("Q6_K", 4096, 11008), ("Q6_K", 32000, 4096)]  # BASELINE.json configs[2]
+PREFILL_M = 512
+
+
+def prefill_leg(torch, device, L, _lib):
+    """Mixed-format prefill GEMM (M = 512 bf16 activations) through jq_linear_bf16: TFLOP/s per shape."""
+    from jitnn_b200 import Tensor, synth
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+        which = "measured sustained"
+    except Exception:
+        peak, which = 1400.0, "fallback"
+    out = {"m": PREFILL_M, "peak_tflops": peak, "peak_source": "of " + which, "shapes": {}}
+    stream = torch.cuda.current_stream(device)
+    sp = ctypes.c_void_p(stream.cuda_stream)
+    for t, n, k in PREFILL_SHAPES:
+        g = torch.Generator(device=device).manual_seed(n + k)
+        wf = torch.randn(n, k, generator=g, device=device) * 0.02
+        raw = synth.QUANTIZERS[t](wf).cpu().numpy()
+        del wf
+        w = Tensor.quantized(t, raw, n, k, device=device.index)
+        x = torch.randn(PREFILL_M, k, generator=g, device=device).to(torch.bfloat16)
+        y = torch.empty(PREFILL_M, n, device=device)
+        for _ in range(3):
+            _lib.check(L.jq_linear_bf16(w._handle(), x.data_ptr(), PREFILL_M, None, y.data_ptr(), 1, sp))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(device)
+        reps = 20
+        a.record(stream)
+        for _ in range(reps):
+            _lib.check(L.jq_linear_bf16(w._handle(), x.data_ptr(), PREFILL_M, None, y.data_ptr(), 1, sp))
+        b.record(stream)
+        torch.cuda.synchronize(device)
+        us = a.elapsed_time(b) * 1e3 / reps
+        tf = 2.0 * PREFILL_M * n * k / us / 1e6
+        out["shapes"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "TFLOPs": round(tf, 1), "frac": round(tf / peak, 4)}
+        w.release()
+    return out
 
 
 def cpu_baseline_leg(threads, fraction, steps=1, warmup=0):
