@@ -174,8 +174,9 @@ static int linear_device(const jq_weight* w, const float* x, int64_t m, const fl
         }
         return rc;
     }
-    // Q4_K's integer tensor-core kernel takes up to 8 activation rows per pass, the other kernels 16.
-    const int64_t group = (w->type == JQ_TYPE_Q4_K && g_opt_gemv_generic.load() == 0) ? 8 : 16;
+    // Q4_K's integer tensor-core kernel takes up to 8 activation rows per pass, Q6_K's 4, the generic kernel 16.
+    const bool tc = g_opt_gemv_generic.load() == 0;
+    const int64_t group = (tc && w->type == JQ_TYPE_Q4_K) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : 16);
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);

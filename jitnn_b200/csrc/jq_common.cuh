@@ -100,6 +100,9 @@ int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStrea
 // Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
+// The same for Q6_K, rows <= 4.
+int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
+size_t gemv_q6k_i8_scratch_bytes(int64_t k, int rows);
 
 // Scratch memory of at least `bytes` on the current device, private to work enqueued on `s` (one buffer per
 // device and stream, grown on demand and kept until the library is unloaded).

@@ -104,6 +104,18 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
             return rc;
         }
     }
+    if (v.type == JQ_TYPE_Q6_K && rows <= 4 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+        bool handled = false;
+        const size_t need = gemv_q6k_i8_scratch_bytes(v.k, rows);
+        uint8_t* image = nullptr;
+        int rc = need > 0 ? scratch_for(s, need, &image) : JQ_OK;
+        if (rc == JQ_OK) {
+            rc = launch_gemv_q6k_i8(v, x, rows, bias, y, s, image, &handled);
+        }
+        if (rc != JQ_OK || handled) {
+            return rc;
+        }
+    }
     switch (v.type) {
         case JQ_TYPE_Q8_0: return by_rows<JQ_TYPE_Q8_0>(v, x, rows, bias, y, s);
         case JQ_TYPE_Q4_0: return by_rows<JQ_TYPE_Q4_0>(v, x, rows, bias, y, s);

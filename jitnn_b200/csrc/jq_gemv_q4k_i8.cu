@@ -497,11 +497,12 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
     // Candidate shapes, best first: (CTAs per SM, ring stages). The slice length KS is a function of MT and k only (so
     // that the summation order never depends on n): the whole k if its image fits beside the ring, else a multiple of 8.
     const int occ_of[3] = {3, 2, 2}, st_of[3] = {3, 4, 3};
-    const size_t fixed = (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + 8 * 1024;  // reduction buffer + room for carried sums
+    const size_t red_bytes = (size_t)(2 * WARPS * 16 * MT) * sizeof(float);
+    const size_t fixed = red_bytes + 8 * 1024;  // sliced shapes: reduction buffer + room for carried sums
     int pick = -1, KS = KB;
     for (int c = 0; c < 3 && pick < 0; c++) {
         const size_t budget = SMEM_MAX / occ_of[c] - 1024;
-        if ((size_t)KB * Cfg<MT>::PB + fixed + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
+        if ((size_t)KB * Cfg<MT>::PB + red_bytes + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
             pick = c;
         }
     }

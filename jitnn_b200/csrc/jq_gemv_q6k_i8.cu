@@ -1,0 +1,545 @@
+// Decode GEMV for Q6_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 4 per pass.
+//
+// Same scheme as the Q4_K kernel (jq_gemv_q4k_i8.cu): a first kernel turns the activations into an "activation image"
+// (per 256-element super-block of k and row of x: power-of-two scale, 22-bit fixed point, three signed base-256 digits
+// laid out as MMA B fragments), the GEMV kernel streams the weights through a per-warp cp.async ring and multiplies with
+// mma.sync on the integer tensor cores, exactly, converting to float once per super-block.
+// What differs for Q6_K (device layout: 208 bytes per super-block = 128 bytes of low nibbles ql, 64 bytes of high bit
+// pairs qh, 16 signed 8-bit scales; fp16 d in a separate plane):
+//   * a scale covers 16 elements, so one mma.sync.m16n8k16 (u8 x s8 -> s32) handles one scale group of 16 weight rows;
+//     its A operand is (ql nibble) | (qh bit pair << 4), built per four weights with two or three logic operations;
+//   * the quants are unsigned 0..63 with an offset of 32: the term -32 * sum(x digits of the group) does not depend on
+//     the weight row, so the image carries it as the C operand of the MMA;
+//   * group results are combined with the int8 scales by integer multiply-add (the sum over 16 groups stays below
+//     2^31), converted to float once per super-block and scaled by fp16 d and the column weight;
+//   * the A fragments are read with ldmatrix: lane (g, t) needs word t of a 16-byte chunk of rows g and g + 8, which
+//     is exactly ldmatrix's distribution, and the 208-byte row pitch makes those reads conflict free.
+// The summation order depends on k only: a row shard of a weight gives bitwise the same outputs as the whole weight.
+#include <mutex>
+
+#include "jq_formats.cuh"
+
+namespace jq {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int ROW_BYTES = 208;                       // one super-block of one row in the quant plane
+constexpr int SLOT_D = 16 * ROW_BYTES;               // behind the 16 rows: one 4-byte word per row holding its fp16 d
+constexpr int SLOT_BYTES = SLOT_D + 16 * 4;
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Byte i (0..3) of a word as a sign-extended integer.
+__device__ __forceinline__ int signed_byte(uint32_t w, int i) {
+    int r;
+    asm("bfe.s32 %0, %1, %2, 8;" : "=r"(r) : "r"(w), "r"(8 * i));
+    return r;
+}
+
+__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+// D = A(16x16 u8) * B(16x8 s8) + C, C given per column pair (the same for rows g and g + 8).
+__device__ __forceinline__ void imma_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, int c0, int c1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%8,%7,%8};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(c0), "r"(c1));
+}
+
+// Four 8x8 matrices of 16-bit elements: register i of lane (g, t) = the 4 bytes at byte offset 4t of row g of matrix i,
+// whose 8 row addresses come from lanes 8i .. 8i + 7.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int MT>
+struct Cfg {
+    static constexpr int COLS = 3 * MT;               // digit columns: column 3m + i is digit i of activation row m
+    static constexpr int NG = (COLS + 7) / 8;         // MMA column groups
+    static constexpr int NCOL = NG == 1 ? COLS : 8;   // columns stored per group
+    // bytes of activation image per super-block: digit fragments of the 16 scale groups, C fragments, column weights
+    static constexpr size_t XD = (size_t)16 * NG * NCOL * 4 * 4;  // 16 groups x column groups x columns x 4 lanes x 4 bytes
+    static constexpr size_t XC = (size_t)16 * NG * 8 * 4;         // 16 groups x column groups x 8 columns x int32
+    static constexpr size_t TAB = (size_t)NG * 8 * 4;             // one float per digit column
+    static constexpr size_t PB = XD + XC + TAB;
+};
+
+// ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
+// One warp per (super-block of k, activation row); lane L holds the 8 activations 8L .. 8L+7: they are k-slots
+// 8 (L % 2) .. + 7 of scale group L / 2 (a group = 16 consecutive elements of the super-block).
+constexpr int PREP_WARPS = 4;
+
+template <int MT>
+__global__ void __launch_bounds__(PREP_WARPS * 32) q6k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
+                                                                             uint8_t* __restrict__ image) {
+    using C = Cfg<MT>;
+    constexpr int NG = C::NG, NCOL = C::NCOL;
+    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    const int b = pair / MT, m = pair % MT;
+    if (b >= (int)(k >> 8)) {
+        return;
+    }
+    const int grp = lane >> 1, half = lane & 1;
+    uint8_t* img = image + (size_t)b * C::PB;
+    uint2* xd = reinterpret_cast<uint2*>(img);
+    int* xc = reinterpret_cast<int*>(img + C::XD);
+    float* tab = reinterpret_cast<float*>(img + C::XD + C::XC);
+    if (m == 0 && lane >= C::COLS && lane < NG * 8) {
+        tab[lane] = 0.0f;  // columns that hold no activation row
+    }
+    float xv[8];
+    if (m < rows) {
+        const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
+        const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
+        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
+        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            xv[i] = 0.0f;
+        }
+    }
+    float am = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        am = fmaxf(am, fabsf(xv[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    }
+    // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
+    uint32_t e = __float_as_uint(am) & 0x7f800000u;
+    e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
+    const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));           // 2^21 / s: |X| <= 2^22
+    int X[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        X[i] = __float2int_rn(xv[i] * inv);
+    }
+#pragma unroll
+    for (int dgt = 0; dgt < 3; dgt++) {
+        uint32_t w0 = 0, w1 = 0;
+        int sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
+            X[i] = (X[i] - d) >> 8;
+            sum += d;
+            if (i < 4) {
+                w0 |= (uint32_t)(d & 0xff) << (8 * i);
+            } else {
+                w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
+            }
+        }
+        const int col = 3 * m + dgt;
+        // lane slots 2 half and 2 half + 1 of this group's B fragment
+        xd[((((size_t)grp * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + 2 * half) / 2] = make_uint2(w0, w1);
+        // -32 * (digit sum of the group's 16 elements): the row-independent part of sum (q - 32) x, the MMA's C operand
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if (half == 0) {
+            xc[((size_t)grp * NG + (col >> 3)) * 8 + (col & 7)] = -32 * sum;
+        }
+        if (lane == 0) {
+            tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
+        }
+    }
+}
+
+// ---- the GEMV ---------------------------------------------------------------------------------------------------
+template <int MT, int STAGES, int OCC>
+__global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
+                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles,
+                                                                  int KS, int max_tiles) {
+    // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
+    // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
+    using C = Cfg<MT>;
+    constexpr int NG = C::NG, NCOL = C::NCOL;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int KB = (int)(v.k >> 8);
+    const int nslices = (KB + KS - 1) / KS;
+    uint8_t* img = smem_raw;                                                         // [KS][PB]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][WARPS][16][MT]
+    float* carry = red + 2 * WARPS * 16 * MT;                                        // [max_tiles][16][MT], only if nslices > 1
+    uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) +
+                    (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int64_t n = v.n;
+    const int64_t row_bytes = (int64_t)KB * ROW_BYTES;
+
+    // ---- weight stream: chunk c = lane + 32 i of the 208 chunks (16 rows x 13) of a super-block, rows at their natural
+    // pitch of 208 bytes; lanes 0-15 also copy the aligned 4-byte word that holds the fp16 d of row `lane`.
+    uint32_t src_off[7], dst_off[7];
+#pragma unroll
+    for (int i = 0; i < 7; i++) {
+        const int c = lane + 32 * i, r = c / 13, ch = c % 13;
+        src_off[i] = (uint32_t)(r * (int)row_bytes + ch * 16);
+        dst_off[i] = (uint32_t)(r * ROW_BYTES + ch * 16);
+    }
+    // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + 8 i.
+    auto blocks_of = [&](int sl) {  // number of super-blocks this warp has in slice sl
+        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
+        return warp < len ? (len - warp + WARPS - 1) / WARPS : 0;
+    };
+    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    int steps = 0;
+    for (int sl = 0; sl < nslices; sl++) {
+        steps += blocks_of(sl) * my_tiles;
+    }
+    int iss_sl = 0, iss_ti = 0, iss_j = 0;
+    while (iss_sl < nslices && blocks_of(iss_sl) == 0) {
+        iss_sl++;
+    }
+    auto issue = [&](int s) {
+        if (s < steps) {
+            const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
+            const int blk = iss_sl * KS + warp + WARPS * iss_j;
+            const uint8_t* base = v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)blk * (uint32_t)ROW_BYTES;
+            const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
+#pragma unroll
+            for (int i = 0; i < 6; i++) {
+                cp_async16(slot + dst_off[i], base + src_off[i]);
+            }
+            if (lane < 16) {
+                cp_async16(slot + dst_off[6], base + src_off[6]);
+                const int64_t didx = ((int64_t)tile * 16 + lane) * KB + blk;  // fp16 index of this row's d
+                cp_async4(slot + SLOT_D + 4u * (uint32_t)lane, v.aux + ((didx * 2) & ~(int64_t)3));
+            }
+            if (++iss_j == blocks_of(iss_sl)) {
+                iss_j = 0;
+                if (++iss_ti == my_tiles) {
+                    iss_ti = 0;
+                    do {
+                        iss_sl++;
+                    } while (iss_sl < nslices && blocks_of(iss_sl) == 0);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        issue(s);  // the first weights are on their way before the activation image is complete
+    }
+
+    // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+
+    // ---- main loop ----------------------------------------------------------------------------------------------
+    // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
+    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 4;
+    const uint8_t* xc_lane = img + C::XD + (size_t)(2 * t) * 4;
+    const uint8_t* tab_lane = img + C::XD + C::XC;
+    // ldmatrix row address of this lane inside a slot: matrix lane / 8 covers rows 8 (matrix % 2) .. + 7 and
+    // chunk (matrix / 2) of a chunk pair
+    const uint32_t ldm_off = (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_BYTES + (lane >> 4) * 16);
+    float acc[NG][2][2];   // [group][row g / g + 8][column 2t / 2t + 1]
+#pragma unroll
+    for (int i = 0; i < NG; i++) {
+        acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
+    }
+
+    auto compute = [&](const uint8_t* slot, uint32_t slot_s, int b, int tile, int blk) {  // b = index inside the resident slice
+        int I[NG][4];
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            I[i][0] = I[i][1] = I[i][2] = I[i][3] = 0;
+        }
+        // the 16 signed scales of rows g and g + 8
+        const uint4 sv0 = *reinterpret_cast<const uint4*>(slot + g * ROW_BYTES + 192);
+        const uint4 sv1 = *reinterpret_cast<const uint4*>(slot + (g + 8) * ROW_BYTES + 192);
+        const uint32_t sc0[4] = {sv0.x, sv0.y, sv0.z, sv0.w}, sc1[4] = {sv1.x, sv1.y, sv1.z, sv1.w};
+        const uint8_t* bx = xd_lane + (size_t)b * C::PB;
+        const uint8_t* bc = xc_lane + (size_t)b * C::PB;
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+            // high bit pairs of half n: registers {row g, row g+8} x {elements 0-15, 16-31}
+            uint32_t qh[4];
+            ldmatrix_x4(qh, slot_s + ldm_off + (uint32_t)(8 + 2 * n) * 16u);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                // low nibbles: bytes 64 n + 32 h + l; their low nibble is sub-block kk = h, their high nibble kk = h + 2
+                uint32_t ql[4];
+                ldmatrix_x4(ql, slot_s + ldm_off + (uint32_t)(4 * n + 2 * h) * 16u);
+#pragma unroll
+                for (int hi = 0; hi < 2; hi++) {
+                    const int kk = h + 2 * hi;
+#pragma unroll
+                    for (int cp = 0; cp < 2; cp++) {
+                        const int gi = 8 * n + 2 * kk + cp;  // scale group = elements 16 gi .. 16 gi + 15
+                        const uint32_t la = hi == 0 ? ql[2 * cp] : ql[2 * cp] >> 4, lb = hi == 0 ? ql[2 * cp + 1] : ql[2 * cp + 1] >> 4;
+                        const uint32_t ha = kk == 0 ? qh[2 * cp] << 4 : (kk == 1 ? qh[2 * cp] << 2 : (kk == 2 ? qh[2 * cp] : qh[2 * cp] >> 2));
+                        const uint32_t hb = kk == 0 ? qh[2 * cp + 1] << 4
+                                                    : (kk == 1 ? qh[2 * cp + 1] << 2 : (kk == 2 ? qh[2 * cp + 1] : qh[2 * cp + 1] >> 2));
+                        const uint32_t a0 = and_or(ha, 0x30303030u, la & 0x0f0f0f0fu);
+                        const uint32_t a1 = and_or(hb, 0x30303030u, lb & 0x0f0f0f0fu);
+                        // sign-extended scale byte gi
+                        const int s0 = signed_byte(sc0[gi >> 2], gi & 3);
+                        const int s1 = signed_byte(sc1[gi >> 2], gi & 3);
+#pragma unroll
+                        for (int i = 0; i < NG; i++) {
+                            const uint32_t bf = *reinterpret_cast<const uint32_t*>(bx + (size_t)((gi * NG + i) * NCOL) * 16);
+                            const int2 cf = *reinterpret_cast<const int2*>(bc + (size_t)((gi * NG + i) * 8) * 4);
+                            int D[4];
+                            imma_k16(D, a0, a1, bf, cf.x, cf.y);
+                            I[i][0] += s0 * D[0];
+                            I[i][1] += s0 * D[1];
+                            I[i][2] += s1 * D[2];
+                            I[i][3] += s1 * D[3];
+                        }
+                    }
+                }
+            }
+        }
+        // fp16 d of rows g and g + 8: the half of the copied word that the row's index selects
+        const int64_t d0i = ((int64_t)tile * 16 + g) * KB + blk, d1i = d0i + (int64_t)8 * KB;
+        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(slot + SLOT_D + 4 * g), w1 = *reinterpret_cast<const uint32_t*>(slot + SLOT_D + 4 * (g + 8));
+        const float d0 = half_bits_to_float(w0 >> (16 * (int)(d0i & 1))), d1 = half_bits_to_float(w1 >> (16 * (int)(d1i & 1)));
+        const uint8_t* tb = tab_lane + (size_t)b * C::PB;
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            const float2 w = *reinterpret_cast<const float2*>(tb + (8 * i + 2 * t) * 4);  // weights of columns 2t, 2t+1
+            acc[i][0][0] = fmaf(d0 * w.x, (float)I[i][0], acc[i][0][0]);
+            acc[i][0][1] = fmaf(d0 * w.y, (float)I[i][1], acc[i][0][1]);
+            acc[i][1][0] = fmaf(d1 * w.x, (float)I[i][2], acc[i][1][0]);
+            acc[i][1][1] = fmaf(d1 * w.y, (float)I[i][3], acc[i][1][1]);
+        }
+    };
+
+    // activation row each accumulator column of this lane belongs to (-1: none)
+    int mq[NG][2];
+#pragma unroll
+    for (int i = 0; i < NG; i++) {
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int col = 8 * i + 2 * t + c;
+            mq[i][c] = col < C::COLS ? col / 3 : -1;
+        }
+    }
+
+    int parity = 0;
+    int step = 0;
+    for (int sl = 0; sl < nslices; sl++) {
+        // ---- bring this slice of the activation image into shared memory ---------------------------------------------
+        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
+        if (sl > 0) {
+            __syncthreads();  // every warp is done with the previous slice
+        }
+        {
+            const uint8_t* src = image + (size_t)sl * KS * C::PB;
+            const int chunks = (int)((size_t)len * C::PB / 16);
+            for (int c = tid; c < chunks; c += THREADS) {
+                cp_async16(img_s + (uint32_t)c * 16u, src + (size_t)c * 16);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+        }
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
+            for (int b = warp; b < len; b += WARPS) {
+                __syncwarp();                 // every lane is done reading the slot that is requested next
+                issue(step + STAGES - 1);
+                cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+                __syncwarp();                 // ... and so have the other lanes'
+                compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, ring_s + (uint32_t)(step % STAGES) * SLOT_BYTES, b, my_tile, sl * KS + b);
+                step++;
+            }
+            // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
+            float* rd = red + (size_t)parity * WARPS * 16 * MT;
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NG; i++) {
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        if (mq[i][c] == m) {
+                            p0 += acc[i][0][c];
+                            p1 += acc[i][1][c];
+                        }
+                    }
+                }
+                p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+                p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+                p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+                p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+                if (t == 0) {
+                    rd[(warp * 16 + g) * MT + m] = p0;
+                    rd[(warp * 16 + g + 8) * MT + m] = p1;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
+            }
+            __syncthreads();
+            // ---- the 8 warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
+            for (int o = tid; o < 16 * MT; o += THREADS) {
+                const int r = o / MT, m = o % MT;
+                const int64_t row = (int64_t)my_tile * 16 + r;
+                const float* p = rd + r * MT + m;
+                float sum = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
+                            ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
+                if (sl > 0) {
+                    sum += carry[(size_t)ti * 16 * MT + o];
+                }
+                if (sl + 1 < nslices) {
+                    carry[(size_t)ti * 16 * MT + o] = sum;
+                } else if (m < rows && row < n) {
+                    y[(int64_t)m * n + row] = sum + (bias != nullptr ? bias[row] : 0.0f);
+                }
+            }
+            parity ^= 1;
+        }
+    }
+}
+
+int g_sms = 0;
+int sm_count() {
+    if (g_sms == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+            g_sms = sms;
+        } else {
+            g_sms = 148;
+        }
+    }
+    return g_sms;
+}
+
+template <int MT, int STAGES, int OCC>
+int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles, size_t smem) {
+    static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
+    int dev = 0;
+    JQ_CUDA(cudaGetDevice(&dev));
+    if ((configured.load() >> (dev & 63) & 1) == 0) {
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q6k_i8_kernel<MT, STAGES, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        configured.fetch_or((uint64_t)1 << (dev & 63));
+    }
+    const int tiles = (int)((v.n + 15) / 16);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the activation kernel runs
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q6k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
+    count_launch();
+    return JQ_OK;
+}
+
+// Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
+template <int MT>
+size_t smem_bytes(int KS, int stages, bool sliced, int max_tiles) {
+    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+           (size_t)WARPS * stages * SLOT_BYTES;
+}
+
+template <int MT>
+int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+    const int KB = (int)(v.k / 256);
+    const int tiles = (int)((v.n + 15) / 16);
+    // Candidate shapes, best first: (CTAs per SM, ring stages). The slice length KS is a function of MT and k only (so
+    // that the summation order never depends on n): the whole k if its image fits beside the ring, else a multiple of 8.
+    const int occ_of[3] = {3, 2, 2}, st_of[3] = {3, 4, 3};
+    const size_t red_bytes = (size_t)(2 * WARPS * 16 * MT) * sizeof(float);
+    const size_t fixed = red_bytes + 8 * 1024;  // sliced shapes: reduction buffer + room for carried sums
+    int pick = -1, KS = KB;
+    for (int c = 0; c < 3 && pick < 0; c++) {
+        const size_t budget = SMEM_MAX / occ_of[c] - 1024;
+        if ((size_t)KB * Cfg<MT>::PB + red_bytes + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
+            pick = c;
+        }
+    }
+    int stages = pick >= 0 ? st_of[pick] : 0;
+    if (pick < 0) {
+        // slices: two CTAs per SM, three ring stages, or two if a slice of 8 super-blocks needs the room
+        pick = 2;
+        for (stages = 3; stages >= 2; stages--) {
+            const size_t budget = SMEM_MAX / 2 - 1024 - fixed - (size_t)WARPS * stages * SLOT_BYTES;
+            KS = (int)(budget / Cfg<MT>::PB) / 8 * 8;
+            if (KS >= 8) {
+                break;
+            }
+        }
+        if (KS < 8) {
+            *handled = false;
+            return JQ_OK;
+        }
+    }
+    const int occ = occ_of[pick];
+    const int grid = tiles < sm_count() * occ ? tiles : sm_count() * occ;
+    const int max_tiles = (tiles + grid - 1) / grid;
+    const bool sliced = KS < KB;
+    const size_t smem = smem_bytes<MT>(KS, stages, sliced, max_tiles);
+    if (smem > SMEM_MAX / occ - 1024) {
+        *handled = false;  // more tiles per CTA than the carried sums have room for
+        return JQ_OK;
+    }
+    *handled = true;
+    q6k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+    count_launch();
+    int rc = check_launch("q6k_activation_image_kernel");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    if (stages == 3) return launch<MT, 3, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+    return launch<MT, 2, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+}
+
+}  // namespace
+
+// Bytes of scratch (activation image) a Q6_K GEMV of `rows` activation rows over k inputs needs; 0 if the
+// shape is not handled by the integer kernel.
+size_t gemv_q6k_i8_scratch_bytes(int64_t k, int rows) {
+    if (rows < 1 || rows > 4 || k <= 0) {
+        return 0;
+    }
+    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : Cfg<4>::PB);
+    return (size_t)(k / 256) * pb;
+}
+
+// Q6_K with rows in [1, 4] on a weight whose planes is padded by 16 rows. `image` is a scratch buffer of
+// gemv_q6k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
+// *handled = false leaves the call to another kernel.
+int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+    *handled = false;
+    if (v.type != JQ_TYPE_Q6_K || v.n == 0 || v.k == 0 || rows > 4 || image == nullptr || (int64_t)16 * (v.k / 256) * 208 >= ((int64_t)1 << 31)) {
+        return JQ_OK;
+    }
+    if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
+    return run<4>(v, x, rows, bias, y, s, image, handled);
+}
+
+}  // namespace jq
