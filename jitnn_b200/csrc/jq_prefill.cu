@@ -3,14 +3,14 @@
 //
 // Replaces the reference's prefill composition (ops/Gguf.java:94-95: dequantise the whole weight to an FP32 [N, K]
 // tensor, then an FP32 CUDA-core GEMM, ops/MatMul.java:488-554): the weight is never materialised. A CTA owns a tile
-// of 128 output features x 128 tokens and walks k in stages of 64:
+// of 128 output features x 128 or 256 tokens and walks k in stages of 64:
 //   * one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle, no multicast) of the activation tile
-//     [128 tokens x 64 k] into shared memory;
-//   * 128 dequantiser threads (one per output feature) decode their row's 64 weights of the stage with the bit-exact
+//     [tokens x 64 k] into shared memory;
+//   * 256 dequantiser threads (two per output feature) decode their row's 64 weights of the stage with the bit-exact
 //     per-format decoders, round them to bfloat16 and store them in the same 128-byte-swizzled K-major layout;
-//   * one thread issues four tcgen05.mma (M = 128 features, N = 128 tokens, K = 16) per stage and commits the stage's
-//     "empty" barrier; the accumulator D[feature][token] (128 lanes x 128 columns of FP32) lives in tensor memory;
-//   * after the last stage the four dequantiser warps read the accumulator with tcgen05.ld (32 lanes x 32 columns
+//   * one thread issues four tcgen05.mma (M = 128 features, N = 128 or 256 tokens, K = 16) per stage and commits the
+//     stage's "empty" barrier; the accumulator D[feature][token] (128 lanes x N columns of FP32) lives in tensor memory;
+//   * after the last stage the dequantiser warps read the accumulator with tcgen05.ld (32 lanes x 32 columns
 //     at a time) and store y[token][feature] (32 consecutive features per warp store: coalesced), adding the bias.
 // Every mbarrier wait is bounded: a wait that does not complete within its poll budget records a status code in
 // g_prefill_status, raises the CTA's abort flag and all roles fall through to the common exit, where tensor memory
@@ -28,15 +28,18 @@ namespace jq {
 // 4 accumulator ready) since the status was last cleared.
 static __device__ int g_prefill_status;
 
+__host__ __device__ constexpr int plane_q_bytes_dev(int type) {
+    return type == JQ_TYPE_Q8_0 ? 32 : 16;  // Q8_0, Q4_0, Q4_1 quant planes
+}
+
 namespace {
 
 constexpr int TILE_F = 128;    // output features per CTA (MMA M)
-constexpr int TILE_T = 128;    // tokens per CTA (MMA N)
 constexpr int STAGE_K = 64;    // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int STAGES = 4;
 constexpr int A_BYTES = TILE_F * STAGE_K * 2;
-constexpr int B_BYTES = TILE_T * STAGE_K * 2;
-constexpr int THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: dequantise, then epilogue
+constexpr int DQ_THREADS = 256;  // two dequantiser threads per output feature, 32 weights each per stage
+constexpr int THREADS = 64 + DQ_THREADS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: dequantise, then epilogue
 constexpr uint32_t POLL_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -90,13 +93,36 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 
 // Instruction descriptor of kind::f16: D = F32 (bits 4-5 = 1), A and B = BF16 (bits 7-9 and 10-12 = 1), both K-major,
 // N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TILE_T >> 3) << 17) | ((uint32_t)(TILE_F >> 4) << 24);
+constexpr uint32_t idesc_of(int tile_t) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tile_t >> 3) << 17) | ((uint32_t)(TILE_F >> 4) << 24);
+}
 
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// Pulls the bytes that dequant_row_chunk will read for [k0, k0 + 64) of `row` towards the SM ahead of time.
+template <int TYPE>
+__device__ __forceinline__ void prefetch_row_chunk(const View& v, int64_t row, int k0) {
+    using F = Fmt<TYPE>;
+    const int blocks_per_row = (int)(v.k / F::QK);
+    const int64_t block = row * blocks_per_row + k0 / F::QK;
+    const int o = k0 % F::QK;
+    const uint8_t* p;
+    if (TYPE == JQ_TYPE_Q4_K) {
+        p = v.q + block * 144 + 16 + (o >> 6) * 32;
+    } else if (TYPE == JQ_TYPE_Q5_K) {
+        p = v.q + block * 176 + 48 + (o >> 6) * 32;
+    } else if (TYPE == JQ_TYPE_Q6_K) {
+        p = v.q + block * 208 + (o >> 7) * 64;
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(p + 128 + (o >> 7) * 32 - (o >> 7) * 64));
+    } else {
+        p = v.q + block * plane_q_bytes_dev(TYPE);
+    }
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -105,7 +131,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 // The 64 weights k0 .. k0 + 63 of one row, decoded bit-exactly (jq_formats.cuh) and rounded to bfloat16, written as
 // one 128-byte row of the swizzled A tile: 16-byte chunk c lands at position c ^ (row & 7).
 template <int TYPE>
-__device__ __forceinline__ void dequant_row_chunk(const View& v, int64_t row, int k0, uint8_t* a_row, int swz) {
+__device__ __forceinline__ void dequant_row_chunk(const View& v, int64_t row, int k0, uint8_t* a_row, int swz, int part) {
+    // `part` (0 or 1) selects this thread's half of the units that cover the chunk
     using F = Fmt<TYPE>;
     const int blocks_per_row = (int)(v.k / F::QK);
     // units whose runs cover [k0, k0 + 64)
@@ -120,11 +147,13 @@ __device__ __forceinline__ void dequant_row_chunk(const View& v, int64_t row, in
             // skip units entirely outside the chunk (compile-time layouts: see Fmt<>::decode positions)
             bool any = false;
             if (TYPE == JQ_TYPE_Q4_K || TYPE == JQ_TYPE_Q5_K) {
-                any = (u >> 1) == ((k0 - base) >> 6);
+                any = (u >> 1) == ((k0 - base) >> 6) && (u & 1) == part;
             } else if (TYPE == JQ_TYPE_Q6_K) {
-                any = (u >> 1) == ((k0 - base) >> 7);
+                any = (u >> 1) == ((k0 - base) >> 7) && (u & 1) == part;
+            } else if (TYPE == JQ_TYPE_Q8_0) {
+                any = u == part;   // two units of 16 per block, two blocks per chunk
             } else {
-                any = true;
+                any = bb == part;  // Q4_0, Q4_1: one unit per block, two blocks per chunk
             }
             if (!any) {
                 continue;
@@ -155,9 +184,11 @@ __device__ __forceinline__ void dequant_row_chunk(const View& v, int64_t row, in
     }
 }
 
-template <int TYPE>
+template <int TYPE, int TILE_T>
 __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m,
                                                                     const float* __restrict__ bias, float* __restrict__ y) {
+    constexpr int B_BYTES = TILE_T * STAGE_K * 2;
+    constexpr uint32_t IDESC = idesc_of(TILE_T);
     extern __shared__ uint8_t smem_unaligned[];
     // the swizzled tiles must start on 1024-byte boundaries of the shared address space
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
@@ -180,7 +211,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_a(s), 128);
+            mbar_init(full_a(s), DQ_THREADS);
             mbar_init(full_b(s), 1);
             mbar_init(empty(s), 1);
         }
@@ -226,7 +257,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
 #pragma unroll
                 for (int ks = 0; ks < STAGE_K / 16; ks++) {
                     // 16 k = 32 bytes further inside the swizzle row: +2 in the (address >> 4) field
-                    umma(tmem, ad + 2u * ks, bd + 2u * ks, (it | ks) != 0 ? 1u : 0u);
+                    umma(tmem, ad + 2u * ks, bd + 2u * ks, IDESC, (it | ks) != 0 ? 1u : 0u);
                 }
                 umma_commit(empty(s));  // arrives when the MMAs that read this stage have finished
             }
@@ -235,8 +266,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
             }
         }
     } else {
-        // ---- dequantise: thread i of 128 owns feature row f0 + i (rows past n repeat the last row; never stored) ----
-        const int i = threadIdx.x - 64;
+        // ---- dequantise: threads i and 128 + i own feature row f0 + i (rows past n repeat the last row; never stored); the
+        // two halves of a row's chunk go to different warps so that no warp diverges
+        const int i = (threadIdx.x - 64) & 127, part = (threadIdx.x - 64) >> 7;
         int64_t row = (int64_t)f0 + i;
         row = row < v.n ? row : v.n - 1;
         const uint32_t row_off = (uint32_t)((i >> 3) * 1024 + (i & 7) * 128);
@@ -248,7 +280,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
                 ok = false;
                 break;
             }
-            dequant_row_chunk<TYPE>(v, row, it * STAGE_K, a_tiles + s * A_BYTES + row_off, i & 7);
+            if (it + 2 < KT) {
+                prefetch_row_chunk<TYPE>(v, row, (it + 2) * STAGE_K);
+            }
+            dequant_row_chunk<TYPE>(v, row, it * STAGE_K, a_tiles + s * A_BYTES + row_off, i & 7, part);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             mbar_arrive(full_a(s));
         }
@@ -256,10 +291,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
         if (ok && mbar_wait(accum, 0, abort_flag, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int lane_group = warp & 3;  // a warp may only read TMEM lanes 32 (warp % 4) .. + 31
+            const int col_half = (warp - 2) >> 2;  // the two warps of a lane group split the token columns
             const int feature = f0 + lane_group * 32 + lane;
             const float b = (bias != nullptr && feature < v.n) ? bias[feature] : 0.0f;
 #pragma unroll 1
-            for (int c = 0; c < TILE_T / 32; c++) {
+            for (int c = col_half * (TILE_T / 64); c < (col_half + 1) * (TILE_T / 64); c++) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(c * 32);
                 asm volatile(
@@ -333,18 +369,19 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int TYPE>
+template <int TYPE, int TILE_T>
 int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
+    constexpr int B_BYTES = TILE_T * STAGE_K * 2;
     const size_t smem = (size_t)STAGES * (A_BYTES + B_BYTES) + 256 + 1024;  // tiles + barriers + slack for the 1024-byte alignment
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     dim3 grid((unsigned)((v.n + TILE_F - 1) / TILE_F), (unsigned)((m + TILE_T - 1) / TILE_T));
-    prefill_tcgen05_kernel<TYPE><<<grid, THREADS, smem, s>>>(v, xmap, m, bias, y);
+    prefill_tcgen05_kernel<TYPE, TILE_T><<<grid, THREADS, smem, s>>>(v, xmap, m, bias, y);
     count_launch();
     return check_launch("prefill_tcgen05_kernel");
 }
@@ -367,21 +404,29 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {(cuuint64_t)v.k, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)v.k * 2};
-    const cuuint32_t box[2] = {STAGE_K, TILE_T};
+    // 256 tokens per CTA when there are enough of them: every dequantised weight tile then feeds twice the tensor work
+    const int64_t ctas256 = ((v.n + TILE_F - 1) / TILE_F) * ((m + 255) / 256);
+    const int tile_t = (m > 128 && ctas256 >= 140) ? 256 : 128;  // not at the price of leaving SMs without a CTA
+    const cuuint32_t box[2] = {STAGE_K, (cuuint32_t)tile_t};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(x_bf16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         return fail(JQ_ERR_CUDA, "prefill: cuTensorMapEncodeTiled failed with code %d", (int)r);
     }
+#define JQ_PREFILL_CASE(T)                                                                         \
+    case T:                                                                                          \
+        return tile_t == 256 ? launch_typed<T, 256>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128>(v, xmap, (int)m, bias, y, s);
     switch (v.type) {
-        case JQ_TYPE_Q8_0: return launch_typed<JQ_TYPE_Q8_0>(v, xmap, (int)m, bias, y, s);
-        case JQ_TYPE_Q4_0: return launch_typed<JQ_TYPE_Q4_0>(v, xmap, (int)m, bias, y, s);
-        case JQ_TYPE_Q4_1: return launch_typed<JQ_TYPE_Q4_1>(v, xmap, (int)m, bias, y, s);
-        case JQ_TYPE_Q4_K: return launch_typed<JQ_TYPE_Q4_K>(v, xmap, (int)m, bias, y, s);
-        case JQ_TYPE_Q5_K: return launch_typed<JQ_TYPE_Q5_K>(v, xmap, (int)m, bias, y, s);
-        default: return launch_typed<JQ_TYPE_Q6_K>(v, xmap, (int)m, bias, y, s);
+        JQ_PREFILL_CASE(JQ_TYPE_Q8_0)
+        JQ_PREFILL_CASE(JQ_TYPE_Q4_0)
+        JQ_PREFILL_CASE(JQ_TYPE_Q4_1)
+        JQ_PREFILL_CASE(JQ_TYPE_Q4_K)
+        JQ_PREFILL_CASE(JQ_TYPE_Q5_K)
+        default:
+            return tile_t == 256 ? launch_typed<JQ_TYPE_Q6_K, 256>(v, xmap, (int)m, bias, y, s) : launch_typed<JQ_TYPE_Q6_K, 128>(v, xmap, (int)m, bias, y, s);
     }
+#undef JQ_PREFILL_CASE
 }
 
 int launch_f32_to_bf16(const float* x, uint16_t* out, int64_t count, cudaStream_t s) {
