@@ -176,6 +176,30 @@ JQ_API int jq_get_option(const char* name, int64_t* value);
  */
 JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, void* stream);
 
+/*
+ * ---- Llama-style decoder over quantised linears -----------------------------------------------------------------
+ * The block math of jitnn-nn/.../nn/models/Llama.java:167-222 (RMSNorm, rotate-half RoPE with base `rope_base`,
+ * causal grouped-query attention with scale 1/sqrt(head_dim), SwiGLU, residual adds, final norm, output projection,
+ * greedy argmax = first index of the maximum, ops/Reduce.java:201) with every nn.Linear replaced by jq_linear_f32 on
+ * a quantised weight. The reference recomputes every position on each call and has no generation loop; the decoder
+ * here keeps keys and values in a cache of `max_seq` positions, which computes the same function.
+ * Linear slots of a layer: 0 wq, 1 wk, 2 wv, 3 wo, 4 w1 (gate), 5 w3 (up), 6 w2 (down); layer -1 slot 7 is the output
+ * projection. Norm slots: 0 attention norm, 1 feed-forward norm; layer -1 is the final norm. Weights set with
+ * jq_decoder_set_linear are borrowed: they must outlive the decoder. One forward call at a time per decoder.
+ */
+typedef struct jq_decoder jq_decoder;
+JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_heads, int hidden, int vocab, int max_seq, float eps,
+                      float rope_base, jq_decoder** out);
+JQ_API int jq_decoder_destroy(jq_decoder* d);
+JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_weight* w);
+JQ_API int jq_decoder_set_norm(jq_decoder* d, int layer, int which, const float* host_weights);
+JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table);
+/* Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 and appends their keys and values to
+ * the cache. logits_host (or NULL) receives float32 [n_tokens, vocab], next_host (or NULL) the greedy next token after
+ * each of them; the call waits for `stream` when either is requested, otherwise it only enqueues work. */
+JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
+                       void* stream);
+
 /* Pinned host memory for activations and results (faster and truly asynchronous copies). */
 JQ_API int jq_host_alloc(void** ptr, int64_t nbytes);
 JQ_API int jq_host_free(void* ptr);

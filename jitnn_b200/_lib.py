@@ -34,6 +34,12 @@ SIGNATURES = {
     "jq_linear_q4k_f32_noalloc": (c_int, [vp, vp, c_i64, vp, vp, vp]),
     "jq_device_status": (c_int, [c_int, ctypes.POINTER(c_int)]),
     "jq_quantize_q8_0": (c_int, [c_int, vp, c_i64, vp, c_int, vp]),
+    "jq_decoder_create": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_float, ctypes.c_float, ctypes.POINTER(vp)]),
+    "jq_decoder_destroy": (c_int, [vp]),
+    "jq_decoder_set_linear": (c_int, [vp, c_int, c_int, vp]),
+    "jq_decoder_set_norm": (c_int, [vp, c_int, c_int, vp]),
+    "jq_decoder_set_embedding": (c_int, [vp, vp]),
+    "jq_decoder_forward": (c_int, [vp, vp, c_int, c_int, vp, vp, vp]),
     "jq_set_option": (c_int, [ctypes.c_char_p, c_i64]),
     "jq_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_i64)]),
     "jq_host_alloc": (c_int, [ctypes.POINTER(vp), c_i64]),

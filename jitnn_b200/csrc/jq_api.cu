@@ -159,7 +159,7 @@ static std::atomic<int64_t> g_prefill_min_rows{0};
 std::atomic<int64_t> g_opt_gemv_generic{0};
 
 // ---- linear on device pointers --------------------------------------------------------------------
-static int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
     View v = view_of(w);
     const int64_t min_rows = g_prefill_min_rows.load();
     if (min_rows > 0 && m >= min_rows && prefill_supported(v)) {

@@ -1,0 +1,596 @@
+// Llama-style decoder around the quantised linears: the glue kernels (embedding, RMSNorm, RoPE, attention over a
+// key/value cache, SwiGLU, residual adds, greedy argmax) and the host loop that strings them together.
+//
+// The block math is the reference's (jitnn-nn/.../nn/models/Llama.java:209-222; ops/RowNorm.java:266-306;
+// ops/Rope.java:84-149; ops/FlashAttention.java:538-626; F.java:588-599,1158-1161; ops/Reduce.java:201) with each
+// nn.Linear replaced by jq_linear_f32 on a quantised weight. The reference recomputes all positions on every call and
+// has no generation loop; here keys and values are kept in a cache [layer][position][kv_head * head_dim], which
+// computes the same function. All arithmetic is FP32 in a fixed order (the reference's host path uses double).
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "jq_common.cuh"
+
+namespace jq {
+
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s);
+
+namespace {
+
+constexpr int MAX_TOKENS = 8;  // activation rows per forward call
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    // fixed-order sum over a CTA of up to 1024 threads
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = v;
+    }
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < nw; i++) {
+        t += scratch[i];
+    }
+    return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = v;
+    }
+    __syncthreads();
+    float t = scratch[0];
+    for (int i = 1; i < nw; i++) {
+        t = fmaxf(t, scratch[i]);
+    }
+    return t;
+}
+
+struct TokenArgs {
+    int tokens[MAX_TOKENS];
+    int pos0;
+};
+
+// Tokens and start position travel as kernel arguments: no host buffer has to stay valid after the call returns.
+__global__ void set_tokens_kernel(TokenArgs a, int* __restrict__ tokens, int* __restrict__ pos) {
+    if (threadIdx.x < MAX_TOKENS) {
+        tokens[threadIdx.x] = a.tokens[threadIdx.x];
+    }
+    if (threadIdx.x == 0) {
+        *pos = a.pos0;
+    }
+}
+
+// x[t, :] = table[token[t], :]
+__global__ void embed_kernel(const int* __restrict__ tokens, const float* __restrict__ table, float* __restrict__ x, int dim, int vocab) {
+    int tok = tokens[blockIdx.x];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const float4* src = reinterpret_cast<const float4*>(table + (int64_t)tok * dim);
+    float4* dst = reinterpret_cast<float4*>(x + (int64_t)blockIdx.x * dim);
+    for (int i = threadIdx.x; i < dim / 4; i += blockDim.x) {
+        dst[i] = src[i];
+    }
+}
+
+// If delta != nullptr: x += delta (the residual add). Then out = x * rsqrt(mean(x^2) + eps) * w (RMSNorm).
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
+                                   float* __restrict__ out, int dim) {
+    __shared__ float scratch[32];
+    float* xr = x + (int64_t)blockIdx.x * dim;
+    const float* dr = delta != nullptr ? delta + (int64_t)blockIdx.x * dim : nullptr;
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = xr[i];
+        if (dr != nullptr) {
+            v += dr[i];
+            xr[i] = v;
+        }
+        sq = fmaf(v, v, sq);
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+    float* o = out + (int64_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        o[i] = xr[i] * inv * w[i];
+    }
+}
+
+// x += delta (the last residual add of a block)
+__global__ void add_kernel(float* __restrict__ x, const float* __restrict__ delta, int64_t count) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        x[i] += delta[i];
+    }
+}
+
+// Rotate-half RoPE on the query heads (in place) and key heads, and the append of key and value to the cache.
+// grid (tokens, heads + 2 * kv_heads), head_dim / 2 threads.
+__global__ void rope_store_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ k_cache,
+                                  float* __restrict__ v_cache, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                  const int* __restrict__ pos0, int heads, int kv_heads, int head_dim) {
+    const int t = blockIdx.x, h = blockIdx.y, p = threadIdx.x, half = head_dim / 2;
+    const int pos = *pos0 + t;
+    const int kv_dim = kv_heads * head_dim;
+    if (h < heads) {
+        float* qh = q + ((int64_t)t * heads + h) * head_dim;
+        const float c = cos_t[pos * half + p], s = sin_t[pos * half + p];
+        const float a = qh[p], b = qh[p + half];
+        qh[p] = a * c - b * s;
+        qh[p + half] = a * s + b * c;
+    } else if (h < heads + kv_heads) {
+        const int kh = h - heads;
+        const float* src = k + (int64_t)t * kv_dim + kh * head_dim;
+        float* dst = k_cache + (int64_t)pos * kv_dim + kh * head_dim;
+        const float c = cos_t[pos * half + p], s = sin_t[pos * half + p];
+        const float a = src[p], b = src[p + half];
+        dst[p] = a * c - b * s;
+        dst[p + half] = a * s + b * c;
+    } else {
+        const int kh = h - heads - kv_heads;
+        const float* src = v + (int64_t)t * kv_dim + kh * head_dim;
+        float* dst = v_cache + (int64_t)pos * kv_dim + kh * head_dim;
+        dst[p] = src[p];
+        dst[p + half] = src[p + half];
+    }
+}
+
+// Causal attention of query (token t, head h) over cache positions 0 .. pos0 + t. grid (heads, tokens), 256 threads,
+// dynamic shared memory: head_dim + max positions floats.
+__global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                        const float* __restrict__ v_cache, float* __restrict__ out,
+                                                        const int* __restrict__ pos0, int heads, int kv_heads, int head_dim, float scale) {
+    extern __shared__ float sm[];
+    __shared__ float scratch[32];
+    float* qs = sm;
+    float* scores = sm + head_dim;
+    float* partial = scores;  // reused after the scores are consumed? no: kept separate below
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int keys = *pos0 + t + 1;
+    const int kv_dim = kv_heads * head_dim;
+    const int kvh = h / (heads / kv_heads);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* qh = q + ((int64_t)t * heads + h) * head_dim;
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+        qs[i] = qh[i];
+    }
+    __syncthreads();
+    // scores: one warp per key
+    for (int j = warp; j < keys; j += nw) {
+        const float* kr = k_cache + (int64_t)j * kv_dim + kvh * head_dim;
+        float dot = 0.0f;
+        for (int d = lane; d < head_dim; d += 32) {
+            dot = fmaf(qs[d], kr[d], dot);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        }
+        if (lane == 0) {
+            scores[j] = dot * scale;
+        }
+    }
+    __syncthreads();
+    float mx = -INFINITY;
+    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
+        mx = fmaxf(mx, scores[j]);
+    }
+    mx = block_max(mx, scratch);
+    float sum = 0.0f;
+    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
+        const float e = expf(scores[j] - mx);
+        scores[j] = e;
+        sum += e;
+    }
+    sum = block_sum(sum, scratch);
+    const float inv = 1.0f / sum;
+    __syncthreads();
+    // out[d] = sum_j p[j] v[j][d]: thread = (key parity group, dimension)
+    const int groups = blockDim.x / head_dim > 0 ? blockDim.x / head_dim : 1;
+    const int d = threadIdx.x % head_dim, grp = threadIdx.x / head_dim;
+    float acc = 0.0f;
+    if (grp < groups) {
+        for (int j = grp; j < keys; j += groups) {
+            acc = fmaf(scores[j], v_cache[(int64_t)j * kv_dim + kvh * head_dim + d], acc);
+        }
+    }
+    (void)partial;
+    __syncthreads();
+    float* red = sm + head_dim + keys;  // behind the scores
+    if (grp < groups) {
+        red[grp * head_dim + d] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < head_dim) {
+        float total = 0.0f;
+        for (int g2 = 0; g2 < groups; g2++) {
+            total += red[g2 * head_dim + threadIdx.x];
+        }
+        out[((int64_t)t * heads + h) * head_dim + threadIdx.x] = total * inv;
+    }
+}
+
+// act = silu(gate) * up
+__global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ act, int64_t count) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) {
+        const float g = gate[i];
+        act[i] = (g / (1.0f + expf(-g))) * up[i];
+    }
+}
+
+// First index of the maximum of each row (ops/Reduce.java:201). grid = rows, 1024 threads.
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    const float* row = logits + (int64_t)blockIdx.x * vocab;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < idx)) {
+            best = v;
+            idx = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        bv[threadIdx.x >> 5] = best;
+        bi[threadIdx.x >> 5] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) {
+            if (bv[w] > best || (bv[w] == best && bi[w] < idx)) {
+                best = bv[w];
+                idx = bi[w];
+            }
+        }
+        out[blockIdx.x] = idx;
+    }
+}
+
+}  // namespace
+}  // namespace jq
+
+#define JQ_DECODER_MAGIC 0x4a514443u
+
+struct jq_decoder {
+    uint32_t magic;
+    int device;
+    int layers, dim, heads, kv_heads, hidden, vocab, max_seq, head_dim;
+    float eps, rope_base;
+    std::vector<const jq_weight*> lin;  // [layers][7]: wq, wk, wv, wo, w1 (gate), w3 (up), w2 (down)
+    const jq_weight* output;
+    float* norms;        // [layers][2][dim] then final [dim]
+    float* embed;        // [vocab][dim]
+    float *cos_t, *sin_t;
+    float *k_cache, *v_cache;  // [layers][max_seq][kv_dim]
+    float *x, *xn, *q, *k, *v, *att, *proj, *gate, *up, *act, *logits;
+    int *tokens, *pos, *argmax;
+    int* host_stage;     // pinned: tokens in, argmax out
+};
+
+using namespace jq;
+
+static int check_decoder(const jq_decoder* d, const char* who) {
+    if (d == nullptr || d->magic != JQ_DECODER_MAGIC) {
+        return fail(JQ_ERR_INVALID, "%s: not a live decoder handle", who);
+    }
+    return JQ_OK;
+}
+
+extern "C" {
+
+JQ_API int jq_decoder_destroy(jq_decoder* d) {
+    if (d == nullptr) {
+        return JQ_OK;
+    }
+    int rc = check_decoder(d, "jq_decoder_destroy");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(d->device);
+    float* bufs[] = {d->norms, d->embed, d->cos_t, d->sin_t, d->k_cache, d->v_cache, d->x, d->xn, d->q, d->k, d->v, d->att, d->proj, d->gate, d->up,
+                     d->act, d->logits};
+    for (float* p : bufs) {
+        cudaFree(p);
+    }
+    cudaFree(d->tokens);
+    cudaFree(d->pos);
+    cudaFree(d->argmax);
+    cudaFreeHost(d->host_stage);
+    if (prev >= 0) {
+        cudaSetDevice(prev);
+    }
+    d->magic = 0;
+    delete d;
+    return JQ_OK;
+}
+
+JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_heads, int hidden, int vocab, int max_seq, float eps, float rope_base,
+                             jq_decoder** out) {
+    if (out == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_create: null result pointer");
+    }
+    *out = nullptr;
+    if (layers < 1 || dim < 1 || heads < 1 || kv_heads < 1 || hidden < 1 || vocab < 1 || max_seq < 1 || dim % heads != 0 || heads % kv_heads != 0) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_create: inconsistent sizes (dim %d, heads %d, kv heads %d)", dim, heads, kv_heads);
+    }
+    const int head_dim = dim / heads;
+    if (head_dim % 2 != 0 || head_dim > 256 || dim % 4 != 0 || max_seq > 8192) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_create: head_dim %d must be even and at most 256, dim a multiple of 4, max_seq at most 8192", head_dim);
+    }
+    int count = 0;
+    JQ_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_create: device %d of %d", device, count);
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    JQ_CUDA(cudaSetDevice(device));
+    jq_decoder* d = new (std::nothrow) jq_decoder();
+    if (d == nullptr) {
+        return fail(JQ_ERR_OOM, "jq_decoder_create: out of host memory");
+    }
+    d->magic = JQ_DECODER_MAGIC;
+    d->device = device;
+    d->layers = layers; d->dim = dim; d->heads = heads; d->kv_heads = kv_heads; d->hidden = hidden; d->vocab = vocab; d->max_seq = max_seq;
+    d->head_dim = head_dim; d->eps = eps; d->rope_base = rope_base;
+    d->lin.assign((size_t)layers * 7, nullptr);
+    d->output = nullptr;
+    const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
+    struct { float** p; size_t n; } allocs[] = {
+        {&d->norms, ((size_t)layers * 2 + 1) * dim}, {&d->embed, (size_t)vocab * dim}, {&d->cos_t, (size_t)max_seq * head_dim / 2},
+        {&d->sin_t, (size_t)max_seq * head_dim / 2}, {&d->k_cache, (size_t)layers * max_seq * kv_dim}, {&d->v_cache, (size_t)layers * max_seq * kv_dim},
+        {&d->x, T * dim}, {&d->xn, T * dim}, {&d->q, T * dim}, {&d->k, T * kv_dim}, {&d->v, T * kv_dim}, {&d->att, T * dim}, {&d->proj, T * dim},
+        {&d->gate, T * hidden}, {&d->up, T * hidden}, {&d->act, T * hidden}, {&d->logits, T * vocab}};
+    cudaError_t e = cudaSuccess;
+    for (auto& a : allocs) {
+        *a.p = nullptr;
+    }
+    d->tokens = d->pos = d->argmax = nullptr;
+    d->host_stage = nullptr;
+    for (auto& a : allocs) {
+        if (e == cudaSuccess) {
+            e = cudaMalloc(a.p, a.n * sizeof(float));
+        }
+    }
+    if (e == cudaSuccess) e = cudaMalloc(&d->tokens, T * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&d->pos, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&d->argmax, T * sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost(&d->host_stage, (2 * T + 1) * sizeof(int));
+    if (e == cudaSuccess) {
+        // cos / sin tables in double, stored as float (ops/Rope.java:84-101)
+        const int half = head_dim / 2;
+        std::vector<float> c((size_t)max_seq * half), s((size_t)max_seq * half);
+        for (int t = 0; t < max_seq; t++) {
+            for (int i = 0; i < half; i++) {
+                const double freq = std::pow((double)rope_base, -2.0 * i / head_dim);
+                c[(size_t)t * half + i] = (float)std::cos(t * freq);
+                s[(size_t)t * half + i] = (float)std::sin(t * freq);
+            }
+        }
+        e = cudaMemcpy(d->cos_t, c.data(), c.size() * sizeof(float), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(d->sin_t, s.data(), s.size() * sizeof(float), cudaMemcpyHostToDevice);
+    }
+    if (prev >= 0) {
+        cudaSetDevice(prev);
+    }
+    if (e != cudaSuccess) {
+        int rc = cuda_fail(e, "jq_decoder_create");
+        jq_decoder_destroy(d);
+        return rc;
+    }
+    *out = d;
+    return JQ_OK;
+}
+
+JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_weight* w) {
+    int rc = check_decoder(d, "jq_decoder_set_linear");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC || w->device != d->device) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_linear: not a live weight on device %d", d->device);
+    }
+    const int64_t kv_dim = (int64_t)d->kv_heads * d->head_dim;
+    int64_t n = 0, k = 0;
+    if (layer == -1 && which == 7) {
+        n = d->vocab; k = d->dim;
+    } else if (layer >= 0 && layer < d->layers && which >= 0 && which < 7) {
+        const int64_t ns[7] = {d->dim, kv_dim, kv_dim, d->dim, d->hidden, d->hidden, d->dim};
+        const int64_t ks[7] = {d->dim, d->dim, d->dim, d->dim, d->dim, d->dim, d->hidden};
+        n = ns[which]; k = ks[which];
+    } else {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_linear: layer %d, slot %d", layer, which);
+    }
+    if (w->n != n || w->k != k) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_linear: layer %d slot %d needs a [%lld, %lld] weight, got [%lld, %lld]", layer, which, (long long)n,
+                    (long long)k, (long long)w->n, (long long)w->k);
+    }
+    if (layer == -1) {
+        d->output = w;
+    } else {
+        d->lin[(size_t)layer * 7 + which] = w;
+    }
+    return JQ_OK;
+}
+
+JQ_API int jq_decoder_set_norm(jq_decoder* d, int layer, int which, const float* host_weights) {
+    int rc = check_decoder(d, "jq_decoder_set_norm");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    size_t slot;
+    if (layer == -1) {
+        slot = (size_t)d->layers * 2;
+    } else if (layer >= 0 && layer < d->layers && (which == 0 || which == 1)) {
+        slot = (size_t)layer * 2 + which;
+    } else {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_norm: layer %d, slot %d", layer, which);
+    }
+    if (host_weights == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_norm: null weights");
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(d->device);
+    cudaError_t e = cudaMemcpy(d->norms + slot * d->dim, host_weights, (size_t)d->dim * sizeof(float), cudaMemcpyHostToDevice);
+    if (prev >= 0) cudaSetDevice(prev);
+    return e == cudaSuccess ? JQ_OK : cuda_fail(e, "jq_decoder_set_norm");
+}
+
+JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table) {
+    int rc = check_decoder(d, "jq_decoder_set_embedding");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (host_table == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_embedding: null table");
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(d->device);
+    cudaError_t e = cudaMemcpy(d->embed, host_table, (size_t)d->vocab * d->dim * sizeof(float), cudaMemcpyHostToDevice);
+    if (prev >= 0) cudaSetDevice(prev);
+    return e == cudaSuccess ? JQ_OK : cuda_fail(e, "jq_decoder_set_embedding");
+}
+
+// Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 through the decoder and appends their
+// keys and values to the cache. logits_host (may be NULL) receives [n_tokens, vocab], next_host (may be NULL) the greedy
+// next token after each of them. Synchronises `stream` before returning when either output is requested.
+JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host, void* stream) {
+    int rc = check_decoder(d, "jq_decoder_forward");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > MAX_TOKENS || pos0 < 0 || pos0 + n_tokens > d->max_seq) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_forward: %d tokens at position %d (at most %d per call, %d positions)", n_tokens, pos0, MAX_TOKENS,
+                    d->max_seq);
+    }
+    if (d->output == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_forward: the output projection is not set");
+    }
+    for (size_t i = 0; i < d->lin.size(); i++) {
+        if (d->lin[i] == nullptr) {
+            return fail(JQ_ERR_INVALID, "jq_decoder_forward: layer %d linear %d is not set", (int)(i / 7), (int)(i % 7));
+        }
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != d->device) {
+        JQ_CUDA(cudaSetDevice(d->device));
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const int T = n_tokens, dim = d->dim, hd = d->head_dim;
+    const int64_t kv_dim = (int64_t)d->kv_heads * hd;
+    TokenArgs ta;
+    for (int i = 0; i < MAX_TOKENS; i++) {
+        ta.tokens[i] = i < T ? tokens_host[i] : 0;
+    }
+    ta.pos0 = pos0;
+    rc = JQ_OK;
+    auto CK = [&](cudaError_t e, const char* what) {
+        if (rc == JQ_OK && e != cudaSuccess) {
+            rc = cuda_fail(e, what);
+        }
+    };
+    set_tokens_kernel<<<1, 32, 0, s>>>(ta, d->tokens, d->pos);
+    count_launch();
+    rc = check_launch("set_tokens_kernel");
+    auto LIN = [&](const jq_weight* w, const float* in, float* out_) {
+        if (rc == JQ_OK) {
+            rc = linear_device(w, in, T, nullptr, out_, s);
+        }
+    };
+    auto LAUNCHED = [&](const char* name) {
+        count_launch(1);
+        if (rc == JQ_OK) {
+            rc = check_launch(name);
+        }
+    };
+    if (rc == JQ_OK) {
+        embed_kernel<<<T, 256, 0, s>>>(d->tokens, d->embed, d->x, dim, d->vocab);
+        LAUNCHED("embed_kernel");
+    }
+    const float scale = (float)(1.0 / std::sqrt((double)hd));
+    const size_t att_smem = ((size_t)hd + (size_t)(pos0 + T) + 256 + 8) * sizeof(float);
+    for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
+        const jq_weight* const* L = &d->lin[(size_t)l * 7];
+        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        // attention block; the residual add of the previous block's feed-forward output is fused into this norm
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        LIN(L[0], d->xn, d->q);
+        LIN(L[1], d->xn, d->k);
+        LIN(L[2], d->xn, d->v);
+        if (rc != JQ_OK) break;
+        rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd);
+        LAUNCHED("rope_store_kernel");
+        attention_kernel<<<dim3(d->heads, T), 256, att_smem, s>>>(d->q, kc, vc, d->att, d->pos, d->heads, d->kv_heads, hd, scale);
+        LAUNCHED("attention_kernel");
+        LIN(L[3], d->att, d->proj);
+        if (rc != JQ_OK) break;
+        // feed-forward block
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        LIN(L[4], d->xn, d->gate);
+        LIN(L[5], d->xn, d->up);
+        if (rc != JQ_OK) break;
+        const int64_t cnt = (int64_t)T * d->hidden;
+        swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
+        LAUNCHED("swiglu_kernel");
+        LIN(L[6], d->act, d->proj);
+    }
+    if (rc == JQ_OK) {
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        LIN(d->output, d->xn, d->logits);
+    }
+    if (rc == JQ_OK) {
+        argmax_kernel<<<T, 1024, 0, s>>>(d->logits, d->argmax, d->vocab);
+        LAUNCHED("argmax_kernel");
+    }
+    if (rc == JQ_OK && (logits_host != nullptr || next_host != nullptr)) {
+        if (logits_host != nullptr) {
+            CK(cudaMemcpyAsync(logits_host, d->logits, (size_t)T * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s), "logits");
+        }
+        if (next_host != nullptr) {
+            CK(cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, T * sizeof(int), cudaMemcpyDeviceToHost, s), "argmax");
+        }
+        CK(cudaStreamSynchronize(s), "jq_decoder_forward");
+        if (rc == JQ_OK && next_host != nullptr) {
+            for (int i = 0; i < T; i++) {
+                next_host[i] = d->host_stage[MAX_TOKENS + 1 + i];
+            }
+        }
+    }
+    if (prev >= 0 && prev != d->device) {
+        cudaSetDevice(prev);
+    }
+    return rc;
+}
+
+}  // extern "C"
