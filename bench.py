@@ -302,6 +302,12 @@ def run_ours(args):
                "ms_per_step": round(dt * 1e3, 4)}
 
     prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
+    decode = None
+    if rank == 0 and world == 1 and not args.only and not args.no_decode:
+        for copies in pools:
+            for w in copies:
+                w.release()  # make room: the decoder holds 5 GB of weights and 1 GB of cache
+        decode = decode_leg(torch, device)
     cpu = cpu_baseline_leg(threads=1, fraction=1, steps=2) if (rank == 0 and world == 1 and not args.no_cpu) else None
 
     if rank == 0:
@@ -321,7 +327,7 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -371,6 +377,69 @@ def prefill_leg(torch, device, L, _lib):
         out["shapes"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "TFLOPs": round(tf, 1), "frac": round(tf / peak, 4)}
         w.release()
     return out
+
+
+def decode_leg(torch, device):
+    """BASELINE.json configs[3]: Llama-style decoder, 7B shape (32 layers, d 4096, 32 heads, FFN 11008, vocab 32000),
+    seeded N(0, 0.02) weights quantised Q4_K_M-style (Q6_K for wv, w2 and the output projection, Q4_K elsewhere),
+    512 uniform-random prompt tokens, then 128 greedy tokens at batch 1. Reports decode tokens/s."""
+    import numpy as np
+    from jitnn_b200 import LlamaDecoder, synth
+    layers, dim, heads, hidden, vocab, prompt_len, gen = 32, 4096, 32, 11008, 32000, 512, 128
+    dec = LlamaDecoder(layers, dim, heads, heads, hidden, vocab, max_seq=prompt_len + gen + 8, device=device.index)
+    g = torch.Generator(device=device).manual_seed(2024)
+
+    def lin(n, k, t):
+        wf = torch.randn(n, k, generator=g, device=device) * 0.02
+        return (t, synth.QUANTIZERS[t](wf).cpu().numpy().reshape(-1), n, k)
+
+    weight_bytes = 0
+    bpw = {"Q4_K": 144 / 256, "Q6_K": 210 / 256}
+    for l in range(layers):
+        w = {}
+        p = "layers.%d." % l
+        for name, n, k, t in [("wq", dim, dim, "Q4_K"), ("wk", dim, dim, "Q4_K"), ("wv", dim, dim, "Q6_K"), ("wo", dim, dim, "Q4_K"),
+                              ("w1", hidden, dim, "Q4_K"), ("w3", hidden, dim, "Q4_K"), ("w2", dim, hidden, "Q6_K")]:
+            w[p + name] = lin(n, k, t)
+            weight_bytes += n * k * bpw[t]
+        w[p + "attention_norm"] = np.ones(dim, np.float32)
+        w[p + "ffn_norm"] = np.ones(dim, np.float32)
+        dec.load(w)
+    dec.load({"output": lin(vocab, dim, "Q6_K"), "norm": np.ones(dim, np.float32),
+              "tok_embeddings": (torch.randn(vocab, dim, generator=g, device=device) * 0.02).cpu().numpy()})
+    weight_bytes += vocab * dim * bpw["Q6_K"]
+    prompt = np.random.default_rng(11).integers(0, vocab, prompt_len).astype(np.int32)
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    for i in range(0, prompt_len - 8, 8):
+        dec.enqueue(prompt[i:i + 8], i)
+    _, nxt = dec.forward(prompt[prompt_len - 8:], prompt_len - 8, want_logits=False)
+    t_prompt = time.perf_counter() - t0
+    tok = int(nxt[-1])
+    out = []
+    # two untimed steps: the first runs eagerly, the second captures the decode step into a CUDA graph
+    pos = prompt_len
+    for _ in range(2):
+        _, nxt = dec.forward([tok], pos, want_logits=False)
+        tok = int(nxt[0])
+        out.append(tok)
+        pos += 1
+    t0 = time.perf_counter()
+    for _ in range(gen - 2):
+        _, nxt = dec.forward([tok], pos, want_logits=False)
+        tok = int(nxt[0])
+        out.append(tok)
+        pos += 1
+    dt = (time.perf_counter() - t0) / (gen - 2)
+    dec.close()
+    peak, which = measured_peaks()
+    kv_bytes = 2 * layers * (prompt_len + gen // 2) * dim * 4
+    return {"tokens_per_s": round(1.0 / dt, 1), "ms_per_token": round(dt * 1e3, 4), "prompt_tokens_per_s": round(prompt_len / t_prompt, 1),
+            "weight_bytes_per_token": int(weight_bytes), "kv_cache_bytes_per_token": int(kv_bytes),
+            "hbm_roofline_tokens_per_s": round(peak * 1e9 / (weight_bytes + kv_bytes), 1),
+            "frac": round((weight_bytes + kv_bytes) / dt / 1e9 / peak, 4), "peak_source": "of " + which,
+            "config": "7B shape, 32 layers, Q4_K + Q6_K (wv, w2, output), prompt 512 in groups of 8, 128 greedy tokens, fp32 KV cache",
+            "first_tokens": out[:8]}
 
 
 def cpu_baseline_leg(threads, fraction, steps=1, warmup=0):
@@ -437,6 +506,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
     ap.add_argument("--eager", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default=None, metavar="NxKxM",
                     help="restrict the sweep to one shape and batch, e.g. 32000x4096x1 (a small case for profiler captures)")

@@ -153,6 +153,7 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "prefill_min_rows"  rows of x from which jq_linear_f32 rounds x to bfloat16 and uses the
  *                       tensor-core prefill kernel (default 0 = never: FP32 results for every m).
  *   "gemv_generic"      non-zero: every decode GEMV runs on the generic CUDA-core kernel (for comparisons).
+ *   "decoder_graph"     zero: the decoder issues its single-token step kernel by kernel instead of replaying a CUDA graph.
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);
@@ -196,7 +197,9 @@ JQ_API int jq_decoder_set_norm(jq_decoder* d, int layer, int which, const float*
 JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table);
 /* Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 and appends their keys and values to
  * the cache. logits_host (or NULL) receives float32 [n_tokens, vocab], next_host (or NULL) the greedy next token after
- * each of them; the call waits for `stream` when either is requested, otherwise it only enqueues work. */
+ * each of them; the call waits for `stream` when either is requested, otherwise it only enqueues work. With a NULL
+ * stream the decoder uses a stream of its own. Single-token calls that ask for the next token (the decode step) are
+ * captured into a CUDA graph on their second occurrence and replayed afterwards. */
 JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
                        void* stream);
 

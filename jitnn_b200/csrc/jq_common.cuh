@@ -119,6 +119,8 @@ int prefill_status(int* status);
 
 // Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_generic;
+// Option "decoder_graph": zero keeps the decoder's single-token step on eager launches (for comparisons).
+extern std::atomic<int64_t> g_opt_decoder_graph;
 
 }  // namespace jq
 

@@ -145,78 +145,122 @@ __global__ void rope_store_kernel(float* __restrict__ q, const float* __restrict
     }
 }
 
-// Causal attention of query (token t, head h) over cache positions 0 .. pos0 + t. grid (heads, tokens), 256 threads,
-// dynamic shared memory: head_dim + max positions floats.
-__global__ void __launch_bounds__(256) attention_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
-                                                        const float* __restrict__ v_cache, float* __restrict__ out,
-                                                        const int* __restrict__ pos0, int heads, int kv_heads, int head_dim, float scale) {
-    extern __shared__ float sm[];
+// Causal attention of query (token t, head h) over cache positions 0 .. pos0 + t, split over the keys so that enough CTAs
+// are in flight to stream the cache at memory speed: CTA (h, split, t) handles keys [split * ATT_CHUNK, + ATT_CHUNK) and
+// writes an unnormalised partial result (running maximum m, sum of exponentials l, sum of exp(score - m) * v); the
+// combine kernel merges the partials of a (token, head) in split order. 128 threads; thread d owns output dimension d.
+constexpr int ATT_CHUNK = 64;
+constexpr int ATT_THREADS = 128;
+
+__global__ void __launch_bounds__(ATT_THREADS) attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                        const float* __restrict__ v_cache, float* __restrict__ part,
+                                                                        const int* __restrict__ pos0, int heads, int kv_heads, int head_dim,
+                                                                        int splits, float scale) {
+    __shared__ float qs[256];
+    __shared__ float sc[ATT_CHUNK];
     __shared__ float scratch[32];
-    float* qs = sm;
-    float* scores = sm + head_dim;
-    float* partial = scores;  // reused after the scores are consumed? no: kept separate below
-    const int h = blockIdx.x, t = blockIdx.y;
+    const int h = blockIdx.x, sp = blockIdx.y, t = blockIdx.z;
     const int keys = *pos0 + t + 1;
+    const int k0 = sp * ATT_CHUNK;
+    float* out = part + (((int64_t)t * heads + h) * splits + sp) * (head_dim + 2);
+    if (k0 >= keys) {
+        if (threadIdx.x == 0) {
+            out[head_dim] = -INFINITY;  // m
+            out[head_dim + 1] = 0.0f;   // l
+        }
+        return;
+    }
+    const int cnt = keys - k0 < ATT_CHUNK ? keys - k0 : ATT_CHUNK;
     const int kv_dim = kv_heads * head_dim;
     const int kvh = h / (heads / kv_heads);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* qh = q + ((int64_t)t * heads + h) * head_dim;
-    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+    for (int i = threadIdx.x; i < head_dim; i += ATT_THREADS) {
         qs[i] = qh[i];
     }
     __syncthreads();
-    // scores: one warp per key
-    for (int j = warp; j < keys; j += nw) {
-        const float* kr = k_cache + (int64_t)j * kv_dim + kvh * head_dim;
-        float dot = 0.0f;
-        for (int d = lane; d < head_dim; d += 32) {
-            dot = fmaf(qs[d], kr[d], dot);
+    // scores: one warp per key, four keys in flight per warp
+    const float* kbase = k_cache + (int64_t)k0 * kv_dim + kvh * head_dim;
+    for (int j0 = warp * 4; j0 < cnt; j0 += 16) {
+        float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            if (j0 + u < cnt) {
+                const float* kr = kbase + (int64_t)(j0 + u) * kv_dim;
+                for (int d = lane; d < head_dim; d += 32) {
+                    dot[u] = fmaf(qs[d], kr[d], dot[u]);
+                }
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        }
-        if (lane == 0) {
-            scores[j] = dot * scale;
+        for (int u = 0; u < 4; u++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+            }
+            if (lane == 0 && j0 + u < cnt) {
+                sc[j0 + u] = dot[u] * scale;
+            }
         }
     }
     __syncthreads();
-    float mx = -INFINITY;
-    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
-        mx = fmaxf(mx, scores[j]);
-    }
+    float mx = threadIdx.x < cnt ? sc[threadIdx.x] : -INFINITY;
     mx = block_max(mx, scratch);
-    float sum = 0.0f;
-    for (int j = threadIdx.x; j < keys; j += blockDim.x) {
-        const float e = expf(scores[j] - mx);
-        scores[j] = e;
-        sum += e;
+    float e = 0.0f;
+    if (threadIdx.x < cnt) {
+        e = expf(sc[threadIdx.x] - mx);
+        sc[threadIdx.x] = e;
     }
-    sum = block_sum(sum, scratch);
-    const float inv = 1.0f / sum;
+    const float l = block_sum(e, scratch);
     __syncthreads();
-    // out[d] = sum_j p[j] v[j][d]: thread = (key parity group, dimension)
-    const int groups = blockDim.x / head_dim > 0 ? blockDim.x / head_dim : 1;
-    const int d = threadIdx.x % head_dim, grp = threadIdx.x / head_dim;
-    float acc = 0.0f;
-    if (grp < groups) {
-        for (int j = grp; j < keys; j += groups) {
-            acc = fmaf(scores[j], v_cache[(int64_t)j * kv_dim + kvh * head_dim + d], acc);
+    // partial output: thread d (and d + 128 for wide heads) sums over the chunk's keys, four at a time
+    const float* vbase = v_cache + (int64_t)k0 * kv_dim + kvh * head_dim;
+    for (int d = threadIdx.x; d < head_dim; d += ATT_THREADS) {
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int j = 0;
+        for (; j + 3 < cnt; j += 4) {
+            a0 = fmaf(sc[j], vbase[(int64_t)j * kv_dim + d], a0);
+            a1 = fmaf(sc[j + 1], vbase[(int64_t)(j + 1) * kv_dim + d], a1);
+            a2 = fmaf(sc[j + 2], vbase[(int64_t)(j + 2) * kv_dim + d], a2);
+            a3 = fmaf(sc[j + 3], vbase[(int64_t)(j + 3) * kv_dim + d], a3);
+        }
+        for (; j < cnt; j++) {
+            a0 = fmaf(sc[j], vbase[(int64_t)j * kv_dim + d], a0);
+        }
+        out[d] = (a0 + a1) + (a2 + a3);
+    }
+    if (threadIdx.x == 0) {
+        out[head_dim] = mx;
+        out[head_dim + 1] = l;
+    }
+}
+
+// out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over the splits of (t, h), in split order.
+__global__ void attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, int heads, int head_dim, int stride_splits,
+                                         int splits) {
+    // stride_splits = chunks the partial buffer was laid out for, splits = chunks written by this call
+    const int h = blockIdx.x, t = blockIdx.y;
+    const float* p = part + ((int64_t)t * heads + h) * stride_splits * (head_dim + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) {
+        M = fmaxf(M, p[(int64_t)s * (head_dim + 2) + head_dim]);
+    }
+    float L = 0.0f;
+    for (int s = 0; s < splits; s++) {
+        const float m = p[(int64_t)s * (head_dim + 2) + head_dim];
+        if (m != -INFINITY) {
+            L = fmaf(expf(m - M), p[(int64_t)s * (head_dim + 2) + head_dim + 1], L);
         }
     }
-    (void)partial;
-    __syncthreads();
-    float* red = sm + head_dim + keys;  // behind the scores
-    if (grp < groups) {
-        red[grp * head_dim + d] = acc;
-    }
-    __syncthreads();
-    if (threadIdx.x < head_dim) {
-        float total = 0.0f;
-        for (int g2 = 0; g2 < groups; g2++) {
-            total += red[g2 * head_dim + threadIdx.x];
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; s++) {
+            const float m = p[(int64_t)s * (head_dim + 2) + head_dim];
+            if (m != -INFINITY) {
+                acc = fmaf(expf(m - M), p[(int64_t)s * (head_dim + 2) + d], acc);
+            }
         }
-        out[((int64_t)t * heads + h) * head_dim + threadIdx.x] = total * inv;
+        out[((int64_t)t * heads + h) * head_dim + d] = acc / L;
     }
 }
 
@@ -285,8 +329,13 @@ struct jq_decoder {
     float *cos_t, *sin_t;
     float *k_cache, *v_cache;  // [layers][max_seq][kv_dim]
     float *x, *xn, *q, *k, *v, *att, *proj, *gate, *up, *act, *logits;
+    float* att_part;     // [tokens][heads][splits][head_dim + 2] partial attention results
+    int splits;          // key chunks of ATT_CHUNK positions covering max_seq
     int *tokens, *pos, *argmax;
-    int* host_stage;     // pinned: tokens in, argmax out
+    int* host_stage;     // pinned: [0..7] tokens in, [8] position in, [9..16] argmax out
+    int warm_calls;      // single-token forwards issued so far
+    cudaGraphExec_t graph;  // the single-token forward, captured on its second call
+    cudaStream_t own_stream;  // used when the caller passes no stream (the legacy default stream cannot be captured)
 };
 
 using namespace jq;
@@ -312,7 +361,7 @@ JQ_API int jq_decoder_destroy(jq_decoder* d) {
     cudaGetDevice(&prev);
     cudaSetDevice(d->device);
     float* bufs[] = {d->norms, d->embed, d->cos_t, d->sin_t, d->k_cache, d->v_cache, d->x, d->xn, d->q, d->k, d->v, d->att, d->proj, d->gate, d->up,
-                     d->act, d->logits};
+                     d->act, d->logits, d->att_part};
     for (float* p : bufs) {
         cudaFree(p);
     }
@@ -320,6 +369,13 @@ JQ_API int jq_decoder_destroy(jq_decoder* d) {
     cudaFree(d->pos);
     cudaFree(d->argmax);
     cudaFreeHost(d->host_stage);
+    if (d->graph != nullptr) {
+        cudaGraphExecDestroy(d->graph);
+    }
+    if (d->own_stream != nullptr) {
+        cudaStreamSynchronize(d->own_stream);
+        cudaStreamDestroy(d->own_stream);
+    }
     if (prev >= 0) {
         cudaSetDevice(prev);
     }
@@ -359,12 +415,17 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     d->head_dim = head_dim; d->eps = eps; d->rope_base = rope_base;
     d->lin.assign((size_t)layers * 7, nullptr);
     d->output = nullptr;
+    d->warm_calls = 0;
+    d->graph = nullptr;
+    d->own_stream = nullptr;
     const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
+    d->splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     struct { float** p; size_t n; } allocs[] = {
         {&d->norms, ((size_t)layers * 2 + 1) * dim}, {&d->embed, (size_t)vocab * dim}, {&d->cos_t, (size_t)max_seq * head_dim / 2},
         {&d->sin_t, (size_t)max_seq * head_dim / 2}, {&d->k_cache, (size_t)layers * max_seq * kv_dim}, {&d->v_cache, (size_t)layers * max_seq * kv_dim},
         {&d->x, T * dim}, {&d->xn, T * dim}, {&d->q, T * dim}, {&d->k, T * kv_dim}, {&d->v, T * kv_dim}, {&d->att, T * dim}, {&d->proj, T * dim},
-        {&d->gate, T * hidden}, {&d->up, T * hidden}, {&d->act, T * hidden}, {&d->logits, T * vocab}};
+        {&d->gate, T * hidden}, {&d->up, T * hidden}, {&d->act, T * hidden}, {&d->logits, T * vocab},
+        {&d->att_part, T * (size_t)heads * d->splits * (head_dim + 2)}};
     cudaError_t e = cudaSuccess;
     for (auto& a : allocs) {
         *a.p = nullptr;
@@ -380,6 +441,7 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     if (e == cudaSuccess) e = cudaMalloc(&d->pos, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&d->argmax, T * sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost(&d->host_stage, (2 * T + 1) * sizeof(int));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) {
         // cos / sin tables in double, stored as float (ops/Rope.java:84-101)
         const int half = head_dim / 2;
@@ -429,6 +491,10 @@ JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_w
         return fail(JQ_ERR_INVALID, "jq_decoder_set_linear: layer %d slot %d needs a [%lld, %lld] weight, got [%lld, %lld]", layer, which, (long long)n,
                     (long long)k, (long long)w->n, (long long)w->k);
     }
+    if (d->graph != nullptr) {
+        cudaGraphExecDestroy(d->graph);  // the captured forward holds the old weight
+        d->graph = nullptr;
+    }
     if (layer == -1) {
         d->output = w;
     } else {
@@ -477,48 +543,12 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table) {
     return e == cudaSuccess ? JQ_OK : cuda_fail(e, "jq_decoder_set_embedding");
 }
 
-// Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 through the decoder and appends their
-// keys and values to the cache. logits_host (may be NULL) receives [n_tokens, vocab], next_host (may be NULL) the greedy
-// next token after each of them. Synchronises `stream` before returning when either output is requested.
-JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host, void* stream) {
-    int rc = check_decoder(d, "jq_decoder_forward");
-    if (rc != JQ_OK) {
-        return rc;
-    }
-    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > MAX_TOKENS || pos0 < 0 || pos0 + n_tokens > d->max_seq) {
-        return fail(JQ_ERR_INVALID, "jq_decoder_forward: %d tokens at position %d (at most %d per call, %d positions)", n_tokens, pos0, MAX_TOKENS,
-                    d->max_seq);
-    }
-    if (d->output == nullptr) {
-        return fail(JQ_ERR_INVALID, "jq_decoder_forward: the output projection is not set");
-    }
-    for (size_t i = 0; i < d->lin.size(); i++) {
-        if (d->lin[i] == nullptr) {
-            return fail(JQ_ERR_INVALID, "jq_decoder_forward: layer %d linear %d is not set", (int)(i / 7), (int)(i % 7));
-        }
-    }
-    int prev = -1;
-    cudaGetDevice(&prev);
-    if (prev != d->device) {
-        JQ_CUDA(cudaSetDevice(d->device));
-    }
-    cudaStream_t s = (cudaStream_t)stream;
-    const int T = n_tokens, dim = d->dim, hd = d->head_dim;
+// Enqueues the forward of T tokens on s. Tokens and position come either from kernel arguments (ta != nullptr) or, for
+// the captured single-token graph, from the pinned staging words through a host-to-device copy.
+static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* ta, cudaStream_t s) {
+    const int dim = d->dim, hd = d->head_dim;
     const int64_t kv_dim = (int64_t)d->kv_heads * hd;
-    TokenArgs ta;
-    for (int i = 0; i < MAX_TOKENS; i++) {
-        ta.tokens[i] = i < T ? tokens_host[i] : 0;
-    }
-    ta.pos0 = pos0;
-    rc = JQ_OK;
-    auto CK = [&](cudaError_t e, const char* what) {
-        if (rc == JQ_OK && e != cudaSuccess) {
-            rc = cuda_fail(e, what);
-        }
-    };
-    set_tokens_kernel<<<1, 32, 0, s>>>(ta, d->tokens, d->pos);
-    count_launch();
-    rc = check_launch("set_tokens_kernel");
+    int rc = JQ_OK;
     auto LIN = [&](const jq_weight* w, const float* in, float* out_) {
         if (rc == JQ_OK) {
             rc = linear_device(w, in, T, nullptr, out_, s);
@@ -530,12 +560,23 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
             rc = check_launch(name);
         }
     };
+    if (ta != nullptr) {
+        set_tokens_kernel<<<1, 32, 0, s>>>(*ta, d->tokens, d->pos);
+        LAUNCHED("set_tokens_kernel");
+    } else {
+        cudaError_t e = cudaMemcpyAsync(d->tokens, d->host_stage, MAX_TOKENS * sizeof(int), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(d->pos, d->host_stage + MAX_TOKENS, sizeof(int), cudaMemcpyHostToDevice, s);
+        }
+        if (e != cudaSuccess) {
+            return cuda_fail(e, "decoder inputs");
+        }
+    }
     if (rc == JQ_OK) {
         embed_kernel<<<T, 256, 0, s>>>(d->tokens, d->embed, d->x, dim, d->vocab);
         LAUNCHED("embed_kernel");
     }
     const float scale = (float)(1.0 / std::sqrt((double)hd));
-    const size_t att_smem = ((size_t)hd + (size_t)(pos0 + T) + 256 + 8) * sizeof(float);
     for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
         float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
@@ -549,8 +590,13 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
         if (rc != JQ_OK) break;
         rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd);
         LAUNCHED("rope_store_kernel");
-        attention_kernel<<<dim3(d->heads, T), 256, att_smem, s>>>(d->q, kc, vc, d->att, d->pos, d->heads, d->kv_heads, hd, scale);
-        LAUNCHED("attention_kernel");
+        // only the key chunks that can hold a position of this call are launched (all of them inside the captured graph)
+        const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
+        attention_partial_kernel<<<dim3(d->heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, d->heads, d->kv_heads, hd,
+                                                                                 d->splits, scale);
+        LAUNCHED("attention_partial_kernel");
+        attention_combine_kernel<<<dim3(d->heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, d->heads, hd, d->splits, splits_now);
+        LAUNCHED("attention_combine_kernel");
         LIN(L[3], d->att, d->proj);
         if (rc != JQ_OK) break;
         // feed-forward block
@@ -573,12 +619,86 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
         argmax_kernel<<<T, 1024, 0, s>>>(d->logits, d->argmax, d->vocab);
         LAUNCHED("argmax_kernel");
     }
+    return rc;
+}
+
+// Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 through the decoder and appends their
+// keys and values to the cache. logits_host (may be NULL) receives [n_tokens, vocab], next_host (may be NULL) the greedy
+// next token after each of them. Synchronises `stream` before returning when either output is requested.
+// A single-token call that asks for the next token is the decode step: its second occurrence is captured into a CUDA
+// graph (all launches of the step read token and position from memory), later ones replay the graph.
+JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host, void* stream) {
+    int rc = check_decoder(d, "jq_decoder_forward");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > MAX_TOKENS || pos0 < 0 || pos0 + n_tokens > d->max_seq) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_forward: %d tokens at position %d (at most %d per call, %d positions)", n_tokens, pos0, MAX_TOKENS,
+                    d->max_seq);
+    }
+    if (d->output == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_forward: the output projection is not set");
+    }
+    for (size_t i = 0; i < d->lin.size(); i++) {
+        if (d->lin[i] == nullptr) {
+            return fail(JQ_ERR_INVALID, "jq_decoder_forward: layer %d linear %d is not set", (int)(i / 7), (int)(i % 7));
+        }
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != d->device) {
+        JQ_CUDA(cudaSetDevice(d->device));
+    }
+    // all state of a decoder is private to it and its inputs come from the host, so its own stream is as good as any
+    cudaStream_t s = stream != nullptr ? (cudaStream_t)stream : d->own_stream;
+    const int T = n_tokens;
+    const bool decode_step = T == 1 && next_host != nullptr && g_opt_decoder_graph.load() != 0;
+    auto CK = [&](cudaError_t e, const char* what) {
+        if (rc == JQ_OK && e != cudaSuccess) {
+            rc = cuda_fail(e, what);
+        }
+    };
+    if (decode_step && d->warm_calls >= 1) {
+        // the staging words are free again: every decode step ends with a wait for the stream
+        d->host_stage[0] = tokens_host[0];
+        d->host_stage[MAX_TOKENS] = pos0;
+        if (d->graph == nullptr) {
+            cudaGraph_t g = nullptr;
+            CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+            if (rc == JQ_OK) {
+                rc = enqueue_forward(d, 1, d->max_seq, nullptr, s);
+                cudaError_t e = cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, sizeof(int), cudaMemcpyDeviceToHost, s);
+                cudaError_t e2 = cudaStreamEndCapture(s, &g);
+                CK(e, "argmax copy");
+                CK(e2, "cudaStreamEndCapture");
+            }
+            if (rc == JQ_OK) {
+                CK(cudaGraphInstantiate(&d->graph, g, 0), "cudaGraphInstantiate");
+            }
+            if (g != nullptr) {
+                cudaGraphDestroy(g);
+            }
+        }
+        if (rc == JQ_OK) {
+            CK(cudaGraphLaunch(d->graph, s), "cudaGraphLaunch");
+        }
+    } else {
+        TokenArgs ta;
+        for (int i = 0; i < MAX_TOKENS; i++) {
+            ta.tokens[i] = i < T ? tokens_host[i] : 0;
+        }
+        ta.pos0 = pos0;
+        rc = enqueue_forward(d, T, pos0 + T, &ta, s);
+        if (rc == JQ_OK && next_host != nullptr) {
+            CK(cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, T * sizeof(int), cudaMemcpyDeviceToHost, s), "argmax");
+        }
+        if (decode_step) {
+            d->warm_calls++;
+        }
+    }
     if (rc == JQ_OK && (logits_host != nullptr || next_host != nullptr)) {
         if (logits_host != nullptr) {
             CK(cudaMemcpyAsync(logits_host, d->logits, (size_t)T * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s), "logits");
-        }
-        if (next_host != nullptr) {
-            CK(cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, T * sizeof(int), cudaMemcpyDeviceToHost, s), "argmax");
         }
         CK(cudaStreamSynchronize(s), "jq_decoder_forward");
         if (rc == JQ_OK && next_host != nullptr) {
