@@ -162,6 +162,12 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     L = jitnn_b200.load()
 
+    if args.leg in ("prefill", "decode"):
+        # one leg alone, for profiler captures: no sweep, a short line of its own
+        out = prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else decode_leg(torch, device)
+        print(json.dumps({"leg": args.leg, "result": out}), flush=True)
+        return
+
     pools, first_raw = make_weights(torch, device, rank, world)
     g = torch.Generator(device=device).manual_seed(99)
     xs = {(k, m): torch.randn(m, k, generator=g, device=device) for _, k in SHAPES for m in BATCHES}
@@ -506,6 +512,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"],
+                    help="run only the prefill GEMM leg or only the 7B-shape decode leg (one GPU; for profiler captures)")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
     ap.add_argument("--eager", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default=None, metavar="NxKxM",
