@@ -55,9 +55,22 @@ struct Fmt;
 template <>
 struct Fmt<JQ_TYPE_Q8_0> {
     static constexpr int QK = 32, UNITS = 2, RUNS = 1;
+    struct Raw {
+        uint4 q;
+        uint32_t d;
+    };
+    __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
+        r.q = ld16(v.q + block * 32 + unit * 16);
+        r.d = __ldg(reinterpret_cast<const unsigned short*>(v.aux) + block);
+    }
     __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
-        uint4 q = ld16(v.q + block * 32 + unit * 16);
-        float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(v.aux) + block));
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 q = r.q;
+        float d = half_bits_to_float(r.d);
         uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int i = 0; i < 16; i++) {
@@ -72,9 +85,22 @@ struct Fmt<JQ_TYPE_Q8_0> {
 template <>
 struct Fmt<JQ_TYPE_Q4_0> {
     static constexpr int QK = 32, UNITS = 1, RUNS = 2;
-    __device__ static void decode(const View& v, int64_t block, int, float (&out)[RUNS][16], int (&pos)[RUNS]) {
-        uint4 q = ld16(v.q + block * 16);
-        float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(v.aux) + block));
+    struct Raw {
+        uint4 q;
+        uint32_t d;
+    };
+    __device__ static void load(const View& v, int64_t block, int, Raw& r) {
+        r.q = ld16(v.q + block * 16);
+        r.d = __ldg(reinterpret_cast<const unsigned short*>(v.aux) + block);
+    }
+    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 q = r.q;
+        float d = half_bits_to_float(r.d);
         uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
         for (int i = 0; i < 16; i++) {
@@ -91,9 +117,22 @@ struct Fmt<JQ_TYPE_Q4_0> {
 template <>
 struct Fmt<JQ_TYPE_Q4_1> {
     static constexpr int QK = 32, UNITS = 1, RUNS = 2;
-    __device__ static void decode(const View& v, int64_t block, int, float (&out)[RUNS][16], int (&pos)[RUNS]) {
-        uint4 q = ld16(v.q + block * 16);
-        uint32_t dm = __ldg(reinterpret_cast<const uint32_t*>(v.aux) + block);
+    struct Raw {
+        uint4 q;
+        uint32_t dm;
+    };
+    __device__ static void load(const View& v, int64_t block, int, Raw& r) {
+        r.q = ld16(v.q + block * 16);
+        r.dm = __ldg(reinterpret_cast<const uint32_t*>(v.aux) + block);
+    }
+    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 q = r.q;
+        const uint32_t dm = r.dm;
         float d = half_bits_to_float(dm), m = half_bits_to_float(dm >> 16);
         uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -111,10 +150,21 @@ struct Fmt<JQ_TYPE_Q4_1> {
 template <>
 struct Fmt<JQ_TYPE_Q4_K> {
     static constexpr int QK = 256, UNITS = 8, RUNS = 2;
-    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+    struct Raw {
+        uint4 h, q;
+    };
+    __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
         const uint8_t* b = v.q + block * 144;
-        uint4 h = ld16(b);
-        uint4 q = ld16(b + 16 + unit * 16);
+        r.h = ld16(b);
+        r.q = ld16(b + 16 + unit * 16);
+    }
+    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 h = r.h, q = r.q;
         float d = half_bits_to_float(h.x), dmin = half_bits_to_float(h.x >> 16);
         int j = unit >> 1, hf = unit & 1;
         int sc0, mn0, sc1, mn1;
@@ -138,12 +188,23 @@ struct Fmt<JQ_TYPE_Q4_K> {
 template <>
 struct Fmt<JQ_TYPE_Q5_K> {
     static constexpr int QK = 256, UNITS = 8, RUNS = 2;
-    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+    struct Raw {
+        uint4 h, hi, q;
+    };
+    __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
         const uint8_t* b = v.q + block * 176;
-        uint4 h = ld16(b);
+        r.h = ld16(b);
+        r.hi = ld16(b + 16 + (unit & 1) * 16);
+        r.q = ld16(b + 48 + unit * 16);
+    }
+    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 h = r.h, hi = r.hi, q = r.q;
         int j = unit >> 1, hf = unit & 1;
-        uint4 hi = ld16(b + 16 + hf * 16);
-        uint4 q = ld16(b + 48 + unit * 16);
         float d = half_bits_to_float(h.x), dmin = half_bits_to_float(h.x >> 16);
         int sc0, mn0, sc1, mn1;
         k_scale_min(h.y, h.z, h.w, 2 * j, sc0, mn0);
@@ -170,14 +231,28 @@ struct Fmt<JQ_TYPE_Q5_K> {
 template <>
 struct Fmt<JQ_TYPE_Q6_K> {
     static constexpr int QK = 256, UNITS = 4, RUNS = 4;
-    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+    struct Raw {
+        uint4 la, lb, hq, sv;
+        uint32_t d;
+    };
+    __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
         const uint8_t* b = v.q + block * 208;
+        const int n = unit >> 1, c = unit & 1;
+        r.la = ld16(b + 64 * n + 16 * c);
+        r.lb = ld16(b + 64 * n + 32 + 16 * c);
+        r.hq = ld16(b + 128 + 32 * n + 16 * c);
+        r.sv = ld16(b + 192);
+        r.d = __ldg(reinterpret_cast<const unsigned short*>(v.aux) + block);
+    }
+    __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        Raw r;
+        load(v, block, unit, r);
+        convert(r, unit, out, pos);
+    }
+    __device__ static void convert(const Raw& r, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
+        const uint4 la = r.la, lb = r.lb, hq = r.hq, sv = r.sv;
         int n = unit >> 1, c = unit & 1;
-        uint4 la = ld16(b + 64 * n + 16 * c);
-        uint4 lb = ld16(b + 64 * n + 32 + 16 * c);
-        uint4 hq = ld16(b + 128 + 32 * n + 16 * c);
-        uint4 sv = ld16(b + 192);
-        float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short*>(v.aux) + block));
+        float d = half_bits_to_float(r.d);
         uint32_t sw0 = n == 0 ? sv.x : sv.z, sw1 = n == 0 ? sv.y : sv.w;  // scale bytes 8n .. 8n+7
         float a[4];
 #pragma unroll

@@ -28,10 +28,6 @@ namespace jq {
 // 4 accumulator ready) since the status was last cleared.
 static __device__ int g_prefill_status;
 
-__host__ __device__ constexpr int plane_q_bytes_dev(int type) {
-    return type == JQ_TYPE_Q8_0 ? 32 : 16;  // Q8_0, Q4_0, Q4_1 quant planes
-}
-
 namespace {
 
 constexpr int TILE_F = 128;    // output features per CTA (MMA M)
@@ -104,80 +100,134 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         : "memory");
 }
 
-// Pulls the bytes that dequant_row_chunk will read for [k0, k0 + 64) of `row` towards the SM ahead of time.
-template <int TYPE>
-__device__ __forceinline__ void prefetch_row_chunk(const View& v, int64_t row, int k0) {
-    using F = Fmt<TYPE>;
-    const int blocks_per_row = (int)(v.k / F::QK);
-    const int64_t block = row * blocks_per_row + k0 / F::QK;
-    const int o = k0 % F::QK;
-    const uint8_t* p;
-    if (TYPE == JQ_TYPE_Q4_K) {
-        p = v.q + block * 144 + 16 + (o >> 6) * 32;
-    } else if (TYPE == JQ_TYPE_Q5_K) {
-        p = v.q + block * 176 + 48 + (o >> 6) * 32;
-    } else if (TYPE == JQ_TYPE_Q6_K) {
-        p = v.q + block * 208 + (o >> 7) * 64;
-        asm volatile("prefetch.global.L1 [%0];" ::"l"(p + 128 + (o >> 7) * 32 - (o >> 7) * 64));
-    } else {
-        p = v.q + block * plane_q_bytes_dev(TYPE);
-    }
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
-}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// The 64 weights k0 .. k0 + 63 of one row, decoded bit-exactly (jq_formats.cuh) and rounded to bfloat16, written as
-// one 128-byte row of the swizzled A tile: 16-byte chunk c lands at position c ^ (row & 7).
+// A dequantiser thread's share of the 64 weights k0 .. k0 + 63 of its row: TASKS (block, unit) pairs of the format's
+// decoder. `part` (0 or 1) says which half of the chunk's units the thread takes.
 template <int TYPE>
-__device__ __forceinline__ void dequant_row_chunk(const View& v, int64_t row, int k0, uint8_t* a_row, int swz, int part) {
-    // `part` (0 or 1) selects this thread's half of the units that cover the chunk
+struct ChunkTasks {
     using F = Fmt<TYPE>;
-    const int blocks_per_row = (int)(v.k / F::QK);
-    // units whose runs cover [k0, k0 + 64)
-    constexpr int SPAN_BLOCKS = F::QK >= 64 ? 1 : 64 / F::QK;
+    static constexpr int TASKS = TYPE == JQ_TYPE_Q8_0 ? 2 : 1;
+    __device__ static void of(const View& v, int64_t row, int k0, int part, int64_t (&block)[TASKS], int (&unit)[TASKS], int (&base)[TASKS]) {
+        const int blocks_per_row = (int)(v.k / F::QK);
+        if (TYPE == JQ_TYPE_Q4_K || TYPE == JQ_TYPE_Q5_K) {
+            block[0] = row * blocks_per_row + k0 / 256;
+            unit[0] = 2 * ((k0 & 255) >> 6) + part;  // group j = chunk index inside the block, units 2j and 2j + 1
+            base[0] = k0 & ~255;
+        } else if (TYPE == JQ_TYPE_Q6_K) {
+            block[0] = row * blocks_per_row + k0 / 256;
+            unit[0] = 2 * ((k0 & 255) >> 7) + part;  // half n of the block, units 2n and 2n + 1 (two of their four runs are used)
+            base[0] = k0 & ~255;
+        } else if (TYPE == JQ_TYPE_Q8_0) {
 #pragma unroll
-    for (int bb = 0; bb < SPAN_BLOCKS; bb++) {
-        const int kb = k0 + bb * F::QK;  // start of this block's part
-        const int64_t block = row * blocks_per_row + kb / F::QK;
-        const int base = (kb / F::QK) * F::QK;  // first k of the block
+            for (int i = 0; i < TASKS; i++) {        // two blocks of 32 per chunk, unit `part` (16 values) of each
+                block[i] = row * blocks_per_row + k0 / 32 + i;
+                unit[i] = part;
+                base[i] = k0 + 32 * i;
+            }
+        } else {                                     // Q4_0, Q4_1: one unit per block of 32, block `part` of the chunk
+            block[0] = row * blocks_per_row + k0 / 32 + part;
+            unit[0] = 0;
+            base[0] = k0 + 32 * part;
+        }
+    }
+};
+
+// Rounds a run of 16 consecutive weights to bfloat16 and writes it into a 128-byte row of the swizzled A tile:
+// the run starts at 16-byte chunk c, and chunk c lands at position c ^ (row & 7).
+__device__ __forceinline__ void store_run(const float (&w)[16], int c, uint8_t* a_row, int swz) {
+    uint4 lo, hi;
+    __nv_bfloat162 t;
+    t = __floats2bfloat162_rn(w[0], w[1]);   lo.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[2], w[3]);   lo.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[4], w[5]);   lo.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[6], w[7]);   lo.w = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[8], w[9]);   hi.x = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[10], w[11]); hi.y = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[12], w[13]); hi.z = *reinterpret_cast<uint32_t*>(&t);
+    t = __floats2bfloat162_rn(w[14], w[15]); hi.w = *reinterpret_cast<uint32_t*>(&t);
+    *reinterpret_cast<uint4*>(a_row + ((c ^ swz) << 4)) = lo;
+    *reinterpret_cast<uint4*>(a_row + (((c + 1) ^ swz) << 4)) = hi;
+}
+
+// Byte i of `packed` as the float 2^23 + byte: one byte permute builds the bit pattern 0x4B0000bb. The integer to
+// float conversion instruction runs at a quarter of the rate of the floating-point pipe, this does not.
+__device__ __forceinline__ float magic_byte(uint32_t packed, int i) {
+    return __uint_as_float(__byte_perm(packed, 0x4B000000u, 0x7440u + (uint32_t)i));
+}
+constexpr float MAGIC = 8388608.0f;  // 2^23
+
+// Converts loaded raw units, rounds to bfloat16 and writes them into the 128-byte row `a_row` of the swizzled A tile.
+// Q4_K and Q6_K take a route without integer to float conversions that gives the reference's values
+// (GgufKernels.java:101-111, 127-140) bit for bit, except that a zero may come out as +0 where the reference has -0,
+// which no product or sum can tell apart:
+//   Q4_K  (d sc) q - dmin m:  fma(a, 2^23 + q, -(a 2^23)) rounds the exact product a q once, as the reference's multiply
+//                             does (a 2^23 is exact), then the separately rounded subtraction follows;
+//   Q6_K  (d sc) (q - 32):    (2^23 + q) - (2^23 + 32) is exact, then the same single multiply as the reference.
+// The other formats go through the bit-exact decoder of jq_formats.cuh.
+template <int TYPE>
+__device__ __forceinline__ void convert_store(const typename Fmt<TYPE>::Raw (&raw)[ChunkTasks<TYPE>::TASKS], const int (&unit)[ChunkTasks<TYPE>::TASKS],
+                                              const int (&base)[ChunkTasks<TYPE>::TASKS], int k0, uint8_t* a_row, int swz) {
+    using F = Fmt<TYPE>;
+    if constexpr (TYPE == JQ_TYPE_Q4_K) {
+        const uint4 h = raw[0].h, q = raw[0].q;
+        const int j = unit[0] >> 1, hf = unit[0] & 1;
+        const float d = half_bits_to_float(h.x), dmin = half_bits_to_float(h.x >> 16);
+        int sc0, mn0, sc1, mn1;
+        k_scale_min(h.y, h.z, h.w, 2 * j, sc0, mn0);
+        k_scale_min(h.y, h.z, h.w, 2 * j + 1, sc1, mn1);
+        const float a0 = __fmul_rn(d, (float)sc0), m0 = __fmul_rn(dmin, (float)mn0);
+        const float a1 = __fmul_rn(d, (float)sc1), m1 = __fmul_rn(dmin, (float)mn1);
+        const float c0 = -__fmul_rn(a0, MAGIC), c1 = -__fmul_rn(a1, MAGIC);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        float lo[16], hi[16];
 #pragma unroll
-        for (int u = 0; u < F::UNITS; u++) {
-            // skip units entirely outside the chunk (compile-time layouts: see Fmt<>::decode positions)
-            bool any = false;
-            if (TYPE == JQ_TYPE_Q4_K || TYPE == JQ_TYPE_Q5_K) {
-                any = (u >> 1) == ((k0 - base) >> 6) && (u & 1) == part;
-            } else if (TYPE == JQ_TYPE_Q6_K) {
-                any = (u >> 1) == ((k0 - base) >> 7) && (u & 1) == part;
-            } else if (TYPE == JQ_TYPE_Q8_0) {
-                any = u == part;   // two units of 16 per block, two blocks per chunk
-            } else {
-                any = bb == part;  // Q4_0, Q4_1: one unit per block, two blocks per chunk
+        for (int x = 0; x < 4; x++) {
+            const uint32_t ln = w[x] & 0x0f0f0f0fu, hn = (w[x] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                lo[4 * x + i] = __fsub_rn(__fmaf_rn(a0, magic_byte(ln, i), c0), m0);
+                hi[4 * x + i] = __fsub_rn(__fmaf_rn(a1, magic_byte(hn, i), c1), m1);
             }
-            if (!any) {
-                continue;
+        }
+        store_run(lo, 2 * hf, a_row, swz);      // elements 16 hf .. of sub-block 2j
+        store_run(hi, 4 + 2 * hf, a_row, swz);  // and of sub-block 2j + 1
+    } else if constexpr (TYPE == JQ_TYPE_Q6_K) {
+        // unit (n, c) holds four runs; this 64-wide chunk is pair p of half n: runs 2p and 2p + 1
+        const int c = unit[0] & 1, p = (k0 & 127) >> 6;
+        const uint4 la = raw[0].la, lb = raw[0].lb, hq = raw[0].hq, sv = raw[0].sv;
+        const float d = half_bits_to_float(raw[0].d);
+        const uint32_t sw = (unit[0] >> 1) == 0 ? (p == 0 ? sv.x : sv.y) : (p == 0 ? sv.z : sv.w);  // scales 8n + 4p .. + 3
+        const float a0 = __fmul_rn(d, (float)(int)(int8_t)byte_of(sw, c));
+        const float a1 = __fmul_rn(d, (float)(int)(int8_t)byte_of(sw, c + 2));
+        const uint32_t wa[4] = {la.x, la.y, la.z, la.w}, wb[4] = {lb.x, lb.y, lb.z, lb.w}, wh[4] = {hq.x, hq.y, hq.z, hq.w};
+        float r0[16], r1[16];
+#pragma unroll
+        for (int x = 0; x < 4; x++) {
+            const uint32_t hx = wh[x] >> (4 * p);
+            const uint32_t qa = ((wa[x] >> (4 * p)) & 0x0f0f0f0fu) | ((hx & 0x03030303u) << 4);
+            const uint32_t qb = ((wb[x] >> (4 * p)) & 0x0f0f0f0fu) | ((hx & 0x0c0c0c0cu) << 2);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                r0[4 * x + i] = __fmul_rn(a0, __fsub_rn(magic_byte(qa, i), MAGIC + 32.0f));
+                r1[4 * x + i] = __fmul_rn(a1, __fsub_rn(magic_byte(qb, i), MAGIC + 32.0f));
             }
+        }
+        store_run(r0, 2 * c, a_row, swz);
+        store_run(r1, 4 + 2 * c, a_row, swz);
+    } else {
+#pragma unroll
+        for (int i = 0; i < ChunkTasks<TYPE>::TASKS; i++) {
             float w[F::RUNS][16];
             int pos[F::RUNS];
-            F::decode(v, block, u, w, pos);
+            F::convert(raw[i], unit[i], w, pos);
 #pragma unroll
             for (int r = 0; r < F::RUNS; r++) {
-                const int rel = base + pos[r] - k0;  // position of the run inside the chunk
+                const int rel = base[i] + pos[r] - k0;  // position of the run inside the chunk
                 if (rel >= 0 && rel < STAGE_K) {
-                    const int c = rel >> 3;  // 16-byte chunk index (two per run)
-                    uint4 lo, hi;
-                    __nv_bfloat162 t;
-                    t = __floats2bfloat162_rn(w[r][0], w[r][1]);   lo.x = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][2], w[r][3]);   lo.y = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][4], w[r][5]);   lo.z = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][6], w[r][7]);   lo.w = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][8], w[r][9]);   hi.x = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][10], w[r][11]); hi.y = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][12], w[r][13]); hi.z = *reinterpret_cast<uint32_t*>(&t);
-                    t = __floats2bfloat162_rn(w[r][14], w[r][15]); hi.w = *reinterpret_cast<uint32_t*>(&t);
-                    *reinterpret_cast<uint4*>(a_row + ((c ^ swz) << 4)) = lo;
-                    *reinterpret_cast<uint4*>(a_row + (((c + 1) ^ swz) << 4)) = hi;
+                    store_run(w[r], rel >> 3, a_row, swz);
                 }
             }
         }
@@ -273,19 +323,43 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, con
         row = row < v.n ? row : v.n - 1;
         const uint32_t row_off = (uint32_t)((i >> 3) * 1024 + (i & 7) * 128);
         bool ok = true;
+        // the raw blocks of the next stage are requested before the current stage is converted
+        using CT = ChunkTasks<TYPE>;
+        typename Fmt<TYPE>::Raw cur[CT::TASKS], nxt[CT::TASKS];
+        int64_t blk[CT::TASKS];
+        int unit[CT::TASKS], base[CT::TASKS], unit_n[CT::TASKS], base_n[CT::TASKS];
+        CT::of(v, row, 0, part, blk, unit, base);
+#pragma unroll
+        for (int q = 0; q < CT::TASKS; q++) {
+            Fmt<TYPE>::load(v, blk[q], unit[q], cur[q]);
+        }
         for (int it = 0; it < KT; it++) {
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+            if (it + 1 < KT) {
+                CT::of(v, row, (it + 1) * STAGE_K, part, blk, unit_n, base_n);
+                if (TYPE == JQ_TYPE_Q6_K && ((it + 1) & 1)) {
+                    nxt[0] = cur[0];  // the second 64 weights of a half come from the unit that is already loaded
+                } else {
+#pragma unroll
+                    for (int q = 0; q < CT::TASKS; q++) {
+                        Fmt<TYPE>::load(v, blk[q], unit_n[q], nxt[q]);
+                    }
+                }
+            }
             if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, 1)) {
                 ok = false;
                 break;
             }
-            if (it + 2 < KT) {
-                prefetch_row_chunk<TYPE>(v, row, (it + 2) * STAGE_K);
-            }
-            dequant_row_chunk<TYPE>(v, row, it * STAGE_K, a_tiles + s * A_BYTES + row_off, i & 7, part);
+            convert_store<TYPE>(cur, unit, base, it * STAGE_K, a_tiles + s * A_BYTES + row_off, i & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             mbar_arrive(full_a(s));
+#pragma unroll
+            for (int q = 0; q < CT::TASKS; q++) {
+                cur[q] = nxt[q];
+                unit[q] = unit_n[q];
+                base[q] = base_n[q];
+            }
         }
         // ---- epilogue: accumulator -> y --------------------------------------------------------------------------------
         if (ok && mbar_wait(accum, 0, abort_flag, 4)) {
