@@ -4,26 +4,31 @@
 // "activation image" in a scratch buffer: per 256-element super-block of k and per row of x, the values
 // are scaled by a power of two s (from the block's largest magnitude), rounded to 22-bit fixed point,
 // X = rint(x / s * 2^21), and split into three signed base-256 digits X = d2 * 65536 + d1 * 256 + d0.
-// The digits are laid out as B fragments of mma.sync.m16n8k32 (u8 x s8 -> s32): column 3m + i holds digit
-// i of activation row m. The GEMV kernel widens four nibbles to four bytes with one AND (one more shift for
-// the high nibbles) and feeds them as the A operand, so one MMA multiplies one 32-element sub-block of 16
-// weight rows with every digit column exactly. Sub-block results are combined with the 6-bit scales in
-// integer arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to float once per
-// super-block and scaled by fp16 d and the column weight s * 2^(8i - 21). The "min" part of Q4_K,
-// dmin * sum_sub m_sub * sum(x over the sub-block), uses one m16n8k16 MMA whose A operand is the eight
-// packed 6-bit mins and whose B operand holds the digit sums of every sub-block. Everything up to the
-// per-super-block float conversion is exact and x keeps 22 bits relative to the largest magnitude of its
-// super-block, so results match an FP32-accumulating kernel. The summation order depends on k only: a row
-// shard of a weight gives bitwise the same outputs as the whole weight.
+// The digits are laid out as B fragments of mma.sync.m16n8k32 (u8 x s8 -> s32), one column per (row of x, digit);
+// the fragments of two sub-blocks sit side by side, so one 16-byte load feeds two MMAs. The GEMV kernel widens four
+// nibbles to four bytes with one AND and feeds them as the A operand, so one MMA multiplies one 32-element sub-block
+// of 16 weight rows with every digit column exactly. Sub-block results are combined with the 6-bit scales in integer
+// arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to float once per super-block and scaled
+// by fp16 d and the column weight s * 2^(8i - 21). The "min" part of Q4_K, dmin * sum_sub m_sub * sum(x over the
+// sub-block), uses one m16n8k16 MMA whose A operand is the eight packed 6-bit mins and whose B operand holds the
+// digit sums of every sub-block. Everything up to the per-super-block float conversion is exact and x keeps 22 bits
+// relative to the largest magnitude of its super-block, so results match an FP32-accumulating kernel. The summation
+// order depends on k and the number of rows of x only: a row shard of a weight gives bitwise the same outputs as the
+// whole weight.
 //
-// Work split: a CTA of 8 warps owns 16 output rows at a time (tiles blockIdx.x, blockIdx.x + gridDim.x,
-// ...), warp p takes super-blocks b = p (mod 8). Weights stream HBM -> shared memory through a per-warp
-// ring of cp.async slots; consecutive lanes copy consecutive 16-byte chunks, so every 32-byte sector is
-// requested once, and the slot layout is swizzled so that the 8-byte fragment reads are conflict free.
-// The weight buffer is padded by 16 rows, which lets the last tile read past n without a bounds check.
-// The GEMV kernel is launched with programmatic stream serialization: it requests its first weights while
-// the activation kernel is still running and waits for it (griddepcontrol.wait) only before copying the
-// image into shared memory.
+// Two column layouts (struct Cfg). One or two rows of x: column 3m + i of a single group; the three digit columns of
+// a row sit in different lanes and are combined by shuffles once per tile; the high nibbles are masked in place
+// (no shift) and their 16-fold products summed apart. Three to eight rows: digit i is column group i and row m its
+// column m, which puts all digits of rows 2t and 2t + 1 into lane t: no exchange between lanes at all.
+//
+// Work split: a CTA of 8 warps (16 for three to eight rows of x, where one CTA per SM shares one copy of the large
+// image) owns 16 output rows at a time (tiles blockIdx.x, blockIdx.x + gridDim.x, ...), warp p takes super-blocks
+// b = p (mod warps). Weights stream HBM -> shared memory through a per-warp ring of cp.async slots; consecutive lanes
+// copy consecutive 16-byte chunks, so every 32-byte sector is requested once, and the slot layout is swizzled so that
+// the 8-byte fragment reads are conflict free. The weight buffer is padded by 16 rows, which lets the last tile read
+// past n without a bounds check. The GEMV kernel is launched with programmatic stream serialization: it requests its
+// first weights while the activation kernel is still running and waits for it (griddepcontrol.wait) only before
+// copying the image into shared memory.
 #include <mutex>
 
 #include "jq_formats.cuh"
@@ -32,14 +37,23 @@ namespace jq {
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
 constexpr int SLOT_BYTES = 16 * 144;        // one super-block of 16 rows: 16 x 128 bytes of nibbles, then 16 headers
 constexpr int SLOT_HEADERS = 16 * 128;
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// The same copy under a predicate, without a branch around it.
+__device__ __forceinline__ void cp_async16_if(uint32_t dst_smem, const void* src, int on) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %2, 0;\n"
+        "@p cp.async.cg.shared.global [%0], [%1], 16;\n"
+        "}\n" ::"r"(dst_smem),
+        "l"(src), "r"(on)
+        : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -67,50 +81,53 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
+// Column layouts of the activation image. Up to two activation rows are "packed": one MMA column group holds column
+// 3m + i for digit i of row m. More rows are "digit major": group i holds digit i, column m of it row m, so that a
+// lane's accumulator columns 2t and 2t + 1 are all three digits of rows 2t and 2t + 1 and need no exchange with
+// other lanes.
 template <int MT>
 struct Cfg {
-    static constexpr int COLS = 3 * MT;               // digit columns: column 3m + i is digit i of activation row m
-    static constexpr int NG = (COLS + 7) / 8;         // MMA column groups for the quants
-    static constexpr int NCOL = NG == 1 ? COLS : 8;   // columns stored per group
-    static constexpr int MCOLS = 2 * COLS;            // mins: column 2c + p is part p (low 7 bits / rest) of the sums of digit column c
-    static constexpr int NGM = (MCOLS + 7) / 8;
-    static constexpr int NCOLM = NGM == 1 ? MCOLS : 8;
+    static constexpr bool DIGIT_MAJOR = MT > 2;
+    static constexpr int COLS = 3 * MT;
+    static constexpr int NG = DIGIT_MAJOR ? 3 : 1;                         // MMA column groups for the quants
+    static constexpr int NCOL = DIGIT_MAJOR ? 8 : COLS;                    // columns stored per group
+    // mins: two columns (low 7 bits / rest of the digit sums) per digit column. Packed: column 2 (3m + i) + part.
+    // Digit major: group 2i + (m & 1), column 2 (m / 2) + part, which hands lane t the rows 2t and 2t + 1 again.
+    static constexpr int NGM = DIGIT_MAJOR ? 6 : (2 * COLS + 7) / 8;
+    static constexpr int NCOLM = NGM == 1 ? 2 * COLS : 8;
     // bytes of activation image per super-block: digit fragments, digit-sum fragments, column weights
     static constexpr size_t XD = (size_t)8 * NG * NCOL * 4 * 8;   // 8 sub-blocks x groups x columns x 4 lanes x 8 bytes
-    static constexpr size_t XM = (size_t)NGM * NCOLM * 2 * 4;     // groups x columns x 2 lanes x 4 bytes
-    static constexpr size_t TAB = (size_t)NG * 8 * 4;             // one float per digit column
+    static constexpr size_t XM = (size_t)NGM * NCOLM * 4 * 4;     // groups x columns x 4 lanes x 4 bytes (lanes 2, 3: zero)
+    // one float per digit column: its weight s 2^(8 i - 21); packed layouts add a second table with the weights / 16
+    static constexpr size_t TAB = (size_t)NG * 8 * 4 * (DIGIT_MAJOR ? 1 : 2);
     static constexpr size_t PB = XD + XM + TAB;
+    static_assert(PB % 16 == 0, "the image is copied in 16-byte pieces");
+    __host__ __device__ static constexpr int qcol(int m, int i) { return DIGIT_MAJOR ? 8 * i + m : 3 * m + i; }
+    __host__ __device__ static constexpr int mcol(int m, int i, int part) {
+        return DIGIT_MAJOR ? 8 * (2 * i + (m & 1)) + 2 * (m >> 1) + part : 2 * (3 * m + i) + part;
+    }
 };
 
-// ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
-// One warp per (super-block of k, activation row); lane = octet: sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of
-// that sub-block's MMA. The kernel is tiny and latency bound, so the work is spread over as many warps as possible.
-constexpr int PREP_WARPS = 4;
-
+// ---- activations -> image ---------------------------------------------------------------------------------------
+// One warp turns one (super-block of k, row of x) into its part of the image at `img` (global or shared memory);
+// lane = octet: sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of that sub-block's MMA. Digit fragments are stored
+// per pair of sub-blocks, so that the GEMV reads the B operands of two MMAs with one 16-byte load.
 template <int MT>
-__global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
-                                                                             uint8_t* __restrict__ image) {
+__device__ __forceinline__ void build_image(const float* __restrict__ x, int rows, int64_t k, int b, int m, uint8_t* img, int lane) {
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NCOLM = C::NCOLM;
-    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
-    const int lane = threadIdx.x & 31;
-    const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
-    const int b = pair / MT, m = pair % MT;
-    if (b >= (int)(k >> 8)) {
-        return;
-    }
     const int sub = lane >> 2, tt = lane & 3;
-    uint8_t* img = image + (size_t)b * C::PB;
     uint2* xd = reinterpret_cast<uint2*>(img);
     uint8_t* xm = img + C::XD;
     float* tab = reinterpret_cast<float*>(img + C::XD + C::XM);
-    if (m == 0 && lane >= C::COLS && lane < NG * 8) {
+    if (!C::DIGIT_MAJOR && m == 0 && lane >= C::COLS && lane < NG * 8) {
         tab[lane] = 0.0f;  // columns that hold no activation row
+        tab[NG * 8 + lane] = 0.0f;
     }
     float xv[8];
     if (m < rows) {
         const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
-        const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
+        const float4 lo = xp[0], hi = xp[1];
         xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
         xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
     } else {
@@ -130,7 +147,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
     }
     // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
     uint32_t e = __float_as_uint(am) & 0x7f800000u;
-    e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
+    e = e < 0x0d000000u ? 0x0d000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-25 normal
     // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
     const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
     int X[8];
@@ -153,102 +170,125 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
                 w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
             }
         }
-        const int col = 3 * m + dgt;
-        xd[(((size_t)sub * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt] = make_uint2(w0, w1);
-        // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte;
-        // byte (sub % 4) of the word of lane slot sub / 4, in mins column 2 col + part
+        const int col = C::qcol(m, dgt);
+        xd[((((size_t)(sub >> 1) * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt) * 2 + (sub & 1)] = make_uint2(w0, w1);
+        // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte.
+        // The mins MMA has k = 16 and eight mins: lane slot sub / 4 holds the sums of sub-blocks 4 (sub / 4) .. + 3 as bytes,
+        // lane slots 2 and 3 (k = 8 .. 15) are zero.
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (tt == 0) {
+        if (tt < 2) {
             const int lo7 = sum & 127, hi = (sum - lo7) >> 7;
 #pragma unroll
             for (int p = 0; p < 2; p++) {
-                const int mc = 2 * col + p;
-                xm[(((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 2 + (sub >> 2)) * 4 + (sub & 3)] = (uint8_t)(p == 0 ? lo7 : hi);
+                const int mc = C::mcol(m, dgt, p);
+                uint8_t* cell = xm + ((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 16;
+                cell[(tt == 0 ? (sub >> 2) : 2 + (sub >> 2)) * 4 + (sub & 3)] = tt == 0 ? (uint8_t)(p == 0 ? lo7 : hi) : (uint8_t)0;
             }
         }
         if (lane == 0) {
             tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
+            if (!C::DIGIT_MAJOR) {
+                tab[NG * 8 + col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (25u << 23)) : 0.0f;  // ... / 16
+            }
         }
     }
 }
 
+// The image in a scratch buffer in global memory, for the GEMV shapes that do not build it themselves. The kernel is
+// tiny and latency bound, so the work is spread over as many warps as possible.
+constexpr int PREP_WARPS = 4;
+
+template <int MT>
+__global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
+                                                                             uint8_t* __restrict__ image) {
+    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    const int b = pair / MT, m = pair % MT;
+    if (b < (int)(k >> 8)) {
+        build_image<MT>(x, rows, k, b, m, image + (size_t)b * Cfg<MT>::PB, threadIdx.x & 31);
+    }
+}
+
 // ---- the GEMV ---------------------------------------------------------------------------------------------------
-template <int MT, int STAGES, int OCC>
-__global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
+template <int MT, int STAGES, int NW, int OCC>
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
                                                                   int KS, int max_tiles) {
     // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
     // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
+    constexpr int THREADS = NW * 32;
+    constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
     const int KB = (int)(v.k >> 8);
     const int nslices = (KB + KS - 1) / KS;
     uint8_t* img = smem_raw;                                                         // [KS][PB]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][WARPS][16][MT]
-    float* carry = red + 2 * WARPS * 16 * MT;                                        // [max_tiles][16][MT], only if nslices > 1
-    uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) +
-                    (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][NW][16][MT]
+    float* carry = red + 2 * NW * 16 * MT;                                           // [max_tiles][16][MT], only if nslices > 1
+    uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) + (size_t)warp * RING_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
     const int64_t n = v.n;
     const int64_t row_bytes = (int64_t)KB * 144;
 
     // ---- weight stream: chunk c = lane + 32 i of the 144 chunks (16 rows x 9) of a super-block -------------
     // Slot layout: row r's 128 bytes of nibbles at r * 128 with its four 32-byte segments permuted by r & 3
     // (segment p sits at position p ^ (r & 3)), the 16 headers behind them.
-    uint32_t src_off[5], dst_off[5];
+    uint32_t src_d[5], dst_off[5];  // source offsets relative to the lane's first chunk
+    uint32_t src0 = 0;
 #pragma unroll
     for (int i = 0; i < 5; i++) {
         const int c = lane + 32 * i, r = c / 9, ch = c % 9;
-        src_off[i] = (uint32_t)(r * (int)row_bytes + ch * 16);
+        const uint32_t so = (uint32_t)(r * (int)row_bytes + ch * 16);
+        if (i == 0) {
+            src0 = so;
+        }
+        src_d[i] = so - src0;
         dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
                              : (uint32_t)(r * 128 + ((((ch - 1) >> 1) ^ (r & 3)) << 5) + ((ch - 1) & 1) * 16);
     }
-    // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + 8 i.
-    auto blocks_of = [&](int sl) {  // number of super-blocks this warp has in slice sl
-        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
-        return warp < len ? (len - warp + WARPS - 1) / WARPS : 0;
-    };
+    const int low16 = lane < 16;
+    // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + NW i.
+    const int len_last = KB - (nslices - 1) * KS;
+    const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + NW - 1) / NW : 0) : 0;
+    const int nb_last = warp < len_last ? (len_last - warp + NW - 1) / NW : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    int steps = 0;
-    for (int sl = 0; sl < nslices; sl++) {
-        steps += blocks_of(sl) * my_tiles;
-    }
-    int iss_sl = 0, iss_ti = 0, iss_j = 0;
-    while (iss_sl < nslices && blocks_of(iss_sl) == 0) {
-        iss_sl++;
-    }
-    auto issue = [&](int s) {
-        if (s < steps) {
-            const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
-            const uint8_t* base = v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)(iss_sl * KS + warp + WARPS * iss_j) * 144u;
-            const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
+    const uint8_t* const gp0 = v.q + (int64_t)blockIdx.x * 16 * row_bytes + (uint32_t)warp * 144u + src0;  // first tile, first block
+    const int64_t tile_stride = (int64_t)gridDim.x * 16 * row_bytes;
+    const uint8_t* gp = gp0;
+    int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
+    int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
+    uint32_t iss_slot = 0;
+    auto issue = [&]() {
+        if (iss_left > 0) {
+            iss_left--;
+            const uint32_t slot = ring_s + iss_slot;
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                cp_async16(slot + dst_off[i], base + src_off[i]);
+                cp_async16(slot + dst_off[i], gp + src_d[i]);
             }
-            if (lane < 16) {
-                cp_async16(slot + dst_off[4], base + src_off[4]);
-            }
-            if (++iss_j == blocks_of(iss_sl)) {
+            cp_async16_if(slot + dst_off[4], gp + src_d[4], low16);
+            gp += NW * 144;
+            if (++iss_j == iss_nb) {
                 iss_j = 0;
+                gp += tile_stride - (int64_t)iss_nb * (NW * 144);
                 if (++iss_ti == my_tiles) {
                     iss_ti = 0;
-                    do {
-                        iss_sl++;
-                    } while (iss_sl < nslices && blocks_of(iss_sl) == 0);
+                    iss_sl++;
+                    iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
+                    gp = gp0 + (int64_t)iss_sl * KS * 144;
                 }
             }
         }
+        iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
         cp_async_commit();
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        issue(s);  // the first weights are on their way before the activation image is complete
+        issue();  // the first weights are on their way before the activation image is complete
     }
 
     // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
@@ -257,26 +297,29 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
 
     // ---- main loop ----------------------------------------------------------------------------------------------
     // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
-    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 8;
-    const uint8_t* xm_lane = img + C::XD + ((size_t)(NCOLM == 8 ? g : g % NCOLM) * 2 + (t & 1)) * 4;
+    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 16;
+    const uint8_t* xm_lane = img + C::XD + ((size_t)(NCOLM == 8 ? g : g % NCOLM) * 4 + t) * 4;
     const uint8_t* tab_lane = img + C::XD + C::XM;
     uint32_t qoff[4];  // this lane's 8 bytes of group j inside a row of the slot
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         qoff[j] = (uint32_t)(((j ^ (g & 3)) << 5) + 8 * t);
     }
-    float acc[NG][2][2];   // [group][row g / g + 8][column 2t / 2t + 1]
-    float accm[NGM][2];    // mins, [group][row]
+    const bool mins_low = (t & 1) == 0;  // lanes t = 0, 2 feed mins 0..3, lanes 1, 3 mins 4..7 (slots 2, 3 meet zeros)
+    // Packed: acc[group][row g / g + 8][column 2t / 2t + 1] and accm[mins group][row]. Digit major: acc[0][row][row of x].
+    constexpr int NACC = C::DIGIT_MAJOR ? 1 : NG, NACCM = C::DIGIT_MAJOR ? 1 : NGM;
+    float acc[NACC][2][2];
+    float accm[NACCM][2];
 #pragma unroll
-    for (int i = 0; i < NG; i++) {
+    for (int i = 0; i < NACC; i++) {
         acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
     }
 #pragma unroll
-    for (int i = 0; i < NGM; i++) {
+    for (int i = 0; i < NACCM; i++) {
         accm[i][0] = accm[i][1] = 0.0f;
     }
 
-    auto compute = [&](const uint8_t* slot, int b) {  // b = super-block index inside the resident slice
+    auto compute = [&](const uint8_t* slot, const uint8_t* blk) {  // blk = this lane's view of the super-block's image
         const uint8_t* q0 = slot + g * 128;
         const uint8_t* q1 = q0 + 8 * 128;
         const uint4 h0 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + g * 16);
@@ -284,83 +327,105 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         // 6-bit scales and mins of the 8 sub-blocks as packed bytes: [0..3] and [4..7]
         const uint32_t sc0a = h0.y & 0x3f3f3f3fu, sc0b = and_or(h0.y >> 2, 0x30303030u, h0.w & 0x0f0f0f0fu);
         const uint32_t sc1a = h1.y & 0x3f3f3f3fu, sc1b = and_or(h1.y >> 2, 0x30303030u, h1.w & 0x0f0f0f0fu);
-        const uint32_t mn0 = t == 0 ? (h0.z & 0x3f3f3f3fu) : (t == 1 ? and_or(h0.z >> 2, 0x30303030u, (h0.w >> 4) & 0x0f0f0f0fu) : 0u);
-        const uint32_t mn1 = t == 0 ? (h1.z & 0x3f3f3f3fu) : (t == 1 ? and_or(h1.z >> 2, 0x30303030u, (h1.w >> 4) & 0x0f0f0f0fu) : 0u);
-        int I[NG][4];
+        const uint32_t mn0 = mins_low ? (h0.z & 0x3f3f3f3fu) : and_or(h0.z >> 2, 0x30303030u, (h0.w >> 4) & 0x0f0f0f0fu);
+        const uint32_t mn1 = mins_low ? (h1.z & 0x3f3f3f3fu) : and_or(h1.z >> 2, 0x30303030u, (h1.w >> 4) & 0x0f0f0f0fu);
+        // Packed layouts keep the high nibbles in place (one AND, no shift): the odd sub-blocks' products come out 16 times
+        // too large, are summed apart from the even ones' and meet them as 16 even + odd; the column weights carry the 1 / 16.
+        constexpr bool SPLIT = !C::DIGIT_MAJOR;
+        int I[NG][4], IO[SPLIT ? NG : 1][4];
 #pragma unroll
         for (int i = 0; i < NG; i++) {
             I[i][0] = I[i][1] = I[i][2] = I[i][3] = 0;
         }
-        const uint8_t* blk = xd_lane + (size_t)b * C::PB;
+#pragma unroll
+        for (int i = 0; i < (SPLIT ? NG : 1); i++) {
+            IO[i][0] = IO[i][1] = IO[i][2] = IO[i][3] = 0;
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             // this lane's 8 bytes of group j for rows g and g + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
             const uint2 wa = *reinterpret_cast<const uint2*>(q0 + qoff[j]);
             const uint2 wb = *reinterpret_cast<const uint2*>(q1 + qoff[j]);
+            uint4 bfp[NG];  // B operands of sub-blocks 2j (x, y) and 2j + 1 (z, w)
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                bfp[i] = *reinterpret_cast<const uint4*>(blk + (size_t)((j * NG + i) * NCOL) * 64);
+            }
 #pragma unroll
             for (int hf = 0; hf < 2; hf++) {
                 const int sub = 2 * j + hf;
-                const uint32_t a0 = (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
-                const uint32_t a2 = (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
-                const uint32_t a1 = (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
-                const uint32_t a3 = (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
+                const bool keep = SPLIT && hf == 1;  // high nibbles stay where they are
+                const uint32_t a0 = keep ? wa.x & 0xf0f0f0f0u : (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
+                const uint32_t a2 = keep ? wa.y & 0xf0f0f0f0u : (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
+                const uint32_t a1 = keep ? wb.x & 0xf0f0f0f0u : (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
+                const uint32_t a3 = keep ? wb.y & 0xf0f0f0f0u : (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
                 const int s0 = (int)__byte_perm(sub < 4 ? sc0a : sc0b, 0u, 0x4440u + (sub & 3));
                 const int s1 = (int)__byte_perm(sub < 4 ? sc1a : sc1b, 0u, 0x4440u + (sub & 3));
 #pragma unroll
                 for (int i = 0; i < NG; i++) {
-                    const uint2 bf = *reinterpret_cast<const uint2*>(blk + (size_t)((sub * NG + i) * NCOL) * 32);
                     int D[4];
-                    imma_k32(D, a0, a1, a2, a3, bf.x, bf.y);
-                    I[i][0] += s0 * D[0];
-                    I[i][1] += s0 * D[1];
-                    I[i][2] += s1 * D[2];
-                    I[i][3] += s1 * D[3];
+                    imma_k32(D, a0, a1, a2, a3, hf == 0 ? bfp[i].x : bfp[i].z, hf == 0 ? bfp[i].y : bfp[i].w);
+                    int(&S)[4] = keep ? IO[i] : I[i];
+                    S[0] += s0 * D[0];
+                    S[1] += s0 * D[1];
+                    S[2] += s1 * D[2];
+                    S[3] += s1 * D[3];
                 }
             }
         }
         const float d0 = half_bits_to_float(h0.x), d1 = half_bits_to_float(h1.x);
         const float dm0 = half_bits_to_float(h0.x >> 16), dm1 = half_bits_to_float(h1.x >> 16);
-        const uint8_t* tb = tab_lane + (size_t)b * C::PB;
+        const uint8_t* tb = blk + (tab_lane - xd_lane);
+        const uint8_t* fm = blk + (xm_lane - xd_lane);
+        if constexpr (C::DIGIT_MAJOR) {
+            float qf[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, mf[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};  // [row][row of x 2t + c]
 #pragma unroll
-        for (int i = 0; i < NG; i++) {
-            const float2 w = *reinterpret_cast<const float2*>(tb + (8 * i + 2 * t) * 4);  // weights of columns 2t, 2t+1
-            acc[i][0][0] = fmaf(d0 * w.x, (float)I[i][0], acc[i][0][0]);
-            acc[i][0][1] = fmaf(d0 * w.y, (float)I[i][1], acc[i][0][1]);
-            acc[i][1][0] = fmaf(d1 * w.x, (float)I[i][2], acc[i][1][0]);
-            acc[i][1][1] = fmaf(d1 * w.y, (float)I[i][3], acc[i][1][1]);
-        }
-        const uint8_t* fm = xm_lane + (size_t)b * C::PB;
+            for (int i = 0; i < 3; i++) {
+                const float2 w = *reinterpret_cast<const float2*>(tb + (8 * i + 2 * t) * 4);  // digit i of rows 2t, 2t + 1 of x
+                qf[0][0] = fmaf(w.x, (float)I[i][0], qf[0][0]);
+                qf[0][1] = fmaf(w.y, (float)I[i][1], qf[0][1]);
+                qf[1][0] = fmaf(w.x, (float)I[i][2], qf[1][0]);
+                qf[1][1] = fmaf(w.y, (float)I[i][3], qf[1][1]);
 #pragma unroll
-        for (int i = 0; i < NGM; i++) {
-            int E[4];
-            imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)i * NCOLM * 8));
-            const float w = *reinterpret_cast<const float*>(tb + (4 * i + t) * 4);  // weight of digit column 4i + t
-            accm[i][0] = fmaf(dm0 * w, (float)(E[1] * 128 + E[0]), accm[i][0]);
-            accm[i][1] = fmaf(dm1 * w, (float)(E[3] * 128 + E[2]), accm[i][1]);
+                for (int c = 0; c < 2; c++) {
+                    int E[4];
+                    imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)(2 * i + c) * NCOLM * 16));
+                    const float wc = c == 0 ? w.x : w.y;
+                    mf[0][c] = fmaf(wc, (float)(E[1] * 128 + E[0]), mf[0][c]);
+                    mf[1][c] = fmaf(wc, (float)(E[3] * 128 + E[2]), mf[1][c]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                acc[0][0][c] = fmaf(-dm0, mf[0][c], fmaf(d0, qf[0][c], acc[0][0][c]));
+                acc[0][1][c] = fmaf(-dm1, mf[1][c], fmaf(d1, qf[1][c], acc[0][1][c]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                const float2 w = *reinterpret_cast<const float2*>(tb + (NG * 8 + 8 * i + 2 * t) * 4);  // weights / 16 of columns 2t, 2t+1
+                acc[i][0][0] = fmaf(d0 * w.x, (float)(16 * I[i][0] + IO[i][0]), acc[i][0][0]);
+                acc[i][0][1] = fmaf(d0 * w.y, (float)(16 * I[i][1] + IO[i][1]), acc[i][0][1]);
+                acc[i][1][0] = fmaf(d1 * w.x, (float)(16 * I[i][2] + IO[i][2]), acc[i][1][0]);
+                acc[i][1][1] = fmaf(d1 * w.y, (float)(16 * I[i][3] + IO[i][3]), acc[i][1][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < NGM; i++) {
+                int E[4];
+                imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)i * NCOLM * 16));
+                const float w = *reinterpret_cast<const float*>(tb + (4 * i + t) * 4);  // weight of digit column 4i + t
+                accm[i][0] = fmaf(dm0 * w, (float)(E[1] * 128 + E[0]), accm[i][0]);
+                accm[i][1] = fmaf(dm1 * w, (float)(E[3] * 128 + E[2]), accm[i][1]);
+            }
         }
     };
 
-    // activation row each accumulator column of this lane belongs to (-1: none)
-    int mq[NG][2], mmn[NGM];
-#pragma unroll
-    for (int i = 0; i < NG; i++) {
-#pragma unroll
-        for (int c = 0; c < 2; c++) {
-            const int col = 8 * i + 2 * t + c;
-            mq[i][c] = col < C::COLS ? col / 3 : -1;
-        }
-    }
-#pragma unroll
-    for (int i = 0; i < NGM; i++) {
-        const int col = 4 * i + t;  // digit column whose two sum parts this lane holds
-        mmn[i] = col < C::COLS ? col / 3 : -1;
-    }
-
     int parity = 0;
-    int step = 0;
+    uint32_t cmp_slot = 0;
     for (int sl = 0; sl < nslices; sl++) {
         // ---- bring this slice of the activation image into shared memory ---------------------------------------------
-        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
+        const int len = sl == nslices - 1 ? len_last : KS;
+        const int nb = sl == nslices - 1 ? nb_last : nb_full;
         if (sl > 0) {
             __syncthreads();  // every warp is done with the previous slice
         }
@@ -376,61 +441,68 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q4k_i8_kernel(View v, const
         }
         for (int ti = 0; ti < my_tiles; ti++) {
             const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
-            for (int b = warp; b < len; b += WARPS) {
+            const uint8_t* blk = xd_lane + (size_t)warp * C::PB;
+            for (int j = 0; j < nb; j++) {
                 __syncwarp();                 // every lane is done reading the slot that is requested next
-                issue(step + STAGES - 1);
-                cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+                issue();
+                cp_async_wait<STAGES - 1>();  // this lane's copies of this step have landed
                 __syncwarp();                 // ... and so have the other lanes'
-                compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, b);
-                step++;
+                compute(ring + cmp_slot, blk);
+                cmp_slot = cmp_slot + SLOT_BYTES == RING_BYTES ? 0u : cmp_slot + SLOT_BYTES;
+                blk += (size_t)NW * C::PB;
             }
-            // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
-            float* rd = red + (size_t)parity * WARPS * 16 * MT;
+            // ---- this warp's partial sums per output row and row of x ---------------------------------------------------
+            float* rd = red + (size_t)parity * NW * 16 * MT;
+            if constexpr (C::DIGIT_MAJOR) {
+                // the lane holds rows g, g + 8 for rows 2t, 2t + 1 of x (MT = 8: two floats side by side)
+                *reinterpret_cast<float2*>(rd + (warp * 16 + g) * MT + 2 * t) = make_float2(acc[0][0][0], acc[0][0][1]);
+                *reinterpret_cast<float2*>(rd + (warp * 16 + g + 8) * MT + 2 * t) = make_float2(acc[0][1][0], acc[0][1][1]);
+                acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
+            } else {
+                // combine the digit columns of a row of x, which sit in the 4 lanes of a quad
 #pragma unroll
-            for (int m = 0; m < MT; m++) {
-                float p0 = 0.0f, p1 = 0.0f;
-#pragma unroll
-                for (int i = 0; i < NG; i++) {
+                for (int m = 0; m < MT; m++) {
+                    float p0 = 0.0f, p1 = 0.0f;
 #pragma unroll
                     for (int c = 0; c < 2; c++) {
-                        if (mq[i][c] == m) {
-                            p0 += acc[i][0][c];
-                            p1 += acc[i][1][c];
-                        }
+                        const int col = 2 * t + c;
+                        const bool mine = col < C::COLS && col / 3 == m;
+                        p0 += mine ? acc[0][0][c] : 0.0f;
+                        p1 += mine ? acc[0][1][c] : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < NGM; i++) {
+                        const int col = 4 * i + t;  // digit column whose two sum parts this lane holds
+                        const bool mine = col < C::COLS && col / 3 == m;
+                        p0 -= mine ? accm[i][0] : 0.0f;
+                        p1 -= mine ? accm[i][1] : 0.0f;
+                    }
+                    p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+                    p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+                    p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+                    p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+                    if (t == 0) {
+                        rd[(warp * 16 + g) * MT + m] = p0;
+                        rd[(warp * 16 + g + 8) * MT + m] = p1;
                     }
                 }
+                acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
 #pragma unroll
                 for (int i = 0; i < NGM; i++) {
-                    if (mmn[i] == m) {
-                        p0 -= accm[i][0];
-                        p1 -= accm[i][1];
-                    }
+                    accm[i][0] = accm[i][1] = 0.0f;
                 }
-                p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
-                p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
-                p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
-                p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
-                if (t == 0) {
-                    rd[(warp * 16 + g) * MT + m] = p0;
-                    rd[(warp * 16 + g + 8) * MT + m] = p1;
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < NG; i++) {
-                acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
-            }
-#pragma unroll
-            for (int i = 0; i < NGM; i++) {
-                accm[i][0] = accm[i][1] = 0.0f;
             }
             __syncthreads();
-            // ---- the 8 warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
+            // ---- the warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
             for (int o = tid; o < 16 * MT; o += THREADS) {
                 const int r = o / MT, m = o % MT;
                 const int64_t row = (int64_t)my_tile * 16 + r;
-                const float* p = rd + r * MT + m;
-                float sum = ((p[0] + p[16 * MT]) + (p[2 * 16 * MT] + p[3 * 16 * MT])) +
-                            ((p[4 * 16 * MT] + p[5 * 16 * MT]) + (p[6 * 16 * MT] + p[7 * 16 * MT]));
+                const float* p = rd + o;
+                constexpr int W = 16 * MT;  // floats per warp
+                float sum = ((p[0] + p[W]) + (p[2 * W] + p[3 * W])) + ((p[4 * W] + p[5 * W]) + (p[6 * W] + p[7 * W]));
+                if constexpr (NW == 16) {
+                    sum += ((p[8 * W] + p[9 * W]) + (p[10 * W] + p[11 * W])) + ((p[12 * W] + p[13 * W]) + (p[14 * W] + p[15 * W]));
+                }
                 if (sl > 0) {
                     sum += carry[(size_t)ti * 16 * MT + o];
                 }
@@ -458,76 +530,80 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT, int STAGES, int OCC>
+template <int MT, int STAGES, int NW, int OCC>
 int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while the activation kernel runs
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may request weights while the activation kernel runs
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
 }
 
 // Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
 template <int MT>
-size_t smem_bytes(int KS, int stages, bool sliced, int max_tiles) {
-    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
-           (size_t)WARPS * stages * SLOT_BYTES;
+size_t smem_bytes(int nw, int KS, int stages, bool sliced, int max_tiles) {
+    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * nw * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+           (size_t)nw * stages * SLOT_BYTES;
 }
+
+// A launch shape: warps per CTA, CTAs per SM, ring stages. KS (the slice length) is a function of MT and k only, so
+// that the summation order never depends on n: the whole k if its image fits beside the ring, else a multiple of the
+// warps per CTA.
+struct Shape {
+    int nw, occ, stages;
+};
 
 template <int MT>
 int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     const int KB = (int)(v.k / 256);
     const int tiles = (int)((v.n + 15) / 16);
-    // Candidate shapes, best first: (CTAs per SM, ring stages). The slice length KS is a function of MT and k only (so
-    // that the summation order never depends on n): the whole k if its image fits beside the ring, else a multiple of 8.
-    const int occ_of[3] = {3, 2, 2}, st_of[3] = {3, 4, 3};
-    const size_t red_bytes = (size_t)(2 * WARPS * 16 * MT) * sizeof(float);
-    const size_t fixed = red_bytes + 8 * 1024;  // sliced shapes: reduction buffer + room for carried sums
-    int pick = -1, KS = KB;
-    for (int c = 0; c < 3 && pick < 0; c++) {
-        const size_t budget = SMEM_MAX / occ_of[c] - 1024;
-        if ((size_t)KB * Cfg<MT>::PB + red_bytes + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
-            pick = c;
+    // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
+    constexpr bool WIDE = MT > 2;
+    const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 2}, Shape{8, 2, 2}};
+    const Shape sliced[2] = {WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
+    Shape sh{0, 0, 0};
+    int KS = KB;
+    for (int c = 0; c < 3 && sh.nw == 0; c++) {
+        if (smem_bytes<MT>(unsliced[c].nw, KB, unsliced[c].stages, false, 0) <= SMEM_MAX / unsliced[c].occ - 1024) {
+            sh = unsliced[c];
         }
     }
-    int stages = pick >= 0 ? st_of[pick] : 0;
-    if (pick < 0) {
-        // slices: two CTAs per SM, three ring stages, or two if a slice of 8 super-blocks needs the room
-        pick = 2;
-        for (stages = 3; stages >= 2; stages--) {
-            const size_t budget = SMEM_MAX / 2 - 1024 - fixed - (size_t)WARPS * stages * SLOT_BYTES;
-            KS = (int)(budget / Cfg<MT>::PB) / 8 * 8;
-            if (KS >= 8) {
-                break;
+    if (sh.nw == 0) {
+        for (int c = 0; c < 2 && sh.nw == 0; c++) {
+            const size_t room = SMEM_MAX / sliced[c].occ - 1024 - 8 * 1024;  // 8 KB set aside for the carried sums
+            const size_t rest = smem_bytes<MT>(sliced[c].nw, 0, sliced[c].stages, false, 0);
+            const int ks = rest < room ? (int)((room - rest) / Cfg<MT>::PB) / sliced[c].nw * sliced[c].nw : 0;
+            if (ks >= sliced[c].nw) {
+                sh = sliced[c];
+                KS = ks;
             }
         }
-        if (KS < 8) {
+        if (sh.nw == 0) {
             *handled = false;
             return JQ_OK;
         }
     }
-    const int occ = occ_of[pick];
-    const int grid = tiles < sm_count() * occ ? tiles : sm_count() * occ;
+    const int grid = tiles < sm_count() * sh.occ ? tiles : sm_count() * sh.occ;
     const int max_tiles = (tiles + grid - 1) / grid;
-    const bool sliced = KS < KB;
-    const size_t smem = smem_bytes<MT>(KS, stages, sliced, max_tiles);
-    if (smem > SMEM_MAX / occ - 1024) {
+    const bool is_sliced = KS < KB;
+    const size_t smem = smem_bytes<MT>(sh.nw, KS, sh.stages, is_sliced, max_tiles);
+    if (smem > SMEM_MAX / sh.occ - 1024) {
         *handled = false;  // more tiles per CTA than the carried sums have room for
         return JQ_OK;
     }
@@ -538,10 +614,19 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
     if (rc != JQ_OK) {
         return rc;
     }
-    if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
-    if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
-    if (stages == 3) return launch<MT, 3, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
-    return launch<MT, 2, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
+#define JQ_SHAPE(NWV, OCCV, STV)                                   \
+    if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
+        return launch<MT, STV, NWV, OCCV>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+    }
+    if constexpr (WIDE) {
+        JQ_SHAPE(16, 1, 3)
+        JQ_SHAPE(16, 1, 2)
+    } else {
+        JQ_SHAPE(8, 2, 3)
+    }
+    JQ_SHAPE(8, 2, 2)
+#undef JQ_SHAPE
+    return fail(JQ_ERR_UNSUPPORTED, "gemv_q4k_i8: no kernel for the chosen launch shape");
 }
 
 }  // namespace
@@ -552,7 +637,7 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
     if (rows < 1 || rows > 8 || k <= 0) {
         return 0;
     }
-    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : (rows <= 4 ? Cfg<4>::PB : Cfg<8>::PB));
+    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : Cfg<8>::PB);
     return (size_t)(k / 256) * pb;
 }
 
@@ -566,7 +651,6 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     }
     if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
     if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
-    if (rows <= 4) return run<4>(v, x, rows, bias, y, s, image, handled);
     return run<8>(v, x, rows, bias, y, s, image, handled);
 }
 
