@@ -164,7 +164,7 @@ def run_ours(args):
 
     if args.leg in ("prefill", "decode"):
         # one leg alone, for profiler captures: no sweep, a short line of its own
-        out = prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else decode_leg(torch, device)
+        out = prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else decode_leg(torch, device, args.decode_shape)
         print(json.dumps({"leg": args.leg, "result": out}), flush=True)
         return
 
@@ -385,13 +385,15 @@ def prefill_leg(torch, device, L, _lib):
     return out
 
 
-def decode_leg(torch, device):
+def decode_leg(torch, device, shape=None):
     """BASELINE.json configs[3]: Llama-style decoder, 7B shape (32 layers, d 4096, 32 heads, FFN 11008, vocab 32000),
     seeded N(0, 0.02) weights quantised Q4_K_M-style (Q6_K for wv, w2 and the output projection, Q4_K elsewhere),
     512 uniform-random prompt tokens, then 128 greedy tokens at batch 1. Reports decode tokens/s."""
     import numpy as np
     from jitnn_b200 import LlamaDecoder, synth
     layers, dim, heads, hidden, vocab, prompt_len, gen = 32, 4096, 32, 11008, 32000, 512, 128
+    if shape:  # "layers,prompt,gen": a cut-down run for profiler captures, not a bench number
+        layers, prompt_len, gen = (int(v) for v in shape.split(","))
     dec = LlamaDecoder(layers, dim, heads, heads, hidden, vocab, max_seq=prompt_len + gen + 8, device=device.index)
     g = torch.Generator(device=device).manual_seed(2024)
 
@@ -515,6 +517,8 @@ def main():
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"],
                     help="run only the prefill GEMM leg or only the 7B-shape decode leg (one GPU; for profiler captures)")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
+    ap.add_argument("--decode-shape", default=None, metavar="LAYERS,PROMPT,GEN",
+                    help="with --leg decode: fewer layers / a shorter prompt and run, for profiler captures")
     ap.add_argument("--eager", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default=None, metavar="NxKxM",
                     help="restrict the sweep to one shape and batch, e.g. 32000x4096x1 (a small case for profiler captures)")

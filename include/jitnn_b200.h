@@ -154,6 +154,8 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *                       tensor-core prefill kernel (default 0 = never: FP32 results for every m).
  *   "gemv_generic"      non-zero: every decode GEMV runs on the generic CUDA-core kernel (for comparisons).
  *   "decoder_graph"     zero: the decoder issues its single-token step kernel by kernel instead of replaying a CUDA graph.
+ *   "decoder_fused"     zero: the decoder's single-token step uses the general kernels (one per operator) instead of the
+ *                       fused ones that hand activations to the next linear as its activation image.
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);

@@ -158,6 +158,7 @@ static const char* type_name(int type) {
 static std::atomic<int64_t> g_prefill_min_rows{0};
 std::atomic<int64_t> g_opt_gemv_generic{0};
 std::atomic<int64_t> g_opt_decoder_graph{1};
+std::atomic<int64_t> g_opt_decoder_fused{1};
 
 // ---- linear on device pointers --------------------------------------------------------------------
 int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
@@ -604,6 +605,10 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_gemv_generic.store(value != 0);
         return JQ_OK;
     }
+    if (name != nullptr && strcmp(name, "decoder_fused") == 0) {
+        g_opt_decoder_fused.store(value != 0);
+        return JQ_OK;
+    }
     if (name != nullptr && strcmp(name, "decoder_graph") == 0) {
         g_opt_decoder_graph.store(value != 0);
         return JQ_OK;
@@ -618,6 +623,10 @@ int jq_get_option(const char* name, int64_t* value) {
     }
     if (name != nullptr && value != nullptr && strcmp(name, "gemv_generic") == 0) {
         *value = g_opt_gemv_generic.load();
+        return JQ_OK;
+    }
+    if (name != nullptr && value != nullptr && strcmp(name, "decoder_fused") == 0) {
+        *value = g_opt_decoder_fused.load();
         return JQ_OK;
     }
     if (name != nullptr && value != nullptr && strcmp(name, "decoder_graph") == 0) {

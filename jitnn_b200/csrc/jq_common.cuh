@@ -100,6 +100,12 @@ int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStrea
 // Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
+// The same GEMVs for one row of x whose activation image a kernel earlier in the stream has already written
+// (jq_q4k_image.cuh, jq_q6k_image.cuh); the Q4_K one can take a second weight with the same k in the same launch.
+size_t q4k_image_bytes_one_row(int64_t k);
+size_t q6k_image_bytes_one_row(int64_t k);
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled);
+int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* bias, float* y, cudaStream_t s, bool* handled);
 // The same for Q6_K, rows <= 4.
 int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
 size_t gemv_q6k_i8_scratch_bytes(int64_t k, int rows);
@@ -121,6 +127,8 @@ int prefill_status(int* status);
 extern std::atomic<int64_t> g_opt_gemv_generic;
 // Option "decoder_graph": zero keeps the decoder's single-token step on eager launches (for comparisons).
 extern std::atomic<int64_t> g_opt_decoder_graph;
+// Option "decoder_fused": zero keeps the decoder's single-token step on the general kernels (one per operator).
+extern std::atomic<int64_t> g_opt_decoder_fused;
 
 }  // namespace jq
 

@@ -11,6 +11,8 @@
 #include <vector>
 
 #include "jq_common.cuh"
+#include "jq_q4k_image.cuh"
+#include "jq_q6k_image.cuh"
 
 namespace jq {
 
@@ -312,6 +314,360 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
+
+// ---- the single-token step with fewer, fused kernels --------------------------------------------------------------
+// For one token and Q4_K / Q6_K linears the kernels that produce an activation vector (norm, attention, SwiGLU) write
+// it straight as the activation image the integer GEMV kernels read (jq_q4k_image.cuh, jq_q6k_image.cuh): no float
+// vector and no separate image kernel in between. Every kernel of the step starts with griddepcontrol.wait (all that
+// the kernel before it wrote is visible from there on) followed by griddepcontrol.launch_dependents (the next kernel
+// may be scheduled and, if it is a GEMV, start requesting its weights), and does not touch global memory before.
+__device__ __forceinline__ void pdl_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+
+struct Images {
+    uint8_t* q4k;  // destination of the Q4_K image, or nullptr if no consumer is Q4_K
+    uint8_t* q6k;
+};
+
+__device__ __forceinline__ void write_images(const float* block, int b, const Images& im, int lane) {
+    if (im.q4k != nullptr) {
+        q4k::build_image<1>(block, 0, im.q4k + (size_t)b * q4k::Cfg<1>::PB, lane);
+    }
+    if (im.q6k != nullptr) {
+        q6k::build_image<1>(block, 0, im.q6k + (size_t)b * q6k::Cfg<1>::PB, lane);
+    }
+}
+
+// x = embedding row of the token (table != nullptr), or x += delta (delta != nullptr), or x as it is; then RMSNorm
+// (ops/RowNorm.java:266-306) into shared memory and from there into the images. One CTA of 1024 threads, dim <= 16384.
+constexpr int NORM_THREADS = 1024;
+__global__ void __launch_bounds__(NORM_THREADS) norm_image_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ table,
+                                                                  const int* __restrict__ token, int vocab, const float* __restrict__ w, float eps, int dim,
+                                                                  Images im) {
+    extern __shared__ __align__(16) float norm_xs[];
+    __shared__ float scratch[32];
+    pdl_enter();
+    const int n4 = dim >> 2;
+    const float4* src = reinterpret_cast<const float4*>(x);
+    if (table != nullptr) {
+        int tok = token[0];
+        tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+        src = reinterpret_cast<const float4*>(table + (int64_t)tok * dim);
+    }
+    float4 v[4];
+    float sq = 0.0f;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const int i = (int)threadIdx.x + u * NORM_THREADS;
+        if (i < n4) {
+            float4 a = src[i];
+            if (delta != nullptr) {
+                const float4 b = reinterpret_cast<const float4*>(delta)[i];
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+            }
+            if (delta != nullptr || table != nullptr) {
+                reinterpret_cast<float4*>(x)[i] = a;
+            }
+            v[u] = a;
+            sq = fmaf(a.x, a.x, sq); sq = fmaf(a.y, a.y, sq); sq = fmaf(a.z, a.z, sq); sq = fmaf(a.w, a.w, sq);
+        }
+    }
+    const float total = block_sum(sq, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const int i = (int)threadIdx.x + u * NORM_THREADS;
+        if (i < n4) {
+            const float4 ww = reinterpret_cast<const float4*>(w)[i];
+            reinterpret_cast<float4*>(norm_xs)[i] = make_float4(v[u].x * inv * ww.x, v[u].y * inv * ww.y, v[u].z * inv * ww.z, v[u].w * inv * ww.w);
+        }
+    }
+    __syncthreads();
+    const int KB = dim >> 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int task = warp; task < 2 * KB; task += NORM_THREADS / 32) {
+        const int b = task < KB ? task : task - KB;
+        Images one{task < KB ? im.q4k : nullptr, task < KB ? nullptr : im.q6k};
+        write_images(norm_xs + (size_t)b * 256, b, one, lane);
+    }
+}
+
+// Attention of the one new token (head_dim 128): RoPE of its query and key (ops/Rope.java:125-149), the append of key
+// and value to the cache, the scores against one chunk of ATT_CHUNK cached keys, and the partial softmax-weighted sum
+// of their values, per CTA (head, chunk) of 256 threads. The CTA that finishes last among those of a pair of heads
+// (256 outputs = one super-block of the next linear's k) merges the chunks' partial results in chunk order and writes
+// them as that linear's activation image.
+constexpr int ATTF_THREADS = 256;
+__global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                                                                       float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                                       const int* __restrict__ pos0, int heads, int kv_heads, int stride_splits, float scale,
+                                                                       float* __restrict__ part, int* __restrict__ counters, Images im) {
+    constexpr int HD = 128, HALF = 64;
+    __shared__ __align__(16) float qs[HD];
+    __shared__ __align__(16) float knew[HD];
+    __shared__ __align__(16) float vnew[HD];
+    __shared__ float sc[ATT_CHUNK];
+    __shared__ __align__(16) float red[8][HD];
+    __shared__ __align__(16) float outs[256];
+    __shared__ float ml[2];
+    __shared__ int last_flag;
+    pdl_enter();
+    const int h = blockIdx.x, sp = blockIdx.y, splits = gridDim.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pos = *pos0, keys = pos + 1, k0 = sp * ATT_CHUNK;
+    const int kv_dim = kv_heads * HD, group = heads / kv_heads, kvh = h / group;
+    float* out = part + ((int64_t)h * stride_splits + sp) * (HD + 2);
+    if (k0 < keys) {
+        const int cnt = keys - k0 < ATT_CHUNK ? keys - k0 : ATT_CHUNK;
+        const bool has_new = pos < k0 + ATT_CHUNK;  // the new token's key and value belong to this chunk
+        if (tid < HALF) {
+            const float c = cos_t[pos * HALF + tid], s = sin_t[pos * HALF + tid];
+            const float a = q[h * HD + tid], b = q[h * HD + tid + HALF];
+            qs[tid] = a * c - b * s;
+            qs[tid + HALF] = a * s + b * c;
+        } else if (tid < 2 * HALF && has_new) {
+            const int p = tid - HALF;
+            const float c = cos_t[pos * HALF + p], s = sin_t[pos * HALF + p];
+            const float a = k[kvh * HD + p], b = k[kvh * HD + p + HALF];
+            const float r0 = a * c - b * s, r1 = a * s + b * c;
+            knew[p] = r0;
+            knew[p + HALF] = r1;
+            if (h % group == 0) {
+                k_cache[(int64_t)pos * kv_dim + kvh * HD + p] = r0;
+                k_cache[(int64_t)pos * kv_dim + kvh * HD + p + HALF] = r1;
+            }
+        } else if (tid >= 2 * HALF && has_new) {
+            const int p = tid - 2 * HALF;
+            const float val = v[kvh * HD + p];
+            vnew[p] = val;
+            if (h % group == 0) {
+                v_cache[(int64_t)pos * kv_dim + kvh * HD + p] = val;
+            }
+        }
+        __syncthreads();
+        // scores: warp w takes keys 8w .. 8w + 7 of the chunk, a lane four consecutive dimensions of each
+        {
+            const float4 qv = reinterpret_cast<const float4*>(qs)[lane];
+            float dot[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int j = warp * 8 + u;
+                dot[u] = 0.0f;
+                if (j < cnt) {
+                    const float4 kv = k0 + j == pos ? reinterpret_cast<const float4*>(knew)[lane]
+                                                    : __ldg(reinterpret_cast<const float4*>(k_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
+                    dot[u] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, qv.w * kv.w)));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+                }
+                if (lane == 0 && warp * 8 + u < cnt) {
+                    sc[warp * 8 + u] = dot[u] * scale;
+                }
+            }
+        }
+        __syncthreads();
+        if (warp == 0) {
+            const float s0 = lane < cnt ? sc[lane] : -INFINITY, s1 = lane + 32 < cnt ? sc[lane + 32] : -INFINITY;
+            float mx = fmaxf(s0, s1);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            }
+            const float e0 = lane < cnt ? expf(s0 - mx) : 0.0f, e1 = lane + 32 < cnt ? expf(s1 - mx) : 0.0f;
+            if (lane < cnt) sc[lane] = e0;
+            if (lane + 32 < cnt) sc[lane + 32] = e1;
+            float l = e0 + e1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                l += __shfl_xor_sync(0xffffffffu, l, o);
+            }
+            if (lane == 0) {
+                ml[0] = mx;
+                ml[1] = l;
+            }
+        }
+        __syncthreads();
+        // weighted values: warp w takes keys w, w + 8, ..., a lane four consecutive dimensions; then the 8 warps are summed
+        {
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int j = warp + 8 * u;
+                if (j < cnt) {
+                    const float4 vv = k0 + j == pos ? reinterpret_cast<const float4*>(vnew)[lane]
+                                                    : __ldg(reinterpret_cast<const float4*>(v_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
+                    const float pj = sc[j];
+                    acc.x = fmaf(pj, vv.x, acc.x); acc.y = fmaf(pj, vv.y, acc.y); acc.z = fmaf(pj, vv.z, acc.z); acc.w = fmaf(pj, vv.w, acc.w);
+                }
+            }
+            reinterpret_cast<float4*>(red[warp])[lane] = acc;
+        }
+        __syncthreads();
+        if (tid < HD) {
+            out[tid] = ((red[0][tid] + red[1][tid]) + (red[2][tid] + red[3][tid])) + ((red[4][tid] + red[5][tid]) + (red[6][tid] + red[7][tid]));
+        } else if (tid == HD) {
+            out[HD] = ml[0];
+            out[HD + 1] = ml[1];
+        }
+    } else if (tid == 0) {
+        out[HD] = -INFINITY;  // no key of this chunk is visible yet
+        out[HD + 1] = 0.0f;
+    }
+    // ---- the last CTA of this pair of heads merges the chunks ---------------------------------------------------------------
+    __threadfence();
+    __syncthreads();
+    const int sb = h >> 1;  // 2 heads of 128 = one super-block of 256
+    if (tid == 0) {
+        const int done = atomicAdd(&counters[sb], 1);
+        last_flag = done == 2 * splits - 1;
+        if (last_flag) {
+            counters[sb] = 0;  // every CTA of the pair has counted: ready for the next launch
+        }
+    }
+    __syncthreads();
+    if (!last_flag) {
+        return;
+    }
+    __threadfence();
+    {
+        const int hh = 2 * sb + (tid >> 7), d = tid & 127;
+        const float* p = part + (int64_t)hh * stride_splits * (HD + 2);
+        float M = -INFINITY;
+        for (int s = 0; s < splits; s++) {
+            M = fmaxf(M, __ldcg(p + (int64_t)s * (HD + 2) + HD));
+        }
+        float L = 0.0f, acc = 0.0f;
+        for (int s = 0; s < splits; s++) {
+            const float m = __ldcg(p + (int64_t)s * (HD + 2) + HD);
+            if (m != -INFINITY) {
+                const float wgt = expf(m - M);
+                L = fmaf(wgt, __ldcg(p + (int64_t)s * (HD + 2) + HD + 1), L);
+                acc = fmaf(wgt, __ldcg(p + (int64_t)s * (HD + 2) + d), acc);
+            }
+        }
+        outs[tid] = acc / L;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        write_images(outs, sb, im, lane);
+    }
+}
+
+// act = silu(gate) * up (F.java:1158-1161) for one super-block of 256 per CTA, written as the next linear's image.
+__global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im) {
+    __shared__ __align__(16) float xs[256];
+    pdl_enter();
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    const float g = gate[i];
+    xs[threadIdx.x] = (g / (1.0f + expf(-g))) * up[i];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        write_images(xs, blockIdx.x, im, threadIdx.x);
+    }
+}
+
+// First index of the maximum (ops/Reduce.java:201) of one row, over ARGMAX_CTAS CTAs: each leaves its best (value,
+// index), the CTA that finishes last picks among them.
+constexpr int ARGMAX_CTAS = 64;
+__global__ void __launch_bounds__(256) argmax_split_kernel(const float* __restrict__ logits, int vocab, float* __restrict__ best_v, int* __restrict__ best_i,
+                                                           int* __restrict__ counter, int* __restrict__ out) {
+    __shared__ float bv[8];
+    __shared__ int bi[8];
+    __shared__ int last_flag;
+    pdl_enter();
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < vocab; i += ARGMAX_CTAS * 256) {
+        const float val = logits[i];
+        if (val > best || (val == best && i < idx)) {
+            best = val;
+            idx = i;
+        }
+    }
+    auto better = [](float v1, int i1, float v2, int i2) { return v1 > v2 || (v1 == v2 && i1 < i2); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        bv[threadIdx.x >> 5] = best;
+        bi[threadIdx.x >> 5] = idx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int wv = 1; wv < 8; wv++) {
+            if (better(bv[wv], bi[wv], best, idx)) {
+                best = bv[wv];
+                idx = bi[wv];
+            }
+        }
+        best_v[blockIdx.x] = best;
+        best_i[blockIdx.x] = idx;
+        __threadfence();
+        const int done = atomicAdd(counter, 1);
+        last_flag = done == ARGMAX_CTAS - 1;
+        if (last_flag) {
+            *counter = 0;
+        }
+    }
+    __syncthreads();
+    if (!last_flag || threadIdx.x >= 32) {
+        return;
+    }
+    __threadfence();
+    best = -INFINITY;
+    idx = 0x7fffffff;
+    for (int c = threadIdx.x; c < ARGMAX_CTAS; c += 32) {
+        const float ov = __ldcg(best_v + c);
+        const int oi = __ldcg(best_i + c);
+        if (better(ov, oi, best, idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) {
+            best = ov;
+            idx = oi;
+        }
+    }
+    if (threadIdx.x == 0) {
+        out[0] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while the one before it still runs
+// (it starts with griddepcontrol.wait).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool programmatic, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace
 }  // namespace jq
 
@@ -332,6 +688,10 @@ struct jq_decoder {
     float* att_part;     // [tokens][heads][splits][head_dim + 2] partial attention results
     int splits;          // key chunks of ATT_CHUNK positions covering max_seq
     int *tokens, *pos, *argmax;
+    uint8_t *img_q4k, *img_q6k;  // activation images of the fused single-token step
+    int* counters;               // [dim / 256 attention merge counters][1 argmax counter], zero between launches
+    float* argmax_v;             // [ARGMAX_CTAS] per-CTA best value
+    int* argmax_i;               // [ARGMAX_CTAS] per-CTA best index
     int* host_stage;     // pinned: [0..7] tokens in, [8] position in, [9..16] argmax out
     int warm_calls;      // single-token forwards issued so far
     cudaGraphExec_t graph;  // the single-token forward, captured on its second call
@@ -368,6 +728,11 @@ JQ_API int jq_decoder_destroy(jq_decoder* d) {
     cudaFree(d->tokens);
     cudaFree(d->pos);
     cudaFree(d->argmax);
+    cudaFree(d->img_q4k);
+    cudaFree(d->img_q6k);
+    cudaFree(d->counters);
+    cudaFree(d->argmax_v);
+    cudaFree(d->argmax_i);
     cudaFreeHost(d->host_stage);
     if (d->graph != nullptr) {
         cudaGraphExecDestroy(d->graph);
@@ -432,6 +797,10 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     }
     d->tokens = d->pos = d->argmax = nullptr;
     d->host_stage = nullptr;
+    d->img_q4k = d->img_q6k = nullptr;
+    d->counters = nullptr;
+    d->argmax_v = nullptr;
+    d->argmax_i = nullptr;
     for (auto& a : allocs) {
         if (e == cudaSuccess) {
             e = cudaMalloc(a.p, a.n * sizeof(float));
@@ -441,7 +810,18 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     if (e == cudaSuccess) e = cudaMalloc(&d->pos, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&d->argmax, T * sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost(&d->host_stage, (2 * T + 1) * sizeof(int));
+    {
+        const int64_t kmax = dim > hidden ? dim : hidden;
+        const size_t ncount = (size_t)(dim / 256 + 2);
+        if (e == cudaSuccess) e = cudaMalloc(&d->img_q4k, q4k_image_bytes_one_row(kmax) + 256);
+        if (e == cudaSuccess) e = cudaMalloc(&d->img_q6k, q6k_image_bytes_one_row(kmax) + 256);
+        if (e == cudaSuccess) e = cudaMalloc(&d->counters, ncount * sizeof(int));
+        if (e == cudaSuccess) e = cudaMemset(d->counters, 0, ncount * sizeof(int));
+        if (e == cudaSuccess) e = cudaMalloc(&d->argmax_v, ARGMAX_CTAS * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&d->argmax_i, ARGMAX_CTAS * sizeof(int));
+    }
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(norm_image_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
     if (e == cudaSuccess) {
         // cos / sin tables in double, stored as float (ops/Rope.java:84-101)
         const int half = head_dim / 2;
@@ -543,9 +923,128 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table) {
     return e == cudaSuccess ? JQ_OK : cuda_fail(e, "jq_decoder_set_embedding");
 }
 
+// Whether the single-token step can take the fused kernels: Q4_K / Q6_K linears, head_dim 128, sizes in whole super-blocks.
+static bool fused_step_possible(const jq_decoder* d) {
+    if (g_opt_decoder_fused.load() == 0 || d->head_dim != 128 || d->dim % 256 != 0 || d->hidden % 256 != 0 || d->dim > 16384) {
+        return false;
+    }
+    for (const jq_weight* w : d->lin) {
+        if (w == nullptr || (w->type != JQ_TYPE_Q4_K && w->type != JQ_TYPE_Q6_K)) {
+            return false;
+        }
+    }
+    return d->output != nullptr && (d->output->type == JQ_TYPE_Q4_K || d->output->type == JQ_TYPE_Q6_K);
+}
+
+// The forward of one token with the fused kernels (see pdl_enter above). `first_programmatic` is false when the
+// operation before the first kernel in the stream is not a kernel (the token copy of the captured graph).
+static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* ta, cudaStream_t s) {
+    const int dim = d->dim;
+    const int64_t kv_dim = (int64_t)d->kv_heads * d->head_dim;
+    int rc = JQ_OK;
+    auto CKL = [&](cudaError_t e, const char* name) {
+        count_launch(1);
+        if (rc == JQ_OK && e != cudaSuccess) {
+            rc = cuda_fail(e, name);
+        }
+    };
+    auto images_for = [&](std::initializer_list<const jq_weight*> consumers) {
+        Images im{nullptr, nullptr};
+        for (const jq_weight* w : consumers) {
+            if (w->type == JQ_TYPE_Q4_K) im.q4k = d->img_q4k;
+            if (w->type == JQ_TYPE_Q6_K) im.q6k = d->img_q6k;
+        }
+        return im;
+    };
+    // y = W x (and y2 = W2 x in the same launch when both are Q4_K), x being the image written just before
+    auto GEMV = [&](const jq_weight* w, float* y, const jq_weight* w2, float* y2) {
+        for (int pass = 0; pass < 2 && rc == JQ_OK; pass++) {
+            const jq_weight* cur = pass == 0 ? w : w2;
+            float* out_ = pass == 0 ? y : y2;
+            if (cur == nullptr) {
+                break;
+            }
+            const View v{cur->q, cur->aux, cur->n, cur->k, cur->type};
+            bool handled = false;
+            if (cur->type == JQ_TYPE_Q4_K) {
+                if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
+                    const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
+                    rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, s, &handled);
+                    pass = 1;  // both done
+                } else {
+                    rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, s, &handled);
+                }
+            } else {
+                rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, s, &handled);
+            }
+            if (rc == JQ_OK && !handled) {
+                rc = fail(JQ_ERR_UNSUPPORTED, "decoder: a [%lld, %lld] linear is outside what the tensor-core GEMV takes (set option decoder_fused to 0)",
+                          (long long)cur->n, (long long)cur->k);
+            }
+        }
+    };
+    bool first_programmatic = true;
+    if (ta != nullptr) {
+        set_tokens_kernel<<<1, 32, 0, s>>>(*ta, d->tokens, d->pos);
+        CKL(cudaGetLastError(), "set_tokens_kernel");
+    } else {
+        cudaError_t e = cudaMemcpyAsync(d->tokens, d->host_stage, MAX_TOKENS * sizeof(int), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(d->pos, d->host_stage + MAX_TOKENS, sizeof(int), cudaMemcpyHostToDevice, s);
+        }
+        if (e != cudaSuccess) {
+            return cuda_fail(e, "decoder inputs");
+        }
+        first_programmatic = false;
+    }
+    const float scale = (float)(1.0 / std::sqrt((double)d->head_dim));
+    const size_t norm_smem = (size_t)dim * sizeof(float);
+    const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
+    for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
+        const jq_weight* const* L = &d->lin[(size_t)l * 7];
+        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        // attention block: x = embedding (first layer) or x += feed-forward output of the layer before; norm -> images
+        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
+                       l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]})),
+            "norm_image_kernel");
+        GEMV(L[0], d->q, L[1], d->k);
+        GEMV(L[2], d->v, nullptr, nullptr);
+        if (rc != JQ_OK) break;
+        CKL(launch_pdl(attention_image_kernel, dim3(d->heads, splits_now), dim3(ATTF_THREADS), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos,
+                       d->heads, d->kv_heads, d->splits, scale, d->att_part, d->counters, images_for({L[3]})),
+            "attention_image_kernel");
+        GEMV(L[3], d->proj, nullptr, nullptr);
+        if (rc != JQ_OK) break;
+        // feed-forward block
+        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
+                       d->norms + (size_t)(2 * l + 1) * dim, d->eps, dim, images_for({L[4], L[5]})),
+            "norm_image_kernel");
+        GEMV(L[4], d->gate, L[5], d->up);
+        if (rc != JQ_OK) break;
+        CKL(launch_pdl(swiglu_image_kernel, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]})), "swiglu_image_kernel");
+        GEMV(L[6], d->proj, nullptr, nullptr);
+    }
+    if (rc == JQ_OK) {
+        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
+                       d->norms + (size_t)(2 * d->layers) * dim, d->eps, dim, images_for({d->output})),
+            "norm_image_kernel");
+        GEMV(d->output, d->logits, nullptr, nullptr);
+    }
+    if (rc == JQ_OK) {
+        CKL(launch_pdl(argmax_split_kernel, dim3(ARGMAX_CTAS), dim3(256), 0, s, true, d->logits, d->vocab, d->argmax_v, d->argmax_i,
+                       d->counters + d->dim / 256 + 1, d->argmax),
+            "argmax_split_kernel");
+    }
+    return rc;
+}
+
 // Enqueues the forward of T tokens on s. Tokens and position come either from kernel arguments (ta != nullptr) or, for
 // the captured single-token graph, from the pinned staging words through a host-to-device copy.
 static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* ta, cudaStream_t s) {
+    if (T == 1 && fused_step_possible(d)) {
+        return enqueue_forward_fused(d, max_keys, ta, s);
+    }
     const int dim = d->dim, hd = d->head_dim;
     const int64_t kv_dim = (int64_t)d->kv_heads * hd;
     int rc = JQ_OK;

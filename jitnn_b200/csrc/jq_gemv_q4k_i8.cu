@@ -32,8 +32,12 @@
 #include <mutex>
 
 #include "jq_formats.cuh"
+#include "jq_q4k_image.cuh"
 
 namespace jq {
+
+using q4k::Cfg;
+using q4k::build_image;
 
 namespace {
 
@@ -81,120 +85,6 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
-// Column layouts of the activation image. Up to two activation rows are "packed": one MMA column group holds column
-// 3m + i for digit i of row m. More rows are "digit major": group i holds digit i, column m of it row m, so that a
-// lane's accumulator columns 2t and 2t + 1 are all three digits of rows 2t and 2t + 1 and need no exchange with
-// other lanes.
-template <int MT>
-struct Cfg {
-    static constexpr bool DIGIT_MAJOR = MT > 2;
-    static constexpr int COLS = 3 * MT;
-    static constexpr int NG = DIGIT_MAJOR ? 3 : 1;                         // MMA column groups for the quants
-    static constexpr int NCOL = DIGIT_MAJOR ? 8 : COLS;                    // columns stored per group
-    // mins: two columns (low 7 bits / rest of the digit sums) per digit column. Packed: column 2 (3m + i) + part.
-    // Digit major: group 2i + (m & 1), column 2 (m / 2) + part, which hands lane t the rows 2t and 2t + 1 again.
-    static constexpr int NGM = DIGIT_MAJOR ? 6 : (2 * COLS + 7) / 8;
-    static constexpr int NCOLM = NGM == 1 ? 2 * COLS : 8;
-    // bytes of activation image per super-block: digit fragments, digit-sum fragments, column weights
-    static constexpr size_t XD = (size_t)8 * NG * NCOL * 4 * 8;   // 8 sub-blocks x groups x columns x 4 lanes x 8 bytes
-    static constexpr size_t XM = (size_t)NGM * NCOLM * 4 * 4;     // groups x columns x 4 lanes x 4 bytes (lanes 2, 3: zero)
-    // one float per digit column: its weight s 2^(8 i - 21); packed layouts add a second table with the weights / 16
-    static constexpr size_t TAB = (size_t)NG * 8 * 4 * (DIGIT_MAJOR ? 1 : 2);
-    static constexpr size_t PB = XD + XM + TAB;
-    static_assert(PB % 16 == 0, "the image is copied in 16-byte pieces");
-    __host__ __device__ static constexpr int qcol(int m, int i) { return DIGIT_MAJOR ? 8 * i + m : 3 * m + i; }
-    __host__ __device__ static constexpr int mcol(int m, int i, int part) {
-        return DIGIT_MAJOR ? 8 * (2 * i + (m & 1)) + 2 * (m >> 1) + part : 2 * (3 * m + i) + part;
-    }
-};
-
-// ---- activations -> image ---------------------------------------------------------------------------------------
-// One warp turns one (super-block of k, row of x) into its part of the image at `img` (global or shared memory);
-// lane = octet: sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of that sub-block's MMA. Digit fragments are stored
-// per pair of sub-blocks, so that the GEMV reads the B operands of two MMAs with one 16-byte load.
-template <int MT>
-__device__ __forceinline__ void build_image(const float* __restrict__ x, int rows, int64_t k, int b, int m, uint8_t* img, int lane) {
-    using C = Cfg<MT>;
-    constexpr int NG = C::NG, NCOL = C::NCOL, NCOLM = C::NCOLM;
-    const int sub = lane >> 2, tt = lane & 3;
-    uint2* xd = reinterpret_cast<uint2*>(img);
-    uint8_t* xm = img + C::XD;
-    float* tab = reinterpret_cast<float*>(img + C::XD + C::XM);
-    if (!C::DIGIT_MAJOR && m == 0 && lane >= C::COLS && lane < NG * 8) {
-        tab[lane] = 0.0f;  // columns that hold no activation row
-        tab[NG * 8 + lane] = 0.0f;
-    }
-    float xv[8];
-    if (m < rows) {
-        const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
-        const float4 lo = xp[0], hi = xp[1];
-        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
-        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            xv[i] = 0.0f;
-        }
-    }
-    float am = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        am = fmaxf(am, fabsf(xv[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    }
-    // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
-    uint32_t e = __float_as_uint(am) & 0x7f800000u;
-    e = e < 0x0d000000u ? 0x0d000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-25 normal
-    // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
-    const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
-    int X[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        X[i] = __float2int_rn(xv[i] * inv);
-    }
-#pragma unroll
-    for (int dgt = 0; dgt < 3; dgt++) {
-        uint32_t w0 = 0, w1 = 0;
-        int sum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
-            X[i] = (X[i] - d) >> 8;
-            sum += d;
-            if (i < 4) {
-                w0 |= (uint32_t)(d & 0xff) << (8 * i);
-            } else {
-                w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
-            }
-        }
-        const int col = C::qcol(m, dgt);
-        xd[((((size_t)(sub >> 1) * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt) * 2 + (sub & 1)] = make_uint2(w0, w1);
-        // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte.
-        // The mins MMA has k = 16 and eight mins: lane slot sub / 4 holds the sums of sub-blocks 4 (sub / 4) .. + 3 as bytes,
-        // lane slots 2 and 3 (k = 8 .. 15) are zero.
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (tt < 2) {
-            const int lo7 = sum & 127, hi = (sum - lo7) >> 7;
-#pragma unroll
-            for (int p = 0; p < 2; p++) {
-                const int mc = C::mcol(m, dgt, p);
-                uint8_t* cell = xm + ((size_t)(mc >> 3) * NCOLM + (mc & 7)) * 16;
-                cell[(tt == 0 ? (sub >> 2) : 2 + (sub >> 2)) * 4 + (sub & 3)] = tt == 0 ? (uint8_t)(p == 0 ? lo7 : hi) : (uint8_t)0;
-            }
-        }
-        if (lane == 0) {
-            tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
-            if (!C::DIGIT_MAJOR) {
-                tab[NG * 8 + col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (25u << 23)) : 0.0f;  // ... / 16
-            }
-        }
-    }
-}
-
 // The image in a scratch buffer in global memory, for the GEMV shapes that do not build it themselves. The kernel is
 // tiny and latency bound, so the work is spread over as many warps as possible.
 constexpr int PREP_WARPS = 4;
@@ -206,15 +96,25 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
     const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
     const int b = pair / MT, m = pair % MT;
     if (b < (int)(k >> 8)) {
-        build_image<MT>(x, rows, k, b, m, image + (size_t)b * Cfg<MT>::PB, threadIdx.x & 31);
+        build_image<MT>(m < rows ? x + (int64_t)m * k + (int64_t)b * 256 : nullptr, m, image + (size_t)b * Cfg<MT>::PB, threadIdx.x & 31);
     }
 }
 
 // ---- the GEMV ---------------------------------------------------------------------------------------------------
+// A second weight with the same k that is multiplied with the same x in the same launch (q = nullptr: none).
+struct Second {
+    const uint8_t* q;
+    int64_t n;
+    float* y;
+    int first_tiles;  // tiles of the first weight
+};
+
 template <int MT, int STAGES, int NW, int OCC>
-__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
                                                                   int KS, int max_tiles) {
+    // Tiles 0 .. w2.first_tiles - 1 are rows of v, the tiles from w2.first_tiles on rows of the second weight w2 (same k,
+    // same x, its own output), if there is one.
     // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
     // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
     using C = Cfg<MT>;
@@ -222,6 +122,7 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
     constexpr int THREADS = NW * 32;
     constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int KB = (int)(v.k >> 8);
@@ -231,7 +132,6 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
     float* carry = red + 2 * NW * 16 * MT;                                           // [max_tiles][16][MT], only if nslices > 1
     uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) + (size_t)warp * RING_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-    const int64_t n = v.n;
     const int64_t row_bytes = (int64_t)KB * 144;
 
     // ---- weight stream: chunk c = lane + 32 i of the 144 chunks (16 rows x 9) of a super-block -------------
@@ -256,9 +156,13 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
     const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + NW - 1) / NW : 0) : 0;
     const int nb_last = warp < len_last ? (len_last - warp + NW - 1) / NW : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const uint8_t* const gp0 = v.q + (int64_t)blockIdx.x * 16 * row_bytes + (uint32_t)warp * 144u + src0;  // first tile, first block
-    const int64_t tile_stride = (int64_t)gridDim.x * 16 * row_bytes;
-    const uint8_t* gp = gp0;
+    // this lane's first chunk of tile number ti of the CTA, first block of this warp in slice sl
+    auto lane_ptr = [&](int ti, int sl) {
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const uint8_t* base = tile < w2.first_tiles ? v.q + (int64_t)tile * 16 * row_bytes : w2.q + (int64_t)(tile - w2.first_tiles) * 16 * row_bytes;
+        return base + (uint32_t)(sl * KS + warp) * 144u + src0;
+    };
+    const uint8_t* gp = lane_ptr(0, 0);
     int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
     int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
     uint32_t iss_slot = 0;
@@ -274,13 +178,12 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
             gp += NW * 144;
             if (++iss_j == iss_nb) {
                 iss_j = 0;
-                gp += tile_stride - (int64_t)iss_nb * (NW * 144);
                 if (++iss_ti == my_tiles) {
                     iss_ti = 0;
                     iss_sl++;
                     iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
-                    gp = gp0 + (int64_t)iss_sl * KS * 144;
                 }
+                gp = lane_ptr(iss_ti, iss_sl);
             }
         }
         iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
@@ -494,9 +397,12 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
             }
             __syncthreads();
             // ---- the warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
+            const bool second = my_tile >= w2.first_tiles;
+            const int64_t n = second ? w2.n : v.n;
+            float* const yo = second ? w2.y : y;
             for (int o = tid; o < 16 * MT; o += THREADS) {
                 const int r = o / MT, m = o % MT;
-                const int64_t row = (int64_t)my_tile * 16 + r;
+                const int64_t row = (int64_t)(second ? my_tile - w2.first_tiles : my_tile) * 16 + r;
                 const float* p = rd + o;
                 constexpr int W = 16 * MT;  // floats per warp
                 float sum = ((p[0] + p[W]) + (p[2 * W] + p[3 * W])) + ((p[4 * W] + p[5 * W]) + (p[6 * W] + p[7 * W]));
@@ -509,7 +415,7 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, const
                 if (sl + 1 < nslices) {
                     carry[(size_t)ti * 16 * MT + o] = sum;
                 } else if (m < rows && row < n) {
-                    y[(int64_t)m * n + row] = sum + (bias != nullptr ? bias[row] : 0.0f);
+                    yo[(int64_t)m * n + row] = sum + (bias != nullptr && !second ? bias[row] : 0.0f);
                 }
             }
             parity ^= 1;
@@ -531,7 +437,8 @@ int sm_count() {
 }
 
 template <int MT, int STAGES, int NW, int OCC>
-int launch(const View& v, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles, size_t smem) {
+int launch(const View& v, const Second& w2, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles,
+           size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
@@ -539,7 +446,7 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
         JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
-    const int tiles = (int)((v.n + 15) / 16);
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(NW * 32);
@@ -550,7 +457,7 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, w2, image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
 }
@@ -570,9 +477,10 @@ struct Shape {
 };
 
 template <int MT>
-int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+int run(const View& v, const Second& w2, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+    // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
     const int KB = (int)(v.k / 256);
-    const int tiles = (int)((v.n + 15) / 16);
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
     // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
     constexpr bool WIDE = MT > 2;
     const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 2}, Shape{8, 2, 2}};
@@ -608,15 +516,17 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         return JQ_OK;
     }
     *handled = true;
-    q4k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
-    count_launch();
-    int rc = check_launch("q4k_activation_image_kernel");
-    if (rc != JQ_OK) {
-        return rc;
+    if (x != nullptr) {
+        q4k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+        count_launch();
+        int rc = check_launch("q4k_activation_image_kernel");
+        if (rc != JQ_OK) {
+            return rc;
+        }
     }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
-        return launch<MT, STV, NWV, OCCV>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        return launch<MT, STV, NWV, OCCV>(v, w2, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
     }
     if constexpr (WIDE) {
         JQ_SHAPE(16, 1, 3)
@@ -649,9 +559,25 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
         return JQ_OK;
     }
-    if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
-    if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
-    return run<8>(v, x, rows, bias, y, s, image, handled);
+    const Second none{nullptr, 0, nullptr, 0x7fffffff};
+    if (rows == 1) return run<1>(v, none, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2>(v, none, x, rows, bias, y, s, image, handled);
+    return run<8>(v, none, x, rows, bias, y, s, image, handled);
+}
+
+size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }
+
+// One row of x whose image (q4k::build_image<1> per super-block) a kernel earlier in the stream has written to `image`;
+// that kernel should execute griddepcontrol.launch_dependents so that this one can request weights meanwhile. With
+// v2 != nullptr the rows of a second Q4_K weight with the same k follow in the same launch, results in y2.
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled) {
+    *handled = false;
+    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31) ||
+        (v2 != nullptr && (v2->type != JQ_TYPE_Q4_K || v2->k != v.k || v2->n == 0 || y2 == nullptr))) {
+        return JQ_OK;
+    }
+    const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
+    return run<1>(v, w2, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
 }
 
 }  // namespace jq

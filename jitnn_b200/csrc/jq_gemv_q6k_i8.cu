@@ -18,8 +18,12 @@
 #include <mutex>
 
 #include "jq_formats.cuh"
+#include "jq_q6k_image.cuh"
 
 namespace jq {
+
+using q6k::Cfg;
+using q6k::build_image;
 
 namespace {
 
@@ -69,99 +73,18 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     return d;
 }
 
-template <int MT>
-struct Cfg {
-    static constexpr int COLS = 3 * MT;               // digit columns: column 3m + i is digit i of activation row m
-    static constexpr int NG = (COLS + 7) / 8;         // MMA column groups
-    static constexpr int NCOL = NG == 1 ? COLS : 8;   // columns stored per group
-    // bytes of activation image per super-block: digit fragments of the 16 scale groups, C fragments, column weights
-    static constexpr size_t XD = (size_t)16 * NG * NCOL * 4 * 4;  // 16 groups x column groups x columns x 4 lanes x 4 bytes
-    static constexpr size_t XC = (size_t)16 * NG * 8 * 4;         // 16 groups x column groups x 8 columns x int32
-    static constexpr size_t TAB = (size_t)NG * 8 * 4;             // one float per digit column
-    static constexpr size_t PB = XD + XC + TAB;
-};
-
 // ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
-// One warp per (super-block of k, activation row); lane L holds the 8 activations 8L .. 8L+7: they are k-slots
-// 8 (L % 2) .. + 7 of scale group L / 2 (a group = 16 consecutive elements of the super-block).
+// One warp per (super-block of k, row of x).
 constexpr int PREP_WARPS = 4;
 
 template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) q6k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
                                                                              uint8_t* __restrict__ image) {
-    using C = Cfg<MT>;
-    constexpr int NG = C::NG, NCOL = C::NCOL;
     asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
-    const int lane = threadIdx.x & 31;
     const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
     const int b = pair / MT, m = pair % MT;
-    if (b >= (int)(k >> 8)) {
-        return;
-    }
-    const int grp = lane >> 1, half = lane & 1;
-    uint8_t* img = image + (size_t)b * C::PB;
-    uint2* xd = reinterpret_cast<uint2*>(img);
-    int* xc = reinterpret_cast<int*>(img + C::XD);
-    float* tab = reinterpret_cast<float*>(img + C::XD + C::XC);
-    if (m == 0 && lane >= C::COLS && lane < NG * 8) {
-        tab[lane] = 0.0f;  // columns that hold no activation row
-    }
-    float xv[8];
-    if (m < rows) {
-        const float4* xp = reinterpret_cast<const float4*>(x + (int64_t)m * k + (int64_t)b * 256) + 2 * lane;
-        const float4 lo = __ldg(xp), hi = __ldg(xp + 1);
-        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
-        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            xv[i] = 0.0f;
-        }
-    }
-    float am = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        am = fmaxf(am, fabsf(xv[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-    }
-    // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
-    uint32_t e = __float_as_uint(am) & 0x7f800000u;
-    e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
-    const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));           // 2^21 / s: |X| <= 2^22
-    int X[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        X[i] = __float2int_rn(xv[i] * inv);
-    }
-#pragma unroll
-    for (int dgt = 0; dgt < 3; dgt++) {
-        uint32_t w0 = 0, w1 = 0;
-        int sum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
-            X[i] = (X[i] - d) >> 8;
-            sum += d;
-            if (i < 4) {
-                w0 |= (uint32_t)(d & 0xff) << (8 * i);
-            } else {
-                w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
-            }
-        }
-        const int col = 3 * m + dgt;
-        // lane slots 2 half and 2 half + 1 of this group's B fragment
-        xd[((((size_t)grp * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + 2 * half) / 2] = make_uint2(w0, w1);
-        // -32 * (digit sum of the group's 16 elements): the row-independent part of sum (q - 32) x, the MMA's C operand
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        if (half == 0) {
-            xc[((size_t)grp * NG + (col >> 3)) * 8 + (col & 7)] = -32 * sum;
-        }
-        if (lane == 0) {
-            tab[col] = m < rows ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
-        }
+    if (b < (int)(k >> 8)) {
+        build_image<MT>(m < rows ? x + (int64_t)m * k + (int64_t)b * 256 : nullptr, m, image + (size_t)b * Cfg<MT>::PB, threadIdx.x & 31);
     }
 }
 
@@ -175,6 +98,7 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL;
     extern __shared__ __align__(16) uint8_t smem_raw[];
+    asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
     const int KB = (int)(v.k >> 8);
     const int nslices = (KB + KS - 1) / KS;
     uint8_t* img = smem_raw;                                                         // [KS][PB]
@@ -505,11 +429,13 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         return JQ_OK;
     }
     *handled = true;
-    q6k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
-    count_launch();
-    int rc = check_launch("q6k_activation_image_kernel");
-    if (rc != JQ_OK) {
-        return rc;
+    if (x != nullptr) {  // else the image is already in `image` (written by a kernel earlier in the stream)
+        q6k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+        count_launch();
+        int rc = check_launch("q6k_activation_image_kernel");
+        if (rc != JQ_OK) {
+            return rc;
+        }
     }
     if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
     if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
@@ -540,6 +466,18 @@ int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bia
     if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
     if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
     return run<4>(v, x, rows, bias, y, s, image, handled);
+}
+
+size_t q6k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }
+
+// One row of x whose image (q6k::build_image<1> per super-block) a kernel earlier in the stream has written to `image`;
+// that kernel should execute griddepcontrol.launch_dependents so that this one can request weights meanwhile.
+int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* bias, float* y, cudaStream_t s, bool* handled) {
+    *handled = false;
+    if (v.type != JQ_TYPE_Q6_K || v.n == 0 || v.k == 0 || image == nullptr || (int64_t)16 * (v.k / 256) * 208 >= ((int64_t)1 << 31)) {
+        return JQ_OK;
+    }
+    return run<1>(v, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
 }
 
 }  // namespace jq

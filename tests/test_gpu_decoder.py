@@ -20,17 +20,29 @@ def build(cfg, seed):
     return weights, dec
 
 
-@pytest.mark.parametrize("heads,kv_heads", [(4, 4), (4, 2)])
-def test_prompt_logits_and_greedy_tokens(heads, kv_heads):
-    cfg = llama_oracle.Config(layers=2, dim=256, heads=heads, kv_heads=kv_heads, hidden=512, vocab=512, max_seq=48)
+# head_dim 64 takes the general kernels; head_dim 128 takes the fused single-token step (and, with the option off,
+# the general kernels again); 61 prompt tokens put the decoded positions across the 64-key chunk boundary
+@pytest.mark.parametrize("dim,heads,kv_heads,prompt_len,fused", [(256, 4, 4, 13, 1), (256, 4, 2, 13, 1), (512, 4, 4, 61, 1), (512, 4, 2, 13, 1),
+                                                                 (512, 4, 2, 61, 0)])
+def test_prompt_logits_and_greedy_tokens(dim, heads, kv_heads, prompt_len, fused):
+    import jitnn_b200
+    jitnn_b200.load().jq_set_option(b"decoder_fused", fused)
+    try:
+        run_prompt_and_greedy(dim, heads, kv_heads, prompt_len)
+    finally:
+        jitnn_b200.load().jq_set_option(b"decoder_fused", 1)
+
+
+def run_prompt_and_greedy(dim, heads, kv_heads, prompt_len):
+    cfg = llama_oracle.Config(layers=2, dim=dim, heads=heads, kv_heads=kv_heads, hidden=2 * dim, vocab=512, max_seq=prompt_len + 24)
     weights, dec = build(cfg, seed=heads * 10 + kv_heads)
     ref = llama_oracle.Decoder(cfg, weights)
     rng = np.random.default_rng(7)
-    prompt = rng.integers(0, cfg.vocab, 13).astype(np.int32)
+    prompt = rng.integers(0, cfg.vocab, prompt_len).astype(np.int32)
 
-    # prompt in chunks of 8 + 5 tokens on the GPU, token by token in the oracle
+    # prompt in chunks of up to 8 tokens on the GPU, token by token in the oracle
     ref_logits = np.stack([ref.forward(int(t), i) for i, t in enumerate(prompt)])
-    got = np.concatenate([dec.forward(prompt[:8], 0)[0], dec.forward(prompt[8:], 8)[0]])
+    got = np.concatenate([dec.forward(prompt[i:i + 8], i)[0] for i in range(0, prompt_len, 8)])
     scale = np.abs(ref_logits).max()
     assert np.abs(got - ref_logits).max() <= 2e-4 * scale, float(np.abs(got - ref_logits).max() / scale)
 
