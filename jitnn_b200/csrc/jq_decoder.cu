@@ -411,7 +411,6 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     __shared__ float sc[ATT_CHUNK];
     __shared__ __align__(16) float red[8][HD];
     __shared__ __align__(16) float outs[256];
-    __shared__ float ml[2];
     __shared__ int last_flag;
     pdl_enter();
     const int h = blockIdx.x, sp = blockIdx.y, splits = gridDim.y;
@@ -422,6 +421,18 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     if (k0 < keys) {
         const int cnt = keys - k0 < ATT_CHUNK ? keys - k0 : ATT_CHUNK;
         const bool has_new = pos < k0 + ATT_CHUNK;  // the new token's key and value belong to this chunk
+        // Warp w owns keys 8w .. 8w + 7 of the chunk, a lane four consecutive dimensions of each. Their cached keys and
+        // values are requested at once, before anything else is waited for.
+        float4 kreg[8], vreg[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int j = warp * 8 + u;
+            kreg[u] = vreg[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < cnt && k0 + j != pos) {
+                kreg[u] = __ldg(reinterpret_cast<const float4*>(k_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
+                vreg[u] = __ldg(reinterpret_cast<const float4*>(v_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
+            }
+        }
         if (tid < HALF) {
             const float c = cos_t[pos * HALF + tid], s = sin_t[pos * HALF + tid];
             const float a = q[h * HD + tid], b = q[h * HD + tid + HALF];
@@ -447,74 +458,60 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
             }
         }
         __syncthreads();
-        // scores: warp w takes keys 8w .. 8w + 7 of the chunk, a lane four consecutive dimensions of each
-        {
-            const float4 qv = reinterpret_cast<const float4*>(qs)[lane];
-            float dot[8];
+        // this warp's scores, its own running maximum and sum of exponentials, and its weighted sum of values
+        const float4 qv = reinterpret_cast<const float4*>(qs)[lane];
+        float sco[8], mw = -INFINITY;
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int j = warp * 8 + u;
-                dot[u] = 0.0f;
-                if (j < cnt) {
-                    const float4 kv = k0 + j == pos ? reinterpret_cast<const float4*>(knew)[lane]
-                                                    : __ldg(reinterpret_cast<const float4*>(k_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
-                    dot[u] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, qv.w * kv.w)));
-                }
+        for (int u = 0; u < 8; u++) {
+            const int j = warp * 8 + u;
+            if (k0 + j == pos) {
+                kreg[u] = reinterpret_cast<const float4*>(knew)[lane];
+                vreg[u] = reinterpret_cast<const float4*>(vnew)[lane];
             }
-#pragma unroll
-            for (int u = 0; u < 8; u++) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
-                }
-                if (lane == 0 && warp * 8 + u < cnt) {
-                    sc[warp * 8 + u] = dot[u] * scale;
-                }
-            }
-        }
-        __syncthreads();
-        if (warp == 0) {
-            const float s0 = lane < cnt ? sc[lane] : -INFINITY, s1 = lane + 32 < cnt ? sc[lane + 32] : -INFINITY;
-            float mx = fmaxf(s0, s1);
+            float dot = fmaf(qv.x, kreg[u].x, fmaf(qv.y, kreg[u].y, fmaf(qv.z, kreg[u].z, qv.w * kreg[u].w)));
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                dot += __shfl_xor_sync(0xffffffffu, dot, o);
             }
-            const float e0 = lane < cnt ? expf(s0 - mx) : 0.0f, e1 = lane + 32 < cnt ? expf(s1 - mx) : 0.0f;
-            if (lane < cnt) sc[lane] = e0;
-            if (lane + 32 < cnt) sc[lane + 32] = e1;
-            float l = e0 + e1;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                l += __shfl_xor_sync(0xffffffffu, l, o);
-            }
-            if (lane == 0) {
-                ml[0] = mx;
-                ml[1] = l;
-            }
+            sco[u] = j < cnt ? dot * scale : -INFINITY;
+            mw = fmaxf(mw, sco[u]);
         }
-        __syncthreads();
-        // weighted values: warp w takes keys w, w + 8, ..., a lane four consecutive dimensions; then the 8 warps are summed
-        {
-            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float lw = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (mw != -INFINITY) {
 #pragma unroll
             for (int u = 0; u < 8; u++) {
-                const int j = warp + 8 * u;
-                if (j < cnt) {
-                    const float4 vv = k0 + j == pos ? reinterpret_cast<const float4*>(vnew)[lane]
-                                                    : __ldg(reinterpret_cast<const float4*>(v_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
-                    const float pj = sc[j];
-                    acc.x = fmaf(pj, vv.x, acc.x); acc.y = fmaf(pj, vv.y, acc.y); acc.z = fmaf(pj, vv.z, acc.z); acc.w = fmaf(pj, vv.w, acc.w);
-                }
+                const float pj = expf(sco[u] - mw);  // 0 for the keys beyond the chunk's count
+                lw += pj;
+                acc.x = fmaf(pj, vreg[u].x, acc.x); acc.y = fmaf(pj, vreg[u].y, acc.y); acc.z = fmaf(pj, vreg[u].z, acc.z); acc.w = fmaf(pj, vreg[u].w, acc.w);
             }
-            reinterpret_cast<float4*>(red[warp])[lane] = acc;
+        }
+        reinterpret_cast<float4*>(red[warp])[lane] = acc;
+        if (lane == 0) {
+            sc[warp] = mw;
+            sc[8 + warp] = lw;
         }
         __syncthreads();
-        if (tid < HD) {
-            out[tid] = ((red[0][tid] + red[1][tid]) + (red[2][tid] + red[3][tid])) + ((red[4][tid] + red[5][tid]) + (red[6][tid] + red[7][tid]));
-        } else if (tid == HD) {
-            out[HD] = ml[0];
-            out[HD + 1] = ml[1];
+        // the 8 warps' results in warp order
+        if (tid <= HD) {
+            float M = sc[0];  // warp 0 always has a key
+#pragma unroll
+            for (int wv = 1; wv < 8; wv++) {
+                M = fmaxf(M, sc[wv]);
+            }
+            float sum = 0.0f, l = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < 8; wv++) {
+                const float wgt = expf(sc[wv] - M);  // 0 for a warp without keys
+                l = fmaf(wgt, sc[8 + wv], l);
+                sum = fmaf(wgt, red[wv][tid & 127], sum);
+            }
+            if (tid < HD) {
+                out[tid] = sum;
+            } else {
+                out[HD] = M;
+                out[HD + 1] = l;
+            }
         }
     } else if (tid == 0) {
         out[HD] = -INFINITY;  // no key of this chunk is visible yet
@@ -537,20 +534,40 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     }
     __threadfence();
     {
-        const int hh = 2 * sb + (tid >> 7), d = tid & 127;
-        const float* p = part + (int64_t)hh * stride_splits * (HD + 2);
-        float M = -INFINITY;
-        for (int s = 0; s < splits; s++) {
-            M = fmaxf(M, __ldcg(p + (int64_t)s * (HD + 2) + HD));
+        // Chunk maxima and sums first, then the weights exp(m - M), then the weighted sums with every load independent of
+        // the others (chunks without a visible key have weight zero and their partial sums are never used).
+        float* wm = red[0];  // [2 heads][splits <= 128]: m, later the weight
+        float* wl = red[2];  // [2 heads][splits]: l
+        for (int i = tid; i < 2 * splits; i += ATTF_THREADS) {
+            const float* cell = part + ((int64_t)(2 * sb + i / splits) * stride_splits + i % splits) * (HD + 2) + HD;
+            wm[(i / splits) * 128 + i % splits] = __ldcg(cell);
+            wl[(i / splits) * 128 + i % splits] = __ldcg(cell + 1);
         }
-        float L = 0.0f, acc = 0.0f;
-        for (int s = 0; s < splits; s++) {
-            const float m = __ldcg(p + (int64_t)s * (HD + 2) + HD);
-            if (m != -INFINITY) {
-                const float wgt = expf(m - M);
-                L = fmaf(wgt, __ldcg(p + (int64_t)s * (HD + 2) + HD + 1), L);
-                acc = fmaf(wgt, __ldcg(p + (int64_t)s * (HD + 2) + d), acc);
+        __syncthreads();
+        if (warp < 2) {
+            float M = -INFINITY;
+            for (int sidx = lane; sidx < splits; sidx += 32) {
+                M = fmaxf(M, wm[warp * 128 + sidx]);
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+            }
+            for (int sidx = lane; sidx < splits; sidx += 32) {
+                const float m = wm[warp * 128 + sidx];
+                wm[warp * 128 + sidx] = m == -INFINITY ? 0.0f : expf(m - M);
+            }
+        }
+        __syncthreads();
+        const int hsel = tid >> 7, d = tid & 127;
+        const float* p = part + (int64_t)(2 * sb + hsel) * stride_splits * (HD + 2) + d;
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll 4
+        for (int sidx = 0; sidx < splits; sidx++) {
+            const float wgt = wm[hsel * 128 + sidx];
+            const float val = __ldcg(p + (int64_t)sidx * (HD + 2));
+            L = fmaf(wgt, wl[hsel * 128 + sidx], L);
+            acc = fmaf(wgt, wgt != 0.0f ? val : 0.0f, acc);
         }
         outs[tid] = acc / L;
     }
