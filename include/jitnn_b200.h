@@ -168,8 +168,8 @@ JQ_API int jq_get_option(const char* name, int64_t* value);
  * cannot have that happen: a process that has already given all device memory to its own pools (the allocation
  * would fail), or a latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives
  * in a 1 MiB array that is part of the library itself, so every GPU that loads the library holds that 1 MiB
- * until the process exits. Limits: the image, (k / 256) * 848 bytes for one row, 1696 for two, 4352 for three or
- * four and 6624 for five to eight rows, must fit 1 MiB (for example k <= 40448 at eight rows); anything larger, any
+ * until the process exits. Limits: the image, (k / 256) * 896 bytes for one row, 1824 for two and 7008 for three to
+ * eight rows, must fit 1 MiB (for example k <= 38144 at eight rows); anything larger, any
  * other format and any other row count is refused with JQ_ERR_INVALID or JQ_ERR_UNSUPPORTED and a message.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call before starting any stream capture. All calls share the one array, which keeps

@@ -52,7 +52,7 @@ def test_refuses_what_it_cannot_hold():
     assert call_noalloc(w, x, None, y) == _lib.JQ_ERR_INVALID and "1 to 8" in _lib.last_error()
     q8 = Tensor.quantized("Q8_0", synth.random_valid_blocks("Q8_0", 8, 512, seed=4).numpy(), 8, 512)
     assert call_noalloc(q8, x[:1], None, y[:1]) == _lib.JQ_ERR_UNSUPPORTED and "not Q4_K" in _lib.last_error()
-    # k = 65536 with 8 rows needs 256 * 6624 bytes of image: more than the 1 MiB the library carries
+    # k = 65536 with 8 rows needs 256 * 7008 bytes of image: more than the 1 MiB the library carries
     big = Tensor.quantized("Q4_K", np.zeros(65536 // 256 * 144, np.uint8), 1, 65536)
     xb = torch.zeros(8, 65536, device="cuda")
     assert call_noalloc(big, xb, None, y[:8, :1].contiguous()) == _lib.JQ_ERR_INVALID
