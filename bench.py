@@ -40,7 +40,7 @@ BYTES_PER_WEIGHT = 144.0 / 256.0
 POOL_COPIES = 4  # distinct copies of every weight; 4 x 134 MB = 537 MB, about 4x the 126 MB L2
 METRIC = "q4k_gemv_sweep_GBps"
 # dram__bytes_read.sum + dram__bytes_write.sum of one step under ncu (profiles/gemv_q4k_i8_sweep.md), per linear
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 269903616 // 8
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 269671168 // 8
 
 
 def algorithmic_bytes(n, k, m):
@@ -510,7 +510,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
