@@ -141,6 +141,34 @@ JQ_API int jq_linear_bf16(const jq_weight* w, const uint16_t* x_bf16, int64_t m,
 JQ_API int jq_device_status(int device, int* status);
 
 /*
+ * Row-sharded linears over the GPUs of one box (one process per GPU): instead of Collective.allGather
+ * (dist/Collective.java:64-65, NCCL form dist/NcclOp.java:184-198) every rank stores its slice of y directly into every
+ * rank's copy of the full y over NVLink and raises a flag there; the rank's later work on `stream` starts after a
+ * bounded wait for all ranks' flags. (No counterpart in the reference, which never shards a linear.)
+ *
+ * jq_peer_alloc    a buffer on `device` for `payload_bytes` of gathered outputs (plus 256 bytes of flags in front, at
+ *                  jq_peer_payload_offset() the payload starts) and its 64-byte CUDA IPC handle, which the caller sends
+ *                  to the other ranks' processes by whatever channel it has.
+ * jq_peer_open     maps another rank's buffer into this process (peer access is enabled on first use); jq_peer_close
+ *                  unmaps it; jq_peer_free releases a buffer made by jq_peer_alloc, after every rank has closed it.
+ * jq_peer_gather   enqueues on `stream`: y_r[0..m, col0 .. col0 + n_slice) = slice [m, n_slice] for every rank r, where
+ *                  y_r [m, n_total] FP32 starts `payload_offset` bytes (a multiple of 16) into the payload of
+ *                  peer_buffers[r] (entry `rank` is this rank's own buffer, the others come from jq_peer_open, all in
+ *                  rank order); then the wait until the slices of all `world` (at most 8) ranks have arrived in this
+ *                  rank's y. All ranks must make the same exchanges on a buffer in the same order, and the same y area
+ *                  must not be the target of two exchanges in a row (alternate two areas, or use other buffers in
+ *                  between): a rank may run one exchange ahead of another. A wait that gives up after about half a
+ *                  second leaves status 32 + (missing rank) for jq_device_status. Works inside a captured CUDA graph.
+ */
+JQ_API int jq_peer_alloc(int device, int64_t payload_bytes, void** ptr, void* handle_out);
+JQ_API int jq_peer_open(int device, const void* handle, void** ptr);
+JQ_API int jq_peer_close(void* ptr);
+JQ_API int jq_peer_free(void* ptr);
+JQ_API int64_t jq_peer_payload_offset(void);
+JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers,
+                          int64_t payload_offset, int rank, int world, void* stream);
+
+/*
  * blocks_out[count/32*34] = Q8_0 blocks of x[count] (count % 32 == 0), following the reference's host
  * quantiser ops/Quant.java:102-118 (F.quantizeQ8): d = (float)(max|x| / 127.0) stored as fp16, q =
  * x / d rounded half away from zero using the unrounded float d, clamped to [-127, 127].

@@ -33,6 +33,12 @@ SIGNATURES = {
     "jq_linear_bf16": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
     "jq_linear_q4k_f32_noalloc": (c_int, [vp, vp, c_i64, vp, vp, vp]),
     "jq_device_status": (c_int, [c_int, ctypes.POINTER(c_int)]),
+    "jq_peer_alloc": (c_int, [c_int, c_i64, ctypes.POINTER(vp), vp]),
+    "jq_peer_open": (c_int, [c_int, vp, ctypes.POINTER(vp)]),
+    "jq_peer_close": (c_int, [vp]),
+    "jq_peer_free": (c_int, [vp]),
+    "jq_peer_payload_offset": (c_i64, []),
+    "jq_peer_gather": (c_int, [vp, c_i64, c_i64, c_i64, c_i64, ctypes.POINTER(vp), c_i64, c_int, c_int, vp]),
     "jq_quantize_q8_0": (c_int, [c_int, vp, c_i64, vp, c_int, vp]),
     "jq_decoder_create": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_float, ctypes.c_float, ctypes.POINTER(vp)]),
     "jq_decoder_destroy": (c_int, [vp]),

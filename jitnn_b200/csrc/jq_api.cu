@@ -551,7 +551,15 @@ int jq_device_status(int device, int* status) {
     }
     DeviceGuard guard(device);
     JQ_CUDA(cudaDeviceSynchronize());
-    return prefill_status(status);
+    int rc = prefill_status(status);
+    int peer = 0;
+    if (rc == JQ_OK) {
+        rc = peer_status(&peer);
+    }
+    if (rc == JQ_OK && *status == 0) {
+        *status = peer;
+    }
+    return rc;
 }
 
 int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blocks_out, int mem, void* stream) {

@@ -122,6 +122,8 @@ bool prefill_supported(const View& v);
 int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const float* bias, float* y, cudaStream_t s);
 int launch_f32_to_bf16(const float* x, uint16_t* out, int64_t count, cudaStream_t s);
 int prefill_status(int* status);
+// Same for the bounded waits of the peer gather (jq_peer.cu): 0, or 32 + the rank whose slice did not arrive.
+int peer_status(int* status);
 
 // Option "gemv_generic": non-zero routes every GEMV to the generic CUDA-core kernel (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_generic;

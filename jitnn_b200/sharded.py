@@ -10,6 +10,11 @@ shard, so the gathered result is bitwise the single-GPU result.
 ``torch.distributed`` is the plumbing (process group, NCCL or gloo); the linear itself is
 ``jq_linear_f32``. The row partition and the gather layout are plain functions so that they can be
 tested without a GPU.
+
+Two ways to complete y: ``gather_rows`` (a torch.distributed all-gather: NCCL on GPUs, gloo in the CPU
+tests) and ``PeerGather`` (the library's own exchange: every rank stores its slice straight into every
+rank's y over NVLink and waits for the others' flags, ``jq_peer_gather``; the process group only carries
+the 64-byte memory handles at set-up).
 """
 import ctypes
 
@@ -71,3 +76,78 @@ class ShardedLinear:
 
     def __call__(self, x):
         return gather_rows(self.local(x), self.n, self.group)
+
+
+class PeerGather:
+    """The gathered output y [m_max, n] of one sharded linear on every rank, filled by peer stores.
+
+    Set-up (collective over the group): every rank allocates its buffer (two y areas, used in turn), the
+    64-byte CUDA IPC handles travel through ``all_gather_object``, every rank maps the others' buffers.
+    ``gather(y_local)`` enqueues the exchange on the current stream and returns this rank's y [m, n] as a
+    torch tensor viewing the buffer; it stays valid until the next-but-one gather on this object.
+    """
+
+    def __init__(self, n, m_max, device, group=None):
+        import torch.distributed as dist
+        from . import _lib
+        self.lib = _lib.load()
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.n, self.m_max, self.device = int(n), int(m_max), int(device)
+        self.begin, self.end = row_range(self.n, self.rank, self.world)
+        self.area = (self.n * self.m_max * 4 + 255) // 256 * 256
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        _lib.check(self.lib.jq_peer_alloc(self.device, 2 * self.area, ctypes.byref(own), handle))
+        self.own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.buffers = (ctypes.c_void_p * self.world)()
+        self.opened = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.buffers[r] = self.own
+            else:
+                p = ctypes.c_void_p()
+                _lib.check(self.lib.jq_peer_open(self.device, ctypes.create_string_buffer(h, 64), ctypes.byref(p)))
+                self.buffers[r] = p.value
+                self.opened.append(p.value)
+        self.turn = 0
+        self.offset = int(self.lib.jq_peer_payload_offset())
+        dist.barrier(group=group)
+
+    def gather(self, y_local, stream=None):
+        """y_local: CUDA float32 tensor [m, rows of this rank]. Returns y [m, n] (a view of this rank's buffer)."""
+        import torch
+        from . import _lib
+        m = int(y_local.shape[0])
+        if m > self.m_max or y_local.shape[1] != self.end - self.begin or y_local.dtype != torch.float32 or not y_local.is_contiguous():
+            raise ValueError("PeerGather: slice %s does not fit rows [%d, %d) x at most %d" % (tuple(y_local.shape), self.begin, self.end, self.m_max))
+        s = torch.cuda.current_stream(y_local.device).cuda_stream if stream is None else stream
+        off = self.turn * self.area
+        _lib.check(self.lib.jq_peer_gather(y_local.data_ptr(), m, self.end - self.begin, self.n, self.begin, self.buffers, off, self.rank, self.world, s))
+        self.turn ^= 1
+        return self.view(off, m)
+
+    def view(self, off, m):
+        """This rank's y area at byte offset `off` of the payload as a torch tensor [m, n] (no copy)."""
+        import torch
+
+        class _Mem:
+            pass
+        holder = _Mem()
+        holder.__cuda_array_interface__ = {"shape": (m, self.n), "typestr": "<f4", "data": (self.own + self.offset + off, False), "version": 3}
+        return torch.as_tensor(holder, device=torch.device("cuda", self.device))
+
+    def close(self):
+        """Collective: unmaps the peers' buffers, then frees the own one once every rank has unmapped it."""
+        import torch
+        import torch.distributed as dist
+        if self.own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        for p in self.opened:
+            self.lib.jq_peer_close(p)
+        self.opened = []
+        dist.barrier(group=self.group)
+        self.lib.jq_peer_free(self.own)
+        self.own = None

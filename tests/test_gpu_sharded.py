@@ -1,5 +1,6 @@
-"""Row-sharded linear on two GPUs (one process per GPU, NCCL): the gathered result equals the
-single-GPU result bit for bit. Skipped on a machine with fewer than two GPUs."""
+"""Row-sharded linear on two GPUs (one process per GPU): the gathered result equals the single-GPU result bit for
+bit, both with the NCCL all-gather and with the library's own peer-store exchange (also replayed from a CUDA graph).
+Skipped on a machine with fewer than two GPUs."""
 import os
 import socket
 import sys
@@ -24,7 +25,9 @@ def _free_port():
 
 def _worker(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
+    import ctypes
     import torch.distributed as dist
+    import jitnn_b200
     from jitnn_b200 import Gguf, Tensor, sharded, synth
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -37,11 +40,47 @@ def _worker(rank, world, port, out_dir):
         bias = torch.randn(n, generator=g).cuda()
         lin = sharded.ShardedLinear(t, raw, n, k, device=rank, bias=bias)
         whole = Tensor.quantized(t, raw, n, k, device=rank)
+        peer = sharded.PeerGather(n, 5, device=rank)
         for m in (1, 5):
             x = torch.randn(m, k, generator=g).cuda()
             y = lin(x)
             ref = Gguf.linear(x, whole, bias)
             results["%s_%d" % (t, m)] = bool(torch.equal(y, ref)) and tuple(y.shape) == (m, n)
+            for rep in range(3):  # both y areas of the buffer, and one of them again
+                yp = peer.gather(lin.local(x))
+                results["%s_%d_peer%d" % (t, m, rep)] = bool(torch.equal(yp, ref)) and tuple(yp.shape) == (m, n)
+        peer.close()
+    # the exchange inside a captured graph: the sequence numbers live on the device, so replays stay in step
+    n, k = 4096, 4096
+    raw = synth.random_valid_blocks("Q4_K", n, k, seed=5).numpy()
+    lin = sharded.ShardedLinear("Q4_K", raw, n, k, device=rank)
+    whole = Tensor.quantized("Q4_K", raw, n, k, device=rank)
+    peer = sharded.PeerGather(n, 1, device=rank)
+    x = torch.randn(1, k, generator=torch.Generator().manual_seed(9)).cuda()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        views = [peer.gather(lin.local(x)) for _ in range(2)]  # warm-up outside the graph (allocations)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            views = [peer.gather(lin.local(x)) for _ in range(2)]
+        ref = Gguf.linear(x, whole, None)
+        for rep in range(4):
+            for v in views:
+                v.zero_()
+            stream.synchronize()
+            dist.barrier()
+            graph.replay()
+            stream.synchronize()
+            results["graph_%d" % rep] = all(bool(torch.equal(v, ref)) for v in views)
+    status = ctypes.c_int(0)
+    jitnn_b200.load().jq_device_status(rank, ctypes.byref(status))
+    results["status"] = status.value == 0
+    dist.barrier()
+    peer.close()
+    bad = [name for name, ok in results.items() if not ok]
+    if bad:
+        print("rank", rank, "failed:", bad, flush=True)
     torch.cuda.synchronize()
     np.save(os.path.join(out_dir, "ok%d.npy" % rank), np.array([all(results.values())]))
     dist.destroy_process_group()
