@@ -176,15 +176,33 @@ def run_ours(args):
         for m in BATCHES:
             ys[(n, k, m)] = torch.empty(m, n // world, device=device)
 
+    # With several ranks y [m, n] is completed on every rank after each linear: by the library's peer-store exchange
+    # (every rank writes its slice into every rank's y over NVLink, then a bounded wait for the others' flags) or, with
+    # --gather nccl, by an NCCL all-gather.
+    peers, gather_kind = {}, "none"
+    if world > 1:
+        gather_kind = args.gather
+        if gather_kind == "peer":
+            try:
+                for n, k in SHAPES:
+                    for m in BATCHES:
+                        peers[(n, k, m)] = sharded.PeerGather(n, m, device=device.index)
+            except Exception as exc:  # no CUDA IPC between these processes: every rank fails alike
+                sys.stderr.write("peer gather unavailable (%s): using the NCCL all-gather\n" % exc)
+                peers, gather_kind = {}, "nccl"
+
     def step(i):
         sp = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
         for si, (n, k) in enumerate(SHAPES):
             for mi, m in enumerate(BATCHES):
                 w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
                 y = ys[(n, k, m)]
+                if gather_kind == "peer":
+                    peers[(n, k, m)].linear(w, xs[(k, m)])  # y [m, n] complete on every rank
+                    continue
                 _lib.check(L.jq_linear_f32(w._handle(), xs[(k, m)].data_ptr(), m, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
-                if world > 1:
-                    sharded.gather_rows(y, n)  # y [m, n] complete on every rank
+                if gather_kind == "nccl":
+                    sharded.gather_rows(y, n)
 
     def barrier():
         if world > 1:
@@ -328,7 +346,8 @@ def run_ours(args):
                        "l2": "every launch reads a different copy from a pool of %d copies per shape (%.0f MB > 126 MB L2)"
                              % (POOL_COPIES, POOL_COPIES * sum(n * k for n, k in SHAPES) * BYTES_PER_WEIGHT / 1e6),
                        "launch": ("CUDA graph of %d steps, replayed" % period) if use_graph else "eager launches through the C ABI",
-                       "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + NCCL all-gather per launch" % world},
+                       "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + %s per launch" % (
+                           world, "peer-store all-gather in the GEMV epilogue (jq_linear_f32_peer)" if gather_kind == "peer" else "NCCL all-gather")},
             "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s", "frac": round(value / world / peak, 4),
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
@@ -514,6 +533,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "none"],
+                    help="N > 1: how every rank gets the whole y after each sharded linear (the library's peer-store exchange, or NCCL; none = no exchange, for diagnosis only)")
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"],
                     help="run only the prefill GEMM leg or only the 7B-shape decode leg (one GPU; for profiler captures)")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")

@@ -167,6 +167,15 @@ JQ_API int jq_peer_free(void* ptr);
 JQ_API int64_t jq_peer_payload_offset(void);
 JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers,
                           int64_t payload_offset, int rank, int world, void* stream);
+/*
+ * The sharded linear in one call: y_r[0..m, col0 .. col0 + n_w) = x W_shard^T (+ bias) for every rank r, then the wait,
+ * with w this rank's row shard (n_w rows, uploaded with jq_weight_upload_rows), x [m, k] and bias [n_w] device
+ * pointers, and the buffers as for jq_peer_gather. For Q4_K with m <= 8 the GEMV kernel itself stores into every
+ * rank's y and publishes the exchange (no slice buffer, no copy kernel); other formats and row counts run the ordinary
+ * kernels into a scratch slice followed by the copy kernel.
+ */
+JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, const float* bias, int64_t n_total, int64_t col0,
+                              void* const* peer_buffers, int64_t payload_offset, int rank, int world, void* stream);
 
 /*
  * blocks_out[count/32*34] = Q8_0 blocks of x[count] (count % 32 == 0), following the reference's host

@@ -92,25 +92,28 @@ static int staging_for(int device, size_t bytes, Staging** out) {
 struct Scratch {
     int device;
     cudaStream_t stream;
+    int slot;
     uint8_t* buf;
     size_t bytes;
 };
 static std::mutex g_scratch_mu;
 static std::vector<Scratch> g_scratch;
 
-int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out) {
+int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out) { return scratch_for_slot(s, 0, bytes, out); }
+
+int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) {
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(g_scratch_mu);
     Scratch* hit = nullptr;
     for (Scratch& sc : g_scratch) {
-        if (sc.device == dev && sc.stream == s) {
+        if (sc.device == dev && sc.stream == s && sc.slot == slot) {
             hit = &sc;
             break;
         }
     }
     if (hit == nullptr) {
-        g_scratch.push_back(Scratch{dev, s, nullptr, 0});
+        g_scratch.push_back(Scratch{dev, s, slot, nullptr, 0});
         hit = &g_scratch.back();
     }
     if (hit->bytes < bytes) {

@@ -98,7 +98,18 @@ int launch_dequantize(const View& v, float* dst, cudaStream_t s);
 int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
 // Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
-int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
+// Where a GEMV's outputs go besides (or instead of) y when the linear is sharded by rows over several GPUs: every
+// rank's copy of the full output and flag words (jq_peer.cu). world = 0: no peers.
+struct PeerOut {
+    float* y[8];         // every rank's y [m, n_total] (this rank's included)
+    uint32_t* flags[8];  // every rank's flag words
+    int world, rank;
+    int64_t n_total, col0;  // this rank's rows are columns col0 .. of y
+};
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
+                       const PeerOut* peer = nullptr);
+// Raises this rank's flag on every rank of `peer`; to be called by the last CTA of a kernel whose threads have all
+// executed __threadfence_system() after their peer stores (device code, jq_peer_device.cuh).
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 // The same GEMVs for one row of x whose activation image a kernel earlier in the stream has already written
 // (jq_q4k_image.cuh, jq_q6k_image.cuh); the Q4_K one can take a second weight with the same k in the same launch.
@@ -113,6 +124,8 @@ size_t gemv_q6k_i8_scratch_bytes(int64_t k, int rows);
 // Scratch memory of at least `bytes` on the current device, private to work enqueued on `s` (one buffer per
 // device and stream, grown on demand and kept until the library is unloaded).
 int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out);
+// A second, third ... scratch buffer of the same (device, stream), for a caller that needs one while a kernel launcher uses slot 0.
+int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out);
 
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;

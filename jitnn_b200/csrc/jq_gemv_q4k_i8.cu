@@ -32,6 +32,7 @@
 #include <mutex>
 
 #include "jq_formats.cuh"
+#include "jq_peer_device.cuh"
 #include "jq_q4k_image.cuh"
 
 namespace jq {
@@ -110,7 +111,7 @@ struct Second {
 };
 
 template <int MT, int STAGES, int NW, int OCC>
-__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const uint8_t* __restrict__ image, int rows,
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, PeerOut peer, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
                                                                   int KS, int max_tiles) {
     // Tiles 0 .. w2.first_tiles - 1 are rows of v, the tiles from w2.first_tiles on rows of the second weight w2 (same k,
@@ -415,11 +416,22 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
                 if (sl + 1 < nslices) {
                     carry[(size_t)ti * 16 * MT + o] = sum;
                 } else if (m < rows && row < n) {
-                    yo[(int64_t)m * n + row] = sum + (bias != nullptr && !second ? bias[row] : 0.0f);
+                    const float val = sum + (bias != nullptr && !second ? bias[row] : 0.0f);
+                    if (peer.world == 0) {
+                        yo[(int64_t)m * n + row] = val;
+                    } else {
+                        // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
+                        for (int r = 0; r < peer.world; r++) {
+                            peer.y[r][(int64_t)m * peer.n_total + peer.col0 + row] = val;
+                        }
+                    }
                 }
             }
             parity ^= 1;
         }
+    }
+    if (peer.world != 0) {
+        peer_publish(peer.flags, peer.rank, peer.world);  // the last CTA raises this rank's flag on every rank
     }
 }
 
@@ -437,13 +449,13 @@ int sm_count() {
 }
 
 template <int MT, int STAGES, int NW, int OCC>
-int launch(const View& v, const Second& w2, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid, int max_tiles,
-           size_t smem) {
+int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid,
+           int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX - 1024));  // the kernel also has a few static bytes
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
@@ -457,7 +469,7 @@ int launch(const View& v, const Second& w2, const uint8_t* image, int rows, cons
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, w2, image, rows, bias, y, tiles, KS, max_tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, w2, peer, image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
 }
@@ -477,7 +489,8 @@ struct Shape {
 };
 
 template <int MT>
-int run(const View& v, const Second& w2, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image,
+        bool* handled) {
     // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
     const int KB = (int)(v.k / 256);
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
@@ -526,7 +539,7 @@ int run(const View& v, const Second& w2, const float* x, int rows, const float* 
     }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
-        return launch<MT, STV, NWV, OCCV>(v, w2, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        return launch<MT, STV, NWV, OCCV>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
     }
     if constexpr (WIDE) {
         JQ_SHAPE(16, 1, 3)
@@ -554,15 +567,18 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
 // Q4_K with rows in [1, 8] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
 // gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
 // *handled = false leaves the call to another kernel.
-int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
+                       const PeerOut* peer) {
     *handled = false;
     if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
         return JQ_OK;
     }
     const Second none{nullptr, 0, nullptr, 0x7fffffff};
-    if (rows == 1) return run<1>(v, none, x, rows, bias, y, s, image, handled);
-    if (rows == 2) return run<2>(v, none, x, rows, bias, y, s, image, handled);
-    return run<8>(v, none, x, rows, bias, y, s, image, handled);
+    PeerOut local{};  // world = 0: results go to y
+    const PeerOut& po = peer != nullptr ? *peer : local;
+    if (rows == 1) return run<1>(v, none, po, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2>(v, none, po, x, rows, bias, y, s, image, handled);
+    return run<8>(v, none, po, x, rows, bias, y, s, image, handled);
 }
 
 size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }
@@ -577,7 +593,8 @@ int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* imag
         return JQ_OK;
     }
     const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
-    return run<1>(v, w2, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
+    const PeerOut local{};
+    return run<1>(v, w2, local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
 }
 
 }  // namespace jq

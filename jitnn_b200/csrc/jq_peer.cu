@@ -21,17 +21,16 @@
 #include <cstring>
 
 #include "jq_common.cuh"
+#include "jq_peer_device.cuh"
 
 namespace jq {
 
 static __device__ int g_peer_status;
 
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s);
+
 namespace {
 
-constexpr int PEER_MAX_WORLD = 8;
-constexpr int PEER_FLAG_BYTES = 256;
-constexpr int PEER_COUNTER_WORD = 16;
-constexpr int PEER_SEQ_WORD = 17;
 constexpr unsigned PEER_POLL_LIMIT = 1u << 22;  // polls of about 100 ns each: gives up after roughly half a second
 
 struct PeerTargets {
@@ -42,7 +41,6 @@ struct PeerTargets {
 // slice [m, n_slice] -> columns col0 .. of every rank's y [m, n_total]; the CTA that finishes last raises the flags.
 __global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restrict__ slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0,
                                                            PeerTargets tg, int rank, int world) {
-    __shared__ int last_flag;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t count = m * n_slice;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
@@ -52,26 +50,7 @@ __global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restri
             tg.y[r][row * n_total + col0 + col] = val;
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* counter = reinterpret_cast<int*>(tg.flags[rank] + PEER_COUNTER_WORD);
-        const int done = atomicAdd(counter, 1);
-        last_flag = done == (int)gridDim.x - 1;
-        if (last_flag) {
-            *counter = 0;
-        }
-    }
-    __syncthreads();
-    if (last_flag && (int)threadIdx.x < world) {
-        const uint32_t seq = tg.flags[rank][PEER_SEQ_WORD] + 1u;  // this exchange's number
-        __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tg.flags[threadIdx.x] + rank), "r"(seq) : "memory");
-        __syncwarp();
-        if (threadIdx.x == 0) {
-            tg.flags[rank][PEER_SEQ_WORD] = seq;
-        }
-    }
+    peer_publish(tg.flags, rank, world);
 }
 
 // Thread r waits until rank r's slice of this rank's latest exchange has arrived in this rank's y.
@@ -173,41 +152,111 @@ JQ_API int jq_peer_free(void* ptr) {
 
 JQ_API int64_t jq_peer_payload_offset(void) { return PEER_FLAG_BYTES; }
 
-JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                          int rank, int world, void* stream) {
-    if (slice == nullptr || peer_buffers == nullptr || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || m < 1 || n_slice < 0 ||
-        col0 < 0 || col0 + n_slice > n_total || payload_offset < 0 || payload_offset % 16 != 0) {
-        return fail(JQ_ERR_INVALID, "jq_peer_gather: rank %d of %d, slice [%lld, %lld] at column %lld of %lld", rank, world, (long long)m, (long long)n_slice,
-                    (long long)col0, (long long)n_total);
+static int fill_targets(void* const* peer_buffers, int64_t payload_offset, int rank, int world, PeerTargets* tg, const char* who) {
+    if (peer_buffers == nullptr || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || payload_offset < 0 || payload_offset % 16 != 0) {
+        return fail(JQ_ERR_INVALID, "%s: rank %d of %d (at most %d), payload offset %lld", who, rank, world, PEER_MAX_WORLD, (long long)payload_offset);
     }
-    PeerTargets tg;
     for (int r = 0; r < PEER_MAX_WORLD; r++) {
         uint8_t* base = r < world ? static_cast<uint8_t*>(peer_buffers[r]) : nullptr;
         if (r < world && base == nullptr) {
-            return fail(JQ_ERR_INVALID, "jq_peer_gather: the buffer of rank %d is null", r);
+            return fail(JQ_ERR_INVALID, "%s: the buffer of rank %d is null", who, r);
         }
-        tg.flags[r] = reinterpret_cast<uint32_t*>(base);
-        tg.y[r] = base != nullptr ? reinterpret_cast<float*>(base + PEER_FLAG_BYTES + payload_offset) : nullptr;
+        tg->flags[r] = reinterpret_cast<uint32_t*>(base);
+        tg->y[r] = base != nullptr ? reinterpret_cast<float*>(base + PEER_FLAG_BYTES + payload_offset) : nullptr;
     }
-    cudaStream_t s = (cudaStream_t)stream;
-    const int64_t count = m * n_slice;
-    int grid = (int)((count + 255) / 256);
-    grid = grid < 1 ? 1 : (grid > 148 ? 148 : grid);
+    return JQ_OK;
+}
+
+static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute* attr, unsigned grid, unsigned block, cudaStream_t s) {
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cfg.stream = s;
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(256);
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_scatter_kernel, slice, m, n_slice, n_total, col0, tg, rank, world));
-    cfg.gridDim = dim3(1);
-    cfg.blockDim = dim3(32);
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    return cfg;
+}
+
+static int enqueue_wait(const PeerTargets& tg, int rank, int world, cudaStream_t s) {
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = pdl_config(attr, 1, 32, s);
     JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_wait_kernel, (const uint32_t*)tg.flags[rank], world));
-    count_launch(2);
+    count_launch(1);
     return JQ_OK;
+}
+
+static int enqueue_scatter(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, const PeerTargets& tg, int rank, int world,
+                           cudaStream_t s) {
+    const int64_t count = m * n_slice;
+    int grid = (int)((count + 255) / 256);
+    grid = grid < 1 ? 1 : (grid > 148 ? 148 : grid);
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = pdl_config(attr, (unsigned)grid, 256, s);
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_scatter_kernel, slice, m, n_slice, n_total, col0, tg, rank, world));
+    count_launch(1);
+    return JQ_OK;
+}
+
+JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
+                          int rank, int world, void* stream) {
+    if (slice == nullptr || m < 1 || n_slice < 0 || col0 < 0 || col0 + n_slice > n_total) {
+        return fail(JQ_ERR_INVALID, "jq_peer_gather: slice [%lld, %lld] at column %lld of %lld", (long long)m, (long long)n_slice, (long long)col0,
+                    (long long)n_total);
+    }
+    PeerTargets tg;
+    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "jq_peer_gather");
+    if (rc == JQ_OK) rc = enqueue_scatter(slice, m, n_slice, n_total, col0, tg, rank, world, (cudaStream_t)stream);
+    if (rc == JQ_OK) rc = enqueue_wait(tg, rank, world, (cudaStream_t)stream);
+    return rc;
+}
+
+JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, const float* bias, int64_t n_total, int64_t col0, void* const* peer_buffers,
+                              int64_t payload_offset, int rank, int world, void* stream) {
+    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC || x == nullptr || m < 1 || col0 < 0 || col0 + w->n > n_total) {
+        return fail(JQ_ERR_INVALID, "jq_linear_f32_peer: not a live weight, null x, or rows [%lld, +%lld) outside %lld", (long long)col0,
+                    (long long)(w != nullptr ? w->n : 0), (long long)n_total);
+    }
+    PeerTargets tg;
+    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "jq_linear_f32_peer");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != w->device) {
+        JQ_CUDA(cudaSetDevice(w->device));
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    const View v{w->q, w->aux, w->n, w->k, w->type};
+    bool fused = false;
+    if (w->type == JQ_TYPE_Q4_K && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
+        // the GEMV kernel itself stores into every rank's y and publishes the exchange
+        PeerOut po;
+        for (int r = 0; r < PEER_MAX_WORLD; r++) {
+            po.y[r] = tg.y[r];
+            po.flags[r] = tg.flags[r];
+        }
+        po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        uint8_t* image = nullptr;
+        rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(w->k, (int)m), &image);
+        if (rc == JQ_OK) {
+            rc = launch_gemv_q4k_i8(v, x, (int)m, bias, nullptr, s, image, &fused, &po);
+        }
+    }
+    if (rc == JQ_OK && !fused) {
+        // any other format or row count: the ordinary kernels into a slice, then the scatter kernel
+        uint8_t* slice = nullptr;
+        rc = scratch_for_slot(s, 1, (size_t)m * w->n * sizeof(float), &slice);
+        if (rc == JQ_OK) rc = linear_device(w, x, m, bias, reinterpret_cast<float*>(slice), s);
+        if (rc == JQ_OK) rc = enqueue_scatter(reinterpret_cast<const float*>(slice), m, w->n, n_total, col0, tg, rank, world, s);
+    }
+    if (rc == JQ_OK) rc = enqueue_wait(tg, rank, world, s);
+    if (prev >= 0 && prev != w->device) {
+        cudaSetDevice(prev);
+    }
+    return rc;
 }
 
 }  // extern "C"

@@ -1,0 +1,44 @@
+// Device side of the peer exchange (jq_peer.cu): the epilogue a kernel runs after storing its outputs into every
+// rank's y. Flag words of a rank's buffer: [0, world) arrival flags written by the peers; word 16 a CTA counter and word
+// 17 the number of this rank's exchanges on the buffer, both private to the rank.
+#pragma once
+
+#include "jq_common.cuh"
+
+namespace jq {
+
+constexpr int PEER_MAX_WORLD = 8;
+constexpr int PEER_FLAG_BYTES = 256;
+constexpr int PEER_COUNTER_WORD = 16;
+constexpr int PEER_SEQ_WORD = 17;
+
+// Every thread of every CTA of the grid calls this once, after its last store to a peer. The CTA that arrives last
+// publishes the exchange: flags_r[rank] = number of this exchange, on every rank r. The CTA barrier orders the CTA's
+// stores before thread 0's system-wide fence, which is cumulative: one fence per CTA, not one per thread.
+__device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, int world) {
+    __shared__ int peer_last_flag;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        int* counter = reinterpret_cast<int*>(flags[rank] + PEER_COUNTER_WORD);
+        const int done = atomicAdd(counter, 1);
+        peer_last_flag = done == (int)gridDim.x - 1;
+        if (peer_last_flag) {
+            *counter = 0;
+        }
+    }
+    __syncthreads();
+    if (peer_last_flag && (int)threadIdx.x < 32) {
+        const uint32_t seq = flags[rank][PEER_SEQ_WORD] + 1u;  // this exchange's number
+        __threadfence_system();
+        if ((int)threadIdx.x < world) {
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags[threadIdx.x] + rank), "r"(seq) : "memory");
+        }
+        __syncwarp();
+        if (threadIdx.x == 0) {
+            flags[rank][PEER_SEQ_WORD] = seq;
+        }
+    }
+}
+
+}  // namespace jq

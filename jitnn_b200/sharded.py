@@ -128,6 +128,21 @@ class PeerGather:
         self.turn ^= 1
         return self.view(off, m)
 
+    def linear(self, weight, x, bias=None, stream=None):
+        """y = x W^T (+ bias) for this rank's row shard `weight` (a quantised Tensor), completed on every rank: the
+        linear and the exchange in one library call (jq_linear_f32_peer). x: CUDA float32 [m, k]."""
+        import torch
+        from . import _lib
+        m = int(x.shape[0])
+        if m > self.m_max or x.dtype != torch.float32 or not x.is_contiguous():
+            raise ValueError("PeerGather.linear: x %s, at most %d rows of float32" % (tuple(x.shape), self.m_max))
+        s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
+        off = self.turn * self.area
+        _lib.check(self.lib.jq_linear_f32_peer(weight._handle(), x.data_ptr(), m, None if bias is None else bias.data_ptr(), self.n, self.begin,
+                                               self.buffers, off, self.rank, self.world, s))
+        self.turn ^= 1
+        return self.view(off, m)
+
     def view(self, off, m):
         """This rank's y area at byte offset `off` of the payload as a torch tensor [m, n] (no copy)."""
         import torch

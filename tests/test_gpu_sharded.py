@@ -49,6 +49,8 @@ def _worker(rank, world, port, out_dir):
             for rep in range(3):  # both y areas of the buffer, and one of them again
                 yp = peer.gather(lin.local(x))
                 results["%s_%d_peer%d" % (t, m, rep)] = bool(torch.equal(yp, ref)) and tuple(yp.shape) == (m, n)
+                yl = peer.linear(lin.weight, x, lin.bias)  # linear and exchange in one call (fused epilogue for Q4_K)
+                results["%s_%d_peerlin%d" % (t, m, rep)] = bool(torch.equal(yl, ref)) and tuple(yl.shape) == (m, n)
         peer.close()
     # the exchange inside a captured graph: the sequence numbers live on the device, so replays stay in step
     n, k = 4096, 4096
@@ -63,7 +65,7 @@ def _worker(rank, world, port, out_dir):
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            views = [peer.gather(lin.local(x)) for _ in range(2)]
+            views = [peer.linear(lin.weight, x) for _ in range(2)]
         ref = Gguf.linear(x, whole, None)
         for rep in range(4):
             for v in views:
