@@ -108,8 +108,6 @@ struct PeerOut {
 };
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
                        const PeerOut* peer = nullptr);
-// Raises this rank's flag on every rank of `peer`; to be called by the last CTA of a kernel whose threads have all
-// executed __threadfence_system() after their peer stores (device code, jq_peer_device.cuh).
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 // The same GEMVs for one row of x whose activation image a kernel earlier in the stream has already written
 // (jq_q4k_image.cuh, jq_q6k_image.cuh); the Q4_K one can take a second weight with the same k in the same launch.
@@ -120,6 +118,9 @@ int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* 
 // The same for Q6_K, rows <= 4.
 int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
 size_t gemv_q6k_i8_scratch_bytes(int64_t k, int rows);
+// The same for Q8_0, Q4_0 and Q4_1 (jq_gemv_blk32_i8.cu): rows <= 2, k a multiple of 256.
+int launch_gemv_blk32_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
+size_t gemv_blk32_i8_scratch_bytes(int type, int64_t k, int rows);
 
 // Scratch memory of at least `bytes` on the current device, private to work enqueued on `s` (one buffer per
 // device and stream, grown on demand and kept until the library is unloaded).

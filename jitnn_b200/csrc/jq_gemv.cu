@@ -116,6 +116,20 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
             return rc;
         }
     }
+    if (rows <= 2 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+        const size_t need = gemv_blk32_i8_scratch_bytes(v.type, v.k, rows);  // 0 unless Q8_0, Q4_0, Q4_1 with k a multiple of 256
+        if (need > 0) {
+            bool handled = false;
+            uint8_t* image = nullptr;
+            int rc = scratch_for(s, need, &image);
+            if (rc == JQ_OK) {
+                rc = launch_gemv_blk32_i8(v, x, rows, bias, y, s, image, &handled);
+            }
+            if (rc != JQ_OK || handled) {
+                return rc;
+            }
+        }
+    }
     switch (v.type) {
         case JQ_TYPE_Q8_0: return by_rows<JQ_TYPE_Q8_0>(v, x, rows, bias, y, s);
         case JQ_TYPE_Q4_0: return by_rows<JQ_TYPE_Q4_0>(v, x, rows, bias, y, s);
