@@ -179,9 +179,12 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
         }
         return rc;
     }
-    // Q4_K's integer tensor-core kernel takes up to 8 activation rows per pass, Q6_K's 4, the generic kernel 16.
+    // The integer tensor-core kernel of Q4_K and Q5_K takes up to 8 activation rows per pass, Q6_K's 4, the generic kernel 16.
     const bool tc = g_opt_gemv_generic.load() == 0;
-    const int64_t group = (tc && w->type == JQ_TYPE_Q4_K) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : 16);
+    // Q8_0, Q4_0 and Q4_1 (k a multiple of 256) go two rows at a time through their tensor-core kernel: re-reading the weights
+    // (mostly from L2) per pair of rows is far cheaper than the generic kernel's arithmetic.
+    const bool blk32 = tc && gemv_blk32_i8_scratch_bytes(w->type, w->k, 2) > 0;
+    const int64_t group = (tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16));
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);

@@ -92,7 +92,7 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
     if (v.n == 0) {
         return JQ_OK;
     }
-    if (v.type == JQ_TYPE_Q4_K && rows <= 8 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+    if ((v.type == JQ_TYPE_Q4_K || v.type == JQ_TYPE_Q5_K) && rows <= 8 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
         bool handled = false;
         const size_t need = gemv_q4k_i8_scratch_bytes(v.k, rows);
         uint8_t* image = nullptr;

@@ -42,8 +42,17 @@ using q4k::build_image;
 
 namespace {
 
-constexpr int SLOT_BYTES = 16 * 144;        // one super-block of 16 rows: 16 x 128 bytes of nibbles, then 16 headers
+// One super-block of 16 rows in a ring slot: 16 x 128 bytes of nibbles, then the 16 headers, then (Q5_K) 16 x 32 bytes of
+// fifth bits. The kernel is written for Q4_K; Q5_K (template flag Q5) is the same format with one more bit per quant.
 constexpr int SLOT_HEADERS = 16 * 128;
+constexpr int SLOT_QH = 16 * 144;
+template <bool Q5>
+struct Blk {
+    static constexpr int BYTES = Q5 ? 176 : 144;           // bytes per super-block and row
+    static constexpr int SLOT = 16 * BYTES;
+    static constexpr int CPR = BYTES / 16;                 // 16-byte chunks per row
+    static constexpr int PER_LANE = (16 * CPR + 31) / 32;  // the last one only by lanes 0-15
+};
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
@@ -110,7 +119,7 @@ struct Second {
     int first_tiles;  // tiles of the first weight
 };
 
-template <int MT, int STAGES, int NW, int OCC>
+template <int MT, int STAGES, int NW, int OCC, bool Q5>
 __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, PeerOut peer, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
                                                                   int KS, int max_tiles) {
@@ -121,6 +130,8 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
     constexpr int THREADS = NW * 32;
+    using B = Blk<Q5>;
+    constexpr int SLOT_BYTES = B::SLOT;
     constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
@@ -133,23 +144,26 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     float* carry = red + 2 * NW * 16 * MT;                                           // [max_tiles][16][MT], only if nslices > 1
     uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) + (size_t)warp * RING_BYTES;
     const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
-    const int64_t row_bytes = (int64_t)KB * 144;
+    const int64_t row_bytes = (int64_t)KB * B::BYTES;
 
-    // ---- weight stream: chunk c = lane + 32 i of the 144 chunks (16 rows x 9) of a super-block -------------
+    // ---- weight stream: chunk c = lane + 32 i of the 144 (Q5_K: 176) chunks (16 rows x 9 or 11) of a super-block ------
     // Slot layout: row r's 128 bytes of nibbles at r * 128 with its four 32-byte segments permuted by r & 3
     // (segment p sits at position p ^ (r & 3)), the 16 headers behind them.
-    uint32_t src_d[5], dst_off[5];  // source offsets relative to the lane's first chunk
+    constexpr int NI = B::PER_LANE;
+    uint32_t src_d[NI], dst_off[NI];  // source offsets relative to the lane's first chunk
     uint32_t src0 = 0;
 #pragma unroll
-    for (int i = 0; i < 5; i++) {
-        const int c = lane + 32 * i, r = c / 9, ch = c % 9;
+    for (int i = 0; i < NI; i++) {
+        const int c = lane + 32 * i, r = c / B::CPR, ch = c % B::CPR;
         const uint32_t so = (uint32_t)(r * (int)row_bytes + ch * 16);
         if (i == 0) {
             src0 = so;
         }
         src_d[i] = so - src0;
+        const int first_q = Q5 ? 3 : 1;  // chunk 0: header; Q5_K chunks 1, 2: fifth bits; then the 8 chunks of nibbles
         dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
-                             : (uint32_t)(r * 128 + ((((ch - 1) >> 1) ^ (r & 3)) << 5) + ((ch - 1) & 1) * 16);
+                             : (ch < first_q ? (uint32_t)(SLOT_QH + r * 32 + (ch - 1) * 16)
+                                             : (uint32_t)(r * 128 + ((((ch - first_q) >> 1) ^ (r & 3)) << 5) + ((ch - first_q) & 1) * 16));
     }
     const int low16 = lane < 16;
     // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + NW i.
@@ -161,7 +175,7 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     auto lane_ptr = [&](int ti, int sl) {
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
         const uint8_t* base = tile < w2.first_tiles ? v.q + (int64_t)tile * 16 * row_bytes : w2.q + (int64_t)(tile - w2.first_tiles) * 16 * row_bytes;
-        return base + (uint32_t)(sl * KS + warp) * 144u + src0;
+        return base + (uint32_t)(sl * KS + warp) * (uint32_t)B::BYTES + src0;
     };
     const uint8_t* gp = lane_ptr(0, 0);
     int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
@@ -172,11 +186,11 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             iss_left--;
             const uint32_t slot = ring_s + iss_slot;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
+            for (int i = 0; i < NI - 1; i++) {
                 cp_async16(slot + dst_off[i], gp + src_d[i]);
             }
-            cp_async16_if(slot + dst_off[4], gp + src_d[4], low16);
-            gp += NW * 144;
+            cp_async16_if(slot + dst_off[NI - 1], gp + src_d[NI - 1], low16);
+            gp += NW * B::BYTES;
             if (++iss_j == iss_nb) {
                 iss_j = 0;
                 if (++iss_ti == my_tiles) {
@@ -235,7 +249,13 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
         const uint32_t mn1 = mins_low ? (h1.z & 0x3f3f3f3fu) : and_or(h1.z >> 2, 0x30303030u, (h1.w >> 4) & 0x0f0f0f0fu);
         // Packed layouts keep the high nibbles in place (one AND, no shift): the odd sub-blocks' products come out 16 times
         // too large, are summed apart from the even ones' and meet them as 16 even + odd; the column weights carry the 1 / 16.
-        constexpr bool SPLIT = !C::DIGIT_MAJOR;
+        constexpr bool SPLIT = !C::DIGIT_MAJOR && !Q5;
+        // Q5_K: the fifth bits of this lane's elements 8t .. 8t+7 of every sub-block, rows g and g + 8 (bit `sub` of each byte)
+        uint2 qh0 = make_uint2(0u, 0u), qh1 = make_uint2(0u, 0u);
+        if constexpr (Q5) {
+            qh0 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + g * 32 + 8 * t);
+            qh1 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + (g + 8) * 32 + 8 * t);
+        }
         int I[NG][4], IO[SPLIT ? NG : 1][4];
 #pragma unroll
         for (int i = 0; i < NG; i++) {
@@ -259,10 +279,17 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             for (int hf = 0; hf < 2; hf++) {
                 const int sub = 2 * j + hf;
                 const bool keep = SPLIT && hf == 1;  // high nibbles stay where they are
-                const uint32_t a0 = keep ? wa.x & 0xf0f0f0f0u : (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
-                const uint32_t a2 = keep ? wa.y & 0xf0f0f0f0u : (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
-                const uint32_t a1 = keep ? wb.x & 0xf0f0f0f0u : (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
-                const uint32_t a3 = keep ? wb.y & 0xf0f0f0f0u : (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
+                uint32_t a0 = keep ? wa.x & 0xf0f0f0f0u : (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
+                uint32_t a2 = keep ? wa.y & 0xf0f0f0f0u : (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
+                uint32_t a1 = keep ? wb.x & 0xf0f0f0f0u : (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
+                uint32_t a3 = keep ? wb.y & 0xf0f0f0f0u : (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
+                if constexpr (Q5) {
+                    auto fifth = [&](uint32_t hw) { return sub < 4 ? hw << (4 - sub) : hw >> (sub - 4); };  // bit `sub` -> bit 4
+                    a0 = and_or(fifth(qh0.x), 0x10101010u, a0);
+                    a2 = and_or(fifth(qh0.y), 0x10101010u, a2);
+                    a1 = and_or(fifth(qh1.x), 0x10101010u, a1);
+                    a3 = and_or(fifth(qh1.y), 0x10101010u, a3);
+                }
                 const int s0 = (int)__byte_perm(sub < 4 ? sc0a : sc0b, 0u, 0x4440u + (sub & 3));
                 const int s1 = (int)__byte_perm(sub < 4 ? sc1a : sc1b, 0u, 0x4440u + (sub & 3));
 #pragma unroll
@@ -448,14 +475,14 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT, int STAGES, int NW, int OCC>
+template <int MT, int STAGES, int NW, int OCC, bool Q5>
 int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid,
            int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX - 1024));  // the kernel also has a few static bytes
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX - 1024));  // the kernel also has a few static bytes
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
@@ -469,16 +496,16 @@ int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC>, v, w2, peer, image, rows, bias, y, tiles, KS, max_tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5>, v, w2, peer, image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
 }
 
 // Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
-template <int MT>
+template <int MT, bool Q5>
 size_t smem_bytes(int nw, int KS, int stages, bool sliced, int max_tiles) {
     return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * nw * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
-           (size_t)nw * stages * SLOT_BYTES;
+           (size_t)nw * stages * Blk<Q5>::SLOT;
 }
 
 // A launch shape: warps per CTA, CTAs per SM, ring stages. KS (the slice length) is a function of MT and k only, so
@@ -488,7 +515,7 @@ struct Shape {
     int nw, occ, stages;
 };
 
-template <int MT>
+template <int MT, bool Q5>
 int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image,
         bool* handled) {
     // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
@@ -501,14 +528,14 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     Shape sh{0, 0, 0};
     int KS = KB;
     for (int c = 0; c < 3 && sh.nw == 0; c++) {
-        if (smem_bytes<MT>(unsliced[c].nw, KB, unsliced[c].stages, false, 0) <= SMEM_MAX / unsliced[c].occ - 1024) {
+        if (smem_bytes<MT, Q5>(unsliced[c].nw, KB, unsliced[c].stages, false, 0) <= SMEM_MAX / unsliced[c].occ - 1024) {
             sh = unsliced[c];
         }
     }
     if (sh.nw == 0) {
         for (int c = 0; c < 2 && sh.nw == 0; c++) {
             const size_t room = SMEM_MAX / sliced[c].occ - 1024 - 8 * 1024;  // 8 KB set aside for the carried sums
-            const size_t rest = smem_bytes<MT>(sliced[c].nw, 0, sliced[c].stages, false, 0);
+            const size_t rest = smem_bytes<MT, Q5>(sliced[c].nw, 0, sliced[c].stages, false, 0);
             const int ks = rest < room ? (int)((room - rest) / Cfg<MT>::PB) / sliced[c].nw * sliced[c].nw : 0;
             if (ks >= sliced[c].nw) {
                 sh = sliced[c];
@@ -523,7 +550,7 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     const int grid = tiles < sm_count() * sh.occ ? tiles : sm_count() * sh.occ;
     const int max_tiles = (tiles + grid - 1) / grid;
     const bool is_sliced = KS < KB;
-    const size_t smem = smem_bytes<MT>(sh.nw, KS, sh.stages, is_sliced, max_tiles);
+    const size_t smem = smem_bytes<MT, Q5>(sh.nw, KS, sh.stages, is_sliced, max_tiles);
     if (smem > SMEM_MAX / sh.occ - 1024) {
         *handled = false;  // more tiles per CTA than the carried sums have room for
         return JQ_OK;
@@ -539,7 +566,7 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
-        return launch<MT, STV, NWV, OCCV>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        return launch<MT, STV, NWV, OCCV, Q5>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
     }
     if constexpr (WIDE) {
         JQ_SHAPE(16, 1, 3)
@@ -564,21 +591,27 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
     return (size_t)(k / 256) * pb;
 }
 
-// Q4_K with rows in [1, 8] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
+// Q4_K or Q5_K with rows in [1, 8] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
 // gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
 // *handled = false leaves the call to another kernel.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
                        const PeerOut* peer) {
     *handled = false;
-    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31)) {
+    if ((v.type != JQ_TYPE_Q4_K && v.type != JQ_TYPE_Q5_K) || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr ||
+        (int64_t)16 * (v.k / 256) * 176 >= ((int64_t)1 << 31)) {
         return JQ_OK;
     }
     const Second none{nullptr, 0, nullptr, 0x7fffffff};
     PeerOut local{};  // world = 0: results go to y
     const PeerOut& po = peer != nullptr ? *peer : local;
-    if (rows == 1) return run<1>(v, none, po, x, rows, bias, y, s, image, handled);
-    if (rows == 2) return run<2>(v, none, po, x, rows, bias, y, s, image, handled);
-    return run<8>(v, none, po, x, rows, bias, y, s, image, handled);
+    if (v.type == JQ_TYPE_Q5_K) {
+        if (rows == 1) return run<1, true>(v, none, po, x, rows, bias, y, s, image, handled);
+        if (rows == 2) return run<2, true>(v, none, po, x, rows, bias, y, s, image, handled);
+        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled);
+    }
+    if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled);
+    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled);
 }
 
 size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }
@@ -594,7 +627,7 @@ int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* imag
     }
     const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
     const PeerOut local{};
-    return run<1>(v, w2, local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
+    return run<1, false>(v, w2, local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
 }
 
 }  // namespace jq
