@@ -162,9 +162,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     L = jitnn_b200.load()
 
-    if args.leg in ("prefill", "decode"):
+    if args.leg in ("prefill", "decode", "formats"):
         # one leg alone, for profiler captures: no sweep, a short line of its own
-        out = prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else decode_leg(torch, device, args.decode_shape)
+        out = (prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else
+               formats_leg(torch, device, L, _lib) if args.leg == "formats" else decode_leg(torch, device, args.decode_shape))
         print(json.dumps({"leg": args.leg, "result": out}), flush=True)
         return
 
@@ -326,6 +327,7 @@ def run_ours(args):
                "ms_per_step": round(dt * 1e3, 4)}
 
     prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
+    formats = formats_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
     decode = None
     if rank == 0 and world == 1 and not args.only and not args.no_decode:
         for copies in pools:
@@ -352,7 +354,7 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "formats": formats, "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -401,6 +403,61 @@ def prefill_leg(torch, device, L, _lib):
         tf = 2.0 * PREFILL_M * n * k / us / 1e6
         out["shapes"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "TFLOPs": round(tf, 1), "frac": round(tf / peak, 4)}
         w.release()
+    return out
+
+
+FORMAT_CASES = [("Q8_0", 4096, 4096), ("Q8_0", 32000, 4096), ("Q4_0", 32000, 4096), ("Q4_1", 32000, 4096), ("Q5_K", 32000, 4096),
+                ("Q6_K", 4096, 11008), ("Q6_K", 32000, 4096)]
+FORMAT_BPW = {"Q8_0": 34 / 32, "Q4_0": 18 / 32, "Q4_1": 20 / 32, "Q4_K": 144 / 256, "Q5_K": 176 / 256, "Q6_K": 210 / 256}
+
+
+def formats_leg(torch, device, L, _lib):
+    """The decode GEMV (M = 1) of the other formats of the path: BASELINE.json configs[0] (Q8_0, 4096x4096, weights from
+    the reference's host quantiser as restated in jq_quantize_q8_0) and one large layer per format. Four copies of every
+    weight in rotation (so that no launch finds its weight in L2), replayed from a CUDA graph; GB/s over the algorithmic
+    bytes N K bytes-per-weight + 4 K + 4 N against the measured HBM copy peak."""
+    import jitnn_b200
+    from jitnn_b200 import Tensor, synth
+    peak, which = measured_peaks()
+    out = {"m": 1, "peak_GBps": peak, "peak_source": "of " + which, "cases": {}}
+    side = torch.cuda.Stream(device)
+    for t, n, k in FORMAT_CASES:
+        g = torch.Generator(device=device).manual_seed(n + 3 * k + len(t))
+        ws = []
+        for c in range(POOL_COPIES):
+            wf = torch.randn(n, k, generator=g, device=device) * 0.02
+            raw = (jitnn_b200.Quant.quantizeQ8Blocks(wf, device.index) if t == "Q8_0" else synth.QUANTIZERS[t](wf)).cpu().numpy()
+            del wf
+            ws.append(Tensor.quantized(t, raw, n, k, device=device.index))
+        x = torch.randn(1, k, generator=g, device=device)
+        y = torch.empty(1, n, device=device)
+        with torch.cuda.stream(side):
+            sp = ctypes.c_void_p(side.cuda_stream)
+
+            def rot():
+                for w in ws:
+                    _lib.check(L.jq_linear_f32(w._handle(), x.data_ptr(), 1, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
+            rot()
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                rot()
+            graph.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(device)
+            reps = 25
+            a.record(side)
+            for _ in range(reps):
+                graph.replay()
+            b.record(side)
+            torch.cuda.synchronize(device)
+        us = a.elapsed_time(b) * 1e3 / (reps * POOL_COPIES)
+        nbytes = n * k * FORMAT_BPW[t] + 4 * k + 4 * n
+        gbps = nbytes / us / 1e3
+        out["cases"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "GBps": round(gbps, 1), "frac": round(gbps / peak, 4)}
+        del graph
+        for w in ws:
+            w.release()
     return out
 
 
@@ -535,7 +592,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "none"],
                     help="N > 1: how every rank gets the whole y after each sharded linear (the library's peer-store exchange, or NCCL; none = no exchange, for diagnosis only)")
-    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode"],
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode", "formats"],
                     help="run only the prefill GEMM leg or only the 7B-shape decode leg (one GPU; for profiler captures)")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
     ap.add_argument("--decode-shape", default=None, metavar="LAYERS,PROMPT,GEN",

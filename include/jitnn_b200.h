@@ -242,6 +242,34 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table);
 JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
                        void* stream);
 
+/*
+ * GGUF file -> device weights (the reference's jitnn-gguf/.../GgufFile.java:100-175,329-418, whose GgufFile.tensor(name)
+ * hands a tensor's block bytes to Tensor.persistent): the file is mapped read-only, header, metadata and tensor table are
+ * parsed with every access bounds-checked, and a tensor's blocks go to the GPU straight from the mapping. GGUF versions 2
+ * and 3, little-endian. Hostile input is an error (JQ_ERR_INVALID with a message naming the file), never a read past
+ * the mapping: wrong magic, truncation, dimensions or offsets beyond 2^63, sizes that overflow, data outside the file or
+ * off the general.alignment grid, arrays nested more than 8 deep (GgufFileTest.java:115-155).
+ *
+ * jq_gguf_tensor       name (valid until close), ggml type id, dimensions outermost first (dims[8], unused = 1), absolute
+ *                      file offset and byte size (-1 for a type id whose block geometry is unknown) of tensor `index`.
+ * jq_gguf_tensor_data  pointer to the tensor's bytes inside the mapping (valid until close).
+ * jq_gguf_meta_*       metadata by key: value type (GGUF ids 0..12; arrays report length and element type), numbers as
+ *                      double and exact int64, strings as pointer + length into the mapping (not NUL-terminated).
+ * jq_gguf_upload       rows [row_begin, row_end) (row_end -1: all) of the 2-D tensor `index` as a jq_weight on `device`.
+ */
+typedef struct jq_gguf jq_gguf;
+JQ_API int jq_gguf_open(const char* path, jq_gguf** out);
+JQ_API int jq_gguf_close(jq_gguf* f);
+JQ_API int jq_gguf_info(const jq_gguf* f, int* version, int64_t* alignment, int64_t* data_offset, int64_t* n_tensors, int64_t* n_meta);
+JQ_API int jq_gguf_tensor(const jq_gguf* f, int64_t index, const char** name, int* ggml_type, int* n_dims, int64_t* dims, int64_t* offset,
+                          int64_t* nbytes);
+JQ_API int jq_gguf_find_tensor(const jq_gguf* f, const char* name, int64_t* index);
+JQ_API int jq_gguf_tensor_data(const jq_gguf* f, int64_t index, const void** data);
+JQ_API int jq_gguf_meta_find(const jq_gguf* f, const char* key, int* value_type, int64_t* array_len, int* elem_type);
+JQ_API int jq_gguf_meta_number(const jq_gguf* f, const char* key, double* value, int64_t* integer);
+JQ_API int jq_gguf_meta_string(const jq_gguf* f, const char* key, const char** bytes, int64_t* length);
+JQ_API int jq_gguf_upload(const jq_gguf* f, int64_t index, int device, int64_t row_begin, int64_t row_end, jq_weight** out);
+
 /* Pinned host memory for activations and results (faster and truly asynchronous copies). */
 JQ_API int jq_host_alloc(void** ptr, int64_t nbytes);
 JQ_API int jq_host_free(void* ptr);

@@ -49,6 +49,17 @@ SIGNATURES = {
     "jq_decoder_forward": (c_int, [vp, vp, c_int, c_int, vp, vp, vp]),
     "jq_set_option": (c_int, [ctypes.c_char_p, c_i64]),
     "jq_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_i64)]),
+    "jq_gguf_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(vp)]),
+    "jq_gguf_close": (c_int, [vp]),
+    "jq_gguf_info": (c_int, [vp, ctypes.POINTER(c_int), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]),
+    "jq_gguf_tensor": (c_int, [vp, c_i64, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_i64),
+                               ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]),
+    "jq_gguf_find_tensor": (c_int, [vp, ctypes.c_char_p, ctypes.POINTER(c_i64)]),
+    "jq_gguf_tensor_data": (c_int, [vp, c_i64, ctypes.POINTER(vp)]),
+    "jq_gguf_meta_find": (c_int, [vp, ctypes.c_char_p, ctypes.POINTER(c_int), ctypes.POINTER(c_i64), ctypes.POINTER(c_int)]),
+    "jq_gguf_meta_number": (c_int, [vp, ctypes.c_char_p, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(c_i64)]),
+    "jq_gguf_meta_string": (c_int, [vp, ctypes.c_char_p, ctypes.POINTER(vp), ctypes.POINTER(c_i64)]),
+    "jq_gguf_upload": (c_int, [vp, c_i64, c_int, c_i64, c_i64, ctypes.POINTER(vp)]),
     "jq_host_alloc": (c_int, [ctypes.POINTER(vp), c_i64]),
     "jq_host_free": (c_int, [vp]),
     "jq_launch_count": (c_i64, []),
