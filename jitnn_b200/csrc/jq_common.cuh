@@ -105,6 +105,7 @@ struct PeerOut {
     uint32_t* flags[8];  // every rank's flag words
     int world, rank;
     int64_t n_total, col0;  // this rank's rows are columns col0 .. of y
+    const PeerOut* table;   // host side only: where a copy of this struct lives in device memory
 };
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
                        const PeerOut* peer = nullptr);

@@ -119,8 +119,10 @@ struct Second {
     int first_tiles;  // tiles of the first weight
 };
 
-template <int MT, int STAGES, int NW, int OCC, bool Q5>
-__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, PeerOut peer, const uint8_t* __restrict__ image, int rows,
+// PEER: the outputs go into every rank's y of a row-sharded linear (jq_peer.cu) instead of y. A template flag, not a
+// run-time branch: the mere presence of the peer stores in the epilogue cost the ordinary kernel a fifth of its speed.
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const PeerOut* __restrict__ peerp, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
                                                                   int KS, int max_tiles) {
     // Tiles 0 .. w2.first_tiles - 1 are rows of v, the tiles from w2.first_tiles on rows of the second weight w2 (same k,
@@ -444,12 +446,12 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
                     carry[(size_t)ti * 16 * MT + o] = sum;
                 } else if (m < rows && row < n) {
                     const float val = sum + (bias != nullptr && !second ? bias[row] : 0.0f);
-                    if (peer.world == 0) {
+                    if constexpr (!PEER) {
                         yo[(int64_t)m * n + row] = val;
                     } else {
                         // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
-                        for (int r = 0; r < peer.world; r++) {
-                            peer.y[r][(int64_t)m * peer.n_total + peer.col0 + row] = val;
+                        for (int r = 0; r < peerp->world; r++) {
+                            peerp->y[r][(int64_t)m * peerp->n_total + peerp->col0 + row] = val;
                         }
                     }
                 }
@@ -457,8 +459,8 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             parity ^= 1;
         }
     }
-    if (peer.world != 0) {
-        peer_publish(peer.flags, peer.rank, peer.world);  // the last CTA raises this rank's flag on every rank
+    if constexpr (PEER) {
+        peer_publish(peerp->flags, peerp->rank, peerp->world, reinterpret_cast<int*>(red));  // the last CTA raises this rank's flag on every rank
     }
 }
 
@@ -475,14 +477,14 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT, int STAGES, int NW, int OCC, bool Q5>
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
 int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid,
            int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX - 1024));  // the kernel also has a few static bytes
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
@@ -496,7 +498,7 @@ int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5>, v, w2, peer, image, rows, bias, y, tiles, KS, max_tiles));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, v, w2, (const PeerOut*)(PEER ? peer.table : nullptr), image, rows, bias, y, tiles, KS, max_tiles));
     count_launch();
     return JQ_OK;
 }
@@ -523,7 +525,7 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
     // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
     constexpr bool WIDE = MT > 2;
-    const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 2}, Shape{8, 2, 2}};
+    const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
     const Shape sliced[2] = {WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
     Shape sh{0, 0, 0};
     int KS = KB;
@@ -566,7 +568,10 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
-        return launch<MT, STV, NWV, OCCV, Q5>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        if (peer.world != 0) {                                                                              \
+            return launch<MT, STV, NWV, OCCV, Q5, true>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        }                                                                                                   \
+        return launch<MT, STV, NWV, OCCV, Q5, false>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
     }
     if constexpr (WIDE) {
         JQ_SHAPE(16, 1, 3)

@@ -9,9 +9,10 @@
 // The reference gathers with Collective.allGather (dist/Collective.java:64-65, NCCL form dist/NcclOp.java:184-198); for
 // the 4 KB - 128 KB slices of a decode step that call costs more than the GEMV it follows.
 //
-// A peer buffer is one cudaMalloc'd allocation: 256 bytes of flags (uint32 [world] arrival flags written by the peers;
+// A peer buffer is one cudaMalloc'd allocation: 1024 bytes of flags (uint32 [world] arrival flags written by the peers;
 // words 16 and 17, never written by peers: a CTA counter and the number of exchanges this rank has made on the
-// buffer), then the payload. A flag carries the number of the exchange it announces. The number lives in device
+// buffer; from byte 128 on up to four copies of the target table PeerOut that the fused GEMV epilogue reads), then the
+// payload. A flag carries the number of the exchange it announces. The number lives in device
 // memory and grows by one per exchange, so a captured CUDA graph can be replayed; all ranks make the same exchanges
 // on a buffer in the same order, which keeps their numbers in step. A rank can run one exchange ahead of another:
 // a payload area must not be the target of two consecutive exchanges (use two areas in turn, or other buffers in
@@ -19,6 +20,8 @@
 // No load ever targets a peer's memory, nothing here uses multicast, and the only wait is bounded: when it gives up
 // it records status 32 + (rank it waited for), readable through jq_device_status, and the kernel returns.
 #include <cstring>
+#include <map>
+#include <mutex>
 
 #include "jq_common.cuh"
 #include "jq_peer_device.cuh"
@@ -50,7 +53,16 @@ __global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restri
             tg.y[r][row * n_total + col0 + col] = val;
         }
     }
-    peer_publish(tg.flags, rank, world);
+    __shared__ int last_word;
+    peer_publish(tg.flags, rank, world, &last_word);
+}
+
+// Writes a target table into this rank's flag area (one thread).
+__global__ void peer_table_kernel(PeerOut table, PeerOut* dst) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        *dst = table;
+    }
 }
 
 // Thread r waits until rank r's slice of this rank's latest exchange has arrived in this rank's y.
@@ -88,6 +100,8 @@ using namespace jq;
 
 extern "C" {
 
+static void forget_tables(const void* buffer);
+
 JQ_API int jq_peer_alloc(int device, int64_t payload_bytes, void** ptr, void* handle_out) {
     if (ptr == nullptr || handle_out == nullptr || payload_bytes < 0) {
         return fail(JQ_ERR_INVALID, "jq_peer_alloc: null result pointer or negative size");
@@ -108,6 +122,7 @@ JQ_API int jq_peer_alloc(int device, int64_t payload_bytes, void** ptr, void* ha
         return e == cudaErrorMemoryAllocation ? fail(JQ_ERR_OOM, "jq_peer_alloc: %lld bytes on device %d", (long long)payload_bytes, device)
                                               : cuda_fail(e, "jq_peer_alloc");
     }
+    forget_tables(p);
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
     memcpy(handle_out, &h, sizeof(h));
     *ptr = p;
@@ -146,6 +161,7 @@ JQ_API int jq_peer_free(void* ptr) {
     if (ptr == nullptr) {
         return JQ_OK;
     }
+    forget_tables(ptr);
     cudaError_t e = cudaFree(ptr);
     return e == cudaSuccess ? JQ_OK : cuda_fail(e, "jq_peer_free");
 }
@@ -177,6 +193,43 @@ static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute* attr, unsigned grid, u
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(block);
     return cfg;
+}
+
+// The device copy of `po` in the flag area of this rank's buffer: found in a small host-side cache of what the area's
+// table slots hold, or written (by a one-thread kernel on `s`) into the next slot in turn.
+struct TableSlots {
+    PeerOut held[PEER_TABLES];
+    int used, next;
+};
+static std::mutex g_table_mu;
+static std::map<const void*, TableSlots> g_table_cache;  // by this rank's buffer; forgotten when the buffer is freed
+
+static void forget_tables(const void* buffer) {
+    std::lock_guard<std::mutex> lock(g_table_mu);
+    g_table_cache.erase(buffer);
+}
+
+static int device_table(const PeerOut& po, cudaStream_t s, const PeerOut** out) {
+    uint8_t* own = reinterpret_cast<uint8_t*>(po.flags[po.rank]);
+    std::lock_guard<std::mutex> lock(g_table_mu);
+    TableSlots& sl = g_table_cache[own];
+    for (int i = 0; i < sl.used; i++) {
+        if (memcmp(&sl.held[i], &po, sizeof(PeerOut)) == 0) {
+            *out = reinterpret_cast<const PeerOut*>(own + PEER_TABLE_OFFSET + i * PEER_TABLE_STRIDE);
+            return JQ_OK;
+        }
+    }
+    const int slot = sl.next;
+    PeerOut* dst = reinterpret_cast<PeerOut*>(own + PEER_TABLE_OFFSET + slot * PEER_TABLE_STRIDE);
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = pdl_config(attr, 1, 32, s);
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_table_kernel, po, dst));
+    count_launch(1);
+    sl.held[slot] = po;
+    sl.next = (slot + 1) % PEER_TABLES;
+    sl.used = sl.used < PEER_TABLES ? sl.used + 1 : PEER_TABLES;
+    *out = dst;
+    return JQ_OK;
 }
 
 static int enqueue_wait(const PeerTargets& tg, int rank, int world, cudaStream_t s) {
@@ -231,16 +284,19 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
     cudaStream_t s = (cudaStream_t)stream;
     const View v{w->q, w->aux, w->n, w->k, w->type};
     bool fused = false;
-    if (w->type == JQ_TYPE_Q4_K && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
-        // the GEMV kernel itself stores into every rank's y and publishes the exchange
+    if ((w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K) && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
+        // the GEMV kernel itself stores into every rank's y and publishes the exchange; it reads the targets from a table
+        // in this rank's flag area, which is written once per distinct (buffers, area, shard) and then found again
         PeerOut po;
+        memset(&po, 0, sizeof(po));
         for (int r = 0; r < PEER_MAX_WORLD; r++) {
             po.y[r] = tg.y[r];
             po.flags[r] = tg.flags[r];
         }
         po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        rc = device_table(po, s, &po.table);
         uint8_t* image = nullptr;
-        rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(w->k, (int)m), &image);
+        if (rc == JQ_OK) rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(w->k, (int)m), &image);
         if (rc == JQ_OK) {
             rc = launch_gemv_q4k_i8(v, x, (int)m, bias, nullptr, s, image, &fused, &po);
         }

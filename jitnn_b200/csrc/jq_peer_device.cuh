@@ -8,15 +8,20 @@
 namespace jq {
 
 constexpr int PEER_MAX_WORLD = 8;
-constexpr int PEER_FLAG_BYTES = 256;
+constexpr int PEER_FLAG_BYTES = 1024;   // flags and counters in the first 128 bytes, then room for PEER_TABLES copies of PeerOut
+constexpr int PEER_TABLE_OFFSET = 128;
+constexpr int PEER_TABLE_STRIDE = 208;
+constexpr int PEER_TABLES = 4;
+static_assert(sizeof(PeerOut) <= PEER_TABLE_STRIDE && PEER_TABLE_OFFSET + PEER_TABLES * PEER_TABLE_STRIDE <= PEER_FLAG_BYTES, "the tables fit the flag area");
 constexpr int PEER_COUNTER_WORD = 16;
 constexpr int PEER_SEQ_WORD = 17;
 
 // Every thread of every CTA of the grid calls this once, after its last store to a peer. The CTA that arrives last
 // publishes the exchange: flags_r[rank] = number of this exchange, on every rank r. The CTA barrier orders the CTA's
 // stores before thread 0's system-wide fence, which is cumulative: one fence per CTA, not one per thread.
-__device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, int world) {
-    __shared__ int peer_last_flag;
+// `shared_word` is a word of shared memory the caller no longer needs.
+__device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, int world, int* shared_word) {
+    int& peer_last_flag = *shared_word;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();

@@ -32,7 +32,9 @@ namespace {
 
 constexpr int TILE_F = 128;    // output features per CTA (MMA M)
 constexpr int STAGE_K = 64;    // k per stage: 64 bf16 = 128 bytes = one swizzle row
-constexpr int STAGES = 4;
+// Pipeline stages: 4 for the 256-token tile (one CTA per SM), 3 for the 128-token tile, whose 97 KB let two CTAs share an SM
+// (one dequantises while the other's MMAs run).
+__host__ __device__ constexpr int stages_of(int tile_t) { return tile_t == 128 ? 3 : 4; }
 constexpr int A_BYTES = TILE_F * STAGE_K * 2;
 constexpr int DQ_THREADS = 256;  // two dequantiser threads per output feature, 32 weights each per stage
 constexpr int THREADS = 64 + DQ_THREADS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: dequantise, then epilogue
@@ -235,9 +237,10 @@ __device__ __forceinline__ void convert_store(const typename Fmt<TYPE>::Raw (&ra
 }
 
 template <int TYPE, int TILE_T>
-__global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m,
+__global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m,
                                                                     const float* __restrict__ bias, float* __restrict__ y) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
+    constexpr int STAGES = stages_of(TILE_T);
     constexpr uint32_t IDESC = idesc_of(TILE_T);
     extern __shared__ uint8_t smem_unaligned[];
     // the swizzled tiles must start on 1024-byte boundaries of the shared address space
@@ -446,6 +449,7 @@ EncodeTiledFn encode_tiled() {
 template <int TYPE, int TILE_T>
 int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
+    constexpr int STAGES = stages_of(TILE_T);
     const size_t smem = (size_t)STAGES * (A_BYTES + B_BYTES) + 256 + 1024;  // tiles + barriers + slack for the 1024-byte alignment
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
