@@ -34,7 +34,7 @@ constexpr int TILE_F = 128;    // output features per CTA (MMA M)
 constexpr int STAGE_K = 64;    // k per stage: 64 bf16 = 128 bytes = one swizzle row
 // Pipeline stages: 4 for the 256-token tile (one CTA per SM), 3 for the 128-token tile, whose 97 KB let two CTAs share an SM
 // (one dequantises while the other's MMAs run).
-__host__ __device__ constexpr int stages_of(int tile_t) { return tile_t == 128 ? 3 : 4; }
+__host__ __device__ constexpr int stages_of(int tile_t, int nf) { return nf == 2 ? (tile_t == 128 ? 4 : 3) : (tile_t == 128 ? 3 : 4); }
 constexpr int A_BYTES = TILE_F * STAGE_K * 2;
 constexpr int DQ_THREADS = 256;  // two dequantiser threads per output feature, 32 weights each per stage
 constexpr int THREADS = 64 + DQ_THREADS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: dequantise, then epilogue
@@ -236,25 +236,28 @@ __device__ __forceinline__ void convert_store(const typename Fmt<TYPE>::Raw (&ra
     }
 }
 
-template <int TYPE, int TILE_T>
-__global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m,
-                                                                    const float* __restrict__ bias, float* __restrict__ y) {
+// NF = 1 or 2 feature tiles of 128 rows per CTA. With two, every activation tile that the TMA brings in from L2 feeds two
+// accumulators (TMEM columns [0, TILE_T) and [TILE_T, 2 TILE_T)), which halves the L2-to-SM traffic per flop; the CTA then
+// has 16 dequantiser warps.
+template <int TYPE, int TILE_T, int NF>
+__global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 1) ? 2 : 1)
+    prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m, const float* __restrict__ bias, float* __restrict__ y) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
-    constexpr int STAGES = stages_of(TILE_T);
+    constexpr int STAGES = stages_of(TILE_T, NF);
     constexpr uint32_t IDESC = idesc_of(TILE_T);
     extern __shared__ uint8_t smem_unaligned[];
     // the swizzled tiles must start on 1024-byte boundaries of the shared address space
     uint8_t* smem = smem_unaligned + ((1024u - (smem_u32(smem_unaligned) & 1023u)) & 1023u);
-    // [STAGES][A_BYTES] weights, [STAGES][B_BYTES] activations (1024-byte aligned tiles), then barriers
+    // [STAGES][NF][A_BYTES] weights, [STAGES][B_BYTES] activations (1024-byte aligned tiles), then barriers
     uint8_t* a_tiles = smem;
-    uint8_t* b_tiles = smem + STAGES * A_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+    uint8_t* b_tiles = smem + STAGES * NF * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (NF * A_BYTES + B_BYTES));
     // bars: full_a[S], full_b[S], empty[S], accum
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int f0 = blockIdx.x * TILE_F, t0 = blockIdx.y * TILE_T;
+    const int f0 = blockIdx.x * (NF * TILE_F), t0 = blockIdx.y * TILE_T;
     const int KT = (int)(v.k / STAGE_K);
     const uint32_t bar0 = smem_u32(bars);
     auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -264,7 +267,7 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_a(s), DQ_THREADS);
+            mbar_init(full_a(s), NF * DQ_THREADS);
             mbar_init(full_b(s), 1);
             mbar_init(empty(s), 1);
         }
@@ -273,7 +276,7 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TILE_T) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NF * TILE_T) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -306,11 +309,15 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t ad = smem_desc(smem_u32(a_tiles + s * A_BYTES)), bd = smem_desc(smem_u32(b_tiles + s * B_BYTES));
+                const uint64_t bd = smem_desc(smem_u32(b_tiles + s * B_BYTES));
 #pragma unroll
-                for (int ks = 0; ks < STAGE_K / 16; ks++) {
-                    // 16 k = 32 bytes further inside the swizzle row: +2 in the (address >> 4) field
-                    umma(tmem, ad + 2u * ks, bd + 2u * ks, IDESC, (it | ks) != 0 ? 1u : 0u);
+                for (int f = 0; f < NF; f++) {
+                    const uint64_t ad = smem_desc(smem_u32(a_tiles + (s * NF + f) * A_BYTES));
+#pragma unroll
+                    for (int ks = 0; ks < STAGE_K / 16; ks++) {
+                        // 16 k = 32 bytes further inside the swizzle row: +2 in the (address >> 4) field
+                        umma(tmem + (uint32_t)(f * TILE_T), ad + 2u * ks, bd + 2u * ks, IDESC, (it | ks) != 0 ? 1u : 0u);
+                    }
                 }
                 umma_commit(empty(s));  // arrives when the MMAs that read this stage have finished
             }
@@ -321,8 +328,8 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
     } else {
         // ---- dequantise: threads i and 128 + i own feature row f0 + i (rows past n repeat the last row; never stored); the
         // two halves of a row's chunk go to different warps so that no warp diverges
-        const int i = (threadIdx.x - 64) & 127, part = (threadIdx.x - 64) >> 7;
-        int64_t row = (int64_t)f0 + i;
+        const int i = (threadIdx.x - 64) & 127, part = ((threadIdx.x - 64) >> 7) & 1, sub = (threadIdx.x - 64) >> 8;  // sub: feature tile
+        int64_t row = (int64_t)f0 + sub * TILE_F + i;
         row = row < v.n ? row : v.n - 1;
         const uint32_t row_off = (uint32_t)((i >> 3) * 1024 + (i & 7) * 128);
         bool ok = true;
@@ -354,7 +361,7 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
                 ok = false;
                 break;
             }
-            convert_store<TYPE>(cur, unit, base, it * STAGE_K, a_tiles + s * A_BYTES + row_off, i & 7);
+            convert_store<TYPE>(cur, unit, base, it * STAGE_K, a_tiles + (s * NF + sub) * A_BYTES + row_off, i & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             mbar_arrive(full_a(s));
 #pragma unroll
@@ -368,13 +375,13 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
         if (ok && mbar_wait(accum, 0, abort_flag, 4)) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int lane_group = warp & 3;  // a warp may only read TMEM lanes 32 (warp % 4) .. + 31
-            const int col_half = (warp - 2) >> 2;  // the two warps of a lane group split the token columns
-            const int feature = f0 + lane_group * 32 + lane;
+            const int col_half = ((warp - 2) >> 2) & 1;  // the two warps of a lane group and feature tile split the token columns
+            const int feature = f0 + sub * TILE_F + lane_group * 32 + lane;
             const float b = (bias != nullptr && feature < v.n) ? bias[feature] : 0.0f;
 #pragma unroll 1
             for (int c = col_half * (TILE_T / 64); c < (col_half + 1) * (TILE_T / 64); c++) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(c * 32);
+                const uint32_t taddr = tmem + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(sub * TILE_T + c * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
@@ -412,7 +419,7 @@ __global__ void __launch_bounds__(THREADS, TILE_T == 128 ? 2 : 1) prefill_tcgen0
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TILE_T) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NF * TILE_T) : "memory");
     }
 }
 
@@ -446,20 +453,20 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int TYPE, int TILE_T>
+template <int TYPE, int TILE_T, int NF>
 int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
-    constexpr int STAGES = stages_of(TILE_T);
-    const size_t smem = (size_t)STAGES * (A_BYTES + B_BYTES) + 256 + 1024;  // tiles + barriers + slack for the 1024-byte alignment
+    constexpr int STAGES = stages_of(TILE_T, NF);
+    const size_t smem = (size_t)STAGES * (NF * A_BYTES + B_BYTES) + 256 + 1024;  // tiles + barriers + slack for the 1024-byte alignment
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
-    dim3 grid((unsigned)((v.n + TILE_F - 1) / TILE_F), (unsigned)((m + TILE_T - 1) / TILE_T));
-    prefill_tcgen05_kernel<TYPE, TILE_T><<<grid, THREADS, smem, s>>>(v, xmap, m, bias, y);
+    dim3 grid((unsigned)((v.n + NF * TILE_F - 1) / (NF * TILE_F)), (unsigned)((m + TILE_T - 1) / TILE_T));
+    prefill_tcgen05_kernel<TYPE, TILE_T, NF><<<grid, 64 + NF * DQ_THREADS, smem, s>>>(v, xmap, m, bias, y);
     count_launch();
     return check_launch("prefill_tcgen05_kernel");
 }
@@ -482,9 +489,28 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     CUtensorMap xmap;
     const cuuint64_t dims[2] = {(cuuint64_t)v.k, (cuuint64_t)m};
     const cuuint64_t strides[1] = {(cuuint64_t)v.k * 2};
-    // 256 tokens per CTA when there are enough of them: every dequantised weight tile then feeds twice the tensor work
-    const int64_t ctas256 = ((v.n + TILE_F - 1) / TILE_F) * ((m + 255) / 256);
-    const int tile_t = (m > 128 && ctas256 >= 140) ? 256 : 128;  // not at the price of leaving SMs without a CTA
+    // Tile shape: 128 or 256 tokens x 128 or 256 features per CTA. More tokens per CTA spread the dequantisation of a weight
+    // tile over more tensor work, two feature tiles halve the activation traffic from L2, but both leave fewer CTAs for
+    // the 148 SMs. Chosen by a small cost model: waves of CTAs x the measured time of one wave (microseconds at k = 4096,
+    // the same for every k up to a common factor).
+    int tile_t = 128, nf = 1;
+    {
+        const int ts[4] = {128, 256, 128, 256}, nfs[4] = {1, 1, 2, 2};
+        const double wave_us[4] = {44.0, 49.0, 67.0, 78.0};
+        double best = 0.0;
+        for (int c = 0; c < 4; c++) {
+            if (ts[c] == 256 && m <= 128) {
+                continue;
+            }
+            const int64_t ctas = ((v.n + 128 * nfs[c] - 1) / (128 * nfs[c])) * ((m + ts[c] - 1) / ts[c]);
+            const double cost = (double)((ctas + 147) / 148) * wave_us[c];
+            if (c == 0 || cost < best) {
+                best = cost;
+                tile_t = ts[c];
+                nf = nfs[c];
+            }
+        }
+    }
     const cuuint32_t box[2] = {STAGE_K, (cuuint32_t)tile_t};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(x_bf16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -494,15 +520,17 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     }
 #define JQ_PREFILL_CASE(T)                                                                         \
     case T:                                                                                          \
-        return tile_t == 256 ? launch_typed<T, 256>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128>(v, xmap, (int)m, bias, y, s);
+        return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 2>(v, xmap, (int)m, bias, y, s)) \
+                       : (tile_t == 256 ? launch_typed<T, 256, 1>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1>(v, xmap, (int)m, bias, y, s));
     switch (v.type) {
         JQ_PREFILL_CASE(JQ_TYPE_Q8_0)
         JQ_PREFILL_CASE(JQ_TYPE_Q4_0)
         JQ_PREFILL_CASE(JQ_TYPE_Q4_1)
         JQ_PREFILL_CASE(JQ_TYPE_Q4_K)
         JQ_PREFILL_CASE(JQ_TYPE_Q5_K)
+        JQ_PREFILL_CASE(JQ_TYPE_Q6_K)
         default:
-            return tile_t == 256 ? launch_typed<JQ_TYPE_Q6_K, 256>(v, xmap, (int)m, bias, y, s) : launch_typed<JQ_TYPE_Q6_K, 128>(v, xmap, (int)m, bias, y, s);
+            return fail(JQ_ERR_UNSUPPORTED, "prefill: type %d has no tensor-core kernel", v.type);
     }
 #undef JQ_PREFILL_CASE
 }
