@@ -239,7 +239,8 @@ __device__ __forceinline__ void convert_store(const typename Fmt<TYPE>::Raw (&ra
 // NF = 1 or 2 feature tiles of 128 rows per CTA. With two, every activation tile that the TMA brings in from L2 feeds two
 // accumulators (TMEM columns [0, TILE_T) and [TILE_T, 2 TILE_T)), which halves the L2-to-SM traffic per flop; the CTA then
 // has 16 dequantiser warps.
-template <int TYPE, int TILE_T, int NF>
+// SPLIT: gridDim.z = 2 CTAs share a tile, each takes half of k and adds its result into a zeroed y.
+template <int TYPE, int TILE_T, int NF, bool SPLIT>
 __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 1) ? 2 : 1)
     prefill_tcgen05_kernel(View v, const __grid_constant__ CUtensorMap xmap, int m, const float* __restrict__ bias, float* __restrict__ y) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
@@ -258,7 +259,9 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * (NF * TILE_F), t0 = blockIdx.y * TILE_T;
-    const int KT = (int)(v.k / STAGE_K);
+    const int KT_all = (int)(v.k / STAGE_K);
+    const int it0 = SPLIT ? (int)blockIdx.z * (KT_all / 2) : 0;                        // first 64-wide stage of k of this CTA
+    const int KT = SPLIT ? (blockIdx.z == 0 ? KT_all / 2 : KT_all - KT_all / 2) : KT_all;  // and their number
     const uint32_t bar0 = smem_u32(bars);
     auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto full_b = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
@@ -294,7 +297,7 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
                     break;
                 }
                 mbar_expect_tx(full_b(s), B_BYTES);
-                tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &xmap, full_b(s), it * STAGE_K, t0);
+                tma_load_2d(smem_u32(b_tiles + s * B_BYTES), &xmap, full_b(s), (it0 + it) * STAGE_K, t0);
             }
         }
     } else if (warp == 1) {
@@ -338,7 +341,7 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
         typename Fmt<TYPE>::Raw cur[CT::TASKS], nxt[CT::TASKS];
         int64_t blk[CT::TASKS];
         int unit[CT::TASKS], base[CT::TASKS], unit_n[CT::TASKS], base_n[CT::TASKS];
-        CT::of(v, row, 0, part, blk, unit, base);
+        CT::of(v, row, it0 * STAGE_K, part, blk, unit, base);
 #pragma unroll
         for (int q = 0; q < CT::TASKS; q++) {
             Fmt<TYPE>::load(v, blk[q], unit[q], cur[q]);
@@ -347,8 +350,8 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
             const int s = it % STAGES;
             const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
             if (it + 1 < KT) {
-                CT::of(v, row, (it + 1) * STAGE_K, part, blk, unit_n, base_n);
-                if (TYPE == JQ_TYPE_Q6_K && ((it + 1) & 1)) {
+                CT::of(v, row, (it0 + it + 1) * STAGE_K, part, blk, unit_n, base_n);
+                if (TYPE == JQ_TYPE_Q6_K && ((it0 + it + 1) & 1)) {
                     nxt[0] = cur[0];  // the second 64 weights of a half come from the unit that is already loaded
                 } else {
 #pragma unroll
@@ -361,7 +364,7 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
                 ok = false;
                 break;
             }
-            convert_store<TYPE>(cur, unit, base, it * STAGE_K, a_tiles + (s * NF + sub) * A_BYTES + row_off, i & 7);
+            convert_store<TYPE>(cur, unit, base, (it0 + it) * STAGE_K, a_tiles + (s * NF + sub) * A_BYTES + row_off, i & 7);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
             mbar_arrive(full_a(s));
 #pragma unroll
@@ -377,7 +380,7 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
             const int lane_group = warp & 3;  // a warp may only read TMEM lanes 32 (warp % 4) .. + 31
             const int col_half = ((warp - 2) >> 2) & 1;  // the two warps of a lane group and feature tile split the token columns
             const int feature = f0 + sub * TILE_F + lane_group * 32 + lane;
-            const float b = (bias != nullptr && feature < v.n) ? bias[feature] : 0.0f;
+            const float b = (bias != nullptr && feature < v.n && (!SPLIT || blockIdx.z == 0)) ? bias[feature] : 0.0f;
 #pragma unroll 1
             for (int c = col_half * (TILE_T / 64); c < (col_half + 1) * (TILE_T / 64); c++) {
                 uint32_t r[32];
@@ -396,7 +399,12 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
                     for (int j = 0; j < 32; j++) {
                         const int token = t0 + c * 32 + j;
                         if (token < m) {
-                            y[(int64_t)token * v.n + feature] = __uint_as_float(r[j]) + b;
+                            float* dst = y + (int64_t)token * v.n + feature;
+                            if constexpr (SPLIT) {
+                                atomicAdd(dst, __uint_as_float(r[j]) + b);  // two parts: the sum does not depend on who comes first
+                            } else {
+                                *dst = __uint_as_float(r[j]) + b;
+                            }
                         }
                     }
                 }
@@ -453,7 +461,7 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int TYPE, int TILE_T, int NF>
+template <int TYPE, int TILE_T, int NF, bool SPLIT>
 int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
     constexpr int STAGES = stages_of(TILE_T, NF);
@@ -462,11 +470,14 @@ int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bia
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T, NF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T, NF, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
-    dim3 grid((unsigned)((v.n + NF * TILE_F - 1) / (NF * TILE_F)), (unsigned)((m + TILE_T - 1) / TILE_T));
-    prefill_tcgen05_kernel<TYPE, TILE_T, NF><<<grid, 64 + NF * DQ_THREADS, smem, s>>>(v, xmap, m, bias, y);
+    if (SPLIT) {
+        JQ_CUDA(cudaMemsetAsync(y, 0, (size_t)m * v.n * sizeof(float), s));
+    }
+    dim3 grid((unsigned)((v.n + NF * TILE_F - 1) / (NF * TILE_F)), (unsigned)((m + TILE_T - 1) / TILE_T), SPLIT ? 2u : 1u);
+    prefill_tcgen05_kernel<TYPE, TILE_T, NF, SPLIT><<<grid, 64 + NF * DQ_THREADS, smem, s>>>(v, xmap, m, bias, y);
     count_launch();
     return check_launch("prefill_tcgen05_kernel");
 }
@@ -493,7 +504,7 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     // tile over more tensor work, two feature tiles halve the activation traffic from L2, but both leave fewer CTAs for
     // the 148 SMs. Chosen by a small cost model: waves of CTAs x the measured time of one wave (microseconds at k = 4096,
     // the same for every k up to a common factor).
-    int tile_t = 128, nf = 1;
+    int tile_t = 128, nf = 1, ksplit = 1;
     {
         const int ts[4] = {128, 256, 128, 256}, nfs[4] = {1, 1, 2, 2};
         const double wave_us[4] = {44.0, 49.0, 67.0, 78.0};
@@ -503,11 +514,18 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
                 continue;
             }
             const int64_t ctas = ((v.n + 128 * nfs[c] - 1) / (128 * nfs[c])) * ((m + ts[c] - 1) / ts[c]);
-            const double cost = (double)((ctas + 147) / 148) * wave_us[c];
-            if (c == 0 || cost < best) {
-                best = cost;
-                tile_t = ts[c];
-                nf = nfs[c];
+            // A one-feature-tile shape can also take k in two halves (two CTAs per tile adding into a zeroed y; two partial
+            // sums add up the same in either order): that fills SMs which few feature tiles leave idle. A half-k CTA costs a
+            // little more than half, and y has to be zeroed first.
+            const double kf = (double)v.k / 4096.0;
+            for (int ks = 1; ks <= (nfs[c] == 1 && v.k / STAGE_K >= 32 ? 2 : 1); ks++) {
+                const double cost = (double)((ctas * ks + 147) / 148) * wave_us[c] * kf * (ks == 2 ? 0.55 : 1.0) + (ks == 2 ? 8.0 : 0.0);
+                if ((c == 0 && ks == 1) || cost < best) {
+                    best = cost;
+                    tile_t = ts[c];
+                    nf = nfs[c];
+                    ksplit = ks;
+                }
             }
         }
     }
@@ -520,8 +538,9 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     }
 #define JQ_PREFILL_CASE(T)                                                                         \
     case T:                                                                                          \
-        return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 2>(v, xmap, (int)m, bias, y, s)) \
-                       : (tile_t == 256 ? launch_typed<T, 256, 1>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1>(v, xmap, (int)m, bias, y, s));
+        if (ksplit == 2) return tile_t == 256 ? launch_typed<T, 256, 1, true>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1, true>(v, xmap, (int)m, bias, y, s); \
+        return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2, false>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 2, false>(v, xmap, (int)m, bias, y, s)) \
+                       : (tile_t == 256 ? launch_typed<T, 256, 1, false>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1, false>(v, xmap, (int)m, bias, y, s));
     switch (v.type) {
         JQ_PREFILL_CASE(JQ_TYPE_Q8_0)
         JQ_PREFILL_CASE(JQ_TYPE_Q4_0)

@@ -56,6 +56,29 @@ def test_benchmark_weights(t):
     check(t, 512, 4096, 512, seed=3, weights="synthetic")
 
 
+@pytest.mark.parametrize("t,n,k", [("Q4_K", 4096, 4096), ("Q4_K", 11008, 4096), ("Q6_K", 4096, 11008)])
+def test_benchmark_shapes_against_a_gpu_reference(t, n, k):
+    """At the benchmark's sizes (M = 512) the kernel takes its other tile shapes: 256 tokens with k split in two for the
+    4096-row weights, two feature tiles per CTA for 11008 rows. The CPU oracle would take minutes here, so the reference is
+    the same product at the same operand precision in float64 on the GPU, from the library's bit-exact dequantiser."""
+    m = 512
+    g = torch.Generator(device="cuda").manual_seed(n + k)
+    wf = torch.randn(n, k, generator=g, device="cuda") * 0.02
+    raw = synth.QUANTIZERS[t](wf).cpu().numpy()
+    del wf
+    w = Tensor.quantized(t, raw, n, k)
+    xb = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(n, generator=g, device="cuda")
+    y = Gguf.linearBf16(xb, w, bias)
+    assert device_status(0) == 0
+    wd = torch.as_tensor(np.asarray(Gguf.dequantize(w))).cuda().to(torch.bfloat16).double()
+    ref = xb.double() @ wd.T + bias.double()
+    err = (torch.as_tensor(np.asarray(y.cpu())).cuda().double() - ref).abs().max().item()
+    assert err <= 2e-4 * ref.abs().max().item(), (t, n, k, err / ref.abs().max().item())
+    # twice the same call: the two halves of k add into y in either order with the same result
+    assert torch.equal(Gguf.linearBf16(xb, w, bias), y)
+
+
 def test_small_m_and_host_memory():
     y, w, xb, bias = check("Q4_K", 130, 512, 5, seed=4)
     host = Gguf.linearBf16(xb.view(torch.uint16).numpy(), w, bias.numpy())
