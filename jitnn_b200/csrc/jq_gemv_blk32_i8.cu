@@ -101,6 +101,7 @@ template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) blk32_image_kernel(const float* __restrict__ x, int rows, int64_t k, uint8_t* __restrict__ image) {
     using I = Img<MT>;
     asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x is complete, and the GEMV before this one is done with the scratch image
     const int lane = threadIdx.x & 31;
     const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
     const int b = pair / MT, m = pair % MT;
@@ -410,12 +411,19 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         JQ_CUDA(cudaFuncSetAttribute(gemv_blk32_i8_kernel<TYPE, MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
-    blk32_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+    // launched programmatically as well: it is scheduled while the kernel before it still runs (it waits for that kernel
+    // before touching memory) and lets the GEMV behind it be scheduled at once
+    cudaLaunchConfig_t icfg = {};
+    cudaLaunchAttribute iattr[1];
+    iattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    iattr[0].val.programmaticStreamSerializationAllowed = 1;
+    icfg.attrs = iattr;
+    icfg.numAttrs = 1;
+    icfg.stream = s;
+    icfg.gridDim = dim3((unsigned)((KB * MT + PREP_WARPS - 1) / PREP_WARPS));
+    icfg.blockDim = dim3(PREP_WARPS * 32);
+    JQ_CUDA(cudaLaunchKernelEx(&icfg, blk32_image_kernel<MT>, x, rows, (int64_t)v.k, image));
     count_launch();
-    int rc = check_launch("blk32_image_kernel");
-    if (rc != JQ_OK) {
-        return rc;
-    }
     const int grid = tiles < sm_count() * 2 ? tiles : sm_count() * 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);

@@ -103,6 +103,7 @@ template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
                                                                              uint8_t* __restrict__ image) {
     asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x is complete, and the GEMV before this one is done with the scratch image
     const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
     const int b = pair / MT, m = pair % MT;
     if (b < (int)(k >> 8)) {
@@ -559,12 +560,19 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     }
     *handled = true;
     if (x != nullptr) {
-        q4k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+        // launched programmatically as well: it is scheduled while the kernel before it still runs (it waits for that kernel
+        // before touching memory) and lets the GEMV behind it be scheduled at once
+        cudaLaunchConfig_t icfg = {};
+        cudaLaunchAttribute iattr[1];
+        iattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        iattr[0].val.programmaticStreamSerializationAllowed = 1;
+        icfg.attrs = iattr;
+        icfg.numAttrs = WIDE ? 0 : 1;  // the 16-warp kernel fills an SM's registers: an early-scheduled successor only gets in its way
+        icfg.stream = s;
+        icfg.gridDim = dim3((unsigned)((KB * MT + PREP_WARPS - 1) / PREP_WARPS));
+        icfg.blockDim = dim3(PREP_WARPS * 32);
+        JQ_CUDA(cudaLaunchKernelEx(&icfg, q4k_activation_image_kernel<MT>, x, rows, (int64_t)v.k, image));
         count_launch();
-        int rc = check_launch("q4k_activation_image_kernel");
-        if (rc != JQ_OK) {
-            return rc;
-        }
     }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \

@@ -81,6 +81,7 @@ template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) q6k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
                                                                              uint8_t* __restrict__ image) {
     asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x is complete, and the GEMV before this one is done with the scratch image
     const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
     const int b = pair / MT, m = pair % MT;
     if (b < (int)(k >> 8)) {
@@ -430,12 +431,19 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
     }
     *handled = true;
     if (x != nullptr) {  // else the image is already in `image` (written by a kernel earlier in the stream)
-        q6k_activation_image_kernel<MT><<<(KB * MT + PREP_WARPS - 1) / PREP_WARPS, PREP_WARPS * 32, 0, s>>>(x, rows, v.k, image);
+        // launched programmatically as well: it is scheduled while the kernel before it still runs (it waits for that kernel
+        // before touching memory) and lets the GEMV behind it be scheduled at once
+        cudaLaunchConfig_t icfg = {};
+        cudaLaunchAttribute iattr[1];
+        iattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        iattr[0].val.programmaticStreamSerializationAllowed = 1;
+        icfg.attrs = iattr;
+        icfg.numAttrs = 1;
+        icfg.stream = s;
+        icfg.gridDim = dim3((unsigned)((KB * MT + PREP_WARPS - 1) / PREP_WARPS));
+        icfg.blockDim = dim3(PREP_WARPS * 32);
+        JQ_CUDA(cudaLaunchKernelEx(&icfg, q6k_activation_image_kernel<MT>, x, rows, (int64_t)v.k, image));
         count_launch();
-        int rc = check_launch("q6k_activation_image_kernel");
-        if (rc != JQ_OK) {
-            return rc;
-        }
     }
     if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
     if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
