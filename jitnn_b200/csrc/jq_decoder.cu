@@ -6,6 +6,8 @@
 // nn.Linear replaced by jq_linear_f32 on a quantised weight. The reference recomputes all positions on every call and
 // has no generation loop; here keys and values are kept in a cache [layer][position][kv_head * head_dim], which
 // computes the same function. All arithmetic is FP32 in a fixed order (the reference's host path uses double).
+#include <cooperative_groups.h>
+
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -341,55 +343,55 @@ __device__ __forceinline__ void write_images(const float* block, int b, const Im
 }
 
 // x = embedding row of the token (table != nullptr), or x += delta (delta != nullptr), or x as it is; then RMSNorm
-// (ops/RowNorm.java:266-306) into shared memory and from there into the images. One CTA of 1024 threads, dim <= 16384.
-constexpr int NORM_THREADS = 1024;
-__global__ void __launch_bounds__(NORM_THREADS) norm_image_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ table,
-                                                                  const int* __restrict__ token, int vocab, const float* __restrict__ w, float eps, int dim,
-                                                                  Images im) {
-    extern __shared__ __align__(16) float norm_xs[];
+// (ops/RowNorm.java:266-306) and from there the images. A thread-block cluster of up to 8 CTAs shares the vector: every
+// CTA takes dim / CTAs elements (whole super-blocks of 256), the sums of squares meet through distributed shared
+// memory (each CTA adds the partial sums of all CTAs in rank order, so all get the same total), and every CTA writes
+// the images of its own super-blocks. blockDim.x = elements per CTA / 4.
+__global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ table,
+                                                          const int* __restrict__ token, int vocab, const float* __restrict__ w, float eps, int dim,
+                                                          Images im) {
+    namespace cg = cooperative_groups;
+    extern __shared__ __align__(16) float norm_xs[];  // this CTA's normalised elements
     __shared__ float scratch[32];
+    __shared__ float partial;
+    cg::cluster_group cluster = cg::this_cluster();
     pdl_enter();
-    const int n4 = dim >> 2;
-    const float4* src = reinterpret_cast<const float4*>(x);
+    const int per_cta = dim / (int)gridDim.x, first = (int)blockIdx.x * per_cta;
+    const float4* src = reinterpret_cast<const float4*>(x + first);
     if (table != nullptr) {
         int tok = token[0];
         tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
-        src = reinterpret_cast<const float4*>(table + (int64_t)tok * dim);
+        src = reinterpret_cast<const float4*>(table + (int64_t)tok * dim + first);
     }
-    float4 v[4];
-    float sq = 0.0f;
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-        const int i = (int)threadIdx.x + u * NORM_THREADS;
-        if (i < n4) {
-            float4 a = src[i];
-            if (delta != nullptr) {
-                const float4 b = reinterpret_cast<const float4*>(delta)[i];
-                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-            }
-            if (delta != nullptr || table != nullptr) {
-                reinterpret_cast<float4*>(x)[i] = a;
-            }
-            v[u] = a;
-            sq = fmaf(a.x, a.x, sq); sq = fmaf(a.y, a.y, sq); sq = fmaf(a.z, a.z, sq); sq = fmaf(a.w, a.w, sq);
-        }
+    const int i = (int)threadIdx.x;
+    float4 a = src[i];
+    if (delta != nullptr) {
+        const float4 b = reinterpret_cast<const float4*>(delta + first)[i];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
     }
-    const float total = block_sum(sq, scratch);
+    if (delta != nullptr || table != nullptr) {
+        reinterpret_cast<float4*>(x + first)[i] = a;
+    }
+    const float sq = fmaf(a.w, a.w, fmaf(a.z, a.z, fmaf(a.y, a.y, a.x * a.x)));
+    const float mine = block_sum(sq, scratch);
+    if (threadIdx.x == 0) {
+        partial = mine;
+    }
+    cluster.sync();
+    float total = 0.0f;
+    for (unsigned r = 0; r < cluster.num_blocks(); r++) {
+        total += *cluster.map_shared_rank(&partial, r);
+    }
+    cluster.sync();  // no CTA leaves (and frees its shared memory) while another may still read its partial sum
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
-#pragma unroll
-    for (int u = 0; u < 4; u++) {
-        const int i = (int)threadIdx.x + u * NORM_THREADS;
-        if (i < n4) {
-            const float4 ww = reinterpret_cast<const float4*>(w)[i];
-            reinterpret_cast<float4*>(norm_xs)[i] = make_float4(v[u].x * inv * ww.x, v[u].y * inv * ww.y, v[u].z * inv * ww.z, v[u].w * inv * ww.w);
-        }
-    }
+    const float4 ww = reinterpret_cast<const float4*>(w + first)[i];
+    reinterpret_cast<float4*>(norm_xs)[i] = make_float4(a.x * inv * ww.x, a.y * inv * ww.y, a.z * inv * ww.z, a.w * inv * ww.w);
     __syncthreads();
-    const int KB = dim >> 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int task = warp; task < 2 * KB; task += NORM_THREADS / 32) {
-        const int b = task < KB ? task : task - KB;
-        Images one{task < KB ? im.q4k : nullptr, task < KB ? nullptr : im.q6k};
-        write_images(norm_xs + (size_t)b * 256, b, one, lane);
+    const int blocks = per_cta >> 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int task = warp; task < 2 * blocks; task += warps) {
+        const int b = task < blocks ? task : task - blocks;
+        Images one{task < blocks ? im.q4k : nullptr, task < blocks ? nullptr : im.q6k};
+        write_images(norm_xs + (size_t)b * 256, (first >> 8) + b, one, lane);
     }
 }
 
@@ -685,6 +687,26 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// The same for a kernel whose whole grid is one thread-block cluster.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_cluster_pdl(void (*kernel)(KArgs...), int ctas, dim3 block, size_t smem, cudaStream_t s, bool programmatic, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = programmatic ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace
 }  // namespace jq
 
@@ -758,6 +780,7 @@ JQ_API int jq_decoder_destroy(jq_decoder* d) {
         cudaStreamSynchronize(d->own_stream);
         cudaStreamDestroy(d->own_stream);
     }
+
     if (prev >= 0) {
         cudaSetDevice(prev);
     }
@@ -838,7 +861,6 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
         if (e == cudaSuccess) e = cudaMalloc(&d->argmax_i, ARGMAX_CTAS * sizeof(int));
     }
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(norm_image_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 * (int)sizeof(float));
     if (e == cudaSuccess) {
         // cos / sin tables in double, stored as float (ops/Rope.java:84-101)
         const int half = head_dim / 2;
@@ -942,7 +964,7 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table) {
 
 // Whether the single-token step can take the fused kernels: Q4_K / Q6_K linears, head_dim 128, sizes in whole super-blocks.
 static bool fused_step_possible(const jq_decoder* d) {
-    if (g_opt_decoder_fused.load() == 0 || d->head_dim != 128 || d->dim % 256 != 0 || d->hidden % 256 != 0 || d->dim > 16384) {
+    if (g_opt_decoder_fused.load() == 0 || d->head_dim != 128 || d->dim % 256 != 0 || d->hidden % 256 != 0 || d->dim > 32768) {
         return false;
     }
     for (const jq_weight* w : d->lin) {
@@ -974,7 +996,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         return im;
     };
     // y = W x (and y2 = W2 x in the same launch when both are Q4_K), x being the image written just before
-    auto GEMV = [&](const jq_weight* w, float* y, const jq_weight* w2, float* y2) {
+    auto GEMV = [&](const jq_weight* w, float* y, const jq_weight* w2, float* y2, cudaStream_t gs) {
         for (int pass = 0; pass < 2 && rc == JQ_OK; pass++) {
             const jq_weight* cur = pass == 0 ? w : w2;
             float* out_ = pass == 0 ? y : y2;
@@ -986,13 +1008,13 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
             if (cur->type == JQ_TYPE_Q4_K) {
                 if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
                     const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
-                    rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, s, &handled);
+                    rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, gs, &handled);
                     pass = 1;  // both done
                 } else {
-                    rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, s, &handled);
+                    rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, gs, &handled);
                 }
             } else {
-                rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, s, &handled);
+                rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, gs, &handled);
             }
             if (rc == JQ_OK && !handled) {
                 rc = fail(JQ_ERR_UNSUPPORTED, "decoder: a [%lld, %lld] linear is outside what the tensor-core GEMV takes (set option decoder_fused to 0)",
@@ -1015,38 +1037,44 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         first_programmatic = false;
     }
     const float scale = (float)(1.0 / std::sqrt((double)d->head_dim));
-    const size_t norm_smem = (size_t)dim * sizeof(float);
+    // the norm kernel's cluster: the most CTAs (up to 8) that still get whole super-blocks each
+    int norm_ctas = 8;
+    while (norm_ctas > 1 && dim % (256 * norm_ctas) != 0) {
+        norm_ctas /= 2;
+    }
+    const size_t norm_smem = (size_t)(dim / norm_ctas) * sizeof(float);
+    const dim3 norm_block((unsigned)(dim / norm_ctas / 4));
     const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
     for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
         float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
         float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
         // attention block: x = embedding (first layer) or x += feed-forward output of the layer before; norm -> images
-        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
+        CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
                        l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]})),
             "norm_image_kernel");
-        GEMV(L[0], d->q, L[1], d->k);
-        GEMV(L[2], d->v, nullptr, nullptr);
+        GEMV(L[0], d->q, L[1], d->k, s);
+        GEMV(L[2], d->v, nullptr, nullptr, s);
         if (rc != JQ_OK) break;
         CKL(launch_pdl(attention_image_kernel, dim3(d->heads, splits_now), dim3(ATTF_THREADS), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos,
                        d->heads, d->kv_heads, d->splits, scale, d->att_part, d->counters, images_for({L[3]})),
             "attention_image_kernel");
-        GEMV(L[3], d->proj, nullptr, nullptr);
+        GEMV(L[3], d->proj, nullptr, nullptr, s);
         if (rc != JQ_OK) break;
         // feed-forward block
-        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
+        CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
                        d->norms + (size_t)(2 * l + 1) * dim, d->eps, dim, images_for({L[4], L[5]})),
             "norm_image_kernel");
-        GEMV(L[4], d->gate, L[5], d->up);
+        GEMV(L[4], d->gate, L[5], d->up, s);
         if (rc != JQ_OK) break;
         CKL(launch_pdl(swiglu_image_kernel, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]})), "swiglu_image_kernel");
-        GEMV(L[6], d->proj, nullptr, nullptr);
+        GEMV(L[6], d->proj, nullptr, nullptr, s);
     }
     if (rc == JQ_OK) {
-        CKL(launch_pdl(norm_image_kernel, dim3(1), dim3(NORM_THREADS), norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
+        CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
                        d->norms + (size_t)(2 * d->layers) * dim, d->eps, dim, images_for({d->output})),
             "norm_image_kernel");
-        GEMV(d->output, d->logits, nullptr, nullptr);
+        GEMV(d->output, d->logits, nullptr, nullptr, s);
     }
     if (rc == JQ_OK) {
         CKL(launch_pdl(argmax_split_kernel, dim3(ARGMAX_CTAS), dim3(256), 0, s, true, d->logits, d->vocab, d->argmax_v, d->argmax_i,
