@@ -324,7 +324,9 @@ def run_ours(args):
         e2e = {"value": round(step_bytes() / dt / 1e9, 2), "unit": "GB/s",
                "h2d_bytes_per_step": int(sum(4 * m * k for _, k in SHAPES for m in BATCHES)),
                "d2h_bytes_per_step": int(sum(4 * m * n for n, _ in SHAPES for m in BATCHES)),
-               "ms_per_step": round(dt * 1e3, 4)}
+               "ms_per_step": round(dt * 1e3, 4),
+               "path": "jq_linear_f32 with page-locked host x and y, one blocking call per linear: x (up to 1 MB) is read by the kernels "
+                       "across PCIe in place, y up to 256 KB is written in place, larger y through a device-to-host copy"}
 
     prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
     formats = formats_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None

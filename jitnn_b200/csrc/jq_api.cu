@@ -132,6 +132,20 @@ int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) {
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// The device-side address of a host buffer that kernels may use directly: page-locked, 16-byte aligned, at most `limit`
+// bytes. nullptr otherwise (pageable memory, or a driver that cannot say).
+static const float* pinned_device_pointer(const void* host, size_t bytes, size_t limit) {
+    if (bytes > limit || ((uintptr_t)host & 15) != 0) {
+        return nullptr;
+    }
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+        cudaGetLastError();  // an unregistered pointer is not an error of this call
+        return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? static_cast<const float*>(attr.devicePointer) : nullptr;
+}
+
 static int check_weight(const jq_weight* w, const char* who) {
     if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC) {
         return fail(JQ_ERR_INVALID, "%s: not a live weight handle", who);
@@ -474,18 +488,32 @@ int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bi
     if (rc != JQ_OK) {
         return rc;
     }
-    float* dx = (float*)st->dev;
-    float* db = (float*)(st->dev + xb);
-    float* dy = (float*)(st->dev + xb + bb);
-    JQ_CUDA(cudaMemcpyAsync(dx, x, (size_t)m * w->k * 4, cudaMemcpyHostToDevice, st->stream));
-    if (bias != nullptr) {
-        JQ_CUDA(cudaMemcpyAsync(db, bias, (size_t)w->n * 4, cudaMemcpyHostToDevice, st->stream));
+    // Page-locked host buffers (jq_host_alloc, cudaHostAlloc, cudaHostRegister) are addressable from the GPU: small inputs
+    // and outputs are then read and written by the kernels themselves across PCIe, which saves the set-up latency of two
+    // copy-engine transfers per call. Pageable memory, and outputs too large for scattered stores, go through copies.
+    const size_t direct_limit = (size_t)256 << 10;
+    const float* dx = pinned_device_pointer(x, (size_t)m * w->k * 4, direct_limit << 2);
+    const float* db = bias != nullptr ? pinned_device_pointer(bias, (size_t)w->n * 4, direct_limit) : nullptr;
+    float* dy = const_cast<float*>(pinned_device_pointer(y, (size_t)m * w->n * 4, direct_limit));
+    const bool copy_y = dy == nullptr;
+    if (dx == nullptr) {
+        JQ_CUDA(cudaMemcpyAsync(st->dev, x, (size_t)m * w->k * 4, cudaMemcpyHostToDevice, st->stream));
+        dx = (const float*)st->dev;
     }
-    rc = linear_device(w, dx, m, bias != nullptr ? db : nullptr, dy, st->stream);
+    if (bias != nullptr && db == nullptr) {
+        JQ_CUDA(cudaMemcpyAsync(st->dev + xb, bias, (size_t)w->n * 4, cudaMemcpyHostToDevice, st->stream));
+        db = (const float*)(st->dev + xb);
+    }
+    if (copy_y) {
+        dy = (float*)(st->dev + xb + bb);
+    }
+    rc = linear_device(w, dx, m, db, dy, st->stream);
     if (rc != JQ_OK) {
         return rc;
     }
-    JQ_CUDA(cudaMemcpyAsync(y, dy, (size_t)m * w->n * 4, cudaMemcpyDeviceToHost, st->stream));
+    if (copy_y) {
+        JQ_CUDA(cudaMemcpyAsync(y, dy, (size_t)m * w->n * 4, cudaMemcpyDeviceToHost, st->stream));
+    }
     JQ_CUDA(cudaStreamSynchronize(st->stream));
     return JQ_OK;
 }

@@ -215,3 +215,20 @@ def test_full_size_linearity_property():
     assert np.array_equal(bits(Gguf.linear(onehot, w, None)[0]), bits(col))
     sample = oracle.linear("Q4_K", raw[:64], x, None, threads=4)
     assert max_rel(sample, y[:, :64]) <= REL_TOL
+
+
+def test_page_locked_host_buffers_are_used_in_place():
+    """jq_linear_f32 with page-locked host x, bias and y (kernels read and write them across PCIe, no staging copies) gives
+    bit for bit what the same call gives with pageable buffers; a large output still goes through a copy."""
+    import ctypes
+    from jitnn_b200 import _lib
+    L = _lib.load()
+    for t, n, k, m in [("Q4_K", 1024, 1024, 1), ("Q6_K", 640, 512, 3), ("Q8_0", 256, 512, 2), ("Q4_K", 16400, 256, 8)]:
+        raw = synth.random_valid_blocks(t, n, k, seed=n + m).numpy()
+        w = Tensor.quantized(t, raw, n, k)
+        g = torch.Generator().manual_seed(n)
+        x, bias = torch.randn(m, k, generator=g), torch.randn(n, generator=g)
+        pageable = Gguf.linear(x.numpy(), w, bias.numpy())
+        xp, bp, yp = x.pin_memory(), bias.pin_memory(), torch.empty(m, n).pin_memory()
+        _lib.check(L.jq_linear_f32(w._handle(), xp.data_ptr(), m, bp.data_ptr(), yp.data_ptr(), _lib.JQ_MEM_HOST, None))
+        assert np.array_equal(bits(yp.numpy()), bits(pageable)), (t, n, k, m)
