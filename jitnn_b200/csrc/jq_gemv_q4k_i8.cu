@@ -363,7 +363,19 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
         if (sl > 0) {
             __syncthreads();  // every warp is done with the previous slice
         }
-        {
+        if (nslices == 1) {
+            // one slice: a warp only ever reads the image of its own super-blocks, so it fetches just those and waits for
+            // nobody else (the wait also covers the weight stages requested so far, which it needs next anyway)
+            constexpr int CH = (int)(C::PB / 16);
+            for (int b = warp; b < KB; b += NW) {
+                for (int c = lane; c < CH; c += 32) {
+                    cp_async16(img_s + (uint32_t)(b * CH + c) * 16u, image + ((size_t)b * CH + c) * 16);
+                }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+        } else {
             const uint8_t* src = image + (size_t)sl * KS * C::PB;
             const int chunks = (int)((size_t)len * C::PB / 16);
             for (int c = tid; c < chunks; c += THREADS) {
