@@ -50,8 +50,26 @@ __device__ __forceinline__ int signed_byte(uint32_t w, int i) {
     return r;
 }
 
-__device__ __forceinline__ void cp_async4(uint32_t dst_smem, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst_smem), "l"(src) : "memory");
+// The same copies under a predicate, without a branch around them.
+__device__ __forceinline__ void cp_async16_if(uint32_t dst_smem, const void* src, int on) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %2, 0;\n"
+        "@p cp.async.cg.shared.global [%0], [%1], 16;\n"
+        "}\n" ::"r"(dst_smem),
+        "l"(src), "r"(on)
+        : "memory");
+}
+__device__ __forceinline__ void cp_async4_if(uint32_t dst_smem, const void* src, int on) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %2, 0;\n"
+        "@p cp.async.ca.shared.global [%0], [%1], 4;\n"
+        "}\n" ::"r"(dst_smem),
+        "l"(src), "r"(on)
+        : "memory");
 }
 
 // D = A(16x16 u8) * B(16x8 s8) + C, C given per column pair (the same for rows g and g + 8).
@@ -124,49 +142,57 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
         dst_off[i] = (uint32_t)(r * ROW_BYTES + ch * 16);
     }
     // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + 8 i.
-    auto blocks_of = [&](int sl) {  // number of super-blocks this warp has in slice sl
-        const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
-        return warp < len ? (len - warp + WARPS - 1) / WARPS : 0;
-    };
+    const int len_last = KB - (nslices - 1) * KS;
+    const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + WARPS - 1) / WARPS : 0) : 0;
+    const int nb_last = warp < len_last ? (len_last - warp + WARPS - 1) / WARPS : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    int steps = 0;
-    for (int sl = 0; sl < nslices; sl++) {
-        steps += blocks_of(sl) * my_tiles;
-    }
-    int iss_sl = 0, iss_ti = 0, iss_j = 0;
-    while (iss_sl < nslices && blocks_of(iss_sl) == 0) {
-        iss_sl++;
-    }
-    auto issue = [&](int s) {
-        if (s < steps) {
-            const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
-            const int blk = iss_sl * KS + warp + WARPS * iss_j;
-            const uint8_t* base = v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)blk * (uint32_t)ROW_BYTES;
-            const uint32_t slot = ring_s + (uint32_t)(s % STAGES) * SLOT_BYTES;
+    const int low16 = lane < 16;
+    int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
+    int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
+    uint32_t iss_slot = 0;
+    constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
+    // quant bytes of the lane's first chunk and the aligned word with the fp16 d of row `lane`, for the block that is requested next
+    auto q_ptr = [&]() {
+        const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
+        return v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)(iss_sl * KS + warp + WARPS * iss_j) * (uint32_t)ROW_BYTES;
+    };
+    auto d_ptr = [&]() {
+        const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
+        const int64_t didx = ((int64_t)tile * 16 + (lane & 15)) * KB + (iss_sl * KS + warp + WARPS * iss_j);  // fp16 index of this row's d
+        return v.aux + ((didx * 2) & ~(int64_t)3);
+    };
+    const uint8_t* gq = q_ptr();
+    const uint8_t* gd = d_ptr();
+    auto issue = [&]() {
+        if (iss_left > 0) {
+            iss_left--;
+            const uint32_t slot = ring_s + iss_slot;
 #pragma unroll
             for (int i = 0; i < 6; i++) {
-                cp_async16(slot + dst_off[i], base + src_off[i]);
+                cp_async16(slot + dst_off[i], gq + src_off[i]);
             }
-            if (lane < 16) {
-                cp_async16(slot + dst_off[6], base + src_off[6]);
-                const int64_t didx = ((int64_t)tile * 16 + lane) * KB + blk;  // fp16 index of this row's d
-                cp_async4(slot + SLOT_D + 4u * (uint32_t)lane, v.aux + ((didx * 2) & ~(int64_t)3));
-            }
-            if (++iss_j == blocks_of(iss_sl)) {
+            cp_async16_if(slot + dst_off[6], gq + src_off[6], low16);
+            cp_async4_if(slot + SLOT_D + 4u * (uint32_t)(lane & 15), gd, low16);
+            if (++iss_j == iss_nb) {
                 iss_j = 0;
                 if (++iss_ti == my_tiles) {
                     iss_ti = 0;
-                    do {
-                        iss_sl++;
-                    } while (iss_sl < nslices && blocks_of(iss_sl) == 0);
+                    iss_sl++;
+                    iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
                 }
+                gq = q_ptr();
+                gd = d_ptr();
+            } else {
+                gq += WARPS * ROW_BYTES;
+                gd = d_ptr();  // the d words of consecutive blocks are 2 bytes apart: recomputed because of the 4-byte alignment
             }
         }
+        iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
         cp_async_commit();
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        issue(s);  // the first weights are on their way before the activation image is complete
+        issue();  // the first weights are on their way before the activation image is complete
     }
 
     // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
@@ -175,8 +201,8 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
 
     // ---- main loop ----------------------------------------------------------------------------------------------
     // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
-    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 4;
-    const uint8_t* xc_lane = img + C::XD + (size_t)(2 * t) * 4;
+    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 16;  // B operands of four groups per 16 bytes
+    const uint8_t* xc_lane = img + C::XD + (size_t)t * 16;                              // C operands of two groups per 16 bytes
     const uint8_t* tab_lane = img + C::XD + C::XC;
     // ldmatrix row address of this lane inside a slot: matrix lane / 8 covers rows 8 (matrix % 2) .. + 7 and
     // chunk (matrix / 2) of a chunk pair
@@ -204,6 +230,16 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
             // high bit pairs of half n: registers {row g, row g+8} x {elements 0-15, 16-31}
             uint32_t qh[4];
             ldmatrix_x4(qh, slot_s + ldm_off + (uint32_t)(8 + 2 * n) * 16u);
+            // B operands of the half's eight groups: two 16-byte loads per column group
+            uint32_t bq[NG][8];
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const uint4 bw = *reinterpret_cast<const uint4*>(bx + (size_t)(((2 * n + q) * NG + i) * NCOL) * 64);
+                    bq[i][4 * q] = bw.x; bq[i][4 * q + 1] = bw.y; bq[i][4 * q + 2] = bw.z; bq[i][4 * q + 3] = bw.w;
+                }
+            }
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 // low nibbles: bytes 64 n + 32 h + l; their low nibble is sub-block kk = h, their high nibble kk = h + 2
@@ -212,6 +248,12 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
 #pragma unroll
                 for (int hi = 0; hi < 2; hi++) {
                     const int kk = h + 2 * hi;
+                    // C operands of the pair of groups 8n + 2kk, + 1: one 16-byte load per column group
+                    int4 cq[NG];
+#pragma unroll
+                    for (int i = 0; i < NG; i++) {
+                        cq[i] = *reinterpret_cast<const int4*>(bc + (size_t)(((4 * n + kk) * NG + i) * 4) * 16);
+                    }
 #pragma unroll
                     for (int cp = 0; cp < 2; cp++) {
                         const int gi = 8 * n + 2 * kk + cp;  // scale group = elements 16 gi .. 16 gi + 15
@@ -226,10 +268,8 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
                         const int s1 = signed_byte(sc1[gi >> 2], gi & 3);
 #pragma unroll
                         for (int i = 0; i < NG; i++) {
-                            const uint32_t bf = *reinterpret_cast<const uint32_t*>(bx + (size_t)((gi * NG + i) * NCOL) * 16);
-                            const int2 cf = *reinterpret_cast<const int2*>(bc + (size_t)((gi * NG + i) * 8) * 4);
                             int D[4];
-                            imma_k16(D, a0, a1, bf, cf.x, cf.y);
+                            imma_k16(D, a0, a1, bq[i][2 * kk + cp], cp == 0 ? cq[i].x : cq[i].z, cp == 0 ? cq[i].y : cq[i].w);
                             I[i][0] += s0 * D[0];
                             I[i][1] += s0 * D[1];
                             I[i][2] += s1 * D[2];
@@ -266,7 +306,7 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
     }
 
     int parity = 0;
-    int step = 0;
+    uint32_t cmp_slot = 0;
     for (int sl = 0; sl < nslices; sl++) {
         // ---- bring this slice of the activation image into shared memory ---------------------------------------------
         const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
@@ -299,11 +339,11 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
             const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
             for (int b = warp; b < len; b += WARPS) {
                 __syncwarp();                 // every lane is done reading the slot that is requested next
-                issue(step + STAGES - 1);
-                cp_async_wait<STAGES - 1>();  // this lane's copies of `step` have landed
+                issue();
+                cp_async_wait<STAGES - 1>();  // this lane's copies of this step have landed
                 __syncwarp();                 // ... and so have the other lanes'
-                compute(ring + (size_t)(step % STAGES) * SLOT_BYTES, ring_s + (uint32_t)(step % STAGES) * SLOT_BYTES, b, my_tile, sl * KS + b);
-                step++;
+                compute(ring + cmp_slot, ring_s + cmp_slot, b, my_tile, sl * KS + b);
+                cmp_slot = cmp_slot + SLOT_BYTES == RING_BYTES ? 0u : cmp_slot + SLOT_BYTES;
             }
             // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
             float* rd = red + (size_t)parity * WARPS * 16 * MT;
@@ -404,9 +444,9 @@ template <int MT>
 int run(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled) {
     const int KB = (int)(v.k / 256);
     const int tiles = (int)((v.n + 15) / 16);
-    // Candidate shapes, best first: (CTAs per SM, ring stages). The slice length KS is a function of MT and k only (so
+    // Candidate shapes, best first: (CTAs per SM, ring stages); two CTAs per SM with three stages measured best. The slice length KS is a function of MT and k only (so
     // that the summation order never depends on n): the whole k if its image fits beside the ring, else a multiple of 8.
-    const int occ_of[3] = {3, 2, 2}, st_of[3] = {3, 4, 3};
+    const int occ_of[3] = {2, 2, 2}, st_of[3] = {3, 3, 2};
     const size_t red_bytes = (size_t)(2 * WARPS * 16 * MT) * sizeof(float);
     const size_t fixed = red_bytes + 8 * 1024;  // sliced shapes: reduction buffer + room for carried sums
     int pick = -1, KS = KB;
@@ -457,8 +497,6 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         JQ_CUDA(cudaLaunchKernelEx(&icfg, q6k_activation_image_kernel<MT>, x, rows, (int64_t)v.k, image));
         count_launch();
     }
-    if (pick == 0) return launch<MT, 3, 3>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
-    if (pick == 1) return launch<MT, 4, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
     if (stages == 3) return launch<MT, 3, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
     return launch<MT, 2, 2>(v, image, rows, bias, y, s, KS, grid, max_tiles, smem);
 }

@@ -13,9 +13,12 @@ struct Cfg {
     static constexpr int COLS = 3 * MT;               // digit columns: column 3m + i is digit i of activation row m
     static constexpr int NG = (COLS + 7) / 8;         // MMA column groups
     static constexpr int NCOL = NG == 1 ? COLS : 8;   // columns stored per group
-    // bytes of activation image per super-block: digit fragments of the 16 scale groups, C fragments, column weights
-    static constexpr size_t XD = (size_t)16 * NG * NCOL * 4 * 4;  // 16 groups x column groups x columns x 4 lanes x 4 bytes
-    static constexpr size_t XC = (size_t)16 * NG * 8 * 4;         // 16 groups x column groups x 8 columns x int32
+    // bytes of activation image per super-block: digit fragments of the 16 scale groups, C fragments, column weights.
+    // Fragments of several groups sit side by side so that the GEMV reads them with 16-byte loads:
+    //   XD  [group / 4][column group][column][lane][group % 4]   4 bytes each: a lane's B operands of four groups
+    //   XC  [group / 2][column group][lane][group % 2][2 columns] int32:      a lane's C operands of two groups
+    static constexpr size_t XD = (size_t)16 * NG * NCOL * 4 * 4;
+    static constexpr size_t XC = (size_t)16 * NG * 8 * 4;
     static constexpr size_t TAB = (size_t)NG * 8 * 4;             // one float per digit column
     static constexpr size_t PB = XD + XC + TAB;
 };
@@ -29,7 +32,7 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL;
     const int grp = lane >> 1, half = lane & 1;
-    uint2* xd = reinterpret_cast<uint2*>(img);
+    uint32_t* xd = reinterpret_cast<uint32_t*>(img);
     int* xc = reinterpret_cast<int*>(img + C::XD);
     float* tab = reinterpret_cast<float*>(img + C::XD + C::XC);
     if (m == 0 && lane >= C::COLS && lane < NG * 8) {
@@ -82,11 +85,13 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
         }
         const int col = 3 * m + dgt;
         // lane slots 2 half and 2 half + 1 of this group's B fragment
-        xd[((((size_t)grp * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + 2 * half) / 2] = make_uint2(w0, w1);
+        uint32_t* cell = xd + ((((size_t)(grp >> 2) * NG + (col >> 3)) * NCOL + (col & 7)) * 16) + (grp & 3);
+        cell[(2 * half) * 4] = w0;
+        cell[(2 * half + 1) * 4] = w1;
         // -32 * (digit sum of the group's 16 elements): the row-independent part of sum (q - 32) x, the MMA's C operand
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         if (half == 0) {
-            xc[((size_t)grp * NG + (col >> 3)) * 8 + (col & 7)] = -32 * sum;
+            xc[((((size_t)(grp >> 1) * NG + (col >> 3)) * 4 + ((col & 7) >> 1)) * 2 + (grp & 1)) * 2 + (col & 1)] = -32 * sum;
         }
         if (lane == 0) {
             tab[col] = xb != nullptr ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
