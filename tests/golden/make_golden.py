@@ -2,7 +2,7 @@
 
 Run once in a container that has the reference tree (the GPU machine does not):
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path of the reference checkout>
 
 Sources (paths inside the reference project):
   * jitnn-gguf/src/test/resources/gguf/fixture.gguf          -> gguf_fixture.npz
@@ -119,4 +119,6 @@ def main(root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
