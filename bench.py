@@ -330,6 +330,7 @@ def run_ours(args):
 
     prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
     formats = formats_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
+    sharded_layer = sharded_layer_leg(torch, device, rank, world, L, _lib) if (not args.only and gather_kind != "nccl") else None
     decode = None
     if rank == 0 and world == 1 and not args.only and not args.no_decode:
         for copies in pools:
@@ -356,7 +357,7 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "formats": formats, "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -459,6 +460,85 @@ def formats_leg(torch, device, L, _lib):
         out["cases"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "GBps": round(gbps, 1), "frac": round(gbps / peak, 4)}
         del graph
         for w in ws:
+            w.release()
+    return out
+
+
+LAYER_70B = [("wq", 8192, 8192), ("wk", 1024, 8192), ("wv", 1024, 8192), ("wo", 8192, 8192), ("w1", 28672, 8192), ("w3", 28672, 8192),
+             ("w2", 8192, 28672)]
+
+
+def sharded_layer_leg(torch, device, rank, world, L, _lib):
+    """The seven linears of one 70B-shape decoder layer (BASELINE.json configs[4]: d 8192, 64 / 8 heads, FFN 28672, all
+    Q4_K), each split by output rows over the ranks and completed on every rank by the peer-store exchange, at batch 1
+    and 16. Every rank quantises only its own rows (seeded by shape and rank); two copies per weight in rotation; one
+    CUDA graph per batch size holds two passes over the layer and is replayed. Reports microseconds per linear and per
+    layer (max over ranks) and the layer's aggregate GB/s over the whole weights' bytes."""
+    import torch.distributed as dist
+    from jitnn_b200 import Tensor, sharded, synth
+    out = {"world": world, "exchange": "peer stores in the GEMV epilogue (batch 1), scatter kernel (batch 16)" if world > 1 else "none", "batches": {}}
+    weights, peers = {}, {}
+    for name, n, k in LAYER_70B:
+        lo, hi = sharded.row_range(n, rank, world)
+        copies = []
+        for c in range(2):
+            g = torch.Generator(device=device).manual_seed(7000 + n + 3 * k + 17 * rank + c)
+            wf = torch.randn(hi - lo, k, generator=g, device=device) * 0.02
+            raw = synth.quantize_q4_k(wf).cpu().numpy()
+            del wf
+            copies.append(Tensor.quantized("Q4_K", raw, hi - lo, k, device=device.index))
+        weights[name] = copies
+    side = torch.cuda.Stream(device)
+    for m in (1, 16):
+        g = torch.Generator(device=device).manual_seed(70 + m)
+        xs = {k: torch.randn(m, k, generator=g, device=device) for k in (8192, 28672)}
+        ys = {name: torch.empty(m, weights[name][0].shape()[0], device=device) for name, _, _ in LAYER_70B}
+        if world > 1:
+            peers = {name: sharded.PeerGather(n, m, device=device.index) for name, n, _ in LAYER_70B}
+
+        def one(name, k, c, sp):
+            w = weights[name][c]
+            if world > 1:
+                peers[name].linear(w, xs[k])
+            else:
+                _lib.check(L.jq_linear_f32(w._handle(), xs[k].data_ptr(), m, None, ys[name].data_ptr(), _lib.JQ_MEM_DEVICE, sp))
+
+        per = {}
+        with torch.cuda.stream(side):
+            sp = ctypes.c_void_p(side.cuda_stream)
+            for c in range(2):  # warm-up: scratch buffers, peer tables
+                for name, n, k in LAYER_70B:
+                    one(name, k, c, sp)
+            torch.cuda.synchronize(device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for c in range(2):
+                    for name, n, k in LAYER_70B:
+                        one(name, k, c, sp)
+            graph.replay()
+            torch.cuda.synchronize(device)
+            if world > 1:
+                dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 50
+            a.record(side)
+            for _ in range(reps):
+                graph.replay()
+            b.record(side)
+            torch.cuda.synchronize(device)
+            t = torch.tensor([a.elapsed_time(b) * 1e3 / (2 * reps)], device=device)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            layer_us = float(t.item())
+        layer_bytes = sum(n * k * BYTES_PER_WEIGHT + 4 * m * k + 4 * m * n for _, n, k in LAYER_70B)
+        out["batches"]["m%d" % m] = {"layer_us": round(layer_us, 2), "GBps": round(layer_bytes / layer_us / 1e3, 1),
+                                      "us_per_linear": round(layer_us / len(LAYER_70B), 2)}
+        del graph
+        for p in peers.values():
+            p.close()
+        peers = {}
+    for copies in weights.values():
+        for w in copies:
             w.release()
     return out
 
