@@ -234,6 +234,19 @@ JQ_API int jq_decoder_destroy(jq_decoder* d);
 JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_weight* w);
 JQ_API int jq_decoder_set_norm(jq_decoder* d, int layer, int which, const float* host_weights);
 JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table);
+/*
+ * The decoder split over the GPUs of one box by output rows of every linear (one process and one decoder per GPU; the
+ * reference never shards a model). jq_decoder_peer_bytes gives the payload size of the peer buffer a rank needs
+ * (jq_peer_alloc); jq_decoder_set_shard, called before any linear is set, makes the decoder rank `rank` of `world`
+ * (at most 8, dividing heads, kv_heads, hidden / 4 and vocab / 4) with peer_buffers[r] rank r's buffer (own at `rank`,
+ * the others from jq_peer_open). From then on jq_decoder_set_linear expects this rank's rows of each weight (n / world
+ * rows: whole heads of wq / wk / wv), norms and the embedding stay whole, and jq_decoder_forward must be called by all
+ * ranks with the same tokens and positions. Every rank gets the full logits and the next token, bitwise those of the
+ * unsharded decoder on its general kernels. A rank that stops calling makes the others' bounded waits give up:
+ * their forward returns JQ_ERR_TIMEOUT when it next waits for the stream.
+ */
+JQ_API int jq_decoder_peer_bytes(const jq_decoder* d, int64_t* payload_bytes);
+JQ_API int jq_decoder_set_shard(jq_decoder* d, int rank, int world, void* const* peer_buffers);
 /* Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 and appends their keys and values to
  * the cache. logits_host (or NULL) receives float32 [n_tokens, vocab], next_host (or NULL) the greedy next token after
  * each of them; the call waits for `stream` when either is requested, otherwise it only enqueues work. With a NULL

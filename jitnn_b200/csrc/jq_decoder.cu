@@ -735,6 +735,12 @@ struct jq_decoder {
     int warm_calls;      // single-token forwards issued so far
     cudaGraphExec_t graph;  // the single-token forward, captured on its second call
     cudaStream_t own_stream;  // used when the caller passes no stream (the legacy default stream cannot be captured)
+    // Row-sharded form (jq_decoder_set_shard): this rank holds rows [rank * n / world, (rank + 1) * n / world) of every
+    // linear, that is heads / world query heads, kv_heads / world key/value heads and hidden / world feed-forward
+    // features; the five gathered activations live in the ranks' peer buffers (jq_peer_alloc).
+    int world, rank;
+    void* peer_buf[8];
+    int64_t area[5];  // payload offsets: attention output, wo output, SwiGLU output, w2 output, logits
 };
 
 using namespace jq;
@@ -823,6 +829,20 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     d->warm_calls = 0;
     d->graph = nullptr;
     d->own_stream = nullptr;
+    d->world = 1;
+    d->rank = 0;
+    for (int r = 0; r < 8; r++) {
+        d->peer_buf[r] = nullptr;
+    }
+    {
+        // areas of the peer payload, each for MAX_TOKENS rows and a multiple of 256 bytes
+        const int64_t widths[5] = {dim, dim, hidden, dim, vocab};
+        int64_t off = 0;
+        for (int i = 0; i < 5; i++) {
+            d->area[i] = off;
+            off += ((int64_t)MAX_TOKENS * widths[i] * (int64_t)sizeof(float) + 255) / 256 * 256;
+        }
+    }
     const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
     d->splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
     struct { float** p; size_t n; } allocs[] = {
@@ -887,6 +907,55 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     return JQ_OK;
 }
 
+JQ_API int jq_decoder_peer_bytes(const jq_decoder* d, int64_t* payload_bytes) {
+    int rc = check_decoder(d, "jq_decoder_peer_bytes");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (payload_bytes == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_peer_bytes: null result pointer");
+    }
+    *payload_bytes = d->area[4] + ((int64_t)MAX_TOKENS * d->vocab * (int64_t)sizeof(float) + 255) / 256 * 256;
+    return JQ_OK;
+}
+
+JQ_API int jq_decoder_set_shard(jq_decoder* d, int rank, int world, void* const* peer_buffers) {
+    int rc = check_decoder(d, "jq_decoder_set_shard");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || (world > 1 && peer_buffers == nullptr)) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_shard: rank %d of %d (at most 8)", rank, world);
+    }
+    if (d->heads % world != 0 || d->kv_heads % world != 0 || d->hidden % (4 * world) != 0 || d->vocab % (4 * world) != 0) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_shard: %d ranks do not divide %d heads, %d key/value heads, %d / 4 hidden features and %d / 4 tokens",
+                    world, d->heads, d->kv_heads, d->hidden, d->vocab);
+    }
+    if (d->output != nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_shard: call it before the linears are set");
+    }
+    for (const jq_weight* w : d->lin) {
+        if (w != nullptr) {
+            return fail(JQ_ERR_INVALID, "jq_decoder_set_shard: call it before the linears are set");
+        }
+    }
+    for (int r = 0; r < world && world > 1; r++) {
+        if (peer_buffers[r] == nullptr) {
+            return fail(JQ_ERR_INVALID, "jq_decoder_set_shard: the buffer of rank %d is null", r);
+        }
+    }
+    if (d->graph != nullptr) {
+        cudaGraphExecDestroy(d->graph);
+        d->graph = nullptr;
+    }
+    d->world = world;
+    d->rank = rank;
+    for (int r = 0; r < 8; r++) {
+        d->peer_buf[r] = world > 1 && r < world ? peer_buffers[r] : nullptr;
+    }
+    return JQ_OK;
+}
+
 JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_weight* w) {
     int rc = check_decoder(d, "jq_decoder_set_linear");
     if (rc != JQ_OK) {
@@ -898,11 +967,11 @@ JQ_API int jq_decoder_set_linear(jq_decoder* d, int layer, int which, const jq_w
     const int64_t kv_dim = (int64_t)d->kv_heads * d->head_dim;
     int64_t n = 0, k = 0;
     if (layer == -1 && which == 7) {
-        n = d->vocab; k = d->dim;
+        n = d->vocab / d->world; k = d->dim;
     } else if (layer >= 0 && layer < d->layers && which >= 0 && which < 7) {
         const int64_t ns[7] = {d->dim, kv_dim, kv_dim, d->dim, d->hidden, d->hidden, d->dim};
         const int64_t ks[7] = {d->dim, d->dim, d->dim, d->dim, d->dim, d->dim, d->hidden};
-        n = ns[which]; k = ks[which];
+        n = ns[which] / d->world; k = ks[which];  // a rank of a sharded decoder holds its rows of every weight
     } else {
         return fail(JQ_ERR_INVALID, "jq_decoder_set_linear: layer %d, slot %d", layer, which);
     }
@@ -964,7 +1033,7 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table) {
 
 // Whether the single-token step can take the fused kernels: Q4_K / Q6_K linears, head_dim 128, sizes in whole super-blocks.
 static bool fused_step_possible(const jq_decoder* d) {
-    if (g_opt_decoder_fused.load() == 0 || d->head_dim != 128 || d->dim % 256 != 0 || d->hidden % 256 != 0 || d->dim > 32768) {
+    if (g_opt_decoder_fused.load() == 0 || d->world != 1 || d->head_dim != 128 || d->dim % 256 != 0 || d->hidden % 256 != 0 || d->dim > 32768) {
         return false;
     }
     for (const jq_weight* w : d->lin) {
@@ -1084,9 +1153,14 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
     return rc;
 }
 
+static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const TokenArgs* ta, cudaStream_t s);
+
 // Enqueues the forward of T tokens on s. Tokens and position come either from kernel arguments (ta != nullptr) or, for
 // the captured single-token graph, from the pinned staging words through a host-to-device copy.
 static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* ta, cudaStream_t s) {
+    if (d->world > 1) {
+        return enqueue_forward_sharded(d, T, max_keys, ta, s);
+    }
     if (T == 1 && fused_step_possible(d)) {
         return enqueue_forward_fused(d, max_keys, ta, s);
     }
@@ -1161,6 +1235,106 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
     }
     if (rc == JQ_OK) {
         argmax_kernel<<<T, 1024, 0, s>>>(d->logits, d->argmax, d->vocab);
+        LAUNCHED("argmax_kernel");
+    }
+    return rc;
+}
+
+// This rank's area `i` of gathered activations.
+static float* shard_area(const jq_decoder* d, int i) {
+    return reinterpret_cast<float*>(static_cast<uint8_t*>(d->peer_buf[d->rank]) + jq_peer_payload_offset() + d->area[i]);
+}
+
+// The forward of a rank of a row-sharded decoder. Every rank runs the replicated parts (embedding, norms, residual
+// adds, argmax) on the whole vectors and its own rows of every linear: wq / wk / wv give this rank's heads, whose
+// attention needs nothing from the other ranks; the attention output and the SwiGLU output are exchanged (each rank
+// stores its columns into every rank's copy, jq_peer_gather) because wo and w2 read all of them; wo, w2 and the output
+// projection store their rows into every rank's copy from the GEMV's epilogue (jq_linear_f32_peer). Five areas of the
+// peer buffer are used in turn, so that no area is the target of two exchanges in a row. Per row the arithmetic is the
+// unsharded decoder's (general kernels), so logits and tokens are bitwise those of one GPU.
+static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const TokenArgs* ta, cudaStream_t s) {
+    const int G = d->world, dim = d->dim, hd = d->head_dim;
+    const int heads = d->heads / G, kv_heads = d->kv_heads / G;
+    const int64_t kv_dim = (int64_t)kv_heads * hd, dim_l = dim / G, hidden_l = d->hidden / G, vocab_l = d->vocab / G;
+    float *A = shard_area(d, 0), *B = shard_area(d, 1), *C = shard_area(d, 2), *D = shard_area(d, 3), *E = shard_area(d, 4);
+    int rc = JQ_OK;
+    auto LIN = [&](const jq_weight* w, const float* in, float* out_) {
+        if (rc == JQ_OK) {
+            rc = linear_device(w, in, T, nullptr, out_, s);
+        }
+    };
+    auto PEER_LIN = [&](const jq_weight* w, const float* in, int64_t n_total, int64_t n_local, int area) {
+        if (rc == JQ_OK) {
+            rc = jq_linear_f32_peer(w, in, T, nullptr, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->rank, G, s);
+        }
+    };
+    auto GATHER = [&](const float* slice, int64_t n_total, int64_t n_local, int area) {
+        if (rc == JQ_OK) {
+            rc = jq_peer_gather(slice, T, n_local, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->rank, G, s);
+        }
+    };
+    auto LAUNCHED = [&](const char* name) {
+        count_launch(1);
+        if (rc == JQ_OK) {
+            rc = check_launch(name);
+        }
+    };
+    if (ta != nullptr) {
+        set_tokens_kernel<<<1, 32, 0, s>>>(*ta, d->tokens, d->pos);
+        LAUNCHED("set_tokens_kernel");
+    } else {
+        cudaError_t e = cudaMemcpyAsync(d->tokens, d->host_stage, MAX_TOKENS * sizeof(int), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(d->pos, d->host_stage + MAX_TOKENS, sizeof(int), cudaMemcpyHostToDevice, s);
+        }
+        if (e != cudaSuccess) {
+            return cuda_fail(e, "decoder inputs");
+        }
+    }
+    if (rc == JQ_OK) {
+        embed_kernel<<<T, 256, 0, s>>>(d->tokens, d->embed, d->x, dim, d->vocab);
+        LAUNCHED("embed_kernel");
+    }
+    const float scale = (float)(1.0 / std::sqrt((double)hd));
+    for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
+        const jq_weight* const* L = &d->lin[(size_t)l * 7];
+        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        LIN(L[0], d->xn, d->q);
+        LIN(L[1], d->xn, d->k);
+        LIN(L[2], d->xn, d->v);
+        if (rc != JQ_OK) break;
+        rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd);
+        LAUNCHED("rope_store_kernel");
+        const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
+        attention_partial_kernel<<<dim3(heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, heads, kv_heads, hd, d->splits,
+                                                                              scale);
+        LAUNCHED("attention_partial_kernel");
+        attention_combine_kernel<<<dim3(heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, heads, hd, d->splits, splits_now);
+        LAUNCHED("attention_combine_kernel");
+        GATHER(d->att, dim, dim_l, 0);
+        PEER_LIN(L[3], A, dim, dim_l, 1);
+        if (rc != JQ_OK) break;
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        LIN(L[4], d->xn, d->gate);
+        LIN(L[5], d->xn, d->up);
+        if (rc != JQ_OK) break;
+        const int64_t cnt = (int64_t)T * hidden_l;
+        swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
+        LAUNCHED("swiglu_kernel");
+        GATHER(d->act, d->hidden, hidden_l, 2);
+        PEER_LIN(L[6], C, dim, dim_l, 3);
+    }
+    if (rc == JQ_OK) {
+        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, D, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+        LAUNCHED("add_rmsnorm_kernel");
+        PEER_LIN(d->output, d->xn, d->vocab, vocab_l, 4);
+    }
+    if (rc == JQ_OK) {
+        argmax_kernel<<<T, 1024, 0, s>>>(E, d->argmax, d->vocab);
         LAUNCHED("argmax_kernel");
     }
     return rc;
@@ -1242,9 +1416,17 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
     }
     if (rc == JQ_OK && (logits_host != nullptr || next_host != nullptr)) {
         if (logits_host != nullptr) {
-            CK(cudaMemcpyAsync(logits_host, d->logits, (size_t)T * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s), "logits");
+            const float* src = d->world > 1 ? shard_area(d, 4) : d->logits;
+            CK(cudaMemcpyAsync(logits_host, src, (size_t)T * d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s), "logits");
         }
         CK(cudaStreamSynchronize(s), "jq_decoder_forward");
+        if (rc == JQ_OK && d->world > 1) {
+            int status = 0;
+            rc = peer_status(&status);
+            if (rc == JQ_OK && status != 0) {
+                rc = fail(JQ_ERR_TIMEOUT, "jq_decoder_forward: the slice of rank %d did not arrive (bounded wait gave up)", status - 32);
+            }
+        }
         if (rc == JQ_OK && next_host != nullptr) {
             for (int i = 0; i < T; i++) {
                 next_host[i] = d->host_stage[MAX_TOKENS + 1 + i];
