@@ -162,11 +162,19 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     L = jitnn_b200.load()
 
-    if args.leg in ("prefill", "decode", "formats"):
+    if args.leg in ("prefill", "decode", "formats", "decode70b"):
         # one leg alone, for profiler captures: no sweep, a short line of its own
         out = (prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else
-               formats_leg(torch, device, L, _lib) if args.leg == "formats" else decode_leg(torch, device, args.decode_shape))
-        print(json.dumps({"leg": args.leg, "result": out}), flush=True)
+               formats_leg(torch, device, L, _lib) if args.leg == "formats" else
+               decode_70b_leg(torch, device, rank, world, args.decode_shape) if args.leg == "decode70b" else
+               decode_leg(torch, device, args.decode_shape))
+        if rank == 0:
+            print(json.dumps({"leg": args.leg, "result": out}), flush=True)
+        if world > 1:
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            sys.stdout.flush()
+            os._exit(0)
         return
 
     pools, first_raw = make_weights(torch, device, rank, world)
@@ -543,6 +551,89 @@ def sharded_layer_leg(torch, device, rank, world, L, _lib):
     return out
 
 
+def decode_70b_leg(torch, device, rank, world, shape=None):
+    """BASELINE.json configs[4]: Llama-style decoder, 70B shape (80 layers, d 8192, 64 query / 8 key-value heads, FFN
+    28672, vocab 32000, all linears Q4_K), split by output rows over the ranks (jitnn_b200.LlamaDecoder sharded: local
+    heads, peer-store exchanges), a 256-token uniform-random prompt per sequence, then greedy decode at batch 16 (16
+    sequences in lockstep) and at batch 1. Every rank quantises only its own rows; the 80 layers cycle through 4
+    distinct seeded weight sets, each layer with a device copy of its own (the bytes streamed per token are those of 80
+    distinct layers). Wall-clock per step around the call that returns the next tokens, max over ranks."""
+    import numpy as np
+    import torch.distributed as dist
+    from jitnn_b200 import LlamaDecoder, synth
+    layers, dim, heads, kv_heads, hidden, vocab, prompt_len, gen, seqs = 80, 8192, 64, 8, 28672, 32000, 256, 34, 16
+    if shape:  # "layers,prompt,gen": a cut-down run for trials, not a bench number
+        layers, prompt_len, gen = (int(v) for v in shape.split(","))
+    kv_dim = kv_heads * (dim // heads)
+    dec = LlamaDecoder(layers, dim, heads, kv_heads, hidden, vocab, max_seq=prompt_len + 2 * gen + 8, device=device.index, sharded=world > 1)
+    dec.set_sequences(seqs)
+    names = [("wq", dim, dim), ("wk", kv_dim, dim), ("wv", kv_dim, dim), ("wo", dim, dim), ("w1", hidden, dim), ("w3", hidden, dim), ("w2", dim, hidden)]
+
+    def rows(n, k, seed):
+        g = torch.Generator(device=device).manual_seed(seed)
+        wf = torch.randn(n // world, k, generator=g, device=device) * 0.02
+        return ("Q4_K", synth.quantize_q4_k(wf).cpu().numpy().reshape(-1), n // world, k)
+
+    sets = [{name: rows(n, k, 9000 + 100 * c + 10 * i + rank) for i, (name, n, k) in enumerate(names)} for c in range(min(4, layers))]
+    ones = np.ones(dim, np.float32)
+    for l in range(layers):
+        w = {"layers.%d.%s" % (l, name): sets[l % len(sets)][name] for name, _, _ in names}
+        dec.load(w, local=True)
+        dec.load({"layers.%d.attention_norm" % l: ones, "layers.%d.ffn_norm" % l: ones})
+    dec.load({"output": rows(vocab, dim, 9900 + rank)}, local=True)
+    g = torch.Generator(device=device).manual_seed(2025)  # the same table on every rank
+    dec.load({"norm": ones, "tok_embeddings": (torch.randn(vocab, dim, generator=g, device=device) * 0.02).cpu().numpy()})
+    del sets
+    weight_bytes = (layers * sum(n * k for _, n, k in names) + vocab * dim) * BYTES_PER_WEIGHT
+    prompts = np.random.default_rng(13).integers(0, vocab, (seqs, prompt_len)).astype(np.int32)
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    first = np.zeros(seqs, np.int32)
+    for b in range(seqs):
+        for i in range(0, prompt_len - 16, 16):
+            dec.enqueue(prompts[b, i:i + 16], i, seq=b)
+        _, nxt = dec.forward(prompts[b, prompt_len - 16:], prompt_len - 16, want_logits=False, seq=b)
+        first[b] = nxt[-1]
+    t_prompt = time.perf_counter() - t0
+
+    def timed(step_fn, toks, pos):
+        out = []
+        for _ in range(2):  # untimed: the first runs eagerly, the second captures the step into a CUDA graph
+            toks = step_fn(toks, pos)
+            pos += 1
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(gen - 2):
+            toks = step_fn(toks, pos)
+            out.append(int(toks[0]))
+            pos += 1
+        dt = torch.tensor([(time.perf_counter() - t0) / (gen - 2)], device=device)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        return float(dt.item()), toks, pos, out
+
+    dt16, toks, pos, out16 = timed(lambda t, p: dec.forward_batch(t, p, want_logits=False)[1], first, prompt_len)
+    dt1, _, _, out1 = timed(lambda t, p: dec.forward([int(t[0])], p, want_logits=False)[1], toks[:1], pos)
+    dec.close()
+    peak, which = measured_peaks()
+    kv1 = 2 * layers * (prompt_len + gen + gen // 2) * kv_dim * 4
+    kv16 = 16 * 2 * layers * (prompt_len + gen // 2) * kv_dim * 4
+    return {"world": world,
+            "batch1": {"tokens_per_s": round(1.0 / dt1, 1), "ms_per_token": round(dt1 * 1e3, 4),
+                       "hbm_roofline_tokens_per_s": round(world * peak * 1e9 / (weight_bytes + kv1), 1),
+                       "frac": round((weight_bytes + kv1) / world / dt1 / 1e9 / peak, 4)},
+            "batch16": {"tokens_per_s": round(16.0 / dt16, 1), "ms_per_step": round(dt16 * 1e3, 4),
+                        "hbm_roofline_tokens_per_s": round(16 * world * peak * 1e9 / (weight_bytes + kv16), 1),
+                        "frac": round((weight_bytes + kv16) / world / dt16 / 1e9 / peak, 4)},
+            "prompt_tokens_per_s": round(seqs * prompt_len / t_prompt, 1), "weight_bytes_per_token": int(weight_bytes), "peak_source": "of " + which,
+            "config": "70B shape, %d layers, all Q4_K, rows split over %d GPU(s), 16 prompts of %d tokens in groups of 16, %d timed greedy steps "
+                      "per batch size, fp32 KV cache, general kernels (one per operator) in a CUDA graph" % (layers, world, prompt_len, gen - 2),
+            "first_tokens": {"batch16_seq0": out16[:6], "batch1": out1[:6]}}
+
+
 def decode_leg(torch, device, shape=None):
     """BASELINE.json configs[3]: Llama-style decoder, 7B shape (32 layers, d 4096, 32 heads, FFN 11008, vocab 32000),
     seeded N(0, 0.02) weights quantised Q4_K_M-style (Q6_K for wv, w2 and the output projection, Q4_K elsewhere),
@@ -674,8 +765,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the one-thread CPU baseline leg")
     ap.add_argument("--gather", default="peer", choices=["peer", "nccl", "none"],
                     help="N > 1: how every rank gets the whole y after each sharded linear (the library's peer-store exchange, or NCCL; none = no exchange, for diagnosis only)")
-    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode", "formats"],
-                    help="run only the prefill GEMM leg or only the 7B-shape decode leg (one GPU; for profiler captures)")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode", "formats", "decode70b"],
+                    help="run only the prefill GEMM leg, the format table, the 7B-shape decode leg (one GPU; for profiler captures) or the sharded 70B-shape decoder leg (any N)")
     ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
     ap.add_argument("--decode-shape", default=None, metavar="LAYERS,PROMPT,GEN",
                     help="with --leg decode: fewer layers / a shorter prompt and run, for profiler captures")

@@ -247,13 +247,26 @@ JQ_API int jq_decoder_set_embedding(jq_decoder* d, const float* host_table);
  */
 JQ_API int jq_decoder_peer_bytes(const jq_decoder* d, int64_t* payload_bytes);
 JQ_API int jq_decoder_set_shard(jq_decoder* d, int rank, int world, void* const* peer_buffers);
-/* Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 and appends their keys and values to
+/* Runs n_tokens (1..16) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 and appends their keys and values to
  * the cache. logits_host (or NULL) receives float32 [n_tokens, vocab], next_host (or NULL) the greedy next token after
  * each of them; the call waits for `stream` when either is requested, otherwise it only enqueues work. With a NULL
  * stream the decoder uses a stream of its own. Single-token calls that ask for the next token (the decode step) are
  * captured into a CUDA graph on their second occurrence and replayed afterwards. */
 JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
                        void* stream);
+/*
+ * Several independent sequences in one decoder (batched decode; the reference has no generation loop):
+ * jq_decoder_set_sequences gives the decoder key/value caches for `sequences` (1..16) sequences (what the caches held is
+ * lost); jq_decoder_forward_seq is jq_decoder_forward on sequence `seq` (jq_decoder_forward works on sequence 0);
+ * jq_decoder_forward_batch runs one token of each of the sequences 0 .. n_seqs - 1, all at position `pos`, as one pass
+ * over the weights: logits_host [n_seqs, vocab], next_host [n_seqs]. Repeated batch steps of one size that ask for the
+ * next tokens are captured into a CUDA graph like the single-token step.
+ */
+JQ_API int jq_decoder_set_sequences(jq_decoder* d, int sequences);
+JQ_API int jq_decoder_forward_seq(jq_decoder* d, int seq, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host,
+                                  int32_t* next_host, void* stream);
+JQ_API int jq_decoder_forward_batch(jq_decoder* d, const int32_t* tokens_host, int n_seqs, int pos, float* logits_host, int32_t* next_host,
+                                    void* stream);
 
 /*
  * GGUF file -> device weights (the reference's jitnn-gguf/.../GgufFile.java:100-175,329-418, whose GgufFile.tensor(name)

@@ -22,7 +22,7 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
 
 namespace {
 
-constexpr int MAX_TOKENS = 8;  // activation rows per forward call
+constexpr int MAX_TOKENS = 16;  // activation rows per forward call
 
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
     // fixed-order sum over a CTA of up to 1024 threads
@@ -122,10 +122,14 @@ __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ delt
 // grid (tokens, heads + 2 * kv_heads), head_dim / 2 threads.
 __global__ void rope_store_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ k_cache,
                                   float* __restrict__ v_cache, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                  const int* __restrict__ pos0, int heads, int kv_heads, int head_dim) {
+                                  const int* __restrict__ pos0, int heads, int kv_heads, int head_dim, int pos_step, int64_t tok_stride) {
+    // consecutive tokens of one sequence: pos_step 1, tok_stride 0; one token each of several sequences at the same
+    // position: pos_step 0, tok_stride = elements between two sequences' caches
     const int t = blockIdx.x, h = blockIdx.y, p = threadIdx.x, half = head_dim / 2;
-    const int pos = *pos0 + t;
+    const int pos = *pos0 + t * pos_step;
     const int kv_dim = kv_heads * head_dim;
+    k_cache += t * tok_stride;
+    v_cache += t * tok_stride;
     if (h < heads) {
         float* qh = q + ((int64_t)t * heads + h) * head_dim;
         const float c = cos_t[pos * half + p], s = sin_t[pos * half + p];
@@ -159,12 +163,14 @@ constexpr int ATT_THREADS = 128;
 __global__ void __launch_bounds__(ATT_THREADS) attention_partial_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                         const float* __restrict__ v_cache, float* __restrict__ part,
                                                                         const int* __restrict__ pos0, int heads, int kv_heads, int head_dim,
-                                                                        int splits, float scale) {
+                                                                        int splits, float scale, int pos_step, int64_t tok_stride) {
     __shared__ float qs[256];
     __shared__ float sc[ATT_CHUNK];
     __shared__ float scratch[32];
     const int h = blockIdx.x, sp = blockIdx.y, t = blockIdx.z;
-    const int keys = *pos0 + t + 1;
+    const int keys = *pos0 + t * pos_step + 1;
+    k_cache += t * tok_stride;
+    v_cache += t * tok_stride;
     const int k0 = sp * ATT_CHUNK;
     float* out = part + (((int64_t)t * heads + h) * splits + sp) * (head_dim + 2);
     if (k0 >= keys) {
@@ -722,7 +728,7 @@ struct jq_decoder {
     float* norms;        // [layers][2][dim] then final [dim]
     float* embed;        // [vocab][dim]
     float *cos_t, *sin_t;
-    float *k_cache, *v_cache;  // [layers][max_seq][kv_dim]
+    float *k_cache, *v_cache;  // [sequences][layers][max_seq][kv_dim]
     float *x, *xn, *q, *k, *v, *att, *proj, *gate, *up, *act, *logits;
     float* att_part;     // [tokens][heads][splits][head_dim + 2] partial attention results
     int splits;          // key chunks of ATT_CHUNK positions covering max_seq
@@ -732,8 +738,12 @@ struct jq_decoder {
     float* argmax_v;             // [ARGMAX_CTAS] per-CTA best value
     int* argmax_i;               // [ARGMAX_CTAS] per-CTA best index
     int* host_stage;     // pinned: [0..7] tokens in, [8] position in, [9..16] argmax out
-    int warm_calls;      // single-token forwards issued so far
-    cudaGraphExec_t graph;  // the single-token forward, captured on its second call
+    int sequences;       // key/value caches held (jq_decoder_set_sequences)
+    int cur_seq;         // the sequence the call being enqueued works on
+    bool cur_batch;      // the call being enqueued runs one token of each of the first T sequences
+    int graph_T, graph_seq;  // what the captured step was captured for (batch: graph_seq = -1)
+    int warm_calls;      // decode steps of that kind issued so far
+    cudaGraphExec_t graph;  // the decode step, captured on its second call
     cudaStream_t own_stream;  // used when the caller passes no stream (the legacy default stream cannot be captured)
     // Row-sharded form (jq_decoder_set_shard): this rank holds rows [rank * n / world, (rank + 1) * n / world) of every
     // linear, that is heads / world query heads, kv_heads / world key/value heads and hidden / world feed-forward
@@ -828,6 +838,11 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     d->output = nullptr;
     d->warm_calls = 0;
     d->graph = nullptr;
+    d->sequences = 1;
+    d->cur_seq = 0;
+    d->cur_batch = false;
+    d->graph_T = 0;
+    d->graph_seq = 0;
     d->own_stream = nullptr;
     d->world = 1;
     d->rank = 0;
@@ -1106,6 +1121,12 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         first_programmatic = false;
     }
     const float scale = (float)(1.0 / std::sqrt((double)d->head_dim));
+    // caches are [sequence][layer][position][kv_dim]; a call works on one sequence, or on one token of each of the first T
+    const size_t seq_elems = (size_t)d->layers * d->max_seq * kv_dim, seq_base = (size_t)d->cur_seq * seq_elems;
+    const int pos_step = d->cur_batch ? 0 : 1;
+    const int64_t tok_stride = d->cur_batch ? (int64_t)seq_elems : 0;
+    (void)pos_step;
+    (void)tok_stride;  // one token of one sequence here
     // the norm kernel's cluster: the most CTAs (up to 8) that still get whole super-blocks each
     int norm_ctas = 8;
     while (norm_ctas > 1 && dim % (256 * norm_ctas) != 0) {
@@ -1116,8 +1137,8 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
     const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
     for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
-        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
-        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         // attention block: x = embedding (first layer) or x += feed-forward output of the layer before; norm -> images
         CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
                        l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]})),
@@ -1195,10 +1216,14 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         LAUNCHED("embed_kernel");
     }
     const float scale = (float)(1.0 / std::sqrt((double)hd));
+    // caches are [sequence][layer][position][kv_dim]; a call works on one sequence, or on one token of each of the first T
+    const size_t seq_elems = (size_t)d->layers * d->max_seq * kv_dim, seq_base = (size_t)d->cur_seq * seq_elems;
+    const int pos_step = d->cur_batch ? 0 : 1;
+    const int64_t tok_stride = d->cur_batch ? (int64_t)seq_elems : 0;
     for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
-        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
-        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         // attention block; the residual add of the previous block's feed-forward output is fused into this norm
         add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
@@ -1206,12 +1231,12 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         LIN(L[1], d->xn, d->k);
         LIN(L[2], d->xn, d->v);
         if (rc != JQ_OK) break;
-        rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd);
+        rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd, pos_step, tok_stride);
         LAUNCHED("rope_store_kernel");
         // only the key chunks that can hold a position of this call are launched (all of them inside the captured graph)
         const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
         attention_partial_kernel<<<dim3(d->heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, d->heads, d->kv_heads, hd,
-                                                                                 d->splits, scale);
+                                                                                 d->splits, scale, pos_step, tok_stride);
         LAUNCHED("attention_partial_kernel");
         attention_combine_kernel<<<dim3(d->heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, d->heads, hd, d->splits, splits_now);
         LAUNCHED("attention_combine_kernel");
@@ -1296,21 +1321,25 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         LAUNCHED("embed_kernel");
     }
     const float scale = (float)(1.0 / std::sqrt((double)hd));
+    // caches are [sequence][layer][position][kv_dim]; a call works on one sequence, or on one token of each of the first T
+    const size_t seq_elems = (size_t)d->layers * d->max_seq * kv_dim, seq_base = (size_t)d->cur_seq * seq_elems;
+    const int pos_step = d->cur_batch ? 0 : 1;
+    const int64_t tok_stride = d->cur_batch ? (int64_t)seq_elems : 0;
     for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
-        float* kc = d->k_cache + (size_t)l * d->max_seq * kv_dim;
-        float* vc = d->v_cache + (size_t)l * d->max_seq * kv_dim;
+        float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
+        float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         LIN(L[0], d->xn, d->q);
         LIN(L[1], d->xn, d->k);
         LIN(L[2], d->xn, d->v);
         if (rc != JQ_OK) break;
-        rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd);
+        rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step, tok_stride);
         LAUNCHED("rope_store_kernel");
         const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
         attention_partial_kernel<<<dim3(heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, heads, kv_heads, hd, d->splits,
-                                                                              scale);
+                                                                              scale, pos_step, tok_stride);
         LAUNCHED("attention_partial_kernel");
         attention_combine_kernel<<<dim3(heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, heads, hd, d->splits, splits_now);
         LAUNCHED("attention_combine_kernel");
@@ -1340,19 +1369,26 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
     return rc;
 }
 
-// Runs n_tokens (1..8) consecutive tokens at positions pos0 .. pos0 + n_tokens - 1 through the decoder and appends their
-// keys and values to the cache. logits_host (may be NULL) receives [n_tokens, vocab], next_host (may be NULL) the greedy
-// next token after each of them. Synchronises `stream` before returning when either output is requested.
-// A single-token call that asks for the next token is the decode step: its second occurrence is captured into a CUDA
-// graph (all launches of the step read token and position from memory), later ones replay the graph.
-JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host, void* stream) {
+// Runs n_tokens consecutive tokens of sequence `seq` at positions pos0 .. pos0 + n_tokens - 1 (batch false), or one token of
+// each of the sequences 0 .. n_tokens - 1, all at position pos0 (batch true), and appends their keys and values to the
+// caches. logits_host (may be NULL) receives [n_tokens, vocab], next_host (may be NULL) the greedy next token after each
+// of them. Synchronises `stream` before returning when either output is requested.
+// A call that asks for the next token of a single token, or of a batch, is a decode step: the second step of the same
+// kind (same sequence, or same batch size) is captured into a CUDA graph (all launches of the step read tokens and
+// position from memory), later ones replay the graph.
+static int decoder_forward(jq_decoder* d, int seq, bool batch, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
+                           void* stream) {
     int rc = check_decoder(d, "jq_decoder_forward");
     if (rc != JQ_OK) {
         return rc;
     }
-    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > MAX_TOKENS || pos0 < 0 || pos0 + n_tokens > d->max_seq) {
+    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > MAX_TOKENS || pos0 < 0 || pos0 + (batch ? 1 : n_tokens) > d->max_seq) {
         return fail(JQ_ERR_INVALID, "jq_decoder_forward: %d tokens at position %d (at most %d per call, %d positions)", n_tokens, pos0, MAX_TOKENS,
                     d->max_seq);
+    }
+    if (seq < 0 || seq >= d->sequences || (batch && n_tokens > d->sequences)) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_forward: sequence %d, batch of %d: the decoder holds %d sequence(s) (jq_decoder_set_sequences)", seq,
+                    batch ? n_tokens : 1, d->sequences);
     }
     if (d->output == nullptr) {
         return fail(JQ_ERR_INVALID, "jq_decoder_forward: the output projection is not set");
@@ -1370,7 +1406,19 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
     // all state of a decoder is private to it and its inputs come from the host, so its own stream is as good as any
     cudaStream_t s = stream != nullptr ? (cudaStream_t)stream : d->own_stream;
     const int T = n_tokens;
-    const bool decode_step = T == 1 && next_host != nullptr && g_opt_decoder_graph.load() != 0;
+    const bool decode_step = (T == 1 || batch) && next_host != nullptr && g_opt_decoder_graph.load() != 0;
+    d->cur_seq = batch ? 0 : seq;
+    d->cur_batch = batch && T > 1;  // a batch of one is the single-token step of sequence 0
+    if (decode_step && (d->graph_T != T || d->graph_seq != (d->cur_batch ? -1 : d->cur_seq))) {
+        // another kind of step than the one counted (and perhaps captured) so far
+        if (d->graph != nullptr) {
+            cudaGraphExecDestroy(d->graph);
+            d->graph = nullptr;
+        }
+        d->warm_calls = 0;
+        d->graph_T = T;
+        d->graph_seq = d->cur_batch ? -1 : d->cur_seq;
+    }
     auto CK = [&](cudaError_t e, const char* what) {
         if (rc == JQ_OK && e != cudaSuccess) {
             rc = cuda_fail(e, what);
@@ -1378,14 +1426,16 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
     };
     if (decode_step && d->warm_calls >= 1) {
         // the staging words are free again: every decode step ends with a wait for the stream
-        d->host_stage[0] = tokens_host[0];
+        for (int i = 0; i < T; i++) {
+            d->host_stage[i] = tokens_host[i];
+        }
         d->host_stage[MAX_TOKENS] = pos0;
         if (d->graph == nullptr) {
             cudaGraph_t g = nullptr;
             CK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
             if (rc == JQ_OK) {
-                rc = enqueue_forward(d, 1, d->max_seq, nullptr, s);
-                cudaError_t e = cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, sizeof(int), cudaMemcpyDeviceToHost, s);
+                rc = enqueue_forward(d, T, d->max_seq, nullptr, s);
+                cudaError_t e = cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, T * sizeof(int), cudaMemcpyDeviceToHost, s);
                 cudaError_t e2 = cudaStreamEndCapture(s, &g);
                 CK(e, "argmax copy");
                 CK(e2, "cudaStreamEndCapture");
@@ -1406,7 +1456,7 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
             ta.tokens[i] = i < T ? tokens_host[i] : 0;
         }
         ta.pos0 = pos0;
-        rc = enqueue_forward(d, T, pos0 + T, &ta, s);
+        rc = enqueue_forward(d, T, pos0 + (batch ? 1 : T), &ta, s);
         if (rc == JQ_OK && next_host != nullptr) {
             CK(cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, T * sizeof(int), cudaMemcpyDeviceToHost, s), "argmax");
         }
@@ -1437,6 +1487,58 @@ JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_t
         cudaSetDevice(prev);
     }
     return rc;
+}
+
+JQ_API int jq_decoder_forward(jq_decoder* d, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host, void* stream) {
+    return decoder_forward(d, 0, false, tokens_host, n_tokens, pos0, logits_host, next_host, stream);
+}
+
+JQ_API int jq_decoder_forward_seq(jq_decoder* d, int seq, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
+                                  void* stream) {
+    return decoder_forward(d, seq, false, tokens_host, n_tokens, pos0, logits_host, next_host, stream);
+}
+
+JQ_API int jq_decoder_forward_batch(jq_decoder* d, const int32_t* tokens_host, int n_seqs, int pos, float* logits_host, int32_t* next_host, void* stream) {
+    return decoder_forward(d, 0, true, tokens_host, n_seqs, pos, logits_host, next_host, stream);
+}
+
+// Key/value caches for `sequences` (1..16) independent sequences; what the caches held is lost.
+JQ_API int jq_decoder_set_sequences(jq_decoder* d, int sequences) {
+    int rc = check_decoder(d, "jq_decoder_set_sequences");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (sequences < 1 || sequences > MAX_TOKENS) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_set_sequences: %d sequences (1 to %d)", sequences, MAX_TOKENS);
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    JQ_CUDA(cudaSetDevice(d->device));
+    JQ_CUDA(cudaDeviceSynchronize());
+    if (d->graph != nullptr) {
+        cudaGraphExecDestroy(d->graph);  // the captured step holds the old cache addresses
+        d->graph = nullptr;
+    }
+    d->warm_calls = 0;
+    d->graph_T = 0;
+    const size_t elems = (size_t)sequences * d->layers * d->max_seq * d->kv_heads * d->head_dim;
+    float *kc = nullptr, *vc = nullptr;
+    cudaError_t e = cudaMalloc(&kc, elems * sizeof(float));
+    if (e == cudaSuccess) {
+        e = cudaMalloc(&vc, elems * sizeof(float));
+    }
+    if (e != cudaSuccess) {
+        cudaFree(kc);
+        if (prev >= 0) cudaSetDevice(prev);
+        return cuda_fail(e, "jq_decoder_set_sequences");
+    }
+    cudaFree(d->k_cache);
+    cudaFree(d->v_cache);
+    d->k_cache = kc;
+    d->v_cache = vc;
+    d->sequences = sequences;
+    if (prev >= 0) cudaSetDevice(prev);
+    return JQ_OK;
 }
 
 }  // extern "C"

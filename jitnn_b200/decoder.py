@@ -86,19 +86,35 @@ class LlamaDecoder:
                 else:
                     check(L.jq_decoder_set_norm(self._h, int(parts[1]), 0 if parts[2] == "attention_norm" else 1, a.ctypes.data))
 
-    def forward(self, tokens, pos0, want_logits=True, stream=None):
-        """Runs up to 8 tokens starting at position pos0; returns (logits [n, vocab] or None, next tokens [n])."""
+    def forward(self, tokens, pos0, want_logits=True, stream=None, seq=0):
+        """Runs up to 16 tokens of sequence `seq` starting at position pos0; returns (logits [n, vocab] or None, next tokens [n])."""
         toks = np.ascontiguousarray(tokens, dtype=np.int32)
         n = toks.size
         logits = np.empty((n, self.vocab), dtype=np.float32) if want_logits else None
         nxt = np.empty(n, dtype=np.int32)
-        check(_lib.load().jq_decoder_forward(self._h, toks.ctypes.data, n, pos0, None if logits is None else logits.ctypes.data, nxt.ctypes.data, stream))
+        check(_lib.load().jq_decoder_forward_seq(self._h, seq, toks.ctypes.data, n, pos0, None if logits is None else logits.ctypes.data,
+                                                 nxt.ctypes.data, stream))
         return logits, nxt
 
-    def enqueue(self, tokens, pos0, stream=None):
+    def enqueue(self, tokens, pos0, stream=None, seq=0):
         """As forward, but only enqueues the work (no outputs, no wait)."""
         toks = np.ascontiguousarray(tokens, dtype=np.int32)
-        check(_lib.load().jq_decoder_forward(self._h, toks.ctypes.data, toks.size, pos0, None, None, stream))
+        check(_lib.load().jq_decoder_forward_seq(self._h, seq, toks.ctypes.data, toks.size, pos0, None, None, stream))
+
+    def set_sequences(self, sequences):
+        """Key/value caches for `sequences` (1..16) independent sequences; cached positions are lost."""
+        check(_lib.load().jq_decoder_set_sequences(self._h, sequences))
+
+    def forward_batch(self, tokens, pos, want_logits=True, stream=None):
+        """One token of each of the sequences 0 .. len(tokens) - 1, all at position `pos`, in one pass over the weights;
+        returns (logits [n, vocab] or None, next tokens [n])."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        n = toks.size
+        logits = np.empty((n, self.vocab), dtype=np.float32) if want_logits else None
+        nxt = np.empty(n, dtype=np.int32)
+        check(_lib.load().jq_decoder_forward_batch(self._h, toks.ctypes.data, n, pos, None if logits is None else logits.ctypes.data,
+                                                   nxt.ctypes.data, stream))
+        return logits, nxt
 
     def close(self, collective=True):
         """Collective for a sharded decoder: the ranks unmap each other's buffers before any is freed."""

@@ -69,6 +69,48 @@ def run_prompt_and_greedy(dim, heads, kv_heads, prompt_len):
     dec.close()
 
 
+@pytest.mark.parametrize("dim,heads,kv_heads,n_seqs", [(512, 4, 2, 3), (256, 4, 4, 16)])
+def test_batched_decode_matches_the_sequences_run_alone(dim, heads, kv_heads, n_seqs):
+    """One token of each of several sequences per step (one pass over the weights) against the same sequences decoded
+    one at a time: logits within the decoder tolerance, same greedy tokens where the margin is decisive."""
+    prompt_len, steps = 13, 6
+    cfg = llama_oracle.Config(layers=2, dim=dim, heads=heads, kv_heads=kv_heads, hidden=2 * dim, vocab=512, max_seq=prompt_len + steps + 2)
+    weights, dec = build(cfg, seed=77)
+    dec.set_sequences(n_seqs)
+    rng = np.random.default_rng(3)
+    prompts = rng.integers(0, cfg.vocab, (n_seqs, prompt_len)).astype(np.int32)
+    # alone: sequence b lives in cache slot b and advances with single-token calls
+    alone_logits = np.zeros((steps, n_seqs, cfg.vocab), np.float32)
+    first = np.zeros(n_seqs, np.int32)
+    for b in range(n_seqs):
+        for i in range(0, prompt_len, 8):
+            _, nxt = dec.forward(prompts[b, i:i + 8], i, seq=b)
+        first[b] = nxt[-1]
+        tok = int(first[b])
+        for t in range(steps):
+            lg, nxt = dec.forward([tok], prompt_len + t, seq=b)
+            alone_logits[t, b] = lg[0]
+            tok = int(nxt[0])
+    # batched: the prompts again (the caches are rewritten position by position), then lockstep steps
+    for b in range(n_seqs):
+        for i in range(0, prompt_len, 8):
+            dec.forward(prompts[b, i:i + 8], i, seq=b)
+    toks = first.copy()
+    scale = np.abs(alone_logits).max()
+    for t in range(steps):
+        lg, nxt = dec.forward_batch(toks, prompt_len + t)
+        assert np.abs(lg - alone_logits[t]).max() <= 2e-4 * scale, (t, float(np.abs(lg - alone_logits[t]).max() / scale))
+        assert np.array_equal(nxt, np.argmax(lg, axis=1))
+        ref_next = np.argmax(alone_logits[t], axis=1)
+        top = np.sort(alone_logits[t], axis=1)[:, -2:]
+        decisive = (top[:, 1] - top[:, 0]) > MARGIN * scale
+        assert np.array_equal(nxt[decisive], ref_next[decisive])
+        toks = ref_next.astype(np.int32)  # stay on the path of the sequences run alone
+    with pytest.raises(ValueError, match="holds %d sequence" % n_seqs):
+        dec.forward([1], 0, seq=n_seqs)
+    dec.close()
+
+
 def test_forward_argument_checks():
     cfg = llama_oracle.Config(layers=1, dim=256, heads=4, kv_heads=4, hidden=256, vocab=64, max_seq=8)
     dec = LlamaDecoder(cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq)
@@ -76,8 +118,8 @@ def test_forward_argument_checks():
         dec.forward([1], 0)
     weights = llama_oracle.random_model(cfg, 3)
     dec.load(weights)
-    with pytest.raises(ValueError, match="at most 8 per call"):
-        dec.forward(list(range(9)), 0)
+    with pytest.raises(ValueError, match="at most 16 per call"):
+        dec.forward(list(range(17)), 0)
     with pytest.raises(ValueError, match="8 positions"):
         dec.forward([1, 2], 7)
     with pytest.raises(ValueError, match="inconsistent sizes"):
