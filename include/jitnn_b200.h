@@ -133,6 +133,15 @@ JQ_API int jq_linear_bf16(const jq_weight* w, const uint16_t* x_bf16, int64_t m,
                    void* stream);
 
 /*
+ * Input gradient of the linear: gx[m, k] = g[m, n] . dequant(W), float32 (the backward of Gguf.linear and Quant.linear,
+ * ops/Gguf.java:208-212 and ops/Quant.java:191-197: the quantised weight gets no gradient, the bias gradient is the
+ * column sum of g and needs no weight). The weight is read once per four (Q6_K: one, 4-bit formats: two) rows of g, in
+ * its quantised form, with FP32 accumulation (the reference accumulates in double; results agree within 1e-3 relative).
+ * `mem` as for jq_linear_f32; device pointers must be 16-byte aligned.
+ */
+JQ_API int jq_linear_backward_f32(const jq_weight* w, const float* g, int64_t m, float* gx, int mem, void* stream);
+
+/*
  * Waits for the work enqueued on `device` and reports, then clears, the status word of its kernels: 0, or the code of
  * the first bounded device-side wait that gave up (the prefill kernel's barrier waits are bounded instead of being
  * able to hang). Calls with host memory check this themselves and return JQ_ERR_TIMEOUT; callers that enqueue with

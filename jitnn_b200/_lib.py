@@ -30,6 +30,7 @@ SIGNATURES = {
     "jq_weight_download": (c_int, [vp, vp, c_i64]),
     "jq_dequantize": (c_int, [vp, vp, c_int, vp]),
     "jq_linear_f32": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
+    "jq_linear_backward_f32": (c_int, [vp, vp, c_i64, vp, c_int, vp]),
     "jq_linear_bf16": (c_int, [vp, vp, c_i64, vp, vp, c_int, vp]),
     "jq_linear_q4k_f32_noalloc": (c_int, [vp, vp, c_i64, vp, vp, vp]),
     "jq_device_status": (c_int, [c_int, ctypes.POINTER(c_int)]),

@@ -518,6 +518,59 @@ int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bi
     return JQ_OK;
 }
 
+int jq_linear_backward_f32(const jq_weight* w, const float* g, int64_t m, float* gx, int mem, void* stream) {
+    int rc = check_weight(w, "jq_linear_backward_f32");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (!has_linear_kernel(w->type)) {
+        return fail(JQ_ERR_UNSUPPORTED, "%s linear backward: the format is dequantise-only", type_name(w->type));
+    }
+    if (m < 0) {
+        return fail(JQ_ERR_INVALID, "%s linear backward: gradient of %lld rows and weight [%lld, %lld]", type_name(w->type), (long long)m,
+                    (long long)w->n, (long long)w->k);
+    }
+    if (m == 0 || w->k == 0) {
+        return JQ_OK;
+    }
+    if (gx == nullptr || (g == nullptr && w->n > 0)) {
+        return fail(JQ_ERR_INVALID, "%s linear backward: null gradient", type_name(w->type));
+    }
+    DeviceGuard guard(w->device);
+    const size_t gb = align256((size_t)m * w->n * 4), xb = (size_t)m * w->k * 4;
+    if (mem == JQ_MEM_DEVICE) {
+        if (((uintptr_t)gx & 15) != 0) {
+            return fail(JQ_ERR_INVALID, "%s linear backward: device pointers must be 16-byte aligned", type_name(w->type));
+        }
+        if (w->n == 0) {
+            JQ_CUDA(cudaMemsetAsync(gx, 0, xb, (cudaStream_t)stream));
+            return JQ_OK;
+        }
+        return launch_linear_backward(view_of(w), g, m, gx, (cudaStream_t)stream);
+    }
+    if (mem != JQ_MEM_HOST) {
+        return fail(JQ_ERR_INVALID, "%s linear backward: unknown memory kind %d", type_name(w->type), mem);
+    }
+    Staging* st;
+    rc = staging_for(w->device, gb + xb, &st);
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    float* dgx = (float*)(st->dev + gb);
+    if (w->n == 0) {
+        JQ_CUDA(cudaMemsetAsync(dgx, 0, xb, st->stream));
+    } else {
+        JQ_CUDA(cudaMemcpyAsync(st->dev, g, (size_t)m * w->n * 4, cudaMemcpyHostToDevice, st->stream));
+        rc = launch_linear_backward(view_of(w), (const float*)st->dev, m, dgx, st->stream);
+        if (rc != JQ_OK) {
+            return rc;
+        }
+    }
+    JQ_CUDA(cudaMemcpyAsync(gx, dgx, xb, cudaMemcpyDeviceToHost, st->stream));
+    JQ_CUDA(cudaStreamSynchronize(st->stream));
+    return JQ_OK;
+}
+
 int jq_linear_bf16(const jq_weight* w, const uint16_t* x, int64_t m, const float* bias, float* y, int mem, void* stream) {
     int rc = check_weight(w, "jq_linear_bf16");
     if (rc != JQ_OK) {

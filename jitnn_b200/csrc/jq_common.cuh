@@ -96,6 +96,8 @@ int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, i
 int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, cudaStream_t s);
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
 int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
+// gx [m, k] = g [m, n] . dequant(W) (jq_backward.cu).
+int launch_linear_backward(const View& v, const float* g, int64_t m, float* gx, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
 // Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
 // Where a GEMV's outputs go besides (or instead of) y when the linear is sharded by rows over several GPUs: every

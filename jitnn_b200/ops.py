@@ -192,6 +192,37 @@ def _linear(x, w, bias, who):
     return y
 
 
+def _linear_backward(g, w):
+    L = _lib.load()
+    if not isinstance(w, Tensor):
+        raise ValueError("linear backward: weight is not a quantised tensor")
+    n, k = w.shape()
+    if _is_torch(g):
+        import torch
+        if g.dtype != torch.float32:
+            raise ValueError("needs an FP32 tensor, got %s" % g.dtype)
+        if g.dim() == 0 or g.shape[-1] != n:
+            raise ValueError("%s linear backward: gradient %s and weight %s" % (w.dtype().name, list(g.shape), list(w.shape())))
+        if not g.is_cuda or g.device.index != w.device():
+            raise ValueError("%s linear backward: gradient on %s, weight on cuda:%d" % (w.dtype().name, g.device, w.device()))
+        gc = g.contiguous()
+        m = gc.numel() // n if n else int(np.prod(g.shape[:-1]))
+        gx = torch.empty(list(g.shape[:-1]) + [k], dtype=torch.float32, device=g.device)
+        with torch.cuda.device(g.device):
+            check(L.jq_linear_backward_f32(w._handle(), gc.data_ptr(), m, gx.data_ptr(), JQ_MEM_DEVICE, _stream_of(g)))
+        return gx
+    g = np.asarray(g)
+    if g.dtype != np.float32:
+        raise ValueError("needs an FP32 tensor, got %s" % g.dtype)
+    if g.ndim == 0 or g.shape[-1] != n:
+        raise ValueError("%s linear backward: gradient %s and weight %s" % (w.dtype().name, list(g.shape), list(w.shape())))
+    gc = np.ascontiguousarray(g)
+    m = gc.size // n if n else int(np.prod(g.shape[:-1]))
+    gx = np.empty(g.shape[:-1] + (k,), dtype=np.float32)
+    check(L.jq_linear_backward_f32(w._handle(), gc.ctypes.data, m, gx.ctypes.data, JQ_MEM_HOST, None))
+    return gx
+
+
 def _dequantize(w, out=None):
     L = _lib.load()
     n, k = w.shape()
@@ -214,6 +245,12 @@ class Gguf:
     @staticmethod
     def dequantize(w, out=None):
         return _dequantize(w, out)
+
+    @staticmethod
+    def linearBackward(g, w):
+        """The input gradient of linear: gx [..., K] = g [..., N] . dequant(W) (ops/Gguf.java:208-212; the weight gets
+        no gradient, the bias gradient is the column sum of g)."""
+        return _linear_backward(g, w)
 
     @staticmethod
     def linearBf16(x, w, bias=None):
@@ -265,6 +302,13 @@ class Quant:
         if not isinstance(w, Tensor) or w.dtype() != DType.Q8_0:
             raise ValueError("Q8_0 linear: weight %s" % (w.dtype().name if isinstance(w, Tensor) else type(w)))
         return _linear(x, w, bias, "Quant.linear")
+
+    @staticmethod
+    def linearBackward(g, w):
+        """gx = g . dequant(W) for a Q8_0 weight (ops/Quant.java:191-197)."""
+        if not isinstance(w, Tensor) or w.dtype() != DType.Q8_0:
+            raise ValueError("Q8_0 linear backward: weight %s" % (w.dtype().name if isinstance(w, Tensor) else type(w)))
+        return _linear_backward(g, w)
 
     @staticmethod
     def dequantize(q, out=None):

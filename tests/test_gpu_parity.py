@@ -71,6 +71,44 @@ def test_golden_linear(golden_cases, fmt, rows):
     golden_close(golden_cases[name + ".out"], y, what=name)
 
 
+@pytest.mark.parametrize("rows", [1, 5, 40])
+@pytest.mark.parametrize("fmt", GOLDEN_FORMATS)
+def test_golden_linear_input_gradient(golden_cases, fmt, rows):
+    """The golden cases' gradient with respect to x for the loss sum(w * out): gx = w . dequant(W)."""
+    name = "gguf_linear_%s_r%d" % (fmt, rows)
+    code, n = golden_cases[name + ".attrs"]
+    w = Tensor.quantized(CODE_TO_TYPE[int(code)], golden_cases[name + ".in1"], int(n), 512)
+    gx = Gguf.linearBackward(golden_cases[name + ".w"], w)
+    assert gx.shape == (rows, 512)
+    golden_close(golden_cases[name + ".grad0"], gx, what=name + ".grad0")
+
+
+@pytest.mark.parametrize("t", LINEAR_TYPES)
+@pytest.mark.parametrize("n,k,m", [(300, 1024, 3), (4096, 4096, 8), (17, 256, 1), (11008, 4096, 5)])
+def test_linear_backward_vs_oracle(t, n, k, m):
+    """gx = g . dequant(W) against float64 over the oracle's dequantised weight, 1e-3 of the largest magnitude; device
+    and host memory give the same bits."""
+    import torch
+    raw = synth.random_valid_blocks(t, n, k, seed=n + k + m).numpy()
+    w = Tensor.quantized(t, raw, n, k)
+    g = np.random.default_rng(n + m).standard_normal((m, n)).astype(np.float32)
+    ref = g.astype(np.float64) @ oracle.dequantize(t, raw).reshape(n, k).astype(np.float64)
+    gx = Gguf.linearBackward(g, w)
+    assert np.abs(gx - ref).max() <= 1e-3 * np.abs(ref).max()
+    gx_dev = Gguf.linearBackward(torch.from_numpy(g).cuda(), w).cpu().numpy()
+    assert np.array_equal(bits(gx), bits(gx_dev))
+
+
+def test_linear_backward_edges():
+    raw = synth.random_valid_blocks("Q4_K", 8, 256, seed=1).numpy()
+    w = Tensor.quantized("Q4_K", raw, 8, 256)
+    assert Gguf.linearBackward(np.zeros((0, 8), np.float32), w).shape == (0, 256)
+    with pytest.raises(ValueError, match="gradient"):
+        Gguf.linearBackward(np.zeros((2, 9), np.float32), w)
+    empty = Tensor.quantized("Q4_K", np.zeros(0, np.uint8), 0, 256)
+    assert np.array_equal(Gguf.linearBackward(np.zeros((2, 0), np.float32), empty), np.zeros((2, 256), np.float32))
+
+
 @pytest.mark.parametrize("t", LINEAR_TYPES)
 def test_fixture_linear_like_gguf_checks(fixture_gguf, t):
     rng = np.random.default_rng(LINEAR_TYPES.index(t))

@@ -38,6 +38,20 @@ def test_golden_linear(golden_cases, fmt, rows):
     golden_close(golden_cases[name + ".out"], y, what=name)
 
 
+@pytest.mark.parametrize("rows", [1, 5, 40])
+@pytest.mark.parametrize("fmt", GOLDEN_FORMATS)
+def test_golden_linear_gradients(golden_cases, fmt, rows):
+    """The golden cases differentiate sum(w * out): grad0 = w . dequant(W) (the operator's input gradient,
+    ops/Gguf.java:208-212) and grad2 = the column sums of w (the bias gradient); there is no weight gradient."""
+    name = "gguf_linear_%s_r%d" % (fmt, rows)
+    code, n = golden_cases[name + ".attrs"]
+    W = oracle.dequantize(CODE_TO_TYPE[int(code)], golden_cases[name + ".in1"]).reshape(int(n), 512).astype(np.float64)
+    g = golden_cases[name + ".w"].astype(np.float64)
+    golden_close(golden_cases[name + ".grad0"], g @ W, what=name + ".grad0")
+    golden_close(golden_cases[name + ".grad2"], g.sum(axis=0), what=name + ".grad2")
+    assert name + ".grad1" not in golden_cases
+
+
 @pytest.mark.parametrize("t", LINEAR_TYPES)
 def test_fixture_linear_like_gguf_checks(fixture_gguf, t):
     """y = x W^T + b for 1, 5 and 40 rows against a double-precision product with expect.<T>."""
