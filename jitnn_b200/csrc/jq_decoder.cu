@@ -1059,6 +1059,46 @@ static bool fused_step_possible(const jq_decoder* d) {
     return d->output != nullptr && (d->output->type == JQ_TYPE_Q4_K || d->output->type == JQ_TYPE_Q6_K);
 }
 
+// The image buffers the kernels in front of the given linears have to fill.
+static Images decoder_images_for(const jq_decoder* d, std::initializer_list<const jq_weight*> consumers) {
+    Images im{nullptr, nullptr};
+    for (const jq_weight* w : consumers) {
+        if (w->type == JQ_TYPE_Q4_K) im.q4k = d->img_q4k;
+        if (w->type == JQ_TYPE_Q6_K) im.q6k = d->img_q6k;
+    }
+    return im;
+}
+
+// y = W x (and y2 = W2 x in the same launch when both are Q4_K), x being the image written just before
+static int decoder_gemv_imaged(jq_decoder* d, const jq_weight* w, float* y, const jq_weight* w2, float* y2, cudaStream_t gs) {
+    int rc = JQ_OK;
+    for (int pass = 0; pass < 2 && rc == JQ_OK; pass++) {
+        const jq_weight* cur = pass == 0 ? w : w2;
+        float* out_ = pass == 0 ? y : y2;
+        if (cur == nullptr) {
+            break;
+        }
+        const View v{cur->q, cur->aux, cur->n, cur->k, cur->type};
+        bool handled = false;
+        if (cur->type == JQ_TYPE_Q4_K) {
+            if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
+                const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
+                rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, gs, &handled);
+                pass = 1;  // both done
+            } else {
+                rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, gs, &handled);
+            }
+        } else {
+            rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, gs, &handled);
+        }
+        if (rc == JQ_OK && !handled) {
+            rc = fail(JQ_ERR_UNSUPPORTED, "decoder: a [%lld, %lld] linear is outside what the tensor-core GEMV takes (set option decoder_fused to 0)",
+                      (long long)cur->n, (long long)cur->k);
+        }
+    }
+    return rc;
+}
+
 // The forward of one token with the fused kernels (see pdl_enter above). `first_programmatic` is false when the
 // operation before the first kernel in the stream is not a kernel (the token copy of the captured graph).
 static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* ta, cudaStream_t s) {
@@ -1071,39 +1111,10 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
             rc = cuda_fail(e, name);
         }
     };
-    auto images_for = [&](std::initializer_list<const jq_weight*> consumers) {
-        Images im{nullptr, nullptr};
-        for (const jq_weight* w : consumers) {
-            if (w->type == JQ_TYPE_Q4_K) im.q4k = d->img_q4k;
-            if (w->type == JQ_TYPE_Q6_K) im.q6k = d->img_q6k;
-        }
-        return im;
-    };
-    // y = W x (and y2 = W2 x in the same launch when both are Q4_K), x being the image written just before
+    auto images_for = [&](std::initializer_list<const jq_weight*> consumers) { return decoder_images_for(d, consumers); };
     auto GEMV = [&](const jq_weight* w, float* y, const jq_weight* w2, float* y2, cudaStream_t gs) {
-        for (int pass = 0; pass < 2 && rc == JQ_OK; pass++) {
-            const jq_weight* cur = pass == 0 ? w : w2;
-            float* out_ = pass == 0 ? y : y2;
-            if (cur == nullptr) {
-                break;
-            }
-            const View v{cur->q, cur->aux, cur->n, cur->k, cur->type};
-            bool handled = false;
-            if (cur->type == JQ_TYPE_Q4_K) {
-                if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
-                    const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
-                    rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, gs, &handled);
-                    pass = 1;  // both done
-                } else {
-                    rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, gs, &handled);
-                }
-            } else {
-                rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, gs, &handled);
-            }
-            if (rc == JQ_OK && !handled) {
-                rc = fail(JQ_ERR_UNSUPPORTED, "decoder: a [%lld, %lld] linear is outside what the tensor-core GEMV takes (set option decoder_fused to 0)",
-                          (long long)cur->n, (long long)cur->k);
-            }
+        if (rc == JQ_OK) {
+            rc = decoder_gemv_imaged(d, w, y, w2, y2, gs);
         }
     };
     bool first_programmatic = true;
@@ -1283,6 +1294,36 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
     const int64_t kv_dim = (int64_t)kv_heads * hd, dim_l = dim / G, hidden_l = d->hidden / G, vocab_l = d->vocab / G;
     float *A = shard_area(d, 0), *B = shard_area(d, 1), *C = shard_area(d, 2), *D = shard_area(d, 3), *E = shard_area(d, 4);
     int rc = JQ_OK;
+    // One token, Q4_K / Q6_K weights: the two norms write the activation images of the linears behind them (the fused
+    // step's norm kernel), and wq|wk and w1|w3 are one launch each: 19 launches per layer instead of 26. The norm's
+    // sum of squares is then added in another order than the general kernel's, so results agree with the unsharded
+    // decoder within rounding instead of bit for bit; option decoder_fused = 0 keeps the general kernels.
+    bool fused_in = T == 1 && g_opt_decoder_fused.load() != 0 && dim % 256 == 0 && dim <= 32768;
+    for (size_t i = 0; i < d->lin.size() && fused_in; i++) {
+        const int slot = (int)(i % 7);
+        if (slot != 3 && slot != 6 && d->lin[i]->type != JQ_TYPE_Q4_K && d->lin[i]->type != JQ_TYPE_Q6_K) {
+            fused_in = false;
+        }
+    }
+    int norm_ctas = 8;
+    while (norm_ctas > 1 && dim % (256 * norm_ctas) != 0) {
+        norm_ctas /= 2;
+    }
+    const size_t norm_smem = (size_t)(dim / norm_ctas) * sizeof(float);
+    const dim3 norm_block((unsigned)(dim / norm_ctas / 4));
+    auto NORM_IMAGE = [&](const float* delta, const float* w, std::initializer_list<const jq_weight*> consumers) {
+        count_launch(1);
+        const cudaError_t e = launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, delta, (const float*)nullptr,
+                                                 (const int*)d->tokens, d->vocab, w, d->eps, dim, decoder_images_for(d, consumers));
+        if (rc == JQ_OK && e != cudaSuccess) {
+            rc = cuda_fail(e, "norm_image_kernel");
+        }
+    };
+    auto GEMV_IMAGED = [&](const jq_weight* w, float* y, const jq_weight* w2, float* y2) {
+        if (rc == JQ_OK) {
+            rc = decoder_gemv_imaged(d, w, y, w2, y2, s);
+        }
+    };
     auto LIN = [&](const jq_weight* w, const float* in, float* out_) {
         if (rc == JQ_OK) {
             rc = linear_device(w, in, T, nullptr, out_, s);
@@ -1329,11 +1370,17 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         const jq_weight* const* L = &d->lin[(size_t)l * 7];
         float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
-        LAUNCHED("add_rmsnorm_kernel");
-        LIN(L[0], d->xn, d->q);
-        LIN(L[1], d->xn, d->k);
-        LIN(L[2], d->xn, d->v);
+        if (fused_in) {
+            NORM_IMAGE(l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, {L[0], L[1], L[2]});
+            GEMV_IMAGED(L[0], d->q, L[1], d->k);
+            GEMV_IMAGED(L[2], d->v, nullptr, nullptr);
+        } else {
+            add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+            LAUNCHED("add_rmsnorm_kernel");
+            LIN(L[0], d->xn, d->q);
+            LIN(L[1], d->xn, d->k);
+            LIN(L[2], d->xn, d->v);
+        }
         if (rc != JQ_OK) break;
         rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step, tok_stride);
         LAUNCHED("rope_store_kernel");
@@ -1346,10 +1393,15 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         GATHER(d->att, dim, dim_l, 0);
         PEER_LIN(L[3], A, dim, dim_l, 1);
         if (rc != JQ_OK) break;
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
-        LAUNCHED("add_rmsnorm_kernel");
-        LIN(L[4], d->xn, d->gate);
-        LIN(L[5], d->xn, d->up);
+        if (fused_in) {
+            NORM_IMAGE(B, d->norms + (size_t)(2 * l + 1) * dim, {L[4], L[5]});
+            GEMV_IMAGED(L[4], d->gate, L[5], d->up);
+        } else {
+            add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+            LAUNCHED("add_rmsnorm_kernel");
+            LIN(L[4], d->xn, d->gate);
+            LIN(L[5], d->xn, d->up);
+        }
         if (rc != JQ_OK) break;
         const int64_t cnt = (int64_t)T * hidden_l;
         swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);

@@ -109,33 +109,43 @@ def _decoder_worker(rank, world, port, out_dir):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     L = jitnn_b200.load()
-    L.jq_set_option(b"decoder_fused", 0)  # the sharded decoder runs the general kernels: compare like with like
     results = {}
-    # grouped-query attention with one key/value head per rank, and mixed formats (Q6_K takes the scatter kernel)
-    for case, (dim, heads, kv_heads, prompt_len) in enumerate([(512, 4, 2, 21), (256, 4, 4, 61)]):
-        cfg = llama_oracle.Config(layers=2, dim=dim, heads=heads, kv_heads=kv_heads, hidden=2 * dim, vocab=512, max_seq=prompt_len + 16)
-        weights = llama_oracle.random_model(cfg, seed=31 + case)
-        args = (cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq, cfg.eps, cfg.rope_base)
-        whole = LlamaDecoder(*args, device=rank)
-        whole.load(weights)
-        split = LlamaDecoder(*args, device=rank, sharded=True)
-        split.load(weights)
-        prompt = np.random.default_rng(5 + case).integers(0, cfg.vocab, prompt_len).astype(np.int32)
-        ok = True
-        for i in range(0, prompt_len, 8):
-            a, na = whole.forward(prompt[i:i + 8], i)
-            b, nb = split.forward(prompt[i:i + 8], i)
-            ok = ok and np.array_equal(a, b) and np.array_equal(na, nb)
-        results["prompt%d" % case] = ok
-        tok, pos, ok = int(na[-1]), prompt_len, True
-        for _ in range(10):  # the second single-token call captures the step, exchanges included, into a CUDA graph
-            a, na = whole.forward([tok], pos)
-            b, nb = split.forward([tok], pos)
-            ok = ok and np.array_equal(a, b) and int(na[0]) == int(nb[0])
-            tok, pos = int(na[0]), pos + 1
-        results["decode%d" % case] = ok
-        whole.close()
-        split.close()
+    # grouped-query attention with one key/value head per rank, and mixed formats (Q6_K takes the scatter kernel).
+    # With the general kernels (decoder_fused 0) both decoders do the same arithmetic per row: bitwise equal. With the
+    # fused kernels the single-token steps sum the norms and the attention in other orders: equal within the decoder
+    # tolerance (2e-4 of the largest logit), same token wherever the top-2 margin is decisive.
+    for fused in (0, 1):
+        L.jq_set_option(b"decoder_fused", fused)
+        for case, (dim, heads, kv_heads, prompt_len) in enumerate([(512, 4, 2, 21), (256, 4, 4, 61)]):
+            cfg = llama_oracle.Config(layers=2, dim=dim, heads=heads, kv_heads=kv_heads, hidden=2 * dim, vocab=512, max_seq=prompt_len + 16)
+            weights = llama_oracle.random_model(cfg, seed=31 + case)
+            args = (cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq, cfg.eps, cfg.rope_base)
+            whole = LlamaDecoder(*args, device=rank)
+            whole.load(weights)
+            split = LlamaDecoder(*args, device=rank, sharded=True)
+            split.load(weights)
+            prompt = np.random.default_rng(5 + case).integers(0, cfg.vocab, prompt_len).astype(np.int32)
+            ok = True
+            for i in range(0, prompt_len, 8):
+                a, na = whole.forward(prompt[i:i + 8], i)
+                b, nb = split.forward(prompt[i:i + 8], i)
+                ok = ok and np.array_equal(a, b) and np.array_equal(na, nb)  # several tokens per call: general kernels in both
+            results["prompt%d_%d" % (case, fused)] = ok
+            tok, pos, ok = int(na[-1]), prompt_len, True
+            for _ in range(10):  # the second single-token call captures the step, exchanges included, into a CUDA graph
+                a, na = whole.forward([tok], pos)
+                b, nb = split.forward([tok], pos)
+                if fused == 0:
+                    ok = ok and np.array_equal(a, b) and int(na[0]) == int(nb[0])
+                else:
+                    scale = np.abs(a).max()
+                    top = np.sort(a[0])[-2:]
+                    ok = ok and np.abs(a - b).max() <= 2e-4 * scale and (int(na[0]) == int(nb[0]) or top[1] - top[0] <= 1e-4 * scale)
+                tok, pos = int(na[0]), pos + 1
+            results["decode%d_%d" % (case, fused)] = ok
+            whole.close()
+            split.close()
+    L.jq_set_option(b"decoder_fused", 1)
     status = ctypes.c_int(0)
     L.jq_device_status(rank, ctypes.byref(status))
     results["status"] = status.value == 0
