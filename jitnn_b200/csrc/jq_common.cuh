@@ -116,7 +116,14 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 // (jq_q4k_image.cuh, jq_q6k_image.cuh); the Q4_K one can take a second weight with the same k in the same launch.
 size_t q4k_image_bytes_one_row(int64_t k);
 size_t q6k_image_bytes_one_row(int64_t k);
-int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled);
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
+                              const PeerOut* peer = nullptr);
+// Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
+// rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
+// stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
+int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s);
+int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
+                           int rank, int world, cudaStream_t s);
 int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* bias, float* y, cudaStream_t s, bool* handled);
 // The same for Q6_K, rows <= 4.
 int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);

@@ -15,6 +15,7 @@
 #include "jq_common.cuh"
 #include "jq_q4k_image.cuh"
 #include "jq_q6k_image.cuh"
+#include "jq_peer_device.cuh"
 
 namespace jq {
 
@@ -407,11 +408,14 @@ __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x,
 // (256 outputs = one super-block of the next linear's k) merges the chunks' partial results in chunk order and writes
 // them as that linear's activation image.
 constexpr int ATTF_THREADS = 256;
+// PEER (a rank of the row-sharded decoder): heads are this rank's, the image block goes to the same place of every
+// rank's image area, and the CTA that finishes last of the whole grid raises this rank's flag on every rank.
+template <bool PEER>
 __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
                                                                        float* __restrict__ k_cache, float* __restrict__ v_cache,
                                                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                                                        const int* __restrict__ pos0, int heads, int kv_heads, int stride_splits, float scale,
-                                                                       float* __restrict__ part, int* __restrict__ counters, Images im) {
+                                                                       float* __restrict__ part, int* __restrict__ counters, Images im, PeerImage pi) {
     constexpr int HD = 128, HALF = 64;
     __shared__ __align__(16) float qs[HD];
     __shared__ __align__(16) float knew[HD];
@@ -538,6 +542,9 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     }
     __syncthreads();
     if (!last_flag) {
+        if constexpr (PEER) {
+            peer_publish(pi.flags, pi.rank, pi.world, &last_flag);
+        }
         return;
     }
     __threadfence();
@@ -581,20 +588,38 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     }
     __syncthreads();
     if (warp == 0) {
-        write_images(outs, sb, im, lane);
+        if constexpr (PEER) {
+            write_images(outs, pi.first_block + sb, im, lane);
+            peer_copy_block(pi, (size_t)(pi.first_block + sb) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, lane);
+        } else {
+            write_images(outs, sb, im, lane);
+        }
+    }
+    if constexpr (PEER) {
+        peer_publish(pi.flags, pi.rank, pi.world, &last_flag);
     }
 }
 
 // act = silu(gate) * up (F.java:1158-1161) for one super-block of 256 per CTA, written as the next linear's image.
-__global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im) {
+template <bool PEER>
+__global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im, PeerImage pi) {
     __shared__ __align__(16) float xs[256];
+    __shared__ int last_word;
     pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     const float g = gate[i];
     xs[threadIdx.x] = (g / (1.0f + expf(-g))) * up[i];
     __syncthreads();
     if (threadIdx.x < 32) {
-        write_images(xs, blockIdx.x, im, threadIdx.x);
+        if constexpr (PEER) {
+            write_images(xs, pi.first_block + (int)blockIdx.x, im, threadIdx.x);
+            peer_copy_block(pi, (size_t)(pi.first_block + (int)blockIdx.x) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, threadIdx.x);
+        } else {
+            write_images(xs, blockIdx.x, im, threadIdx.x);
+        }
+    }
+    if constexpr (PEER) {
+        peer_publish(pi.flags, pi.rank, pi.world, &last_word);
     }
 }
 
@@ -750,7 +775,8 @@ struct jq_decoder {
     // features; the five gathered activations live in the ranks' peer buffers (jq_peer_alloc).
     int world, rank;
     void* peer_buf[8];
-    int64_t area[5];  // payload offsets: attention output, wo output, SwiGLU output, w2 output, logits
+    int64_t area[8];  // payload offsets: attention output, wo output, SwiGLU output, w2 output, logits; the Q4_K activation
+                      // images of the attention output and of the SwiGLU output; [7] = the end
 };
 
 using namespace jq;
@@ -857,6 +883,11 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
             d->area[i] = off;
             off += ((int64_t)MAX_TOKENS * widths[i] * (int64_t)sizeof(float) + 255) / 256 * 256;
         }
+        d->area[5] = off;
+        off += ((int64_t)q4k_image_bytes_one_row(dim) + 511) / 256 * 256;
+        d->area[6] = off;
+        off += ((int64_t)q4k_image_bytes_one_row(hidden) + 511) / 256 * 256;
+        d->area[7] = off;
     }
     const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
     d->splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
@@ -930,7 +961,7 @@ JQ_API int jq_decoder_peer_bytes(const jq_decoder* d, int64_t* payload_bytes) {
     if (payload_bytes == nullptr) {
         return fail(JQ_ERR_INVALID, "jq_decoder_peer_bytes: null result pointer");
     }
-    *payload_bytes = d->area[4] + ((int64_t)MAX_TOKENS * d->vocab * (int64_t)sizeof(float) + 255) / 256 * 256;
+    *payload_bytes = d->area[7];
     return JQ_OK;
 }
 
@@ -1157,8 +1188,8 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         GEMV(L[0], d->q, L[1], d->k, s);
         GEMV(L[2], d->v, nullptr, nullptr, s);
         if (rc != JQ_OK) break;
-        CKL(launch_pdl(attention_image_kernel, dim3(d->heads, splits_now), dim3(ATTF_THREADS), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos,
-                       d->heads, d->kv_heads, d->splits, scale, d->att_part, d->counters, images_for({L[3]})),
+        CKL(launch_pdl(attention_image_kernel<false>, dim3(d->heads, splits_now), dim3(ATTF_THREADS), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos,
+                       d->heads, d->kv_heads, d->splits, scale, d->att_part, d->counters, images_for({L[3]}), PeerImage{}),
             "attention_image_kernel");
         GEMV(L[3], d->proj, nullptr, nullptr, s);
         if (rc != JQ_OK) break;
@@ -1168,7 +1199,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
             "norm_image_kernel");
         GEMV(L[4], d->gate, L[5], d->up, s);
         if (rc != JQ_OK) break;
-        CKL(launch_pdl(swiglu_image_kernel, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]})), "swiglu_image_kernel");
+        CKL(launch_pdl(swiglu_image_kernel<false>, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]}), PeerImage{}), "swiglu_image_kernel");
         GEMV(L[6], d->proj, nullptr, nullptr, s);
     }
     if (rc == JQ_OK) {
@@ -1281,6 +1312,24 @@ static float* shard_area(const jq_decoder* d, int i) {
     return reinterpret_cast<float*>(static_cast<uint8_t*>(d->peer_buf[d->rank]) + jq_peer_payload_offset() + d->area[i]);
 }
 
+// This rank's image area `i` (5 or 6), and the same area of every rank for the kernels that write an image into all of them.
+static uint8_t* shard_image(const jq_decoder* d, int i) {
+    return static_cast<uint8_t*>(d->peer_buf[d->rank]) + jq_peer_payload_offset() + d->area[i];
+}
+
+static PeerImage peer_image(const jq_decoder* d, int i, int blocks_per_rank) {
+    PeerImage pi;
+    memset(&pi, 0, sizeof(pi));
+    for (int r = 0; r < d->world; r++) {
+        pi.q4k[r] = static_cast<uint8_t*>(d->peer_buf[r]) + jq_peer_payload_offset() + d->area[i];
+        pi.flags[r] = static_cast<uint32_t*>(d->peer_buf[r]);
+    }
+    pi.world = d->world;
+    pi.rank = d->rank;
+    pi.first_block = d->rank * blocks_per_rank;
+    return pi;
+}
+
 // The forward of a rank of a row-sharded decoder. Every rank runs the replicated parts (embedding, norms, residual
 // adds, argmax) on the whole vectors and its own rows of every linear: wq / wk / wv give this rank's heads, whose
 // attention needs nothing from the other ranks; the attention output and the SwiGLU output are exchanged (each rank
@@ -1382,16 +1431,32 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             LIN(L[2], d->xn, d->v);
         }
         if (rc != JQ_OK) break;
-        rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step, tok_stride);
-        LAUNCHED("rope_store_kernel");
         const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
-        attention_partial_kernel<<<dim3(heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, heads, kv_heads, hd, d->splits,
-                                                                              scale, pos_step, tok_stride);
-        LAUNCHED("attention_partial_kernel");
-        attention_combine_kernel<<<dim3(heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, heads, hd, d->splits, splits_now);
-        LAUNCHED("attention_combine_kernel");
-        GATHER(d->att, dim, dim_l, 0);
-        PEER_LIN(L[3], A, dim, dim_l, 1);
+        if (fused_in && hd == 128 && heads % 2 == 0 && L[3]->type == JQ_TYPE_Q4_K) {
+            // the fused attention kernel on this rank's heads; its merging CTAs store their super-block of wo's activation
+            // image into every rank's image area, the last CTA raises the flags; wo then reads the image all ranks wrote
+            count_launch(1);
+            const cudaError_t e = launch_pdl(attention_image_kernel<true>, dim3(heads, splits_now), dim3(ATTF_THREADS), 0, s, true, (const float*)d->q,
+                                             (const float*)d->k, (const float*)d->v, kc, vc, (const float*)d->cos_t, (const float*)d->sin_t,
+                                             (const int*)d->pos, heads, kv_heads, d->splits, scale, d->att_part, d->counters,
+                                             Images{shard_image(d, 5), nullptr}, peer_image(d, 5, (int)(dim_l / 256)));
+            if (rc == JQ_OK && e != cudaSuccess) {
+                rc = cuda_fail(e, "attention_image_kernel");
+            }
+            if (rc == JQ_OK) rc = peer_wait_enqueue(d->peer_buf, d->rank, G, s);
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[3], shard_image(d, 5), dim, d->rank * dim_l, d->peer_buf, d->area[1], d->rank, G, s);
+        } else {
+            rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step,
+                                                                               tok_stride);
+            LAUNCHED("rope_store_kernel");
+            attention_partial_kernel<<<dim3(heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, heads, kv_heads, hd, d->splits,
+                                                                                  scale, pos_step, tok_stride);
+            LAUNCHED("attention_partial_kernel");
+            attention_combine_kernel<<<dim3(heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, heads, hd, d->splits, splits_now);
+            LAUNCHED("attention_combine_kernel");
+            GATHER(d->att, dim, dim_l, 0);
+            PEER_LIN(L[3], A, dim, dim_l, 1);
+        }
         if (rc != JQ_OK) break;
         if (fused_in) {
             NORM_IMAGE(B, d->norms + (size_t)(2 * l + 1) * dim, {L[4], L[5]});
@@ -1403,11 +1468,22 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             LIN(L[5], d->xn, d->up);
         }
         if (rc != JQ_OK) break;
-        const int64_t cnt = (int64_t)T * hidden_l;
-        swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
-        LAUNCHED("swiglu_kernel");
-        GATHER(d->act, d->hidden, hidden_l, 2);
-        PEER_LIN(L[6], C, dim, dim_l, 3);
+        if (fused_in && hidden_l % 256 == 0 && L[6]->type == JQ_TYPE_Q4_K) {
+            count_launch(1);
+            const cudaError_t e = launch_pdl(swiglu_image_kernel<true>, dim3((unsigned)(hidden_l / 256)), dim3(256), 0, s, true, (const float*)d->gate,
+                                             (const float*)d->up, Images{shard_image(d, 6), nullptr}, peer_image(d, 6, (int)(hidden_l / 256)));
+            if (rc == JQ_OK && e != cudaSuccess) {
+                rc = cuda_fail(e, "swiglu_image_kernel");
+            }
+            if (rc == JQ_OK) rc = peer_wait_enqueue(d->peer_buf, d->rank, G, s);
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[6], shard_image(d, 6), dim, d->rank * dim_l, d->peer_buf, d->area[3], d->rank, G, s);
+        } else {
+            const int64_t cnt = (int64_t)T * hidden_l;
+            swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
+            LAUNCHED("swiglu_kernel");
+            GATHER(d->act, d->hidden, hidden_l, 2);
+            PEER_LIN(L[6], C, dim, dim_l, 3);
+        }
     }
     if (rc == JQ_OK) {
         add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, D, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);

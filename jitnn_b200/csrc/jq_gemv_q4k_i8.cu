@@ -644,15 +644,19 @@ size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::P
 // One row of x whose image (q4k::build_image<1> per super-block) a kernel earlier in the stream has written to `image`;
 // that kernel should execute griddepcontrol.launch_dependents so that this one can request weights meanwhile. With
 // v2 != nullptr the rows of a second Q4_K weight with the same k follow in the same launch, results in y2.
-int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled) {
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
+                              const PeerOut* peer) {
     *handled = false;
     if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || image == nullptr || (int64_t)16 * (v.k / 256) * 144 >= ((int64_t)1 << 31) ||
         (v2 != nullptr && (v2->type != JQ_TYPE_Q4_K || v2->k != v.k || v2->n == 0 || y2 == nullptr))) {
         return JQ_OK;
     }
     const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
-    const PeerOut local{};
-    return run<1, false>(v, w2, local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
+    const PeerOut local{};  // world = 0: results go to y (and y2)
+    if (peer != nullptr && v2 != nullptr) {
+        return JQ_OK;  // a second weight has no place in a peer's y
+    }
+    return run<1, false>(v, w2, peer != nullptr ? *peer : local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
 }
 
 }  // namespace jq

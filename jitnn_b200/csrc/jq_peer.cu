@@ -252,6 +252,49 @@ static int enqueue_scatter(const float* slice, int64_t m, int64_t n_slice, int64
     return JQ_OK;
 }
 
+}  // extern "C"
+
+namespace jq {
+
+int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s) {
+    PeerTargets tg;
+    int rc = fill_targets(peer_buffers, 0, rank, world, &tg, "peer wait");
+    return rc == JQ_OK ? enqueue_wait(tg, rank, world, s) : rc;
+}
+
+int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
+                           int rank, int world, cudaStream_t s) {
+    PeerTargets tg;
+    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "peer linear");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    PeerOut po;
+    memset(&po, 0, sizeof(po));
+    for (int r = 0; r < PEER_MAX_WORLD; r++) {
+        po.y[r] = tg.y[r];
+        po.flags[r] = tg.flags[r];
+    }
+    po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+    rc = device_table(po, s, &po.table);
+    bool handled = false;
+    if (rc == JQ_OK) {
+        const View v{w->q, w->aux, w->n, w->k, w->type};
+        rc = launch_gemv_q4k_i8_imaged(v, nullptr, image, nullptr, nullptr, nullptr, s, &handled, &po);
+    }
+    if (rc == JQ_OK && !handled) {
+        rc = fail(JQ_ERR_UNSUPPORTED, "peer linear: a [%lld, %lld] shard is outside what the tensor-core GEMV takes", (long long)w->n, (long long)w->k);
+    }
+    if (rc == JQ_OK) {
+        rc = enqueue_wait(tg, rank, world, s);
+    }
+    return rc;
+}
+
+}  // namespace jq
+
+extern "C" {
+
 JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
                           int rank, int world, void* stream) {
     if (slice == nullptr || m < 1 || n_slice < 0 || col0 < 0 || col0 + n_slice > n_total) {

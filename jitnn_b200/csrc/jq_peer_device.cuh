@@ -27,7 +27,7 @@ __device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, i
         __threadfence_system();
         int* counter = reinterpret_cast<int*>(flags[rank] + PEER_COUNTER_WORD);
         const int done = atomicAdd(counter, 1);
-        peer_last_flag = done == (int)gridDim.x - 1;
+        peer_last_flag = done == (int)(gridDim.x * gridDim.y * gridDim.z) - 1;
         if (peer_last_flag) {
             *counter = 0;
         }
@@ -42,6 +42,29 @@ __device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, i
         __syncwarp();
         if (threadIdx.x == 0) {
             flags[rank][PEER_SEQ_WORD] = seq;
+        }
+    }
+}
+
+// Where a kernel that writes one super-block of a Q4_K activation image (jq_q4k_image.cuh, one row of x) puts it when
+// the image is shared by the ranks of a row-sharded decoder: the same offset of every rank's image area.
+struct PeerImage {
+    uint8_t* q4k[PEER_MAX_WORLD];     // every rank's image area (this rank's included)
+    uint32_t* flags[PEER_MAX_WORLD];  // every rank's flag words
+    int world, rank;
+    int first_block;                  // this rank's first super-block of the image
+};
+
+// One warp copies `bytes` (a multiple of 16) it has just written at own + offset to the same offset of the other ranks.
+__device__ __forceinline__ void peer_copy_block(const PeerImage& pi, size_t offset, int bytes, int lane) {
+    __syncwarp();  // the warp's own stores are visible to all its lanes
+    const int4* src = reinterpret_cast<const int4*>(pi.q4k[pi.rank] + offset);
+    for (int c = lane; c < bytes / 16; c += 32) {
+        const int4 v = __ldcg(src + c);
+        for (int r = 0; r < pi.world; r++) {
+            if (r != pi.rank) {
+                reinterpret_cast<int4*>(pi.q4k[r] + offset)[c] = v;
+            }
         }
     }
 }

@@ -116,9 +116,11 @@ def _decoder_worker(rank, world, port, out_dir):
     # tolerance (2e-4 of the largest logit), same token wherever the top-2 margin is decisive.
     for fused in (0, 1):
         L.jq_set_option(b"decoder_fused", fused)
-        for case, (dim, heads, kv_heads, prompt_len) in enumerate([(512, 4, 2, 21), (256, 4, 4, 61)]):
+        # the third case is all Q4_K: with the fused kernels both activation images (attention, SwiGLU) are exchanged
+        all_q4k = {"wv": "Q4_K", "w2": "Q4_K", "output": "Q4_K"}
+        for case, (dim, heads, kv_heads, prompt_len, formats) in enumerate([(512, 4, 2, 21, None), (256, 4, 4, 61, None), (512, 4, 4, 70, all_q4k)]):
             cfg = llama_oracle.Config(layers=2, dim=dim, heads=heads, kv_heads=kv_heads, hidden=2 * dim, vocab=512, max_seq=prompt_len + 16)
-            weights = llama_oracle.random_model(cfg, seed=31 + case)
+            weights = llama_oracle.random_model(cfg, seed=31 + case, formats=formats)
             args = (cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq, cfg.eps, cfg.rope_base)
             whole = LlamaDecoder(*args, device=rank)
             whole.load(weights)
