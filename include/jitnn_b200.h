@@ -155,7 +155,7 @@ JQ_API int jq_device_status(int device, int* status);
  * rank's copy of the full y over NVLink and raises a flag there; the rank's later work on `stream` starts after a
  * bounded wait for all ranks' flags. (No counterpart in the reference, which never shards a linear.)
  *
- * jq_peer_alloc    a buffer on `device` for `payload_bytes` of gathered outputs (plus 1024 bytes of flags in front, at
+ * jq_peer_alloc    a buffer on `device` for `payload_bytes` of gathered outputs (plus 2048 bytes of flags in front, at
  *                  jq_peer_payload_offset() the payload starts) and its 64-byte CUDA IPC handle, which the caller sends
  *                  to the other ranks' processes by whatever channel it has.
  * jq_peer_open     maps another rank's buffer into this process (peer access is enabled on first use); jq_peer_close

@@ -646,6 +646,13 @@ int jq_device_status(int device, int* status) {
     if (rc == JQ_OK && *status == 0) {
         *status = peer;
     }
+    for (int part = 0; part < 2 && rc == JQ_OK; part++) {
+        int other = 0;
+        rc = part == 0 ? gemv_peer_status(&other) : decoder_peer_status(&other);
+        if (rc == JQ_OK && *status == 0) {
+            *status = other;
+        }
+    }
     return rc;
 }
 

@@ -108,6 +108,7 @@ struct PeerOut {
     int world, rank;
     int64_t n_total, col0;  // this rank's rows are columns col0 .. of y
     const PeerOut* table;   // host side only: where a copy of this struct lives in device memory
+    int wait_first;         // the kernel's input is what this rank's latest exchange delivered: wait for all ranks' flags before reading it
 };
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
                        const PeerOut* peer = nullptr);
@@ -123,7 +124,10 @@ int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* imag
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
 int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s);
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                           int rank, int world, cudaStream_t s);
+                           int rank, int world, cudaStream_t s, bool wait_first, bool wait_after);
+// Status words of the waits that kernels of other translation units make themselves (peer_wait_inline): 0 or 32 + rank, cleared by the call.
+int gemv_peer_status(int* status);
+int decoder_peer_status(int* status);
 int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* bias, float* y, cudaStream_t s, bool* handled);
 // The same for Q6_K, rows <= 4.
 int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);

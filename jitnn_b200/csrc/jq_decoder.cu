@@ -335,6 +335,8 @@ __device__ __forceinline__ void pdl_enter() {
     asm volatile("griddepcontrol.launch_dependents;");
 }
 
+__device__ int g_decoder_peer_status;  // 0, or 32 + rank once a wait of peer_wait_inline in this file has given up
+
 struct Images {
     uint8_t* q4k;  // destination of the Q4_K image, or nullptr if no consumer is Q4_K
     uint8_t* q6k;
@@ -356,13 +358,20 @@ __device__ __forceinline__ void write_images(const float* block, int b, const Im
 // the images of its own super-blocks. blockDim.x = elements per CTA / 4.
 __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ table,
                                                           const int* __restrict__ token, int vocab, const float* __restrict__ w, float eps, int dim,
-                                                          Images im) {
+                                                          Images im, const uint32_t* wait_flags, int wait_world) {
     namespace cg = cooperative_groups;
     extern __shared__ __align__(16) float norm_xs[];  // this CTA's normalised elements
     __shared__ float scratch[32];
     __shared__ float partial;
     cg::cluster_group cluster = cg::this_cluster();
     pdl_enter();
+    if (wait_flags != nullptr) {
+        // delta is what the ranks' latest exchange delivered (row-sharded decoder): complete once all their flags are up
+        if (threadIdx.x < 32) {
+            peer_wait_inline(wait_flags, wait_world, threadIdx.x, &g_decoder_peer_status);
+        }
+        __syncthreads();
+    }
     const int per_cta = dim / (int)gridDim.x, first = (int)blockIdx.x * per_cta;
     const float4* src = reinterpret_cast<const float4*>(x + first);
     if (table != nullptr) {
@@ -739,6 +748,15 @@ cudaError_t launch_cluster_pdl(void (*kernel)(KArgs...), int ctas, dim3 block, s
 }
 
 }  // namespace
+
+// Reads and clears the status of the exchange waits made by kernels of this file.
+int decoder_peer_status(int* status) {
+    const int zero = 0;
+    JQ_CUDA(cudaMemcpyFromSymbol(status, g_decoder_peer_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_decoder_peer_status, &zero, sizeof(int)));
+    return JQ_OK;
+}
+
 }  // namespace jq
 
 #define JQ_DECODER_MAGIC 0x4a514443u
@@ -1183,7 +1201,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         // attention block: x = embedding (first layer) or x += feed-forward output of the layer before; norm -> images
         CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
-                       l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]})),
+                       l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]}), (const uint32_t*)nullptr, 0),
             "norm_image_kernel");
         GEMV(L[0], d->q, L[1], d->k, s);
         GEMV(L[2], d->v, nullptr, nullptr, s);
@@ -1195,7 +1213,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         if (rc != JQ_OK) break;
         // feed-forward block
         CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
-                       d->norms + (size_t)(2 * l + 1) * dim, d->eps, dim, images_for({L[4], L[5]})),
+                       d->norms + (size_t)(2 * l + 1) * dim, d->eps, dim, images_for({L[4], L[5]}), (const uint32_t*)nullptr, 0),
             "norm_image_kernel");
         GEMV(L[4], d->gate, L[5], d->up, s);
         if (rc != JQ_OK) break;
@@ -1204,7 +1222,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
     }
     if (rc == JQ_OK) {
         CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, d->proj, nullptr, d->tokens, d->vocab,
-                       d->norms + (size_t)(2 * d->layers) * dim, d->eps, dim, images_for({d->output})),
+                       d->norms + (size_t)(2 * d->layers) * dim, d->eps, dim, images_for({d->output}), (const uint32_t*)nullptr, 0),
             "norm_image_kernel");
         GEMV(d->output, d->logits, nullptr, nullptr, s);
     }
@@ -1360,10 +1378,14 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
     }
     const size_t norm_smem = (size_t)(dim / norm_ctas) * sizeof(float);
     const dim3 norm_block((unsigned)(dim / norm_ctas / 4));
+    // A peer linear whose flag wait has not been enqueued as a kernel: the norm that reads its output waits itself.
+    bool pending_wait = false;
     auto NORM_IMAGE = [&](const float* delta, const float* w, std::initializer_list<const jq_weight*> consumers) {
         count_launch(1);
         const cudaError_t e = launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, true, d->x, delta, (const float*)nullptr,
-                                                 (const int*)d->tokens, d->vocab, w, d->eps, dim, decoder_images_for(d, consumers));
+                                                 (const int*)d->tokens, d->vocab, w, d->eps, dim, decoder_images_for(d, consumers),
+                                                 pending_wait ? (const uint32_t*)d->peer_buf[d->rank] : (const uint32_t*)nullptr, G);
+        pending_wait = false;
         if (rc == JQ_OK && e != cudaSuccess) {
             rc = cuda_fail(e, "norm_image_kernel");
         }
@@ -1443,8 +1465,9 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             if (rc == JQ_OK && e != cudaSuccess) {
                 rc = cuda_fail(e, "attention_image_kernel");
             }
-            if (rc == JQ_OK) rc = peer_wait_enqueue(d->peer_buf, d->rank, G, s);
-            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[3], shard_image(d, 5), dim, d->rank * dim_l, d->peer_buf, d->area[1], d->rank, G, s);
+            // wo waits for the image's flags itself, and the norm behind it for wo's (no wait kernels in between)
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[3], shard_image(d, 5), dim, d->rank * dim_l, d->peer_buf, d->area[1], d->rank, G, s, true, false);
+            pending_wait = true;
         } else {
             rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step,
                                                                                tok_stride);
@@ -1475,8 +1498,9 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             if (rc == JQ_OK && e != cudaSuccess) {
                 rc = cuda_fail(e, "swiglu_image_kernel");
             }
-            if (rc == JQ_OK) rc = peer_wait_enqueue(d->peer_buf, d->rank, G, s);
-            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[6], shard_image(d, 6), dim, d->rank * dim_l, d->peer_buf, d->area[3], d->rank, G, s);
+            const bool last = l == d->layers - 1;  // the final norm is the general kernel: it gets a wait kernel in front
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[6], shard_image(d, 6), dim, d->rank * dim_l, d->peer_buf, d->area[3], d->rank, G, s, true, last);
+            pending_wait = !last;
         } else {
             const int64_t cnt = (int64_t)T * hidden_l;
             swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
@@ -1599,8 +1623,12 @@ static int decoder_forward(jq_decoder* d, int seq, bool batch, const int32_t* to
         }
         CK(cudaStreamSynchronize(s), "jq_decoder_forward");
         if (rc == JQ_OK && d->world > 1) {
-            int status = 0;
+            int status = 0, part = 0;
             rc = peer_status(&status);
+            if (rc == JQ_OK) rc = gemv_peer_status(&part);
+            status = status != 0 ? status : part;
+            if (rc == JQ_OK) rc = decoder_peer_status(&part);
+            status = status != 0 ? status : part;
             if (rc == JQ_OK && status != 0) {
                 rc = fail(JQ_ERR_TIMEOUT, "jq_decoder_forward: the slice of rank %d did not arrive (bounded wait gave up)", status - 32);
             }

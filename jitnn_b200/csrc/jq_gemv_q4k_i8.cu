@@ -98,6 +98,7 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
 // The image in a scratch buffer in global memory, for the GEMV shapes that do not build it themselves. The kernel is
 // tiny and latency bound, so the work is spread over as many warps as possible.
 constexpr int PREP_WARPS = 4;
+__device__ int g_gemv_peer_status;  // 0, or 32 + rank once a GEMV's own wait for an exchange has given up
 
 template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
@@ -215,6 +216,15 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+    if constexpr (PEER) {
+        if (peerp->wait_first) {
+            // the image is what the ranks' latest exchange delivered: complete once all their flags are up
+            if (warp == 0) {
+                peer_wait_inline(peerp->flags[peerp->rank], peerp->world, lane, &g_gemv_peer_status);
+            }
+            __syncthreads();
+        }
+    }
 
     // ---- main loop ----------------------------------------------------------------------------------------------
     // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
@@ -637,6 +647,13 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled);
     if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled);
     return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled);
+}
+
+int gemv_peer_status(int* status) {
+    const int zero = 0;
+    JQ_CUDA(cudaMemcpyFromSymbol(status, g_gemv_peer_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_gemv_peer_status, &zero, sizeof(int)));
+    return JQ_OK;
 }
 
 size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }

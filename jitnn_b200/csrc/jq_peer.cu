@@ -9,9 +9,9 @@
 // The reference gathers with Collective.allGather (dist/Collective.java:64-65, NCCL form dist/NcclOp.java:184-198); for
 // the 4 KB - 128 KB slices of a decode step that call costs more than the GEMV it follows.
 //
-// A peer buffer is one cudaMalloc'd allocation: 1024 bytes of flags (uint32 [world] arrival flags written by the peers;
+// A peer buffer is one cudaMalloc'd allocation: 2048 bytes of flags (uint32 [world] arrival flags written by the peers;
 // words 16 and 17, never written by peers: a CTA counter and the number of exchanges this rank has made on the
-// buffer; from byte 128 on up to four copies of the target table PeerOut that the fused GEMV epilogue reads), then the
+// buffer; from byte 128 on up to eight copies of the target table PeerOut that the fused GEMV epilogue reads), then the
 // payload. A flag carries the number of the exchange it announces. The number lives in device
 // memory and grows by one per exchange, so a captured CUDA graph can be replayed; all ranks make the same exchanges
 // on a buffer in the same order, which keeps their numbers in step. A rank can run one exchange ahead of another:
@@ -34,7 +34,6 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
 
 namespace {
 
-constexpr unsigned PEER_POLL_LIMIT = 1u << 22;  // polls of about 100 ns each: gives up after roughly half a second
 
 struct PeerTargets {
     float* y[PEER_MAX_WORLD];         // every rank's full y [m, n_total] (own included)
@@ -263,7 +262,7 @@ int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream
 }
 
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                           int rank, int world, cudaStream_t s) {
+                           int rank, int world, cudaStream_t s, bool wait_first, bool wait_after) {
     PeerTargets tg;
     int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "peer linear");
     if (rc != JQ_OK) {
@@ -276,6 +275,7 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
         po.flags[r] = tg.flags[r];
     }
     po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+    po.wait_first = wait_first ? 1 : 0;
     rc = device_table(po, s, &po.table);
     bool handled = false;
     if (rc == JQ_OK) {
@@ -285,7 +285,7 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
     if (rc == JQ_OK && !handled) {
         rc = fail(JQ_ERR_UNSUPPORTED, "peer linear: a [%lld, %lld] shard is outside what the tensor-core GEMV takes", (long long)w->n, (long long)w->k);
     }
-    if (rc == JQ_OK) {
+    if (rc == JQ_OK && wait_after) {
         rc = enqueue_wait(tg, rank, world, s);
     }
     return rc;

@@ -8,10 +8,10 @@
 namespace jq {
 
 constexpr int PEER_MAX_WORLD = 8;
-constexpr int PEER_FLAG_BYTES = 1024;   // flags and counters in the first 128 bytes, then room for PEER_TABLES copies of PeerOut
+constexpr int PEER_FLAG_BYTES = 2048;   // flags and counters in the first 128 bytes, then room for PEER_TABLES copies of PeerOut
 constexpr int PEER_TABLE_OFFSET = 128;
 constexpr int PEER_TABLE_STRIDE = 208;
-constexpr int PEER_TABLES = 4;
+constexpr int PEER_TABLES = 8;
 static_assert(sizeof(PeerOut) <= PEER_TABLE_STRIDE && PEER_TABLE_OFFSET + PEER_TABLES * PEER_TABLE_STRIDE <= PEER_FLAG_BYTES, "the tables fit the flag area");
 constexpr int PEER_COUNTER_WORD = 16;
 constexpr int PEER_SEQ_WORD = 17;
@@ -44,6 +44,30 @@ __device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, i
             flags[rank][PEER_SEQ_WORD] = seq;
         }
     }
+}
+
+// The wait for all ranks' flags of this rank's latest exchange, made by one warp (lane r polls rank r's flag) of a kernel
+// that consumes what the exchange delivered, after its griddepcontrol.wait (the kernel that made this rank's part of
+// the exchange has then finished and advanced the number). Bounded: gives up after about half a second and records
+// 32 + r in *status; the caller carries on with whatever is there.
+constexpr unsigned PEER_POLL_LIMIT = 1u << 22;  // polls of about 100 ns each
+__device__ __forceinline__ void peer_wait_inline(const uint32_t* flags, int world, int lane, int* status) {
+    if (lane < world) {
+        const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(flags + PEER_SEQ_WORD);
+        bool arrived = false;
+        for (unsigned poll = 0; poll < PEER_POLL_LIMIT && !arrived; poll++) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
+            arrived = (int32_t)(seen - seq) >= 0;
+            if (!arrived) {
+                __nanosleep(100);
+            }
+        }
+        if (!arrived) {
+            atomicCAS(status, 0, 32 + lane);
+        }
+    }
+    __syncwarp();
 }
 
 // Where a kernel that writes one super-block of a Q4_K activation image (jq_q4k_image.cuh, one row of x) puts it when
