@@ -345,6 +345,19 @@ def run_ours(args):
             for w in copies:
                 w.release()  # make room: the decoder holds 5 GB of weights and 1 GB of cache
         decode = decode_leg(torch, device)
+    decode_70b = None
+    if not args.only and not args.no_decode and gather_kind != "nccl":
+        # every rank takes part (the decoder is split by rows over the ranks); a failure is reported, not fatal to the line
+        for copies in pools:
+            for w in copies:
+                w.release()
+        for p in peers.values():
+            p.close()
+        peers = {}
+        try:
+            decode_70b = decode_70b_leg(torch, device, rank, world)
+        except Exception as exc:  # noqa: BLE001 - whatever it is, the sweep's numbers above are still valid
+            decode_70b = {"error": "%s: %s" % (type(exc).__name__, exc)}
     cpu = cpu_baseline_leg(threads=1, fraction=1, steps=2) if (rank == 0 and world == 1 and not args.no_cpu) else None
 
     if rank == 0:
@@ -365,7 +378,7 @@ def run_ours(args):
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "decode_70b": decode_70b, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -770,7 +783,7 @@ def main():
                     help="N > 1: how every rank gets the whole y after each sharded linear (the library's peer-store exchange, or NCCL; none = no exchange, for diagnosis only)")
     ap.add_argument("--leg", default="all", choices=["all", "prefill", "decode", "formats", "decode70b"],
                     help="run only the prefill GEMM leg, the format table, the 7B-shape decode leg (one GPU; for profiler captures) or the sharded 70B-shape decoder leg (any N)")
-    ap.add_argument("--no-decode", action="store_true", help="skip the 7B-shape decoder tokens/s leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decoder tokens/s legs (7B shape on one GPU, 70B shape row-sharded at any N)")
     ap.add_argument("--decode-shape", default=None, metavar="LAYERS,PROMPT,GEN",
                     help="with --leg decode: fewer layers / a shorter prompt and run, for profiler captures")
     ap.add_argument("--eager", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
