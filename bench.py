@@ -165,7 +165,7 @@ def run_ours(args):
     if args.leg in ("prefill", "decode", "formats", "decode70b"):
         # one leg alone, for profiler captures: no sweep, a short line of its own
         out = (prefill_leg(torch, device, L, _lib) if args.leg == "prefill" else
-               formats_leg(torch, device, L, _lib) if args.leg == "formats" else
+               formats_leg(torch, device, L, _lib, reps=max(1, min(25, args.steps))) if args.leg == "formats" else  # --steps 1: a short run for profiler captures
                decode_70b_leg(torch, device, rank, world, args.decode_shape) if args.leg == "decode70b" else
                decode_leg(torch, device, args.decode_shape))
         if rank == 0:
@@ -435,7 +435,7 @@ FORMAT_CASES = [("Q8_0", 4096, 4096), ("Q8_0", 32000, 4096), ("Q4_0", 32000, 409
 FORMAT_BPW = {"Q8_0": 34 / 32, "Q4_0": 18 / 32, "Q4_1": 20 / 32, "Q4_K": 144 / 256, "Q5_K": 176 / 256, "Q6_K": 210 / 256}
 
 
-def formats_leg(torch, device, L, _lib):
+def formats_leg(torch, device, L, _lib, reps=25):
     """The decode GEMV (M = 1) of the other formats of the path: BASELINE.json configs[0] (Q8_0, 4096x4096, weights from
     the reference's host quantiser as restated in jq_quantize_q8_0) and one large layer per format. Four copies of every
     weight in rotation (so that no launch finds its weight in L2), replayed from a CUDA graph; GB/s over the algorithmic
@@ -469,7 +469,6 @@ def formats_leg(torch, device, L, _lib):
             graph.replay()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize(device)
-            reps = 25
             a.record(side)
             for _ in range(reps):
                 graph.replay()
