@@ -255,6 +255,28 @@ def test_full_size_linearity_property():
     assert max_rel(sample, y[:, :64]) <= REL_TOL
 
 
+def test_full_size_q8_round_trip_and_gradient_properties():
+    """Size-independent properties at BASELINE configs[0]'s shape (4096 x 4096, Q8_0): quantise -> dequantise -> quantise
+    gives the same blocks (every non-zero block has a value of magnitude 127, so its scale survives the round trip);
+    the input gradient is linear in g, and a one-hot g reads back one dequantised row exactly."""
+    n, k = 4096, 4096
+    g = torch.Generator().manual_seed(17)
+    wf = (torch.randn(n, k, generator=g) * 0.02).cuda()
+    blocks = Quant.quantizeQ8Blocks(wf)
+    w = Tensor.quantized("Q8_0", blocks.cpu().numpy(), n, k)
+    back = torch.empty(n, k, device="cuda")
+    Quant.dequantize(w, back)
+    assert torch.equal(Quant.quantizeQ8Blocks(back), blocks)
+    assert float((back - wf).abs().max()) <= float(wf.abs().max()) / 127 * 0.5 + 1e-7
+    g2 = torch.randn(2, n, generator=g).cuda()
+    gx = Gguf.linearBackward(g2, w)
+    combo = (0.25 * g2[0] + 3.0 * g2[1])[None].contiguous()
+    assert max_rel((0.25 * gx[0] + 3.0 * gx[1]).cpu().numpy(), Gguf.linearBackward(combo, w)[0].cpu().numpy()) < 1e-5
+    onehot = torch.zeros(1, n, device="cuda")
+    onehot[0, 321] = 1.0
+    assert torch.equal(Gguf.linearBackward(onehot, w)[0], back[321])
+
+
 def test_page_locked_host_buffers_are_used_in_place():
     """jq_linear_f32 with page-locked host x, bias and y (kernels read and write them across PCIe, no staging copies) gives
     bit for bit what the same call gives with pageable buffers; a large output still goes through a copy."""
