@@ -45,8 +45,11 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // Byte i (0..3) of a word as a sign-extended integer.
 __device__ __forceinline__ int signed_byte(uint32_t w, int i) {
+    // one byte permute: byte i below three copies of its sign (a selector digit of 8 + i replicates the byte's top bit)
+    // (prmt in PTX: the __byte_perm intrinsic only honours the three low bits of a selector digit)
+    const uint32_t s = (uint32_t)(8 + i);
     int r;
-    asm("bfe.s32 %0, %1, %2, 8;" : "=r"(r) : "r"(w), "r"(8 * i));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "r"((uint32_t)i | (s << 4) | (s << 8) | (s << 12)));
     return r;
 }
 
