@@ -398,7 +398,6 @@ __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x,
     for (unsigned r = 0; r < cluster.num_blocks(); r++) {
         total += *cluster.map_shared_rank(&partial, r);
     }
-    cluster.sync();  // no CTA leaves (and frees its shared memory) while another may still read its partial sum
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
     const float4 ww = reinterpret_cast<const float4*>(w + first)[i];
     reinterpret_cast<float4*>(norm_xs)[i] = make_float4(a.x * inv * ww.x, a.y * inv * ww.y, a.z * inv * ww.z, a.w * inv * ww.w);
@@ -409,6 +408,7 @@ __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x,
         Images one{task < blocks ? im.q4k : nullptr, task < blocks ? nullptr : im.q6k};
         write_images(norm_xs + (size_t)b * 256, (first >> 8) + b, one, lane);
     }
+    cluster.sync();  // no CTA leaves (and frees its shared memory) while another may still read its partial sum
 }
 
 // Attention of the one new token (head_dim 128): RoPE of its query and key (ops/Rope.java:125-149), the append of key
