@@ -125,3 +125,35 @@ def test_forward_argument_checks():
     with pytest.raises(ValueError, match="inconsistent sizes"):
         LlamaDecoder(1, 250, 4, 3, 256, 64, 8)
     dec.close()
+
+
+def test_shard_and_sequence_argument_checks():
+    """jq_decoder_set_shard and jq_decoder_set_sequences refuse what they cannot serve, with a message."""
+    import ctypes
+    import jitnn_b200
+    from jitnn_b200._lib import check
+    L = jitnn_b200.load()
+    cfg = llama_oracle.Config(layers=1, dim=256, heads=4, kv_heads=2, hidden=256, vocab=64, max_seq=8)
+    dec = LlamaDecoder(cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq)
+    nbytes = ctypes.c_int64()
+    check(L.jq_decoder_peer_bytes(dec._h, ctypes.byref(nbytes)))
+    assert nbytes.value > 16 * (2 * cfg.dim + cfg.hidden + cfg.dim + cfg.vocab) * 4
+    fake = (ctypes.c_void_p * 4)(1, 1, 1, 1)  # never dereferenced by the checks below
+    with pytest.raises(ValueError, match="do not divide"):
+        check(L.jq_decoder_set_shard(dec._h, 0, 3, fake))  # 3 ranks, 4 heads
+    with pytest.raises(ValueError, match="do not divide"):
+        check(L.jq_decoder_set_shard(dec._h, 0, 4, fake))  # 4 ranks, 2 key/value heads
+    with pytest.raises(ValueError, match="rank 2 of 2"):
+        check(L.jq_decoder_set_shard(dec._h, 2, 2, fake))
+    check(L.jq_decoder_set_shard(dec._h, 0, 1, None))  # one rank: the ordinary decoder
+    with pytest.raises(ValueError, match="1 to 16"):
+        dec.set_sequences(17)
+    dec.load(llama_oracle.random_model(cfg, 5))
+    with pytest.raises(ValueError, match="before the linears are set"):
+        check(L.jq_decoder_set_shard(dec._h, 0, 2, fake))
+    dec.set_sequences(2)
+    with pytest.raises(ValueError, match="batch of 3"):
+        dec.forward_batch([1, 2, 3], 0)
+    lg, nxt = dec.forward_batch([1, 2], 0)
+    assert lg.shape == (2, cfg.vocab) and nxt.shape == (2,)
+    dec.close()
