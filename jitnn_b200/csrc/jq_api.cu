@@ -89,6 +89,9 @@ static int staging_for(int device, size_t bytes, Staging** out) {
 }
 
 // ---- per (device, stream) scratch ------------------------------------------------------------------
+// A buffer that has been handed out may be baked into a captured CUDA graph (the decoder's step, a caller's own capture
+// of jq_linear_*), so it is never freed or moved: a request that outgrows it gets a new allocation and the old one stays
+// where it is until the process ends.
 struct Scratch {
     int device;
     cudaStream_t stream;
@@ -98,10 +101,11 @@ struct Scratch {
 };
 static std::mutex g_scratch_mu;
 static std::vector<Scratch> g_scratch;
+static std::vector<uint8_t*> g_scratch_retired;
 
 int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out) { return scratch_for_slot(s, 0, bytes, out); }
 
-int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) {
+static int scratch_impl(cudaStream_t s, int slot, size_t bytes, bool zeroed, uint8_t** out) {
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(g_scratch_mu);
@@ -117,18 +121,27 @@ int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) {
         hit = &g_scratch.back();
     }
     if (hit->bytes < bytes) {
-        if (hit->buf != nullptr) {
-            JQ_CUDA(cudaFree(hit->buf));  // waits for the device, so no kernel still reads the old buffer
-            hit->buf = nullptr;
-            hit->bytes = 0;
+        const size_t floor_bytes = zeroed ? ((size_t)64 << 10) : ((size_t)1 << 20);
+        const size_t want = bytes < floor_bytes ? floor_bytes : bytes + bytes / 2;
+        uint8_t* fresh = nullptr;
+        JQ_CUDA(cudaMalloc(&fresh, want));
+        if (zeroed) {
+            JQ_CUDA(cudaMemsetAsync(fresh, 0, want, s));  // in stream order before the first kernel that uses it
         }
-        const size_t want = bytes < ((size_t)1 << 20) ? ((size_t)1 << 20) : bytes + bytes / 2;
-        JQ_CUDA(cudaMalloc(&hit->buf, want));
+        if (hit->buf != nullptr) {
+            g_scratch_retired.push_back(hit->buf);
+        }
+        hit->buf = fresh;
         hit->bytes = want;
     }
     *out = hit->buf;
     return JQ_OK;
 }
+
+int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) { return scratch_impl(s, slot, bytes, false, out); }
+
+// The same, for words that kernels use as counters and leave at zero: a new allocation starts out zeroed.
+int scratch_zeroed_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out) { return scratch_impl(s, slot, bytes, true, out); }
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -198,7 +211,9 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
     // Q8_0, Q4_0 and Q4_1 (k a multiple of 256) go two rows at a time through their tensor-core kernel: re-reading the weights
     // (mostly from L2) per pair of rows is far cheaper than the generic kernel's arithmetic.
     const bool blk32 = tc && gemv_blk32_i8_scratch_bytes(w->type, w->k, 2) > 0;
-    const int64_t group = (tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16));
+    const int64_t group = gemv_umma_takes(w->type, w->k, 16)
+                              ? 16
+                              : ((tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16)));
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
@@ -646,9 +661,9 @@ int jq_device_status(int device, int* status) {
     if (rc == JQ_OK && *status == 0) {
         *status = peer;
     }
-    for (int part = 0; part < 2 && rc == JQ_OK; part++) {
+    for (int part = 0; part < 3 && rc == JQ_OK; part++) {
         int other = 0;
-        rc = part == 0 ? gemv_peer_status(&other) : decoder_peer_status(&other);
+        rc = part == 0 ? gemv_peer_status(&other) : (part == 1 ? decoder_peer_status(&other) : gemv_umma_status(&other));
         if (rc == JQ_OK && *status == 0) {
             *status = other;
         }
@@ -711,6 +726,17 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_decoder_fused.store(value != 0);
         return JQ_OK;
     }
+    if (name != nullptr && strcmp(name, "gemv_tcgen05") == 0) {
+        g_opt_gemv_umma.store(value != 0);
+        return JQ_OK;
+    }
+    if (name != nullptr && strcmp(name, "wait_poll_limit") == 0) {
+        if (value < 1 || value > ((int64_t)1 << 30)) {
+            return fail(JQ_ERR_INVALID, "option wait_poll_limit: %lld is outside [1, 2^30]", (long long)value);
+        }
+        g_opt_wait_poll_limit.store(value);
+        return JQ_OK;
+    }
     if (name != nullptr && strcmp(name, "decoder_graph") == 0) {
         g_opt_decoder_graph.store(value != 0);
         return JQ_OK;
@@ -729,6 +755,14 @@ int jq_get_option(const char* name, int64_t* value) {
     }
     if (name != nullptr && value != nullptr && strcmp(name, "decoder_fused") == 0) {
         *value = g_opt_decoder_fused.load();
+        return JQ_OK;
+    }
+    if (name != nullptr && value != nullptr && strcmp(name, "gemv_tcgen05") == 0) {
+        *value = g_opt_gemv_umma.load();
+        return JQ_OK;
+    }
+    if (name != nullptr && value != nullptr && strcmp(name, "wait_poll_limit") == 0) {
+        *value = g_opt_wait_poll_limit.load();
         return JQ_OK;
     }
     if (name != nullptr && value != nullptr && strcmp(name, "decoder_graph") == 0) {

@@ -142,6 +142,21 @@ int scratch_for(cudaStream_t s, size_t bytes, uint8_t** out);
 // A second, third ... scratch buffer of the same (device, stream), for a caller that needs one while a kernel launcher uses slot 0.
 int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out);
 
+// The same for words that kernels use as counters and leave at zero: a new allocation starts out zeroed (in stream order).
+int scratch_zeroed_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out);
+
+// Decode GEMV on tcgen05 (jq_gemv_umma.cu): Q4_K and Q5_K, 1 to 16 rows of x in one pass over the weights.
+bool gemv_umma_takes(int type, int64_t k, int rows);
+size_t gemv_umma_image_bytes(int64_t k, int rows);
+int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s);
+int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
+                     const PeerOut* peer = nullptr);
+int gemv_umma_status(int* status);
+// Option "gemv_tcgen05": zero keeps Q4_K and Q5_K decode on the mma.sync kernels (for comparisons).
+extern std::atomic<int64_t> g_opt_gemv_umma;
+// Option "wait_poll_limit": polls after which a bounded device-side wait gives up.
+extern std::atomic<int64_t> g_opt_wait_poll_limit;
+
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;
 

@@ -1,0 +1,851 @@
+// Decode GEMV on the 5th-generation tensor cores: y[m, n] = x[m, k] . W[n, k]^T for 1 <= m <= 16 rows of x, W in Q4_K or
+// Q5_K, one pass over the weights for every m.
+//
+// Replaces the reference's matrix-vector kernels (kernels/jitllm/TransformerComputeKernelsQ4_K.java:130-215,
+// ...Q5_K.java:422-532, dispatch ops/Gguf.java:170-183). The quants never become floating point:
+//   * the activations are turned into an "image" of signed byte digits (jq_umma_image.cuh: 22-bit fixed point per
+//     super-block of k, three base-256 digits per value, one MMA column per (row of x, digit));
+//   * a persistent CTA per SM walks units of 128 weight rows x one 256-element super-block of k. Per unit
+//       - one thread asks the copy engine for the unit's 128 x 144 bytes of blocks (one cp.async.bulk.tensor.2d box of a
+//         tensor map over the weight as it lies in memory) and for the super-block's image (one cp.async.bulk), both
+//         into shared-memory rings that complete on mbarriers;
+//       - 128 "unpack" threads, one per weight row, widen the row's nibbles to bytes with one AND per four weights and
+//         store them into tensor memory as the A operand (tcgen05.st); the row's 6-bit scales and mins are decoded
+//         once into a small shared-memory ring;
+//       - one thread issues eight tcgen05.mma.cta_group::1.kind::i8 (M = 128 rows, N = 8..48 digit columns, K = 32:
+//         one sub-block each, A from tensor memory, B = the image in shared memory), each into its own accumulator
+//         columns, because every sub-block has its own scale;
+//       - 128 "epilogue" threads, one per weight row, read the accumulators (tcgen05.ld), fold the 6-bit scales in
+//         with integer multiply-adds (the sum over the eight sub-blocks stays below 2^31), convert once per
+//         super-block and digit, and apply fp16 d, dmin and the mins (through the sub-blocks' sums of x).
+//   * a row's result is the sum of its super-blocks' contributions in k order, each contribution rounded to FP32
+//     first. Units are dealt to the CTAs in contiguous runs, so a run can start or end inside a tile; such
+//     pieces are written to a scratch buffer (the first piece as a running sum, later pieces contribution by
+//     contribution) and the CTA that finishes a tile's last piece adds them in k order. The result therefore does not
+//     depend on how many CTAs or rows there are: a row shard of a weight gives bitwise the outputs of the whole weight.
+// Everything up to the float conversion is exact; x keeps 22 bits relative to the largest magnitude of its super-block.
+//
+// Every wait (mbarrier phases) is bounded: a wait that runs out records 64 + its role in a status word, raises the
+// CTA's abort flag, all roles fall through to the common exit and tensor memory is released. No CTA waits for another.
+#include <cstdlib>
+#include <mutex>
+
+#include "jq_formats.cuh"
+#include "jq_peer_device.cuh"
+#include "jq_tc.cuh"
+#include "jq_umma_image.cuh"
+
+namespace jq {
+
+// 0, or 64 + the role whose wait gave up first (1 copy issue, 2 MMA issue, 3 unpack, 4 epilogue) since the last read.
+static __device__ int g_umma_status;
+static __device__ int g_umma_peer_status;
+
+std::atomic<int64_t> g_opt_gemv_umma{1};
+std::atomic<int64_t> g_opt_wait_poll_limit{1 << 22};
+
+namespace {
+
+constexpr int ROWS = 128;        // weight rows per unit (MMA M)
+constexpr int THREADS = 320;     // warp 0: copies, warp 1: MMA issue and tensor-memory owner, warps 2-5: unpack, warps 6-9: epilogue
+constexpr int SP = 4;            // stages of the row-parameter ring
+constexpr int P_BYTES = 2 * ROWS * 16;
+constexpr int SX = 3;            // stages of the image ring
+constexpr int MAX_SW = 12;       // stages of the weight ring (as many as fit)
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+template <int TYPE>
+struct UFmt;
+template <>
+struct UFmt<JQ_TYPE_Q4_K> {
+    static constexpr int BYTES = 144;
+    static constexpr int QS = 16;             // offset of the nibbles
+    static constexpr bool IN_PLACE = true;    // high nibbles stay where they are (16 q): the even sub-blocks' scales carry a factor 16 instead
+};
+template <>
+struct UFmt<JQ_TYPE_Q5_K> {
+    static constexpr int BYTES = 176;
+    static constexpr int QS = 48;
+    static constexpr bool IN_PLACE = false;
+};
+
+struct UArgs {
+    const uint8_t* image;   // [KB][image block]
+    const float* bias;
+    float* y0;
+    float* y1;
+    int64_t n0, n1;         // rows of the first and of the second weight (n1 = 0: none)
+    int KB;                 // super-blocks per weight row
+    int tiles0, tiles;      // 128-row tiles of the first weight, of both
+    int rows;               // rows of x
+    int SW;                 // stages of the weight ring
+    float* partial;         // per CTA [max_pieces + 1][rows][128] floats
+    int* counters;          // per tile: pieces finished (back to zero when the kernel ends)
+    int max_pieces;
+    uint32_t poll_limit;
+    uint32_t lbo, sbo;      // byte offsets of the image's shared-memory descriptor
+    const PeerOut* peer;
+};
+
+template <int NREG>
+__device__ __forceinline__ void tmem_ld(uint32_t (&r)[NREG], uint32_t taddr);
+template <>
+__device__ __forceinline__ void tmem_ld<4>(uint32_t (&r)[4], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<8>(uint32_t (&r)[8], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<16>(uint32_t (&r)[16], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+                   "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr)
+                 : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld<32>(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+          "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]),
+                 "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[128 x N] (tensor memory, s32) = A[128 x 32] (tensor memory, u8) . B[32 x N] (shared memory, s8)
+__device__ __forceinline__ void umma_i8_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d), "r"(tmem_a),
+        "l"(bdesc), "r"(idesc), "r"(0u)
+        : "memory");
+}
+
+// Instruction descriptor of kind::i8: D = S32 (bits 4-5 = 2), A = unsigned 8 bit (bits 7-9 = 0), B = signed 8 bit (bits 10-12 = 1),
+// both K-major, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t idesc_of(int n_cols) { return (2u << 4) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24); }
+
+// Shared-memory descriptor of a K-major operand without swizzle: 8 rows x 16 bytes per core matrix, `lbo` bytes between the
+// core matrices of consecutive 16-byte steps of k, `sbo` bytes between those of consecutive groups of 8 rows; descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+// A wait made by every lane of a warp whose outcome is the same for all of them (the warp executes .sync.aligned instructions next).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit) {
+    return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, abort_flag, &g_umma_status, code, limit) ? 1 : 0) != 0;
+}
+
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+template <int N>
+__global__ void __launch_bounds__(128) umma_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k, uint8_t* __restrict__ image) {
+    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV may start asking for weights
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x is complete, and the GEMV before this one is done with the image
+    const int pair = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int b = pair / rows, m = pair % rows;
+    if (b < (int)(k >> 8)) {
+        umma::build_image<N>(x + (int64_t)m * k + (int64_t)b * 256, m, rows, image + (size_t)b * umma::ImageCfg<N>::BYTES, threadIdx.x & 31);
+    }
+}
+
+// MR = rows of x the epilogue computes (1, 2, 5, 8, 10 or 16; a call with fewer rows leaves the others unused).
+template <int TYPE, int MR, bool PEER>
+__global__ void __launch_bounds__(THREADS, 1)
+    gemv_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const UArgs a) {
+    constexpr int N = umma::columns_for_rows(MR);
+    using IC = umma::ImageCfg<N>;
+    using F = UFmt<TYPE>;
+    constexpr int SG = N <= 16 ? 8 : 4;         // sub-blocks per accumulator stage
+    constexpr int NGROUPS = 8 / SG;
+    constexpr int D_COLS = SG * N;              // tensor-memory columns of an accumulator stage
+    constexpr int A_COLS = 64;                  // of an A stage: 8 sub-blocks x 32 bytes
+    constexpr int D_BASE = 2 * A_COLS;
+    constexpr uint32_t TMEM_COLS = D_BASE + 2 * D_COLS <= 256 ? 256u : 512u;
+    static_assert(D_BASE + 2 * D_COLS <= 512, "tensor memory has 512 columns");
+    constexpr int WB = ROWS * F::BYTES;
+    constexpr int XB = (IC::BYTES + 127) & ~127;
+    constexpr uint32_t IDESC = idesc_of(N);
+    constexpr int LDC = MR == 1 ? 4 : (N == 8 ? 8 : (N == 16 ? 16 : 32));  // accumulator columns per tcgen05.ld (N = 48: one of 32, one of 16)
+
+    extern __shared__ uint8_t smem_unaligned[];
+    uint8_t* smem = smem_unaligned + ((128u - (tc::smem_u32(smem_unaligned) & 127u)) & 127u);
+    const int SW = a.SW;
+    uint8_t* w_ring = smem;
+    uint8_t* x_ring = w_ring + (size_t)SW * WB;
+    uint8_t* p_ring = x_ring + SX * XB;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_ring + SP * P_BYTES);
+    const uint32_t bar0 = tc::smem_u32(bars);
+    auto full_w = [&](int s) { return bar0 + 8u * (uint32_t)s; };
+    auto empty_w = [&](int s) { return bar0 + 8u * (uint32_t)(MAX_SW + s); };
+    auto full_x = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + s); };
+    auto empty_x = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + SX + s); };
+    auto full_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * SX + s); };
+    auto empty_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * SX + SP + s); };
+    constexpr int B2 = 2 * MAX_SW + 2 * SX + 2 * SP;
+    auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + s); };
+    auto empty_a = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 2 + s); };
+    auto full_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 4 + s); };
+    auto empty_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 6 + s); };
+    constexpr int NBARS = B2 + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* fin = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [0] this CTA adds the tile up, [1], [2] first and last CTA of the tile
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = a.KB;
+    const int64_t U = (int64_t)a.tiles * KB;
+    const int64_t G = gridDim.x;
+    const int64_t u0 = (int64_t)blockIdx.x * U / G;
+    const int units = (int)(((int64_t)blockIdx.x + 1) * U / G - u0);
+    const uint32_t limit = a.poll_limit;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < MAX_SW; s++) {
+            tc::mbar_init(full_w(s), 1);
+            tc::mbar_init(empty_w(s), ROWS);
+        }
+        for (int s = 0; s < SX; s++) {
+            tc::mbar_init(full_x(s), 1);
+            tc::mbar_init(empty_x(s), 1 + 4);  // the MMAs that read the digits, and one lane of each epilogue warp
+        }
+        for (int s = 0; s < SP; s++) {
+            tc::mbar_init(full_p(s), ROWS);
+            tc::mbar_init(empty_p(s), ROWS);
+        }
+        for (int s = 0; s < 2; s++) {
+            tc::mbar_init(full_a(s), ROWS);
+            tc::mbar_init(empty_a(s), 1);
+            tc::mbar_init(full_d(s), 1);
+            tc::mbar_init(empty_d(s), ROWS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- copies: weights as soon as a slot is free (they depend on nothing), images once the kernel before has finished ----
+        int iw = 0, ix = 0;
+        bool dep_done = false;
+        uint32_t idle = 0;
+        const int prologue = units < SW ? units : SW;
+        while (iw < units || ix < units) {
+            bool progress = false;
+            if (lane == 0 && iw < units) {
+                const int s = iw % SW;
+                if (tc::mbar_try(empty_w(s), (((uint32_t)(iw / SW)) & 1u) ^ 1u)) {
+                    const int64_t u = u0 + iw;
+                    const int t = (int)(u / KB), b = (int)(u % KB);
+                    tc::mbar_expect_tx(full_w(s), WB);
+                    const bool first = t < a.tiles0;
+                    tc::tma_load_2d(tc::smem_u32(w_ring + (size_t)s * WB), first ? &map0 : &map1, full_w(s), b * F::BYTES, (first ? t : t - a.tiles0) * ROWS);
+                    iw++;
+                    progress = true;
+                }
+            }
+            iw = __shfl_sync(0xffffffffu, iw, 0);
+            if (!dep_done && iw >= prologue) {
+                asm volatile("griddepcontrol.wait;" ::: "memory");  // the image is complete
+                if constexpr (PEER) {
+                    if (a.peer->wait_first) {
+                        // the image is what the ranks' latest exchange delivered: complete once all their flags are up
+                        peer_wait_inline(a.peer->flags[a.peer->rank], a.peer->world, lane, &g_umma_peer_status);
+                    }
+                }
+                dep_done = true;
+            }
+            if (lane == 0 && dep_done && ix < units) {
+                const int s = ix % SX;
+                if (tc::mbar_try(empty_x(s), (((uint32_t)(ix / SX)) & 1u) ^ 1u)) {
+                    const int b = (int)((u0 + ix) % KB);
+                    tc::mbar_expect_tx(full_x(s), IC::BYTES);
+                    tc::bulk_load(tc::smem_u32(x_ring + s * XB), a.image + (size_t)b * IC::BYTES, IC::BYTES, full_x(s));
+                    ix++;
+                    progress = true;
+                }
+            }
+            ix = __shfl_sync(0xffffffffu, ix, 0);
+            int stop = 0;
+            if (lane == 0) {
+                if (progress) {
+                    idle = 0;
+                } else if (++idle >= limit) {
+                    atomicCAS(&g_umma_status, 0, 64 + 1);
+                    *abort_flag = 1;
+                    stop = 1;
+                } else if ((idle & 63u) == 0 && *abort_flag != 0) {
+                    stop = 1;
+                }
+            }
+            if (__shfl_sync(0xffffffffu, stop, 0) != 0) {
+                break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue -------------------------------------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t dcount = 0;
+            bool ok = true;
+            for (int i = 0; i < units && ok; i++) {
+                const int as = i & 1, xs = i % SX;
+                ok = tc::mbar_wait(full_x(xs), ((uint32_t)(i / SX)) & 1u, abort_flag, &g_umma_status, 64 + 2, limit) &&
+                     tc::mbar_wait(full_a(as), ((uint32_t)(i >> 1)) & 1u, abort_flag, &g_umma_status, 64 + 2, limit);
+                if (!ok) {
+                    break;
+                }
+                const uint32_t xaddr = tc::smem_u32(x_ring + xs * XB);
+#pragma unroll
+                for (int g = 0; g < NGROUPS; g++) {
+                    const uint32_t ds = dcount & 1u;
+                    ok = tc::mbar_wait(empty_d(ds), ((dcount >> 1) & 1u) ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
+                    if (!ok) {
+                        break;
+                    }
+                    tc::fence_after_sync();
+#pragma unroll
+                    for (int sg = 0; sg < SG; sg++) {
+                        const int s = g * SG + sg;
+                        umma_i8_ts(tmem + (uint32_t)(D_BASE + ds * D_COLS + sg * N), tmem + (uint32_t)(as * A_COLS + s * 8),
+                                   smem_desc_plain(xaddr + (uint32_t)(s * IC::SUB_BYTES), a.lbo, a.sbo), IDESC);
+                    }
+                    tc::umma_commit(full_d(ds));
+                    dcount++;
+                }
+                if (ok) {
+                    tc::umma_commit(empty_a(as));
+                    tc::umma_commit(empty_x(xs));
+                }
+            }
+        }
+    } else if (warp < 6) {
+        // ---- unpack: thread = weight row; a warp may only touch the tensor-memory lanes 32 (warp % 4) .. + 31 --------------------
+        const int r = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        for (int i = 0; i < units; i++) {
+            const int ws = i % SW, ps = i % SP, as = i & 1;
+            if (!warp_wait(full_w(ws), ((uint32_t)(i / SW)) & 1u, abort_flag, 64 + 3, limit)) {
+                break;
+            }
+            const uint8_t* wrow = w_ring + (size_t)ws * WB + r * F::BYTES;
+            const uint4 h = *reinterpret_cast<const uint4*>(wrow);  // fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins
+            const uint32_t sca = h.y & 0x3f3f3f3fu, scb = and_or(h.y >> 2, 0x30303030u, h.w & 0x0f0f0f0fu);            // scales 0..3, 4..7
+            const uint32_t mna = h.z & 0x3f3f3f3fu, mnb = and_or(h.z >> 2, 0x30303030u, (h.w >> 4) & 0x0f0f0f0fu);     // mins 0..3, 4..7
+            uint32_t sc16[4];  // the scales of sub-blocks 2j and 2j + 1 as 16-bit halves
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t pr = __byte_perm(j < 2 ? sca : scb, 0u, 0x4140u + (uint32_t)(2 * (j & 1)) * 0x0101u);  // bytes (e, 0, o, 0)
+                sc16[j] = F::IN_PLACE ? pr + (pr & 0xffffu) * 15u : pr;
+            }
+            if (!warp_wait(empty_p(ps), (((uint32_t)(i / SP)) & 1u) ^ 1u, abort_flag, 64 + 3, limit)) {
+                break;
+            }
+            uint4* prow = reinterpret_cast<uint4*>(p_ring + ps * P_BYTES) + r;
+            prow[0] = make_uint4(sc16[0], sc16[1], sc16[2], sc16[3]);
+            prow[ROWS] = make_uint4(mna, mnb, h.x, 0u);
+            tc::mbar_arrive(full_p(ps));
+            if (!warp_wait(empty_a(as), (((uint32_t)(i >> 1)) & 1u) ^ 1u, abort_flag, 64 + 3, limit)) {
+                break;
+            }
+            tc::fence_after_sync();
+            uint4 qh0 = make_uint4(0u, 0u, 0u, 0u), qh1 = qh0;
+            if constexpr (TYPE == JQ_TYPE_Q5_K) {
+                qh0 = *reinterpret_cast<const uint4*>(wrow + 16);
+                qh1 = *reinterpret_cast<const uint4*>(wrow + 32);
+            }
+            const uint32_t hw[8] = {qh0.x, qh0.y, qh0.z, qh0.w, qh1.x, qh1.y, qh1.z, qh1.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 qa = *reinterpret_cast<const uint4*>(wrow + F::QS + 32 * j);
+                const uint4 qb = *reinterpret_cast<const uint4*>(wrow + F::QS + 32 * j + 16);
+                const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                uint32_t av[16];  // sub-block 2j: bytes 0..31, then sub-block 2j + 1
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    if constexpr (TYPE == JQ_TYPE_Q5_K) {
+                        // bit 2j (2j + 1) of the fifth-bit bytes goes to bit 4 of the low (high) nibbles' bytes
+                        const uint32_t e = 2 * j <= 4 ? hw[c] << (4 - 2 * j) : hw[c] >> (2 * j - 4);
+                        const uint32_t o = 2 * j + 1 <= 4 ? hw[c] << (3 - 2 * j) : hw[c] >> (2 * j - 3);
+                        av[c] = and_or(e, 0x10101010u, w[c] & 0x0f0f0f0fu);
+                        av[8 + c] = and_or(o, 0x10101010u, (w[c] >> 4) & 0x0f0f0f0fu);
+                    } else {
+                        av[c] = w[c] & 0x0f0f0f0fu;
+                        av[8 + c] = w[c] & 0xf0f0f0f0u;
+                    }
+                }
+                tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 16 * j), av);
+            }
+            tmem_st_wait();
+            tc::mbar_arrive(empty_w(ws));  // this row's bytes of the slot are in registers or tensor memory
+            tc::fence_before_sync();
+            tc::mbar_arrive(full_a(as));
+        }
+    } else {
+        // ---- epilogue: thread = weight row -----------------------------------------------------------------------------------------
+        const int r = (warp & 3) * 32 + lane;
+        const int et = threadIdx.x - 6 * 32;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // y and the scratch are no longer in use by the kernel before
+        float acc[MR];
+#pragma unroll
+        for (int m = 0; m < MR; m++) {
+            acc[m] = 0.0f;
+        }
+        int t = (int)(u0 / KB), b = (int)(u0 % KB);
+        bool piecewise = b > 0;  // the run starts inside a tile: its contributions go to the scratch one by one
+        int piece_b0 = b;
+        uint32_t dcount = 0;
+        const size_t slot_floats = (size_t)(a.max_pieces + 1) * a.rows * ROWS;
+        float* const my_slot = a.partial + (size_t)blockIdx.x * slot_floats;
+        bool ok = true;
+        for (int i = 0; i < units && ok; i++) {
+            const int ps = i % SP, xs = i % SX;
+            if (!warp_wait(full_p(ps), ((uint32_t)(i / SP)) & 1u, abort_flag, 64 + 4, limit)) {
+                break;
+            }
+            const uint4* prow = reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r;
+            const uint4 pa = prow[0], pb = prow[ROWS];
+            tc::mbar_arrive(empty_p(ps));
+            const uint32_t sc16[4] = {pa.x, pa.y, pa.z, pa.w};
+            int I[MR][3];
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                I[m][0] = I[m][1] = I[m][2] = 0;
+            }
+#pragma unroll
+            for (int g = 0; g < NGROUPS; g++) {
+                const uint32_t ds = dcount & 1u;
+                ok = warp_wait(full_d(ds), (dcount >> 1) & 1u, abort_flag, 64 + 4, limit);
+                if (!ok) {
+                    break;
+                }
+                tc::fence_after_sync();
+                const uint32_t dbase = tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS);
+                if constexpr (N == 48) {
+#pragma unroll
+                    for (int sg = 0; sg < SG; sg++) {
+                        uint32_t dlo[32], dhi[16];
+                        tmem_ld<32>(dlo, dbase + (uint32_t)(sg * N));
+                        tmem_ld<16>(dhi, dbase + (uint32_t)(sg * N + 32));
+                        tmem_ld_wait();
+                        const int s = g * SG + sg;
+                        const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+#pragma unroll
+                            for (int dg = 0; dg < 3; dg++) {
+                                const int col = 3 * m + dg;
+                                I[m][dg] += scale * (int)(col < 32 ? dlo[col < 32 ? col : 0] : dhi[col >= 32 ? col - 32 : 0]);
+                            }
+                        }
+                    }
+                } else {
+                    constexpr int CS = (64 / LDC) < SG ? (64 / LDC) : SG;  // sub-blocks whose accumulators are in registers at a time
+#pragma unroll
+                    for (int c0 = 0; c0 < SG; c0 += CS) {
+                        uint32_t dv[CS][LDC];
+#pragma unroll
+                        for (int c = 0; c < CS; c++) {
+                            tmem_ld<LDC>(dv[c], dbase + (uint32_t)((c0 + c) * N));
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < CS; c++) {
+                            const int s = g * SG + c0 + c;
+                            const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
+#pragma unroll
+                            for (int m = 0; m < MR; m++) {
+#pragma unroll
+                                for (int dg = 0; dg < 3; dg++) {
+                                    I[m][dg] += scale * (int)dv[c][3 * m + dg];
+                                }
+                            }
+                        }
+                    }
+                }
+                tc::fence_before_sync();
+                tc::mbar_arrive(empty_d(ds));
+                dcount++;
+            }
+            if (!ok || !warp_wait(full_x(xs), ((uint32_t)(i / SX)) & 1u, abort_flag, 64 + 4, limit)) {
+                ok = false;
+                break;
+            }
+            // ---- this super-block's contribution: d (sum over digits of weight x integer) - dmin (sum over sub-blocks of min x sum of x) ----
+            const float* aux = reinterpret_cast<const float*>(x_ring + xs * XB + IC::XD);
+            const float d = half_bits_to_float(pb.z) * (F::IN_PLACE ? 0.0625f : 1.0f), dmin = half_bits_to_float(pb.z >> 16);
+            float msum[MR];
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                msum[m] = 0.0f;
+            }
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                const float mn = (float)(((s < 4 ? pb.x : pb.y) >> (8 * (s & 3))) & 0xffu);
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    msum[m] = fmaf(mn, aux[s * IC::MPAD + m], msum[m]);
+                }
+            }
+            float c[MR];
+#pragma unroll
+            for (int m = 0; m < MR; m++) {
+                const float w0 = aux[8 * IC::MPAD + m];
+                const float q = fmaf(w0 * 65536.0f, (float)I[m][2], fmaf(w0 * 256.0f, (float)I[m][1], w0 * (float)I[m][0]));
+                c[m] = fmaf(d, q, -(dmin * msum[m]));
+            }
+            __syncwarp();
+            if (lane == 0) {
+                tc::mbar_arrive(empty_x(xs));
+            }
+            if (piecewise) {
+                float* dst = my_slot + (size_t)(b - piece_b0) * a.rows * ROWS + r;
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    if (m < a.rows) {
+                        dst[m * ROWS] = c[m];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    acc[m] += c[m];
+                }
+            }
+            const bool tile_end = b == KB - 1;
+            if (tile_end || i == units - 1) {
+                const bool second = t >= a.tiles0;
+                const int64_t n = second ? a.n1 : a.n0;
+                const int64_t row = (int64_t)(second ? t - a.tiles0 : t) * ROWS + r;
+                float* const yo = second ? a.y1 : a.y0;
+                bool write = !piecewise && tile_end;  // a whole tile
+                if (!write) {
+                    if (!piecewise) {
+                        float* dst = my_slot + (size_t)a.max_pieces * a.rows * ROWS + r;  // the running sum of the tile's first super-blocks
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+                            if (m < a.rows) {
+                                dst[m * ROWS] = acc[m];
+                            }
+                        }
+                    }
+                    __threadfence();
+                    epilogue_barrier();
+                    if (et == 0) {
+                        const int c_first = (int)((((int64_t)t * KB + 1) * G - 1) / U), c_last = (int)((((int64_t)(t + 1) * KB) * G - 1) / U);
+                        const int done = atomicAdd(a.counters + t, 1);
+                        const int last = done == c_last - c_first;
+                        if (last) {
+                            a.counters[t] = 0;
+                        }
+                        fin[0] = last;
+                        fin[1] = c_first;
+                        fin[2] = c_last;
+                    }
+                    epilogue_barrier();
+                    if (fin[0] != 0) {
+                        // every piece of the tile is in the scratch: add them in k order
+                        __threadfence();
+                        const int c_first = fin[1], c_last = fin[2];
+#pragma unroll
+                        for (int m = 0; m < MR; m++) {
+                            acc[m] = 0.0f;
+                        }
+                        for (int cta = c_first; cta <= c_last; cta++) {
+                            const int64_t lo = (int64_t)cta * U / G, hi = ((int64_t)cta + 1) * U / G, tb = (int64_t)t * KB;
+                            const int s0 = (int)((lo > tb ? lo : tb) - tb), s1 = (int)((hi < tb + KB ? hi : tb + KB) - tb);
+                            const float* slot = a.partial + (size_t)cta * slot_floats + r;
+                            if (s0 == 0) {
+#pragma unroll
+                                for (int m = 0; m < MR; m++) {
+                                    if (m < a.rows) {
+                                        acc[m] = __ldcg(slot + ((size_t)a.max_pieces * a.rows + m) * ROWS);
+                                    }
+                                }
+                            } else {
+                                for (int p = 0; p < s1 - s0; p++) {
+#pragma unroll
+                                    for (int m = 0; m < MR; m++) {
+                                        if (m < a.rows) {
+                                            acc[m] += __ldcg(slot + ((size_t)p * a.rows + m) * ROWS);
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                        write = true;
+                    }
+                }
+                if (write && row < n) {
+                    const float bv = (a.bias != nullptr && !second) ? a.bias[row] : 0.0f;
+#pragma unroll
+                    for (int m = 0; m < MR; m++) {
+                        if (m < a.rows) {
+                            const float val = acc[m] + bv;
+                            if constexpr (!PEER) {
+                                yo[(int64_t)m * n + row] = val;
+                            } else {
+                                // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
+                                for (int rk = 0; rk < a.peer->world; rk++) {
+                                    a.peer->y[rk][(int64_t)m * a.peer->n_total + a.peer->col0 + row] = val;
+                                }
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    acc[m] = 0.0f;
+                }
+                piecewise = false;
+                piece_b0 = 0;
+            }
+            if (++b == KB) {
+                b = 0;
+                t++;
+            }
+        }
+    }
+    // ---- common exit: everyone arrives, copies in flight get a bounded time to land after an abort, tensor memory is released ----
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0) {
+        for (int s = 0; s < SW + SX; s++) {
+            const uint32_t bar = s < SW ? full_w(s) : full_x(s - SW);
+            for (uint32_t p = 0; p < (1u << 14); p++) {
+                if (tc::mbar_try(bar, 0) || tc::mbar_try(bar, 1)) {
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    if constexpr (PEER) {
+        peer_publish(a.peer->flags, a.peer->rank, a.peer->world, const_cast<int*>(fin));  // the last CTA raises this rank's flag on every rank
+    }
+}
+
+int sm_count_of_current_device() {
+    static std::atomic<int> cached{0};
+    int v = cached.load();
+    if (v == 0) {
+        int dev = 0, sms = 0;
+        v = (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) ? sms : 148;
+        cached.store(v);
+    }
+    return v;
+}
+
+int weight_map(const View& v, int block_bytes, CUtensorMap* map) {
+    EncodeTiledFn enc = encode_tiled();
+    if (enc == nullptr) {
+        return fail(JQ_ERR_CUDA, "decode GEMV: cuTensorMapEncodeTiled is not available from this driver");
+    }
+    // the weight as a matrix of bytes [n rows][k / 256 x block bytes]; a box is one block of 128 consecutive rows
+    const cuuint64_t dims[2] = {(cuuint64_t)(v.k / 256) * (cuuint64_t)block_bytes, (cuuint64_t)v.n};
+    const cuuint64_t strides[1] = {dims[0]};
+    const cuuint32_t box[2] = {(cuuint32_t)block_bytes, (cuuint32_t)ROWS};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(v.q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(JQ_ERR_CUDA, "decode GEMV: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    }
+    return JQ_OK;
+}
+
+template <int TYPE, int MR, bool PEER>
+int launch_typed(const CUtensorMap& m0, const CUtensorMap& m1, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    JQ_CUDA(cudaGetDevice(&dev));
+    if ((configured.load() >> (dev & 63) & 1) == 0) {
+        JQ_CUDA(cudaFuncSetAttribute(gemv_umma_kernel<TYPE, MR, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        configured.fetch_or((uint64_t)1 << (dev & 63));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may ask for weights while the kernel before it still runs
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_umma_kernel<TYPE, MR, PEER>, m0, m1, a));
+    count_launch();
+    return JQ_OK;
+}
+
+template <int TYPE, bool PEER>
+int by_rows(int mr, const CUtensorMap& m0, const CUtensorMap& m1, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+    switch (mr) {
+        case 1: return launch_typed<TYPE, 1, PEER>(m0, m1, a, grid, smem, s);
+        case 2: return launch_typed<TYPE, 2, PEER>(m0, m1, a, grid, smem, s);
+        case 5: return launch_typed<TYPE, 5, PEER>(m0, m1, a, grid, smem, s);
+        case 8: return launch_typed<TYPE, 8, PEER>(m0, m1, a, grid, smem, s);
+        case 10: return launch_typed<TYPE, 10, PEER>(m0, m1, a, grid, smem, s);
+        default: return launch_typed<TYPE, 16, PEER>(m0, m1, a, grid, smem, s);
+    }
+}
+
+template <int N>
+int launch_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.stream = s;
+    cfg.gridDim = dim3((unsigned)(((k / 256) * rows + 3) / 4));
+    cfg.blockDim = dim3(128);
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, umma_activation_image_kernel<N>, x, rows, k, image));
+    count_launch();
+    return JQ_OK;
+}
+
+int rows_bucket(int rows) { return rows <= 2 ? rows : (rows <= 5 ? 5 : (rows <= 8 ? 8 : (rows <= 10 ? 10 : 16))); }
+
+}  // namespace
+
+size_t gemv_umma_image_bytes(int64_t k, int rows) {
+    if (rows < 1 || rows > 16 || k <= 0 || k % 256 != 0) {
+        return 0;
+    }
+    return (size_t)(k / 256) * umma::image_block_bytes(umma::columns_for_rows(rows_bucket(rows)));
+}
+
+bool gemv_umma_takes(int type, int64_t k, int rows) {
+    return (type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K) && rows >= 1 && rows <= 16 && k > 0 && k % 256 == 0 &&
+           g_opt_gemv_umma.load(std::memory_order_relaxed) != 0 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0;
+}
+
+// Writes the activation image of x [rows, k] for gemv_umma (rows in [1, 16]) into `image` (gemv_umma_image_bytes bytes).
+int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s) {
+    switch (umma::columns_for_rows(rows_bucket(rows))) {
+        case 8: return launch_image<8>(x, rows, k, image, s);
+        case 16: return launch_image<16>(x, rows, k, image, s);
+        case 32: return launch_image<32>(x, rows, k, image, s);
+        default: return launch_image<48>(x, rows, k, image, s);
+    }
+}
+
+// y [rows, n] = x . W^T (+ bias) for a Q4_K or Q5_K weight and 1 to 16 rows of x whose image is in `image` (written earlier
+// in the stream). With v2 != nullptr the rows of a second weight of the same type and k follow in the same launch
+// (results in y2, no bias). `peer`: the outputs go into every rank's y of a row-sharded linear instead.
+int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
+                     const PeerOut* peer) {
+    if (!gemv_umma_takes(v.type, v.k, rows) || v.n <= 0 || (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
+        return fail(JQ_ERR_UNSUPPORTED, "decode GEMV: type %d, k = %lld, %d rows is outside what the tcgen05 kernel takes", v.type, (long long)v.k, rows);
+    }
+    const int bb = v.type == JQ_TYPE_Q4_K ? 144 : 176;
+    const int mr = rows_bucket(rows);
+    const int ncols = umma::columns_for_rows(mr);
+    CUtensorMap m0, m1;
+    int rc = weight_map(v, bb, &m0);
+    if (rc == JQ_OK) {
+        rc = v2 != nullptr ? weight_map(*v2, bb, &m1) : weight_map(v, bb, &m1);
+    }
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    UArgs a = {};
+    a.image = image;
+    a.bias = bias;
+    a.y0 = y;
+    a.y1 = y2;
+    a.n0 = v.n;
+    a.n1 = v2 != nullptr ? v2->n : 0;
+    a.KB = (int)(v.k / 256);
+    a.tiles0 = (int)((v.n + ROWS - 1) / ROWS);
+    a.tiles = a.tiles0 + (v2 != nullptr ? (int)((v2->n + ROWS - 1) / ROWS) : 0);
+    a.rows = rows;
+    const int64_t U = (int64_t)a.tiles * a.KB;
+    const int sms = sm_count_of_current_device();
+    const int grid = (int)(U < sms ? U : sms);
+    const int64_t per_cta = (U + grid - 1) / grid;
+    a.max_pieces = (int)(per_cta < a.KB - 1 ? per_cta : a.KB - 1);
+    if (a.max_pieces < 1) {
+        a.max_pieces = 1;
+    }
+    const size_t xb = (umma::image_block_bytes(ncols) + 127) & ~(size_t)127;
+    const size_t fixed = 128 + SX * xb + SP * P_BYTES + 1024;
+    int sw = (int)((SMEM_MAX - fixed) / ((size_t)ROWS * bb));
+    a.SW = sw > MAX_SW ? MAX_SW : sw;
+    const size_t smem = fixed + (size_t)a.SW * ROWS * bb;
+    a.poll_limit = (uint32_t)g_opt_wait_poll_limit.load(std::memory_order_relaxed);
+    a.lbo = (uint32_t)(ncols / 8) * 128u;
+    a.sbo = 128u;
+    if (getenv("JQ_UMMA_DESC_SWAP") != nullptr) {
+        a.lbo = 128u;
+        a.sbo = (uint32_t)(ncols / 8) * 128u;
+    }
+    a.peer = peer != nullptr ? peer->table : nullptr;
+    uint8_t* partial = nullptr;
+    uint8_t* counters = nullptr;
+    rc = scratch_for_slot(s, 2, (size_t)grid * (a.max_pieces + 1) * rows * ROWS * sizeof(float), &partial);
+    if (rc == JQ_OK) {
+        rc = scratch_zeroed_for_slot(s, 3, (size_t)a.tiles * sizeof(int), &counters);
+    }
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    a.partial = reinterpret_cast<float*>(partial);
+    a.counters = reinterpret_cast<int*>(counters);
+    if (v.type == JQ_TYPE_Q4_K) {
+        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, m0, m1, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, m0, m1, a, grid, smem, s);
+    }
+    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, m0, m1, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, m0, m1, a, grid, smem, s);
+}
+
+// Reads and clears the status words of the tcgen05 GEMV on the current device (0 = no wait ever gave up).
+int gemv_umma_status(int* status) {
+    const int zero = 0;
+    int peer = 0;
+    JQ_CUDA(cudaMemcpyFromSymbol(status, g_umma_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(int)));
+    JQ_CUDA(cudaMemcpyFromSymbol(&peer, g_umma_peer_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_umma_peer_status, &zero, sizeof(int)));
+    if (*status == 0) {
+        *status = peer;
+    }
+    return JQ_OK;
+}
+
+}  // namespace jq

@@ -327,7 +327,22 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
     cudaStream_t s = (cudaStream_t)stream;
     const View v{w->q, w->aux, w->n, w->k, w->type};
     bool fused = false;
-    if ((w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K) && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
+    if (w->n > 0 && gemv_umma_takes(w->type, w->k, (int)m)) {
+        // the tcgen05 GEMV stores into every rank's y and publishes the exchange itself
+        PeerOut po;
+        memset(&po, 0, sizeof(po));
+        for (int r = 0; r < PEER_MAX_WORLD; r++) {
+            po.y[r] = tg.y[r];
+            po.flags[r] = tg.flags[r];
+        }
+        po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        rc = device_table(po, s, &po.table);
+        uint8_t* image = nullptr;
+        if (rc == JQ_OK) rc = scratch_for(s, gemv_umma_image_bytes(w->k, (int)m), &image);
+        if (rc == JQ_OK) rc = launch_gemv_umma_image(x, (int)m, w->k, image, s);
+        if (rc == JQ_OK) rc = launch_gemv_umma(v, nullptr, image, (int)m, bias, nullptr, nullptr, s, &po);
+        fused = rc == JQ_OK;
+    } else if ((w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K) && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
         // the GEMV kernel itself stores into every rank's y and publishes the exchange; it reads the targets from a table
         // in this rank's flag area, which is written once per distinct (buffers, area, shard) and then found again
         PeerOut po;

@@ -21,6 +21,7 @@
 #include <mutex>
 
 #include "jq_formats.cuh"
+#include "jq_tc.cuh"
 
 namespace jq {
 
@@ -445,22 +446,6 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* _
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-        }
-    });
-    return fn;
-}
-
 template <int TYPE, int TILE_T, int NF, bool SPLIT>
 int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
@@ -483,6 +468,19 @@ int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bia
 }
 
 }  // namespace
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    });
+    return fn;
+}
 
 bool prefill_supported(const View& v) {
     return has_linear_kernel(v.type) && v.k % STAGE_K == 0 && v.n > 0 && v.k > 0;
