@@ -110,8 +110,13 @@ JQ_API int jq_weight_download(const jq_weight* w, void* host_blocks, int64_t nby
 JQ_API int jq_dequantize(const jq_weight* w, float* dst, int dst_mem, void* stream);
 
 /*
- * y[m, n] = x[m, k] * W^T (+ bias[n]), float32 activations and outputs, FP32 accumulation; the
- * activations are never quantised. Stands in for Gguf.linear(x, w, bias) (ops/Gguf.java:76-98) and
+ * y[m, n] = x[m, k] * W^T (+ bias[n]), float32 activations and outputs. The reference never quantises
+ * activations to a block format and neither does this: the decode kernels of the K-quant and 32-block formats
+ * multiply the integer quants exactly with x held as 22-bit fixed point per 256-element super-block of k (relative
+ * to the super-block's largest magnitude: a rounding of at most 2^-22 of that magnitude per element, the order of
+ * FP32's own), and add the super-blocks' results up in FP32 in k order; measured against the double-precision
+ * reference arithmetic the error stays below 1e-6 of the largest output. An x that holds a NaN or an Inf gives
+ * non-finite outputs (Q4_K, Q5_K: NaN in every output of that row of x). Stands in for Gguf.linear(x, w, bias) (ops/Gguf.java:76-98) and
  * Quant.linear / F.linearQ8 (ops/Quant.java:66-80): any m >= 0 (leading axes of x flattened by the
  * caller as ops/Gguf.java:86-93 does), bias may be NULL. Rows are dispatched like the reference
  * dispatches them (ops/Gguf.java:90): m <= 16 to the fused dequantise-GEMV kernels, larger m in
@@ -202,21 +207,27 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "decoder_graph"     zero: the decoder issues its single-token step kernel by kernel instead of replaying a CUDA graph.
  *   "decoder_fused"     zero: the decoder's single-token step uses the general kernels (one per operator) instead of the
  *                       fused ones that hand activations to the next linear as its activation image.
+ *   "gemv_tcgen05"      zero: Q4_K and Q5_K decode GEMVs run on the generic kernel instead of the tcgen05 one (for comparisons).
+ *   "wait_poll_limit"   polls after which a bounded device-side wait of the tcgen05 GEMV gives up (default 2^22; a wait that
+ *                       gives up makes jq_device_status report 64 + the waiting role and the outputs of that call undefined).
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);
 
 /*
- * y[m, n] = x[m, k] * W^T (+ bias[n]) for a Q4_K weight, 1 <= m <= 8, device pointers only (16-byte aligned),
- * enqueued on `stream`: the same kernels and the same results as jq_linear_f32, but the call allocates no
- * memory. It has no counterpart in the reference. jq_linear_f32 keeps its intermediate "activation image" in a
- * buffer it allocates with cudaMalloc when a stream first needs one; this entry point is for callers that
- * cannot have that happen: a process that has already given all device memory to its own pools (the allocation
- * would fail), or a latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives
- * in a 1 MiB array that is part of the library itself, so every GPU that loads the library holds that 1 MiB
- * until the process exits. Limits: the image, (k / 256) * 896 bytes for one row, 1824 for two and 7008 for three to
- * eight rows, must fit 1 MiB (for example k <= 38144 at eight rows); anything larger, any
- * other format and any other row count is refused with JQ_ERR_INVALID or JQ_ERR_UNSUPPORTED and a message.
+ * y[m, n] = x[m, k] * W^T (+ bias[n]) for a Q4_K weight, 1 <= m <= 16, device pointers only (16-byte aligned),
+ * enqueued on `stream`: the same kernels and bit for bit the same results as jq_linear_f32, but the call allocates
+ * no memory. It has no counterpart in the reference. jq_linear_f32 keeps its intermediate data (the "activation
+ * image" of x, and partial sums of weight tiles that several thread blocks share) in buffers it allocates with
+ * cudaMalloc when a stream first needs them; this entry point is for callers that cannot have that happen: a
+ * process that has already given all device memory to its own pools (the allocation would fail), or a
+ * latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives in a 1 MiB array that
+ * is part of the library itself, so every GPU that loads the library holds that 1 MiB until the process exits, and
+ * the thread blocks are dealt whole tiles of 128 weight rows, which needs no partial sums (and is slower than
+ * jq_linear_f32 for weights of few rows). Limits: the image, (k / 256) * 2192 bytes for one or two rows of x, 4384
+ * for three to five, 8624 for six to ten and 12864 for eleven to sixteen rows, must fit 1 MiB (for example
+ * k <= 20736 at sixteen rows); anything larger and any other row count is refused with JQ_ERR_INVALID, any other
+ * format with JQ_ERR_UNSUPPORTED, both with a message.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call before starting any stream capture. All calls share the one array, which keeps
  * whatever the last call left in it; every call rewrites the part it reads, nothing has to start at zero.

@@ -206,14 +206,12 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
         }
         return rc;
     }
-    // The integer tensor-core kernel of Q4_K and Q5_K takes up to 8 activation rows per pass, Q6_K's 4, the generic kernel 16.
+    // The tcgen05 kernel of Q4_K and Q5_K takes up to 16 activation rows per pass, Q6_K's integer kernel 4, the generic kernel 16.
     const bool tc = g_opt_gemv_generic.load() == 0;
     // Q8_0, Q4_0 and Q4_1 (k a multiple of 256) go two rows at a time through their tensor-core kernel: re-reading the weights
     // (mostly from L2) per pair of rows is far cheaper than the generic kernel's arithmetic.
     const bool blk32 = tc && gemv_blk32_i8_scratch_bytes(w->type, w->k, 2) > 0;
-    const int64_t group = gemv_umma_takes(w->type, w->k, 16)
-                              ? 16
-                              : ((tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16)));
+    const int64_t group = gemv_umma_takes(w->type, w->k, 16) ? 16 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16));
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
@@ -303,7 +301,7 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
     w->layout = layout;
     w->n = rows;
     w->k = k;
-    w->q_bytes = blocks * plane_q_bytes(type);
+    w->q_bytes = tiled_layout(type) ? tiled_rows(rows) * (k / qk) * plane_q_bytes(type) : blocks * plane_q_bytes(type);
     w->aux_bytes = blocks * plane_aux_bytes(type);
     w->q = nullptr;
     w->aux = nullptr;
@@ -314,7 +312,8 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
     const int64_t pad_q = (int64_t)PAD_ROWS * (k / qk) * plane_q_bytes(type), pad_aux = (int64_t)PAD_ROWS * (k / qk) * plane_aux_bytes(type);
     cudaError_t e = cudaMalloc(&w->q, (size_t)(w->q_bytes + pad_q + 16));
     if (e == cudaSuccess) {
-        e = cudaMemset(w->q + w->q_bytes, 0, (size_t)(pad_q + 16));
+        // a tiled weight is zeroed as a whole (the rows that pad its last tile), the others behind their last row
+        e = tiled_layout(type) ? cudaMemset(w->q, 0, (size_t)(w->q_bytes + pad_q + 16)) : cudaMemset(w->q + w->q_bytes, 0, (size_t)(pad_q + 16));
     }
     if (e == cudaSuccess && w->aux_bytes > 0) {
         e = cudaMalloc(&w->aux, (size_t)(w->aux_bytes + pad_aux));
@@ -326,7 +325,7 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
         rc = cuda_fail(e, "cudaMalloc(weight)");
     }
     if (rc == JQ_OK && src_bytes > 0) {
-        if (plane_aux_bytes(type) == 0) {
+        if (plane_aux_bytes(type) == 0 && !tiled_layout(type)) {
             e = cudaMemcpy(w->q, src, (size_t)src_bytes, cudaMemcpyHostToDevice);
             if (e != cudaSuccess) {
                 rc = cuda_fail(e, "cudaMemcpy(weight)");
@@ -339,7 +338,7 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
             if (e != cudaSuccess) {
                 rc = cuda_fail(e, "staging the verbatim blocks");
             } else {
-                rc = launch_repack(type, tmp, w->q, w->aux, blocks, nullptr);
+                rc = tiled_layout(type) ? launch_tile(type, tmp, w->q, rows, k / qk, false, nullptr) : launch_repack(type, tmp, w->q, w->aux, blocks, nullptr);
                 if (rc == JQ_OK) {
                     e = cudaDeviceSynchronize();
                     if (e != cudaSuccess) {
@@ -416,13 +415,14 @@ int jq_weight_download(const jq_weight* w, void* host_blocks, int64_t nbytes) {
         return JQ_OK;
     }
     DeviceGuard guard(w->device);
-    if (plane_aux_bytes(w->type) == 0) {
+    if (plane_aux_bytes(w->type) == 0 && !tiled_layout(w->type)) {
         JQ_CUDA(cudaMemcpy(host_blocks, w->q, (size_t)want, cudaMemcpyDeviceToHost));
         return JQ_OK;
     }
     uint8_t* tmp = nullptr;
     JQ_CUDA(cudaMalloc(&tmp, (size_t)want));
-    rc = launch_unpack(w->type, w->q, w->aux, tmp, blocks, nullptr);
+    rc = tiled_layout(w->type) ? launch_tile(w->type, tmp, w->q, w->n, w->k / block_values(w->type), true, nullptr)
+                               : launch_unpack(w->type, w->q, w->aux, tmp, blocks, nullptr);
     if (rc == JQ_OK) {
         cudaError_t e = cudaMemcpy(host_blocks, tmp, (size_t)want, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) {
@@ -661,9 +661,9 @@ int jq_device_status(int device, int* status) {
     if (rc == JQ_OK && *status == 0) {
         *status = peer;
     }
-    for (int part = 0; part < 3 && rc == JQ_OK; part++) {
+    for (int part = 0; part < 2 && rc == JQ_OK; part++) {
         int other = 0;
-        rc = part == 0 ? gemv_peer_status(&other) : (part == 1 ? decoder_peer_status(&other) : gemv_umma_status(&other));
+        rc = part == 0 ? decoder_peer_status(&other) : gemv_umma_status(&other);
         if (rc == JQ_OK && *status == 0) {
             *status = other;
         }

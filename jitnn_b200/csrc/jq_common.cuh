@@ -77,6 +77,18 @@ inline int plane_aux_bytes(int type) {
     }
 }
 
+// Q4_K and Q5_K weights are stored tile by tile: 128 consecutive rows form a tile, and within a tile the blocks of one
+// 256-element super-block of k lie together, row after row: [tile][super-block b][row in tile][block bytes]. One
+// (tile, super-block) unit is then a single contiguous run of 128 x block bytes, which the copy engine moves with one bulk copy.
+// The last tile is padded with zero rows. No byte of a block changes; jq_weight_download restores GGUF's order.
+constexpr int TILE_ROWS = 128;
+__host__ __device__ inline bool tiled_layout(int type) { return type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K; }
+__host__ __device__ inline int64_t tiled_rows(int64_t n) { return (n + TILE_ROWS - 1) / TILE_ROWS * TILE_ROWS; }
+// Byte offset of block b of `row` in a tiled weight with kb blocks of `bytes` bytes per row.
+__host__ __device__ inline int64_t tiled_offset(int64_t row, int64_t b, int64_t kb, int bytes) {
+    return ((row >> 7) * kb + b) * (int64_t)(TILE_ROWS * bytes) + (row & (TILE_ROWS - 1)) * bytes;
+}
+
 inline bool has_linear_kernel(int type) {
     return type == JQ_TYPE_Q8_0 || type == JQ_TYPE_Q4_0 || type == JQ_TYPE_Q4_1 || type == JQ_TYPE_Q4_K ||
            type == JQ_TYPE_Q5_K || type == JQ_TYPE_Q6_K;
@@ -84,7 +96,7 @@ inline bool has_linear_kernel(int type) {
 
 // What the kernels see of a weight.
 struct View {
-    const uint8_t* q;    // quant plane (or verbatim blocks), 256-byte aligned
+    const uint8_t* q;    // quant plane, tiled blocks (Q4_K, Q5_K) or verbatim blocks, 256-byte aligned
     const uint8_t* aux;  // scale plane, or nullptr
     int64_t n;           // output rows
     int64_t k;           // input features
@@ -94,12 +106,13 @@ struct View {
 // ---- kernel launchers (one translation unit each) ----------------------------------------------
 int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, cudaStream_t s);
 int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, cudaStream_t s);
+// Verbatim blocks [n, kb] <-> the tiled layout of Q4_K and Q5_K (`tiled` holds tiled_rows(n) rows).
+int launch_tile(int type, const uint8_t* verbatim, uint8_t* tiled, int64_t n, int64_t kb, bool inverse, cudaStream_t s);
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
 int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
 // gx [m, k] = g [m, n] . dequant(W) (jq_backward.cu).
 int launch_linear_backward(const View& v, const float* g, int64_t m, float* gx, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
-// Integer tensor-core GEMV for Q4_K, rows <= 8; *handled = false leaves the call to the generic kernel. Needs the 16 padding rows every uploaded weight has.
 // Where a GEMV's outputs go besides (or instead of) y when the linear is sharded by rows over several GPUs: every
 // rank's copy of the full output and flag words (jq_peer.cu). world = 0: no peers.
 struct PeerOut {
@@ -110,24 +123,16 @@ struct PeerOut {
     const PeerOut* table;   // host side only: where a copy of this struct lives in device memory
     int wait_first;         // the kernel's input is what this rank's latest exchange delivered: wait for all ranks' flags before reading it
 };
-int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
-                       const PeerOut* peer = nullptr);
-size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
-// The same GEMVs for one row of x whose activation image a kernel earlier in the stream has already written
-// (jq_q4k_image.cuh, jq_q6k_image.cuh); the Q4_K one can take a second weight with the same k in the same launch.
-size_t q4k_image_bytes_one_row(int64_t k);
-size_t q6k_image_bytes_one_row(int64_t k);
-int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
-                              const PeerOut* peer = nullptr);
 // Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
 // rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
 int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s);
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
                            int rank, int world, cudaStream_t s, bool wait_first, bool wait_after);
-// Status words of the waits that kernels of other translation units make themselves (peer_wait_inline): 0 or 32 + rank, cleared by the call.
-int gemv_peer_status(int* status);
+// Status word of the waits that the decoder's kernels make themselves (peer_wait_inline): 0 or 32 + rank, cleared by the call.
 int decoder_peer_status(int* status);
+// Q6_K for one row of x whose activation image (jq_q6k_image.cuh) a kernel earlier in the stream has written.
+size_t q6k_image_bytes_one_row(int64_t k);
 int launch_gemv_q6k_i8_imaged(const View& v, const uint8_t* image, const float* bias, float* y, cudaStream_t s, bool* handled);
 // The same for Q6_K, rows <= 4.
 int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled);
@@ -148,9 +153,10 @@ int scratch_zeroed_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** ou
 // Decode GEMV on tcgen05 (jq_gemv_umma.cu): Q4_K and Q5_K, 1 to 16 rows of x in one pass over the weights.
 bool gemv_umma_takes(int type, int64_t k, int rows);
 size_t gemv_umma_image_bytes(int64_t k, int rows);
+inline size_t gemv_umma_image_bytes_one_row(int64_t k) { return gemv_umma_image_bytes(k, 1); }
 int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s);
 int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
-                     const PeerOut* peer = nullptr);
+                     const PeerOut* peer = nullptr, bool no_scratch = false);
 int gemv_umma_status(int* status);
 // Option "gemv_tcgen05": zero keeps Q4_K and Q5_K decode on the mma.sync kernels (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_umma;

@@ -8,8 +8,9 @@
 // contracted into a fused multiply-add), in the reference's association order.
 //
 // Device layouts (what View::q and View::aux hold):
-//   Q4_K  verbatim 144-byte blocks: fp16 d, fp16 dmin, 12 scale bytes, 128 bytes of nibbles
-//   Q5_K  verbatim 176-byte blocks: fp16 d, fp16 dmin, 12 scale bytes, 32 bytes qh, 128 bytes qs
+//   Q4_K  144-byte blocks as in GGUF (fp16 d, fp16 dmin, 12 scale bytes, 128 bytes of nibbles), stored tile by tile
+//   Q5_K  176-byte blocks as in GGUF (fp16 d, fp16 dmin, 12 scale bytes, 32 bytes qh, 128 bytes qs), stored tile by tile
+//         (tiles of 128 rows, the blocks of one super-block of k together: tiled_offset in jq_common.cuh)
 //   Q6_K  q: 208 bytes per block (128 ql, 64 qh, 16 int8 scales); aux: fp16 d per block
 //   Q8_0  q: 32 int8 per block; aux: fp16 d per block
 //   Q4_0  q: 16 nibble bytes per block; aux: fp16 d per block
@@ -27,6 +28,13 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
 }
 
 __device__ __forceinline__ uint4 ld16(const uint8_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// Address of block number `block` (row-major numbering: row * blocks per row + b) of a tiled weight.
+__device__ __forceinline__ const uint8_t* tiled_block(const View& v, int64_t block, int bytes) {
+    const uint32_t kb = (uint32_t)(v.k >> 8);
+    const uint32_t row = (uint32_t)block / kb, b = (uint32_t)block - row * kb;  // fewer than 2^23 blocks: weights have fewer than 2^31 elements
+    return v.q + tiled_offset(row, b, kb, bytes);
+}
 
 __device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xffu; }
 
@@ -154,7 +162,7 @@ struct Fmt<JQ_TYPE_Q4_K> {
         uint4 h, q;
     };
     __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
-        const uint8_t* b = v.q + block * 144;
+        const uint8_t* b = tiled_block(v, block, 144);
         r.h = ld16(b);
         r.q = ld16(b + 16 + unit * 16);
     }
@@ -192,7 +200,7 @@ struct Fmt<JQ_TYPE_Q5_K> {
         uint4 h, hi, q;
     };
     __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
-        const uint8_t* b = v.q + block * 176;
+        const uint8_t* b = tiled_block(v, block, 176);
         r.h = ld16(b);
         r.hi = ld16(b + 16 + (unit & 1) * 16);
         r.q = ld16(b + 48 + unit * 16);

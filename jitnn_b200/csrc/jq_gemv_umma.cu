@@ -6,9 +6,9 @@
 //   * the activations are turned into an "image" of signed byte digits (jq_umma_image.cuh: 22-bit fixed point per
 //     super-block of k, three base-256 digits per value, one MMA column per (row of x, digit));
 //   * a persistent CTA per SM walks units of 128 weight rows x one 256-element super-block of k. Per unit
-//       - one thread asks the copy engine for the unit's 128 x 144 bytes of blocks (one cp.async.bulk.tensor.2d box of a
-//         tensor map over the weight as it lies in memory) and for the super-block's image (one cp.async.bulk), both
-//         into shared-memory rings that complete on mbarriers;
+//       - one thread asks the copy engine for the unit's weights (one cp.async.bulk of 128 x 144 contiguous bytes: the
+//         weight is stored tile by tile for exactly this, jq_common.cuh) and for the super-block's image (another
+//         cp.async.bulk), both into shared-memory rings that complete on mbarriers;
 //       - 128 "unpack" threads, one per weight row, widen the row's nibbles to bytes with one AND per four weights and
 //         store them into tensor memory as the A operand (tcgen05.st); the row's 6-bit scales and mins are decoded
 //         once into a small shared-memory ring;
@@ -27,7 +27,6 @@
 //
 // Every wait (mbarrier phases) is bounded: a wait that runs out records 64 + its role in a status word, raises the
 // CTA's abort flag, all roles fall through to the common exit and tensor memory is released. No CTA waits for another.
-#include <cstdlib>
 #include <mutex>
 
 #include "jq_formats.cuh"
@@ -50,7 +49,7 @@ constexpr int ROWS = 128;        // weight rows per unit (MMA M)
 constexpr int THREADS = 320;     // warp 0: copies, warp 1: MMA issue and tensor-memory owner, warps 2-5: unpack, warps 6-9: epilogue
 constexpr int SP = 4;            // stages of the row-parameter ring
 constexpr int P_BYTES = 2 * ROWS * 16;
-constexpr int SX = 3;            // stages of the image ring
+constexpr int MAX_SX = 8;        // stages of the image ring: enough of them in flight to cover the latency of a copy from L2
 constexpr int MAX_SW = 12;       // stages of the weight ring (as many as fit)
 constexpr size_t SMEM_MAX = 227 * 1024;
 
@@ -70,6 +69,8 @@ struct UFmt<JQ_TYPE_Q5_K> {
 };
 
 struct UArgs {
+    const uint8_t* q0;      // blocks of the first weight, row after row
+    const uint8_t* q1;      // of the second weight, if there is one
     const uint8_t* image;   // [KB][image block]
     const float* bias;
     float* y0;
@@ -79,9 +80,11 @@ struct UArgs {
     int tiles0, tiles;      // 128-row tiles of the first weight, of both
     int rows;               // rows of x
     int SW;                 // stages of the weight ring
+    int SX;                 // stages of the image ring
     float* partial;         // per CTA [max_pieces + 1][rows][128] floats
     int* counters;          // per tile: pieces finished (back to zero when the kernel ends)
     int max_pieces;
+    int whole_tiles;        // non-zero: every CTA's run is whole tiles (partial and counters are not used)
     uint32_t poll_limit;
     uint32_t lbo, sbo;      // byte offsets of the image's shared-memory descriptor
     const PeerOut* peer;
@@ -147,9 +150,57 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo,
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) | ((uint64_t)1 << 46);
 }
 
-// A wait made by every lane of a warp whose outcome is the same for all of them (the warp executes .sync.aligned instructions next).
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit) {
-    return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, abort_flag, &g_umma_status, code, limit) ? 1 : 0) != 0;
+// A poll of an mbarrier takes well over a hundred clocks to come back from the shared-memory unit even when the phase is
+// already complete, so a role polls everything a unit needs at once (the round trips overlap) and only then waits, bounded,
+// for what was not complete.
+struct Phase {
+    uint32_t bar, parity;
+};
+__device__ __forceinline__ bool wait_phases(const Phase& p0, const Phase& p1, const Phase& p2, bool use2, volatile int* abort_flag, int code, uint32_t limit) {
+    const bool r0 = tc::mbar_try(p0.bar, p0.parity);
+    const bool r1 = tc::mbar_try(p1.bar, p1.parity);
+    const bool r2 = use2 ? tc::mbar_try(p2.bar, p2.parity) : true;
+    if (r0 && r1 && r2) {
+        return true;
+    }
+    return (r0 || tc::mbar_wait(p0.bar, p0.parity, abort_flag, &g_umma_status, code, limit)) &&
+           (r1 || tc::mbar_wait(p1.bar, p1.parity, abort_flag, &g_umma_status, code, limit)) &&
+           (r2 || tc::mbar_wait(p2.bar, p2.parity, abort_flag, &g_umma_status, code, limit));
+}
+// The same on behalf of a whole warp: lane 0 polls (32 lanes polling one word would serialise), the outcome goes to the other
+// lanes, and __shfl_sync orders their later reads behind lane 0's acquire.
+__device__ __forceinline__ bool warp_wait_phases(const Phase& p0, const Phase& p1, const Phase& p2, bool use2, volatile int* abort_flag, int code,
+                                                 uint32_t limit, int lane) {
+    int ok = 1;
+    if (lane == 0) {
+        ok = wait_phases(p0, p1, p2, use2, abort_flag, code, limit) ? 1 : 0;
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit, int lane) {
+    int ok = 1;
+    if (lane == 0) {
+        ok = tc::mbar_wait(bar, parity, abort_flag, &g_umma_status, code, limit) ? 1 : 0;
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// A ring position: stage and the parity of the phase in which the stage gets filled.
+struct Ring {
+    int s = 0;
+    uint32_t ph = 0;
+    __device__ __forceinline__ void next(int stages) {
+        if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+        }
+    }
+};
+// One arrival per warp, after all of its lanes have got here (their shared-memory writes come before lane 0's release).
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) {
+        tc::mbar_arrive(bar);
+    }
 }
 
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -174,7 +225,7 @@ __global__ void __launch_bounds__(128) umma_activation_image_kernel(const float*
 // MR = rows of x the epilogue computes (1, 2, 5, 8, 10 or 16; a call with fewer rows leaves the others unused).
 template <int TYPE, int MR, bool PEER>
 __global__ void __launch_bounds__(THREADS, 1)
-    gemv_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const UArgs a) {
+    gemv_umma_kernel(const UArgs a) {
     constexpr int N = umma::columns_for_rows(MR);
     using IC = umma::ImageCfg<N>;
     using F = UFmt<TYPE>;
@@ -182,9 +233,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     constexpr int NGROUPS = 8 / SG;
     constexpr int D_COLS = SG * N;              // tensor-memory columns of an accumulator stage
     constexpr int A_COLS = 64;                  // of an A stage: 8 sub-blocks x 32 bytes
-    constexpr int D_BASE = 2 * A_COLS;
-    constexpr uint32_t TMEM_COLS = D_BASE + 2 * D_COLS <= 256 ? 256u : 512u;
-    static_assert(D_BASE + 2 * D_COLS <= 512, "tensor memory has 512 columns");
+    constexpr int NA = N == 48 ? 2 : 3;         // A stages
+    constexpr int ND = N == 8 ? 4 : 2;          // accumulator stages
+    constexpr int D_BASE = NA * A_COLS;
+    constexpr uint32_t TMEM_COLS = 512u;
+    static_assert(D_BASE + ND * D_COLS <= 512, "tensor memory has 512 columns");
     constexpr int WB = ROWS * F::BYTES;
     constexpr int XB = (IC::BYTES + 127) & ~127;
     constexpr uint32_t IDESC = idesc_of(N);
@@ -192,7 +245,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((128u - (tc::smem_u32(smem_unaligned) & 127u)) & 127u);
-    const int SW = a.SW;
+    const int SW = a.SW, SX = a.SX;
     uint8_t* w_ring = smem;
     uint8_t* x_ring = w_ring + (size_t)SW * WB;
     uint8_t* p_ring = x_ring + SX * XB;
@@ -201,15 +254,15 @@ __global__ void __launch_bounds__(THREADS, 1)
     auto full_w = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto empty_w = [&](int s) { return bar0 + 8u * (uint32_t)(MAX_SW + s); };
     auto full_x = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + s); };
-    auto empty_x = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + SX + s); };
-    auto full_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * SX + s); };
-    auto empty_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * SX + SP + s); };
-    constexpr int B2 = 2 * MAX_SW + 2 * SX + 2 * SP;
+    auto empty_x = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + MAX_SX + s); };
+    auto full_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * MAX_SX + s); };
+    auto empty_p = [&](int s) { return bar0 + 8u * (uint32_t)(2 * MAX_SW + 2 * MAX_SX + SP + s); };
+    constexpr int B2 = 2 * MAX_SW + 2 * MAX_SX + 2 * SP;
     auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + s); };
-    auto empty_a = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 2 + s); };
-    auto full_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 4 + s); };
-    auto empty_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 6 + s); };
-    constexpr int NBARS = B2 + 8;
+    auto empty_a = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 4 + s); };
+    auto full_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 8 + s); };
+    auto empty_d = [&](int s) { return bar0 + 8u * (uint32_t)(B2 + 12 + s); };
+    constexpr int NBARS = B2 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* fin = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [0] this CTA adds the tile up, [1], [2] first and last CTA of the tile
@@ -219,28 +272,29 @@ __global__ void __launch_bounds__(THREADS, 1)
     const int KB = a.KB;
     const int64_t U = (int64_t)a.tiles * KB;
     const int64_t G = gridDim.x;
-    const int64_t u0 = (int64_t)blockIdx.x * U / G;
-    const int units = (int)(((int64_t)blockIdx.x + 1) * U / G - u0);
+    // This CTA's run of units: an even share of all units, or (no scratch for pieces of tiles) an even share of the tiles.
+    const int64_t u0 = a.whole_tiles ? (int64_t)blockIdx.x * a.tiles / G * KB : (int64_t)blockIdx.x * U / G;
+    const int units = (int)((a.whole_tiles ? ((int64_t)blockIdx.x + 1) * a.tiles / G * KB : ((int64_t)blockIdx.x + 1) * U / G) - u0);
     const uint32_t limit = a.poll_limit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MAX_SW; s++) {
             tc::mbar_init(full_w(s), 1);
-            tc::mbar_init(empty_w(s), ROWS);
+            tc::mbar_init(empty_w(s), 4);  // one arrival per unpack warp
         }
-        for (int s = 0; s < SX; s++) {
+        for (int s = 0; s < MAX_SX; s++) {
             tc::mbar_init(full_x(s), 1);
             tc::mbar_init(empty_x(s), 1 + 4);  // the MMAs that read the digits, and one lane of each epilogue warp
         }
         for (int s = 0; s < SP; s++) {
-            tc::mbar_init(full_p(s), ROWS);
-            tc::mbar_init(empty_p(s), ROWS);
+            tc::mbar_init(full_p(s), 4);
+            tc::mbar_init(empty_p(s), 4);
         }
-        for (int s = 0; s < 2; s++) {
-            tc::mbar_init(full_a(s), ROWS);
+        for (int s = 0; s < 4; s++) {
+            tc::mbar_init(full_a(s), 4);
             tc::mbar_init(empty_a(s), 1);
             tc::mbar_init(full_d(s), 1);
-            tc::mbar_init(empty_d(s), ROWS);
+            tc::mbar_init(empty_d(s), 4);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -255,108 +309,122 @@ __global__ void __launch_bounds__(THREADS, 1)
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        // ---- copies: weights as soon as a slot is free (they depend on nothing), images once the kernel before has finished ----
-        int iw = 0, ix = 0;
-        bool dep_done = false;
-        uint32_t idle = 0;
-        const int prologue = units < SW ? units : SW;
-        while (iw < units || ix < units) {
-            bool progress = false;
-            if (lane == 0 && iw < units) {
-                const int s = iw % SW;
-                if (tc::mbar_try(empty_w(s), (((uint32_t)(iw / SW)) & 1u) ^ 1u)) {
-                    const int64_t u = u0 + iw;
-                    const int t = (int)(u / KB), b = (int)(u % KB);
-                    tc::mbar_expect_tx(full_w(s), WB);
-                    const bool first = t < a.tiles0;
-                    tc::tma_load_2d(tc::smem_u32(w_ring + (size_t)s * WB), first ? &map0 : &map1, full_w(s), b * F::BYTES, (first ? t : t - a.tiles0) * ROWS);
-                    iw++;
-                    progress = true;
-                }
+        // ---- copies: one thread asks the copy engine for a unit's weights (one contiguous run of the tiled layout) and for
+        // its super-block's image. Weights depend on nothing and are requested at once, as many as the ring holds; the image
+        // is complete only when the kernel before this one has finished.
+        auto issue_w = [&](int i, int s) {
+            const int64_t u = u0 + i;
+            const int t = (int)(u / KB), b = (int)(u % KB);
+            const bool first = t < a.tiles0;
+            const uint8_t* src = (first ? a.q0 : a.q1) + ((int64_t)(first ? t : t - a.tiles0) * KB + b) * WB;
+            tc::mbar_expect_tx(full_w(s), WB);
+            tc::bulk_load(tc::smem_u32(w_ring + (size_t)s * WB), src, WB, full_w(s));
+        };
+        auto issue_x = [&](int i, int s) {
+            const int b = (int)((u0 + i) % KB);
+            tc::mbar_expect_tx(full_x(s), IC::BYTES);
+            tc::bulk_load(tc::smem_u32(x_ring + s * XB), a.image + (size_t)b * IC::BYTES, IC::BYTES, full_x(s));
+        };
+        int iw = units < SW ? units : SW;
+        if (lane == 0) {
+            for (int i = 0; i < iw; i++) {
+                issue_w(i, i);  // the ring starts out empty
             }
-            iw = __shfl_sync(0xffffffffu, iw, 0);
-            if (!dep_done && iw >= prologue) {
-                asm volatile("griddepcontrol.wait;" ::: "memory");  // the image is complete
-                if constexpr (PEER) {
-                    if (a.peer->wait_first) {
-                        // the image is what the ranks' latest exchange delivered: complete once all their flags are up
-                        peer_wait_inline(a.peer->flags[a.peer->rank], a.peer->world, lane, &g_umma_peer_status);
-                    }
-                }
-                dep_done = true;
+        }
+        __syncwarp();
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if constexpr (PEER) {
+            if (a.peer->wait_first) {
+                // the image is what the ranks' latest exchange delivered: complete once all their flags are up
+                peer_wait_inline(a.peer->flags[a.peer->rank], a.peer->world, lane, &g_umma_peer_status);
             }
-            if (lane == 0 && dep_done && ix < units) {
-                const int s = ix % SX;
-                if (tc::mbar_try(empty_x(s), (((uint32_t)(ix / SX)) & 1u) ^ 1u)) {
-                    const int b = (int)((u0 + ix) % KB);
-                    tc::mbar_expect_tx(full_x(s), IC::BYTES);
-                    tc::bulk_load(tc::smem_u32(x_ring + s * XB), a.image + (size_t)b * IC::BYTES, IC::BYTES, full_x(s));
-                    ix++;
-                    progress = true;
-                }
+        }
+        if (lane == 0) {
+            int ix = units < SX ? units : SX;
+            for (int i = 0; i < ix; i++) {
+                issue_x(i, i);
             }
-            ix = __shfl_sync(0xffffffffu, ix, 0);
-            int stop = 0;
-            if (lane == 0) {
-                if (progress) {
+            Ring wr, xr;  // the next slot to fill, and the parity of the phase in which it was last filled ...
+            wr.s = iw == SW ? 0 : iw;
+            xr.s = ix == SX ? 0 : ix;  // ... which is phase 0 for both after the first round (if there is a second one at all)
+            uint32_t idle = 0;
+            while (iw < units || ix < units) {
+                // both rings polled together and without suspending: a slot of either may come free first
+                const bool wfree = iw < units && tc::mbar_test(empty_w(wr.s), wr.ph);
+                const bool xfree = ix < units && tc::mbar_test(empty_x(xr.s), xr.ph);
+                if (wfree) {
+                    issue_w(iw++, wr.s);
+                    wr.next(SW);
+                }
+                if (xfree) {
+                    issue_x(ix++, xr.s);
+                    xr.next(SX);
+                }
+                if (wfree || xfree) {
                     idle = 0;
                 } else if (++idle >= limit) {
                     atomicCAS(&g_umma_status, 0, 64 + 1);
                     *abort_flag = 1;
-                    stop = 1;
+                    break;
                 } else if ((idle & 63u) == 0 && *abort_flag != 0) {
-                    stop = 1;
+                    break;
                 }
-            }
-            if (__shfl_sync(0xffffffffu, stop, 0) != 0) {
-                break;
             }
         }
     } else if (warp == 1) {
         // ---- MMA issue -------------------------------------------------------------------------------------------------
         if (lane == 0) {
-            uint32_t dcount = 0;
             bool ok = true;
+            Ring xr, ar, dr;
+            // descriptor of sub-block 0 of image stage 0; stages and sub-blocks only move the 14-bit address field (16-byte units)
+            const uint64_t desc0 = smem_desc_plain(tc::smem_u32(x_ring), a.lbo, a.sbo);
             for (int i = 0; i < units && ok; i++) {
-                const int as = i & 1, xs = i % SX;
-                ok = tc::mbar_wait(full_x(xs), ((uint32_t)(i / SX)) & 1u, abort_flag, &g_umma_status, 64 + 2, limit) &&
-                     tc::mbar_wait(full_a(as), ((uint32_t)(i >> 1)) & 1u, abort_flag, &g_umma_status, 64 + 2, limit);
+                ok = wait_phases(Phase{full_x(xr.s), xr.ph}, Phase{full_a(ar.s), ar.ph}, Phase{empty_d(dr.s), dr.ph ^ 1u}, true, abort_flag, 64 + 2, limit);
                 if (!ok) {
                     break;
                 }
-                const uint32_t xaddr = tc::smem_u32(x_ring + xs * XB);
+                tc::fence_after_sync();
+                const uint64_t xdesc = desc0 + (uint64_t)((uint32_t)(xr.s * XB) >> 4);
+                const uint32_t abase = tmem + (uint32_t)(ar.s * A_COLS);
 #pragma unroll
                 for (int g = 0; g < NGROUPS; g++) {
-                    const uint32_t ds = dcount & 1u;
-                    ok = tc::mbar_wait(empty_d(ds), ((dcount >> 1) & 1u) ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
-                    if (!ok) {
-                        break;
+                    if (g > 0) {
+                        ok = tc::mbar_wait(empty_d(dr.s), dr.ph ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
+                        if (!ok) {
+                            break;
+                        }
+                        tc::fence_after_sync();
                     }
-                    tc::fence_after_sync();
+                    const uint32_t dbase = tmem + (uint32_t)D_BASE + (uint32_t)(dr.s * D_COLS);
 #pragma unroll
                     for (int sg = 0; sg < SG; sg++) {
                         const int s = g * SG + sg;
-                        umma_i8_ts(tmem + (uint32_t)(D_BASE + ds * D_COLS + sg * N), tmem + (uint32_t)(as * A_COLS + s * 8),
-                                   smem_desc_plain(xaddr + (uint32_t)(s * IC::SUB_BYTES), a.lbo, a.sbo), IDESC);
+                        umma_i8_ts(dbase + (uint32_t)(sg * N), abase + (uint32_t)(s * 8), xdesc + (uint64_t)((s * IC::SUB_BYTES) >> 4), IDESC);
                     }
-                    tc::umma_commit(full_d(ds));
-                    dcount++;
+                    tc::umma_commit(full_d(dr.s));
+                    dr.next(ND);
                 }
                 if (ok) {
-                    tc::umma_commit(empty_a(as));
-                    tc::umma_commit(empty_x(xs));
+                    tc::umma_commit(empty_a(ar.s));
+                    tc::umma_commit(empty_x(xr.s));
                 }
+                xr.next(SX);
+                ar.next(NA);
             }
         }
     } else if (warp < 6) {
         // ---- unpack: thread = weight row; a warp may only touch the tensor-memory lanes 32 (warp % 4) .. + 31 --------------------
         const int r = (warp & 3) * 32 + lane;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        Ring wr, ar, pr;
         for (int i = 0; i < units; i++) {
-            const int ws = i % SW, ps = i % SP, as = i & 1;
-            if (!warp_wait(full_w(ws), ((uint32_t)(i / SW)) & 1u, abort_flag, 64 + 3, limit)) {
+            const int ws = wr.s, as = ar.s, ps = pr.s;
+            // the weights have landed, the MMAs that read the A stage before have finished, the epilogue has read the parameter slot
+            if (!warp_wait_phases(Phase{full_w(ws), wr.ph}, Phase{empty_a(as), ar.ph ^ 1u}, Phase{empty_p(ps), pr.ph ^ 1u}, true, abort_flag, 64 + 3, limit,
+                                  lane)) {
                 break;
             }
+            tc::fence_after_sync();
             const uint8_t* wrow = w_ring + (size_t)ws * WB + r * F::BYTES;
             const uint4 h = *reinterpret_cast<const uint4*>(wrow);  // fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins
             const uint32_t sca = h.y & 0x3f3f3f3fu, scb = and_or(h.y >> 2, 0x30303030u, h.w & 0x0f0f0f0fu);            // scales 0..3, 4..7
@@ -364,20 +432,13 @@ __global__ void __launch_bounds__(THREADS, 1)
             uint32_t sc16[4];  // the scales of sub-blocks 2j and 2j + 1 as 16-bit halves
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                const uint32_t pr = __byte_perm(j < 2 ? sca : scb, 0u, 0x4140u + (uint32_t)(2 * (j & 1)) * 0x0101u);  // bytes (e, 0, o, 0)
-                sc16[j] = F::IN_PLACE ? pr + (pr & 0xffffu) * 15u : pr;
-            }
-            if (!warp_wait(empty_p(ps), (((uint32_t)(i / SP)) & 1u) ^ 1u, abort_flag, 64 + 3, limit)) {
-                break;
+                const uint32_t pair = __byte_perm(j < 2 ? sca : scb, 0u, 0x4140u + (uint32_t)(2 * (j & 1)) * 0x0101u);  // bytes (e, 0, o, 0)
+                sc16[j] = F::IN_PLACE ? pair + (pair & 0xffffu) * 15u : pair;
             }
             uint4* prow = reinterpret_cast<uint4*>(p_ring + ps * P_BYTES) + r;
             prow[0] = make_uint4(sc16[0], sc16[1], sc16[2], sc16[3]);
             prow[ROWS] = make_uint4(mna, mnb, h.x, 0u);
-            tc::mbar_arrive(full_p(ps));
-            if (!warp_wait(empty_a(as), (((uint32_t)(i >> 1)) & 1u) ^ 1u, abort_flag, 64 + 3, limit)) {
-                break;
-            }
-            tc::fence_after_sync();
+            warp_arrive(full_p(ps), lane);
             uint4 qh0 = make_uint4(0u, 0u, 0u, 0u), qh1 = qh0;
             if constexpr (TYPE == JQ_TYPE_Q5_K) {
                 qh0 = *reinterpret_cast<const uint4*>(wrow + 16);
@@ -406,9 +467,15 @@ __global__ void __launch_bounds__(THREADS, 1)
                 tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 16 * j), av);
             }
             tmem_st_wait();
-            tc::mbar_arrive(empty_w(ws));  // this row's bytes of the slot are in registers or tensor memory
             tc::fence_before_sync();
-            tc::mbar_arrive(full_a(as));
+            __syncwarp();
+            if (lane == 0) {
+                tc::mbar_arrive(empty_w(ws));  // the warp's rows of the slot are in registers or tensor memory
+                tc::mbar_arrive(full_a(as));
+            }
+            wr.next(SW);
+            ar.next(NA);
+            pr.next(SP);
         }
     } else {
         // ---- epilogue: thread = weight row -----------------------------------------------------------------------------------------
@@ -424,18 +491,19 @@ __global__ void __launch_bounds__(THREADS, 1)
         int t = (int)(u0 / KB), b = (int)(u0 % KB);
         bool piecewise = b > 0;  // the run starts inside a tile: its contributions go to the scratch one by one
         int piece_b0 = b;
-        uint32_t dcount = 0;
+        Ring xr, pr, dr;
         const size_t slot_floats = (size_t)(a.max_pieces + 1) * a.rows * ROWS;
         float* const my_slot = a.partial + (size_t)blockIdx.x * slot_floats;
         bool ok = true;
         for (int i = 0; i < units && ok; i++) {
-            const int ps = i % SP, xs = i % SX;
-            if (!warp_wait(full_p(ps), ((uint32_t)(i / SP)) & 1u, abort_flag, 64 + 4, limit)) {
+            const int ps = pr.s, xs = xr.s;
+            if (!warp_wait_phases(Phase{full_p(ps), pr.ph}, Phase{full_d(dr.s), dr.ph}, Phase{full_x(xs), xr.ph}, true, abort_flag, 64 + 4, limit, lane)) {
                 break;
             }
+            tc::fence_after_sync();
             const uint4* prow = reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r;
             const uint4 pa = prow[0], pb = prow[ROWS];
-            tc::mbar_arrive(empty_p(ps));
+            warp_arrive(empty_p(ps), lane);
             const uint32_t sc16[4] = {pa.x, pa.y, pa.z, pa.w};
             int I[MR][3];
 #pragma unroll
@@ -444,12 +512,14 @@ __global__ void __launch_bounds__(THREADS, 1)
             }
 #pragma unroll
             for (int g = 0; g < NGROUPS; g++) {
-                const uint32_t ds = dcount & 1u;
-                ok = warp_wait(full_d(ds), (dcount >> 1) & 1u, abort_flag, 64 + 4, limit);
-                if (!ok) {
-                    break;
+                const uint32_t ds = (uint32_t)dr.s;
+                if (g > 0) {
+                    ok = warp_wait(full_d(ds), dr.ph, abort_flag, 64 + 4, limit, lane);
+                    if (!ok) {
+                        break;
+                    }
+                    tc::fence_after_sync();
                 }
-                tc::fence_after_sync();
                 const uint32_t dbase = tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS);
                 if constexpr (N == 48) {
 #pragma unroll
@@ -494,11 +564,10 @@ __global__ void __launch_bounds__(THREADS, 1)
                     }
                 }
                 tc::fence_before_sync();
-                tc::mbar_arrive(empty_d(ds));
-                dcount++;
+                warp_arrive(empty_d(ds), lane);
+                dr.next(ND);
             }
-            if (!ok || !warp_wait(full_x(xs), ((uint32_t)(i / SX)) & 1u, abort_flag, 64 + 4, limit)) {
-                ok = false;
+            if (!ok) {
                 break;
             }
             // ---- this super-block's contribution: d (sum over digits of weight x integer) - dmin (sum over sub-blocks of min x sum of x) ----
@@ -630,6 +699,8 @@ __global__ void __launch_bounds__(THREADS, 1)
                 piecewise = false;
                 piece_b0 = 0;
             }
+            xr.next(SX);
+            pr.next(SP);
             if (++b == KB) {
                 b = 0;
                 t++;
@@ -670,26 +741,8 @@ int sm_count_of_current_device() {
     return v;
 }
 
-int weight_map(const View& v, int block_bytes, CUtensorMap* map) {
-    EncodeTiledFn enc = encode_tiled();
-    if (enc == nullptr) {
-        return fail(JQ_ERR_CUDA, "decode GEMV: cuTensorMapEncodeTiled is not available from this driver");
-    }
-    // the weight as a matrix of bytes [n rows][k / 256 x block bytes]; a box is one block of 128 consecutive rows
-    const cuuint64_t dims[2] = {(cuuint64_t)(v.k / 256) * (cuuint64_t)block_bytes, (cuuint64_t)v.n};
-    const cuuint64_t strides[1] = {dims[0]};
-    const cuuint32_t box[2] = {(cuuint32_t)block_bytes, (cuuint32_t)ROWS};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(v.q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        return fail(JQ_ERR_CUDA, "decode GEMV: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    }
-    return JQ_OK;
-}
-
 template <int TYPE, int MR, bool PEER>
-int launch_typed(const CUtensorMap& m0, const CUtensorMap& m1, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+int launch_typed(const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
@@ -707,20 +760,20 @@ int launch_typed(const CUtensorMap& m0, const CUtensorMap& m1, const UArgs& a, i
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_umma_kernel<TYPE, MR, PEER>, m0, m1, a));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_umma_kernel<TYPE, MR, PEER>, a));
     count_launch();
     return JQ_OK;
 }
 
 template <int TYPE, bool PEER>
-int by_rows(int mr, const CUtensorMap& m0, const CUtensorMap& m1, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+int by_rows(int mr, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     switch (mr) {
-        case 1: return launch_typed<TYPE, 1, PEER>(m0, m1, a, grid, smem, s);
-        case 2: return launch_typed<TYPE, 2, PEER>(m0, m1, a, grid, smem, s);
-        case 5: return launch_typed<TYPE, 5, PEER>(m0, m1, a, grid, smem, s);
-        case 8: return launch_typed<TYPE, 8, PEER>(m0, m1, a, grid, smem, s);
-        case 10: return launch_typed<TYPE, 10, PEER>(m0, m1, a, grid, smem, s);
-        default: return launch_typed<TYPE, 16, PEER>(m0, m1, a, grid, smem, s);
+        case 1: return launch_typed<TYPE, 1, PEER>(a, grid, smem, s);
+        case 2: return launch_typed<TYPE, 2, PEER>(a, grid, smem, s);
+        case 5: return launch_typed<TYPE, 5, PEER>(a, grid, smem, s);
+        case 8: return launch_typed<TYPE, 8, PEER>(a, grid, smem, s);
+        case 10: return launch_typed<TYPE, 10, PEER>(a, grid, smem, s);
+        default: return launch_typed<TYPE, 16, PEER>(a, grid, smem, s);
     }
 }
 
@@ -751,9 +804,12 @@ size_t gemv_umma_image_bytes(int64_t k, int rows) {
     return (size_t)(k / 256) * umma::image_block_bytes(umma::columns_for_rows(rows_bucket(rows)));
 }
 
+static bool shape_ok(int type, int64_t k, int rows) {
+    return (type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K) && rows >= 1 && rows <= 16 && k > 0 && k % 256 == 0;
+}
+
 bool gemv_umma_takes(int type, int64_t k, int rows) {
-    return (type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K) && rows >= 1 && rows <= 16 && k > 0 && k % 256 == 0 &&
-           g_opt_gemv_umma.load(std::memory_order_relaxed) != 0 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0;
+    return shape_ok(type, k, rows) && g_opt_gemv_umma.load(std::memory_order_relaxed) != 0 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0;
 }
 
 // Writes the activation image of x [rows, k] for gemv_umma (rows in [1, 16]) into `image` (gemv_umma_image_bytes bytes).
@@ -769,23 +825,19 @@ int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, 
 // y [rows, n] = x . W^T (+ bias) for a Q4_K or Q5_K weight and 1 to 16 rows of x whose image is in `image` (written earlier
 // in the stream). With v2 != nullptr the rows of a second weight of the same type and k follow in the same launch
 // (results in y2, no bias). `peer`: the outputs go into every rank's y of a row-sharded linear instead.
+// no_scratch: deal whole tiles to the CTAs, which needs no scratch buffers (and balances the load worse).
 int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
-                     const PeerOut* peer) {
-    if (!gemv_umma_takes(v.type, v.k, rows) || v.n <= 0 || (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
+                     const PeerOut* peer, bool no_scratch) {
+    if (!shape_ok(v.type, v.k, rows) || v.n <= 0 || (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
         return fail(JQ_ERR_UNSUPPORTED, "decode GEMV: type %d, k = %lld, %d rows is outside what the tcgen05 kernel takes", v.type, (long long)v.k, rows);
     }
     const int bb = v.type == JQ_TYPE_Q4_K ? 144 : 176;
     const int mr = rows_bucket(rows);
     const int ncols = umma::columns_for_rows(mr);
-    CUtensorMap m0, m1;
-    int rc = weight_map(v, bb, &m0);
-    if (rc == JQ_OK) {
-        rc = v2 != nullptr ? weight_map(*v2, bb, &m1) : weight_map(v, bb, &m1);
-    }
-    if (rc != JQ_OK) {
-        return rc;
-    }
+    int rc = JQ_OK;
     UArgs a = {};
+    a.q0 = v.q;
+    a.q1 = v2 != nullptr ? v2->q : v.q;
     a.image = image;
     a.bias = bias;
     a.y0 = y;
@@ -796,42 +848,42 @@ int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int ro
     a.tiles0 = (int)((v.n + ROWS - 1) / ROWS);
     a.tiles = a.tiles0 + (v2 != nullptr ? (int)((v2->n + ROWS - 1) / ROWS) : 0);
     a.rows = rows;
-    const int64_t U = (int64_t)a.tiles * a.KB;
+    const int64_t U = no_scratch ? a.tiles : (int64_t)a.tiles * a.KB;
     const int sms = sm_count_of_current_device();
     const int grid = (int)(U < sms ? U : sms);
+    a.whole_tiles = no_scratch ? 1 : 0;
     const int64_t per_cta = (U + grid - 1) / grid;
     a.max_pieces = (int)(per_cta < a.KB - 1 ? per_cta : a.KB - 1);
     if (a.max_pieces < 1) {
         a.max_pieces = 1;
     }
     const size_t xb = (umma::image_block_bytes(ncols) + 127) & ~(size_t)127;
-    const size_t fixed = 128 + SX * xb + SP * P_BYTES + 1024;
+    a.SX = ncols <= 16 ? 8 : (ncols == 32 ? 6 : 5);
+    const size_t fixed = 128 + a.SX * xb + SP * P_BYTES + 1024;
     int sw = (int)((SMEM_MAX - fixed) / ((size_t)ROWS * bb));
     a.SW = sw > MAX_SW ? MAX_SW : sw;
     const size_t smem = fixed + (size_t)a.SW * ROWS * bb;
     a.poll_limit = (uint32_t)g_opt_wait_poll_limit.load(std::memory_order_relaxed);
     a.lbo = (uint32_t)(ncols / 8) * 128u;
     a.sbo = 128u;
-    if (getenv("JQ_UMMA_DESC_SWAP") != nullptr) {
-        a.lbo = 128u;
-        a.sbo = (uint32_t)(ncols / 8) * 128u;
-    }
     a.peer = peer != nullptr ? peer->table : nullptr;
     uint8_t* partial = nullptr;
     uint8_t* counters = nullptr;
-    rc = scratch_for_slot(s, 2, (size_t)grid * (a.max_pieces + 1) * rows * ROWS * sizeof(float), &partial);
-    if (rc == JQ_OK) {
-        rc = scratch_zeroed_for_slot(s, 3, (size_t)a.tiles * sizeof(int), &counters);
-    }
-    if (rc != JQ_OK) {
-        return rc;
+    if (!no_scratch) {
+        rc = scratch_for_slot(s, 2, (size_t)grid * (a.max_pieces + 1) * rows * ROWS * sizeof(float), &partial);
+        if (rc == JQ_OK) {
+            rc = scratch_zeroed_for_slot(s, 3, (size_t)a.tiles * sizeof(int), &counters);
+        }
+        if (rc != JQ_OK) {
+            return rc;
+        }
     }
     a.partial = reinterpret_cast<float*>(partial);
     a.counters = reinterpret_cast<int*>(counters);
     if (v.type == JQ_TYPE_Q4_K) {
-        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, m0, m1, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, m0, m1, a, grid, smem, s);
+        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, a, grid, smem, s);
     }
-    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, m0, m1, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, m0, m1, a, grid, smem, s);
+    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, a, grid, smem, s);
 }
 
 // Reads and clears the status words of the tcgen05 GEMV on the current device (0 = no wait ever gave up).
@@ -849,3 +901,85 @@ int gemv_umma_status(int* status) {
 }
 
 }  // namespace jq
+
+// ---- an entry point that allocates nothing -------------------------------------------------------------------------
+// jq_linear_f32 keeps the activation image and the sums of split tiles in scratch buffers that the library allocates
+// with cudaMalloc the first time a stream needs them. Some callers cannot have that: a serving process that has handed
+// every byte of device memory to its own pools fails the allocation, and cudaMalloc also makes the whole device wait,
+// which a latency-bound decode loop on another stream would feel. For them the image lives in the array below, which is
+// part of the loaded library image (every GPU that loads the library holds these bytes until the process exits, whether
+// or not the entry point is ever called), and the CTAs are dealt whole tiles, so nothing else needs scratch.
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)1 << 20;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+uint8_t* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of g_noalloc_scratch, per device
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use: the device
+// address has to be asked for, once per device and with that device current.
+int noalloc_scratch_address(int device, uint8_t** out) {
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: device %d is beyond the %d this entry point keeps addresses for", device,
+                        NOALLOC_MAX_DEVICES);
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_addr[device] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            return jq::cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        }
+        g_noalloc_addr[device] = static_cast<uint8_t*>(p);
+    }
+    *out = g_noalloc_addr[device];
+    return JQ_OK;
+}
+
+}  // namespace
+
+extern "C" JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, void* stream) {
+    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: not a live weight handle");
+    }
+    if (w->type != JQ_TYPE_Q4_K) {
+        return jq::fail(JQ_ERR_UNSUPPORTED, "jq_linear_q4k_f32_noalloc: the weight is not Q4_K (type id %d)", w->type);
+    }
+    if (m < 1 || m > 16) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: %lld activation rows, this entry point takes 1 to 16", (long long)m);
+    }
+    if (x == nullptr || y == nullptr || (((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: x and y must be non-null, 16-byte aligned device pointers");
+    }
+    if (w->n == 0) {
+        return JQ_OK;
+    }
+    const size_t need = jq::gemv_umma_image_bytes(w->k, (int)m);
+    if (need == 0 || need > NOALLOC_SCRATCH_BYTES) {
+        return jq::fail(JQ_ERR_INVALID,
+                        "jq_linear_q4k_f32_noalloc: k = %lld with %lld rows needs %zu bytes of activation image, the built-in scratch holds %zu", (long long)w->k,
+                        (long long)m, need, NOALLOC_SCRATCH_BYTES);
+    }
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) {
+        prev = -1;
+    }
+    if (prev != w->device && cudaSetDevice(w->device) != cudaSuccess) {
+        return jq::fail(JQ_ERR_CUDA, "jq_linear_q4k_f32_noalloc: cannot select device %d", w->device);
+    }
+    uint8_t* image = nullptr;
+    int rc = noalloc_scratch_address(w->device, &image);
+    if (rc == JQ_OK) {
+        const jq::View v{w->q, w->aux, w->n, w->k, w->type};
+        rc = jq::launch_gemv_umma_image(x, (int)m, w->k, image, (cudaStream_t)stream);
+        if (rc == JQ_OK) {
+            rc = jq::launch_gemv_umma(v, nullptr, image, (int)m, bias, y, nullptr, (cudaStream_t)stream, nullptr, true);
+        }
+    }
+    if (prev >= 0 && prev != w->device) {
+        cudaSetDevice(prev);
+    }
+    return rc;
+}

@@ -1,4 +1,4 @@
-// Load-time repacking between GGUF's verbatim blocks and the device layout (planes).
+// Load-time repacking between GGUF's verbatim blocks and the device layouts (planes, tiles).
 //
 // Q8_0 (34 B), Q4_0 (18 B), Q4_1 (20 B) and Q6_K (210 B) blocks are only 2-byte aligned, which rules
 // out 128-bit loads. At upload their blocks are split into a plane of quants whose per-block size is a
@@ -74,6 +74,37 @@ int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verba
     repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sp, (const uint16_t*)verbatim, (uint16_t*)q, (uint16_t*)aux, blocks, true);
     count_launch();
     return check_launch("repack_kernel");
+}
+
+// One thread per 16-byte piece of a block: GGUF's order (row after row) <-> the tiled order.
+__global__ void tile_kernel(const uint4* __restrict__ verbatim, uint4* __restrict__ tiled, int64_t n, int64_t kb, int pieces, bool inverse) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * kb * pieces) {
+        return;
+    }
+    const int64_t block = i / pieces, row = block / kb, b = block % kb;
+    const int piece = (int)(i % pieces);
+    uint4* t = tiled + tiled_offset(row, b, kb, pieces * 16) / 16 + piece;
+    uint4* v = const_cast<uint4*>(verbatim) + i;
+    if (inverse) {
+        *v = *t;
+    } else {
+        *t = *v;
+    }
+}
+
+int launch_tile(int type, const uint8_t* verbatim, uint8_t* tiled, int64_t n, int64_t kb, bool inverse, cudaStream_t s) {
+    if (!tiled_layout(type)) {
+        return fail(JQ_ERR_INVALID, "tile: type %d has no tiled layout", type);
+    }
+    const int pieces = block_bytes(type) / 16;
+    const int64_t total = n * kb * pieces;
+    if (total == 0) {
+        return JQ_OK;
+    }
+    tile_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>((const uint4*)verbatim, (uint4*)tiled, n, kb, pieces, inverse);
+    count_launch();
+    return check_launch("tile_kernel");
 }
 
 }  // namespace jq
