@@ -208,8 +208,9 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "decoder_fused"     zero: the decoder's single-token step uses the general kernels (one per operator) instead of the
  *                       fused ones that hand activations to the next linear as its activation image.
  *   "gemv_tcgen05"      zero: Q4_K and Q5_K decode GEMVs run on the generic kernel instead of the tcgen05 one (for comparisons).
- *   "wait_poll_limit"   polls after which a bounded device-side wait of the tcgen05 GEMV gives up (default 2^22; a wait that
- *                       gives up makes jq_device_status report 64 + the waiting role and the outputs of that call undefined).
+ *   "wait_limit_us"     microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up (default 2 000 000; a
+ *                       wait that gives up makes jq_device_status report 64 + the waiting role, and the outputs of that call
+ *                       are undefined).
  */
 JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);

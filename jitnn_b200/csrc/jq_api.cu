@@ -730,11 +730,11 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_gemv_umma.store(value != 0);
         return JQ_OK;
     }
-    if (name != nullptr && strcmp(name, "wait_poll_limit") == 0) {
-        if (value < 1 || value > ((int64_t)1 << 30)) {
-            return fail(JQ_ERR_INVALID, "option wait_poll_limit: %lld is outside [1, 2^30]", (long long)value);
+    if (name != nullptr && strcmp(name, "wait_limit_us") == 0) {
+        if (value < 1 || value > 60000000) {
+            return fail(JQ_ERR_INVALID, "option wait_limit_us: %lld is outside [1, 60000000]", (long long)value);
         }
-        g_opt_wait_poll_limit.store(value);
+        g_opt_wait_limit_us.store(value);
         return JQ_OK;
     }
     if (name != nullptr && strcmp(name, "decoder_graph") == 0) {
@@ -761,8 +761,8 @@ int jq_get_option(const char* name, int64_t* value) {
         *value = g_opt_gemv_umma.load();
         return JQ_OK;
     }
-    if (name != nullptr && value != nullptr && strcmp(name, "wait_poll_limit") == 0) {
-        *value = g_opt_wait_poll_limit.load();
+    if (name != nullptr && value != nullptr && strcmp(name, "wait_limit_us") == 0) {
+        *value = g_opt_wait_limit_us.load();
         return JQ_OK;
     }
     if (name != nullptr && value != nullptr && strcmp(name, "decoder_graph") == 0) {

@@ -155,13 +155,13 @@ bool gemv_umma_takes(int type, int64_t k, int rows);
 size_t gemv_umma_image_bytes(int64_t k, int rows);
 inline size_t gemv_umma_image_bytes_one_row(int64_t k) { return gemv_umma_image_bytes(k, 1); }
 int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s);
-int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
+int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
                      const PeerOut* peer = nullptr, bool no_scratch = false);
 int gemv_umma_status(int* status);
 // Option "gemv_tcgen05": zero keeps Q4_K and Q5_K decode on the mma.sync kernels (for comparisons).
 extern std::atomic<int64_t> g_opt_gemv_umma;
-// Option "wait_poll_limit": polls after which a bounded device-side wait gives up.
-extern std::atomic<int64_t> g_opt_wait_poll_limit;
+// Option "wait_limit_us": microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up.
+extern std::atomic<int64_t> g_opt_wait_limit_us;
 
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;

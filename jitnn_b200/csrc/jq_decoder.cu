@@ -1132,11 +1132,11 @@ static int decoder_gemv_imaged(jq_decoder* d, const jq_weight* w, float* y, cons
         if (cur->type == JQ_TYPE_Q4_K) {
             if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
                 const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
-                rc = launch_gemv_umma(v, &v2, d->img_q4k, 1, nullptr, y, y2, gs);
+                rc = launch_gemv_umma(v, &v2, nullptr, d->img_q4k, 1, nullptr, y, y2, gs);
                 handled = true;
                 pass = 1;  // both done
             } else {
-                rc = launch_gemv_umma(v, nullptr, d->img_q4k, 1, nullptr, out_, nullptr, gs);
+                rc = launch_gemv_umma(v, nullptr, nullptr, d->img_q4k, 1, nullptr, out_, nullptr, gs);
                 handled = true;
             }
         } else {

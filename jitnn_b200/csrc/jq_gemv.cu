@@ -96,10 +96,7 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
         // Q4_K, Q5_K: the tcgen05 kernel, one pass over the weights for up to 16 rows
         uint8_t* image = nullptr;
         int rc = scratch_for(s, gemv_umma_image_bytes(v.k, rows), &image);
-        if (rc == JQ_OK) {
-            rc = launch_gemv_umma_image(x, rows, v.k, image, s);
-        }
-        return rc == JQ_OK ? launch_gemv_umma(v, nullptr, image, rows, bias, y, nullptr, s) : rc;
+        return rc == JQ_OK ? launch_gemv_umma(v, nullptr, x, image, rows, bias, y, nullptr, s) : rc;
     }
     if (v.type == JQ_TYPE_Q6_K && rows <= 4 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
         bool handled = false;

@@ -40,18 +40,45 @@ namespace jq {
 static __device__ int g_umma_status;
 static __device__ int g_umma_peer_status;
 
+// Development aid, compiled in with -DJQ_UMMA_TRACE: CTA 0 records clock64() at the hand-over points of every role for
+// its first 64 units; jq_debug_umma_trace copies the record out.
+#ifdef JQ_UMMA_TRACE
+__device__ long long g_umma_cta[160 * 8];  // per CTA: %globaltimer at start, after the wait for the kernel before, image built, first unit's inputs ready, last unit done
+__device__ __forceinline__ long long gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define CT(k)                                                                  \
+    do {                                                                       \
+        if (blockIdx.x < 160) g_umma_cta[blockIdx.x * 8 + (k)] = gtime();      \
+    } while (0)
+__device__ long long g_umma_trace[5 * 64 * 4];
+#define TR(role, i, k)                                                                       \
+    do {                                                                                     \
+        if (blockIdx.x == 0 && lane == 0 && (i) < 64) g_umma_trace[((role) * 64 + (i)) * 4 + (k)] = clock64(); \
+    } while (0)
+#else
+#define TR(role, i, k) \
+    do {               \
+    } while (0)
+#define CT(k) \
+    do {      \
+    } while (0)
+#endif
+
 std::atomic<int64_t> g_opt_gemv_umma{1};
-std::atomic<int64_t> g_opt_wait_poll_limit{1 << 22};
+std::atomic<int64_t> g_opt_wait_limit_us{2000000};
 
 namespace {
 
 constexpr int ROWS = 128;        // weight rows per unit (MMA M)
-constexpr int THREADS = 320;     // warp 0: copies, warp 1: MMA issue and tensor-memory owner, warps 2-5: unpack, warps 6-9: epilogue
 constexpr int SP = 4;            // stages of the row-parameter ring
 constexpr int P_BYTES = 2 * ROWS * 16;
 constexpr int MAX_SX = 8;        // stages of the image ring: enough of them in flight to cover the latency of a copy from L2
 constexpr int MAX_SW = 12;       // stages of the weight ring (as many as fit)
 constexpr size_t SMEM_MAX = 227 * 1024;
+constexpr size_t RESIDENT_MAX = 96 * 1024;  // largest activation image that stays in shared memory for the whole kernel
 
 template <int TYPE>
 struct UFmt;
@@ -71,7 +98,8 @@ struct UFmt<JQ_TYPE_Q5_K> {
 struct UArgs {
     const uint8_t* q0;      // blocks of the first weight, row after row
     const uint8_t* q1;      // of the second weight, if there is one
-    const uint8_t* image;   // [KB][image block]
+    const uint8_t* image;   // [KB][image block], unless the kernel builds the image itself ...
+    const float* x;         // ... from x [rows, k]
     const float* bias;
     float* y0;
     float* y1;
@@ -81,11 +109,11 @@ struct UArgs {
     int rows;               // rows of x
     int SW;                 // stages of the weight ring
     int SX;                 // stages of the image ring
-    float* partial;         // per CTA [max_pieces + 1][rows][128] floats
-    int* counters;          // per tile: pieces finished (back to zero when the kernel ends)
+    unsigned long long* partial;  // per CTA [max_pieces][rows][128] marked floats: what the CTA has of a tile it does not finish (all zero between launches)
+    float* aside;           // per CTA [max_pieces][rows][128] floats, private to the CTA
     int max_pieces;
-    int whole_tiles;        // non-zero: every CTA's run is whole tiles (partial and counters are not used)
-    uint32_t poll_limit;
+    int whole_tiles;        // non-zero: every CTA's run is whole tiles (partial is not used)
+    long long wait_clocks;  // clocks after which a bounded wait gives up
     uint32_t lbo, sbo;      // byte offsets of the image's shared-memory descriptor
     const PeerOut* peer;
 };
@@ -156,7 +184,7 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo,
 struct Phase {
     uint32_t bar, parity;
 };
-__device__ __forceinline__ bool wait_phases(const Phase& p0, const Phase& p1, const Phase& p2, bool use2, volatile int* abort_flag, int code, uint32_t limit) {
+__device__ __forceinline__ bool wait_phases(const Phase& p0, const Phase& p1, const Phase& p2, bool use2, volatile int* abort_flag, int code, long long limit) {
     const bool r0 = tc::mbar_try(p0.bar, p0.parity);
     const bool r1 = tc::mbar_try(p1.bar, p1.parity);
     const bool r2 = use2 ? tc::mbar_try(p2.bar, p2.parity) : true;
@@ -170,20 +198,61 @@ __device__ __forceinline__ bool wait_phases(const Phase& p0, const Phase& p1, co
 // The same on behalf of a whole warp: lane 0 polls (32 lanes polling one word would serialise), the outcome goes to the other
 // lanes, and __shfl_sync orders their later reads behind lane 0's acquire.
 __device__ __forceinline__ bool warp_wait_phases(const Phase& p0, const Phase& p1, const Phase& p2, bool use2, volatile int* abort_flag, int code,
-                                                 uint32_t limit, int lane) {
+                                                 long long limit, int lane) {
     int ok = 1;
     if (lane == 0) {
         ok = wait_phases(p0, p1, p2, use2, abort_flag, code, limit) ? 1 : 0;
     }
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, uint32_t limit, int lane) {
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit, int lane) {
     int ok = 1;
     if (lane == 0) {
         ok = tc::mbar_wait(bar, parity, abort_flag, &g_umma_status, code, limit) ? 1 : 0;
     }
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
+// The order in which a CTA visits the units [u0, u1) of its run: tile after tile from the last tile of the run to the first,
+// the super-blocks of a tile in ascending order. The tile in which the run ends (of which the CTA has the first super-blocks)
+// is visited first, so that its running sums are known to the CTA that continues the tile long before that CTA gets there:
+// the tile in which a run begins is visited last.
+struct Walk {
+    int t, b, e;        // tile, super-block, end of the tile's super-blocks that belong to the run
+    int t_first, b0;    // the run's first tile and its first super-block in it
+    int kb;
+    __device__ __forceinline__ void start(int64_t u0, int64_t u1, int kb_) {
+        kb = kb_;
+        t_first = (int)(u0 / kb);
+        b0 = (int)(u0 - (int64_t)t_first * kb);
+        t = (int)((u1 - 1) / kb);
+        e = (int)(u1 - (int64_t)t * kb);
+        b = t == t_first ? b0 : 0;
+    }
+    __device__ __forceinline__ void next() {
+        if (++b == e) {
+            t--;
+            b = t == t_first ? b0 : 0;
+            e = kb;
+        }
+    }
+};
+
+// What one CTA hands to another through the scratch buffer: a float and, in the same naturally aligned 8-byte word, a mark that
+// says the float has been written. An 8-byte store is seen whole or not at all, so the reader needs no flag and the writer no
+// fence: the reader polls the word until the mark is there, takes the float and clears the word for the next launch.
+__device__ __forceinline__ void handoff_store(unsigned long long* p, float v) {
+    const unsigned long long w = (unsigned long long)__float_as_uint(v) | (1ull << 32);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long handoff_load(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ void handoff_clear(unsigned long long* p) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(0ull) : "memory");
+}
+
 // A ring position: stage and the parity of the phase in which the stage gets filled.
 struct Ring {
     int s = 0;
@@ -203,7 +272,7 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
     }
 }
 
-__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
@@ -222,13 +291,23 @@ __global__ void __launch_bounds__(128) umma_activation_image_kernel(const float*
     }
 }
 
-// MR = rows of x the epilogue computes (1, 2, 5, 8, 10 or 16; a call with fewer rows leaves the others unused).
-template <int TYPE, int MR, bool PEER>
-__global__ void __launch_bounds__(THREADS, 1)
-    gemv_umma_kernel(const UArgs a) {
+// MR = rows of x the kernel computes (1, 2, 5, 8, 10 or 16; a call with fewer rows leaves the others unused). From eight rows on
+// two sets of epilogue warps share the rows of x (the scale fold is 24 integer multiply-adds per weight row, super-block
+// and row of x). RES: the image of the whole k is built by this kernel into shared memory and stays there (small k x rows).
+template <int MR>
+struct Roles {
+    static constexpr int ES = MR >= 8 ? 2 : 1;     // sets of four epilogue warps
+    static constexpr int HM = MR / ES;             // rows of x per epilogue thread
+    static constexpr int THREADS = 192 + 128 * ES + 32;  // warp 0: copies, warp 1: MMA issue and tensor-memory owner, warps 2-5: unpack, then epilogue, last warp: MMA issue
+};
+
+template <int TYPE, int MR, bool PEER, bool RES>
+__global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const UArgs a) {
     constexpr int N = umma::columns_for_rows(MR);
     using IC = umma::ImageCfg<N>;
     using F = UFmt<TYPE>;
+    constexpr int ES = Roles<MR>::ES, HM = Roles<MR>::HM;
+    constexpr int MMA2_WARP = 6 + 4 * ES;       // the second MMA issuer
     constexpr int SG = N <= 16 ? 8 : 4;         // sub-blocks per accumulator stage
     constexpr int NGROUPS = 8 / SG;
     constexpr int D_COLS = SG * N;              // tensor-memory columns of an accumulator stage
@@ -241,14 +320,15 @@ __global__ void __launch_bounds__(THREADS, 1)
     constexpr int WB = ROWS * F::BYTES;
     constexpr int XB = (IC::BYTES + 127) & ~127;
     constexpr uint32_t IDESC = idesc_of(N);
-    constexpr int LDC = MR == 1 ? 4 : (N == 8 ? 8 : (N == 16 ? 16 : 32));  // accumulator columns per tcgen05.ld (N = 48: one of 32, one of 16)
+    constexpr int LDW = 3 * HM <= 4 ? 4 : (3 * HM <= 8 ? 8 : (3 * HM <= 16 ? 16 : 24));  // accumulator columns an epilogue thread reads per sub-block
 
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((128u - (tc::smem_u32(smem_unaligned) & 127u)) & 127u);
     const int SW = a.SW, SX = a.SX;
+    const int KB = a.KB;
     uint8_t* w_ring = smem;
-    uint8_t* x_ring = w_ring + (size_t)SW * WB;
-    uint8_t* p_ring = x_ring + SX * XB;
+    uint8_t* x_ring = w_ring + (size_t)SW * WB;  // RES: the KB blocks of the image; else SX stages
+    uint8_t* p_ring = x_ring + (size_t)(RES ? KB : SX) * XB;
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_ring + SP * P_BYTES);
     const uint32_t bar0 = tc::smem_u32(bars);
     auto full_w = [&](int s) { return bar0 + 8u * (uint32_t)s; };
@@ -265,17 +345,18 @@ __global__ void __launch_bounds__(THREADS, 1)
     constexpr int NBARS = B2 + 16;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    volatile int* fin = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [0] this CTA adds the tile up, [1], [2] first and last CTA of the tile
+    volatile int* d_issued = reinterpret_cast<volatile int*>(tmem_slot + 2);  // per accumulator stage: fillings whose wait for the stage has passed
+    volatile int* fin_all = reinterpret_cast<volatile int*>(tmem_slot + 6);  // per epilogue set: [0] this CTA adds the tile up, [1], [2] first and last CTA of the tile
 
     asm volatile("griddepcontrol.launch_dependents;");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int KB = a.KB;
     const int64_t U = (int64_t)a.tiles * KB;
     const int64_t G = gridDim.x;
     // This CTA's run of units: an even share of all units, or (no scratch for pieces of tiles) an even share of the tiles.
     const int64_t u0 = a.whole_tiles ? (int64_t)blockIdx.x * a.tiles / G * KB : (int64_t)blockIdx.x * U / G;
     const int units = (int)((a.whole_tiles ? ((int64_t)blockIdx.x + 1) * a.tiles / G * KB : ((int64_t)blockIdx.x + 1) * U / G) - u0);
-    const uint32_t limit = a.poll_limit;
+    const int64_t u1 = u0 + units;
+    const long long limit = a.wait_clocks;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MAX_SW; s++) {
@@ -284,19 +365,22 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         for (int s = 0; s < MAX_SX; s++) {
             tc::mbar_init(full_x(s), 1);
-            tc::mbar_init(empty_x(s), 1 + 4);  // the MMAs that read the digits, and one lane of each epilogue warp
+            tc::mbar_init(empty_x(s), 1 + 4 * ES);  // the MMAs that read the digits, and one lane of each epilogue warp
         }
         for (int s = 0; s < SP; s++) {
             tc::mbar_init(full_p(s), 4);
-            tc::mbar_init(empty_p(s), 4);
+            tc::mbar_init(empty_p(s), 4 * ES);
         }
         for (int s = 0; s < 4; s++) {
             tc::mbar_init(full_a(s), 4);
             tc::mbar_init(empty_a(s), 1);
             tc::mbar_init(full_d(s), 1);
-            tc::mbar_init(empty_d(s), 4);  // one arrival per epilogue warp
+            tc::mbar_init(empty_d(s), 4 * ES);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
+        for (int s = 0; s < 4; s++) {
+            d_issued[s] = 0;
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -308,91 +392,186 @@ __global__ void __launch_bounds__(THREADS, 1)
     tc::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    // Weights depend on nothing that runs before this kernel: the first ring-full of them is requested at once.
+    auto issue_w = [&](int i, int s, int t, int b) {
+        const bool first = t < a.tiles0;
+        const uint8_t* src = (first ? a.q0 : a.q1) + ((int64_t)(first ? t : t - a.tiles0) * KB + b) * WB;
+        tc::mbar_expect_tx(full_w(s), WB);
+        tc::bulk_load(tc::smem_u32(w_ring + (size_t)s * WB), src, WB, full_w(s));
+        TR(0, i, 0);
+    };
+    const int w_prologue = units < SW ? units : SW;
+    Walk ww;  // thread 0: the unit whose weights are requested next
+    ww.start(u0, u1, KB);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < w_prologue; i++) {
+            issue_w(i, i, ww.t, ww.b);
+            ww.next();
+        }
+    }
+    if constexpr (RES) {
+        // The activation image of the whole k, built here from x by the warps that have nothing to do yet: one warp per
+        // (super-block, row of x). x is complete once the kernel before this one has finished.
+        if (warp >= 2) {
+            if (warp == 2 && lane == 0) CT(0);
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if (warp == 2 && lane == 0) CT(1);
+            const int workers = Roles<MR>::THREADS / 32 - 2;  // every warp but the copy and the first MMA warp
+            // the values of a warp's next part are requested before its current part is worked on
+            const int tasks = KB * a.rows;
+            auto src_of = [&](int task) { return a.x + (int64_t)(task % a.rows) * KB * 256 + (int64_t)(task / a.rows) * 256; };
+            float4 lo, hi, lo_next = make_float4(0.f, 0.f, 0.f, 0.f), hi_next = lo_next;
+            int task = warp - 2;
+            if (task < tasks) {
+                umma::load_lane_values(src_of(task), lane, lo_next, hi_next);
+            }
+            for (; task < tasks; task += workers) {
+                lo = lo_next;
+                hi = hi_next;
+                if (task + workers < tasks) {
+                    umma::load_lane_values(src_of(task + workers), lane, lo_next, hi_next);
+                }
+                umma::build_image_from<N>(lo, hi, task % a.rows, a.rows, x_ring + (size_t)(task / a.rows) * XB, lane);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the tensor core reads the digits through the async proxy
+            if (warp == 2 && lane == 0) CT(2);
+        }
+        __syncthreads();
+    }
+
     if (warp == 0) {
-        // ---- copies: one thread asks the copy engine for a unit's weights (one contiguous run of the tiled layout) and for
-        // its super-block's image. Weights depend on nothing and are requested at once, as many as the ring holds; the image
-        // is complete only when the kernel before this one has finished.
-        auto issue_w = [&](int i, int s) {
-            const int64_t u = u0 + i;
-            const int t = (int)(u / KB), b = (int)(u % KB);
-            const bool first = t < a.tiles0;
-            const uint8_t* src = (first ? a.q0 : a.q1) + ((int64_t)(first ? t : t - a.tiles0) * KB + b) * WB;
-            tc::mbar_expect_tx(full_w(s), WB);
-            tc::bulk_load(tc::smem_u32(w_ring + (size_t)s * WB), src, WB, full_w(s));
-        };
-        auto issue_x = [&](int i, int s) {
-            const int b = (int)((u0 + i) % KB);
+        // ---- copies: one thread asks the copy engine for a unit's weights (one contiguous run of the tiled layout) and, unless
+        // the image is resident, for its super-block's image, which is complete only when the kernel before this one has finished.
+        auto issue_x = [&](int i, int s, int b) {
             tc::mbar_expect_tx(full_x(s), IC::BYTES);
             tc::bulk_load(tc::smem_u32(x_ring + s * XB), a.image + (size_t)b * IC::BYTES, IC::BYTES, full_x(s));
+            TR(0, i, 1);
         };
-        int iw = units < SW ? units : SW;
-        if (lane == 0) {
-            for (int i = 0; i < iw; i++) {
-                issue_w(i, i);  // the ring starts out empty
-            }
-        }
-        __syncwarp();
-        asm volatile("griddepcontrol.wait;" ::: "memory");
-        if constexpr (PEER) {
-            if (a.peer->wait_first) {
-                // the image is what the ranks' latest exchange delivered: complete once all their flags are up
-                peer_wait_inline(a.peer->flags[a.peer->rank], a.peer->world, lane, &g_umma_peer_status);
+        if constexpr (!RES) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            if constexpr (PEER) {
+                if (a.peer->wait_first) {
+                    // the image is what the ranks' latest exchange delivered: complete once all their flags are up
+                    peer_wait_inline(a.peer->flags[a.peer->rank], a.peer->world, lane, &g_umma_peer_status);
+                }
             }
         }
         if (lane == 0) {
-            int ix = units < SX ? units : SX;
-            for (int i = 0; i < ix; i++) {
-                issue_x(i, i);
+            int iw = w_prologue;
+            int ix = RES ? units : (units < SX ? units : SX);
+            Walk wx;
+            wx.start(u0, u1, KB);
+            if constexpr (!RES) {
+                for (int i = 0; i < ix; i++) {
+                    issue_x(i, i, wx.b);
+                    wx.next();
+                }
             }
-            Ring wr, xr;  // the next slot to fill, and the parity of the phase in which it was last filled ...
+            Ring wr, xr;  // the next slot to fill, and the parity of the phase in which its last filling was consumed
             wr.s = iw == SW ? 0 : iw;
-            xr.s = ix == SX ? 0 : ix;  // ... which is phase 0 for both after the first round (if there is a second one at all)
-            uint32_t idle = 0;
+            xr.s = ix == SX ? 0 : ix;
+            long long idle_since = 0;
             while (iw < units || ix < units) {
                 // both rings polled together and without suspending: a slot of either may come free first
                 const bool wfree = iw < units && tc::mbar_test(empty_w(wr.s), wr.ph);
                 const bool xfree = ix < units && tc::mbar_test(empty_x(xr.s), xr.ph);
                 if (wfree) {
-                    issue_w(iw++, wr.s);
+                    issue_w(iw++, wr.s, ww.t, ww.b);
+                    ww.next();
                     wr.next(SW);
                 }
                 if (xfree) {
-                    issue_x(ix++, xr.s);
+                    issue_x(ix++, xr.s, wx.b);
+                    wx.next();
                     xr.next(SX);
                 }
                 if (wfree || xfree) {
-                    idle = 0;
-                } else if (++idle >= limit) {
+                    idle_since = 0;
+                } else if (*abort_flag != 0) {
+                    break;
+                } else if (idle_since == 0) {
+                    idle_since = clock64();
+                } else if (clock64() - idle_since > limit) {
                     atomicCAS(&g_umma_status, 0, 64 + 1);
                     *abort_flag = 1;
-                    break;
-                } else if ((idle & 63u) == 0 && *abort_flag != 0) {
                     break;
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---- MMA issue -------------------------------------------------------------------------------------------------
+    } else if (warp == 1 || warp == MMA2_WARP) {
+        // ---- MMA issue: one thread of warp 1 takes the even units of the run, one thread of the last warp the odd ones. An
+        // MMA of this shape keeps the tensor core busy for 60 to 75 clocks whatever N is, and issuing stalls while the
+        // tensor core's queue is full; with two issuers one waits for its unit's inputs (a poll of an mbarrier takes a few
+        // hundred clocks to come back) while the other's MMAs run.
         if (lane == 0) {
+            const int first = warp == 1 ? 0 : 1;
             bool ok = true;
             Ring xr, ar, dr;
-            // descriptor of sub-block 0 of image stage 0; stages and sub-blocks only move the 14-bit address field (16-byte units)
+            for (int k = 0; k < first; k++) {
+                xr.next(SX);
+                ar.next(NA);
+                for (int g = 0; g < NGROUPS; g++) {
+                    dr.next(ND);
+                }
+            }
+            Walk wk;
+            wk.start(u0, u1, KB);
+            if (first == 1 && units > 1) {
+                wk.next();
+            }
+            // descriptor of sub-block 0 of image block 0; blocks and sub-blocks only move the 14-bit address field (16-byte units)
             const uint64_t desc0 = smem_desc_plain(tc::smem_u32(x_ring), a.lbo, a.sbo);
-            for (int i = 0; i < units && ok; i++) {
-                ok = wait_phases(Phase{full_x(xr.s), xr.ph}, Phase{full_a(ar.s), ar.ph}, Phase{empty_d(dr.s), dr.ph ^ 1u}, true, abort_flag, 64 + 2, limit);
+            // Both issuers fill the same accumulator stages in turn. A wait for "the stage's previous filling has been read" may only
+            // be made once that filling's own wait has passed (an mbarrier tells two phases apart, not three), so the issuers
+            // count per stage the fillings that have got that far.
+            auto my_turn = [&](int stage, int filling) {
+                if (d_issued[stage] >= filling) {
+                    return true;
+                }
+                const long long t0 = clock64();
+                while (d_issued[stage] < filling) {
+                    if (*abort_flag != 0) {
+                        return false;
+                    }
+                    if (clock64() - t0 > limit) {
+                        atomicCAS(&g_umma_status, 0, 64 + 2);
+                        *abort_flag = 1;
+                        return false;
+                    }
+                }
+                return true;
+            };
+            int filling[4] = {0, 0, 0, 0};  // per stage: the number of the next filling by this issuer
+            {
+                // where the first unit of this issuer stands
+                int q = 0;
+                for (int k = 0; k < first; k++) {
+                    q += NGROUPS;
+                }
+                for (int st = 0; st < ND; st++) {
+                    filling[st] = (q + ND - 1 - st) / ND;  // groups before q that fell on stage st
+                }
+            }
+            for (int i = first; i < units && ok; i += 2) {
+                ok = my_turn(dr.s, filling[dr.s]) &&
+                     wait_phases(Phase{full_a(ar.s), ar.ph}, Phase{empty_d(dr.s), dr.ph ^ 1u}, Phase{full_x(xr.s), xr.ph}, !RES, abort_flag, 64 + 2, limit);
                 if (!ok) {
                     break;
                 }
+                d_issued[dr.s] = filling[dr.s] + 1;
                 tc::fence_after_sync();
-                const uint64_t xdesc = desc0 + (uint64_t)((uint32_t)(xr.s * XB) >> 4);
+                TR(1, i, 0);
+                if (i == 0) CT(3);
+                const uint64_t xdesc = desc0 + (uint64_t)((uint32_t)((RES ? wk.b : xr.s) * XB) >> 4);
                 const uint32_t abase = tmem + (uint32_t)(ar.s * A_COLS);
 #pragma unroll
                 for (int g = 0; g < NGROUPS; g++) {
                     if (g > 0) {
-                        ok = tc::mbar_wait(empty_d(dr.s), dr.ph ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
+                        ok = my_turn(dr.s, filling[dr.s]) && tc::mbar_wait(empty_d(dr.s), dr.ph ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
                         if (!ok) {
                             break;
                         }
+                        d_issued[dr.s] = filling[dr.s] + 1;
                         tc::fence_after_sync();
                     }
                     const uint32_t dbase = tmem + (uint32_t)D_BASE + (uint32_t)(dr.s * D_COLS);
@@ -402,14 +581,32 @@ __global__ void __launch_bounds__(THREADS, 1)
                         umma_i8_ts(dbase + (uint32_t)(sg * N), abase + (uint32_t)(s * 8), xdesc + (uint64_t)((s * IC::SUB_BYTES) >> 4), IDESC);
                     }
                     tc::umma_commit(full_d(dr.s));
+                    TR(1, i, 1 + (g & 1));
                     dr.next(ND);
                 }
-                if (ok) {
-                    tc::umma_commit(empty_a(ar.s));
+                if (!ok) {
+                    break;
+                }
+                // the other issuer's unit takes the next NGROUPS fillings, this issuer's next unit the NGROUPS after them
+                for (int st = 0; st < ND; st++) {
+                    filling[st] = ((i + 2) * NGROUPS + ND - 1 - st) / ND;
+                }
+                tc::umma_commit(empty_a(ar.s));
+                if constexpr (!RES) {
                     tc::umma_commit(empty_x(xr.s));
                 }
-                xr.next(SX);
-                ar.next(NA);
+                TR(1, i, 3);
+                // on to the unit after the other issuer's
+                for (int k = 0; k < 2; k++) {
+                    xr.next(SX);
+                    ar.next(NA);
+                    if (i + 1 + k < units) {
+                        wk.next();
+                    }
+                }
+                for (int g = 0; g < NGROUPS; g++) {
+                    dr.next(ND);
+                }
             }
         }
     } else if (warp < 6) {
@@ -425,6 +622,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                 break;
             }
             tc::fence_after_sync();
+            if (warp == 2) TR(2, i, 0);
             const uint8_t* wrow = w_ring + (size_t)ws * WB + r * F::BYTES;
             const uint4 h = *reinterpret_cast<const uint4*>(wrow);  // fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins
             const uint32_t sca = h.y & 0x3f3f3f3fu, scb = and_or(h.y >> 2, 0x30303030u, h.w & 0x0f0f0f0fu);            // scales 0..3, 4..7
@@ -439,6 +637,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             prow[0] = make_uint4(sc16[0], sc16[1], sc16[2], sc16[3]);
             prow[ROWS] = make_uint4(mna, mnb, h.x, 0u);
             warp_arrive(full_p(ps), lane);
+            if (warp == 2) TR(2, i, 1);
             uint4 qh0 = make_uint4(0u, 0u, 0u, 0u), qh1 = qh0;
             if constexpr (TYPE == JQ_TYPE_Q5_K) {
                 qh0 = *reinterpret_cast<const uint4*>(wrow + 16);
@@ -467,47 +666,174 @@ __global__ void __launch_bounds__(THREADS, 1)
                 tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 16 * j), av);
             }
             tmem_st_wait();
+            if (warp == 2) TR(2, i, 2);
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) {
                 tc::mbar_arrive(empty_w(ws));  // the warp's rows of the slot are in registers or tensor memory
                 tc::mbar_arrive(full_a(as));
             }
+            if (warp == 2) TR(2, i, 3);
             wr.next(SW);
             ar.next(NA);
             pr.next(SP);
         }
     } else {
-        // ---- epilogue: thread = weight row -----------------------------------------------------------------------------------------
+        // ---- epilogue: thread = weight row; set `eset` of four warps takes rows m0 .. m0 + HM - 1 of x ------------------------------
         const int r = (warp & 3) * 32 + lane;
-        const int et = threadIdx.x - 6 * 32;
+        const int eset = (warp - 6) >> 2;
+        const int m0 = eset * HM;
+        const bool et0 = ((threadIdx.x - 192) & 127) == 0;
+        volatile int* fin = fin_all + 4 * eset;
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         asm volatile("griddepcontrol.wait;" ::: "memory");  // y and the scratch are no longer in use by the kernel before
-        float acc[MR];
+        float acc[HM];
 #pragma unroll
-        for (int m = 0; m < MR; m++) {
+        for (int m = 0; m < HM; m++) {
             acc[m] = 0.0f;
         }
-        int t = (int)(u0 / KB), b = (int)(u0 % KB);
-        bool piecewise = b > 0;  // the run starts inside a tile: its contributions go to the scratch one by one
-        int piece_b0 = b;
+        Walk we;
+        we.start(u0, u1, KB);
+        int part_b0 = we.b;  // first super-block of the part of a tile that is being visited
         Ring xr, pr, dr;
-        const size_t slot_floats = (size_t)(a.max_pieces + 1) * a.rows * ROWS;
-        float* const my_slot = a.partial + (size_t)blockIdx.x * slot_floats;
+        const size_t slot_words = (size_t)a.max_pieces * a.rows * ROWS;
+        unsigned long long* const my_slot = a.partial + (size_t)blockIdx.x * slot_words;
+        float* const my_aside = a.aside + (size_t)blockIdx.x * slot_words;  // this CTA's own contributions to a tile it finishes after its run
+        int late_tile = -1, late_len = 0;
         bool ok = true;
+        if (et0) {
+            fin[0] = 1;  // cleared by a thread of the set whose wait for another CTA's sums has run out
+        }
+        epilogue_barrier(1 + eset);
+        // y (or every rank's y) for this thread's row of tile `tile`
+        auto write_tile = [&](int tile, const float (&sum)[HM]) {
+            const bool second = tile >= a.tiles0;
+            const int64_t n = second ? a.n1 : a.n0;
+            const int64_t row = (int64_t)(second ? tile - a.tiles0 : tile) * ROWS + r;
+            float* const yo = second ? a.y1 : a.y0;
+            if (row < n) {
+                const float bv = (a.bias != nullptr && !second) ? a.bias[row] : 0.0f;
+#pragma unroll
+                for (int m = 0; m < HM; m++) {
+                    if (m0 + m < a.rows) {
+                        const float val = sum[m] + bv;
+                        if constexpr (!PEER) {
+                            yo[(int64_t)(m0 + m) * n + row] = val;
+                        } else {
+                            // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
+                            for (int rk = 0; rk < a.peer->world; rk++) {
+                                a.peer->y[rk][(int64_t)(m0 + m) * a.peer->n_total + a.peer->col0 + row] = val;
+                            }
+                        }
+                    }
+                }
+            }
+        };
+        // The sum of the super-blocks of `tile` that the CTAs before this one hold: the first of them its running sum, the ones
+        // between it and this CTA (few output rows: a tile is then shared by several CTAs) their contributions one by one. Every
+        // float is polled, bounded, until its mark is there; with many output rows the one running sum was written at the start of
+        // the other CTA's run. Eight words are requested together (a load from L2 takes the better part of a microsecond).
+        auto gather = [&](int tile, float (&sum)[HM]) {
+            const int c_first = (int)((((int64_t)tile * KB + 1) * G - 1) / U);
+            const int64_t tb = (int64_t)tile * KB;
+            bool good = true;
+            // the words in k order: the first CTA's running sum, then every contribution of the CTAs between it and this one
+            int cta = c_first, q = 0, len = 1;
+            bool more = cta < (int)blockIdx.x;
+            while (more && good) {
+                constexpr int CH = 16;  // words requested together, and asked for again together until every one has its mark
+                unsigned long long* ptr[CH];
+                int count = 0;
+                while (count < CH && more) {
+                    ptr[count++] = a.partial + (size_t)cta * slot_words + ((size_t)q * a.rows + m0) * ROWS + r;
+                    if (++q == len) {
+                        cta++;
+                        q = 0;
+                        more = cta < (int)blockIdx.x;
+                        len = (int)(((int64_t)cta + 1) * U / G - (int64_t)cta * U / G);  // a CTA between the first and this one: its whole run
+                    }
+                }
+                const bool starts = ptr[0] == a.partial + (size_t)c_first * slot_words + (size_t)m0 * ROWS + r;
+#pragma unroll
+                for (int m = 0; m < HM; m++) {
+                    if (m0 + m < a.rows && good) {
+                        unsigned long long w[CH];
+                        long long t0 = 0;
+                        for (;;) {
+                            bool all = true;
+#pragma unroll
+                            for (int c = 0; c < CH; c++) {
+                                w[c] = c < count ? handoff_load(ptr[c] + (size_t)m * ROWS) : (1ull << 32);
+                            }
+#pragma unroll
+                            for (int c = 0; c < CH; c++) {
+                                all = all && (w[c] >> 32) != 0;
+                            }
+                            if (all) {
+                                break;
+                            }
+                            if (t0 == 0) {
+                                t0 = clock64();
+                            } else if (*abort_flag != 0 || clock64() - t0 > limit) {
+                                atomicCAS(&g_umma_status, 0, 64 + 5);
+                                *abort_flag = 1;
+                                good = false;
+                                break;
+                            }
+                        }
+                        if (good) {
+#pragma unroll
+                            for (int c = 0; c < CH; c++) {
+                                if (c < count) {
+                                    handoff_clear(ptr[c] + (size_t)m * ROWS);
+                                    const float v = __uint_as_float((uint32_t)w[c]);
+                                    sum[m] = (starts && c == 0) ? v : sum[m] + v;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            // every thread of the set continues only if all of them got what they waited for
+            if (!good) {
+                fin[0] = 0;
+            }
+            epilogue_barrier(1 + eset);
+            const bool all_good = fin[0] != 0;
+            epilogue_barrier(1 + eset);
+            return all_good;
+        };
         for (int i = 0; i < units && ok; i++) {
             const int ps = pr.s, xs = xr.s;
-            if (!warp_wait_phases(Phase{full_p(ps), pr.ph}, Phase{full_d(dr.s), dr.ph}, Phase{full_x(xs), xr.ph}, true, abort_flag, 64 + 4, limit, lane)) {
+            const int t = we.t, b = we.b;
+            // What this CTA has of tile t: [part_b0, we.e). Starting at 0 it holds the running sum (written out at KB, handed on as
+            // it stands before); starting later it continues a sum that the CTAs before it hold, if it reaches KB, or stores its
+            // contributions one by one for the CTA that does.
+            const bool stores_each = part_b0 > 0 && we.e < KB;
+            // The end of a tile whose beginning other CTAs hold. If only one does (many output rows), it wrote its running sum at the
+            // start of its run, long ago: fetch it now and carry on from it. If several do (few output rows), they are still at
+            // work: keep this CTA's contributions aside and put everything together when the run is over.
+            const bool continues = part_b0 > 0 && we.e == KB;
+            const bool aside = continues && (int)blockIdx.x - (int)((((int64_t)t * KB + 1) * G - 1) / U) > 1;
+            if (b == part_b0 && continues && !aside) {
+                ok = gather(t, acc);
+                if (!ok) {
+                    break;
+                }
+            }
+            if (!warp_wait_phases(Phase{full_p(ps), pr.ph}, Phase{full_d(dr.s), dr.ph}, Phase{full_x(xs), xr.ph}, !RES, abort_flag, 64 + 4, limit, lane)) {
+                ok = false;
                 break;
             }
             tc::fence_after_sync();
+            if (warp == 6) TR(3, i, 0);
             const uint4* prow = reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r;
             const uint4 pa = prow[0], pb = prow[ROWS];
             warp_arrive(empty_p(ps), lane);
             const uint32_t sc16[4] = {pa.x, pa.y, pa.z, pa.w};
-            int I[MR][3];
+            int I[HM][3];
 #pragma unroll
-            for (int m = 0; m < MR; m++) {
+            for (int m = 0; m < HM; m++) {
                 I[m][0] = I[m][1] = I[m][2] = 0;
             }
 #pragma unroll
@@ -520,198 +846,167 @@ __global__ void __launch_bounds__(THREADS, 1)
                     }
                     tc::fence_after_sync();
                 }
-                const uint32_t dbase = tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS);
-                if constexpr (N == 48) {
+                const uint32_t dbase = tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS + 3 * m0);
+                constexpr int CS = (64 / LDW) < SG ? (64 / LDW) : SG;  // sub-blocks whose accumulators are in registers at a time
 #pragma unroll
-                    for (int sg = 0; sg < SG; sg++) {
-                        uint32_t dlo[32], dhi[16];
-                        tmem_ld<32>(dlo, dbase + (uint32_t)(sg * N));
-                        tmem_ld<16>(dhi, dbase + (uint32_t)(sg * N + 32));
-                        tmem_ld_wait();
-                        const int s = g * SG + sg;
-                        const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
+                for (int c0 = 0; c0 < SG; c0 += CS) {
+                    uint32_t dv[CS][LDW];
 #pragma unroll
-                        for (int m = 0; m < MR; m++) {
+                    for (int c = 0; c < CS; c++) {
+                        if constexpr (LDW == 24) {
+                            uint32_t lo[16], hi[8];
+                            tmem_ld<16>(lo, dbase + (uint32_t)((c0 + c) * N));
+                            tmem_ld<8>(hi, dbase + (uint32_t)((c0 + c) * N + 16));
 #pragma unroll
-                            for (int dg = 0; dg < 3; dg++) {
-                                const int col = 3 * m + dg;
-                                I[m][dg] += scale * (int)(col < 32 ? dlo[col < 32 ? col : 0] : dhi[col >= 32 ? col - 32 : 0]);
+                            for (int q = 0; q < 16; q++) {
+                                dv[c][q] = lo[q];
                             }
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                dv[c][16 + q] = hi[q];
+                            }
+                        } else {
+                            tmem_ld<LDW>(dv[c], dbase + (uint32_t)((c0 + c) * N));
                         }
                     }
-                } else {
-                    constexpr int CS = (64 / LDC) < SG ? (64 / LDC) : SG;  // sub-blocks whose accumulators are in registers at a time
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int c0 = 0; c0 < SG; c0 += CS) {
-                        uint32_t dv[CS][LDC];
+                    for (int c = 0; c < CS; c++) {
+                        const int s = g * SG + c0 + c;
+                        const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
 #pragma unroll
-                        for (int c = 0; c < CS; c++) {
-                            tmem_ld<LDC>(dv[c], dbase + (uint32_t)((c0 + c) * N));
-                        }
-                        tmem_ld_wait();
+                        for (int m = 0; m < HM; m++) {
 #pragma unroll
-                        for (int c = 0; c < CS; c++) {
-                            const int s = g * SG + c0 + c;
-                            const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
-#pragma unroll
-                            for (int m = 0; m < MR; m++) {
-#pragma unroll
-                                for (int dg = 0; dg < 3; dg++) {
-                                    I[m][dg] += scale * (int)dv[c][3 * m + dg];
-                                }
+                            for (int dg = 0; dg < 3; dg++) {
+                                I[m][dg] += scale * (int)dv[c][3 * m + dg];
                             }
                         }
                     }
                 }
                 tc::fence_before_sync();
                 warp_arrive(empty_d(ds), lane);
+                if (warp == 6) TR(3, i, 1 + (g & 1));
                 dr.next(ND);
             }
             if (!ok) {
                 break;
             }
             // ---- this super-block's contribution: d (sum over digits of weight x integer) - dmin (sum over sub-blocks of min x sum of x) ----
-            const float* aux = reinterpret_cast<const float*>(x_ring + xs * XB + IC::XD);
+            const float* aux = reinterpret_cast<const float*>(x_ring + (size_t)(RES ? b : xs) * XB + IC::XD) + m0;
             const float d = half_bits_to_float(pb.z) * (F::IN_PLACE ? 0.0625f : 1.0f), dmin = half_bits_to_float(pb.z >> 16);
-            float msum[MR];
+            float msum[HM];
 #pragma unroll
-            for (int m = 0; m < MR; m++) {
+            for (int m = 0; m < HM; m++) {
                 msum[m] = 0.0f;
             }
 #pragma unroll
             for (int s = 0; s < 8; s++) {
                 const float mn = (float)(((s < 4 ? pb.x : pb.y) >> (8 * (s & 3))) & 0xffu);
 #pragma unroll
-                for (int m = 0; m < MR; m++) {
+                for (int m = 0; m < HM; m++) {
                     msum[m] = fmaf(mn, aux[s * IC::MPAD + m], msum[m]);
                 }
             }
-            float c[MR];
+            float c[HM];
 #pragma unroll
-            for (int m = 0; m < MR; m++) {
+            for (int m = 0; m < HM; m++) {
                 const float w0 = aux[8 * IC::MPAD + m];
                 const float q = fmaf(w0 * 65536.0f, (float)I[m][2], fmaf(w0 * 256.0f, (float)I[m][1], w0 * (float)I[m][0]));
                 c[m] = fmaf(d, q, -(dmin * msum[m]));
             }
-            __syncwarp();
-            if (lane == 0) {
-                tc::mbar_arrive(empty_x(xs));
+            if constexpr (!RES) {
+                __syncwarp();
+                if (lane == 0) {
+                    tc::mbar_arrive(empty_x(xs));
+                }
             }
-            if (piecewise) {
-                float* dst = my_slot + (size_t)(b - piece_b0) * a.rows * ROWS + r;
+            if (stores_each) {
+                unsigned long long* dst = my_slot + ((size_t)(b - part_b0) * a.rows + m0) * ROWS + r;
 #pragma unroll
-                for (int m = 0; m < MR; m++) {
-                    if (m < a.rows) {
-                        dst[m * ROWS] = c[m];
+                for (int m = 0; m < HM; m++) {
+                    if (m0 + m < a.rows) {
+                        handoff_store(dst + m * ROWS, c[m]);
                     }
                 }
+            } else if (aside) {
+                float* dst = my_aside + ((size_t)(b - part_b0) * a.rows + m0) * ROWS + r;
+#pragma unroll
+                for (int m = 0; m < HM; m++) {
+                    if (m0 + m < a.rows) {
+                        __stcg(dst + m * ROWS, c[m]);
+                    }
+                }
+                late_tile = t;
+                late_len = b - part_b0 + 1;
             } else {
 #pragma unroll
-                for (int m = 0; m < MR; m++) {
+                for (int m = 0; m < HM; m++) {
                     acc[m] += c[m];
                 }
             }
-            const bool tile_end = b == KB - 1;
-            if (tile_end || i == units - 1) {
-                const bool second = t >= a.tiles0;
-                const int64_t n = second ? a.n1 : a.n0;
-                const int64_t row = (int64_t)(second ? t - a.tiles0 : t) * ROWS + r;
-                float* const yo = second ? a.y1 : a.y0;
-                bool write = !piecewise && tile_end;  // a whole tile
-                if (!write) {
-                    if (!piecewise) {
-                        float* dst = my_slot + (size_t)a.max_pieces * a.rows * ROWS + r;  // the running sum of the tile's first super-blocks
-#pragma unroll
-                        for (int m = 0; m < MR; m++) {
-                            if (m < a.rows) {
-                                dst[m * ROWS] = acc[m];
-                            }
-                        }
+            if (b == we.e - 1) {
+                // the CTA's part of the tile is done
+                if (we.e == KB) {
+                    if (!aside) {
+                        write_tile(t, acc);
                     }
-                    __threadfence();
-                    epilogue_barrier();
-                    if (et == 0) {
-                        const int c_first = (int)((((int64_t)t * KB + 1) * G - 1) / U), c_last = (int)((((int64_t)(t + 1) * KB) * G - 1) / U);
-                        const int done = atomicAdd(a.counters + t, 1);
-                        const int last = done == c_last - c_first;
-                        if (last) {
-                            a.counters[t] = 0;
-                        }
-                        fin[0] = last;
-                        fin[1] = c_first;
-                        fin[2] = c_last;
-                    }
-                    epilogue_barrier();
-                    if (fin[0] != 0) {
-                        // every piece of the tile is in the scratch: add them in k order
-                        __threadfence();
-                        const int c_first = fin[1], c_last = fin[2];
+                } else {
+                    if (part_b0 == 0) {
+                        unsigned long long* dst = my_slot + (size_t)m0 * ROWS + r;  // the running sum of the tile's first super-blocks
 #pragma unroll
-                        for (int m = 0; m < MR; m++) {
-                            acc[m] = 0.0f;
-                        }
-                        for (int cta = c_first; cta <= c_last; cta++) {
-                            const int64_t lo = (int64_t)cta * U / G, hi = ((int64_t)cta + 1) * U / G, tb = (int64_t)t * KB;
-                            const int s0 = (int)((lo > tb ? lo : tb) - tb), s1 = (int)((hi < tb + KB ? hi : tb + KB) - tb);
-                            const float* slot = a.partial + (size_t)cta * slot_floats + r;
-                            if (s0 == 0) {
-#pragma unroll
-                                for (int m = 0; m < MR; m++) {
-                                    if (m < a.rows) {
-                                        acc[m] = __ldcg(slot + ((size_t)a.max_pieces * a.rows + m) * ROWS);
-                                    }
-                                }
-                            } else {
-                                for (int p = 0; p < s1 - s0; p++) {
-#pragma unroll
-                                    for (int m = 0; m < MR; m++) {
-                                        if (m < a.rows) {
-                                            acc[m] += __ldcg(slot + ((size_t)p * a.rows + m) * ROWS);
-                                        }
-                                    }
-                                }
-                            }
-                        }
-                        write = true;
-                    }
-                }
-                if (write && row < n) {
-                    const float bv = (a.bias != nullptr && !second) ? a.bias[row] : 0.0f;
-#pragma unroll
-                    for (int m = 0; m < MR; m++) {
-                        if (m < a.rows) {
-                            const float val = acc[m] + bv;
-                            if constexpr (!PEER) {
-                                yo[(int64_t)m * n + row] = val;
-                            } else {
-                                // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
-                                for (int rk = 0; rk < a.peer->world; rk++) {
-                                    a.peer->y[rk][(int64_t)m * a.peer->n_total + a.peer->col0 + row] = val;
-                                }
+                        for (int m = 0; m < HM; m++) {
+                            if (m0 + m < a.rows) {
+                                handoff_store(dst + m * ROWS, acc[m]);
                             }
                         }
                     }
                 }
 #pragma unroll
-                for (int m = 0; m < MR; m++) {
+                for (int m = 0; m < HM; m++) {
                     acc[m] = 0.0f;
                 }
-                piecewise = false;
-                piece_b0 = 0;
             }
+            if (warp == 6) TR(3, i, 3);
             xr.next(SX);
             pr.next(SP);
-            if (++b == KB) {
-                b = 0;
-                t++;
+            we.next();
+            if (we.t != t) {
+                part_b0 = we.b;
+            }
+        }
+        if (ok && late_tile >= 0) {
+            // the tile whose end this CTA computed and kept aside: the other CTAs' sums first, then its own contributions, in k order
+            ok = gather(late_tile, acc);
+            if (ok) {
+                const float* own = my_aside + (size_t)m0 * ROWS + r;
+                for (int q0 = 0; q0 < late_len; q0 += 8) {
+#pragma unroll
+                    for (int m = 0; m < HM; m++) {
+                        if (m0 + m < a.rows) {
+                            float v[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                v[q] = q0 + q < late_len ? __ldcg(own + ((size_t)(q0 + q) * a.rows + m) * ROWS) : 0.0f;
+                            }
+#pragma unroll
+                            for (int q = 0; q < 8; q++) {
+                                if (q0 + q < late_len) {
+                                    acc[m] += v[q];
+                                }
+                            }
+                        }
+                    }
+                }
+                write_tile(late_tile, acc);
             }
         }
     }
+    if (warp == 6 && lane == 0) CT(4);
     // ---- common exit: everyone arrives, copies in flight get a bounded time to land after an abort, tensor memory is released ----
     tc::fence_before_sync();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0) {
-        for (int s = 0; s < SW + SX; s++) {
+        for (int s = 0; s < SW + (RES ? 0 : SX); s++) {
             const uint32_t bar = s < SW ? full_w(s) : full_x(s - SW);
             for (uint32_t p = 0; p < (1u << 14); p++) {
                 if (tc::mbar_try(bar, 0) || tc::mbar_try(bar, 1)) {
@@ -726,7 +1021,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
     if constexpr (PEER) {
-        peer_publish(a.peer->flags, a.peer->rank, a.peer->world, const_cast<int*>(fin));  // the last CTA raises this rank's flag on every rank
+        peer_publish(a.peer->flags, a.peer->rank, a.peer->world, const_cast<int*>(fin_all));  // the last CTA raises this rank's flag on every rank
     }
 }
 
@@ -741,18 +1036,18 @@ int sm_count_of_current_device() {
     return v;
 }
 
-template <int TYPE, int MR, bool PEER>
+template <int TYPE, int MR, bool PEER, bool RES>
 int launch_typed(const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_umma_kernel<TYPE, MR, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_umma_kernel<TYPE, MR, PEER, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(Roles<MR>::THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -760,20 +1055,27 @@ int launch_typed(const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_umma_kernel<TYPE, MR, PEER>, a));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_umma_kernel<TYPE, MR, PEER, RES>, a));
     count_launch();
     return JQ_OK;
 }
 
 template <int TYPE, bool PEER>
-int by_rows(int mr, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+int by_rows(int mr, bool resident, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
+    if (resident) {
+        switch (mr) {
+            case 1: return launch_typed<TYPE, 1, PEER, true>(a, grid, smem, s);
+            case 2: return launch_typed<TYPE, 2, PEER, true>(a, grid, smem, s);
+            default: return launch_typed<TYPE, 5, PEER, true>(a, grid, smem, s);
+        }
+    }
     switch (mr) {
-        case 1: return launch_typed<TYPE, 1, PEER>(a, grid, smem, s);
-        case 2: return launch_typed<TYPE, 2, PEER>(a, grid, smem, s);
-        case 5: return launch_typed<TYPE, 5, PEER>(a, grid, smem, s);
-        case 8: return launch_typed<TYPE, 8, PEER>(a, grid, smem, s);
-        case 10: return launch_typed<TYPE, 10, PEER>(a, grid, smem, s);
-        default: return launch_typed<TYPE, 16, PEER>(a, grid, smem, s);
+        case 1: return launch_typed<TYPE, 1, PEER, false>(a, grid, smem, s);
+        case 2: return launch_typed<TYPE, 2, PEER, false>(a, grid, smem, s);
+        case 5: return launch_typed<TYPE, 5, PEER, false>(a, grid, smem, s);
+        case 8: return launch_typed<TYPE, 8, PEER, false>(a, grid, smem, s);
+        case 10: return launch_typed<TYPE, 10, PEER, false>(a, grid, smem, s);
+        default: return launch_typed<TYPE, 16, PEER, false>(a, grid, smem, s);
     }
 }
 
@@ -822,13 +1124,16 @@ int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, 
     }
 }
 
-// y [rows, n] = x . W^T (+ bias) for a Q4_K or Q5_K weight and 1 to 16 rows of x whose image is in `image` (written earlier
-// in the stream). With v2 != nullptr the rows of a second weight of the same type and k follow in the same launch
-// (results in y2, no bias). `peer`: the outputs go into every rank's y of a row-sharded linear instead.
+// y [rows, n] = x . W^T (+ bias) for a Q4_K or Q5_K weight and 1 to 16 rows of x. Either x is given (FP32 [rows, k]; `image`
+// is then scratch of gemv_umma_image_bytes(k, rows) bytes that is used unless the kernel can keep the whole image in shared
+// memory), or x is nullptr and `image` already holds the activation image, written earlier in the stream.
+// With v2 != nullptr the rows of a second weight of the same type and k follow in the same launch (results in y2, no
+// bias). `peer`: the outputs go into every rank's y of a row-sharded linear instead.
 // no_scratch: deal whole tiles to the CTAs, which needs no scratch buffers (and balances the load worse).
-int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
+int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
                      const PeerOut* peer, bool no_scratch) {
-    if (!shape_ok(v.type, v.k, rows) || v.n <= 0 || (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
+    if (!shape_ok(v.type, v.k, rows) || v.n <= 0 || (x == nullptr && image == nullptr) ||
+        (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
         return fail(JQ_ERR_UNSUPPORTED, "decode GEMV: type %d, k = %lld, %d rows is outside what the tcgen05 kernel takes", v.type, (long long)v.k, rows);
     }
     const int bb = v.type == JQ_TYPE_Q4_K ? 144 : 176;
@@ -859,33 +1164,53 @@ int launch_gemv_umma(const View& v, const View* v2, const uint8_t* image, int ro
     }
     const size_t xb = (umma::image_block_bytes(ncols) + 127) & ~(size_t)127;
     a.SX = ncols <= 16 ? 8 : (ncols == 32 ? 6 : 5);
-    const size_t fixed = 128 + a.SX * xb + SP * P_BYTES + 1024;
-    int sw = (int)((SMEM_MAX - fixed) / ((size_t)ROWS * bb));
-    a.SW = sw > MAX_SW ? MAX_SW : sw;
-    const size_t smem = fixed + (size_t)a.SW * ROWS * bb;
-    a.poll_limit = (uint32_t)g_opt_wait_poll_limit.load(std::memory_order_relaxed);
-    a.lbo = (uint32_t)(ncols / 8) * 128u;
-    a.sbo = 128u;
-    a.peer = peer != nullptr ? peer->table : nullptr;
-    uint8_t* partial = nullptr;
-    uint8_t* counters = nullptr;
-    if (!no_scratch) {
-        rc = scratch_for_slot(s, 2, (size_t)grid * (a.max_pieces + 1) * rows * ROWS * sizeof(float), &partial);
-        if (rc == JQ_OK) {
-            rc = scratch_zeroed_for_slot(s, 3, (size_t)a.tiles * sizeof(int), &counters);
+    // Few rows of x and a k whose whole image fits beside the weight ring: the kernel builds the image itself in shared memory
+    // (no image kernel, no trip of the image through global memory).
+    const bool resident = x != nullptr && ncols <= 16 && (size_t)a.KB * xb <= RESIDENT_MAX;
+    if (x != nullptr && !resident) {
+        if (image == nullptr) {
+            return fail(JQ_ERR_INVALID, "decode GEMV: no scratch for the activation image");
         }
+        rc = launch_gemv_umma_image(x, rows, v.k, image, s);
         if (rc != JQ_OK) {
             return rc;
         }
     }
-    a.partial = reinterpret_cast<float*>(partial);
-    a.counters = reinterpret_cast<int*>(counters);
-    if (v.type == JQ_TYPE_Q4_K) {
-        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, a, grid, smem, s);
+    a.x = x;
+    const size_t fixed = 128 + (resident ? (size_t)a.KB : (size_t)a.SX) * xb + SP * P_BYTES + 1024;
+    int sw = (int)((SMEM_MAX - fixed) / ((size_t)ROWS * bb));
+    a.SW = sw > MAX_SW ? MAX_SW : sw;
+    const size_t smem = fixed + (size_t)a.SW * ROWS * bb;
+    a.wait_clocks = g_opt_wait_limit_us.load(std::memory_order_relaxed) * 2000;  // about 2 GHz
+    a.lbo = (uint32_t)(ncols / 8) * 128u;
+    a.sbo = 128u;
+    a.peer = peer != nullptr ? peer->table : nullptr;
+    uint8_t* partial = nullptr;
+    if (!no_scratch) {
+        const size_t words = (size_t)grid * a.max_pieces * rows * ROWS;
+        rc = scratch_zeroed_for_slot(s, 2, words * (sizeof(unsigned long long) + sizeof(float)), &partial);
+        if (rc != JQ_OK) {
+            return rc;
+        }
     }
-    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, a, grid, smem, s);
+    a.partial = reinterpret_cast<unsigned long long*>(partial);
+    a.aside = reinterpret_cast<float*>(a.partial + (size_t)grid * a.max_pieces * rows * ROWS);
+    if (v.type == JQ_TYPE_Q4_K) {
+        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, resident, a, grid, smem, s);
+    }
+    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, resident, a, grid, smem, s);
 }
 
+#ifdef JQ_UMMA_TRACE
+}  // namespace jq
+extern "C" JQ_API int jq_debug_umma_trace(long long* out) {
+    return cudaMemcpyFromSymbol(out, jq::g_umma_trace, sizeof(jq::g_umma_trace)) == cudaSuccess ? 0 : -3;
+}
+extern "C" JQ_API int jq_debug_umma_cta(long long* out) {
+    return cudaMemcpyFromSymbol(out, jq::g_umma_cta, sizeof(jq::g_umma_cta)) == cudaSuccess ? 0 : -3;
+}
+namespace jq {
+#endif
 // Reads and clears the status words of the tcgen05 GEMV on the current device (0 = no wait ever gave up).
 int gemv_umma_status(int* status) {
     const int zero = 0;
@@ -973,10 +1298,7 @@ extern "C" JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float*
     int rc = noalloc_scratch_address(w->device, &image);
     if (rc == JQ_OK) {
         const jq::View v{w->q, w->aux, w->n, w->k, w->type};
-        rc = jq::launch_gemv_umma_image(x, (int)m, w->k, image, (cudaStream_t)stream);
-        if (rc == JQ_OK) {
-            rc = jq::launch_gemv_umma(v, nullptr, image, (int)m, bias, y, nullptr, (cudaStream_t)stream, nullptr, true);
-        }
+        rc = jq::launch_gemv_umma(v, nullptr, x, image, (int)m, bias, y, nullptr, (cudaStream_t)stream, nullptr, true);
     }
     if (prev >= 0 && prev != w->device) {
         cudaSetDevice(prev);

@@ -279,7 +279,7 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
     rc = device_table(po, s, &po.table);
     if (rc == JQ_OK) {
         const View v{w->q, w->aux, w->n, w->k, w->type};
-        rc = launch_gemv_umma(v, nullptr, image, 1, nullptr, nullptr, nullptr, s, &po);
+        rc = launch_gemv_umma(v, nullptr, nullptr, const_cast<uint8_t*>(image), 1, nullptr, nullptr, nullptr, s, &po);
     }
     if (rc == JQ_OK && wait_after) {
         rc = enqueue_wait(tg, rank, world, s);
@@ -335,8 +335,7 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
         rc = device_table(po, s, &po.table);
         uint8_t* image = nullptr;
         if (rc == JQ_OK) rc = scratch_for(s, gemv_umma_image_bytes(w->k, (int)m), &image);
-        if (rc == JQ_OK) rc = launch_gemv_umma_image(x, (int)m, w->k, image, s);
-        if (rc == JQ_OK) rc = launch_gemv_umma(v, nullptr, image, (int)m, bias, nullptr, nullptr, s, &po);
+        if (rc == JQ_OK) rc = launch_gemv_umma(v, nullptr, x, image, (int)m, bias, nullptr, nullptr, s, &po);
         fused = rc == JQ_OK;
     }
     if (rc == JQ_OK && !fused) {

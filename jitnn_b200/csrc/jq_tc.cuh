@@ -41,20 +41,27 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Waits for the phase with the given parity. Gives up after `limit` polls, or earlier when another role of the CTA has
-// given up (abort flag in shared memory); the first wait that runs out records `code` in *status (global memory).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, uint32_t limit) {
-    for (uint32_t i = 0; i < limit; i++) {
+// Waits for the phase with the given parity, for at most `limit` clocks of the SM (a poll may suspend the thread for a time the
+// hardware chooses, so the bound counts time, not polls). Gives up earlier when another role of the CTA has given up (abort
+// flag in shared memory); the first wait that runs out records `code` in *status (global memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code, long long limit) {
+    if (mbar_try(bar, parity)) {
+        return true;
+    }
+    const long long t0 = clock64();
+    for (;;) {
         if (mbar_try(bar, parity)) {
             return true;
         }
-        if ((i & 255u) == 255u && *abort_flag != 0) {
+        if (*abort_flag != 0) {
+            return false;
+        }
+        if (clock64() - t0 > limit) {
+            atomicCAS(status, 0, code);
+            *abort_flag = 1;
             return false;
         }
     }
-    atomicCAS(status, 0, code);
-    *abort_flag = 1;
-    return false;
 }
 
 // One contiguous run of bytes (a multiple of 16, both addresses 16-byte aligned) from global into shared memory.

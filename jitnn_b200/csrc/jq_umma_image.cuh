@@ -40,13 +40,18 @@ __host__ __device__ constexpr size_t image_block_bytes(int n_cols) {
 // One warp turns the 256 values at xb (super-block b of row m of x) into its part of the image block `img` (global or
 // shared memory). lane = 4 sub + tt: elements 8 tt .. 8 tt + 7 of sub-block `sub`. The warp of row 0 also clears the
 // columns and aux entries of rows >= rows, so a block is complete once the warps of rows 0 .. rows - 1 have run.
+// This lane's eight values of the super-block at xb.
+__device__ __forceinline__ void load_lane_values(const float* xb, int lane, float4& lo, float4& hi) {
+    const float4* xp = reinterpret_cast<const float4*>(xb) + 2 * lane;
+    lo = xp[0];
+    hi = xp[1];
+}
+
 template <int N>
-__device__ __forceinline__ void build_image(const float* xb, int m, int rows, uint8_t* img, int lane) {
+__device__ __forceinline__ void build_image_from(const float4& lo, const float4& hi, int m, int rows, uint8_t* img, int lane) {
     using C = ImageCfg<N>;
     const int sub = lane >> 2, tt = lane & 3;
     float* aux = reinterpret_cast<float*>(img + C::XD);
-    const float4* xp = reinterpret_cast<const float4*>(xb) + 2 * lane;
-    const float4 lo = xp[0], hi = xp[1];
     const float xv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     float am = 0.0f;
     bool bad = false;
@@ -108,6 +113,13 @@ __device__ __forceinline__ void build_image(const float* xb, int m, int rows, ui
             }
         }
     }
+}
+
+template <int N>
+__device__ __forceinline__ void build_image(const float* xb, int m, int rows, uint8_t* img, int lane) {
+    float4 lo, hi;
+    load_lane_values(xb, lane, lo, hi);
+    build_image_from<N>(lo, hi, m, rows, img, lane);
 }
 
 }  // namespace umma
