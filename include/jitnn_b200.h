@@ -207,7 +207,9 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "decoder_graph"     zero: the decoder issues its single-token step kernel by kernel instead of replaying a CUDA graph.
  *   "decoder_fused"     zero: the decoder's single-token step uses the general kernels (one per operator) instead of the
  *                       fused ones that hand activations to the next linear as its activation image.
- *   "gemv_tcgen05"      zero: Q4_K and Q5_K decode GEMVs run on the generic kernel instead of the tcgen05 one (for comparisons).
+ *   "gemv_tcgen05"      non-zero: Q4_K and Q5_K decode GEMVs (1 to 16 rows in one pass over the weights) run on the tcgen05
+ *                       kernel instead of the mma.sync one (which takes up to 8 rows per pass and is the faster of the two
+ *                       on every measured shape, hence the default).
  *   "wait_limit_us"     microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up (default 2 000 000; a
  *                       wait that gives up makes jq_device_status report 64 + the waiting role, and the outputs of that call
  *                       are undefined).
@@ -216,19 +218,17 @@ JQ_API int jq_set_option(const char* name, int64_t value);
 JQ_API int jq_get_option(const char* name, int64_t* value);
 
 /*
- * y[m, n] = x[m, k] * W^T (+ bias[n]) for a Q4_K weight, 1 <= m <= 16, device pointers only (16-byte aligned),
+ * y[m, n] = x[m, k] * W^T (+ bias[n]) for a Q4_K weight, 1 <= m <= 8, device pointers only (16-byte aligned),
  * enqueued on `stream`: the same kernels and bit for bit the same results as jq_linear_f32, but the call allocates
- * no memory. It has no counterpart in the reference. jq_linear_f32 keeps its intermediate data (the "activation
- * image" of x, and partial sums of weight tiles that several thread blocks share) in buffers it allocates with
- * cudaMalloc when a stream first needs them; this entry point is for callers that cannot have that happen: a
- * process that has already given all device memory to its own pools (the allocation would fail), or a
- * latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives in a 1 MiB array that
- * is part of the library itself, so every GPU that loads the library holds that 1 MiB until the process exits, and
- * the thread blocks are dealt whole tiles of 128 weight rows, which needs no partial sums (and is slower than
- * jq_linear_f32 for weights of few rows). Limits: the image, (k / 256) * 2192 bytes for one or two rows of x, 4384
- * for three to five, 8624 for six to ten and 12864 for eleven to sixteen rows, must fit 1 MiB (for example
- * k <= 20736 at sixteen rows); anything larger and any other row count is refused with JQ_ERR_INVALID, any other
- * format with JQ_ERR_UNSUPPORTED, both with a message.
+ * no memory. It has no counterpart in the reference. jq_linear_f32 keeps its intermediate "activation image" in a
+ * buffer it allocates with cudaMalloc when a stream first needs one; this entry point is for callers that
+ * cannot have that happen: a process that has already given all device memory to its own pools (the allocation
+ * would fail), or a latency-bound loop that must not meet cudaMalloc's device-wide wait. Here the image lives
+ * in a 1 MiB array that is part of the library itself, so every GPU that loads the library holds that 1 MiB
+ * until the process exits. Limits: the image, (k / 256) * 928 bytes for one row, 1856 for two and 7008 for three to
+ * eight rows, must fit 1 MiB (for example k <= 38144 at eight rows); anything larger and any other row count is
+ * refused with JQ_ERR_INVALID, any other format, and a shape whose carried sums do not fit the kernel's shared
+ * memory (which jq_linear_f32 would hand to its generic kernel), with JQ_ERR_UNSUPPORTED, all with a message.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call before starting any stream capture. All calls share the one array, which keeps
  * whatever the last call left in it; every call rewrites the part it reads, nothing has to start at zero.

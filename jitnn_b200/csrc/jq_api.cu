@@ -206,12 +206,15 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
         }
         return rc;
     }
-    // The tcgen05 kernel of Q4_K and Q5_K takes up to 16 activation rows per pass, Q6_K's integer kernel 4, the generic kernel 16.
+    // The integer tensor-core kernel of Q4_K and Q5_K takes up to 8 activation rows per pass (the tcgen05 one, if selected, 16),
+    // Q6_K's 4, the generic kernel 16.
     const bool tc = g_opt_gemv_generic.load() == 0;
     // Q8_0, Q4_0 and Q4_1 (k a multiple of 256) go two rows at a time through their tensor-core kernel: re-reading the weights
     // (mostly from L2) per pair of rows is far cheaper than the generic kernel's arithmetic.
     const bool blk32 = tc && gemv_blk32_i8_scratch_bytes(w->type, w->k, 2) > 0;
-    const int64_t group = gemv_umma_takes(w->type, w->k, 16) ? 16 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16));
+    const int64_t group = gemv_umma_takes(w->type, w->k, 16)
+                              ? 16
+                              : ((tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16)));
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
@@ -661,9 +664,9 @@ int jq_device_status(int device, int* status) {
     if (rc == JQ_OK && *status == 0) {
         *status = peer;
     }
-    for (int part = 0; part < 2 && rc == JQ_OK; part++) {
+    for (int part = 0; part < 3 && rc == JQ_OK; part++) {
         int other = 0;
-        rc = part == 0 ? decoder_peer_status(&other) : gemv_umma_status(&other);
+        rc = part == 0 ? gemv_peer_status(&other) : (part == 1 ? decoder_peer_status(&other) : gemv_umma_status(&other));
         if (rc == JQ_OK && *status == 0) {
             *status = other;
         }

@@ -123,6 +123,18 @@ struct PeerOut {
     const PeerOut* table;   // host side only: where a copy of this struct lives in device memory
     int wait_first;         // the kernel's input is what this rank's latest exchange delivered: wait for all ranks' flags before reading it
 };
+// Integer tensor-core GEMV (mma.sync) for Q4_K and Q5_K, rows <= 8 (jq_gemv_q4k_i8.cu); *handled = false leaves the call to
+// another kernel. `image` is scratch of gemv_q4k_i8_scratch_bytes(k, rows) bytes.
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
+                       const PeerOut* peer = nullptr);
+size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
+// The same for one row of x whose activation image (jq_q4k_image.cuh) a kernel earlier in the stream has already written; a
+// second Q4_K weight with the same k can ride in the same launch.
+size_t q4k_image_bytes_one_row(int64_t k);
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
+                              const PeerOut* peer = nullptr);
+// Status word of the waits a GEMV makes itself for a peer exchange (peer_wait_inline): 0 or 32 + rank, cleared by the call.
+int gemv_peer_status(int* status);
 // Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
 // rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
@@ -158,7 +170,7 @@ int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, 
 int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
                      const PeerOut* peer = nullptr, bool no_scratch = false);
 int gemv_umma_status(int* status);
-// Option "gemv_tcgen05": zero keeps Q4_K and Q5_K decode on the mma.sync kernels (for comparisons).
+// Option "gemv_tcgen05": non-zero sends Q4_K and Q5_K decode (1 to 16 rows) to the tcgen05 kernel instead of the mma.sync one.
 extern std::atomic<int64_t> g_opt_gemv_umma;
 // Option "wait_limit_us": microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up.
 extern std::atomic<int64_t> g_opt_wait_limit_us;

@@ -13,7 +13,7 @@
 #include <vector>
 
 #include "jq_common.cuh"
-#include "jq_umma_image.cuh"
+#include "jq_q4k_image.cuh"
 #include "jq_q6k_image.cuh"
 #include "jq_peer_device.cuh"
 
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 
 // ---- the single-token step with fewer, fused kernels --------------------------------------------------------------
 // For one token and Q4_K / Q6_K linears the kernels that produce an activation vector (norm, attention, SwiGLU) write
-// it straight as the activation image the integer GEMV kernels read (jq_umma_image.cuh, jq_q6k_image.cuh): no float
+// it straight as the activation image the integer GEMV kernels read (jq_q4k_image.cuh, jq_q6k_image.cuh): no float
 // vector and no separate image kernel in between. Every kernel of the step starts with griddepcontrol.wait (all that
 // the kernel before it wrote is visible from there on) followed by griddepcontrol.launch_dependents (the next kernel
 // may be scheduled and, if it is a GEMV, start requesting its weights), and does not touch global memory before.
@@ -344,7 +344,7 @@ struct Images {
 
 __device__ __forceinline__ void write_images(const float* block, int b, const Images& im, int lane) {
     if (im.q4k != nullptr) {
-        umma::build_image<8>(block, 0, 1, im.q4k + (size_t)b * umma::ImageCfg<8>::BYTES, lane);
+        q4k::build_image<1>(block, 0, im.q4k + (size_t)b * q4k::Cfg<1>::PB, lane);
     }
     if (im.q6k != nullptr) {
         q6k::build_image<1>(block, 0, im.q6k + (size_t)b * q6k::Cfg<1>::PB, lane);
@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     if (warp == 0) {
         if constexpr (PEER) {
             write_images(outs, pi.first_block + sb, im, lane);
-            peer_copy_block(pi, (size_t)(pi.first_block + sb) * umma::ImageCfg<8>::BYTES, (int)umma::ImageCfg<8>::BYTES, lane);
+            peer_copy_block(pi, (size_t)(pi.first_block + sb) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, lane);
         } else {
             write_images(outs, sb, im, lane);
         }
@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restri
     if (threadIdx.x < 32) {
         if constexpr (PEER) {
             write_images(xs, pi.first_block + (int)blockIdx.x, im, threadIdx.x);
-            peer_copy_block(pi, (size_t)(pi.first_block + (int)blockIdx.x) * umma::ImageCfg<8>::BYTES, (int)umma::ImageCfg<8>::BYTES, threadIdx.x);
+            peer_copy_block(pi, (size_t)(pi.first_block + (int)blockIdx.x) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, threadIdx.x);
         } else {
             write_images(xs, blockIdx.x, im, threadIdx.x);
         }
@@ -902,9 +902,9 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
             off += ((int64_t)MAX_TOKENS * widths[i] * (int64_t)sizeof(float) + 255) / 256 * 256;
         }
         d->area[5] = off;
-        off += ((int64_t)gemv_umma_image_bytes_one_row(dim) + 511) / 256 * 256;
+        off += ((int64_t)q4k_image_bytes_one_row(dim) + 511) / 256 * 256;
         d->area[6] = off;
-        off += ((int64_t)gemv_umma_image_bytes_one_row(hidden) + 511) / 256 * 256;
+        off += ((int64_t)q4k_image_bytes_one_row(hidden) + 511) / 256 * 256;
         d->area[7] = off;
     }
     const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
@@ -937,7 +937,7 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     {
         const int64_t kmax = dim > hidden ? dim : hidden;
         const size_t ncount = (size_t)(dim / 256 + 2);
-        if (e == cudaSuccess) e = cudaMalloc(&d->img_q4k, gemv_umma_image_bytes_one_row(kmax) + 256);
+        if (e == cudaSuccess) e = cudaMalloc(&d->img_q4k, q4k_image_bytes_one_row(kmax) + 256);
         if (e == cudaSuccess) e = cudaMalloc(&d->img_q6k, q6k_image_bytes_one_row(kmax) + 256);
         if (e == cudaSuccess) e = cudaMalloc(&d->counters, ncount * sizeof(int));
         if (e == cudaSuccess) e = cudaMemset(d->counters, 0, ncount * sizeof(int));
@@ -1132,12 +1132,10 @@ static int decoder_gemv_imaged(jq_decoder* d, const jq_weight* w, float* y, cons
         if (cur->type == JQ_TYPE_Q4_K) {
             if (pass == 0 && w2 != nullptr && w2->type == JQ_TYPE_Q4_K) {
                 const View v2{w2->q, w2->aux, w2->n, w2->k, w2->type};
-                rc = launch_gemv_umma(v, &v2, nullptr, d->img_q4k, 1, nullptr, y, y2, gs);
-                handled = true;
+                rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, gs, &handled);
                 pass = 1;  // both done
             } else {
-                rc = launch_gemv_umma(v, nullptr, nullptr, d->img_q4k, 1, nullptr, out_, nullptr, gs);
-                handled = true;
+                rc = launch_gemv_q4k_i8_imaged(v, nullptr, d->img_q4k, nullptr, out_, nullptr, gs, &handled);
             }
         } else {
             rc = launch_gemv_q6k_i8_imaged(v, d->img_q6k, nullptr, out_, gs, &handled);
@@ -1627,7 +1625,7 @@ static int decoder_forward(jq_decoder* d, int seq, bool batch, const int32_t* to
         if (rc == JQ_OK && d->world > 1) {
             int status = 0, part = 0;
             rc = peer_status(&status);
-            if (rc == JQ_OK) rc = gemv_umma_status(&part);
+            if (rc == JQ_OK) rc = gemv_peer_status(&part);
             status = status != 0 ? status : part;
             if (rc == JQ_OK) rc = decoder_peer_status(&part);
             status = status != 0 ? status : part;

@@ -98,6 +98,18 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
         int rc = scratch_for(s, gemv_umma_image_bytes(v.k, rows), &image);
         return rc == JQ_OK ? launch_gemv_umma(v, nullptr, x, image, rows, bias, y, nullptr, s) : rc;
     }
+    if ((v.type == JQ_TYPE_Q4_K || v.type == JQ_TYPE_Q5_K) && rows <= 8 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
+        bool handled = false;
+        const size_t need = gemv_q4k_i8_scratch_bytes(v.k, rows);
+        uint8_t* image = nullptr;
+        int rc = need > 0 ? scratch_for(s, need, &image) : JQ_OK;
+        if (rc == JQ_OK) {
+            rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, image, &handled);
+        }
+        if (rc != JQ_OK || handled) {
+            return rc;
+        }
+    }
     if (v.type == JQ_TYPE_Q6_K && rows <= 4 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {
         bool handled = false;
         const size_t need = gemv_q6k_i8_scratch_bytes(v.k, rows);

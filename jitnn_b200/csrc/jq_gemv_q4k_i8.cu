@@ -1,0 +1,760 @@
+// Decode GEMV for Q4_K with integer tensor-core arithmetic: y[m, n] = x[m, k] . W[n, k]^T, m <= 8.
+//
+// The 4-bit quants never become floating point. A small first kernel turns the activations into an
+// "activation image" in a scratch buffer: per 256-element super-block of k and per row of x, the values
+// are scaled by a power of two s (from the block's largest magnitude), rounded to 22-bit fixed point,
+// X = rint(x / s * 2^21), and split into three signed base-256 digits X = d2 * 65536 + d1 * 256 + d0.
+// The digits are laid out as B fragments of mma.sync.m16n8k32 (u8 x s8 -> s32), one column per (row of x, digit);
+// the fragments of two sub-blocks sit side by side, so one 16-byte load feeds two MMAs. The GEMV kernel widens four
+// nibbles to four bytes with one AND and feeds them as the A operand, so one MMA multiplies one 32-element sub-block
+// of 16 weight rows with every digit column exactly. Sub-block results are combined with the 6-bit scales in integer
+// arithmetic (sum over 8 sub-blocks of sc * D stays below 2^31), converted to float once per super-block and scaled
+// by fp16 d and the column weight s * 2^(8i - 21). The "min" part of Q4_K, dmin * sum_sub m_sub * sum(x over the
+// sub-block), uses one m16n8k16 MMA whose A operand is the eight packed 6-bit mins and whose B operand holds the
+// digit sums of every sub-block. Everything up to the per-super-block float conversion is exact and x keeps 22 bits
+// relative to the largest magnitude of its super-block, so results match an FP32-accumulating kernel. The summation
+// order depends on k and the number of rows of x only: a row shard of a weight gives bitwise the same outputs as the
+// whole weight.
+//
+// Two column layouts (struct Cfg). One or two rows of x: column 3m + i of a single group; the three digit columns of
+// a row sit in different lanes and are combined by shuffles once per tile; the high nibbles are masked in place
+// (no shift) and their 16-fold products summed apart. Three to eight rows: digit i is column group i and row m its
+// column m, which puts all digits of rows 2t and 2t + 1 into lane t: no exchange between lanes at all.
+//
+// Work split: a CTA of 8 warps (16 for three to eight rows of x, where one CTA per SM shares one copy of the large
+// image) owns 16 output rows at a time (tiles blockIdx.x, blockIdx.x + gridDim.x, ...), warp p takes super-blocks
+// b = p (mod warps). Weights stream HBM -> shared memory through a per-warp ring of cp.async slots; consecutive lanes
+// copy consecutive 16-byte chunks, so every 32-byte sector is requested once, and the slot layout is swizzled so that
+// the 8-byte fragment reads are conflict free. The weight buffer is padded by 16 rows, which lets the last tile read
+// past n without a bounds check (the tiled layout pads the last 128 rows with zeros). The GEMV kernel is launched with programmatic stream serialization: it requests its
+// first weights while the activation kernel is still running and waits for it (griddepcontrol.wait) only before
+// copying the image into shared memory.
+#include <mutex>
+
+#include "jq_formats.cuh"
+#include "jq_peer_device.cuh"
+#include "jq_q4k_image.cuh"
+
+namespace jq {
+
+using q4k::Cfg;
+using q4k::build_image;
+
+namespace {
+
+// One super-block of 16 rows in a ring slot: 16 x 128 bytes of nibbles, then the 16 headers, then (Q5_K) 16 x 32 bytes of
+// fifth bits. The kernel is written for Q4_K; Q5_K (template flag Q5) is the same format with one more bit per quant.
+constexpr int SLOT_HEADERS = 16 * 128;
+constexpr int SLOT_QH = 16 * 144;
+template <bool Q5>
+struct Blk {
+    static constexpr int BYTES = Q5 ? 176 : 144;           // bytes per super-block and row
+    static constexpr int SLOT = 16 * BYTES;
+    static constexpr int CPR = BYTES / 16;                 // 16-byte chunks per row
+    static constexpr int PER_LANE = (16 * CPR + 31) / 32;  // the last one only by lanes 0-15
+};
+constexpr size_t SMEM_MAX = 227 * 1024;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+// The same copy under a predicate, without a branch around it.
+__device__ __forceinline__ void cp_async16_if(uint32_t dst_smem, const void* src, int on) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %2, 0;\n"
+        "@p cp.async.cg.shared.global [%0], [%1], 16;\n"
+        "}\n" ::"r"(dst_smem),
+        "l"(src), "r"(on)
+        : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// D = A(16x32 u8) * B(32x8 s8), accumulators start at zero.
+__device__ __forceinline__ void imma_k32(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// D = A(16x16 u8) * B(16x8 s8), accumulators start at zero.
+__device__ __forceinline__ void imma_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// The image in a scratch buffer in global memory, for the GEMV shapes that do not build it themselves. The kernel is
+// tiny and latency bound, so the work is spread over as many warps as possible.
+constexpr int PREP_WARPS = 4;
+__device__ int g_gemv_peer_status;  // 0, or 32 + rank once a GEMV's own wait for an exchange has given up
+
+template <int MT>
+__global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
+                                                                             uint8_t* __restrict__ image) {
+    asm volatile("griddepcontrol.launch_dependents;");  // the GEMV kernel may start requesting weights now
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x is complete, and the GEMV before this one is done with the scratch image
+    const int pair = blockIdx.x * PREP_WARPS + (threadIdx.x >> 5);
+    const int b = pair / MT, m = pair % MT;
+    if (b < (int)(k >> 8)) {
+        build_image<MT>(m < rows ? x + (int64_t)m * k + (int64_t)b * 256 : nullptr, m, image + (size_t)b * Cfg<MT>::PB, threadIdx.x & 31);
+    }
+}
+
+// ---- the GEMV ---------------------------------------------------------------------------------------------------
+// A second weight with the same k that is multiplied with the same x in the same launch (q = nullptr: none).
+struct Second {
+    const uint8_t* q;
+    int64_t n;
+    float* y;
+    int first_tiles;  // tiles of the first weight
+};
+
+// PEER: the outputs go into every rank's y of a row-sharded linear (jq_peer.cu) instead of y. A template flag, not a
+// run-time branch: the mere presence of the peer stores in the epilogue cost the ordinary kernel a fifth of its speed.
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const PeerOut* __restrict__ peerp, const uint8_t* __restrict__ image, int rows,
+                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles,
+                                                                  int KS, int max_tiles) {
+    // Tiles 0 .. w2.first_tiles - 1 are rows of v, the tiles from w2.first_tiles on rows of the second weight w2 (same k,
+    // same x, its own output), if there is one.
+    // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
+    // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
+    using C = Cfg<MT>;
+    constexpr int NG = C::NG, NCOL = C::NCOL, NGM = C::NGM, NCOLM = C::NCOLM;
+    constexpr int THREADS = NW * 32;
+    using B = Blk<Q5>;
+    constexpr int SLOT_BYTES = B::SLOT;
+    constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int KB = (int)(v.k >> 8);
+    const int nslices = (KB + KS - 1) / KS;
+    uint8_t* img = smem_raw;                                                         // [KS][PB]
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][NW][16][MT]
+    float* carry = red + 2 * NW * 16 * MT;                                           // [max_tiles][16][MT], only if nslices > 1
+    uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) + (size_t)warp * RING_BYTES;
+    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+    // The weight is stored tile by tile (jq_common.cuh): the 16 rows of a tile of this kernel and one super-block are 16 x BYTES
+    // consecutive bytes inside a unit of 128 rows, and the units of consecutive super-blocks follow each other.
+    constexpr int64_t UNIT = (int64_t)TILE_ROWS * B::BYTES;
+
+    // ---- weight stream: chunk c = lane + 32 i of the 144 (Q5_K: 176) chunks (16 rows x 9 or 11) of a super-block ------
+    // Slot layout: row r's 128 bytes of nibbles at r * 128 with its four 32-byte segments permuted by r & 3
+    // (segment p sits at position p ^ (r & 3)), the 16 headers behind them.
+    constexpr int NI = B::PER_LANE;
+    uint32_t dst_off[NI];
+#pragma unroll
+    for (int i = 0; i < NI; i++) {
+        const int c = lane + 32 * i, r = c / B::CPR, ch = c % B::CPR;
+        const int first_q = Q5 ? 3 : 1;  // chunk 0: header; Q5_K chunks 1, 2: fifth bits; then the 8 chunks of nibbles
+        dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
+                             : (ch < first_q ? (uint32_t)(SLOT_QH + r * 32 + (ch - 1) * 16)
+                                             : (uint32_t)(r * 128 + ((((ch - first_q) >> 1) ^ (r & 3)) << 5) + ((ch - first_q) & 1) * 16));
+    }
+    const int low16 = lane < 16;
+    // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + NW i.
+    const int len_last = KB - (nslices - 1) * KS;
+    const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + NW - 1) / NW : 0) : 0;
+    const int nb_last = warp < len_last ? (len_last - warp + NW - 1) / NW : 0;
+    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    // this lane's first chunk of tile number ti of the CTA, first block of this warp in slice sl
+    auto lane_ptr = [&](int ti, int sl) {
+        const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
+        const int local = tile < w2.first_tiles ? tile : tile - w2.first_tiles;
+        const uint8_t* base = tile < w2.first_tiles ? v.q : w2.q;
+        return base + ((int64_t)(local >> 3) * KB + (sl * KS + warp)) * UNIT + (local & 7) * 16 * B::BYTES + lane * 16;
+    };
+    const uint8_t* gp = lane_ptr(0, 0);
+    int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
+    int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
+    uint32_t iss_slot = 0;
+    auto issue = [&]() {
+        if (iss_left > 0) {
+            iss_left--;
+            const uint32_t slot = ring_s + iss_slot;
+#pragma unroll
+            for (int i = 0; i < NI - 1; i++) {
+                cp_async16(slot + dst_off[i], gp + 512 * i);
+            }
+            cp_async16_if(slot + dst_off[NI - 1], gp + 512 * (NI - 1), low16);
+            gp += NW * UNIT;
+            if (++iss_j == iss_nb) {
+                iss_j = 0;
+                if (++iss_ti == my_tiles) {
+                    iss_ti = 0;
+                    iss_sl++;
+                    iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
+                }
+                gp = lane_ptr(iss_ti, iss_sl);
+            }
+        }
+        iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; s++) {
+        issue();  // the first weights are on their way before the activation image is complete
+    }
+
+    // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+    if constexpr (PEER) {
+        if (peerp->wait_first) {
+            // the image is what the ranks' latest exchange delivered: complete once all their flags are up
+            if (warp == 0) {
+                peer_wait_inline(peerp->flags[peerp->rank], peerp->world, lane, &g_gemv_peer_status);
+            }
+            __syncthreads();
+        }
+    }
+
+    // ---- main loop ----------------------------------------------------------------------------------------------
+    // Lanes whose column is not stored read another lane's fragment; those columns have weight zero.
+    const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 16;
+    const uint8_t* xm_lane = img + C::XD + ((size_t)(NCOLM == 8 ? g : g % NCOLM) * 4 + t) * 4;
+    const uint8_t* tab_lane = img + C::XD + C::XM;
+    uint32_t qoff[4];  // this lane's 8 bytes of group j inside a row of the slot
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        qoff[j] = (uint32_t)(((j ^ (g & 3)) << 5) + 8 * t);
+    }
+    const bool mins_low = (t & 1) == 0;  // lanes t = 0, 2 feed mins 0..3, lanes 1, 3 mins 4..7 (slots 2, 3 meet zeros)
+    // Packed: acc[group][row g / g + 8][column 2t / 2t + 1] and accm[mins group][row]. Digit major: acc[0][row][row of x].
+    constexpr int NACC = C::DIGIT_MAJOR ? 1 : NG, NACCM = C::DIGIT_MAJOR ? 1 : NGM;
+    float acc[NACC][2][2];
+    float accm[NACCM][2];
+#pragma unroll
+    for (int i = 0; i < NACC; i++) {
+        acc[i][0][0] = acc[i][0][1] = acc[i][1][0] = acc[i][1][1] = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < NACCM; i++) {
+        accm[i][0] = accm[i][1] = 0.0f;
+    }
+
+    auto compute = [&](const uint8_t* slot, const uint8_t* blk) {  // blk = this lane's view of the super-block's image
+        const uint8_t* q0 = slot + g * 128;
+        const uint8_t* q1 = q0 + 8 * 128;
+        const uint4 h0 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + g * 16);
+        const uint4 h1 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + (g + 8) * 16);
+        // 6-bit scales and mins of the 8 sub-blocks as packed bytes: [0..3] and [4..7]
+        const uint32_t sc0a = h0.y & 0x3f3f3f3fu, sc0b = and_or(h0.y >> 2, 0x30303030u, h0.w & 0x0f0f0f0fu);
+        const uint32_t sc1a = h1.y & 0x3f3f3f3fu, sc1b = and_or(h1.y >> 2, 0x30303030u, h1.w & 0x0f0f0f0fu);
+        const uint32_t mn0 = mins_low ? (h0.z & 0x3f3f3f3fu) : and_or(h0.z >> 2, 0x30303030u, (h0.w >> 4) & 0x0f0f0f0fu);
+        const uint32_t mn1 = mins_low ? (h1.z & 0x3f3f3f3fu) : and_or(h1.z >> 2, 0x30303030u, (h1.w >> 4) & 0x0f0f0f0fu);
+        // Packed layouts keep the high nibbles in place (one AND, no shift): the odd sub-blocks' products come out 16 times
+        // too large, are summed apart from the even ones' and meet them as 16 even + odd; the column weights carry the 1 / 16.
+        constexpr bool SPLIT = !C::DIGIT_MAJOR && !Q5;
+        // Q5_K: the fifth bits of this lane's elements 8t .. 8t+7 of every sub-block, rows g and g + 8 (bit `sub` of each byte)
+        uint2 qh0 = make_uint2(0u, 0u), qh1 = make_uint2(0u, 0u);
+        if constexpr (Q5) {
+            qh0 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + g * 32 + 8 * t);
+            qh1 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + (g + 8) * 32 + 8 * t);
+        }
+        int I[NG][4], IO[SPLIT ? NG : 1][4];
+#pragma unroll
+        for (int i = 0; i < NG; i++) {
+            I[i][0] = I[i][1] = I[i][2] = I[i][3] = 0;
+        }
+#pragma unroll
+        for (int i = 0; i < (SPLIT ? NG : 1); i++) {
+            IO[i][0] = IO[i][1] = IO[i][2] = IO[i][3] = 0;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // this lane's 8 bytes of group j for rows g and g + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
+            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + qoff[j]);
+            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + qoff[j]);
+            uint4 bfp[NG];  // B operands of sub-blocks 2j (x, y) and 2j + 1 (z, w)
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                bfp[i] = *reinterpret_cast<const uint4*>(blk + (size_t)((j * NG + i) * NCOL) * 64);
+            }
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const int sub = 2 * j + hf;
+                const bool keep = SPLIT && hf == 1;  // high nibbles stay where they are
+                uint32_t a0 = keep ? wa.x & 0xf0f0f0f0u : (hf == 0 ? wa.x : wa.x >> 4) & 0x0f0f0f0fu;
+                uint32_t a2 = keep ? wa.y & 0xf0f0f0f0u : (hf == 0 ? wa.y : wa.y >> 4) & 0x0f0f0f0fu;
+                uint32_t a1 = keep ? wb.x & 0xf0f0f0f0u : (hf == 0 ? wb.x : wb.x >> 4) & 0x0f0f0f0fu;
+                uint32_t a3 = keep ? wb.y & 0xf0f0f0f0u : (hf == 0 ? wb.y : wb.y >> 4) & 0x0f0f0f0fu;
+                if constexpr (Q5) {
+                    auto fifth = [&](uint32_t hw) { return sub < 4 ? hw << (4 - sub) : hw >> (sub - 4); };  // bit `sub` -> bit 4
+                    a0 = and_or(fifth(qh0.x), 0x10101010u, a0);
+                    a2 = and_or(fifth(qh0.y), 0x10101010u, a2);
+                    a1 = and_or(fifth(qh1.x), 0x10101010u, a1);
+                    a3 = and_or(fifth(qh1.y), 0x10101010u, a3);
+                }
+                const int s0 = (int)__byte_perm(sub < 4 ? sc0a : sc0b, 0u, 0x4440u + (sub & 3));
+                const int s1 = (int)__byte_perm(sub < 4 ? sc1a : sc1b, 0u, 0x4440u + (sub & 3));
+#pragma unroll
+                for (int i = 0; i < NG; i++) {
+                    int D[4];
+                    imma_k32(D, a0, a1, a2, a3, hf == 0 ? bfp[i].x : bfp[i].z, hf == 0 ? bfp[i].y : bfp[i].w);
+                    int(&S)[4] = keep ? IO[i] : I[i];
+                    S[0] += s0 * D[0];
+                    S[1] += s0 * D[1];
+                    S[2] += s1 * D[2];
+                    S[3] += s1 * D[3];
+                }
+            }
+        }
+        const float d0 = half_bits_to_float(h0.x), d1 = half_bits_to_float(h1.x);
+        const float dm0 = half_bits_to_float(h0.x >> 16), dm1 = half_bits_to_float(h1.x >> 16);
+        const uint8_t* tb = blk + (tab_lane - xd_lane);
+        const uint8_t* fm = blk + (xm_lane - xd_lane);
+        if constexpr (C::DIGIT_MAJOR) {
+            float qf[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}}, mf[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};  // [row][row of x 2t + c]
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                const float2 w = *reinterpret_cast<const float2*>(tb + (8 * i + 2 * t) * 4);  // digit i of rows 2t, 2t + 1 of x
+                qf[0][0] = fmaf(w.x, (float)I[i][0], qf[0][0]);
+                qf[0][1] = fmaf(w.y, (float)I[i][1], qf[0][1]);
+                qf[1][0] = fmaf(w.x, (float)I[i][2], qf[1][0]);
+                qf[1][1] = fmaf(w.y, (float)I[i][3], qf[1][1]);
+#pragma unroll
+                for (int c = 0; c < 2; c++) {
+                    int E[4];
+                    imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)(2 * i + c) * NCOLM * 16));
+                    const float wc = c == 0 ? w.x : w.y;
+                    mf[0][c] = fmaf(wc, (float)(E[1] * 128 + E[0]), mf[0][c]);
+                    mf[1][c] = fmaf(wc, (float)(E[3] * 128 + E[2]), mf[1][c]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                acc[0][0][c] = fmaf(-dm0, mf[0][c], fmaf(d0, qf[0][c], acc[0][0][c]));
+                acc[0][1][c] = fmaf(-dm1, mf[1][c], fmaf(d1, qf[1][c], acc[0][1][c]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NG; i++) {
+                const float2 w = *reinterpret_cast<const float2*>(tb + (NG * 8 + 8 * i + 2 * t) * 4);  // weights / 16 of columns 2t, 2t+1
+                acc[i][0][0] = fmaf(d0 * w.x, (float)(16 * I[i][0] + IO[i][0]), acc[i][0][0]);
+                acc[i][0][1] = fmaf(d0 * w.y, (float)(16 * I[i][1] + IO[i][1]), acc[i][0][1]);
+                acc[i][1][0] = fmaf(d1 * w.x, (float)(16 * I[i][2] + IO[i][2]), acc[i][1][0]);
+                acc[i][1][1] = fmaf(d1 * w.y, (float)(16 * I[i][3] + IO[i][3]), acc[i][1][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < NGM; i++) {
+                int E[4];
+                imma_k16(E, mn0, mn1, *reinterpret_cast<const uint32_t*>(fm + (size_t)i * NCOLM * 16));
+                const float w = *reinterpret_cast<const float*>(tb + (4 * i + t) * 4);  // weight of digit column 4i + t
+                accm[i][0] = fmaf(dm0 * w, (float)(E[1] * 128 + E[0]), accm[i][0]);
+                accm[i][1] = fmaf(dm1 * w, (float)(E[3] * 128 + E[2]), accm[i][1]);
+            }
+        }
+    };
+
+    int parity = 0;
+    uint32_t cmp_slot = 0;
+    for (int sl = 0; sl < nslices; sl++) {
+        // ---- bring this slice of the activation image into shared memory ---------------------------------------------
+        const int len = sl == nslices - 1 ? len_last : KS;
+        const int nb = sl == nslices - 1 ? nb_last : nb_full;
+        if (sl > 0) {
+            __syncthreads();  // every warp is done with the previous slice
+        }
+        if (nslices == 1) {
+            // one slice: a warp only ever reads the image of its own super-blocks, so it fetches just those and waits for
+            // nobody else (the wait also covers the weight stages requested so far, which it needs next anyway)
+            constexpr int CH = (int)(C::PB / 16);
+            for (int b = warp; b < KB; b += NW) {
+                for (int c = lane; c < CH; c += 32) {
+                    cp_async16(img_s + (uint32_t)(b * CH + c) * 16u, image + ((size_t)b * CH + c) * 16);
+                }
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncwarp();
+        } else {
+            const uint8_t* src = image + (size_t)sl * KS * C::PB;
+            const int chunks = (int)((size_t)len * C::PB / 16);
+            for (int c = tid; c < chunks; c += THREADS) {
+                cp_async16(img_s + (uint32_t)c * 16u, src + (size_t)c * 16);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+        }
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
+            const uint8_t* blk = xd_lane + (size_t)warp * C::PB;
+            for (int j = 0; j < nb; j++) {
+                __syncwarp();                 // every lane is done reading the slot that is requested next
+                issue();
+                cp_async_wait<STAGES - 1>();  // this lane's copies of this step have landed
+                __syncwarp();                 // ... and so have the other lanes'
+                compute(ring + cmp_slot, blk);
+                cmp_slot = cmp_slot + SLOT_BYTES == RING_BYTES ? 0u : cmp_slot + SLOT_BYTES;
+                blk += (size_t)NW * C::PB;
+            }
+            // ---- this warp's partial sums per output row and row of x ---------------------------------------------------
+            float* rd = red + (size_t)parity * NW * 16 * MT;
+            if constexpr (C::DIGIT_MAJOR) {
+                // the lane holds rows g, g + 8 for rows 2t, 2t + 1 of x (MT = 8: two floats side by side)
+                *reinterpret_cast<float2*>(rd + (warp * 16 + g) * MT + 2 * t) = make_float2(acc[0][0][0], acc[0][0][1]);
+                *reinterpret_cast<float2*>(rd + (warp * 16 + g + 8) * MT + 2 * t) = make_float2(acc[0][1][0], acc[0][1][1]);
+                acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
+            } else {
+                // combine the digit columns of a row of x, which sit in the 4 lanes of a quad
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 2; c++) {
+                        const int col = 2 * t + c;
+                        const bool mine = col < C::COLS && col / 3 == m;
+                        p0 += mine ? acc[0][0][c] : 0.0f;
+                        p1 += mine ? acc[0][1][c] : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < NGM; i++) {
+                        const int col = 4 * i + t;  // digit column whose two sum parts this lane holds
+                        const bool mine = col < C::COLS && col / 3 == m;
+                        p0 -= mine ? accm[i][0] : 0.0f;
+                        p1 -= mine ? accm[i][1] : 0.0f;
+                    }
+                    p0 += __shfl_xor_sync(0xffffffffu, p0, 1);
+                    p1 += __shfl_xor_sync(0xffffffffu, p1, 1);
+                    p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
+                    p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
+                    if (t == 0) {
+                        rd[(warp * 16 + g) * MT + m] = p0;
+                        rd[(warp * 16 + g + 8) * MT + m] = p1;
+                    }
+                }
+                acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < NGM; i++) {
+                    accm[i][0] = accm[i][1] = 0.0f;
+                }
+            }
+            __syncthreads();
+            // ---- the warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
+            const bool second = my_tile >= w2.first_tiles;
+            const int64_t n = second ? w2.n : v.n;
+            float* const yo = second ? w2.y : y;
+            for (int o = tid; o < 16 * MT; o += THREADS) {
+                const int r = o / MT, m = o % MT;
+                const int64_t row = (int64_t)(second ? my_tile - w2.first_tiles : my_tile) * 16 + r;
+                const float* p = rd + o;
+                constexpr int W = 16 * MT;  // floats per warp
+                float sum = ((p[0] + p[W]) + (p[2 * W] + p[3 * W])) + ((p[4 * W] + p[5 * W]) + (p[6 * W] + p[7 * W]));
+                if constexpr (NW == 16) {
+                    sum += ((p[8 * W] + p[9 * W]) + (p[10 * W] + p[11 * W])) + ((p[12 * W] + p[13 * W]) + (p[14 * W] + p[15 * W]));
+                }
+                if (sl > 0) {
+                    sum += carry[(size_t)ti * 16 * MT + o];
+                }
+                if (sl + 1 < nslices) {
+                    carry[(size_t)ti * 16 * MT + o] = sum;
+                } else if (m < rows && row < n) {
+                    const float val = sum + (bias != nullptr && !second ? bias[row] : 0.0f);
+                    if constexpr (!PEER) {
+                        yo[(int64_t)m * n + row] = val;
+                    } else {
+                        // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
+                        for (int r = 0; r < peerp->world; r++) {
+                            peerp->y[r][(int64_t)m * peerp->n_total + peerp->col0 + row] = val;
+                        }
+                    }
+                }
+            }
+            parity ^= 1;
+        }
+    }
+    if constexpr (PEER) {
+        peer_publish(peerp->flags, peerp->rank, peerp->world, reinterpret_cast<int*>(red));  // the last CTA raises this rank's flag on every rank
+    }
+}
+
+int g_sms = 0;
+int sm_count() {
+    if (g_sms == 0) {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+            g_sms = sms;
+        } else {
+            g_sms = 148;
+        }
+    }
+    return g_sms;
+}
+
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
+int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid,
+           int max_tiles, size_t smem) {
+    static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
+    int dev = 0;
+    JQ_CUDA(cudaGetDevice(&dev));
+    if ((configured.load() >> (dev & 63) & 1) == 0) {
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        configured.fetch_or((uint64_t)1 << (dev & 63));
+    }
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NW * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may request weights while the activation kernel runs
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, v, w2, (const PeerOut*)(PEER ? peer.table : nullptr), image, rows, bias, y, tiles, KS, max_tiles));
+    count_launch();
+    return JQ_OK;
+}
+
+// Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
+template <int MT, bool Q5>
+size_t smem_bytes(int nw, int KS, int stages, bool sliced, int max_tiles) {
+    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * nw * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+           (size_t)nw * stages * Blk<Q5>::SLOT;
+}
+
+// A launch shape: warps per CTA, CTAs per SM, ring stages. KS (the slice length) is a function of MT and k only, so
+// that the summation order never depends on n: the whole k if its image fits beside the ring, else a multiple of the
+// warps per CTA.
+struct Shape {
+    int nw, occ, stages;
+};
+
+template <int MT, bool Q5>
+int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image,
+        bool* handled) {
+    // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
+    const int KB = (int)(v.k / 256);
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
+    // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
+    constexpr bool WIDE = MT > 2;
+    const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
+    const Shape sliced[2] = {WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
+    Shape sh{0, 0, 0};
+    int KS = KB;
+    for (int c = 0; c < 3 && sh.nw == 0; c++) {
+        if (smem_bytes<MT, Q5>(unsliced[c].nw, KB, unsliced[c].stages, false, 0) <= SMEM_MAX / unsliced[c].occ - 1024) {
+            sh = unsliced[c];
+        }
+    }
+    if (sh.nw == 0) {
+        for (int c = 0; c < 2 && sh.nw == 0; c++) {
+            const size_t room = SMEM_MAX / sliced[c].occ - 1024 - 8 * 1024;  // 8 KB set aside for the carried sums
+            const size_t rest = smem_bytes<MT, Q5>(sliced[c].nw, 0, sliced[c].stages, false, 0);
+            const int ks = rest < room ? (int)((room - rest) / Cfg<MT>::PB) / sliced[c].nw * sliced[c].nw : 0;
+            if (ks >= sliced[c].nw) {
+                sh = sliced[c];
+                KS = ks;
+            }
+        }
+        if (sh.nw == 0) {
+            *handled = false;
+            return JQ_OK;
+        }
+    }
+    const int grid = tiles < sm_count() * sh.occ ? tiles : sm_count() * sh.occ;
+    const int max_tiles = (tiles + grid - 1) / grid;
+    const bool is_sliced = KS < KB;
+    const size_t smem = smem_bytes<MT, Q5>(sh.nw, KS, sh.stages, is_sliced, max_tiles);
+    if (smem > SMEM_MAX / sh.occ - 1024) {
+        *handled = false;  // more tiles per CTA than the carried sums have room for
+        return JQ_OK;
+    }
+    *handled = true;
+    if (x != nullptr) {
+        // launched programmatically as well: it is scheduled while the kernel before it still runs (it waits for that kernel
+        // before touching memory) and lets the GEMV behind it be scheduled at once
+        cudaLaunchConfig_t icfg = {};
+        cudaLaunchAttribute iattr[1];
+        iattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        iattr[0].val.programmaticStreamSerializationAllowed = 1;
+        icfg.attrs = iattr;
+        icfg.numAttrs = WIDE ? 0 : 1;  // the 16-warp kernel fills an SM's registers: an early-scheduled successor only gets in its way
+        icfg.stream = s;
+        icfg.gridDim = dim3((unsigned)((KB * MT + PREP_WARPS - 1) / PREP_WARPS));
+        icfg.blockDim = dim3(PREP_WARPS * 32);
+        JQ_CUDA(cudaLaunchKernelEx(&icfg, q4k_activation_image_kernel<MT>, x, rows, (int64_t)v.k, image));
+        count_launch();
+    }
+#define JQ_SHAPE(NWV, OCCV, STV)                                   \
+    if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
+        if (peer.world != 0) {                                                                              \
+            return launch<MT, STV, NWV, OCCV, Q5, true>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        }                                                                                                   \
+        return launch<MT, STV, NWV, OCCV, Q5, false>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+    }
+    if constexpr (WIDE) {
+        JQ_SHAPE(16, 1, 3)
+        JQ_SHAPE(16, 1, 2)
+    } else {
+        JQ_SHAPE(8, 2, 3)
+    }
+    JQ_SHAPE(8, 2, 2)
+#undef JQ_SHAPE
+    return fail(JQ_ERR_UNSUPPORTED, "gemv_q4k_i8: no kernel for the chosen launch shape");
+}
+
+}  // namespace
+
+// Bytes of scratch (activation image) a Q4_K GEMV of `rows` activation rows over k inputs needs; 0 if the
+// shape is not handled by the integer kernel.
+size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
+    if (rows < 1 || rows > 8 || k <= 0) {
+        return 0;
+    }
+    const size_t pb = rows == 1 ? Cfg<1>::PB : (rows == 2 ? Cfg<2>::PB : Cfg<8>::PB);
+    return (size_t)(k / 256) * pb;
+}
+
+// Q4_K or Q5_K with rows in [1, 8] on a weight whose buffer is padded by 16 rows. `image` is a scratch buffer of
+// gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
+// *handled = false leaves the call to another kernel.
+int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
+                       const PeerOut* peer) {
+    *handled = false;
+    if ((v.type != JQ_TYPE_Q4_K && v.type != JQ_TYPE_Q5_K) || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr ||
+        v.k / 256 >= (1 << 20)) {
+        return JQ_OK;
+    }
+    const Second none{nullptr, 0, nullptr, 0x7fffffff};
+    PeerOut local{};  // world = 0: results go to y
+    const PeerOut& po = peer != nullptr ? *peer : local;
+    if (v.type == JQ_TYPE_Q5_K) {
+        if (rows == 1) return run<1, true>(v, none, po, x, rows, bias, y, s, image, handled);
+        if (rows == 2) return run<2, true>(v, none, po, x, rows, bias, y, s, image, handled);
+        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled);
+    }
+    if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled);
+    if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled);
+    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled);
+}
+
+int gemv_peer_status(int* status) {
+    const int zero = 0;
+    JQ_CUDA(cudaMemcpyFromSymbol(status, g_gemv_peer_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_gemv_peer_status, &zero, sizeof(int)));
+    return JQ_OK;
+}
+
+size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }
+
+// One row of x whose image (q4k::build_image<1> per super-block) a kernel earlier in the stream has written to `image`;
+// that kernel should execute griddepcontrol.launch_dependents so that this one can request weights meanwhile. With
+// v2 != nullptr the rows of a second Q4_K weight with the same k follow in the same launch, results in y2.
+int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
+                              const PeerOut* peer) {
+    *handled = false;
+    if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || image == nullptr || v.k / 256 >= (1 << 20) ||
+        (v2 != nullptr && (v2->type != JQ_TYPE_Q4_K || v2->k != v.k || v2->n == 0 || y2 == nullptr))) {
+        return JQ_OK;
+    }
+    const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
+    const PeerOut local{};  // world = 0: results go to y (and y2)
+    if (peer != nullptr && v2 != nullptr) {
+        return JQ_OK;  // a second weight has no place in a peer's y
+    }
+    return run<1, false>(v, w2, peer != nullptr ? *peer : local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
+}
+
+}  // namespace jq
+
+// ---- an entry point that allocates nothing -------------------------------------------------------------------------
+// jq_linear_f32 keeps the activation image in a scratch buffer that the library allocates with cudaMalloc the
+// first time a stream needs one. Some callers cannot have that: a serving process that has handed every byte
+// of device memory to its own pools fails the allocation, and cudaMalloc also makes the whole device wait,
+// which a latency-bound decode loop on another stream would feel. For them the image lives in the array below,
+// which is part of the loaded library image: every GPU that loads the library holds these bytes until the
+// process exits, whether or not the entry point is ever called.
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)1 << 20;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+uint8_t* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of g_noalloc_scratch, per device
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use: the device
+// address has to be asked for, once per device and with that device current.
+int noalloc_scratch_address(int device, uint8_t** out) {
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: device %d is beyond the %d this entry point keeps addresses for", device,
+                        NOALLOC_MAX_DEVICES);
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_addr[device] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            return jq::cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+        }
+        g_noalloc_addr[device] = static_cast<uint8_t*>(p);
+    }
+    *out = g_noalloc_addr[device];
+    return JQ_OK;
+}
+
+}  // namespace
+
+extern "C" JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, void* stream) {
+    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: not a live weight handle");
+    }
+    if (w->type != JQ_TYPE_Q4_K) {
+        return jq::fail(JQ_ERR_UNSUPPORTED, "jq_linear_q4k_f32_noalloc: the weight is not Q4_K (type id %d)", w->type);
+    }
+    if (m < 1 || m > 8) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: %lld activation rows, this entry point takes 1 to 8", (long long)m);
+    }
+    if (x == nullptr || y == nullptr || (((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
+        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: x and y must be non-null, 16-byte aligned device pointers");
+    }
+    if (w->n == 0) {
+        return JQ_OK;
+    }
+    const size_t need = jq::gemv_q4k_i8_scratch_bytes(w->k, (int)m);
+    if (need == 0 || need > NOALLOC_SCRATCH_BYTES) {
+        return jq::fail(JQ_ERR_INVALID,
+                        "jq_linear_q4k_f32_noalloc: k = %lld with %lld rows needs %zu bytes of activation image, the built-in scratch holds %zu", (long long)w->k,
+                        (long long)m, need, NOALLOC_SCRATCH_BYTES);
+    }
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) {
+        prev = -1;
+    }
+    if (prev != w->device && cudaSetDevice(w->device) != cudaSuccess) {
+        return jq::fail(JQ_ERR_CUDA, "jq_linear_q4k_f32_noalloc: cannot select device %d", w->device);
+    }
+    uint8_t* image = nullptr;
+    int rc = noalloc_scratch_address(w->device, &image);
+    if (rc == JQ_OK) {
+        bool handled = false;
+        const jq::View v{w->q, w->aux, w->n, w->k, w->type};
+        rc = jq::launch_gemv_q4k_i8(v, x, (int)m, bias, y, (cudaStream_t)stream, image, &handled);
+        if (rc == JQ_OK && !handled) {
+            rc = jq::fail(JQ_ERR_UNSUPPORTED, "jq_linear_q4k_f32_noalloc: shape [%lld, %lld] x %lld rows is outside what the tensor-core kernel takes",
+                          (long long)w->n, (long long)w->k, (long long)m);
+        }
+    }
+    if (prev >= 0 && prev != w->device) {
+        cudaSetDevice(prev);
+    }
+    return rc;
+}

@@ -67,7 +67,7 @@ __device__ long long g_umma_trace[5 * 64 * 4];
     } while (0)
 #endif
 
-std::atomic<int64_t> g_opt_gemv_umma{1};
+std::atomic<int64_t> g_opt_gemv_umma{0};
 std::atomic<int64_t> g_opt_wait_limit_us{2000000};
 
 namespace {
@@ -1226,82 +1226,3 @@ int gemv_umma_status(int* status) {
 }
 
 }  // namespace jq
-
-// ---- an entry point that allocates nothing -------------------------------------------------------------------------
-// jq_linear_f32 keeps the activation image and the sums of split tiles in scratch buffers that the library allocates
-// with cudaMalloc the first time a stream needs them. Some callers cannot have that: a serving process that has handed
-// every byte of device memory to its own pools fails the allocation, and cudaMalloc also makes the whole device wait,
-// which a latency-bound decode loop on another stream would feel. For them the image lives in the array below, which is
-// part of the loaded library image (every GPU that loads the library holds these bytes until the process exits, whether
-// or not the entry point is ever called), and the CTAs are dealt whole tiles, so nothing else needs scratch.
-constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)1 << 20;
-static __device__ __align__(256) uint8_t g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
-
-namespace {
-
-constexpr int NOALLOC_MAX_DEVICES = 64;
-std::mutex g_noalloc_mu;
-uint8_t* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of g_noalloc_scratch, per device
-
-// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use: the device
-// address has to be asked for, once per device and with that device current.
-int noalloc_scratch_address(int device, uint8_t** out) {
-    if (device < 0 || device >= NOALLOC_MAX_DEVICES) {
-        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: device %d is beyond the %d this entry point keeps addresses for", device,
-                        NOALLOC_MAX_DEVICES);
-    }
-    std::lock_guard<std::mutex> lock(g_noalloc_mu);
-    if (g_noalloc_addr[device] == nullptr) {
-        void* p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-        if (e != cudaSuccess || p == nullptr) {
-            return jq::cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
-        }
-        g_noalloc_addr[device] = static_cast<uint8_t*>(p);
-    }
-    *out = g_noalloc_addr[device];
-    return JQ_OK;
-}
-
-}  // namespace
-
-extern "C" JQ_API int jq_linear_q4k_f32_noalloc(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, void* stream) {
-    if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC) {
-        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: not a live weight handle");
-    }
-    if (w->type != JQ_TYPE_Q4_K) {
-        return jq::fail(JQ_ERR_UNSUPPORTED, "jq_linear_q4k_f32_noalloc: the weight is not Q4_K (type id %d)", w->type);
-    }
-    if (m < 1 || m > 16) {
-        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: %lld activation rows, this entry point takes 1 to 16", (long long)m);
-    }
-    if (x == nullptr || y == nullptr || (((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
-        return jq::fail(JQ_ERR_INVALID, "jq_linear_q4k_f32_noalloc: x and y must be non-null, 16-byte aligned device pointers");
-    }
-    if (w->n == 0) {
-        return JQ_OK;
-    }
-    const size_t need = jq::gemv_umma_image_bytes(w->k, (int)m);
-    if (need == 0 || need > NOALLOC_SCRATCH_BYTES) {
-        return jq::fail(JQ_ERR_INVALID,
-                        "jq_linear_q4k_f32_noalloc: k = %lld with %lld rows needs %zu bytes of activation image, the built-in scratch holds %zu", (long long)w->k,
-                        (long long)m, need, NOALLOC_SCRATCH_BYTES);
-    }
-    int prev = -1;
-    if (cudaGetDevice(&prev) != cudaSuccess) {
-        prev = -1;
-    }
-    if (prev != w->device && cudaSetDevice(w->device) != cudaSuccess) {
-        return jq::fail(JQ_ERR_CUDA, "jq_linear_q4k_f32_noalloc: cannot select device %d", w->device);
-    }
-    uint8_t* image = nullptr;
-    int rc = noalloc_scratch_address(w->device, &image);
-    if (rc == JQ_OK) {
-        const jq::View v{w->q, w->aux, w->n, w->k, w->type};
-        rc = jq::launch_gemv_umma(v, nullptr, x, image, (int)m, bias, y, nullptr, (cudaStream_t)stream, nullptr, true);
-    }
-    if (prev >= 0 && prev != w->device) {
-        cudaSetDevice(prev);
-    }
-    return rc;
-}

@@ -277,9 +277,13 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
     po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
     po.wait_first = wait_first ? 1 : 0;
     rc = device_table(po, s, &po.table);
+    bool handled = false;
     if (rc == JQ_OK) {
         const View v{w->q, w->aux, w->n, w->k, w->type};
-        rc = launch_gemv_umma(v, nullptr, nullptr, const_cast<uint8_t*>(image), 1, nullptr, nullptr, nullptr, s, &po);
+        rc = launch_gemv_q4k_i8_imaged(v, nullptr, image, nullptr, nullptr, nullptr, s, &handled, &po);
+    }
+    if (rc == JQ_OK && !handled) {
+        rc = fail(JQ_ERR_UNSUPPORTED, "peer linear: a [%lld, %lld] shard is outside what the tensor-core GEMV takes", (long long)w->n, (long long)w->k);
     }
     if (rc == JQ_OK && wait_after) {
         rc = enqueue_wait(tg, rank, world, s);
@@ -337,6 +341,22 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
         if (rc == JQ_OK) rc = scratch_for(s, gemv_umma_image_bytes(w->k, (int)m), &image);
         if (rc == JQ_OK) rc = launch_gemv_umma(v, nullptr, x, image, (int)m, bias, nullptr, nullptr, s, &po);
         fused = rc == JQ_OK;
+    } else if ((w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K) && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
+        // the GEMV kernel itself stores into every rank's y and publishes the exchange; it reads the targets from a table
+        // in this rank's flag area, which is written once per distinct (buffers, area, shard) and then found again
+        PeerOut po;
+        memset(&po, 0, sizeof(po));
+        for (int r = 0; r < PEER_MAX_WORLD; r++) {
+            po.y[r] = tg.y[r];
+            po.flags[r] = tg.flags[r];
+        }
+        po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        rc = device_table(po, s, &po.table);
+        uint8_t* image = nullptr;
+        if (rc == JQ_OK) rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(w->k, (int)m), &image);
+        if (rc == JQ_OK) {
+            rc = launch_gemv_q4k_i8(v, x, (int)m, bias, nullptr, s, image, &fused, &po);
+        }
     }
     if (rc == JQ_OK && !fused) {
         // any other format or row count: the ordinary kernels into a slice, then the scatter kernel

@@ -51,14 +51,17 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
         }
     }
     float am = 0.0f;
+    bool bad = false;  // a NaN or an Inf among the values: the column weights become NaN and with them every output of this row of x
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         am = fmaxf(am, fabsf(xv[i]));
+        bad = bad || (__float_as_uint(xv[i]) & 0x7f800000u) == 0x7f800000u;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
     }
+    bad = __any_sync(0xffffffffu, bad);
     // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
     uint32_t e = __float_as_uint(am) & 0x7f800000u;
     e = e < 0x0c000000u ? 0x0c000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-21 normal
@@ -94,7 +97,7 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
             xc[((((size_t)(grp >> 1) * NG + (col >> 3)) * 4 + ((col & 7) >> 1)) * 2 + (grp & 1)) * 2 + (col & 1)] = -32 * sum;
         }
         if (lane == 0) {
-            tab[col] = xb != nullptr ? __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)) : 0.0f;  // s * 2^(8 dgt - 21)
+            tab[col] = xb == nullptr ? 0.0f : (bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)));  // s * 2^(8 dgt - 21)
         }
     }
 }

@@ -91,10 +91,10 @@ def test_nine_to_sixteen_rows(t, m):
     close_like_reference(expect, got, "%s m=%d" % (t, m))
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K"])
-def test_rows_of_a_split_tile_equal_the_unsplit_ones_bitwise(t):
-    """The same 128 rows as a weight of their own (one CTA per super-block, every contribution through the scratch) and as
-    part of a large weight (whole tiles inside one CTA's run) give bitwise the same outputs."""
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0"])
+def test_rows_of_a_large_weight_equal_their_own_shard_bitwise(t):
+    """The same rows as a weight of their own and as part of a large weight (where a thread block walks several tiles) give
+    bitwise the same outputs: the sum over k has one order, whatever the number of rows."""
     n, k = 4096, 4096
     raw = synth.random_valid_blocks(t, n, k, seed=77).numpy()
     x = np.random.default_rng(78).standard_normal((5, k)).astype(np.float32)
@@ -104,7 +104,7 @@ def test_rows_of_a_split_tile_equal_the_unsplit_ones_bitwise(t):
         assert np.array_equal(part.view(np.uint32), whole[:, lo:hi].view(np.uint32)), (lo, hi)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q5_K"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1"])
 def test_non_finite_activations_give_non_finite_outputs(t):
     """A NaN or Inf in x reaches every output row in the reference (each row multiplies every x); the fixed-point image
     must not turn it into a finite number."""

@@ -32,7 +32,7 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(n, k):
     w = Tensor.quantized("Q4_K", raw, n, k)
     bias = torch.randn(n, generator=g).cuda()
     # two calls in a row with different row counts and inputs: the second must not see anything of the first
-    for m in (5, 1, 2, 3, 8, 16):
+    for m in (5, 1, 2, 3, 8):
         x = torch.randn(m, k, generator=g).cuda()
         expect = Gguf.linear(x, w, bias)
         y = torch.full((m, n), float("nan"), device="cuda")
@@ -40,7 +40,7 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(n, k):
         torch.cuda.synchronize()
         diff = float((y - expect).abs().max() / expect.abs().max())
         assert diff <= REL_TOL, diff
-        assert torch.equal(y, expect)  # same arithmetic in the same order, however the tiles are dealt to the thread blocks
+        assert torch.equal(y, expect)  # same kernels, same summation order
 
 
 def test_no_device_memory_is_allocated():
@@ -51,12 +51,12 @@ def test_no_device_memory_is_allocated():
     x = torch.randn(16, k, device="cuda")
     y = torch.empty(16, n, device="cuda")
     L = _lib.load()
-    for m in (1, 2, 5, 8, 10, 16):  # one warm-up call per kernel variant
+    for m in (1, 2, 5, 8):  # one warm-up call per kernel variant
         assert L.jq_linear_q4k_f32_noalloc(w._handle(), x.data_ptr(), m, None, y.data_ptr(), None) == 0, _lib.last_error()
     torch.cuda.synchronize()
     fresh = torch.cuda.Stream()
     free_before = torch.cuda.mem_get_info()[0]
-    for m in (1, 2, 5, 8, 10, 16):
+    for m in (1, 2, 5, 8):
         assert L.jq_linear_q4k_f32_noalloc(w._handle(), x.data_ptr(), m, None, y.data_ptr(), ctypes.c_void_p(fresh.cuda_stream)) == 0
     fresh.synchronize()
     assert torch.cuda.mem_get_info()[0] == free_before
@@ -66,12 +66,12 @@ def test_refuses_what_it_cannot_hold():
     L = _lib.load()
     raw = synth.random_valid_blocks("Q4_K", 8, 512, seed=3).numpy()
     w = Tensor.quantized("Q4_K", raw, 8, 512)
-    x = torch.zeros(17, 512, device="cuda")
-    y = torch.zeros(17, 8, device="cuda")
-    assert call_noalloc(w, x, None, y) == _lib.JQ_ERR_INVALID and "1 to 16" in _lib.last_error()
+    x = torch.zeros(9, 512, device="cuda")
+    y = torch.zeros(9, 8, device="cuda")
+    assert call_noalloc(w, x, None, y) == _lib.JQ_ERR_INVALID and "1 to 8" in _lib.last_error()
     q8 = Tensor.quantized("Q8_0", synth.random_valid_blocks("Q8_0", 8, 512, seed=4).numpy(), 8, 512)
     assert call_noalloc(q8, x[:1], None, y[:1]) == _lib.JQ_ERR_UNSUPPORTED and "not Q4_K" in _lib.last_error()
-    # k = 65536 with 8 rows needs 256 * 8624 bytes of image: more than the 1 MiB the library carries
+    # k = 65536 with 8 rows needs 256 * 7008 bytes of image: more than the 1 MiB the library carries
     big = Tensor.quantized("Q4_K", np.zeros(65536 // 256 * 144, np.uint8), 1, 65536)
     xb = torch.zeros(8, 65536, device="cuda")
     assert call_noalloc(big, xb, None, y[:8, :1].contiguous()) == _lib.JQ_ERR_INVALID
