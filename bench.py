@@ -39,8 +39,12 @@ TYPE = "Q4_K"
 BYTES_PER_WEIGHT = 144.0 / 256.0
 POOL_COPIES = 4  # distinct copies of every weight; 4 x 134 MB = 537 MB, about 4x the 126 MB L2
 METRIC = "q4k_gemv_sweep_GBps"
-# dram__bytes_read.sum + dram__bytes_write.sum of one step under ncu (profiles/gemv_q4k_i8_sweep.md), per linear
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one step of this sweep, per linear: not measured by the run
+# itself but taken from an ncu capture of the same command line (`--steps 20 --warmup 3 --no-cpu --eager`, one pass,
+# --clock-control none); the line names the source beside the figure.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 269671168 // 8
+NCU_TRAFFIC_SOURCE = "ncu capture of the sweep (16 launches of one eager step), not measured by this run"
+WORKLOAD = "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; 8 launches per step"
 
 
 def algorithmic_bytes(n, k, m):
@@ -117,7 +121,7 @@ class ClockSampler:
 def make_weights(torch, device, rank, world):
     """Seeded N(0, 0.02) weights quantised to Q4_K on the GPU; each rank uploads its row shard."""
     from jitnn_b200 import Tensor, synth
-    pools = []
+    pools, samples = [], []
     for si, (n, k) in enumerate(SHAPES):
         copies = []
         for c in range(POOL_COPIES):
@@ -128,10 +132,21 @@ def make_weights(torch, device, rank, world):
             lo, hi = rank * n // world, (rank + 1) * n // world
             copies.append(Tensor.quantized(TYPE, raw, n, k, device=device.index, rows=(lo, hi)) if world > 1
                           else Tensor.quantized(TYPE, raw, n, k, device=device.index))
-            if c == 0 and si == 0:
-                first_raw = raw[:64].copy()
+            if c == 0:
+                rows = guard_rows(n, world)
+                samples.append((rows, raw[rows].copy()))
         pools.append(copies)
-    return pools, first_raw
+    return pools, samples
+
+
+def guard_rows(n, world):
+    """Rows the parity guard compares with the oracle: the first and last rows of the weight and the rows on both sides of every
+    shard border (at 8 ranks, whatever the run's world size: the same rows at every N)."""
+    rows = set(range(16)) | set(range(n - 16, n))
+    for g in range(1, 8):
+        b = g * n // 8
+        rows |= {b - 2, b - 1, b, b + 1}
+    return sorted(rows)
 
 
 def launches_per_step(L, step, side, torch, device):
@@ -177,7 +192,7 @@ def run_ours(args):
             os._exit(0)
         return
 
-    pools, first_raw = make_weights(torch, device, rank, world)
+    pools, samples = make_weights(torch, device, rank, world)
     g = torch.Generator(device=device).manual_seed(99)
     xs = {(k, m): torch.randn(m, k, generator=g, device=device) for _, k in SHAPES for m in BATCHES}
     ys = {}
@@ -218,15 +233,41 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(device)
 
-    # correctness guard: the first rows of the first weight against the CPU oracle (not timed)
-    if rank == 0 and world == 1:
-        from oracle import oracle
-        x0 = xs[(SHAPES[0][1], BATCHES[0])]
-        xh = x0.cpu().numpy()
-        yh = jitnn_b200.Gguf.linear(x0, pools[0][0], None).cpu().numpy()
-        ref = oracle.linear(TYPE, first_raw, xh, None)
-        rel = float(np.abs(yh[:, :64] - ref).max() / np.abs(ref).max())
-        assert rel <= 1e-3, "GEMV differs from the oracle: %g" % rel
+    # Parity guard, at every N and on every rank (not timed): one pass over the sweep on copy 0 of every weight, through the same
+    # calls the timed steps make; sampled rows of the complete y (first, last, both sides of every shard border) against the
+    # CPU oracle. The weights are the same at every N (seeded by shape and copy; a rank uploads its rows of them).
+    from oracle import oracle
+    worst = 0.0
+    for si, (n, k) in enumerate(SHAPES):
+        rows, raw_rows = samples[si]
+        for m in BATCHES:
+            w = pools[si][0]
+            x0 = xs[(k, m)]
+            if gather_kind == "peer":
+                full = peers[(n, k, m)].linear(w, x0)
+            else:
+                y = ys[(n, k, m)]
+                sp0 = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+                _lib.check(L.jq_linear_f32(w._handle(), x0.data_ptr(), m, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp0))
+                full = sharded.gather_rows(y, n) if gather_kind == "nccl" else y
+            torch.cuda.synchronize(device)
+            got = full.cpu().numpy()
+            if gather_kind == "none" and world > 1:  # diagnosis mode: every rank only has its own rows
+                lo = rank * n // world
+                keep = [i for i, r in enumerate(rows) if lo <= r < (rank + 1) * n // world]
+                ref = oracle.linear(TYPE, raw_rows[keep], x0.cpu().numpy(), None, threads=4)
+                got = got[:, [rows[i] - lo for i in keep]]
+            else:
+                ref = oracle.linear(TYPE, raw_rows, x0.cpu().numpy(), None, threads=4)
+                got = got[:, rows]
+            worst = max(worst, float(np.abs(got - ref).max() / np.abs(ref).max()))
+    if world > 1:
+        t = torch.tensor([worst], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = float(t.item())
+    assert worst <= 1e-3, "GEMV differs from the oracle: max relative error %g" % worst
+    parity_check = {"against": "CPU oracle (ops/Gguf.java:187-205 semantics)", "max_rel_err": worst, "tolerance": 1e-3, "ranks_checked": world,
+                    "rows_per_shape": len(samples[0][0]), "shapes": len(SHAPES) * len(BATCHES), "ok": True}
 
     # The weight rotation repeats every `period` steps. That many steps are captured into a CUDA graph (the launches of
     # a step are a few microseconds each, less than the host needs to issue them) and the graph is replayed; with
@@ -247,32 +288,40 @@ def run_ours(args):
             for _ in range(3):
                 graph.replay()
     timed_steps = args.steps if not use_graph else max(period, args.steps // period * period)
+    # The region of `timed_steps` steps is timed `regions` times back to back, each with its own pair of events; the line
+    # reports the median region (and the spread), so that a region of a few milliseconds still sits inside a window long
+    # enough for the clock sampler.
+    regions = max(1, min(200, -(-2000 // timed_steps)))
     sampler = ClockSampler(local) if rank == 0 else None
     time.sleep(0.2)  # lets the sampler take its first readings; every rank waits, then all start together
     barrier()
     t_start = time.time()
     launches0 = L.jq_launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(regions)]
     with torch.cuda.stream(side):
-        e0.record(side)
-        if use_graph:
-            for _ in range(timed_steps // period):
-                graph.replay()
-        else:
-            for i in range(timed_steps):
-                step(args.warmup + i)
-        e1.record(side)
+        for e0, e1 in events:
+            e0.record(side)
+            if use_graph:
+                for _ in range(timed_steps // period):
+                    graph.replay()
+            else:
+                for i in range(timed_steps):
+                    step(args.warmup + i)
+            e1.record(side)
     barrier()
     t_end = time.time()
-    ms = e0.elapsed_time(e1)
-    # kernels of this library that ran in the timed region: counted at launch, or launches per captured step x replays
-    launches = (L.jq_launch_count() - launches0) if not use_graph else timed_steps * launches_per_step(L, step, side, torch, device)
+    region_ms = [e0.elapsed_time(e1) for e0, e1 in events]
+    # kernels of this library that ran in the timed regions: counted at launch, or launches per captured step x replays
+    launches = (L.jq_launch_count() - launches0) if not use_graph else regions * timed_steps * launches_per_step(L, step, side, torch, device)
     if world > 1:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        t = torch.tensor(region_ms, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every region: the slowest rank
+        region_ms = [float(v) for v in t.tolist()]
+    ms = statistics.median(region_ms)
     clocks = sampler.stop(t_start, t_end) if sampler else None
     ms_per_step = ms / timed_steps
+    spread = {"regions": regions, "steps_per_region": timed_steps, "ms_per_step_min": round(min(region_ms) / timed_steps, 5),
+              "ms_per_step_median": round(ms_per_step, 5), "ms_per_step_max": round(max(region_ms) / timed_steps, 5)}
     args.steps = timed_steps
     value = step_bytes() / (ms_per_step * 1e-3) / 1e9
     stream = torch.cuda.current_stream(device)
@@ -311,6 +360,7 @@ def run_ours(args):
 
     # end to end through the C ABI with host buffers (pinned), copies inside the timed region
     e2e = None
+    e2e_steps = min(args.steps, 200)
     if world == 1:
         hx = {key: torch.randn(key[1], key[0], generator=torch.Generator().manual_seed(5)).pin_memory() for key in xs}
         hy = {key: torch.empty(key[2], key[0]).pin_memory() for key in ys}
@@ -325,16 +375,50 @@ def run_ours(args):
             host_step(i)
         torch.cuda.synchronize(device)
         t0 = time.perf_counter()
-        for i in range(args.steps):
+        for i in range(e2e_steps):
             host_step(args.warmup + i)
         torch.cuda.synchronize(device)
-        dt = (time.perf_counter() - t0) / args.steps
+        dt = (time.perf_counter() - t0) / e2e_steps
         e2e = {"value": round(step_bytes() / dt / 1e9, 2), "unit": "GB/s",
                "h2d_bytes_per_step": int(sum(4 * m * k for _, k in SHAPES for m in BATCHES)),
                "d2h_bytes_per_step": int(sum(4 * m * n for n, _ in SHAPES for m in BATCHES)),
-               "ms_per_step": round(dt * 1e3, 4),
+               "ms_per_step": round(dt * 1e3, 4), "steps": e2e_steps,
                "path": "jq_linear_f32 with page-locked host x and y, one blocking call per linear: x (up to 1 MB) is read by the kernels "
                        "across PCIe in place, y up to 256 KB is written in place, larger y through a device-to-host copy"}
+    elif gather_kind == "peer":
+        # N > 1: every rank's process holds x in its own page-locked host memory and copies it in; the row-sharded linear with
+        # the peer exchange completes y on every rank; rank 0 reads the whole y back to its host memory. One call per linear,
+        # the stream synchronised after each (the result is needed on the host), max over ranks of the wall clock.
+        hx = {key: torch.randn(key[1], key[0], generator=torch.Generator().manual_seed(5)).pin_memory() for key in xs}
+        hy = {key: torch.empty(key[2], key[0] * world).pin_memory() for key in ys} if rank == 0 else {}
+        dx = {key: torch.empty_like(xs[key]) for key in xs}
+
+        def host_step(i):
+            for si, (n, k) in enumerate(SHAPES):
+                for mi, m in enumerate(BATCHES):
+                    w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
+                    dx[(k, m)].copy_(hx[(k, m)], non_blocking=True)
+                    full = peers[(n, k, m)].linear(w, dx[(k, m)])
+                    if rank == 0:
+                        hy[(n, k, m)].copy_(full, non_blocking=True)
+                    torch.cuda.current_stream(device).synchronize()
+
+        for i in range(args.warmup):
+            host_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            host_step(args.warmup + i)
+        barrier()
+        t = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+        e2e = {"value": round(step_bytes() / dt / 1e9, 2), "unit": "GB/s",
+               "h2d_bytes_per_step": int(world * sum(4 * m * k for _, k in SHAPES for m in BATCHES)),
+               "d2h_bytes_per_step": int(sum(4 * m * n for n, _ in SHAPES for m in BATCHES)),
+               "ms_per_step": round(dt * 1e3, 4), "steps": e2e_steps,
+               "path": "every rank copies x from its page-locked host memory, jq_linear_f32_peer (row shard + peer-store exchange), rank 0 copies "
+                       "the whole y to its host memory; one call and one stream synchronisation per linear, max over ranks"}
 
     prefill = prefill_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
     formats = formats_leg(torch, device, L, _lib) if (rank == 0 and world == 1 and not args.only) else None
@@ -358,7 +442,16 @@ def run_ours(args):
             decode_70b = decode_70b_leg(torch, device, rank, world)
         except Exception as exc:  # noqa: BLE001 - whatever it is, the sweep's numbers above are still valid
             decode_70b = {"error": "%s: %s" % (type(exc).__name__, exc)}
-    cpu = cpu_baseline_leg(threads=1, fraction=1, steps=2) if (rank == 0 and world == 1 and not args.no_cpu) else None
+    cpu = None
+    if rank == 0 and not args.no_cpu:
+        # the reference's CPU backend runs these operators on one thread (engine/CpuExecutor.java:233-239): that is the baseline;
+        # the same loops over all host cores are printed beside it as a courtesy figure. Thread counts are explicit: the
+        # environment (OMP_NUM_THREADS, which the multi-rank launcher sets to 1) does not change them.
+        cpu = cpu_baseline_leg(threads=1, fraction=8, steps=1)
+        cores = host_cores()
+        allc = cpu_baseline_leg(threads=cores, fraction=1 if cores >= 8 else 4, steps=1)
+        cpu["all_cores"] = {"value": allc["value"], "unit": "GB/s", "cores": cores, "sample": allc["sample"],
+                            "note": "the same loops split by output rows over every host core: something the reference does not do"}
 
     if rank == 0:
         peak, which = measured_peaks()
@@ -367,7 +460,7 @@ def run_ours(args):
             "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; 8 launches per step",
+            "config": {"workload": WORKLOAD,
                        "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32",
                        "l2": "every launch reads a different copy from a pool of %d copies per shape (%.0f MB > 126 MB L2)"
                              % (POOL_COPIES, POOL_COPIES * sum(n * k for n, k in SHAPES) * BYTES_PER_WEIGHT / 1e6),
@@ -375,10 +468,11 @@ def run_ours(args):
                        "parallelism": "single GPU" if world == 1 else "output rows split over %d GPUs + %s per launch" % (
                            world, "peer-store all-gather in the GEMV epilogue (jq_linear_f32_peer)" if gather_kind == "peer" else "NCCL all-gather")},
             "roofline": {"bound": "hbm", "achieved": round(value / world, 2), "peak": peak, "unit": "GB/s", "frac": round(value / world / peak, 4),
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and not args.only) else None,
+                         "traffic_source": NCU_TRAFFIC_SOURCE if (world == 1 and not args.only) else None, "peak_source": "of " + which, "frac_of_nominal_8TBps": round(value / world / 8000.0, 4),
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
-            "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "decode_70b": decode_70b, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "decode_70b": decode_70b, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "parity_check": parity_check, "timing": spread,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -491,7 +585,7 @@ LAYER_70B = [("wq", 8192, 8192), ("wk", 1024, 8192), ("wv", 1024, 8192), ("wo", 
 def sharded_layer_leg(torch, device, rank, world, L, _lib):
     """The seven linears of one 70B-shape decoder layer (BASELINE.json configs[4]: d 8192, 64 / 8 heads, FFN 28672, all
     Q4_K), each split by output rows over the ranks and completed on every rank by the peer-store exchange, at batch 1
-    and 16. Every rank quantises only its own rows (seeded by shape and rank); two copies per weight in rotation; one
+    and 16. Every rank quantises only its own rows of weights that are the same at every N (seeded by shape); two copies per weight in rotation; one
     CUDA graph per batch size holds two passes over the layer and is replayed. Reports microseconds per linear and per
     layer (max over ranks) and the layer's aggregate GB/s over the whole weights' bytes."""
     import torch.distributed as dist
@@ -502,9 +596,9 @@ def sharded_layer_leg(torch, device, rank, world, L, _lib):
         lo, hi = sharded.row_range(n, rank, world)
         copies = []
         for c in range(2):
-            g = torch.Generator(device=device).manual_seed(7000 + n + 3 * k + 17 * rank + c)
-            wf = torch.randn(hi - lo, k, generator=g, device=device) * 0.02
-            raw = synth.quantize_q4_k(wf).cpu().numpy()
+            g = torch.Generator(device=device).manual_seed(7000 + n + 3 * k + c)  # the same weight at every N: a rank takes its rows of it
+            wf = torch.randn(n, k, generator=g, device=device) * 0.02
+            raw = synth.quantize_q4_k(wf[lo:hi]).cpu().numpy()
             del wf
             copies.append(Tensor.quantized("Q4_K", raw, hi - lo, k, device=device.index))
         weights[name] = copies
@@ -582,17 +676,20 @@ def decode_70b_leg(torch, device, rank, world, shape=None):
     names = [("wq", dim, dim), ("wk", kv_dim, dim), ("wv", kv_dim, dim), ("wo", dim, dim), ("w1", hidden, dim), ("w3", hidden, dim), ("w2", dim, hidden)]
 
     def rows(n, k, seed):
+        # the model is the same at every N (seeded by weight, not by rank): a rank quantises its rows of it
         g = torch.Generator(device=device).manual_seed(seed)
-        wf = torch.randn(n // world, k, generator=g, device=device) * 0.02
-        return ("Q4_K", synth.quantize_q4_k(wf).cpu().numpy().reshape(-1), n // world, k)
+        wf = torch.randn(n, k, generator=g, device=device) * 0.02
+        per = n // world
+        return ("Q4_K", synth.quantize_q4_k(wf[rank * per:(rank + 1) * per]).cpu().numpy().reshape(-1), per, k)
 
-    sets = [{name: rows(n, k, 9000 + 100 * c + 10 * i + rank) for i, (name, n, k) in enumerate(names)} for c in range(min(4, layers))]
+    parity = sharded_decoder_check(torch, device, rank, world) if world > 1 else None
+    sets = [{name: rows(n, k, 9000 + 100 * c + 10 * i) for i, (name, n, k) in enumerate(names)} for c in range(min(4, layers))]
     ones = np.ones(dim, np.float32)
     for l in range(layers):
         w = {"layers.%d.%s" % (l, name): sets[l % len(sets)][name] for name, _, _ in names}
         dec.load(w, local=True)
         dec.load({"layers.%d.attention_norm" % l: ones, "layers.%d.ffn_norm" % l: ones})
-    dec.load({"output": rows(vocab, dim, 9900 + rank)}, local=True)
+    dec.load({"output": rows(vocab, dim, 9900)}, local=True)
     g = torch.Generator(device=device).manual_seed(2025)  # the same table on every rank
     dec.load({"norm": ones, "tok_embeddings": (torch.randn(vocab, dim, generator=g, device=device) * 0.02).cpu().numpy()})
     del sets
@@ -646,7 +743,56 @@ def decode_70b_leg(torch, device, rank, world, shape=None):
                       "SwiGLU kernels store the next linear's activation image into every rank, wo / w2 store their rows into every rank's "
                       "vector, the consumers wait for the flags themselves); batch 16: general kernels, rows 9-16 in a second pass over the "
                       "weights; both replayed as CUDA graphs" % (layers, world, prompt_len, gen - 2),
-            "first_tokens": {"batch16_seq0": out16[:6], "batch1": out1[:6]}}
+            "first_tokens": {"batch16_seq0": out16[:6], "batch1": out1[:6]}, "parity_check": parity}
+
+
+def sharded_decoder_check(torch, device, rank, world):
+    """Before the timed run at N > 1: a two-layer decoder of the 70B layer shape (d 8192, 64 / 8 heads, FFN 28672, vocab 32000,
+    all Q4_K, seeded) split over the ranks against the same decoder on this rank's GPU alone, on the general kernels
+    (option decoder_fused = 0), where both do the same arithmetic per output row: logits and greedy tokens of a prompt of 12
+    tokens and of 3 single-token steps must be bitwise equal on every rank."""
+    import numpy as np
+    import torch.distributed as dist
+    import jitnn_b200
+    from jitnn_b200 import LlamaDecoder, synth
+    layers, dim, heads, kv_heads, hidden, vocab = 2, 8192, 64, 8, 28672, 32000
+    kv_dim = kv_heads * (dim // heads)
+    L = jitnn_b200.load()
+    L.jq_set_option(b"decoder_fused", 0)
+    whole = LlamaDecoder(layers, dim, heads, kv_heads, hidden, vocab, max_seq=32, device=device.index)
+    split = LlamaDecoder(layers, dim, heads, kv_heads, hidden, vocab, max_seq=32, device=device.index, sharded=True)
+    g = torch.Generator(device=device).manual_seed(4242)
+    ones = np.ones(dim, np.float32)
+    for l in range(layers):
+        for name, n, k in [("wq", dim, dim), ("wk", kv_dim, dim), ("wv", kv_dim, dim), ("wo", dim, dim), ("w1", hidden, dim), ("w3", hidden, dim), ("w2", dim, hidden)]:
+            raw = synth.quantize_q4_k(torch.randn(n, k, generator=g, device=device) * 0.02).cpu().numpy().reshape(-1)
+            for d in (whole, split):
+                d.load({"layers.%d.%s" % (l, name): ("Q4_K", raw, n, k)})
+        for d in (whole, split):
+            d.load({"layers.%d.attention_norm" % l: ones, "layers.%d.ffn_norm" % l: ones})
+    raw = synth.quantize_q4_k(torch.randn(vocab, dim, generator=g, device=device) * 0.02).cpu().numpy().reshape(-1)
+    table = (torch.randn(vocab, dim, generator=g, device=device) * 0.02).cpu().numpy()
+    for d in (whole, split):
+        d.load({"output": ("Q4_K", raw, vocab, dim), "norm": ones, "tok_embeddings": table})
+    prompt = np.random.default_rng(3).integers(0, vocab, 12).astype(np.int32)
+    a, na = whole.forward(prompt, 0)
+    b, nb = split.forward(prompt, 0)
+    ok = bool(np.array_equal(a, b) and np.array_equal(na, nb))
+    tok, pos = int(na[-1]), 12
+    for _ in range(3):
+        a, na = whole.forward([tok], pos)
+        b, nb = split.forward([tok], pos)
+        ok = ok and bool(np.array_equal(a, b)) and int(na[0]) == int(nb[0])
+        tok, pos = int(na[0]), pos + 1
+    whole.close()
+    split.close()
+    L.jq_set_option(b"decoder_fused", 1)
+    t = torch.tensor([1 if ok else 0], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    all_ok = bool(int(t.item()))
+    assert all_ok, "the row-sharded decoder differs from the single-GPU decoder"
+    return {"against": "the same 2-layer 70B-shape decoder on one GPU, general kernels", "bitwise_equal": all_ok, "ranks_checked": world,
+            "tokens": 12 + 3}
 
 
 def decode_leg(torch, device, shape=None):
@@ -714,6 +860,14 @@ def decode_leg(torch, device, shape=None):
             "first_tokens": out[:8]}
 
 
+def host_cores():
+    """Cores this process may run on, whatever OMP_NUM_THREADS says."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_baseline_leg(threads, fraction, steps=1, warmup=0):
     """Times the CPU port of the reference's host loops on the sweep (rows [0, N/fraction) of every shape)."""
     import numpy as np
@@ -749,22 +903,24 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle
-    threads = max(1, min(oracle.max_threads(), os.cpu_count() or 1))
+    threads = host_cores()  # explicit: the launcher's OMP_NUM_THREADS does not decide this
     # size the per-step sample so that the whole run stays within about two minutes: time rows [0, N/64) once,
     # then take the largest power-of-two share of the rows that fits
     probe = cpu_baseline_leg(threads=threads, fraction=64, steps=1, warmup=0)
     total_steps = args.steps + min(args.warmup, 1)
     fraction = 1
-    while fraction < 64 and probe["seconds_per_step"] * 64 / fraction * total_steps > 120.0:
+    while fraction < 64 and probe["seconds_per_step"] * 64 / fraction * total_steps > 100.0:
         fraction *= 2
     cpu = cpu_baseline_leg(threads=threads, fraction=fraction, steps=args.steps, warmup=min(args.warmup, 1))
+    one = cpu_baseline_leg(threads=1, fraction=64, steps=1, warmup=0)
+    cpu["one_thread"] = {"value": one["value"], "unit": "GB/s", "cores": 1, "sample": one["sample"],
+                         "note": "the reference's CPU backend as shipped runs these operators on one thread (engine/CpuExecutor.java:233-239)"}
     line = {
         "impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(cpu["seconds_per_step"] * 1e3, 3), "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-        "config": {"workload": "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; rows [0, N/%d) of each" % fraction,
-                   "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32"},
+        "config": {"workload": WORKLOAD, "weights": "seeded N(0,0.02) quantised to Q4_K, x ~ N(0,1) fp32",
+                   "sample": "rows [0, N/%d) of every shape per step, %d host threads" % (fraction, threads)},
         "cpu_baseline": cpu, "e2e": {"value": cpu["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
