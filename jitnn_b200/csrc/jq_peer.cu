@@ -198,7 +198,7 @@ static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute* attr, unsigned grid, u
 // table slots hold, or written (by a one-thread kernel on `s`) into the next slot in turn.
 struct TableSlots {
     PeerOut held[PEER_TABLES];
-    int used, next;
+    int used;
 };
 static std::mutex g_table_mu;
 static std::map<const void*, TableSlots> g_table_cache;  // by this rank's buffer; forgotten when the buffer is freed
@@ -218,15 +218,19 @@ static int device_table(const PeerOut& po, cudaStream_t s, const PeerOut** out) 
             return JQ_OK;
         }
     }
-    const int slot = sl.next;
+    if (sl.used == PEER_TABLES) {
+        // a slot that has been handed out may be baked into a captured graph: it is never overwritten
+        return fail(JQ_ERR_INVALID, "peer exchange: this buffer already serves %d distinct (area, shard) targets, the most it has room for; "
+                                    "use another buffer (jq_peer_alloc) for more", PEER_TABLES);
+    }
+    const int slot = sl.used;
     PeerOut* dst = reinterpret_cast<PeerOut*>(own + PEER_TABLE_OFFSET + slot * PEER_TABLE_STRIDE);
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(attr, 1, 32, s);
     JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_table_kernel, po, dst));
     count_launch(1);
     sl.held[slot] = po;
-    sl.next = (slot + 1) % PEER_TABLES;
-    sl.used = sl.used < PEER_TABLES ? sl.used + 1 : PEER_TABLES;
+    sl.used++;
     *out = dst;
     return JQ_OK;
 }

@@ -17,8 +17,12 @@ cache or generation loop; the cached decode below computes exactly what its full
   * greedy token           ops/Reduce.java:201 (first index of the maximum)
 
 Every operator's result is rounded to float32 before the next one uses it, as the reference's engine does.
-Parity status: unpinned against a run of the reference (no JVM here, and its GGUF decode loop lives in the
-un-vendored jitllm); pinned only through the per-operator formulas cited above.
+Parity status: every operator function below (rmsnorm, rope, attend, silu / swiglu, embedding, greedy) is pinned by
+the reference's own golden vectors for it (rms_norm*, rope_heads, sdpa_bthd_causal, silu*, swiglu, embedding*,
+argmax of jitnn-core/src/test/resources/golden, extracted into tests/golden/golden_decoder_ops.npz and checked by
+tests/test_decoder_oracle_golden.py within Golden.java:483-498's tolerances), and the linears by the gguf_linear
+vectors; the composition follows Llama.java:167-222 line by line. What stays unpinned is an end-to-end run of
+the reference's GGUF decode loop, which lives in the un-vendored jitllm (no JVM here either).
 """
 import numpy as np
 
@@ -55,6 +59,34 @@ def rope(x, cos, sin, pos):
     return np.concatenate([(a * c - b * s), (a * s + b * c)], axis=-1).astype(np.float32)
 
 
+def attend(q, keys, values, group, scale):
+    """Causal attention of one position: q [heads, head_dim]; keys, values [positions so far, kv_heads * head_dim];
+    query head h reads key/value head h // group. Scores, softmax and the weighted sum in double."""
+    heads, hd = q.shape
+    y = np.empty((heads, hd), dtype=np.float32)
+    for h in range(heads):
+        kh = keys[:, (h // group) * hd:(h // group + 1) * hd].astype(np.float64)
+        vh = values[:, (h // group) * hd:(h // group + 1) * hd].astype(np.float64)
+        s = (kh @ q[h].astype(np.float64)) * scale
+        pr = np.exp(s - s.max())
+        pr /= pr.sum()
+        y[h] = (pr @ vh).astype(np.float32)
+    return y
+
+
+def silu(x):
+    xd = x.astype(np.float64)
+    return (xd / (1.0 + np.exp(-xd))).astype(np.float32)
+
+
+def swiglu(gate, up):
+    return (silu(gate) * up.astype(np.float32)).astype(np.float32)
+
+
+def embedding(table, token):
+    return table[token].astype(np.float32)
+
+
 class Decoder:
     """weights: dict name -> (type name, raw blocks uint8, n, k) for the linears, float32 arrays for norms and embeddings.
 
@@ -77,7 +109,7 @@ class Decoder:
         cfg = self.cfg
         hd, group = cfg.head_dim, cfg.heads // cfg.kv_heads
         scale = np.float64(np.float32(1.0 / np.sqrt(hd)))
-        x = self.w["tok_embeddings"][token].astype(np.float32)
+        x = embedding(self.w["tok_embeddings"], token)
         for l in range(cfg.layers):
             p = "layers.%d." % l
             n = rmsnorm(x, self.w[p + "attention_norm"], cfg.eps)
@@ -86,19 +118,10 @@ class Decoder:
             v = self.linear(p + "wv", n)
             self.k_cache[l, pos] = k.reshape(-1)
             self.v_cache[l, pos] = v
-            y = np.empty((cfg.heads, hd), dtype=np.float32)
-            for h in range(cfg.heads):
-                kh = self.k_cache[l, :pos + 1, (h // group) * hd:(h // group + 1) * hd].astype(np.float64)
-                vh = self.v_cache[l, :pos + 1, (h // group) * hd:(h // group + 1) * hd].astype(np.float64)
-                s = (kh @ q[h].astype(np.float64)) * scale
-                pr = np.exp(s - s.max())
-                pr /= pr.sum()
-                y[h] = (pr @ vh).astype(np.float32)
+            y = attend(q, self.k_cache[l, :pos + 1], self.v_cache[l, :pos + 1], group, scale)
             x = (x + self.linear(p + "wo", y.reshape(-1))).astype(np.float32)
             m = rmsnorm(x, self.w[p + "ffn_norm"], cfg.eps)
-            gate = self.linear(p + "w1", m).astype(np.float64)
-            silu = (gate / (1.0 + np.exp(-gate))).astype(np.float32)
-            act = (silu * self.linear(p + "w3", m)).astype(np.float32)
+            act = swiglu(self.linear(p + "w1", m), self.linear(p + "w3", m))
             x = (x + self.linear(p + "w2", act)).astype(np.float32)
         h = rmsnorm(x, self.w["norm"], cfg.eps)
         return self.linear("output", h)

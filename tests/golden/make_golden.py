@@ -12,6 +12,11 @@ Sources (paths inside the reference project):
     the 15 ``gguf_linear_*`` and 5 ``gguf_dequant_*`` cases written by scripts/pytorch/goldens.py
     (manifest format: ``case <name> <op> <attrs>`` lines, then ``<name> <role> <f32|i32> <offset>
     <dims...>`` lines addressing little-endian arrays in data.bin).
+  * the same two files -> golden_decoder_ops.npz: the cases of the operators the decoder is made of
+    (rms_norm*, rope_heads, sdpa_bthd_causal, silu*, swiglu, embedding*, argmax), inputs and expected
+    outputs only (the gradients are left out), which pin the decoder oracle operator by operator.
+  * jitnn-gguf/src/test/resources/gguf/fixture.gguf is also copied as it is (106 400 bytes): the reader tests
+    parse the reference's own file, not only files from this project's writer.
 The parser for the GGUF file is written here (header, metadata skip, tensor table) so that the
 extraction does not depend on any package.
 """
@@ -81,7 +86,11 @@ def read_gguf_tensors(path):
     return out
 
 
-def read_golden_cases(root):
+DECODER_CASES = ("rms_norm", "rms_norm_3d", "rms_norm_long", "rms_norm_rows", "rope_heads", "sdpa_bthd_causal", "silu", "silu_tails", "swiglu",
+                 "embedding", "embedding_padding", "embedding_wide", "argmax")
+
+
+def read_golden_cases(root, decoder_ops=False):
     res = os.path.join(root, "jitnn-core/src/test/resources/golden")
     blob = open(os.path.join(res, "data.bin"), "rb").read()
     cases, arrays = {}, {}
@@ -90,18 +99,20 @@ def read_golden_cases(root):
         if not p:
             continue
         if p[0] == "case":
-            if p[2] in ("gguf_linear", "gguf_dequant"):
-                cases[p[1]] = (p[2], [int(float(a)) for a in p[3:]])
+            if (p[1] in DECODER_CASES) if decoder_ops else (p[2] in ("gguf_linear", "gguf_dequant")):
+                cases[p[1]] = (p[2], [float(a) for a in p[3:]])
         elif p[0] in cases:
             name, role, kind, off = p[0], p[1], p[2], int(p[3])
+            if decoder_ops and (role.startswith("grad") or role == "w"):
+                continue
             dims = [int(d) for d in p[4:]]
             a = np.frombuffer(blob, dtype="<f4" if kind == "f32" else "<i4", count=int(np.prod(dims)), offset=off).reshape(dims)
-            if kind == "i32":
+            if kind == "i32" and not decoder_ops:
                 assert a.min() >= 0 and a.max() <= 255
                 a = a.astype(np.uint8)
             arrays["%s.%s" % (name, role)] = a.copy()
     for name, (op, attrs) in cases.items():
-        arrays["%s.attrs" % name] = np.array(attrs, dtype=np.int32)
+        arrays["%s.attrs" % name] = np.array(attrs, dtype=np.float64 if decoder_ops else np.int32)
     return arrays
 
 
@@ -115,7 +126,12 @@ def main(root):
     np.savez_compressed(os.path.join(HERE, "gguf_fixture.npz"), **keep)
     cases = read_golden_cases(root)
     np.savez_compressed(os.path.join(HERE, "golden_gguf_cases.npz"), **cases)
-    print("fixture tensors:", len(keep), "golden arrays:", len(cases))
+    ops = read_golden_cases(root, decoder_ops=True)
+    assert all(name + ".out" in ops for name in DECODER_CASES)
+    np.savez_compressed(os.path.join(HERE, "golden_decoder_ops.npz"), **ops)
+    with open(os.path.join(root, "jitnn-gguf/src/test/resources/gguf/fixture.gguf"), "rb") as src, open(os.path.join(HERE, "fixture.gguf"), "wb") as dst:
+        dst.write(src.read())
+    print("fixture tensors:", len(keep), "golden arrays:", len(cases), "decoder operator arrays:", len(ops))
 
 
 if __name__ == "__main__":

@@ -114,3 +114,76 @@ def test_weights_upload_from_the_mapping(tmp_path):
             assert np.array_equal(np.asarray(Gguf.dequantize(shard)), np.asarray(got)[1:3])
         with pytest.raises(ValueError, match="2-D tensor of a known type"):
             f.weight("odd.type")
+
+
+# ---- the reference's own fixture file (jitnn-gguf/src/test/resources/gguf/fixture.gguf, copied by tests/golden/make_golden.py) ----
+REFERENCE_FILE = os.path.join(GOLDEN, "fixture.gguf")
+
+
+def meta_kind(f, key):
+    import ctypes
+    from jitnn_b200 import _lib
+    vt, n, et = ctypes.c_int(), ctypes.c_int64(), ctypes.c_int()
+    _lib.check(f._lib.jq_gguf_meta_find(f._h, key.encode(), ctypes.byref(vt), ctypes.byref(n), ctypes.byref(et)))
+    return vt.value, n.value, et.value
+
+
+def test_reference_fixture_header_and_metadata_of_every_type():
+    """GgufFileTest.header and .metadataOfEveryType (GgufFileTest.java:41-86): version, alignment, the 13 value types."""
+    with gguf.GgufFile(REFERENCE_FILE) as f:
+        assert (f.version, f.alignment) == (3, 32)
+        assert f.data_offset % 32 == 0
+        assert len(f.tensors) == 30
+        assert f.string("general.architecture") == "llama"
+        assert f.number("test.u8") == 250 and f.number("test.i8") == -100
+        assert f.number("test.u16") == 60000 and f.number("test.i16") == -30000
+        assert f.number("test.u32") == 3_000_000_000 and f.number("test.i32") == -2_000_000_000
+        assert f.number("test.f32") == 1.5 and f.number("test.bool") == 1
+        assert f.string("test.string") == "héllo, wörld"
+        assert f.number("test.u64") == (1 << 40) + 3 and f.number("test.i64") == -(1 << 40)
+        assert f.number("test.f64") == 2.25
+        assert f.number("llama.block_count") == 2
+        # arrays: found with their element type and length (type ids of the GGUF specification: 4 u32, 5 i32, 6 f32, 7 bool, 8 string, 9 array, 12 f64)
+        assert meta_kind(f, "test.ints") == (9, 3, 5) and meta_kind(f, "test.floats") == (9, 2, 6)
+        assert meta_kind(f, "test.strings") == (9, 3, 8) and meta_kind(f, "test.bools") == (9, 2, 7)
+        assert meta_kind(f, "test.nested") == (9, 2, 9) and meta_kind(f, "test.u32s") == (9, 2, 4) and meta_kind(f, "test.f64s") == (9, 2, 12)
+        with pytest.raises(ValueError, match="no metadata key"):
+            f.string("llama.missing")
+        with pytest.raises(ValueError):
+            f.string("test.u8")
+
+
+def test_reference_fixture_tensor_table():
+    """GgufFileTest.shapesInJitnnOrder and .typesWithoutJitnnCounterpart (:88-113): shapes outermost first, 1-D / 3-D / I32
+    tensors, a block type this library has no kernels for."""
+    fx = np.load(FIXTURE)
+    with gguf.GgufFile(REFERENCE_FILE) as f:
+        q = f.info("w.Q4_K")
+        assert (q.shape, q.ggml_type, q.nbytes) == ((3, 512), 12, 3 * 512 // 256 * 144)
+        assert f.info("axes.1d").shape == (5,) and f.info("axes.3d").shape == (2, 3, 4)
+        assert np.array_equal(f.raw("axes.3d").view("<f4"), np.arange(24, dtype=np.float32))  # numpy's row-major order is jitNN's
+        assert np.array_equal(f.raw("axes.1d").view("<f4"), np.arange(5, dtype=np.float32))
+        ints = f.info("ints.I32")
+        assert ints.ggml_type == 26 and list(f.raw("ints.I32").view("<i4")) == [1, -2, 3, 4, 5, -6]
+        q8k = f.info("w.Q8_K")
+        assert q8k.ggml_type == 15 and q8k.nbytes == 3 * 512 // 256 * 292 and f.raw("w.Q8_K").size == q8k.nbytes
+        with pytest.raises(ValueError, match="no tensor"):
+            f.info("no.such.tensor")
+        for t in TYPE_IDS:  # the block tensors are byte for byte what make_golden.py extracted with its own parser
+            assert f.raw("w." + t).tobytes() == fx["w." + t].tobytes()
+            assert f.raw("expect." + t).tobytes() == fx["expect." + t].astype("<f4").tobytes()
+
+
+@pytest.mark.gpu
+def test_reference_fixture_uploads_and_dequantises_bit_exactly():
+    """Every block tensor of the reference's file, uploaded straight from the mapping, dequantises to its expect.<T> bit for bit;
+    the type without kernels is refused."""
+    from jitnn_b200 import Gguf, Quant
+    with gguf.GgufFile(REFERENCE_FILE) as f:
+        for t in TYPE_IDS:
+            w = f.weight("w." + t)
+            got = w.toFloatArray()
+            assert np.array_equal(got.view(np.uint32), f.raw("expect." + t).view(np.uint32)), t
+            w.release()
+        with pytest.raises(ValueError):
+            f.weight("w.Q8_K")

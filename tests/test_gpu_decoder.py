@@ -157,3 +157,37 @@ def test_shard_and_sequence_argument_checks():
     lg, nxt = dec.forward_batch([1, 2], 0)
     assert lg.shape == (2, cfg.vocab) and nxt.shape == (2,)
     dec.close()
+
+
+# ---- the benchmark's own widths: sliced activation images (k = 11008, 28672), the 32000-row argmax, grouped-query heads of the
+# 70B shape, the Q4_K + Q6_K mix; a prompt of a few tokens and four greedy steps against the oracle, fused and general kernels
+@pytest.mark.parametrize("fused", [1, 0])
+@pytest.mark.parametrize("layers,dim,heads,kv_heads,hidden,formats", [(2, 4096, 32, 32, 11008, None),
+                                                                      (1, 8192, 64, 8, 28672, {"wv": "Q4_K", "w2": "Q4_K", "output": "Q4_K"})])
+def test_full_width_decoder(layers, dim, heads, kv_heads, hidden, formats, fused):
+    import jitnn_b200
+    cfg = llama_oracle.Config(layers=layers, dim=dim, heads=heads, kv_heads=kv_heads, hidden=hidden, vocab=32000, max_seq=16)
+    weights = llama_oracle.random_model(cfg, seed=dim // 64, formats=formats)
+    jitnn_b200.load().jq_set_option(b"decoder_fused", fused)
+    try:
+        dec = LlamaDecoder(cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq, cfg.eps, cfg.rope_base)
+        dec.load(weights)
+        ref = llama_oracle.Decoder(cfg, weights, threads=8)
+        prompt = np.random.default_rng(dim).integers(0, cfg.vocab, 3).astype(np.int32)
+        ref_logits = np.stack([ref.forward(int(t), i) for i, t in enumerate(prompt)])
+        got, nxt = dec.forward(prompt, 0)
+        scale = np.abs(ref_logits).max()
+        assert np.abs(got - ref_logits).max() <= 2e-4 * scale, float(np.abs(got - ref_logits).max() / scale)
+        tok, pos, lr = llama_oracle.greedy(ref_logits[-1]), len(prompt), ref_logits[-1]
+        for _ in range(4):
+            top = np.sort(lr)[-2:]
+            if (top[1] - top[0]) > MARGIN * scale:
+                assert int(nxt[-1]) == tok, "greedy tokens diverge at position %d" % pos
+            lr = ref.forward(tok, pos)
+            lg, nxt = dec.forward([tok], pos)  # on the oracle's path, so that later positions stay comparable
+            assert np.abs(lg[0] - lr).max() <= 2e-4 * max(scale, np.abs(lr).max())
+            assert int(nxt[0]) == int(np.argmax(lg[0]))
+            tok, pos = llama_oracle.greedy(lr), pos + 1
+        dec.close()
+    finally:
+        jitnn_b200.load().jq_set_option(b"decoder_fused", 1)
