@@ -390,7 +390,7 @@ def run_ours(args):
         # the peer exchange completes y on every rank; rank 0 reads the whole y back to its host memory. One call per linear,
         # the stream synchronised after each (the result is needed on the host), max over ranks of the wall clock.
         hx = {key: torch.randn(key[1], key[0], generator=torch.Generator().manual_seed(5)).pin_memory() for key in xs}
-        hy = {key: torch.empty(key[2], key[0] * world).pin_memory() for key in ys} if rank == 0 else {}
+        hy = {key: torch.empty(key[2], key[0]).pin_memory() for key in ys} if rank == 0 else {}
         dx = {key: torch.empty_like(xs[key]) for key in xs}
 
         def host_step(i):
