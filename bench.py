@@ -327,6 +327,48 @@ def run_ours(args):
     stream = torch.cuda.current_stream(device)
     sp = ctypes.c_void_p(stream.cuda_stream)
 
+    # With several ranks: the same sweep without the exchange (every rank computes its rows into a private y), so that the
+    # line names what the exchange costs per linear at this N.
+    exchange = None
+    if world > 1 and gather_kind == "peer":
+        def shard_step(i):
+            sps = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+            for si, (n, k) in enumerate(SHAPES):
+                for mi, m in enumerate(BATCHES):
+                    w = pools[si][(i * len(BATCHES) + mi) % POOL_COPIES]
+                    _lib.check(L.jq_linear_f32(w._handle(), xs[(k, m)].data_ptr(), m, None, ys[(n, k, m)].data_ptr(), _lib.JQ_MEM_DEVICE, sps))
+        with torch.cuda.stream(side):
+            for i in range(period):
+                shard_step(i)
+            torch.cuda.synchronize(device)
+            runner = None
+            if use_graph:
+                runner = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(runner, stream=side):
+                    for i in range(period):
+                        shard_step(i)
+                runner.replay()
+            barrier()
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(20)]
+            for e0, e1 in ev:
+                e0.record(side)
+                for rep in range(timed_steps // period):
+                    if use_graph:
+                        runner.replay()
+                    else:
+                        for i in range(period):
+                            shard_step(i)
+                e1.record(side)
+            barrier()
+        tt = torch.tensor([e0.elapsed_time(e1) for e0, e1 in ev], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        alone = statistics.median(float(v) for v in tt.tolist()) / (timed_steps // period * period)
+        n_lin = len(SHAPES) * len(BATCHES)
+        exchange = {"ms_per_step_rows_only": round(alone, 5), "ms_per_step_with_exchange": round(ms_per_step, 5),
+                    "exchange_us_per_linear": round((ms_per_step - alone) * 1e3 / n_lin, 3),
+                    "note": "rows only = every rank multiplies its rows and keeps them (jq_linear_f32 on the shard); with exchange = jq_linear_f32_peer, "
+                            "whose kernel stores into every rank's y, announces its part and ends when all ranks' parts have arrived"}
+
     # per-shape kernel times (device-resident, same rotation, graph replay), for the roofline breakdown
     per_shape = {}
     if world == 1:
@@ -473,6 +515,7 @@ def run_ours(args):
                          "bytes_per_launch": round(step_bytes() / n_launch / world), "us_per_launch": round(ms_per_step * 1e3 / n_launch, 3),
                          "per_shape": per_shape},
             "formats": formats, "sharded_70b_layer": sharded_layer, "prefill": prefill, "decode": decode, "decode_70b": decode_70b, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "parity_check": parity_check, "timing": spread,
+            "exchange": exchange,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

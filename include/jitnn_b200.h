@@ -157,10 +157,12 @@ JQ_API int jq_device_status(int device, int* status);
 /*
  * Row-sharded linears over the GPUs of one box (one process per GPU): instead of Collective.allGather
  * (dist/Collective.java:64-65, NCCL form dist/NcclOp.java:184-198) every rank stores its slice of y directly into every
- * rank's copy of the full y over NVLink and raises a flag there; the rank's later work on `stream` starts after a
- * bounded wait for all ranks' flags. (No counterpart in the reference, which never shards a linear.)
+ * rank's buffer over NVLink, each value as one 8-byte word {value, number of the exchange} in the rank's staging area; the
+ * same kernel then collects the other ranks' slices from its own staging area into its y, polling each word (bounded)
+ * until it carries the number of this exchange. No fence and no atomic crosses NVLink, and the call's kernel ends when this
+ * rank's y is complete. (No counterpart in the reference, which never shards a linear.)
  *
- * jq_peer_alloc    a buffer on `device` for `payload_bytes` of gathered outputs (plus 2048 bytes of flags in front, at
+ * jq_peer_alloc    a buffer on `device` for `payload_bytes` of gathered outputs (plus 4096 bytes of flags in front, at
  *                  jq_peer_payload_offset() the payload starts) and its 64-byte CUDA IPC handle, which the caller sends
  *                  to the other ranks' processes by whatever channel it has.
  * jq_peer_open     maps another rank's buffer into this process (peer access is enabled on first use); jq_peer_close
@@ -168,11 +170,14 @@ JQ_API int jq_device_status(int device, int* status);
  * jq_peer_gather   enqueues on `stream`: y_r[0..m, col0 .. col0 + n_slice) = slice [m, n_slice] for every rank r, where
  *                  y_r [m, n_total] FP32 starts `payload_offset` bytes (a multiple of 16) into the payload of
  *                  peer_buffers[r] (entry `rank` is this rank's own buffer, the others come from jq_peer_open, all in
- *                  rank order); then the wait until the slices of all `world` (at most 8) ranks have arrived in this
- *                  rank's y. All ranks must make the same exchanges on a buffer in the same order, and the same y area
- *                  must not be the target of two exchanges in a row (alternate two areas, or use other buffers in
- *                  between): a rank may run one exchange ahead of another. A wait that gives up after about half a
- *                  second leaves status 32 + (missing rank) for jq_device_status. Works inside a captured CUDA graph.
+ *                  rank order) and the staging words [m, n_total] x 8 bytes start `staging_offset` bytes (a multiple of 16)
+ *                  into it, overlapping no y; the kernel ends when the slices of all `world` (at most 8) ranks have arrived
+ *                  in this rank's y. All ranks must make the same exchanges on a buffer in the same order, and the same
+ *                  (y, staging) area must not be the target of two exchanges in a row (alternate two areas, or use other
+ *                  buffers in between): a rank may run one exchange ahead of another. A thread that has waited
+ *                  "peer_wait_us" (option, default 400 000) in all leaves status 32 + r for jq_device_status, r being the
+ *                  rank that owns the missing column when the n_total columns are split evenly, and the kernel returns
+ *                  with that part of y unwritten. Works inside a captured CUDA graph.
  */
 JQ_API int jq_peer_alloc(int device, int64_t payload_bytes, void** ptr, void* handle_out);
 JQ_API int jq_peer_open(int device, const void* handle, void** ptr);
@@ -180,16 +185,17 @@ JQ_API int jq_peer_close(void* ptr);
 JQ_API int jq_peer_free(void* ptr);
 JQ_API int64_t jq_peer_payload_offset(void);
 JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers,
-                          int64_t payload_offset, int rank, int world, void* stream);
+                          int64_t payload_offset, int64_t staging_offset, int rank, int world, void* stream);
 /*
- * The sharded linear in one call: y_r[0..m, col0 .. col0 + n_w) = x W_shard^T (+ bias) for every rank r, then the wait,
- * with w this rank's row shard (n_w rows, uploaded with jq_weight_upload_rows), x [m, k] and bias [n_w] device
- * pointers, and the buffers as for jq_peer_gather. For Q4_K with m <= 8 the GEMV kernel itself stores into every
- * rank's y and publishes the exchange (no slice buffer, no copy kernel); other formats and row counts run the ordinary
- * kernels into a scratch slice followed by the copy kernel.
+ * The sharded linear in one call: y_r[0..m, col0 .. col0 + n_w) = x W_shard^T (+ bias) for every rank r, complete on
+ * this rank when the call's last kernel ends, with w this rank's row shard (n_w rows, uploaded with
+ * jq_weight_upload_rows), x [m, k] and bias [n_w] device pointers, and the buffers and offsets as for jq_peer_gather.
+ * For Q4_K and Q5_K with m <= 8 the GEMV kernel itself stores into every rank's buffer and collects the other ranks'
+ * rows (no slice buffer, no copy kernel); other formats and row counts run the ordinary kernels into a scratch slice
+ * followed by the copy kernel.
  */
 JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, const float* bias, int64_t n_total, int64_t col0,
-                              void* const* peer_buffers, int64_t payload_offset, int rank, int world, void* stream);
+                              void* const* peer_buffers, int64_t payload_offset, int64_t staging_offset, int rank, int world, void* stream);
 
 /*
  * blocks_out[count/32*34] = Q8_0 blocks of x[count] (count % 32 == 0), following the reference's host

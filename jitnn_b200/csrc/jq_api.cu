@@ -191,7 +191,7 @@ std::atomic<int64_t> g_opt_decoder_graph{1};
 std::atomic<int64_t> g_opt_decoder_fused{1};
 
 // ---- linear on device pointers --------------------------------------------------------------------
-int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s) {
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s, bool x_remote) {
     View v = view_of(w);
     const int64_t min_rows = g_prefill_min_rows.load();
     if (min_rows > 0 && m >= min_rows && prefill_supported(v)) {
@@ -217,7 +217,7 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
                               : ((tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16)));
     for (int64_t m0 = 0; m0 < m; m0 += group) {
         int rows = (int)(m - m0 < group ? m - m0 : group);
-        int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s);
+        int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s, x_remote);
         if (rc != JQ_OK) {
             return rc;
         }
@@ -495,7 +495,7 @@ int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bi
         if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0) {
             return fail(JQ_ERR_INVALID, "%s linear: device pointers must be 16-byte aligned", type_name(w->type));
         }
-        return linear_device(w, x, m, bias, y, (cudaStream_t)stream);
+        return linear_device(w, x, m, bias, y, (cudaStream_t)stream, false);
     }
     if (mem != JQ_MEM_HOST) {
         return fail(JQ_ERR_INVALID, "%s linear: unknown memory kind %d", type_name(w->type), mem);
@@ -525,7 +525,7 @@ int jq_linear_f32(const jq_weight* w, const float* x, int64_t m, const float* bi
     if (copy_y) {
         dy = (float*)(st->dev + xb + bb);
     }
-    rc = linear_device(w, dx, m, db, dy, st->stream);
+    rc = linear_device(w, dx, m, db, dy, st->stream, dx == x);  // x in host memory: read it once, not once per thread block
     if (rc != JQ_OK) {
         return rc;
     }
@@ -740,6 +740,13 @@ int jq_set_option(const char* name, int64_t value) {
         g_opt_wait_limit_us.store(value);
         return JQ_OK;
     }
+    if (name != nullptr && strcmp(name, "peer_wait_us") == 0) {
+        if (value < 1 || value > 60000000) {
+            return fail(JQ_ERR_INVALID, "option peer_wait_us: %lld is outside [1, 60000000]", (long long)value);
+        }
+        g_opt_peer_wait_us.store(value);
+        return JQ_OK;
+    }
     if (name != nullptr && strcmp(name, "decoder_graph") == 0) {
         g_opt_decoder_graph.store(value != 0);
         return JQ_OK;
@@ -766,6 +773,10 @@ int jq_get_option(const char* name, int64_t* value) {
     }
     if (name != nullptr && value != nullptr && strcmp(name, "wait_limit_us") == 0) {
         *value = g_opt_wait_limit_us.load();
+        return JQ_OK;
+    }
+    if (name != nullptr && value != nullptr && strcmp(name, "peer_wait_us") == 0) {
+        *value = g_opt_peer_wait_us.load();
         return JQ_OK;
     }
     if (name != nullptr && value != nullptr && strcmp(name, "decoder_graph") == 0) {

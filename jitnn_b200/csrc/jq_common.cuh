@@ -109,7 +109,8 @@ int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verba
 // Verbatim blocks [n, kb] <-> the tiled layout of Q4_K and Q5_K (`tiled` holds tiled_rows(n) rows).
 int launch_tile(int type, const uint8_t* verbatim, uint8_t* tiled, int64_t n, int64_t kb, bool inverse, cudaStream_t s);
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
-int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s);
+// x_remote: x lies in host memory that the GPU reads across PCIe; kernels then read it once instead of once per thread block.
+int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool x_remote = false);
 // gx [m, k] = g [m, n] . dequant(W) (jq_backward.cu).
 int launch_linear_backward(const View& v, const float* g, int64_t m, float* gx, cudaStream_t s);
 int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStream_t s);
@@ -118,15 +119,20 @@ int launch_quantize_q8_0(const float* x, int64_t blocks, uint8_t* out, cudaStrea
 struct PeerOut {
     float* y[8];         // every rank's y [m, n_total] (this rank's included)
     uint32_t* flags[8];  // every rank's flag words
+    unsigned long long* stage[8];  // every rank's staging words [m, n_total] (value and exchange number in one 8-byte word), or null:
+                                   // the outputs then go straight into y and the exchange is announced through the arrival counters
     int world, rank;
     int64_t n_total, col0;  // this rank's rows are columns col0 .. of y
+    int64_t n_own;          // how many of them: rows of this rank's shard
     const PeerOut* table;   // host side only: where a copy of this struct lives in device memory
-    int wait_first;         // the kernel's input is what this rank's latest exchange delivered: wait for all ranks' flags before reading it
+    int wait_first;         // the kernel's input is what this rank's latest exchange delivered: wait for all ranks' parts before reading it
+    int wait_after;         // the kernel ends only when all ranks' parts of its own exchange have arrived in this rank's y (bounded wait by one CTA)
+    long long wait_clocks;  // clocks a thread waits in all for the other ranks' marked words
 };
 // Integer tensor-core GEMV (mma.sync) for Q4_K and Q5_K, rows <= 8 (jq_gemv_q4k_i8.cu); *handled = false leaves the call to
 // another kernel. `image` is scratch of gemv_q4k_i8_scratch_bytes(k, rows) bytes.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
-                       const PeerOut* peer = nullptr);
+                       const PeerOut* peer = nullptr, bool x_remote = false);
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 // The same for one row of x whose activation image (jq_q4k_image.cuh) a kernel earlier in the stream has already written; a
 // second Q4_K weight with the same k can ride in the same launch.
@@ -138,7 +144,6 @@ int gemv_peer_status(int* status);
 // Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
 // rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
-int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s);
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
                            int rank, int world, cudaStream_t s, bool wait_first, bool wait_after);
 // Status word of the waits that the decoder's kernels make themselves (peer_wait_inline): 0 or 32 + rank, cleared by the call.
@@ -174,6 +179,7 @@ int gemv_umma_status(int* status);
 extern std::atomic<int64_t> g_opt_gemv_umma;
 // Option "wait_limit_us": microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up.
 extern std::atomic<int64_t> g_opt_wait_limit_us;
+extern std::atomic<int64_t> g_opt_peer_wait_us;  // microseconds a thread waits in all for the other ranks' values of a sharded linear
 
 // Rows of zero padding behind every uploaded weight plane: kernels that work on 16-row tiles read past n.
 constexpr int PAD_ROWS = 16;

@@ -19,7 +19,7 @@
 
 namespace jq {
 
-int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s);
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s, bool x_remote = false);
 
 namespace {
 
@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     __syncthreads();
     if (!last_flag) {
         if constexpr (PEER) {
-            peer_publish(pi.flags, pi.rank, pi.world, &last_flag);
+            peer_publish(pi.flags, pi.rank, pi.world);
         }
         return;
     }
@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
         }
     }
     if constexpr (PEER) {
-        peer_publish(pi.flags, pi.rank, pi.world, &last_flag);
+        peer_publish(pi.flags, pi.rank, pi.world);
     }
 }
 
@@ -613,7 +613,6 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
 template <bool PEER>
 __global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im, PeerImage pi) {
     __shared__ __align__(16) float xs[256];
-    __shared__ int last_word;
     pdl_enter();
     const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
     const float g = gate[i];
@@ -628,7 +627,7 @@ __global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restri
         }
     }
     if constexpr (PEER) {
-        peer_publish(pi.flags, pi.rank, pi.world, &last_word);
+        peer_publish(pi.flags, pi.rank, pi.world);
     }
 }
 
@@ -794,7 +793,8 @@ struct jq_decoder {
     int world, rank;
     void* peer_buf[8];
     int64_t area[8];  // payload offsets: attention output, wo output, SwiGLU output, w2 output, logits; the Q4_K activation
-                      // images of the attention output and of the SwiGLU output; [7] = the end
+                      // images of the attention output and of the SwiGLU output; [7] = the end of those
+    int64_t stage[6]; // payload offsets of the staging words (8 bytes per element) of the five gathered activations; [5] = the end
 };
 
 using namespace jq;
@@ -906,6 +906,11 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
         d->area[6] = off;
         off += ((int64_t)q4k_image_bytes_one_row(hidden) + 511) / 256 * 256;
         d->area[7] = off;
+        for (int i = 0; i < 5; i++) {
+            d->stage[i] = off;
+            off += ((int64_t)MAX_TOKENS * widths[i] * 8 + 255) / 256 * 256;
+        }
+        d->stage[5] = off;
     }
     const size_t kv_dim = (size_t)kv_heads * head_dim, T = MAX_TOKENS;
     d->splits = (max_seq + ATT_CHUNK - 1) / ATT_CHUNK;
@@ -979,7 +984,7 @@ JQ_API int jq_decoder_peer_bytes(const jq_decoder* d, int64_t* payload_bytes) {
     if (payload_bytes == nullptr) {
         return fail(JQ_ERR_INVALID, "jq_decoder_peer_bytes: null result pointer");
     }
-    *payload_bytes = d->area[7];
+    *payload_bytes = d->stage[5];
     return JQ_OK;
 }
 
@@ -1402,12 +1407,12 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
     };
     auto PEER_LIN = [&](const jq_weight* w, const float* in, int64_t n_total, int64_t n_local, int area) {
         if (rc == JQ_OK) {
-            rc = jq_linear_f32_peer(w, in, T, nullptr, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->rank, G, s);
+            rc = jq_linear_f32_peer(w, in, T, nullptr, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->stage[area], d->rank, G, s);
         }
     };
     auto GATHER = [&](const float* slice, int64_t n_total, int64_t n_local, int area) {
         if (rc == JQ_OK) {
-            rc = jq_peer_gather(slice, T, n_local, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->rank, G, s);
+            rc = jq_peer_gather(slice, T, n_local, n_total, d->rank * n_local, d->peer_buf, d->area[area], d->stage[area], d->rank, G, s);
         }
     };
     auto LAUNCHED = [&](const char* name) {

@@ -88,7 +88,7 @@ static int by_rows(const View& v, const float* x, int rows, const float* bias, f
 }
 
 // rows in [1, 16].
-int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s) {
+int launch_gemv(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, bool x_remote) {
     if (v.n == 0) {
         return JQ_OK;
     }
@@ -104,7 +104,7 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
         uint8_t* image = nullptr;
         int rc = need > 0 ? scratch_for(s, need, &image) : JQ_OK;
         if (rc == JQ_OK) {
-            rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, image, &handled);
+            rc = launch_gemv_q4k_i8(v, x, rows, bias, y, s, image, &handled, nullptr, x_remote);
         }
         if (rc != JQ_OK || handled) {
             return rc;

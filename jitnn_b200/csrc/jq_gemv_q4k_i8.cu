@@ -23,17 +23,22 @@
 //
 // Work split: a CTA of 8 warps (16 for three to eight rows of x, where one CTA per SM shares one copy of the large
 // image) owns 16 output rows at a time (tiles blockIdx.x, blockIdx.x + gridDim.x, ...), warp p takes super-blocks
-// b = p (mod warps). Weights stream HBM -> shared memory through a per-warp ring of cp.async slots; consecutive lanes
-// copy consecutive 16-byte chunks, so every 32-byte sector is requested once, and the slot layout is swizzled so that
-// the 8-byte fragment reads are conflict free. The weight buffer is padded by 16 rows, which lets the last tile read
-// past n without a bounds check (the tiled layout pads the last 128 rows with zeros). The GEMV kernel is launched with programmatic stream serialization: it requests its
-// first weights while the activation kernel is still running and waits for it (griddepcontrol.wait) only before
-// copying the image into shared memory.
+// b = p (mod warps). Weights stream HBM -> shared memory through a per-warp ring of slots: the 16 rows of a tile and one
+// super-block are one contiguous run of bytes in the tiled device layout, which one lane requests with a single bulk copy
+// (cp.async.bulk) that completes on the slot's mbarrier. A slot holds the rows as they are in global memory; lane group g
+// works on rows 2 (g & 3) + (g >> 2) and eight further, which makes the 8-byte fragment reads conflict free (the row
+// pitch of 144 or 176 bytes advances 4 or 12 banks per row). The tiled layout pads the last 128 rows with zeros, so the
+// last tile needs no bounds check. The kernel is launched with programmatic stream serialization: it requests its first
+// weights while the kernel before it is still running and waits for it (griddepcontrol.wait) only before it touches x or
+// the image. With one or two rows of x that are given as floats the kernel builds the image itself: every warp makes
+// exactly the super-blocks it consumes, straight from x, so there is no image kernel, no scratch round trip and no
+// barrier between warps for it.
 #include <mutex>
 
 #include "jq_formats.cuh"
 #include "jq_peer_device.cuh"
 #include "jq_q4k_image.cuh"
+#include "jq_tc.cuh"
 
 namespace jq {
 
@@ -42,32 +47,20 @@ using q4k::build_image;
 
 namespace {
 
-// One super-block of 16 rows in a ring slot: 16 x 128 bytes of nibbles, then the 16 headers, then (Q5_K) 16 x 32 bytes of
-// fifth bits. The kernel is written for Q4_K; Q5_K (template flag Q5) is the same format with one more bit per quant.
-constexpr int SLOT_HEADERS = 16 * 128;
-constexpr int SLOT_QH = 16 * 144;
+// One super-block of 16 rows in a ring slot, as in global memory: per row the 16-byte header, (Q5_K) 32 bytes of fifth
+// bits, 128 bytes of nibbles. The kernel is written for Q4_K; Q5_K (template flag Q5) is the same format with one more
+// bit per quant.
 template <bool Q5>
 struct Blk {
-    static constexpr int BYTES = Q5 ? 176 : 144;           // bytes per super-block and row
+    static constexpr int BYTES = Q5 ? 176 : 144;  // bytes per super-block and row
     static constexpr int SLOT = 16 * BYTES;
-    static constexpr int CPR = BYTES / 16;                 // 16-byte chunks per row
-    static constexpr int PER_LANE = (16 * CPR + 31) / 32;  // the last one only by lanes 0-15
+    static constexpr int QH = 16;                  // offset of the fifth bits in a row (Q5_K)
+    static constexpr int QS = Q5 ? 48 : 16;        // offset of the nibbles
 };
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
-// The same copy under a predicate, without a branch around it.
-__device__ __forceinline__ void cp_async16_if(uint32_t dst_smem, const void* src, int on) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %2, 0;\n"
-        "@p cp.async.cg.shared.global [%0], [%1], 16;\n"
-        "}\n" ::"r"(dst_smem),
-        "l"(src), "r"(on)
-        : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -112,6 +105,25 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q4k_activation_image_kernel(c
     }
 }
 
+// Development aid, compiled in with -DJQ_Q4K_TRACE: thread 0 of every CTA records %globaltimer at a few points of the kernel
+// into the next free record; jq_debug_q4k_trace copies the records out.
+#ifdef JQ_Q4K_TRACE
+constexpr int TRACE_SLOTS = 16384;
+__device__ long long g_q4k_tr[TRACE_SLOTS * 8];
+__device__ int g_q4k_ticket;
+__device__ __forceinline__ long long gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define QT(k)                                        \
+    do {                                             \
+        if (threadIdx.x == 0) g_q4k_tr[tslot * 8 + (k)] = gtime(); \
+    } while (0)
+#else
+#define QT(k) do { } while (0)
+#endif
+
 // ---- the GEMV ---------------------------------------------------------------------------------------------------
 // A second weight with the same k that is multiplied with the same x in the same launch (q = nullptr: none).
 struct Second {
@@ -123,10 +135,12 @@ struct Second {
 
 // PEER: the outputs go into every rank's y of a row-sharded linear (jq_peer.cu) instead of y. A template flag, not a
 // run-time branch: the mere presence of the peer stores in the epilogue cost the ordinary kernel a fifth of its speed.
-template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
-__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const PeerOut* __restrict__ peerp, const uint8_t* __restrict__ image, int rows,
-                                                                  const float* __restrict__ bias, float* __restrict__ y, int tiles,
-                                                                  int KS, int max_tiles) {
+// FUSED: `xin` holds the rows of x as floats and every warp builds the image of its own super-blocks; otherwise `image`
+// holds the image, written by a kernel earlier in the stream.
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER, bool FUSED>
+__global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Second w2, const PeerOut* __restrict__ peerp, const uint8_t* __restrict__ image,
+                                                                  const float* __restrict__ xin, int rows, const float* __restrict__ bias, float* __restrict__ y,
+                                                                  int tiles, int KS, int max_tiles, long long wait_clocks) {
     // Tiles 0 .. w2.first_tiles - 1 are rows of v, the tiles from w2.first_tiles on rows of the second weight w2 (same k,
     // same x, its own output), if there is one.
     // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
@@ -140,57 +154,63 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     extern __shared__ __align__(16) uint8_t smem_raw[];
     asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef JQ_Q4K_TRACE
+    int tslot = 0;
+    if (tid == 0) {
+        tslot = atomicAdd(&g_q4k_ticket, 1) % TRACE_SLOTS;
+        g_q4k_tr[tslot * 8 + 6] = (long long)v.q | (blockIdx.x == 0 ? 1 : 0);
+        g_q4k_tr[tslot * 8 + 7] = 0;
+    }
+    QT(0);
+#endif
     const int g = lane >> 2, t = lane & 3;
+    const int R = 2 * (g & 3) + (g >> 2);  // this lane's rows of the tile: R and R + 8
     const int KB = (int)(v.k >> 8);
     const int nslices = (KB + KS - 1) / KS;
-    uint8_t* img = smem_raw;                                                         // [KS][PB]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][NW][16][MT]
+    constexpr int BAR_BYTES = NW * STAGES * 8;                                       // one mbarrier per slot
+    static_assert(BAR_BYTES % 16 == 0, "what follows the barriers stays 16-byte aligned");
+    uint8_t* img = smem_raw + BAR_BYTES;                                             // [KS][PB]
+    float* red = reinterpret_cast<float*>(img + (size_t)KS * C::PB);                 // [2][NW][16][MT]
     float* carry = red + 2 * NW * 16 * MT;                                           // [max_tiles][16][MT], only if nslices > 1
     uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) + (size_t)warp * RING_BYTES;
-    const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
+    const uint32_t ring_s = tc::smem_u32(ring);
+    const uint32_t bars_s = tc::smem_u32(smem_raw) + (uint32_t)(warp * STAGES * 8);  // this warp's barriers
     // The weight is stored tile by tile (jq_common.cuh): the 16 rows of a tile of this kernel and one super-block are 16 x BYTES
     // consecutive bytes inside a unit of 128 rows, and the units of consecutive super-blocks follow each other.
     constexpr int64_t UNIT = (int64_t)TILE_ROWS * B::BYTES;
 
-    // ---- weight stream: chunk c = lane + 32 i of the 144 (Q5_K: 176) chunks (16 rows x 9 or 11) of a super-block ------
-    // Slot layout: row r's 128 bytes of nibbles at r * 128 with its four 32-byte segments permuted by r & 3
-    // (segment p sits at position p ^ (r & 3)), the 16 headers behind them.
-    constexpr int NI = B::PER_LANE;
-    uint32_t dst_off[NI];
+    // ---- weight stream: one bulk copy per step, requested by lane 0, complete when the slot's barrier says so -----------
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < NI; i++) {
-        const int c = lane + 32 * i, r = c / B::CPR, ch = c % B::CPR;
-        const int first_q = Q5 ? 3 : 1;  // chunk 0: header; Q5_K chunks 1, 2: fifth bits; then the 8 chunks of nibbles
-        dst_off[i] = ch == 0 ? (uint32_t)(SLOT_HEADERS + r * 16)
-                             : (ch < first_q ? (uint32_t)(SLOT_QH + r * 32 + (ch - 1) * 16)
-                                             : (uint32_t)(r * 128 + ((((ch - first_q) >> 1) ^ (r & 3)) << 5) + ((ch - first_q) & 1) * 16));
+        for (int s = 0; s < STAGES; s++) {
+            tc::mbar_init(bars_s + 8 * s, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");  // the copy engine sees initialised barriers
     }
-    const int low16 = lane < 16;
+    __syncwarp();
     // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + NW i.
     const int len_last = KB - (nslices - 1) * KS;
     const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + NW - 1) / NW : 0) : 0;
     const int nb_last = warp < len_last ? (len_last - warp + NW - 1) / NW : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    // this lane's first chunk of tile number ti of the CTA, first block of this warp in slice sl
-    auto lane_ptr = [&](int ti, int sl) {
+    // the slot of tile number ti of the CTA, first block of this warp in slice sl
+    auto step_ptr = [&](int ti, int sl) {
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
         const int local = tile < w2.first_tiles ? tile : tile - w2.first_tiles;
         const uint8_t* base = tile < w2.first_tiles ? v.q : w2.q;
-        return base + ((int64_t)(local >> 3) * KB + (sl * KS + warp)) * UNIT + (local & 7) * 16 * B::BYTES + lane * 16;
+        return base + ((int64_t)(local >> 3) * KB + (sl * KS + warp)) * UNIT + (local & 7) * 16 * B::BYTES;
     };
-    const uint8_t* gp = lane_ptr(0, 0);
+    const uint8_t* gp = step_ptr(0, 0);
     int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
     int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
-    uint32_t iss_slot = 0;
-    auto issue = [&]() {
+    int iss_slot = 0;
+    auto issue = [&]() {  // every lane keeps the bookkeeping, lane 0 makes the request
         if (iss_left > 0) {
             iss_left--;
-            const uint32_t slot = ring_s + iss_slot;
-#pragma unroll
-            for (int i = 0; i < NI - 1; i++) {
-                cp_async16(slot + dst_off[i], gp + 512 * i);
+            if (lane == 0) {
+                tc::mbar_expect_tx(bars_s + 8 * iss_slot, SLOT_BYTES);
+                tc::bulk_load(ring_s + iss_slot * SLOT_BYTES, gp, SLOT_BYTES, bars_s + 8 * iss_slot);
             }
-            cp_async16_if(slot + dst_off[NI - 1], gp + 512 * (NI - 1), low16);
             gp += NW * UNIT;
             if (++iss_j == iss_nb) {
                 iss_j = 0;
@@ -199,21 +219,27 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
                     iss_sl++;
                     iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
                 }
-                gp = lane_ptr(iss_ti, iss_sl);
+                gp = step_ptr(iss_ti, iss_sl);
             }
         }
-        iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
-        cp_async_commit();
+        iss_slot = iss_slot + 1 == STAGES ? 0 : iss_slot + 1;
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
-        issue();  // the first weights are on their way before the activation image is complete
+        issue();  // the first weights are on their way before x or the activation image is complete
     }
 
-    // ---- the activation image is complete once the kernel that writes it has finished ----------------------------
+    // ---- x (or the image made from it) is complete once the kernel before this one has finished --------------------------
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t img_s = (uint32_t)__cvta_generic_to_shared(img);
+    QT(1);
+    const uint32_t img_s = tc::smem_u32(img);
+    bool peer_marks = false;  // the outputs travel as marked words (jq_peer_device.cuh) rather than behind a release
+    uint32_t peer_seq = 0;
     if constexpr (PEER) {
+        peer_marks = peerp->stage[0] != nullptr;
+        if (peer_marks) {
+            peer_seq = peer_marks_seq(peerp);
+        }
         if (peerp->wait_first) {
             // the image is what the ranks' latest exchange delivered: complete once all their flags are up
             if (warp == 0) {
@@ -228,13 +254,9 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     const uint8_t* xd_lane = img + ((size_t)(NCOL == 8 ? g : g % NCOL) * 4 + t) * 16;
     const uint8_t* xm_lane = img + C::XD + ((size_t)(NCOLM == 8 ? g : g % NCOLM) * 4 + t) * 4;
     const uint8_t* tab_lane = img + C::XD + C::XM;
-    uint32_t qoff[4];  // this lane's 8 bytes of group j inside a row of the slot
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        qoff[j] = (uint32_t)(((j ^ (g & 3)) << 5) + 8 * t);
-    }
+    const int row_off = R * B::BYTES;  // this lane's first row inside a slot
     const bool mins_low = (t & 1) == 0;  // lanes t = 0, 2 feed mins 0..3, lanes 1, 3 mins 4..7 (slots 2, 3 meet zeros)
-    // Packed: acc[group][row g / g + 8][column 2t / 2t + 1] and accm[mins group][row]. Digit major: acc[0][row][row of x].
+    // Packed: acc[group][row R / R + 8][column 2t / 2t + 1] and accm[mins group][row]. Digit major: acc[0][row][row of x].
     constexpr int NACC = C::DIGIT_MAJOR ? 1 : NG, NACCM = C::DIGIT_MAJOR ? 1 : NGM;
     float acc[NACC][2][2];
     float accm[NACCM][2];
@@ -248,10 +270,12 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     }
 
     auto compute = [&](const uint8_t* slot, const uint8_t* blk) {  // blk = this lane's view of the super-block's image
-        const uint8_t* q0 = slot + g * 128;
-        const uint8_t* q1 = q0 + 8 * 128;
-        const uint4 h0 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + g * 16);
-        const uint4 h1 = *reinterpret_cast<const uint4*>(slot + SLOT_HEADERS + (g + 8) * 16);
+        const uint8_t* r0 = slot + row_off;     // row R of the tile: header, (fifth bits,) nibbles
+        const uint8_t* r1 = r0 + 8 * B::BYTES;  // row R + 8
+        const uint8_t* q0 = r0 + B::QS + 8 * t;
+        const uint8_t* q1 = r1 + B::QS + 8 * t;
+        const uint4 h0 = *reinterpret_cast<const uint4*>(r0);
+        const uint4 h1 = *reinterpret_cast<const uint4*>(r1);
         // 6-bit scales and mins of the 8 sub-blocks as packed bytes: [0..3] and [4..7]
         const uint32_t sc0a = h0.y & 0x3f3f3f3fu, sc0b = and_or(h0.y >> 2, 0x30303030u, h0.w & 0x0f0f0f0fu);
         const uint32_t sc1a = h1.y & 0x3f3f3f3fu, sc1b = and_or(h1.y >> 2, 0x30303030u, h1.w & 0x0f0f0f0fu);
@@ -260,11 +284,11 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
         // Packed layouts keep the high nibbles in place (one AND, no shift): the odd sub-blocks' products come out 16 times
         // too large, are summed apart from the even ones' and meet them as 16 even + odd; the column weights carry the 1 / 16.
         constexpr bool SPLIT = !C::DIGIT_MAJOR && !Q5;
-        // Q5_K: the fifth bits of this lane's elements 8t .. 8t+7 of every sub-block, rows g and g + 8 (bit `sub` of each byte)
+        // Q5_K: the fifth bits of this lane's elements 8t .. 8t+7 of every sub-block, rows R and R + 8 (bit `sub` of each byte)
         uint2 qh0 = make_uint2(0u, 0u), qh1 = make_uint2(0u, 0u);
         if constexpr (Q5) {
-            qh0 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + g * 32 + 8 * t);
-            qh1 = *reinterpret_cast<const uint2*>(slot + SLOT_QH + (g + 8) * 32 + 8 * t);
+            qh0 = *reinterpret_cast<const uint2*>(r0 + B::QH + 8 * t);
+            qh1 = *reinterpret_cast<const uint2*>(r1 + B::QH + 8 * t);
         }
         int I[NG][4], IO[SPLIT ? NG : 1][4];
 #pragma unroll
@@ -277,9 +301,9 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
         }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            // this lane's 8 bytes of group j for rows g and g + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
-            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + qoff[j]);
-            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + qoff[j]);
+            // this lane's 8 bytes of group j for rows R and R + 8: elements 8t .. 8t+7 of sub-blocks 2j (low) and 2j+1 (high)
+            const uint2 wa = *reinterpret_cast<const uint2*>(q0 + 32 * j);
+            const uint2 wb = *reinterpret_cast<const uint2*>(q1 + 32 * j);
             uint4 bfp[NG];  // B operands of sub-blocks 2j (x, y) and 2j + 1 (z, w)
 #pragma unroll
             for (int i = 0; i < NG; i++) {
@@ -362,17 +386,34 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     };
 
     int parity = 0;
-    uint32_t cmp_slot = 0;
+    int cmp_slot = 0;
+    uint32_t cmp_phase = 0;
+    bool gave_up = false;  // a wait for weights ran out: the status word says so, the warp stops waiting and finishes with whatever is there
     for (int sl = 0; sl < nslices; sl++) {
-        // ---- bring this slice of the activation image into shared memory ---------------------------------------------
+        // ---- this slice of the activation image in shared memory ---------------------------------------------------------
         const int len = sl == nslices - 1 ? len_last : KS;
         const int nb = sl == nslices - 1 ? nb_last : nb_full;
-        if (sl > 0) {
-            __syncthreads();  // every warp is done with the previous slice
-        }
-        if (nslices == 1) {
-            // one slice: a warp only ever reads the image of its own super-blocks, so it fetches just those and waits for
-            // nobody else (the wait also covers the weight stages requested so far, which it needs next anyway)
+        if constexpr (FUSED) {
+            // a warp only ever reads the image of its own super-blocks, so it makes just those and waits for nobody
+            __syncwarp();  // the warp's lanes are done with the previous slice
+            // two (super-block, row) parts at a time, so that the loads of the second are in flight while the first is made
+            const int parts = nb * MT;  // part p: block warp + NW (p / MT) of the slice, row p % MT of x
+            for (int p = 0; p < parts; p += 2) {
+                float xa[8], xb[8];
+                const int bl0 = warp + NW * (p / MT), m0 = p % MT;
+                const int bl1 = warp + NW * ((p + 1) / MT), m1 = (p + 1) % MT;
+                const bool two = p + 1 < parts;
+                const bool have0 = m0 < rows, have1 = two && m1 < rows;
+                q4k::load_image_values(have0 ? xin + (int64_t)m0 * v.k + (int64_t)(sl * KS + bl0) * 256 : nullptr, lane, xa);
+                q4k::load_image_values(have1 ? xin + (int64_t)m1 * v.k + (int64_t)(sl * KS + bl1) * 256 : nullptr, lane, xb);
+                q4k::build_image_from<MT>(xa, have0, m0, img + (size_t)bl0 * C::PB, lane);
+                if (two) {
+                    q4k::build_image_from<MT>(xb, have1, m1, img + (size_t)bl1 * C::PB, lane);
+                }
+            }
+            __syncwarp();
+        } else if (nslices == 1) {
+            // one slice: a warp fetches the image of its own super-blocks and waits for nobody else
             constexpr int CH = (int)(C::PB / 16);
             for (int b = warp; b < KB; b += NW) {
                 for (int c = lane; c < CH; c += 32) {
@@ -383,6 +424,9 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             cp_async_wait<0>();
             __syncwarp();
         } else {
+            if (sl > 0) {
+                __syncthreads();  // every warp is done with the previous slice
+            }
             const uint8_t* src = image + (size_t)sl * KS * C::PB;
             const int chunks = (int)((size_t)len * C::PB / 16);
             for (int c = tid; c < chunks; c += THREADS) {
@@ -392,24 +436,48 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             cp_async_wait<0>();
             __syncthreads();
         }
+        if (sl == 0) {
+            QT(2);
+        }
         for (int ti = 0; ti < my_tiles; ti++) {
             const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
             const uint8_t* blk = xd_lane + (size_t)warp * C::PB;
             for (int j = 0; j < nb; j++) {
-                __syncwarp();                 // every lane is done reading the slot that is requested next
+                __syncwarp();  // every lane is done reading the slot that is requested next
                 issue();
-                cp_async_wait<STAGES - 1>();  // this lane's copies of this step have landed
-                __syncwarp();                 // ... and so have the other lanes'
-                compute(ring + cmp_slot, blk);
-                cmp_slot = cmp_slot + SLOT_BYTES == RING_BYTES ? 0u : cmp_slot + SLOT_BYTES;
+                if (!gave_up) {
+                    // the copy of this step has landed (bounded: the clock, not the number of polls)
+                    const uint32_t bar = bars_s + 8 * cmp_slot;
+                    if (!tc::mbar_try(bar, cmp_phase)) {
+                        const long long t0 = clock64();
+                        while (!tc::mbar_try(bar, cmp_phase)) {
+                            if (clock64() - t0 > wait_clocks) {
+                                atomicCAS(&g_gemv_peer_status, 0, 24);
+                                gave_up = true;
+                                break;
+                            }
+                        }
+                    }
+                }
+                if (sl == 0 && ti == 0 && j == 0) {
+                    QT(3);
+                }
+                compute(ring + cmp_slot * SLOT_BYTES, blk);
+                if (++cmp_slot == STAGES) {
+                    cmp_slot = 0;
+                    cmp_phase ^= 1u;
+                }
                 blk += (size_t)NW * C::PB;
+            }
+            if (sl == nslices - 1 && ti == my_tiles - 1) {
+                QT(4);
             }
             // ---- this warp's partial sums per output row and row of x ---------------------------------------------------
             float* rd = red + (size_t)parity * NW * 16 * MT;
             if constexpr (C::DIGIT_MAJOR) {
-                // the lane holds rows g, g + 8 for rows 2t, 2t + 1 of x (MT = 8: two floats side by side)
-                *reinterpret_cast<float2*>(rd + (warp * 16 + g) * MT + 2 * t) = make_float2(acc[0][0][0], acc[0][0][1]);
-                *reinterpret_cast<float2*>(rd + (warp * 16 + g + 8) * MT + 2 * t) = make_float2(acc[0][1][0], acc[0][1][1]);
+                // the lane holds rows R, R + 8 for rows 2t, 2t + 1 of x (MT = 8: two floats side by side)
+                *reinterpret_cast<float2*>(rd + (warp * 16 + R) * MT + 2 * t) = make_float2(acc[0][0][0], acc[0][0][1]);
+                *reinterpret_cast<float2*>(rd + (warp * 16 + R + 8) * MT + 2 * t) = make_float2(acc[0][1][0], acc[0][1][1]);
                 acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
             } else {
                 // combine the digit columns of a row of x, which sit in the 4 lanes of a quad
@@ -435,8 +503,8 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
                     p0 += __shfl_xor_sync(0xffffffffu, p0, 2);
                     p1 += __shfl_xor_sync(0xffffffffu, p1, 2);
                     if (t == 0) {
-                        rd[(warp * 16 + g) * MT + m] = p0;
-                        rd[(warp * 16 + g + 8) * MT + m] = p1;
+                        rd[(warp * 16 + R) * MT + m] = p0;
+                        rd[(warp * 16 + R + 8) * MT + m] = p1;
                     }
                 }
                 acc[0][0][0] = acc[0][0][1] = acc[0][1][0] = acc[0][1][1] = 0.0f;
@@ -470,8 +538,13 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
                         yo[(int64_t)m * n + row] = val;
                     } else {
                         // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
-                        for (int r = 0; r < peerp->world; r++) {
-                            peerp->y[r][(int64_t)m * peerp->n_total + peerp->col0 + row] = val;
+                        const int64_t idx = (int64_t)m * peerp->n_total + peerp->col0 + row;
+                        if (peer_marks) {
+                            peer_store_marked(peerp, idx, val, peer_seq);
+                        } else {
+                            for (int r = 0; r < peerp->world; r++) {
+                                peerp->y[r][idx] = val;
+                            }
                         }
                     }
                 }
@@ -479,8 +552,14 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             parity ^= 1;
         }
     }
+    QT(5);
     if constexpr (PEER) {
-        peer_publish(peerp->flags, peerp->rank, peerp->world, reinterpret_cast<int*>(red));  // the last CTA raises this rank's flag on every rank
+        if (peer_marks) {
+            peer_collect(peerp, rows, peer_seq, &g_gemv_peer_status);  // the other ranks' rows, from this rank's staging words into its y
+        } else {
+            peer_publish(peerp->flags, peerp->rank, peerp->world, peerp->wait_after != 0, &g_gemv_peer_status);  // every CTA adds its share to this rank's counter on every rank
+        }
+        QT(7);
     }
 }
 
@@ -497,14 +576,14 @@ int sm_count() {
     return g_sms;
 }
 
-template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER>
-int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, int rows, const float* bias, float* y, cudaStream_t s, int KS, int grid,
-           int max_tiles, size_t smem) {
+template <int MT, int STAGES, int NW, int OCC, bool Q5, bool PEER, bool FUSED>
+int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* image, const float* x, int rows, const float* bias, float* y, cudaStream_t s,
+           int KS, int grid, int max_tiles, size_t smem) {
     static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
     int dev = 0;
     JQ_CUDA(cudaGetDevice(&dev));
     if ((configured.load() >> (dev & 63) & 1) == 0) {
-        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
+        JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
@@ -518,15 +597,17 @@ int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER>, v, w2, (const PeerOut*)(PEER ? peer.table : nullptr), image, rows, bias, y, tiles, KS, max_tiles));
+    const long long wait_clocks = (long long)g_opt_wait_limit_us.load(std::memory_order_relaxed) * 2000;  // about 2 GHz
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER, FUSED>, v, w2, (const PeerOut*)(PEER ? peer.table : nullptr), image, x, rows,
+                               bias, y, tiles, KS, max_tiles, wait_clocks));
     count_launch();
     return JQ_OK;
 }
 
-// Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
+// Shared memory of one CTA: the ring's barriers, image slice, cross-warp reduction, carried sums, weight ring.
 template <int MT, bool Q5>
 size_t smem_bytes(int nw, int KS, int stages, bool sliced, int max_tiles) {
-    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * nw * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+    return (size_t)nw * stages * 8 + (size_t)KS * Cfg<MT>::PB + (size_t)(2 * nw * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
            (size_t)nw * stages * Blk<Q5>::SLOT;
 }
 
@@ -539,12 +620,14 @@ struct Shape {
 
 template <int MT, bool Q5>
 int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image,
-        bool* handled) {
+        bool* handled, bool may_fuse) {
     // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
     const int KB = (int)(v.k / 256);
     const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
     // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
     constexpr bool WIDE = MT > 2;
+    // (Three CTAs of 8 warps per SM, which 80 registers per thread allow, measured no faster than two on any shape and
+    // slower on the small ones: the kernel is not short of warps.)
     const Shape unsliced[3] = {WIDE ? Shape{16, 1, 3} : Shape{8, 2, 3}, WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
     const Shape sliced[2] = {WIDE ? Shape{16, 1, 2} : Shape{8, 2, 3}, Shape{8, 2, 2}};
     Shape sh{0, 0, 0};
@@ -578,7 +661,12 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
         return JQ_OK;
     }
     *handled = true;
-    if (x != nullptr) {
+    // One or two rows of x and k <= 8192: the GEMV builds the image itself (every CTA makes all of it, which is redundant work
+    // that grows with k; up to four super-blocks per warp it costs less than a launch and the scratch round trip). Not when
+    // x lies in host memory: the image kernel reads it once, the thread blocks of the GEMV would each read it across PCIe.
+    constexpr bool CAN_FUSE = !WIDE;
+    const bool fuse = CAN_FUSE && may_fuse && x != nullptr && KB <= 4 * sh.nw;
+    if (x != nullptr && !fuse) {
         // launched programmatically as well: it is scheduled while the kernel before it still runs (it waits for that kernel
         // before touching memory) and lets the GEMV behind it be scheduled at once
         cudaLaunchConfig_t icfg = {};
@@ -593,12 +681,23 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
         JQ_CUDA(cudaLaunchKernelEx(&icfg, q4k_activation_image_kernel<MT>, x, rows, (int64_t)v.k, image));
         count_launch();
     }
+#define JQ_VARIANT(NWV, OCCV, STV, PEERV)                                                                                               \
+    if constexpr (CAN_FUSE) {                                                                                                            \
+        if (fuse) {                                                                                                                      \
+            return launch<MT, STV, NWV, OCCV, Q5, PEERV, true>(v, w2, peer, image, x, rows, bias, y, s, KS, grid, max_tiles, smem);      \
+        }                                                                                                                                \
+    }                                                                                                                                    \
+    if constexpr (true) {                                                                                                                \
+        return launch<MT, STV, NWV, OCCV, Q5, PEERV, false>(v, w2, peer, image, nullptr, rows, bias, y, s, KS, grid, max_tiles, smem);   \
+    }
 #define JQ_SHAPE(NWV, OCCV, STV)                                   \
     if (sh.nw == NWV && sh.occ == OCCV && sh.stages == STV) {       \
-        if (peer.world != 0) {                                                                              \
-            return launch<MT, STV, NWV, OCCV, Q5, true>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
-        }                                                                                                   \
-        return launch<MT, STV, NWV, OCCV, Q5, false>(v, w2, peer, image, rows, bias, y, s, KS, grid, max_tiles, smem); \
+        if (peer.world != 0) {                                      \
+            JQ_VARIANT(NWV, OCCV, STV, true)                        \
+        } else {                                                    \
+            JQ_VARIANT(NWV, OCCV, STV, false)                       \
+        }                                                           \
+        return fail(JQ_ERR_UNSUPPORTED, "gemv_q4k_i8: no ready-made image is taken for this format and row count"); \
     }
     if constexpr (WIDE) {
         JQ_SHAPE(16, 1, 3)
@@ -607,6 +706,7 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
         JQ_SHAPE(8, 2, 3)
     }
     JQ_SHAPE(8, 2, 2)
+#undef JQ_VARIANT
 #undef JQ_SHAPE
     return fail(JQ_ERR_UNSUPPORTED, "gemv_q4k_i8: no kernel for the chosen launch shape");
 }
@@ -627,7 +727,7 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows) {
 // gemv_q4k_i8_scratch_bytes(k, rows) bytes, 16-byte aligned, private to `s` until the GEMV kernel has run.
 // *handled = false leaves the call to another kernel.
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
-                       const PeerOut* peer) {
+                       const PeerOut* peer, bool x_remote) {
     *handled = false;
     if ((v.type != JQ_TYPE_Q4_K && v.type != JQ_TYPE_Q5_K) || v.n == 0 || v.k == 0 || rows > 8 || image == nullptr ||
         v.k / 256 >= (1 << 20)) {
@@ -637,15 +737,23 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     PeerOut local{};  // world = 0: results go to y
     const PeerOut& po = peer != nullptr ? *peer : local;
     if (v.type == JQ_TYPE_Q5_K) {
-        if (rows == 1) return run<1, true>(v, none, po, x, rows, bias, y, s, image, handled);
-        if (rows == 2) return run<2, true>(v, none, po, x, rows, bias, y, s, image, handled);
-        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled);
+        if (rows == 1) return run<1, true>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
+        if (rows == 2) return run<2, true>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
+        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled, false);
     }
-    if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled);
-    if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled);
-    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled);
+    if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
+    if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
+    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled, false);
 }
 
+#ifdef JQ_Q4K_TRACE
+}  // namespace jq
+extern "C" JQ_API int jq_debug_q4k_trace(long long* out, int* tickets) {
+    if (cudaMemcpyFromSymbol(tickets, jq::g_q4k_ticket, sizeof(int)) != cudaSuccess) return -3;
+    return cudaMemcpyFromSymbol(out, jq::g_q4k_tr, sizeof(jq::g_q4k_tr)) == cudaSuccess ? 0 : -3;
+}
+namespace jq {
+#endif
 int gemv_peer_status(int* status) {
     const int zero = 0;
     JQ_CUDA(cudaMemcpyFromSymbol(status, g_gemv_peer_status, sizeof(int)));
@@ -670,7 +778,7 @@ int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* imag
     if (peer != nullptr && v2 != nullptr) {
         return JQ_OK;  // a second weight has no place in a peer's y
     }
-    return run<1, false>(v, w2, peer != nullptr ? *peer : local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled);
+    return run<1, false>(v, w2, peer != nullptr ? *peer : local, nullptr, 1, bias, y, s, const_cast<uint8_t*>(image), handled, false);
 }
 
 }  // namespace jq

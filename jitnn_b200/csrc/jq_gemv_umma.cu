@@ -721,8 +721,13 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
                             yo[(int64_t)(m0 + m) * n + row] = val;
                         } else {
                             // a row shard: the value goes into every rank's y [m, n_total] at this rank's columns
-                            for (int rk = 0; rk < a.peer->world; rk++) {
-                                a.peer->y[rk][(int64_t)(m0 + m) * a.peer->n_total + a.peer->col0 + row] = val;
+                            const int64_t idx = (int64_t)(m0 + m) * a.peer->n_total + a.peer->col0 + row;
+                            if (a.peer->stage[0] != nullptr) {
+                                peer_store_marked(a.peer, idx, val, peer_marks_seq(a.peer));  // this kernel's number: read after the wait for the kernel before
+                            } else {
+                                for (int rk = 0; rk < a.peer->world; rk++) {
+                                    a.peer->y[rk][idx] = val;
+                                }
                             }
                         }
                     }
@@ -1021,7 +1026,12 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
     if constexpr (PEER) {
-        peer_publish(a.peer->flags, a.peer->rank, a.peer->world, const_cast<int*>(fin_all));  // the last CTA raises this rank's flag on every rank
+        if (a.peer->stage[0] != nullptr) {
+            __syncthreads();  // no thread of the CTA reads the exchange number after this
+            peer_collect(a.peer, a.rows, peer_marks_seq(a.peer), &g_umma_peer_status);  // the other ranks' rows, from this rank's staging words into its y
+        } else {
+            peer_publish(a.peer->flags, a.peer->rank, a.peer->world, a.peer->wait_after != 0, &g_umma_peer_status);  // every CTA adds its share to this rank's counter on every rank
+        }
     }
 }
 

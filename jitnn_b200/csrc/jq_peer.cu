@@ -2,19 +2,24 @@
 // slice of y straight into every rank's copy of the full y over NVLink (plain peer stores into memory mapped with CUDA
 // IPC), then raises a flag on every rank; a rank's next kernels start after a bounded wait on its own flags.
 //
-//   rank g:   GEMV over its rows  ->  peer_scatter_kernel: y_r[:, col0 .. col0 + n_g) = slice for every rank r,
-//                                     __threadfence_system, last CTA: flags_r[g] = seq for every rank r
-//             peer_wait_kernel: until flags_g[r] >= seq for every r (bounded)  ->  consumers of y_g
+//   rank g:   GEMV over its rows  ->  peer_scatter_kernel: every value of the slice goes into y_g and, as an 8-byte word
+//                                     {value, number of the exchange}, into every other rank's staging area; then the
+//                                     kernel's threads collect what the other ranks own: each polls a staging word until it
+//                                     carries this exchange's number (bounded) and moves the value into y_g
+//             (for Q4_K and Q5_K decode shapes the GEMV's own epilogue does what the scatter kernel does)
+// Nothing in this path needs a fence or an atomic between GPUs (a system-wide release costs a thread block 2.5 to 8
+// microseconds when every block of a grid makes one). The decoder's activation images, which cannot carry marks, use
+// the other form (jq_peer_device.cuh): release-ordered remote adds to arrival counters.
 //
 // The reference gathers with Collective.allGather (dist/Collective.java:64-65, NCCL form dist/NcclOp.java:184-198); for
 // the 4 KB - 128 KB slices of a decode step that call costs more than the GEMV it follows.
 //
-// A peer buffer is one cudaMalloc'd allocation: 2048 bytes of flags (uint32 [world] arrival flags written by the peers;
-// words 16 and 17, never written by peers: a CTA counter and the number of exchanges this rank has made on the
+// A peer buffer is one cudaMalloc'd allocation: 4096 bytes of flags (uint32 [world] arrival counters, counter r added
+// to by rank r; word 17, never written by peers: the number of exchanges this rank has made on the
 // buffer; from byte 128 on up to eight copies of the target table PeerOut that the fused GEMV epilogue reads), then the
-// payload. A flag carries the number of the exchange it announces. The number lives in device
-// memory and grows by one per exchange, so a captured CUDA graph can be replayed; all ranks make the same exchanges
-// on a buffer in the same order, which keeps their numbers in step. A rank can run one exchange ahead of another:
+// payload. Every exchange adds 2^16 to a counter, so a counter says which exchange has completely arrived. The number
+// lives in device memory and grows by one per exchange, so a captured CUDA graph can be replayed; all ranks make the
+// same exchanges on a buffer in the same order, which keeps their numbers in step. A rank can run one exchange ahead of another:
 // a payload area must not be the target of two consecutive exchanges (use two areas in turn, or other buffers in
 // between).
 // No load ever targets a peer's memory, nothing here uses multicast, and the only wait is bounded: when it gives up
@@ -29,31 +34,30 @@
 namespace jq {
 
 static __device__ int g_peer_status;
+std::atomic<int64_t> g_opt_peer_wait_us{400000};
 
-int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s);
+int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s, bool x_remote = false);
 
 namespace {
 
 
 struct PeerTargets {
-    float* y[PEER_MAX_WORLD];         // every rank's full y [m, n_total] (own included)
-    uint32_t* flags[PEER_MAX_WORLD];  // every rank's flag words
+    float* y[PEER_MAX_WORLD];                   // every rank's full y [m, n_total] (own included)
+    uint32_t* flags[PEER_MAX_WORLD];            // every rank's flag words
+    unsigned long long* stage[PEER_MAX_WORLD];  // every rank's staging words [m, n_total]
 };
 
-// slice [m, n_slice] -> columns col0 .. of every rank's y [m, n_total]; the CTA that finishes last raises the flags.
-__global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restrict__ slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0,
-                                                           PeerTargets tg, int rank, int world) {
+// slice [m, n_slice] -> columns col0 .. of this rank's y [m, n_total] and, marked, of every other rank's staging area;
+// then the other ranks' columns from this rank's staging area into its y.
+__global__ void __launch_bounds__(256) peer_scatter_kernel(const float* __restrict__ slice, int64_t m, PeerOut po) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t count = m * n_slice;
+    const uint32_t seq = peer_marks_seq(&po);
+    const int64_t count = m * po.n_own;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = i / n_slice, col = i % n_slice;
-        const float val = slice[i];
-        for (int r = 0; r < world; r++) {
-            tg.y[r][row * n_total + col0 + col] = val;
-        }
+        const int64_t row = i / po.n_own, col = i % po.n_own;
+        peer_store_marked(&po, row * po.n_total + po.col0 + col, slice[i], seq);
     }
-    __shared__ int last_word;
-    peer_publish(tg.flags, rank, world, &last_word);
+    peer_collect(&po, (int)m, seq, &g_peer_status);
 }
 
 // Writes a target table into this rank's flag area (one thread).
@@ -62,25 +66,6 @@ __global__ void peer_table_kernel(PeerOut table, PeerOut* dst) {
     if (threadIdx.x == 0) {
         *dst = table;
     }
-}
-
-// Thread r waits until rank r's slice of this rank's latest exchange has arrived in this rank's y.
-__global__ void peer_wait_kernel(const uint32_t* flags, int world) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the scatter kernel before this one has advanced the number
-    const int r = threadIdx.x;
-    if (r >= world) {
-        return;
-    }
-    const uint32_t seq = *reinterpret_cast<const volatile uint32_t*>(flags + PEER_SEQ_WORD);
-    for (unsigned poll = 0; poll < PEER_POLL_LIMIT; poll++) {
-        uint32_t seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + r) : "memory");
-        if ((int32_t)(seen - seq) >= 0) {
-            return;
-        }
-        __nanosleep(100);
-    }
-    atomicCAS(&g_peer_status, 0, 32 + r);
 }
 
 }  // namespace
@@ -167,9 +152,12 @@ JQ_API int jq_peer_free(void* ptr) {
 
 JQ_API int64_t jq_peer_payload_offset(void) { return PEER_FLAG_BYTES; }
 
-static int fill_targets(void* const* peer_buffers, int64_t payload_offset, int rank, int world, PeerTargets* tg, const char* who) {
-    if (peer_buffers == nullptr || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || payload_offset < 0 || payload_offset % 16 != 0) {
-        return fail(JQ_ERR_INVALID, "%s: rank %d of %d (at most %d), payload offset %lld", who, rank, world, PEER_MAX_WORLD, (long long)payload_offset);
+static int fill_targets(void* const* peer_buffers, int64_t payload_offset, int64_t staging_offset, int rank, int world, PeerTargets* tg, const char* who) {
+    // staging_offset < 0: an exchange that does not use staging words (the decoder's)
+    if (peer_buffers == nullptr || world < 1 || world > PEER_MAX_WORLD || rank < 0 || rank >= world || payload_offset < 0 || payload_offset % 16 != 0 ||
+        staging_offset % 16 != 0) {
+        return fail(JQ_ERR_INVALID, "%s: rank %d of %d (at most %d), payload offset %lld, staging offset %lld (multiples of 16)", who, rank, world, PEER_MAX_WORLD,
+                    (long long)payload_offset, (long long)staging_offset);
     }
     for (int r = 0; r < PEER_MAX_WORLD; r++) {
         uint8_t* base = r < world ? static_cast<uint8_t*>(peer_buffers[r]) : nullptr;
@@ -178,6 +166,7 @@ static int fill_targets(void* const* peer_buffers, int64_t payload_offset, int r
         }
         tg->flags[r] = reinterpret_cast<uint32_t*>(base);
         tg->y[r] = base != nullptr ? reinterpret_cast<float*>(base + PEER_FLAG_BYTES + payload_offset) : nullptr;
+        tg->stage[r] = base != nullptr && staging_offset >= 0 ? reinterpret_cast<unsigned long long*>(base + PEER_FLAG_BYTES + staging_offset) : nullptr;
     }
     return JQ_OK;
 }
@@ -235,22 +224,30 @@ static int device_table(const PeerOut& po, cudaStream_t s, const PeerOut** out) 
     return JQ_OK;
 }
 
-static int enqueue_wait(const PeerTargets& tg, int rank, int world, cudaStream_t s) {
-    cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = pdl_config(attr, 1, 32, s);
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_wait_kernel, (const uint32_t*)tg.flags[rank], world));
-    count_launch(1);
-    return JQ_OK;
+static long long wait_clocks() { return (long long)g_opt_peer_wait_us.load(std::memory_order_relaxed) * 2000; }  // about 2 GHz
+
+static PeerOut peer_out(const PeerTargets& tg, int64_t n_own, int64_t n_total, int64_t col0, int rank, int world) {
+    PeerOut po;
+    memset(&po, 0, sizeof(po));
+    for (int r = 0; r < PEER_MAX_WORLD; r++) {
+        po.y[r] = tg.y[r];
+        po.flags[r] = tg.flags[r];
+        po.stage[r] = tg.stage[r];
+    }
+    po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0; po.n_own = n_own;
+    po.wait_clocks = wait_clocks();
+    return po;
 }
 
 static int enqueue_scatter(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, const PeerTargets& tg, int rank, int world,
                            cudaStream_t s) {
-    const int64_t count = m * n_slice;
+    // the grid also collects the other ranks' columns: sized for all of y
+    const int64_t count = m * n_total;
     int grid = (int)((count + 255) / 256);
     grid = grid < 1 ? 1 : (grid > 148 ? 148 : grid);
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(attr, (unsigned)grid, 256, s);
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_scatter_kernel, slice, m, n_slice, n_total, col0, tg, rank, world));
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, peer_scatter_kernel, slice, m, peer_out(tg, n_slice, n_total, col0, rank, world)));
     count_launch(1);
     return JQ_OK;
 }
@@ -259,27 +256,16 @@ static int enqueue_scatter(const float* slice, int64_t m, int64_t n_slice, int64
 
 namespace jq {
 
-int peer_wait_enqueue(void* const* peer_buffers, int rank, int world, cudaStream_t s) {
-    PeerTargets tg;
-    int rc = fill_targets(peer_buffers, 0, rank, world, &tg, "peer wait");
-    return rc == JQ_OK ? enqueue_wait(tg, rank, world, s) : rc;
-}
-
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
                            int rank, int world, cudaStream_t s, bool wait_first, bool wait_after) {
     PeerTargets tg;
-    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "peer linear");
+    int rc = fill_targets(peer_buffers, payload_offset, -16, rank, world, &tg, "peer linear");
     if (rc != JQ_OK) {
         return rc;
     }
-    PeerOut po;
-    memset(&po, 0, sizeof(po));
-    for (int r = 0; r < PEER_MAX_WORLD; r++) {
-        po.y[r] = tg.y[r];
-        po.flags[r] = tg.flags[r];
-    }
-    po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+    PeerOut po = peer_out(tg, w->n, n_total, col0, rank, world);  // no staging words: announced through the arrival counters
     po.wait_first = wait_first ? 1 : 0;
+    po.wait_after = wait_after ? 1 : 0;
     rc = device_table(po, s, &po.table);
     bool handled = false;
     if (rc == JQ_OK) {
@@ -289,9 +275,6 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
     if (rc == JQ_OK && !handled) {
         rc = fail(JQ_ERR_UNSUPPORTED, "peer linear: a [%lld, %lld] shard is outside what the tensor-core GEMV takes", (long long)w->n, (long long)w->k);
     }
-    if (rc == JQ_OK && wait_after) {
-        rc = enqueue_wait(tg, rank, world, s);
-    }
     return rc;
 }
 
@@ -300,26 +283,27 @@ int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_t
 extern "C" {
 
 JQ_API int jq_peer_gather(const float* slice, int64_t m, int64_t n_slice, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                          int rank, int world, void* stream) {
+                          int64_t staging_offset, int rank, int world, void* stream) {
     if (slice == nullptr || m < 1 || n_slice < 0 || col0 < 0 || col0 + n_slice > n_total) {
         return fail(JQ_ERR_INVALID, "jq_peer_gather: slice [%lld, %lld] at column %lld of %lld", (long long)m, (long long)n_slice, (long long)col0,
                     (long long)n_total);
     }
     PeerTargets tg;
-    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "jq_peer_gather");
-    if (rc == JQ_OK) rc = enqueue_scatter(slice, m, n_slice, n_total, col0, tg, rank, world, (cudaStream_t)stream);
-    if (rc == JQ_OK) rc = enqueue_wait(tg, rank, world, (cudaStream_t)stream);
+    int rc = staging_offset < 0 ? fail(JQ_ERR_INVALID, "jq_peer_gather: negative staging offset")
+                                : fill_targets(peer_buffers, payload_offset, staging_offset, rank, world, &tg, "jq_peer_gather");
+    if (rc == JQ_OK) rc = enqueue_scatter(slice, m, n_slice, n_total, col0, tg, rank, world, (cudaStream_t)stream);  // waits itself
     return rc;
 }
 
 JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, const float* bias, int64_t n_total, int64_t col0, void* const* peer_buffers,
-                              int64_t payload_offset, int rank, int world, void* stream) {
+                              int64_t payload_offset, int64_t staging_offset, int rank, int world, void* stream) {
     if (w == nullptr || w->magic != JQ_WEIGHT_MAGIC || x == nullptr || m < 1 || col0 < 0 || col0 + w->n > n_total) {
         return fail(JQ_ERR_INVALID, "jq_linear_f32_peer: not a live weight, null x, or rows [%lld, +%lld) outside %lld", (long long)col0,
                     (long long)(w != nullptr ? w->n : 0), (long long)n_total);
     }
     PeerTargets tg;
-    int rc = fill_targets(peer_buffers, payload_offset, rank, world, &tg, "jq_linear_f32_peer");
+    int rc = staging_offset < 0 ? fail(JQ_ERR_INVALID, "jq_linear_f32_peer: negative staging offset")
+                                : fill_targets(peer_buffers, payload_offset, staging_offset, rank, world, &tg, "jq_linear_f32_peer");
     if (rc != JQ_OK) {
         return rc;
     }
@@ -333,13 +317,7 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
     bool fused = false;
     if (w->n > 0 && gemv_umma_takes(w->type, w->k, (int)m)) {
         // the tcgen05 GEMV stores into every rank's y and publishes the exchange itself
-        PeerOut po;
-        memset(&po, 0, sizeof(po));
-        for (int r = 0; r < PEER_MAX_WORLD; r++) {
-            po.y[r] = tg.y[r];
-            po.flags[r] = tg.flags[r];
-        }
-        po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        PeerOut po = peer_out(tg, w->n, n_total, col0, rank, world);
         rc = device_table(po, s, &po.table);
         uint8_t* image = nullptr;
         if (rc == JQ_OK) rc = scratch_for(s, gemv_umma_image_bytes(w->k, (int)m), &image);
@@ -348,13 +326,7 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
     } else if ((w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K) && m <= 8 && w->n > 0 && g_opt_gemv_generic.load() == 0) {
         // the GEMV kernel itself stores into every rank's y and publishes the exchange; it reads the targets from a table
         // in this rank's flag area, which is written once per distinct (buffers, area, shard) and then found again
-        PeerOut po;
-        memset(&po, 0, sizeof(po));
-        for (int r = 0; r < PEER_MAX_WORLD; r++) {
-            po.y[r] = tg.y[r];
-            po.flags[r] = tg.flags[r];
-        }
-        po.world = world; po.rank = rank; po.n_total = n_total; po.col0 = col0;
+        PeerOut po = peer_out(tg, w->n, n_total, col0, rank, world);
         rc = device_table(po, s, &po.table);
         uint8_t* image = nullptr;
         if (rc == JQ_OK) rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(w->k, (int)m), &image);
@@ -369,7 +341,6 @@ JQ_API int jq_linear_f32_peer(const jq_weight* w, const float* x, int64_t m, con
         if (rc == JQ_OK) rc = linear_device(w, x, m, bias, reinterpret_cast<float*>(slice), s);
         if (rc == JQ_OK) rc = enqueue_scatter(reinterpret_cast<const float*>(slice), m, w->n, n_total, col0, tg, rank, world, s);
     }
-    if (rc == JQ_OK) rc = enqueue_wait(tg, rank, world, s);
     if (prev >= 0 && prev != w->device) {
         cudaSetDevice(prev);
     }

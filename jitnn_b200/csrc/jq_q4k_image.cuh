@@ -40,7 +40,9 @@ struct Cfg {
 // lane = octet: sub-block lane / 4, k-slots 8 (lane % 4) .. + 7 of that sub-block's MMA. Digit fragments are stored
 // per pair of sub-blocks, so that the GEMV reads the B operands of two MMAs with one 16-byte load.
 template <int MT>
-__device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img, int lane) {
+__device__ __forceinline__ void build_image_from(const float (&xv)[8], bool present, int m, uint8_t* img, int lane) {
+    // xv: this lane's eight values (lane = octet: sub-block lane / 4, elements 8 (lane % 4) .. + 7 of it); present = false:
+    // a row beyond those of x, all zero
     using C = Cfg<MT>;
     constexpr int NG = C::NG, NCOL = C::NCOL, NCOLM = C::NCOLM;
     const int sub = lane >> 2, tt = lane & 3;
@@ -51,55 +53,45 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
         tab[lane] = 0.0f;  // columns that hold no activation row
         tab[NG * 8 + lane] = 0.0f;
     }
-    float xv[8];
-    if (xb != nullptr) {
-        const float4* xp = reinterpret_cast<const float4*>(xb) + 2 * lane;
-        const float4 lo = xp[0], hi = xp[1];
-        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
-        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            xv[i] = 0.0f;
-        }
-    }
-    float am = 0.0f;
-    bool bad = false;  // a NaN or an Inf among the values: the column weights become NaN and with them every output of this row of x
+    // largest magnitude as an integer (NaN > Inf > every finite value in this order), so one comparison finds a value that is
+    // not finite: the column weights then become NaN and with them every output of this row of x
+    uint32_t amb = 0u;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        am = fmaxf(am, fabsf(xv[i]));
-        bad = bad || (__float_as_uint(xv[i]) & 0x7f800000u) == 0x7f800000u;
+        amb = max(amb, __float_as_uint(xv[i]) & 0x7fffffffu);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        amb = max(amb, __shfl_xor_sync(0xffffffffu, amb, o));
     }
-    bad = __any_sync(0xffffffffu, bad);
+    const bool bad = amb >= 0x7f800000u;
     // s = 2^floor(log2(amax)): the largest |x| / s of the super-block lies in [1, 2)
-    uint32_t e = __float_as_uint(am) & 0x7f800000u;
+    uint32_t e = amb & 0x7f800000u;
     e = e < 0x0d000000u ? 0x0d000000u : (e > 0x7e800000u ? 0x7e800000u : e);  // keeps 2^21 / s and s * 2^-25 normal
     // 2^21 / s: |X| <= 2^22, so the top digit stays within a signed byte after the carries
     const float inv = __uint_as_float(0x7f000000u - e + (21u << 23));
-    int X[8];
+    // X = rint(x * inv) lands in the mantissa of x * inv + 1.5 * 2^23 (the product is exact: inv is a power of two). With 128
+    // added at every byte position the three low bytes of Y = X + 0x808080 are the signed base-256 digits plus 128 each
+    // (X = d0 + 256 d1 + 65536 d2 with -128 <= d < 128 has exactly one such form), so digit = byte ^ 0x80.
+    uint32_t Y[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        X[i] = __float2int_rn(xv[i] * inv);
+        Y[i] = __float_as_uint(fmaf(xv[i], inv, 12582912.0f)) - 0x4b400000u + 0x00808080u;
+    }
+    // bytes of four values side by side: [Y0.b, Y1.b, Y2.b, Y3.b] for b = 0, 1, 2
+    uint32_t dw[3][2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const uint32_t t01 = __byte_perm(Y[4 * h], Y[4 * h + 1], 0x5140), t23 = __byte_perm(Y[4 * h + 2], Y[4 * h + 3], 0x5140);
+        const uint32_t h01 = __byte_perm(Y[4 * h], Y[4 * h + 1], 0x0062), h23 = __byte_perm(Y[4 * h + 2], Y[4 * h + 3], 0x0062);
+        dw[0][h] = __byte_perm(t01, t23, 0x5410) ^ 0x80808080u;
+        dw[1][h] = __byte_perm(t01, t23, 0x7632) ^ 0x80808080u;
+        dw[2][h] = __byte_perm(h01, h23, 0x5410) ^ 0x80808080u;
     }
 #pragma unroll
     for (int dgt = 0; dgt < 3; dgt++) {
-        uint32_t w0 = 0, w1 = 0;
-        int sum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int d = dgt == 2 ? X[i] : (int)(int8_t)(X[i] & 0xff);  // signed low byte
-            X[i] = (X[i] - d) >> 8;
-            sum += d;
-            if (i < 4) {
-                w0 |= (uint32_t)(d & 0xff) << (8 * i);
-            } else {
-                w1 |= (uint32_t)(d & 0xff) << (8 * (i - 4));
-            }
-        }
+        const uint32_t w0 = dw[dgt][0], w1 = dw[dgt][1];
+        int sum = __dp4a((int)w0, 0x01010101, __dp4a((int)w1, 0x01010101, 0));  // the eight digits as signed bytes
         const int col = C::qcol(m, dgt);
         xd[((((size_t)(sub >> 1) * NG + (col >> 3)) * NCOL + (col & 7)) * 4 + tt) * 2 + (sub & 1)] = make_uint2(w0, w1);
         // digit sum of the sub-block (its 4 octets sit in 4 consecutive lanes): sum = 128 hi + lo7, both fit a signed byte.
@@ -117,12 +109,34 @@ __device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img
             }
         }
         if (lane == 0) {
-            tab[col] = xb == nullptr ? 0.0f : (bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)));  // s * 2^(8 dgt - 21)
+            tab[col] = !present ? 0.0f : (bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (21u << 23)));  // s * 2^(8 dgt - 21)
             if (!C::DIGIT_MAJOR) {
-                tab[NG * 8 + col] = xb == nullptr ? 0.0f : (bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (25u << 23)));  // ... / 16
+                tab[NG * 8 + col] = !present ? 0.0f : (bad ? __uint_as_float(0x7fc00000u) : __uint_as_float(e + ((uint32_t)(8 * dgt) << 23) - (25u << 23)));  // ... / 16
             }
         }
     }
+}
+
+// This lane's eight values of the super-block at xb (nullptr: zeros).
+__device__ __forceinline__ void load_image_values(const float* xb, int lane, float (&xv)[8]) {
+    if (xb != nullptr) {
+        const float4* xp = reinterpret_cast<const float4*>(xb) + 2 * lane;
+        const float4 lo = xp[0], hi = xp[1];
+        xv[0] = lo.x; xv[1] = lo.y; xv[2] = lo.z; xv[3] = lo.w;
+        xv[4] = hi.x; xv[5] = hi.y; xv[6] = hi.z; xv[7] = hi.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            xv[i] = 0.0f;
+        }
+    }
+}
+
+template <int MT>
+__device__ __forceinline__ void build_image(const float* xb, int m, uint8_t* img, int lane) {
+    float xv[8];
+    load_image_values(xb, lane, xv);
+    build_image_from<MT>(xv, xb != nullptr, m, img, lane);
 }
 
 }  // namespace q4k

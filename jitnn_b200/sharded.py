@@ -13,8 +13,8 @@ tested without a GPU.
 
 Two ways to complete y: ``gather_rows`` (a torch.distributed all-gather: NCCL on GPUs, gloo in the CPU
 tests) and ``PeerGather`` (the library's own exchange: every rank stores its slice straight into every
-rank's y over NVLink and waits for the others' flags, ``jq_peer_gather``; the process group only carries
-the 64-byte memory handles at set-up).
+rank's buffer over NVLink as marked 8-byte words and collects the others' words into its y,
+``jq_peer_gather``; the process group only carries the 64-byte memory handles at set-up).
 """
 import ctypes
 
@@ -95,7 +95,8 @@ class PeerGather:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.n, self.m_max, self.device = int(n), int(m_max), int(device)
         self.begin, self.end = row_range(self.n, self.rank, self.world)
-        self.area = (self.n * self.m_max * 4 + 255) // 256 * 256
+        self.y_bytes = (self.n * self.m_max * 4 + 255) // 256 * 256
+        self.area = 3 * self.y_bytes  # y [m_max, n] floats, then the staging words [m_max, n] of 8 bytes that the exchange travels in
         own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
         _lib.check(self.lib.jq_peer_alloc(self.device, 2 * self.area, ctypes.byref(own), handle))
         self.own = own.value
@@ -124,7 +125,8 @@ class PeerGather:
             raise ValueError("PeerGather: slice %s does not fit rows [%d, %d) x at most %d" % (tuple(y_local.shape), self.begin, self.end, self.m_max))
         s = torch.cuda.current_stream(y_local.device).cuda_stream if stream is None else stream
         off = self.turn * self.area
-        _lib.check(self.lib.jq_peer_gather(y_local.data_ptr(), m, self.end - self.begin, self.n, self.begin, self.buffers, off, self.rank, self.world, s))
+        _lib.check(self.lib.jq_peer_gather(y_local.data_ptr(), m, self.end - self.begin, self.n, self.begin, self.buffers, off, off + self.y_bytes,
+                                           self.rank, self.world, s))
         self.turn ^= 1
         return self.view(off, m)
 
@@ -139,7 +141,7 @@ class PeerGather:
         s = torch.cuda.current_stream(x.device).cuda_stream if stream is None else stream
         off = self.turn * self.area
         _lib.check(self.lib.jq_linear_f32_peer(weight._handle(), x.data_ptr(), m, None if bias is None else bias.data_ptr(), self.n, self.begin,
-                                               self.buffers, off, self.rank, self.world, s))
+                                               self.buffers, off, off + self.y_bytes, self.rank, self.world, s))
         self.turn ^= 1
         return self.view(off, m)
 
