@@ -40,10 +40,10 @@ BYTES_PER_WEIGHT = 144.0 / 256.0
 POOL_COPIES = 4  # distinct copies of every weight; 4 x 134 MB = 537 MB, about 4x the 126 MB L2
 METRIC = "q4k_gemv_sweep_GBps"
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one step of this sweep, per linear: not measured by the run
-# itself but taken from an ncu capture of the same command line (`--steps 20 --warmup 3 --no-cpu --eager`, one pass,
+# itself but taken from an ncu capture of the same command line (`--steps 20 --warmup 3 --no-cpu --no-decode --eager`, one pass,
 # --clock-control none); the line names the source beside the figure.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 269671168 // 8
-NCU_TRAFFIC_SOURCE = "ncu capture of the sweep (16 launches of one eager step), not measured by this run"
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 269226240 // 8
+NCU_TRAFFIC_SOURCE = "ncu capture of the sweep (the 12 launches of one eager step), not measured by this run"
 WORKLOAD = "Q4_K GEMV sweep: [N,K] in 4096x4096, 11008x4096, 4096x11008, 32000x4096, M in {1,8}; 8 launches per step"
 
 
@@ -871,6 +871,12 @@ def decode_leg(torch, device, shape=None):
     weight_bytes += vocab * dim * bpw["Q6_K"]
     prompt = np.random.default_rng(11).integers(0, vocab, prompt_len).astype(np.int32)
     torch.cuda.synchronize(device)
+    # the prompt twice: in one pass over the weights on the tensor-core path (bfloat16 operands; the first call also allocates
+    # its workspace, so it is run once untimed), then in groups of 8 on the FP32 path, whose cache the greedy steps go on from
+    dec.prompt(prompt, 0, want_logits=False)
+    t0 = time.perf_counter()
+    _, nxt_bf16 = dec.prompt(prompt, 0, want_logits=False)
+    t_prompt_bf16 = time.perf_counter() - t0
     t0 = time.perf_counter()
     for i in range(0, prompt_len - 8, 8):
         dec.enqueue(prompt[i:i + 8], i)
@@ -896,6 +902,10 @@ def decode_leg(torch, device, shape=None):
     peak, which = measured_peaks()
     kv_bytes = 2 * layers * (prompt_len + gen // 2) * dim * 4
     return {"tokens_per_s": round(1.0 / dt, 1), "ms_per_token": round(dt * 1e3, 4), "prompt_tokens_per_s": round(prompt_len / t_prompt, 1),
+            "prompt_tokens_per_s_tensor_core": round(prompt_len / t_prompt_bf16, 1),
+            "prompt_note": "prompt_tokens_per_s: FP32 operands, groups of 8 tokens through the decode kernels; ..._tensor_core: jq_decoder_prompt, the whole "
+                           "prompt in one pass, linears on the tcgen05 prefill kernel with bfloat16 operands (next token %s the FP32 path's)"
+                           % ("equals" if int(nxt_bf16) == int(nxt[-1]) else "differs from"),
             "weight_bytes_per_token": int(weight_bytes), "kv_cache_bytes_per_token": int(kv_bytes),
             "hbm_roofline_tokens_per_s": round(peak * 1e9 / (weight_bytes + kv_bytes), 1),
             "frac": round((weight_bytes + kv_bytes) / dt / 1e9 / peak, 4), "peak_source": "of " + which,

@@ -294,6 +294,19 @@ JQ_API int jq_decoder_forward_seq(jq_decoder* d, int seq, const int32_t* tokens_
                                   int32_t* next_host, void* stream);
 JQ_API int jq_decoder_forward_batch(jq_decoder* d, const int32_t* tokens_host, int n_seqs, int pos, float* logits_host, int32_t* next_host,
                                     void* stream);
+/*
+ * The prompt path: n_tokens (1..4096) consecutive tokens of sequence `seq` at positions pos0 .. in one pass over the
+ * weights, their keys and values appended to the cache. Every linear runs on the tensor-core prefill kernel, which rounds
+ * its input to bfloat16 (what jq_linear_bf16 computes; FP32 accumulation, everything else in FP32), so the results
+ * agree with jq_decoder_forward's to about 1e-2 of the largest logit, not to FP32 precision: the caller chooses this
+ * path, jq_decoder_forward never takes it by itself. Only the last token's logits are computed: logits_host (or NULL)
+ * receives float32 [vocab], next_host (or NULL) the greedy token after the last one; the call waits for `stream` when
+ * either is requested. Head sizes 64 and 128; not for the row-sharded decoder (JQ_ERR_UNSUPPORTED). The workspace
+ * (activations of n_tokens rows) is allocated by the first call and grows with the longest run seen.
+ * (The reference has no generation loop; the operators are those of models/Llama.java:192-222 on T rows.)
+ */
+JQ_API int jq_decoder_prompt(jq_decoder* d, int seq, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
+                             void* stream);
 
 /*
  * GGUF file -> device weights (the reference's jitnn-gguf/.../GgufFile.java:100-175,329-418, whose GgufFile.tensor(name)

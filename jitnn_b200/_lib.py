@@ -51,6 +51,7 @@ SIGNATURES = {
     "jq_decoder_set_sequences": (c_int, [vp, c_int]),
     "jq_decoder_forward_seq": (c_int, [vp, c_int, vp, c_int, c_int, vp, vp, vp]),
     "jq_decoder_forward_batch": (c_int, [vp, vp, c_int, c_int, vp, vp, vp]),
+    "jq_decoder_prompt": (c_int, [vp, c_int, vp, c_int, c_int, vp, vp, vp]),
     "jq_decoder_peer_bytes": (c_int, [vp, ctypes.POINTER(ctypes.c_int64)]),
     "jq_decoder_set_shard": (c_int, [vp, c_int, c_int, vp]),
     "jq_set_option": (c_int, [ctypes.c_char_p, c_i64]),

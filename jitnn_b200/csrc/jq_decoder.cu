@@ -275,6 +275,144 @@ __global__ void attention_combine_kernel(const float* __restrict__ part, float* 
     }
 }
 
+// Causal attention for a long run of consecutive tokens (the prompt path): CTA (head h, group of PA_Q queries) walks the keys
+// 0 .. (its last query's position) in tiles of PA_KEYS. A tile of keys and values is loaded into shared memory once and
+// serves all PA_Q queries; per query a running maximum m, a running sum l and the output row are carried from tile to
+// tile (the usual streaming softmax: out = sum_j exp(s_j - m) v_j / sum_j exp(s_j - m)). Thread (query, key) pairs compute
+// the scores, two queries per warp the softmax statistics, thread d the output dimension d of every query.
+constexpr int PA_Q = 8;
+constexpr int PA_KEYS = 64;
+constexpr int PA_THREADS = 128;
+
+template <int HD>
+constexpr size_t prompt_attention_smem() {
+    return (size_t)(PA_Q * HD + PA_KEYS * (HD + 4) + PA_KEYS * HD + PA_Q * PA_KEYS + 3 * PA_Q) * sizeof(float);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(PA_THREADS) attention_prompt_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                       const float* __restrict__ v_cache, float* __restrict__ out,
+                                                                       const int* __restrict__ pos0p, int heads, int kv_heads, int T, float scale) {
+    static_assert(HD == 64 || HD == 128, "head sizes of the prompt path");
+    extern __shared__ __align__(16) float pa_smem[];
+    float* qs = pa_smem;                          // [PA_Q][HD]
+    float* ks = qs + PA_Q * HD;                   // [PA_KEYS][HD + 4]: the pad spreads a key's 16-byte pieces over the banks
+    float* vs = ks + PA_KEYS * (HD + 4);          // [PA_KEYS][HD]
+    float* ps = vs + PA_KEYS * HD;                // [PA_Q][PA_KEYS] scores, then exp(score - m)
+    float* m_s = ps + PA_Q * PA_KEYS;             // [PA_Q] running maximum
+    float* l_s = m_s + PA_Q;                      // [PA_Q] running sum
+    float* a_s = l_s + PA_Q;                      // [PA_Q] exp(m before - m after) of the tile
+    const int h = blockIdx.x, t0 = blockIdx.y * PA_Q, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nq = T - t0 < PA_Q ? T - t0 : PA_Q;
+    const int pos0 = *pos0p;
+    const int kv_dim = kv_heads * HD;
+    const int kvh = h / (heads / kv_heads);
+    const int keys_all = pos0 + t0 + nq;  // keys the last query of the group sees
+    for (int i = tid; i < PA_Q * HD; i += PA_THREADS) {
+        const int qi = i / HD, d = i % HD;
+        qs[i] = qi < nq ? q[((int64_t)(t0 + qi) * heads + h) * HD + d] : 0.0f;
+    }
+    if (tid < PA_Q) {
+        m_s[tid] = -INFINITY;
+        l_s[tid] = 0.0f;
+    }
+    float acc[PA_Q];
+#pragma unroll
+    for (int i = 0; i < PA_Q; i++) {
+        acc[i] = 0.0f;
+    }
+    for (int kc = 0; kc < keys_all; kc += PA_KEYS) {
+        const int cnt = keys_all - kc < PA_KEYS ? keys_all - kc : PA_KEYS;
+        __syncthreads();  // the tile before is used up (first pass: qs, m_s, l_s are written)
+        // ---- the tile's keys and values
+        constexpr int V4 = HD / 4;
+        for (int i = tid; i < PA_KEYS * V4; i += PA_THREADS) {
+            const int r = i / V4, c = i % V4;
+            float4 kv4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), vv4 = kv4;
+            if (r < cnt) {
+                const int64_t off = (int64_t)(kc + r) * kv_dim + kvh * HD + 4 * c;
+                kv4 = *reinterpret_cast<const float4*>(k_cache + off);
+                vv4 = *reinterpret_cast<const float4*>(v_cache + off);
+            }
+            *reinterpret_cast<float4*>(ks + r * (HD + 4) + 4 * c) = kv4;
+            *reinterpret_cast<float4*>(vs + r * HD + 4 * c) = vv4;
+        }
+        __syncthreads();
+        // ---- scores: pair p = (query p / PA_KEYS, key p % PA_KEYS)
+        for (int p = tid; p < PA_Q * PA_KEYS; p += PA_THREADS) {
+            const int qi = p / PA_KEYS, j = p % PA_KEYS;
+            const float4* kr = reinterpret_cast<const float4*>(ks + j * (HD + 4));
+            const float4* qr = reinterpret_cast<const float4*>(qs + qi * HD);
+            float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll 8
+            for (int c = 0; c < V4; c++) {
+                const float4 a = qr[c], b = kr[c];
+                d0 = fmaf(a.x, b.x, d0);
+                d1 = fmaf(a.y, b.y, d1);
+                d2 = fmaf(a.z, b.z, d2);
+                d3 = fmaf(a.w, b.w, d3);
+            }
+            const bool seen = qi < nq && j < cnt && kc + j <= pos0 + t0 + qi;
+            ps[p] = seen ? ((d0 + d1) + (d2 + d3)) * scale : -INFINITY;
+        }
+        __syncthreads();
+        // ---- statistics: warp w takes queries w and w + 4
+#pragma unroll
+        for (int u = 0; u < PA_Q / 4; u++) {
+            const int qi = warp + 4 * u;
+            const float s0 = ps[qi * PA_KEYS + lane], s1 = ps[qi * PA_KEYS + lane + 32];
+            float mx = fmaxf(s0, s1);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            }
+            const float m_old = m_s[qi];
+            const float m_new = fmaxf(m_old, mx);
+            const float e0 = s0 == -INFINITY ? 0.0f : expf(s0 - m_new), e1 = s1 == -INFINITY ? 0.0f : expf(s1 - m_new);
+            float sum = e0 + e1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            }
+            ps[qi * PA_KEYS + lane] = e0;
+            ps[qi * PA_KEYS + lane + 32] = e1;
+            __syncwarp();
+            if (lane == 0) {
+                const float alpha = m_old == -INFINITY ? 0.0f : expf(m_old - m_new);  // no key seen so far: nothing to carry
+                a_s[qi] = alpha;
+                l_s[qi] = fmaf(l_s[qi], alpha, sum);
+                m_s[qi] = m_new;
+            }
+        }
+        __syncthreads();
+        // ---- weighted values: thread d, every query
+        if (tid < HD) {
+#pragma unroll
+            for (int qi = 0; qi < PA_Q; qi++) {
+                acc[qi] *= a_s[qi];
+            }
+            for (int j = 0; j < PA_KEYS; j += 4) {
+                const float v0 = vs[j * HD + tid], v1 = vs[(j + 1) * HD + tid], v2 = vs[(j + 2) * HD + tid], v3 = vs[(j + 3) * HD + tid];
+#pragma unroll
+                for (int qi = 0; qi < PA_Q; qi++) {
+                    const float4 pr = *reinterpret_cast<const float4*>(ps + qi * PA_KEYS + j);
+                    acc[qi] = fmaf(pr.w, v3, fmaf(pr.z, v2, fmaf(pr.y, v1, fmaf(pr.x, v0, acc[qi]))));
+                }
+            }
+        }
+    }
+    if (tid < HD) {
+#pragma unroll
+        for (int qi = 0; qi < PA_Q; qi++) {
+            if (qi < nq) {
+                out[((int64_t)(t0 + qi) * heads + h) * HD + tid] = acc[qi] / l_s[qi];
+            }
+        }
+    }
+}
+
+__global__ void set_pos_kernel(int pos0, int* __restrict__ pos) { *pos = pos0; }
+
 // act = silu(gate) * up
 __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ act, int64_t count) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -795,6 +933,12 @@ struct jq_decoder {
     int64_t area[8];  // payload offsets: attention output, wo output, SwiGLU output, w2 output, logits; the Q4_K activation
                       // images of the attention output and of the SwiGLU output; [7] = the end of those
     int64_t stage[6]; // payload offsets of the staging words (8 bytes per element) of the five gathered activations; [5] = the end
+    // Workspace of the prompt path (jq_decoder_prompt), allocated by its first call and grown when a longer run arrives:
+    // one float buffer cut into the activations of `prompt_rows` tokens, a bfloat16 copy of a linear's input, the tokens.
+    float* prompt_buf;
+    uint16_t* prompt_bf16;
+    int* prompt_tokens;
+    int prompt_rows;
 };
 
 using namespace jq;
@@ -833,6 +977,9 @@ JQ_API int jq_decoder_destroy(jq_decoder* d) {
     cudaFree(d->argmax_v);
     cudaFree(d->argmax_i);
     cudaFreeHost(d->host_stage);
+    cudaFree(d->prompt_buf);
+    cudaFree(d->prompt_bf16);
+    cudaFree(d->prompt_tokens);
     if (d->graph != nullptr) {
         cudaGraphExecDestroy(d->graph);
     }
@@ -888,6 +1035,10 @@ JQ_API int jq_decoder_create(int device, int layers, int dim, int heads, int kv_
     d->graph_T = 0;
     d->graph_seq = 0;
     d->own_stream = nullptr;
+    d->prompt_buf = nullptr;
+    d->prompt_bf16 = nullptr;
+    d->prompt_tokens = nullptr;
+    d->prompt_rows = 0;
     d->world = 1;
     d->rank = 0;
     for (int r = 0; r < 8; r++) {
@@ -1661,6 +1812,201 @@ JQ_API int jq_decoder_forward_seq(jq_decoder* d, int seq, const int32_t* tokens_
 
 JQ_API int jq_decoder_forward_batch(jq_decoder* d, const int32_t* tokens_host, int n_seqs, int pos, float* logits_host, int32_t* next_host, void* stream) {
     return decoder_forward(d, 0, true, tokens_host, n_seqs, pos, logits_host, next_host, stream);
+}
+
+// ---- the prompt path ---------------------------------------------------------------------------------------------------------
+// A long run of consecutive tokens in one pass over the weights: the general path's operators on T rows, with every linear
+// on the tensor-core prefill kernel (its input rounded to bfloat16, FP32 accumulation) and the attention of all T queries by
+// attention_prompt_kernel. Only the last token's logits are computed.
+constexpr int PROMPT_MAX_TOKENS = 4096;
+
+static int ensure_prompt_workspace(jq_decoder* d, int rows) {
+    if (rows <= d->prompt_rows) {
+        return JQ_OK;
+    }
+    cudaFree(d->prompt_buf);
+    cudaFree(d->prompt_bf16);
+    cudaFree(d->prompt_tokens);
+    d->prompt_buf = nullptr;
+    d->prompt_bf16 = nullptr;
+    d->prompt_tokens = nullptr;
+    d->prompt_rows = 0;
+    const size_t kv_dim = (size_t)d->kv_heads * d->head_dim;
+    const size_t per_row = (size_t)5 * d->dim + 2 * kv_dim + 3 * (size_t)d->hidden;  // x, xn, q, att, proj; k, v; gate, up, act
+    const size_t widest = (size_t)(d->dim > d->hidden ? d->dim : d->hidden);
+    cudaError_t e = cudaMalloc(&d->prompt_buf, (size_t)rows * per_row * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&d->prompt_bf16, (size_t)rows * widest * sizeof(uint16_t));
+    if (e == cudaSuccess) e = cudaMalloc(&d->prompt_tokens, (size_t)rows * sizeof(int));
+    if (e != cudaSuccess) {
+        cudaFree(d->prompt_buf);
+        cudaFree(d->prompt_bf16);
+        cudaFree(d->prompt_tokens);
+        d->prompt_buf = nullptr;
+        d->prompt_bf16 = nullptr;
+        d->prompt_tokens = nullptr;
+        return e == cudaErrorMemoryAllocation ? fail(JQ_ERR_OOM, "jq_decoder_prompt: workspace for %d tokens", rows) : cuda_fail(e, "jq_decoder_prompt workspace");
+    }
+    d->prompt_rows = rows;
+    return JQ_OK;
+}
+
+JQ_API int jq_decoder_prompt(jq_decoder* d, int seq, const int32_t* tokens_host, int n_tokens, int pos0, float* logits_host, int32_t* next_host,
+                             void* stream) {
+    int rc = check_decoder(d, "jq_decoder_prompt");
+    if (rc != JQ_OK) {
+        return rc;
+    }
+    if (tokens_host == nullptr || n_tokens < 1 || n_tokens > PROMPT_MAX_TOKENS || pos0 < 0 || pos0 + n_tokens > d->max_seq) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_prompt: %d tokens at position %d (at most %d per call, %d positions)", n_tokens, pos0, PROMPT_MAX_TOKENS,
+                    d->max_seq);
+    }
+    if (seq < 0 || seq >= d->sequences) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_prompt: sequence %d of %d", seq, d->sequences);
+    }
+    if (d->world > 1) {
+        return fail(JQ_ERR_UNSUPPORTED, "jq_decoder_prompt: the row-sharded decoder takes its prompt through jq_decoder_forward");
+    }
+    if (d->head_dim != 64 && d->head_dim != 128) {
+        return fail(JQ_ERR_UNSUPPORTED, "jq_decoder_prompt: head size %d (64 or 128)", d->head_dim);
+    }
+    if (d->output == nullptr) {
+        return fail(JQ_ERR_INVALID, "jq_decoder_prompt: the output projection is not set");
+    }
+    for (size_t i = 0; i < d->lin.size(); i++) {
+        if (d->lin[i] == nullptr) {
+            return fail(JQ_ERR_INVALID, "jq_decoder_prompt: layer %d linear %d is not set", (int)(i / 7), (int)(i % 7));
+        }
+        if (!prefill_supported(View{d->lin[i]->q, d->lin[i]->aux, d->lin[i]->n, d->lin[i]->k, d->lin[i]->type})) {
+            return fail(JQ_ERR_UNSUPPORTED, "jq_decoder_prompt: layer %d linear %d has a format or shape the tensor-core kernel does not take", (int)(i / 7),
+                        (int)(i % 7));
+        }
+    }
+    int prev = -1;
+    cudaGetDevice(&prev);
+    if (prev != d->device) {
+        JQ_CUDA(cudaSetDevice(d->device));
+    }
+    cudaStream_t s = stream != nullptr ? (cudaStream_t)stream : d->own_stream;
+    const int T = n_tokens, dim = d->dim, hd = d->head_dim, hidden = d->hidden;
+    const int64_t kv_dim = (int64_t)d->kv_heads * hd;
+    rc = ensure_prompt_workspace(d, T);
+    auto CK = [&](cudaError_t e, const char* what) {
+        if (rc == JQ_OK && e != cudaSuccess) {
+            rc = cuda_fail(e, what);
+        }
+    };
+    auto LAUNCHED = [&](const char* name) {
+        count_launch(1);
+        if (rc == JQ_OK) {
+            rc = check_launch(name);
+        }
+    };
+    if (rc == JQ_OK) {
+        float* p = d->prompt_buf;
+        float* x = p; p += (size_t)T * dim;
+        float* xn = p; p += (size_t)T * dim;
+        float* q = p; p += (size_t)T * dim;
+        float* att = p; p += (size_t)T * dim;
+        float* proj = p; p += (size_t)T * dim;
+        float* k = p; p += (size_t)T * kv_dim;
+        float* v = p; p += (size_t)T * kv_dim;
+        float* gate = p; p += (size_t)T * hidden;
+        float* up = p; p += (size_t)T * hidden;
+        float* act = p;
+        uint16_t* xb = d->prompt_bf16;
+        // a linear on all T rows: the input rounded to bfloat16 once (`fresh`), then the tensor-core kernel
+        auto LIN = [&](const jq_weight* w, const float* in, float* out_, bool fresh) {
+            if (rc == JQ_OK && fresh) {
+                rc = launch_f32_to_bf16(in, xb, (int64_t)T * w->k, s);
+            }
+            if (rc == JQ_OK) {
+                rc = launch_prefill_bf16(View{w->q, w->aux, w->n, w->k, w->type}, xb, T, nullptr, out_, s);
+            }
+        };
+        // the copy out of pageable host memory is staged before the call returns: the caller's buffer is free afterwards
+        CK(cudaMemcpyAsync(d->prompt_tokens, tokens_host, (size_t)T * sizeof(int), cudaMemcpyHostToDevice, s), "prompt tokens");
+        if (rc == JQ_OK) {
+            set_pos_kernel<<<1, 1, 0, s>>>(pos0, d->pos);
+            LAUNCHED("set_pos_kernel");
+        }
+        if (rc == JQ_OK) {
+            embed_kernel<<<T, 256, 0, s>>>(d->prompt_tokens, d->embed, x, dim, d->vocab);
+            LAUNCHED("embed_kernel");
+        }
+        const float scale = (float)(1.0 / std::sqrt((double)hd));
+        const size_t seq_elems = (size_t)d->layers * d->max_seq * kv_dim, seq_base = (size_t)seq * seq_elems;
+        static std::atomic<uint64_t> configured{0};  // the opt-in for large dynamic shared memory is per device
+        if (rc == JQ_OK && (configured.load() >> (d->device & 63) & 1) == 0) {
+            CK(cudaFuncSetAttribute(attention_prompt_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prompt_attention_smem<64>()), "attention_prompt_kernel");
+            CK(cudaFuncSetAttribute(attention_prompt_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prompt_attention_smem<128>()), "attention_prompt_kernel");
+            configured.fetch_or((uint64_t)1 << (d->device & 63));
+        }
+        for (int l = 0; l < d->layers && rc == JQ_OK; l++) {
+            const jq_weight* const* L = &d->lin[(size_t)l * 7];
+            float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
+            float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
+            add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, l == 0 ? nullptr : proj, d->norms + (size_t)(2 * l) * dim, d->eps, xn, dim);
+            LAUNCHED("add_rmsnorm_kernel");
+            LIN(L[0], xn, q, true);
+            LIN(L[1], xn, k, false);
+            LIN(L[2], xn, v, false);
+            if (rc != JQ_OK) break;
+            rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(q, k, v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd, 1, 0);
+            LAUNCHED("rope_store_kernel");
+            const dim3 agrid((unsigned)d->heads, (unsigned)((T + PA_Q - 1) / PA_Q));
+            if (hd == 128) {
+                attention_prompt_kernel<128><<<agrid, PA_THREADS, prompt_attention_smem<128>(), s>>>(q, kc, vc, att, d->pos, d->heads, d->kv_heads, T, scale);
+            } else {
+                attention_prompt_kernel<64><<<agrid, PA_THREADS, prompt_attention_smem<64>(), s>>>(q, kc, vc, att, d->pos, d->heads, d->kv_heads, T, scale);
+            }
+            LAUNCHED("attention_prompt_kernel");
+            LIN(L[3], att, proj, true);
+            if (rc != JQ_OK) break;
+            add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, xn, dim);
+            LAUNCHED("add_rmsnorm_kernel");
+            LIN(L[4], xn, gate, true);
+            LIN(L[5], xn, up, false);
+            if (rc != JQ_OK) break;
+            const int64_t cnt = (int64_t)T * hidden;
+            swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(gate, up, act, cnt);
+            LAUNCHED("swiglu_kernel");
+            LIN(L[6], act, proj, true);
+        }
+        if (rc == JQ_OK) {
+            // the last token alone goes on: final residual add and norm, output projection (FP32 path), first index of the maximum
+            const size_t last = (size_t)(T - 1) * dim;
+            add_rmsnorm_kernel<<<1, 256, 0, s>>>(x + last, proj + last, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+            LAUNCHED("add_rmsnorm_kernel");
+            if (rc == JQ_OK) rc = linear_device(d->output, d->xn, 1, nullptr, d->logits, s);
+        }
+        if (rc == JQ_OK) {
+            argmax_kernel<<<1, 1024, 0, s>>>(d->logits, d->argmax, d->vocab);
+            LAUNCHED("argmax_kernel");
+        }
+    }
+    if (rc == JQ_OK && (logits_host != nullptr || next_host != nullptr)) {
+        if (logits_host != nullptr) {
+            CK(cudaMemcpyAsync(logits_host, d->logits, (size_t)d->vocab * sizeof(float), cudaMemcpyDeviceToHost, s), "logits");
+        }
+        if (next_host != nullptr) {
+            CK(cudaMemcpyAsync(d->host_stage + MAX_TOKENS + 1, d->argmax, sizeof(int), cudaMemcpyDeviceToHost, s), "argmax");
+        }
+        CK(cudaStreamSynchronize(s), "jq_decoder_prompt");
+        if (rc == JQ_OK) {
+            int status = 0;
+            rc = prefill_status(&status);
+            if (rc == JQ_OK && status != 0) {
+                rc = fail(JQ_ERR_TIMEOUT, "jq_decoder_prompt: a bounded wait of the tensor-core kernel gave up (code %d)", status);
+            }
+        }
+        if (rc == JQ_OK && next_host != nullptr) {
+            next_host[0] = d->host_stage[MAX_TOKENS + 1];
+        }
+    }
+    if (prev >= 0 && prev != d->device) {
+        cudaSetDevice(prev);
+    }
+    return rc;
 }
 
 // Key/value caches for `sequences` (1..16) independent sequences; what the caches held is lost.

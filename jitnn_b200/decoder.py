@@ -101,6 +101,17 @@ class LlamaDecoder:
         toks = np.ascontiguousarray(tokens, dtype=np.int32)
         check(_lib.load().jq_decoder_forward_seq(self._h, seq, toks.ctypes.data, toks.size, pos0, None, None, stream))
 
+    def prompt(self, tokens, pos0, want_logits=True, stream=None, seq=0):
+        """Runs a long run of tokens (up to 4096) of sequence `seq` starting at position pos0 in one pass over the weights, the
+        linears on the tensor-core prefill kernel with bfloat16 operands; returns (logits [vocab] of the last token or None,
+        the greedy token after it)."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        logits = np.empty(self.vocab, dtype=np.float32) if want_logits else None
+        nxt = np.empty(1, dtype=np.int32)
+        check(_lib.load().jq_decoder_prompt(self._h, seq, toks.ctypes.data, toks.size, pos0, None if logits is None else logits.ctypes.data,
+                                            nxt.ctypes.data, stream))
+        return logits, int(nxt[0])
+
     def set_sequences(self, sequences):
         """Key/value caches for `sequences` (1..16) independent sequences; cached positions are lost."""
         check(_lib.load().jq_decoder_set_sequences(self._h, sequences))
