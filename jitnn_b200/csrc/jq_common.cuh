@@ -144,8 +144,10 @@ int gemv_peer_status(int* status);
 // Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
 // rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.
+// staging_offset >= 0: the outputs travel as marked words through that area of the payload and the kernel ends when this
+// rank's y is complete (wait_after is then moot); < 0: straight into every rank's y, announced through the arrival counters.
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                           int rank, int world, cudaStream_t s, bool wait_first, bool wait_after);
+                           int64_t staging_offset, int rank, int world, cudaStream_t s, bool wait_first, bool wait_after);
 // Status word of the waits that the decoder's kernels make themselves (peer_wait_inline): 0 or 32 + rank, cleared by the call.
 int decoder_peer_status(int* status);
 // Q6_K for one row of x whose activation image (jq_q6k_image.cuh) a kernel earlier in the stream has written.

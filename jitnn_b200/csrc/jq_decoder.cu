@@ -690,7 +690,7 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     __syncthreads();
     if (!last_flag) {
         if constexpr (PEER) {
-            peer_publish(pi.flags, pi.rank, pi.world);
+            peer_publish(pi.flags, pi.rank, pi.world, false, nullptr, false);  // this CTA stored nothing to a peer
         }
         return;
     }
@@ -748,20 +748,32 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
 }
 
 // act = silu(gate) * up (F.java:1158-1161) for one super-block of 256 per CTA, written as the next linear's image.
+// The sharded form takes SWIGLU_PEER_BLOCKS super-blocks per CTA (one warp each), so that fewer CTAs have to announce
+// their stores to the other ranks (each announcement is a release at system scope).
+constexpr int SWIGLU_PEER_BLOCKS = 4;
 template <bool PEER>
-__global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im, PeerImage pi) {
-    __shared__ __align__(16) float xs[256];
+__global__ void __launch_bounds__(256) swiglu_image_kernel(const float* __restrict__ gate, const float* __restrict__ up, Images im, PeerImage pi, int blocks) {
+    constexpr int PER_CTA = PEER ? SWIGLU_PEER_BLOCKS : 1;
+    __shared__ __align__(16) float xs[PER_CTA][256];
     pdl_enter();
-    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-    const float g = gate[i];
-    xs[threadIdx.x] = (g / (1.0f + expf(-g))) * up[i];
+    const int b0 = (int)blockIdx.x * PER_CTA;
+    const int nb = blocks - b0 < PER_CTA ? blocks - b0 : PER_CTA;
+#pragma unroll
+    for (int j = 0; j < PER_CTA; j++) {
+        if (j < nb) {
+            const int64_t i = (int64_t)(b0 + j) * 256 + threadIdx.x;
+            const float g = gate[i];
+            xs[j][threadIdx.x] = (g / (1.0f + expf(-g))) * up[i];
+        }
+    }
     __syncthreads();
-    if (threadIdx.x < 32) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp < nb) {
         if constexpr (PEER) {
-            write_images(xs, pi.first_block + (int)blockIdx.x, im, threadIdx.x);
-            peer_copy_block(pi, (size_t)(pi.first_block + (int)blockIdx.x) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, threadIdx.x);
+            write_images(xs[warp], pi.first_block + b0 + warp, im, lane);
+            peer_copy_block(pi, (size_t)(pi.first_block + b0 + warp) * q4k::Cfg<1>::PB, (int)q4k::Cfg<1>::PB, lane);
         } else {
-            write_images(xs, blockIdx.x, im, threadIdx.x);
+            write_images(xs[warp], b0 + warp, im, lane);
         }
     }
     if constexpr (PEER) {
@@ -1373,7 +1385,7 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
             "norm_image_kernel");
         GEMV(L[4], d->gate, L[5], d->up, s);
         if (rc != JQ_OK) break;
-        CKL(launch_pdl(swiglu_image_kernel<false>, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]}), PeerImage{}), "swiglu_image_kernel");
+        CKL(launch_pdl(swiglu_image_kernel<false>, dim3(d->hidden / 256), dim3(256), 0, s, true, d->gate, d->up, images_for({L[6]}), PeerImage{}, d->hidden / 256), "swiglu_image_kernel");
         GEMV(L[6], d->proj, nullptr, nullptr, s);
     }
     if (rc == JQ_OK) {
@@ -1621,9 +1633,9 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             if (rc == JQ_OK && e != cudaSuccess) {
                 rc = cuda_fail(e, "attention_image_kernel");
             }
-            // wo waits for the image's flags itself, and the norm behind it for wo's (no wait kernels in between)
-            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[3], shard_image(d, 5), dim, d->rank * dim_l, d->peer_buf, d->area[1], d->rank, G, s, true, false);
-            pending_wait = true;
+            // wo waits for the image's counters itself; its outputs travel as marked words that its own threads collect, so
+            // the norm behind it finds the vector complete
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[3], shard_image(d, 5), dim, d->rank * dim_l, d->peer_buf, d->area[1], d->stage[1], d->rank, G, s, true, false);
         } else {
             rope_store_kernel<<<dim3(T, heads + 2 * kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, heads, kv_heads, hd, pos_step,
                                                                                tok_stride);
@@ -1649,14 +1661,13 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         if (rc != JQ_OK) break;
         if (fused_in && hidden_l % 256 == 0 && L[6]->type == JQ_TYPE_Q4_K) {
             count_launch(1);
-            const cudaError_t e = launch_pdl(swiglu_image_kernel<true>, dim3((unsigned)(hidden_l / 256)), dim3(256), 0, s, true, (const float*)d->gate,
-                                             (const float*)d->up, Images{shard_image(d, 6), nullptr}, peer_image(d, 6, (int)(hidden_l / 256)));
+            const int blocks = (int)(hidden_l / 256);
+            const cudaError_t e = launch_pdl(swiglu_image_kernel<true>, dim3((unsigned)((blocks + SWIGLU_PEER_BLOCKS - 1) / SWIGLU_PEER_BLOCKS)), dim3(256), 0, s, true,
+                                             (const float*)d->gate, (const float*)d->up, Images{shard_image(d, 6), nullptr}, peer_image(d, 6, blocks), blocks);
             if (rc == JQ_OK && e != cudaSuccess) {
                 rc = cuda_fail(e, "swiglu_image_kernel");
             }
-            const bool last = l == d->layers - 1;  // the final norm is the general kernel: it gets a wait kernel in front
-            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[6], shard_image(d, 6), dim, d->rank * dim_l, d->peer_buf, d->area[3], d->rank, G, s, true, last);
-            pending_wait = !last;
+            if (rc == JQ_OK) rc = peer_linear_q4k_imaged(L[6], shard_image(d, 6), dim, d->rank * dim_l, d->peer_buf, d->area[3], d->stage[3], d->rank, G, s, true, false);
         } else {
             const int64_t cnt = (int64_t)T * hidden_l;
             swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);

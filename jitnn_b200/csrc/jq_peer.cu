@@ -257,13 +257,13 @@ static int enqueue_scatter(const float* slice, int64_t m, int64_t n_slice, int64
 namespace jq {
 
 int peer_linear_q4k_imaged(const jq_weight* w, const uint8_t* image, int64_t n_total, int64_t col0, void* const* peer_buffers, int64_t payload_offset,
-                           int rank, int world, cudaStream_t s, bool wait_first, bool wait_after) {
+                           int64_t staging_offset, int rank, int world, cudaStream_t s, bool wait_first, bool wait_after) {
     PeerTargets tg;
-    int rc = fill_targets(peer_buffers, payload_offset, -16, rank, world, &tg, "peer linear");
+    int rc = fill_targets(peer_buffers, payload_offset, staging_offset < 0 ? -16 : staging_offset, rank, world, &tg, "peer linear");
     if (rc != JQ_OK) {
         return rc;
     }
-    PeerOut po = peer_out(tg, w->n, n_total, col0, rank, world);  // no staging words: announced through the arrival counters
+    PeerOut po = peer_out(tg, w->n, n_total, col0, rank, world);
     po.wait_first = wait_first ? 1 : 0;
     po.wait_after = wait_after ? 1 : 0;
     rc = device_table(po, s, &po.table);

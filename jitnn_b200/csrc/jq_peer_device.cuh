@@ -51,13 +51,19 @@ __device__ __forceinline__ void peer_wait_for(const uint32_t* flags, uint32_t se
 // exchange number (a plain store: the kernels behind this one in the stream read it). With `wait` CTA 0 then waits
 // (bounded) until the other ranks' parts of the same exchange have arrived here, so that the kernel itself ends only
 // when this rank's y is complete and no separate waiting launch is needed. `status` as for peer_wait_for.
-__device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, int world, bool wait = false, int* status = nullptr) {
+// wrote = false: this CTA stored nothing to a peer, so its share needs no ordering and travels as a relaxed add (a release
+// at system scope costs microseconds, and the releases of a grid queue up).
+__device__ __forceinline__ void peer_publish(uint32_t* const* flags, int rank, int world, bool wait = false, int* status = nullptr, bool wrote = true) {
     const uint32_t G = gridDim.x * gridDim.y * gridDim.z;
     const uint32_t i = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
     __syncthreads();
     if ((int)threadIdx.x < world) {
         const uint32_t share = (uint32_t)(((uint64_t)(i + 1) * PEER_UNITS) / G) - (uint32_t)(((uint64_t)i * PEER_UNITS) / G);
-        asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flags[threadIdx.x] + rank), "r"(share) : "memory");
+        if (wrote) {
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flags[threadIdx.x] + rank), "r"(share) : "memory");
+        } else {
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(flags[threadIdx.x] + rank), "r"(share) : "memory");
+        }
     }
     if (i == 0 && threadIdx.x < 32) {
         uint32_t seq = 0;
