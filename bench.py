@@ -573,14 +573,15 @@ FORMAT_BPW = {"Q8_0": 34 / 32, "Q4_0": 18 / 32, "Q4_1": 20 / 32, "Q4_K": 144 / 2
 
 
 def formats_leg(torch, device, L, _lib, reps=25):
-    """The decode GEMV (M = 1) of the other formats of the path: BASELINE.json configs[0] (Q8_0, 4096x4096, weights from
-    the reference's host quantiser as restated in jq_quantize_q8_0) and one large layer per format. Four copies of every
+    """The decode GEMV of the other formats of the path at M = 1, 8 and 16: BASELINE.json configs[0] (Q8_0, 4096x4096, weights
+    from the reference's host quantiser as restated in jq_quantize_q8_0) and one large layer per format. Four copies of every
     weight in rotation (so that no launch finds its weight in L2), replayed from a CUDA graph; GB/s over the algorithmic
-    bytes N K bytes-per-weight + 4 K + 4 N against the measured HBM copy peak."""
+    bytes N K bytes-per-weight + 4 M K + 4 M N against the measured HBM copy peak. The top-level figures of a case are those
+    of M = 1; `m8` and `m16` sit beside them (a format whose kernel takes fewer rows per pass reads its weights several times)."""
     import jitnn_b200
     from jitnn_b200 import Tensor, synth
     peak, which = measured_peaks()
-    out = {"m": 1, "peak_GBps": peak, "peak_source": "of " + which, "cases": {}}
+    out = {"m": [1, 8, 16], "peak_GBps": peak, "peak_source": "of " + which, "cases": {}}
     side = torch.cuda.Stream(device)
     for t, n, k in FORMAT_CASES:
         g = torch.Generator(device=device).manual_seed(n + 3 * k + len(t))
@@ -590,32 +591,39 @@ def formats_leg(torch, device, L, _lib, reps=25):
             raw = (jitnn_b200.Quant.quantizeQ8Blocks(wf, device.index) if t == "Q8_0" else synth.QUANTIZERS[t](wf)).cpu().numpy()
             del wf
             ws.append(Tensor.quantized(t, raw, n, k, device=device.index))
-        x = torch.randn(1, k, generator=g, device=device)
-        y = torch.empty(1, n, device=device)
-        with torch.cuda.stream(side):
-            sp = ctypes.c_void_p(side.cuda_stream)
+        case = {}
+        for m in (1, 8, 16):
+            x = torch.randn(m, k, generator=g, device=device)
+            y = torch.empty(m, n, device=device)
+            with torch.cuda.stream(side):
+                sp = ctypes.c_void_p(side.cuda_stream)
 
-            def rot():
-                for w in ws:
-                    _lib.check(L.jq_linear_f32(w._handle(), x.data_ptr(), 1, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
-            rot()
-            torch.cuda.synchronize(device)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
+                def rot():
+                    for w in ws:
+                        _lib.check(L.jq_linear_f32(w._handle(), x.data_ptr(), m, None, y.data_ptr(), _lib.JQ_MEM_DEVICE, sp))
                 rot()
-            graph.replay()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize(device)
-            a.record(side)
-            for _ in range(reps):
+                torch.cuda.synchronize(device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    rot()
                 graph.replay()
-            b.record(side)
-            torch.cuda.synchronize(device)
-        us = a.elapsed_time(b) * 1e3 / (reps * POOL_COPIES)
-        nbytes = n * k * FORMAT_BPW[t] + 4 * k + 4 * n
-        gbps = nbytes / us / 1e3
-        out["cases"]["%s_%dx%d" % (t, n, k)] = {"us": round(us, 2), "GBps": round(gbps, 1), "frac": round(gbps / peak, 4)}
-        del graph
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize(device)
+                a.record(side)
+                for _ in range(reps):
+                    graph.replay()
+                b.record(side)
+                torch.cuda.synchronize(device)
+            us = a.elapsed_time(b) * 1e3 / (reps * POOL_COPIES)
+            nbytes = n * k * FORMAT_BPW[t] + 4 * m * k + 4 * m * n
+            gbps = nbytes / us / 1e3
+            res = {"us": round(us, 2), "GBps": round(gbps, 1), "frac": round(gbps / peak, 4)}
+            if m == 1:
+                case.update(res)
+            else:
+                case["m%d" % m] = res
+            del graph
+        out["cases"]["%s_%dx%d" % (t, n, k)] = case
         for w in ws:
             w.release()
     return out

@@ -56,7 +56,7 @@ def test_benchmark_weights(t):
     check(t, 512, 4096, 512, seed=3, weights="synthetic")
 
 
-@pytest.mark.parametrize("t,n,k", [("Q4_K", 4096, 4096), ("Q4_K", 11008, 4096), ("Q6_K", 4096, 11008)])
+@pytest.mark.parametrize("t,n,k", [("Q4_K", 4096, 4096), ("Q4_K", 11008, 4096), ("Q6_K", 4096, 11008), ("Q6_K", 32000, 4096)])
 def test_benchmark_shapes_against_a_gpu_reference(t, n, k):
     """At the benchmark's sizes (M = 512) the kernel takes its other tile shapes: 256 tokens with k split in two for the
     4096-row weights, two feature tiles per CTA for 11008 rows. The CPU oracle would take minutes here, so the reference is
