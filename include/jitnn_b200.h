@@ -177,7 +177,10 @@ JQ_API int jq_device_status(int device, int* status);
  *                  buffers in between): a rank may run one exchange ahead of another. A thread that has waited
  *                  "peer_wait_us" (option, default 400 000) in all leaves status 32 + r for jq_device_status, r being the
  *                  rank that owns the missing column when the n_total columns are split evenly, and the kernel returns
- *                  with that part of y unwritten. Works inside a captured CUDA graph.
+ *                  with that part of y unwritten. After such a timeout the ranks' exchange numbers on the buffers are out
+ *                  of step: the buffers are to be released (jq_peer_close / jq_peer_free) and allocated anew before the
+ *                  ranks exchange again. Works inside a captured CUDA graph (a captured call pins the library's per-stream
+ *                  scratch buffers and the buffer's target-table slot it uses: neither is ever freed or reused).
  */
 JQ_API int jq_peer_alloc(int device, int64_t payload_bytes, void** ptr, void* handle_out);
 JQ_API int jq_peer_open(int device, const void* handle, void** ptr);

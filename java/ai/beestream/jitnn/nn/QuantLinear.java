@@ -8,7 +8,7 @@ import ai.beestream.jitnn.Tensor;
  * A linear layer whose weight stays in its GGUF block format: the counterpart of nn/Linear.java:56-58 (forward =
  * F.linear(x, weight, bias)) for a quantised weight, so that a Llama built from jitnn-nn's modules can hold the tensors of
  * a GGUF file as they are. forward goes through Gguf.linear (ops/Gguf.java:76-98), whose MatVec / LinearQ8 operators
- * carry the cpu(Node) hook of INTEGRATION.md section 3; with -Djitnn.b200=true that hook runs libjitnn_b200, otherwise
+ * carry a cpu(Node) hook (engine/Op.java:46-55) that asks B200Gate; with -Djitnn.b200=true that hook runs libjitnn_b200, otherwise
  * jitNN's own kernels, with the same results within the operator's tolerance.
  *
  * The weight takes no gradient (a quantised tensor is a constant of the graph, ops/Gguf.java:208-212); the input does.

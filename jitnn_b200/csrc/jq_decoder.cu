@@ -502,6 +502,8 @@ __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x,
     __shared__ float scratch[32];
     __shared__ float partial;
     cg::cluster_group cluster = cg::this_cluster();
+    // the norm weights never change: requested before the wait for the kernel in front
+    const float4 ww = reinterpret_cast<const float4*>(w + (int)blockIdx.x * (dim / (int)gridDim.x))[threadIdx.x];
     pdl_enter();
     if (wait_flags != nullptr) {
         // delta is what the ranks' latest exchange delivered (row-sharded decoder): complete once all their flags are up
@@ -537,7 +539,6 @@ __global__ void __launch_bounds__(1024) norm_image_kernel(float* __restrict__ x,
         total += *cluster.map_shared_rank(&partial, r);
     }
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
-    const float4 ww = reinterpret_cast<const float4*>(w + first)[i];
     reinterpret_cast<float4*>(norm_xs)[i] = make_float4(a.x * inv * ww.x, a.y * inv * ww.y, a.z * inv * ww.z, a.w * inv * ww.w);
     __syncthreads();
     const int blocks = per_cta >> 8, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -571,27 +572,29 @@ __global__ void __launch_bounds__(ATTF_THREADS) attention_image_kernel(const flo
     __shared__ __align__(16) float red[8][HD];
     __shared__ __align__(16) float outs[256];
     __shared__ int last_flag;
-    pdl_enter();
+    // The position was set before the first kernel of this step started, and the cached keys and values of earlier
+    // positions by earlier steps: both are read before the wait for the kernel in front, so that a CTA scheduled while that
+    // kernel still runs has its cache lines on the way.
     const int h = blockIdx.x, sp = blockIdx.y, splits = gridDim.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int pos = *pos0, keys = pos + 1, k0 = sp * ATT_CHUNK;
     const int kv_dim = kv_heads * HD, group = heads / kv_heads, kvh = h / group;
     float* out = part + ((int64_t)h * stride_splits + sp) * (HD + 2);
-    if (k0 < keys) {
-        const int cnt = keys - k0 < ATT_CHUNK ? keys - k0 : ATT_CHUNK;
-        const bool has_new = pos < k0 + ATT_CHUNK;  // the new token's key and value belong to this chunk
-        // Warp w owns keys 8w .. 8w + 7 of the chunk, a lane four consecutive dimensions of each. Their cached keys and
-        // values are requested at once, before anything else is waited for.
-        float4 kreg[8], vreg[8];
+    const int cnt = keys - k0 < ATT_CHUNK ? keys - k0 : ATT_CHUNK;
+    // Warp w owns keys 8w .. 8w + 7 of the chunk, a lane four consecutive dimensions of each.
+    float4 kreg[8], vreg[8];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int j = warp * 8 + u;
-            kreg[u] = vreg[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (j < cnt && k0 + j != pos) {
-                kreg[u] = __ldg(reinterpret_cast<const float4*>(k_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
-                vreg[u] = __ldg(reinterpret_cast<const float4*>(v_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
-            }
+    for (int u = 0; u < 8; u++) {
+        const int j = warp * 8 + u;
+        kreg[u] = vreg[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (j < cnt && k0 + j != pos) {
+            kreg[u] = __ldg(reinterpret_cast<const float4*>(k_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
+            vreg[u] = __ldg(reinterpret_cast<const float4*>(v_cache + (int64_t)(k0 + j) * kv_dim + kvh * HD) + lane);
         }
+    }
+    pdl_enter();
+    if (k0 < keys) {
+        const bool has_new = pos < k0 + ATT_CHUNK;  // the new token's key and value belong to this chunk
         if (tid < HALF) {
             const float c = cos_t[pos * HALF + tid], s = sin_t[pos * HALF + tid];
             const float a = q[h * HD + tid], b = q[h * HD + tid + HALF];

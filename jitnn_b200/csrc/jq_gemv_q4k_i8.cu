@@ -664,6 +664,8 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
     // One or two rows of x and k <= 8192: the GEMV builds the image itself (every CTA makes all of it, which is redundant work
     // that grows with k; up to four super-blocks per warp it costs less than a launch and the scratch round trip). Not when
     // x lies in host memory: the image kernel reads it once, the thread blocks of the GEMV would each read it across PCIe.
+    // With three to eight rows a warp would build eight parts for k = 4096, each behind a load of x from L2 (about 0.7
+    // microseconds, two in flight): measured 3 microseconds slower per launch than the image kernel, so those rows keep it.
     constexpr bool CAN_FUSE = !WIDE;
     const bool fuse = CAN_FUSE && may_fuse && x != nullptr && KB <= 4 * sh.nw;
     if (x != nullptr && !fuse) {
@@ -739,11 +741,11 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     if (v.type == JQ_TYPE_Q5_K) {
         if (rows == 1) return run<1, true>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
         if (rows == 2) return run<2, true>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
-        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled, false);
+        return run<8, true>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
     }
     if (rows == 1) return run<1, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
     if (rows == 2) return run<2, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
-    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled, false);
+    return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
 }
 
 #ifdef JQ_Q4K_TRACE
