@@ -304,8 +304,9 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
     w->layout = layout;
     w->n = rows;
     w->k = k;
-    w->q_bytes = tiled_layout(type) ? tiled_rows(rows) * (k / qk) * plane_q_bytes(type) : blocks * plane_q_bytes(type);
-    w->aux_bytes = blocks * plane_aux_bytes(type);
+    const bool tiled = tiled_layout(type) || tiled_planes(type);
+    w->q_bytes = tiled ? tiled_rows(rows) * (k / qk) * plane_q_bytes(type) : blocks * plane_q_bytes(type);
+    w->aux_bytes = (tiled_planes(type) ? tiled_rows(rows) * (k / qk) : blocks) * plane_aux_bytes(type);
     w->q = nullptr;
     w->aux = nullptr;
 
@@ -316,12 +317,12 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
     cudaError_t e = cudaMalloc(&w->q, (size_t)(w->q_bytes + pad_q + 16));
     if (e == cudaSuccess) {
         // a tiled weight is zeroed as a whole (the rows that pad its last tile), the others behind their last row
-        e = tiled_layout(type) ? cudaMemset(w->q, 0, (size_t)(w->q_bytes + pad_q + 16)) : cudaMemset(w->q + w->q_bytes, 0, (size_t)(pad_q + 16));
+        e = tiled ? cudaMemset(w->q, 0, (size_t)(w->q_bytes + pad_q + 16)) : cudaMemset(w->q + w->q_bytes, 0, (size_t)(pad_q + 16));
     }
     if (e == cudaSuccess && w->aux_bytes > 0) {
         e = cudaMalloc(&w->aux, (size_t)(w->aux_bytes + pad_aux));
         if (e == cudaSuccess) {
-            e = cudaMemset(w->aux + w->aux_bytes, 0, (size_t)pad_aux);
+            e = tiled ? cudaMemset(w->aux, 0, (size_t)(w->aux_bytes + pad_aux)) : cudaMemset(w->aux + w->aux_bytes, 0, (size_t)pad_aux);
         }
     }
     if (e != cudaSuccess) {
@@ -341,7 +342,7 @@ int jq_weight_upload_rows(int device, int type, const void* host_blocks, int64_t
             if (e != cudaSuccess) {
                 rc = cuda_fail(e, "staging the verbatim blocks");
             } else {
-                rc = tiled_layout(type) ? launch_tile(type, tmp, w->q, rows, k / qk, false, nullptr) : launch_repack(type, tmp, w->q, w->aux, blocks, nullptr);
+                rc = tiled_layout(type) ? launch_tile(type, tmp, w->q, rows, k / qk, false, nullptr) : launch_repack(type, tmp, w->q, w->aux, blocks, k / qk, nullptr);
                 if (rc == JQ_OK) {
                     e = cudaDeviceSynchronize();
                     if (e != cudaSuccess) {
@@ -425,7 +426,7 @@ int jq_weight_download(const jq_weight* w, void* host_blocks, int64_t nbytes) {
     uint8_t* tmp = nullptr;
     JQ_CUDA(cudaMalloc(&tmp, (size_t)want));
     rc = tiled_layout(w->type) ? launch_tile(w->type, tmp, w->q, w->n, w->k / block_values(w->type), true, nullptr)
-                               : launch_unpack(w->type, w->q, w->aux, tmp, blocks, nullptr);
+                               : launch_unpack(w->type, w->q, w->aux, tmp, blocks, w->k / block_values(w->type), nullptr);
     if (rc == JQ_OK) {
         cudaError_t e = cudaMemcpy(host_blocks, tmp, (size_t)want, cudaMemcpyDeviceToHost);
         if (e != cudaSuccess) {
@@ -664,9 +665,9 @@ int jq_device_status(int device, int* status) {
     if (rc == JQ_OK && *status == 0) {
         *status = peer;
     }
-    for (int part = 0; part < 3 && rc == JQ_OK; part++) {
+    for (int part = 0; part < 4 && rc == JQ_OK; part++) {
         int other = 0;
-        rc = part == 0 ? gemv_peer_status(&other) : (part == 1 ? decoder_peer_status(&other) : gemv_umma_status(&other));
+        rc = part == 0 ? gemv_peer_status(&other) : (part == 1 ? decoder_peer_status(&other) : (part == 2 ? gemv_umma_status(&other) : gemv_q6k_status(&other)));
         if (rc == JQ_OK && *status == 0) {
             *status = other;
         }

@@ -83,7 +83,14 @@ inline int plane_aux_bytes(int type) {
 // The last tile is padded with zero rows. No byte of a block changes; jq_weight_download restores GGUF's order.
 constexpr int TILE_ROWS = 128;
 __host__ __device__ inline bool tiled_layout(int type) { return type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K; }
+// Q6_K keeps its two planes (208 bytes of quants and scales, one fp16 d per block) and orders the blocks of each plane the
+// same way, so that 16 rows x one super-block are 3328 contiguous bytes of the quant plane and 32 of the d plane.
+__host__ __device__ inline bool tiled_planes(int type) { return type == JQ_TYPE_Q6_K; }
 __host__ __device__ inline int64_t tiled_rows(int64_t n) { return (n + TILE_ROWS - 1) / TILE_ROWS * TILE_ROWS; }
+// Position of block b of `row` among the blocks of a tiled plane with kb blocks per row.
+__host__ __device__ inline int64_t tiled_index(int64_t row, int64_t b, int64_t kb) {
+    return ((row >> 7) * kb + b) * TILE_ROWS + (row & (TILE_ROWS - 1));
+}
 // Byte offset of block b of `row` in a tiled weight with kb blocks of `bytes` bytes per row.
 __host__ __device__ inline int64_t tiled_offset(int64_t row, int64_t b, int64_t kb, int bytes) {
     return ((row >> 7) * kb + b) * (int64_t)(TILE_ROWS * bytes) + (row & (TILE_ROWS - 1)) * bytes;
@@ -104,8 +111,9 @@ struct View {
 };
 
 // ---- kernel launchers (one translation unit each) ----------------------------------------------
-int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, cudaStream_t s);
-int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, cudaStream_t s);
+// kb: blocks per row; the planes of a type with tiled_planes() hold their blocks in tiled order (tiled_rows(n) rows).
+int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, int64_t kb, cudaStream_t s);
+int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, int64_t kb, cudaStream_t s);
 // Verbatim blocks [n, kb] <-> the tiled layout of Q4_K and Q5_K (`tiled` holds tiled_rows(n) rows).
 int launch_tile(int type, const uint8_t* verbatim, uint8_t* tiled, int64_t n, int64_t kb, bool inverse, cudaStream_t s);
 int launch_dequantize(const View& v, float* dst, cudaStream_t s);
@@ -141,6 +149,7 @@ int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* imag
                               const PeerOut* peer = nullptr);
 // Status word of the waits a GEMV makes itself for a peer exchange (peer_wait_inline): 0 or 32 + rank, cleared by the call.
 int gemv_peer_status(int* status);
+int gemv_q6k_status(int* status);  // the same for the Q6_K kernel's weight-ring waits (0 or 25)
 // Pieces of the peer exchange (jq_peer.cu) for the row-sharded decoder: the bounded wait for all ranks' flags of this
 // rank's latest exchange, and a Q4_K row shard applied to an activation image that is already complete, its outputs
 // stored into every rank's y [1, n_total] at payload_offset, followed by that wait.

@@ -244,13 +244,16 @@ struct Fmt<JQ_TYPE_Q6_K> {
         uint32_t d;
     };
     __device__ static void load(const View& v, int64_t block, int unit, Raw& r) {
-        const uint8_t* b = v.q + block * 208;
+        const uint32_t kb = (uint32_t)(v.k >> 8);
+        const uint32_t row = (uint32_t)block / kb;
+        const int64_t at = tiled_index(row, (uint32_t)block - row * kb, kb);  // the planes hold their blocks in tiled order
+        const uint8_t* b = v.q + at * 208;
         const int n = unit >> 1, c = unit & 1;
         r.la = ld16(b + 64 * n + 16 * c);
         r.lb = ld16(b + 64 * n + 32 + 16 * c);
         r.hq = ld16(b + 128 + 32 * n + 16 * c);
         r.sv = ld16(b + 192);
-        r.d = __ldg(reinterpret_cast<const unsigned short*>(v.aux) + block);
+        r.d = __ldg(reinterpret_cast<const unsigned short*>(v.aux) + at);
     }
     __device__ static void decode(const View& v, int64_t block, int unit, float (&out)[RUNS][16], int (&pos)[RUNS]) {
         Raw r;

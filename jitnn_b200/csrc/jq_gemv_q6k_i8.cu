@@ -19,6 +19,7 @@
 
 #include "jq_formats.cuh"
 #include "jq_q6k_image.cuh"
+#include "jq_tc.cuh"
 
 namespace jq {
 
@@ -30,8 +31,9 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int ROW_BYTES = 208;                       // one super-block of one row in the quant plane
-constexpr int SLOT_D = 16 * ROW_BYTES;               // behind the 16 rows: one 4-byte word per row holding its fp16 d
-constexpr int SLOT_BYTES = SLOT_D + 16 * 4;
+constexpr int SLOT_D = 16 * ROW_BYTES;               // behind the 16 rows: their 16 fp16 d
+constexpr int SLOT_BYTES = SLOT_D + 16 * 2;
+static_assert(SLOT_BYTES % 16 == 0 && SLOT_D % 16 == 0, "bulk copies move multiples of 16 bytes to 16-byte aligned addresses");
 constexpr size_t SMEM_MAX = 227 * 1024;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
@@ -97,6 +99,7 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
 // ---- activations -> image (scratch buffer in global memory) ---------------------------------------------------
 // One warp per (super-block of k, row of x).
 constexpr int PREP_WARPS = 4;
+__device__ int g_q6k_status;  // 0, or 25 once a wait for the weight ring has given up
 
 template <int MT>
 __global__ void __launch_bounds__(PREP_WARPS * 32) q6k_activation_image_kernel(const float* __restrict__ x, int rows, int64_t k,
@@ -114,7 +117,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) q6k_activation_image_kernel(c
 template <int MT, int STAGES, int OCC>
 __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const uint8_t* __restrict__ image, int rows,
                                                                   const float* __restrict__ bias, float* __restrict__ y, int tiles,
-                                                                  int KS, int max_tiles) {
+                                                                  int KS, int max_tiles, long long wait_clocks) {
     // KS = super-blocks of k per slice: the activation image of one slice is resident in shared memory at a time;
     // with more than one slice the per-tile sums are carried in shared memory (max_tiles tiles per CTA).
     using C = Cfg<MT>;
@@ -123,8 +126,10 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
     asm volatile("griddepcontrol.launch_dependents;");  // the kernel after this one may be scheduled as room becomes free
     const int KB = (int)(v.k >> 8);
     const int nslices = (KB + KS - 1) / KS;
-    uint8_t* img = smem_raw;                                                         // [KS][PB]
-    float* red = reinterpret_cast<float*>(smem_raw + (size_t)KS * C::PB);            // [2][WARPS][16][MT]
+    constexpr int BAR_BYTES = WARPS * STAGES * 8;                                    // one mbarrier per slot
+    static_assert(BAR_BYTES % 16 == 0, "what follows the barriers stays 16-byte aligned");
+    uint8_t* img = smem_raw + BAR_BYTES;                                             // [KS][PB]
+    float* red = reinterpret_cast<float*>(img + (size_t)KS * C::PB);                 // [2][WARPS][16][MT]
     float* carry = red + 2 * WARPS * 16 * MT;                                        // [max_tiles][16][MT], only if nslices > 1
     uint8_t* ring = reinterpret_cast<uint8_t*>(carry + (nslices > 1 ? (size_t)max_tiles * 16 * MT : 0)) +
                     (size_t)(threadIdx.x >> 5) * STAGES * SLOT_BYTES;
@@ -133,49 +138,43 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int64_t n = v.n;
-    const int64_t row_bytes = (int64_t)KB * ROW_BYTES;
+    const uint32_t bars_s = tc::smem_u32(smem_raw) + (uint32_t)(warp * STAGES * 8);  // this warp's barriers
 
-    // ---- weight stream: chunk c = lane + 32 i of the 208 chunks (16 rows x 13) of a super-block, rows at their natural
-    // pitch of 208 bytes; lanes 0-15 also copy the aligned 4-byte word that holds the fp16 d of row `lane`.
-    uint32_t src_off[7], dst_off[7];
+    // ---- weight stream: the planes hold their blocks tile by tile (jq_common.cuh), so the 16 rows of a tile of this kernel and
+    // one super-block are 16 x 208 contiguous bytes of the quant plane and 32 of the d plane: two bulk copies per step,
+    // requested by lane 0, complete when the slot's barrier says so. A slot holds the rows at their pitch of 208 bytes.
+    if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < 7; i++) {
-        const int c = lane + 32 * i, r = c / 13, ch = c % 13;
-        src_off[i] = (uint32_t)(r * (int)row_bytes + ch * 16);
-        dst_off[i] = (uint32_t)(r * ROW_BYTES + ch * 16);
+        for (int s = 0; s < STAGES; s++) {
+            tc::mbar_init(bars_s + 8 * s, 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");  // the copy engine sees initialised barriers
     }
+    __syncwarp();
     // This warp's steps, in order: for every slice, for every tile of the CTA, the super-blocks b = slice start + warp + 8 i.
     const int len_last = KB - (nslices - 1) * KS;
     const int nb_full = nslices > 1 ? (warp < KS ? (KS - warp + WARPS - 1) / WARPS : 0) : 0;
     const int nb_last = warp < len_last ? (len_last - warp + WARPS - 1) / WARPS : 0;
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int low16 = lane < 16;
     int iss_left = ((nslices - 1) * nb_full + nb_last) * my_tiles;
     int iss_sl = 0, iss_ti = 0, iss_j = 0, iss_nb = nslices > 1 ? nb_full : nb_last;
-    uint32_t iss_slot = 0;
+    int iss_slot = 0;
     constexpr uint32_t RING_BYTES = STAGES * SLOT_BYTES;
-    // quant bytes of the lane's first chunk and the aligned word with the fp16 d of row `lane`, for the block that is requested next
-    auto q_ptr = [&]() {
+    // position, among the blocks of a plane, of row 0 of the tile and the block that is requested next
+    auto step_index = [&]() {
         const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
-        return v.q + (int64_t)tile * 16 * row_bytes + (uint32_t)(iss_sl * KS + warp + WARPS * iss_j) * (uint32_t)ROW_BYTES;
+        return ((int64_t)(tile >> 3) * KB + (iss_sl * KS + warp + WARPS * iss_j)) * TILE_ROWS + (tile & 7) * 16;
     };
-    auto d_ptr = [&]() {
-        const int tile = (int)blockIdx.x + iss_ti * (int)gridDim.x;
-        const int64_t didx = ((int64_t)tile * 16 + (lane & 15)) * KB + (iss_sl * KS + warp + WARPS * iss_j);  // fp16 index of this row's d
-        return v.aux + ((didx * 2) & ~(int64_t)3);
-    };
-    const uint8_t* gq = q_ptr();
-    const uint8_t* gd = d_ptr();
-    auto issue = [&]() {
+    auto issue = [&]() {  // every lane keeps the bookkeeping, lane 0 makes the requests
         if (iss_left > 0) {
             iss_left--;
-            const uint32_t slot = ring_s + iss_slot;
-#pragma unroll
-            for (int i = 0; i < 6; i++) {
-                cp_async16(slot + dst_off[i], gq + src_off[i]);
+            if (lane == 0) {
+                const int64_t at = step_index();
+                const uint32_t bar = bars_s + 8 * iss_slot, slot = ring_s + iss_slot * SLOT_BYTES;
+                tc::mbar_expect_tx(bar, SLOT_BYTES);
+                tc::bulk_load(slot, v.q + at * ROW_BYTES, SLOT_D, bar);
+                tc::bulk_load(slot + SLOT_D, v.aux + at * 2, 32, bar);
             }
-            cp_async16_if(slot + dst_off[6], gq + src_off[6], low16);
-            cp_async4_if(slot + SLOT_D + 4u * (uint32_t)(lane & 15), gd, low16);
             if (++iss_j == iss_nb) {
                 iss_j = 0;
                 if (++iss_ti == my_tiles) {
@@ -183,15 +182,9 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
                     iss_sl++;
                     iss_nb = iss_sl == nslices - 1 ? nb_last : nb_full;
                 }
-                gq = q_ptr();
-                gd = d_ptr();
-            } else {
-                gq += WARPS * ROW_BYTES;
-                gd = d_ptr();  // the d words of consecutive blocks are 2 bytes apart: recomputed because of the 4-byte alignment
             }
         }
-        iss_slot = iss_slot + SLOT_BYTES == RING_BYTES ? 0u : iss_slot + SLOT_BYTES;
-        cp_async_commit();
+        iss_slot = iss_slot + 1 == STAGES ? 0 : iss_slot + 1;
     };
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
@@ -282,10 +275,9 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
                 }
             }
         }
-        // fp16 d of rows g and g + 8: the half of the copied word that the row's index selects
-        const int64_t d0i = ((int64_t)tile * 16 + g) * KB + blk, d1i = d0i + (int64_t)8 * KB;
-        const uint32_t w0 = *reinterpret_cast<const uint32_t*>(slot + SLOT_D + 4 * g), w1 = *reinterpret_cast<const uint32_t*>(slot + SLOT_D + 4 * (g + 8));
-        const float d0 = half_bits_to_float(w0 >> (16 * (int)(d0i & 1))), d1 = half_bits_to_float(w1 >> (16 * (int)(d1i & 1)));
+        // fp16 d of rows g and g + 8
+        const float d0 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(slot + SLOT_D + 2 * g));
+        const float d1 = half_bits_to_float(*reinterpret_cast<const uint16_t*>(slot + SLOT_D + 2 * (g + 8)));
         const uint8_t* tb = tab_lane + (size_t)b * C::PB;
 #pragma unroll
         for (int i = 0; i < NG; i++) {
@@ -309,7 +301,9 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
     }
 
     int parity = 0;
-    uint32_t cmp_slot = 0;
+    int cmp_slot = 0;
+    uint32_t cmp_phase = 0;
+    bool gave_up = false;  // a wait for weights ran out: the status word says so, the warp stops waiting and finishes with whatever is there
     for (int sl = 0; sl < nslices; sl++) {
         // ---- bring this slice of the activation image into shared memory ---------------------------------------------
         const int len = (KB - sl * KS) < KS ? (KB - sl * KS) : KS;
@@ -341,12 +335,27 @@ __global__ void __launch_bounds__(THREADS, OCC) gemv_q6k_i8_kernel(View v, const
         for (int ti = 0; ti < my_tiles; ti++) {
             const int my_tile = (int)blockIdx.x + ti * (int)gridDim.x;
             for (int b = warp; b < len; b += WARPS) {
-                __syncwarp();                 // every lane is done reading the slot that is requested next
+                __syncwarp();  // every lane is done reading the slot that is requested next
                 issue();
-                cp_async_wait<STAGES - 1>();  // this lane's copies of this step have landed
-                __syncwarp();                 // ... and so have the other lanes'
-                compute(ring + cmp_slot, ring_s + cmp_slot, b, my_tile, sl * KS + b);
-                cmp_slot = cmp_slot + SLOT_BYTES == RING_BYTES ? 0u : cmp_slot + SLOT_BYTES;
+                if (!gave_up) {
+                    // the copies of this step have landed (bounded: the clock, not the number of polls)
+                    const uint32_t bar = bars_s + 8 * cmp_slot;
+                    if (!tc::mbar_try(bar, cmp_phase)) {
+                        const long long t0 = clock64();
+                        while (!tc::mbar_try(bar, cmp_phase)) {
+                            if (clock64() - t0 > wait_clocks) {
+                                atomicCAS(&g_q6k_status, 0, 25);
+                                gave_up = true;
+                                break;
+                            }
+                        }
+                    }
+                }
+                compute(ring + cmp_slot * SLOT_BYTES, ring_s + cmp_slot * SLOT_BYTES, b, my_tile, sl * KS + b);
+                if (++cmp_slot == STAGES) {
+                    cmp_slot = 0;
+                    cmp_phase ^= 1u;
+                }
             }
             // ---- this warp's partial sums per activation row: combine the digit columns, then the 4 lanes of a row ------
             float* rd = red + (size_t)parity * WARPS * 16 * MT;
@@ -431,7 +440,8 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q6k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles));
+    const long long wait_clocks = (long long)g_opt_wait_limit_us.load(std::memory_order_relaxed) * 2000;  // about 2 GHz
+    JQ_CUDA(cudaLaunchKernelEx(&cfg, gemv_q6k_i8_kernel<MT, STAGES, OCC>, v, image, rows, bias, y, tiles, KS, max_tiles, wait_clocks));
     count_launch();
     return JQ_OK;
 }
@@ -439,7 +449,7 @@ int launch(const View& v, const uint8_t* image, int rows, const float* bias, flo
 // Shared memory of one CTA: image slice, cross-warp reduction, carried sums, weight ring.
 template <int MT>
 size_t smem_bytes(int KS, int stages, bool sliced, int max_tiles) {
-    return (size_t)KS * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
+    return (size_t)WARPS * stages * 8 + (size_t)KS * Cfg<MT>::PB + (size_t)(2 * WARPS * 16 * MT) * sizeof(float) + (sliced ? (size_t)max_tiles * 16 * MT * sizeof(float) : 0) +
            (size_t)WARPS * stages * SLOT_BYTES;
 }
 
@@ -455,7 +465,7 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
     int pick = -1, KS = KB;
     for (int c = 0; c < 3 && pick < 0; c++) {
         const size_t budget = SMEM_MAX / occ_of[c] - 1024;
-        if ((size_t)KB * Cfg<MT>::PB + red_bytes + (size_t)WARPS * st_of[c] * SLOT_BYTES <= budget) {
+        if ((size_t)KB * Cfg<MT>::PB + red_bytes + (size_t)WARPS * st_of[c] * (SLOT_BYTES + 8) <= budget) {
             pick = c;
         }
     }
@@ -464,7 +474,7 @@ int run(const View& v, const float* x, int rows, const float* bias, float* y, cu
         // slices: two CTAs per SM, three ring stages, or two if a slice of 8 super-blocks needs the room
         pick = 2;
         for (stages = 3; stages >= 2; stages--) {
-            const size_t budget = SMEM_MAX / 2 - 1024 - fixed - (size_t)WARPS * stages * SLOT_BYTES;
+            const size_t budget = SMEM_MAX / 2 - 1024 - fixed - (size_t)WARPS * stages * (SLOT_BYTES + 8);
             KS = (int)(budget / Cfg<MT>::PB) / 8 * 8;
             if (KS >= 8) {
                 break;
@@ -527,6 +537,14 @@ int launch_gemv_q6k_i8(const View& v, const float* x, int rows, const float* bia
     if (rows == 1) return run<1>(v, x, rows, bias, y, s, image, handled);
     if (rows == 2) return run<2>(v, x, rows, bias, y, s, image, handled);
     return run<4>(v, x, rows, bias, y, s, image, handled);
+}
+
+// Reads and clears the status of the weight-ring waits on the current device.
+int gemv_q6k_status(int* status) {
+    const int zero = 0;
+    JQ_CUDA(cudaMemcpyFromSymbol(status, g_q6k_status, sizeof(int)));
+    JQ_CUDA(cudaMemcpyToSymbol(g_q6k_status, &zero, sizeof(int)));
+    return JQ_OK;
 }
 
 size_t q6k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::PB; }

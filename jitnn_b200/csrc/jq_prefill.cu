@@ -39,7 +39,6 @@ __host__ __device__ constexpr int stages_of(int tile_t, int nf) { return nf == 2
 constexpr int A_BYTES = TILE_F * STAGE_K * 2;
 constexpr int DQ_THREADS = 256;  // two dequantiser threads per output feature, 32 weights each per stage
 constexpr int THREADS = 64 + DQ_THREADS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: dequantise, then epilogue
-constexpr uint32_t POLL_LIMIT = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -62,14 +61,25 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Waits for the phase with the given parity; gives up after POLL_LIMIT polls or when another role aborted.
+// Waits for the phase with the given parity; gives up after WAIT_CLOCKS of the SM's clock (a poll may suspend the thread for
+// a time the hardware chooses, so the bound counts time, not polls) or when another role aborted.
+constexpr long long WAIT_CLOCKS = 4000000000ll;  // about two seconds
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-    for (uint32_t i = 0; i < POLL_LIMIT; i++) {
+    if (mbar_try(bar, parity)) {
+        return true;
+    }
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; i++) {
         if (mbar_try(bar, parity)) {
             return true;
         }
-        if ((i & 1023u) == 1023u && *abort_flag != 0) {
-            return false;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag != 0) {
+                return false;
+            }
+            if (clock64() - t0 > WAIT_CLOCKS) {
+                break;
+            }
         }
     }
     atomicCAS(&g_prefill_status, 0, code);

@@ -26,7 +26,7 @@ static Split split_of(int type) {
 
 // One thread per 2 bytes of a block (every block size and field offset here is even).
 __global__ void repack_kernel(Split sp, const uint16_t* __restrict__ src, uint16_t* __restrict__ q, uint16_t* __restrict__ aux,
-                              int64_t blocks, bool inverse) {
+                              int64_t blocks, int64_t kb, bool tiled, bool inverse) {
     int64_t halves_per_block = sp.block / 2;
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= blocks * halves_per_block) {
@@ -34,6 +34,9 @@ __global__ void repack_kernel(Split sp, const uint16_t* __restrict__ src, uint16
     }
     int64_t b = i / halves_per_block;
     int off = (int)(i % halves_per_block) * 2;
+    if (tiled) {
+        b = tiled_index(b / kb, b % kb, kb);  // where the block sits in the planes
+    }
     uint16_t* verbatim = const_cast<uint16_t*>(src) + i;
     uint16_t* plane;
     if (off >= sp.aux_off && off < sp.aux_off + sp.aux_bytes) {
@@ -48,7 +51,7 @@ __global__ void repack_kernel(Split sp, const uint16_t* __restrict__ src, uint16
     }
 }
 
-int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, cudaStream_t s) {
+int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, int64_t blocks, int64_t kb, cudaStream_t s) {
     Split sp = split_of(type);
     if (sp.block == 0) {
         return fail(JQ_ERR_INVALID, "repack: type %d has no plane layout", type);
@@ -57,12 +60,12 @@ int launch_repack(int type, const uint8_t* verbatim, uint8_t* q, uint8_t* aux, i
     if (total == 0) {
         return JQ_OK;
     }
-    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sp, (const uint16_t*)verbatim, (uint16_t*)q, (uint16_t*)aux, blocks, false);
+    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sp, (const uint16_t*)verbatim, (uint16_t*)q, (uint16_t*)aux, blocks, kb, tiled_planes(type), false);
     count_launch();
     return check_launch("repack_kernel");
 }
 
-int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, cudaStream_t s) {
+int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verbatim, int64_t blocks, int64_t kb, cudaStream_t s) {
     Split sp = split_of(type);
     if (sp.block == 0) {
         return fail(JQ_ERR_INVALID, "unpack: type %d has no plane layout", type);
@@ -71,7 +74,7 @@ int launch_unpack(int type, const uint8_t* q, const uint8_t* aux, uint8_t* verba
     if (total == 0) {
         return JQ_OK;
     }
-    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sp, (const uint16_t*)verbatim, (uint16_t*)q, (uint16_t*)aux, blocks, true);
+    repack_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(sp, (const uint16_t*)verbatim, (uint16_t*)q, (uint16_t*)aux, blocks, kb, tiled_planes(type), true);
     count_launch();
     return check_launch("repack_kernel");
 }
