@@ -271,8 +271,10 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int f0 = blockIdx.x * (NF * TILE_F), t0 = blockIdx.y * TILE_T;
     const int KT_all = (int)(v.k / STAGE_K);
-    const int it0 = SPLIT ? (int)blockIdx.z * (KT_all / 2) : 0;                        // first 64-wide stage of k of this CTA
-    const int KT = SPLIT ? (blockIdx.z == 0 ? KT_all / 2 : KT_all - KT_all / 2) : KT_all;  // and their number
+    // SPLIT: k is cut into gridDim.z ranges, CTA z takes stages [z KT_all / S, (z + 1) KT_all / S) and leaves its partial
+    // sums in part z of the buffer at y ([S][m][n]); split_sum_kernel adds the parts in order afterwards.
+    const int it0 = SPLIT ? (int)(((int64_t)blockIdx.z * KT_all) / (int)gridDim.z) : 0;  // first 64-wide stage of k of this CTA
+    const int KT = SPLIT ? (int)(((int64_t)(blockIdx.z + 1) * KT_all) / (int)gridDim.z) - it0 : KT_all;  // and their number
     const uint32_t bar0 = smem_u32(bars);
     auto full_a = [&](int s) { return bar0 + 8u * (uint32_t)s; };
     auto full_b = [&](int s) { return bar0 + 8u * (uint32_t)(STAGES + s); };
@@ -391,7 +393,8 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
             const int lane_group = warp & 3;  // a warp may only read TMEM lanes 32 (warp % 4) .. + 31
             const int col_half = ((warp - 2) >> 2) & 1;  // the two warps of a lane group and feature tile split the token columns
             const int feature = f0 + sub * TILE_F + lane_group * 32 + lane;
-            const float b = (bias != nullptr && feature < v.n && (!SPLIT || blockIdx.z == 0)) ? bias[feature] : 0.0f;
+            const float b = (bias != nullptr && feature < v.n && !SPLIT) ? bias[feature] : 0.0f;
+            float* const out = SPLIT ? y + (int64_t)blockIdx.z * m * v.n : y;
 #pragma unroll 1
             for (int c = col_half * (TILE_T / 64); c < (col_half + 1) * (TILE_T / 64); c++) {
                 uint32_t r[32];
@@ -410,12 +413,7 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
                     for (int j = 0; j < 32; j++) {
                         const int token = t0 + c * 32 + j;
                         if (token < m) {
-                            float* dst = y + (int64_t)token * v.n + feature;
-                            if constexpr (SPLIT) {
-                                atomicAdd(dst, __uint_as_float(r[j]) + b);  // two parts: the sum does not depend on who comes first
-                            } else {
-                                *dst = __uint_as_float(r[j]) + b;
-                            }
+                            out[(int64_t)token * v.n + feature] = __uint_as_float(r[j]) + b;
                         }
                     }
                 }
@@ -442,6 +440,35 @@ __global__ void __launch_bounds__(64 + NF * DQ_THREADS, (TILE_T == 128 && NF == 
     }
 }
 
+// y = parts[0] + parts[1] + ... (in that order) + bias: the second stage of a linear whose k was cut into ranges.
+// Four elements per thread where the row length allows 16-byte accesses.
+template <bool VEC>
+__global__ void split_sum_kernel(const float* __restrict__ parts, int nparts, int64_t count, int64_t n, const float* __restrict__ bias,
+                                 float* __restrict__ y) {
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * (VEC ? 4 : 1);
+    if (i >= count) {
+        return;
+    }
+    if constexpr (VEC) {
+        float4 sum = *reinterpret_cast<const float4*>(parts + i);
+        for (int p = 1; p < nparts; p++) {
+            const float4 a = *reinterpret_cast<const float4*>(parts + (int64_t)p * count + i);
+            sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+        }
+        if (bias != nullptr) {
+            const float4 b = *reinterpret_cast<const float4*>(bias + i % n);
+            sum.x += b.x; sum.y += b.y; sum.z += b.z; sum.w += b.w;
+        }
+        *reinterpret_cast<float4*>(y + i) = sum;
+    } else {
+        float sum = parts[i];
+        for (int p = 1; p < nparts; p++) {
+            sum += parts[(int64_t)p * count + i];
+        }
+        y[i] = bias != nullptr ? sum + bias[i % n] : sum;
+    }
+}
+
 // fp32 -> bf16 (round to nearest even, as the reference's LowPrecision.java:36-46), for jq_linear_f32's prefill option
 __global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t count) {
     int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -457,7 +484,7 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* _
 }
 
 template <int TYPE, int TILE_T, int NF, bool SPLIT>
-int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s) {
+int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bias, float* y, cudaStream_t s, int ksplit) {
     constexpr int B_BYTES = TILE_T * STAGE_K * 2;
     constexpr int STAGES = stages_of(TILE_T, NF);
     const size_t smem = (size_t)STAGES * (NF * A_BYTES + B_BYTES) + 256 + 1024;  // tiles + barriers + slack for the 1024-byte alignment
@@ -468,13 +495,30 @@ int launch_typed(const View& v, const CUtensorMap& xmap, int m, const float* bia
         JQ_CUDA(cudaFuncSetAttribute(prefill_tcgen05_kernel<TYPE, TILE_T, NF, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
+    float* out = y;
     if (SPLIT) {
-        JQ_CUDA(cudaMemsetAsync(y, 0, (size_t)m * v.n * sizeof(float), s));
+        uint8_t* parts = nullptr;
+        int rc = scratch_for_slot(s, 3, (size_t)ksplit * m * v.n * sizeof(float), &parts);
+        if (rc != JQ_OK) {
+            return rc;
+        }
+        out = reinterpret_cast<float*>(parts);
     }
-    dim3 grid((unsigned)((v.n + NF * TILE_F - 1) / (NF * TILE_F)), (unsigned)((m + TILE_T - 1) / TILE_T), SPLIT ? 2u : 1u);
-    prefill_tcgen05_kernel<TYPE, TILE_T, NF, SPLIT><<<grid, 64 + NF * DQ_THREADS, smem, s>>>(v, xmap, m, bias, y);
+    dim3 grid((unsigned)((v.n + NF * TILE_F - 1) / (NF * TILE_F)), (unsigned)((m + TILE_T - 1) / TILE_T), SPLIT ? (unsigned)ksplit : 1u);
+    prefill_tcgen05_kernel<TYPE, TILE_T, NF, SPLIT><<<grid, 64 + NF * DQ_THREADS, smem, s>>>(v, xmap, m, bias, out);
     count_launch();
-    return check_launch("prefill_tcgen05_kernel");
+    int rc = check_launch("prefill_tcgen05_kernel");
+    if (rc == JQ_OK && SPLIT) {
+        const int64_t count = (int64_t)m * v.n;
+        if (v.n % 4 == 0 && (((uintptr_t)y | (uintptr_t)bias) & 15) == 0) {
+            split_sum_kernel<true><<<(unsigned)((count / 4 + 255) / 256), 256, 0, s>>>(out, ksplit, count, v.n, bias, y);
+        } else {
+            split_sum_kernel<false><<<(unsigned)((count + 255) / 256), 256, 0, s>>>(out, ksplit, count, v.n, bias, y);
+        }
+        count_launch();
+        rc = check_launch("split_sum_kernel");
+    }
+    return rc;
 }
 
 }  // namespace
@@ -522,12 +566,20 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
                 continue;
             }
             const int64_t ctas = ((v.n + 128 * nfs[c] - 1) / (128 * nfs[c])) * ((m + ts[c] - 1) / ts[c]);
-            // A one-feature-tile shape can also take k in two halves (two CTAs per tile adding into a zeroed y; two partial
-            // sums add up the same in either order): that fills SMs which few feature tiles leave idle. A half-k CTA costs a
-            // little more than half, and y has to be zeroed first.
+            // Any shape can also take k in 2 to 4 ranges: the CTAs of a tile leave partial sums in a scratch buffer and a
+            // second small kernel adds them in order (the same result whoever finishes first). That fills SMs which few
+            // tiles leave idle and evens out the last wave. A part-k CTA costs a little more than its share, and the
+            // second kernel reads every part once (from L2, mostly).
             const double kf = (double)v.k / 4096.0;
-            for (int ks = 1; ks <= (nfs[c] == 1 && v.k / STAGE_K >= 32 ? 2 : 1); ks++) {
-                const double cost = (double)((ctas * ks + 147) / 148) * wave_us[c] * kf * (ks == 2 ? 0.55 : 1.0) + (ks == 2 ? 8.0 : 0.0);
+            const int max_split = v.k / STAGE_K >= 32 ? 4 : 1;
+            for (int ks = 1; ks <= max_split; ks++) {
+                const double part_bytes = (double)ks * m * v.n * 4.0;
+                if (ks > 1 && part_bytes > 192e6) {
+                    break;  // the parts stay in a scratch buffer for good: not for very long prompts
+                }
+                // (measured: with a smaller fixed cost the model cuts 11008 x 4096 in three and loses 20 microseconds)
+                const double cost = (double)((ctas * ks + 147) / 148) * wave_us[c] * kf / ks * (ks > 1 ? 1.1 : 1.0) +
+                                    (ks > 1 ? 8.0 + part_bytes / 5e6 : 0.0);  // microseconds
                 if ((c == 0 && ks == 1) || cost < best) {
                     best = cost;
                     tile_t = ts[c];
@@ -546,9 +598,12 @@ int launch_prefill_bf16(const View& v, const uint16_t* x_bf16, int64_t m, const 
     }
 #define JQ_PREFILL_CASE(T)                                                                         \
     case T:                                                                                          \
-        if (ksplit == 2) return tile_t == 256 ? launch_typed<T, 256, 1, true>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1, true>(v, xmap, (int)m, bias, y, s); \
-        return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2, false>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 2, false>(v, xmap, (int)m, bias, y, s)) \
-                       : (tile_t == 256 ? launch_typed<T, 256, 1, false>(v, xmap, (int)m, bias, y, s) : launch_typed<T, 128, 1, false>(v, xmap, (int)m, bias, y, s));
+        if (ksplit > 1) {                                                                            \
+            return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2, true>(v, xmap, (int)m, bias, y, s, ksplit) : launch_typed<T, 128, 2, true>(v, xmap, (int)m, bias, y, s, ksplit)) \
+                           : (tile_t == 256 ? launch_typed<T, 256, 1, true>(v, xmap, (int)m, bias, y, s, ksplit) : launch_typed<T, 128, 1, true>(v, xmap, (int)m, bias, y, s, ksplit)); \
+        }                                                                                            \
+        return nf == 2 ? (tile_t == 256 ? launch_typed<T, 256, 2, false>(v, xmap, (int)m, bias, y, s, 1) : launch_typed<T, 128, 2, false>(v, xmap, (int)m, bias, y, s, 1)) \
+                       : (tile_t == 256 ? launch_typed<T, 256, 1, false>(v, xmap, (int)m, bias, y, s, 1) : launch_typed<T, 128, 1, false>(v, xmap, (int)m, bias, y, s, 1));
     switch (v.type) {
         JQ_PREFILL_CASE(JQ_TYPE_Q8_0)
         JQ_PREFILL_CASE(JQ_TYPE_Q4_0)
