@@ -216,9 +216,10 @@ JQ_API int jq_quantize_q8_0(int device, const float* x, int64_t count, void* blo
  *   "decoder_graph"     zero: the decoder issues its single-token step kernel by kernel instead of replaying a CUDA graph.
  *   "decoder_fused"     zero: the decoder's single-token step uses the general kernels (one per operator) instead of the
  *                       fused ones that hand activations to the next linear as its activation image.
- *   "gemv_tcgen05"      non-zero: Q4_K and Q5_K decode GEMVs (1 to 16 rows in one pass over the weights) run on the tcgen05
- *                       kernel instead of the mma.sync one (which takes up to 8 rows per pass and is the faster of the two
- *                       on every measured shape, hence the default).
+ *   "gemv_tcgen05"      which Q4_K and Q5_K decode GEMVs run on the tcgen05 kernel (1 to 16 rows of x in one pass over the weights)
+ *                       instead of the mma.sync one (up to 8 rows per pass). 0 (default): those where it is the faster of the
+ *                       two, 11 or more rows of x on a weight of at least one 128-row tile per SM, and the shapes the mma.sync
+ *                       kernel declines; 1: all; 2: none.
  *   "wait_limit_us"     microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up (default 2 000 000; a
  *                       wait that gives up makes jq_device_status report 64 + the waiting role, and the outputs of that call
  *                       are undefined).

@@ -206,21 +206,21 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
         }
         return rc;
     }
-    // The integer tensor-core kernel of Q4_K and Q5_K takes up to 8 activation rows per pass (the tcgen05 one, if selected, 16),
+    // The integer tensor-core kernel of Q4_K and Q5_K takes up to 8 activation rows per pass (the tcgen05 one, where it is chosen, 16),
     // Q6_K's 4, the generic kernel 16.
     const bool tc = g_opt_gemv_generic.load() == 0;
     // Q8_0, Q4_0 and Q4_1 (k a multiple of 256) go two rows at a time through their tensor-core kernel: re-reading the weights
     // (mostly from L2) per pair of rows is far cheaper than the generic kernel's arithmetic.
     const bool blk32 = tc && gemv_blk32_i8_scratch_bytes(w->type, w->k, 2) > 0;
-    const int64_t group = gemv_umma_takes(w->type, w->k, 16)
-                              ? 16
-                              : ((tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16)));
-    for (int64_t m0 = 0; m0 < m; m0 += group) {
-        int rows = (int)(m - m0 < group ? m - m0 : group);
+    const int64_t group = (tc && (w->type == JQ_TYPE_Q4_K || w->type == JQ_TYPE_Q5_K)) ? 8 : ((tc && w->type == JQ_TYPE_Q6_K) ? 4 : (blk32 ? 2 : 16));
+    for (int64_t m0 = 0; m0 < m;) {
+        const int left = (int)(m - m0 < 16 ? m - m0 : 16);
+        const int rows = gemv_umma_takes(w->type, w->k, left, w->n) ? left : (int)(left < group ? left : group);
         int rc = launch_gemv(v, x + m0 * w->k, rows, bias, y + m0 * w->n, s, x_remote);
         if (rc != JQ_OK) {
             return rc;
         }
+        m0 += rows;
     }
     return JQ_OK;
 }
@@ -731,7 +731,10 @@ int jq_set_option(const char* name, int64_t value) {
         return JQ_OK;
     }
     if (name != nullptr && strcmp(name, "gemv_tcgen05") == 0) {
-        g_opt_gemv_umma.store(value != 0);
+        if (value < 0 || value > 2) {
+            return fail(JQ_ERR_INVALID, "option gemv_tcgen05: %lld is not 0 (where faster), 1 (always) or 2 (never)", (long long)value);
+        }
+        g_opt_gemv_umma.store(value);
         return JQ_OK;
     }
     if (name != nullptr && strcmp(name, "wait_limit_us") == 0) {

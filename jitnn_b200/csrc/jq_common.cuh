@@ -179,14 +179,16 @@ int scratch_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out);
 int scratch_zeroed_for_slot(cudaStream_t s, int slot, size_t bytes, uint8_t** out);
 
 // Decode GEMV on tcgen05 (jq_gemv_umma.cu): Q4_K and Q5_K, 1 to 16 rows of x in one pass over the weights.
-bool gemv_umma_takes(int type, int64_t k, int rows);
+bool gemv_umma_takes(int type, int64_t k, int rows, int64_t n = 0);
+bool gemv_umma_fallback(int type, int64_t k, int rows);  // may stand in for the mma.sync kernel on a shape that one declines
 size_t gemv_umma_image_bytes(int64_t k, int rows);
 inline size_t gemv_umma_image_bytes_one_row(int64_t k) { return gemv_umma_image_bytes(k, 1); }
 int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s);
 int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
                      const PeerOut* peer = nullptr, bool no_scratch = false);
 int gemv_umma_status(int* status);
-// Option "gemv_tcgen05": non-zero sends Q4_K and Q5_K decode (1 to 16 rows) to the tcgen05 kernel instead of the mma.sync one.
+// Option "gemv_tcgen05": 1 sends Q4_K and Q5_K decode (1 to 16 rows) to the tcgen05 kernel instead of the mma.sync one, 2 never,
+// 0 where it is faster (many rows of x, many rows of the weight).
 extern std::atomic<int64_t> g_opt_gemv_umma;
 // Option "wait_limit_us": microseconds after which a bounded device-side wait of the tcgen05 GEMV gives up.
 extern std::atomic<int64_t> g_opt_wait_limit_us;

@@ -92,7 +92,7 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
     if (v.n == 0) {
         return JQ_OK;
     }
-    if (gemv_umma_takes(v.type, v.k, rows)) {
+    if (gemv_umma_takes(v.type, v.k, rows, v.n)) {
         // Q4_K, Q5_K: the tcgen05 kernel, one pass over the weights for up to 16 rows
         uint8_t* image = nullptr;
         int rc = scratch_for(s, gemv_umma_image_bytes(v.k, rows), &image);
@@ -108,6 +108,12 @@ int launch_gemv(const View& v, const float* x, int rows, const float* bias, floa
         }
         if (rc != JQ_OK || handled) {
             return rc;
+        }
+        if (gemv_umma_fallback(v.type, v.k, rows)) {
+            // a shape that kernel declines (a large k whose image does not fit beside the sums of many tiles per CTA):
+            // the tcgen05 kernel streams the image and is many times faster than the CUDA-core kernel below
+            rc = scratch_for(s, gemv_umma_image_bytes(v.k, rows), &image);
+            return rc == JQ_OK ? launch_gemv_umma(v, nullptr, x, image, rows, bias, y, nullptr, s) : rc;
         }
     }
     if (v.type == JQ_TYPE_Q6_K && rows <= 4 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0) {

@@ -2,28 +2,29 @@
 // Q5_K, one pass over the weights for every m.
 //
 // Replaces the reference's matrix-vector kernels (kernels/jitllm/TransformerComputeKernelsQ4_K.java:130-215,
-// ...Q5_K.java:422-532, dispatch ops/Gguf.java:170-183). The quants never become floating point:
-//   * the activations are turned into an "image" of signed byte digits (jq_umma_image.cuh: 22-bit fixed point per
-//     super-block of k, three base-256 digits per value, one MMA column per (row of x, digit));
+// ...Q5_K.java:422-532, dispatch ops/Gguf.java:170-183).
+//   * the activations are turned into an "image" of half-precision digits (jq_umma_image.cuh: 22-bit fixed point per
+//     super-block of k, two signed 11-bit digits per value, one MMA column per (row of x, digit));
 //   * a persistent CTA per SM walks units of 128 weight rows x one 256-element super-block of k. Per unit
 //       - one thread asks the copy engine for the unit's weights (one cp.async.bulk of 128 x 144 contiguous bytes: the
 //         weight is stored tile by tile for exactly this, jq_common.cuh) and for the super-block's image (another
 //         cp.async.bulk), both into shared-memory rings that complete on mbarriers;
-//       - 128 "unpack" threads, one per weight row, widen the row's nibbles to bytes with one AND per four weights and
-//         store them into tensor memory as the A operand (tcgen05.st); the row's 6-bit scales and mins are decoded
-//         once into a small shared-memory ring;
-//       - one thread issues eight tcgen05.mma.cta_group::1.kind::i8 (M = 128 rows, N = 8..48 digit columns, K = 32:
-//         one sub-block each, A from tensor memory, B = the image in shared memory), each into its own accumulator
-//         columns, because every sub-block has its own scale;
-//       - 128 "epilogue" threads, one per weight row, read the accumulators (tcgen05.ld), fold the 6-bit scales in
-//         with integer multiply-adds (the sum over the eight sub-blocks stays below 2^31), convert once per
-//         super-block and digit, and apply fp16 d, dmin and the mins (through the sub-blocks' sums of x).
+//       - 128 "unpack" threads, one per weight row, turn the row's quants into quant x 6-bit scale (an integer below
+//         2048, exact in half precision: one byte permute per two quants and one fused multiply-add per pair) and store
+//         them into tensor memory as the A operand (tcgen05.st); the row's mins, d and dmin go into a small
+//         shared-memory ring;
+//       - one thread issues sixteen tcgen05.mma.cta_group::1.kind::f16 (M = 128 rows, N = 8..32 digit columns, K = 16,
+//         A from tensor memory, B = the image in shared memory) that accumulate the whole super-block into one FP32
+//         accumulator: the scales are already in the operand;
+//       - 128 "epilogue" threads, one per weight row, read the accumulators (tcgen05.ld), weigh the two digits, and
+//         apply fp16 d, dmin and the mins (through the sub-blocks' sums of x).
 //   * a row's result is the sum of its super-blocks' contributions in k order, each contribution rounded to FP32
 //     first. Units are dealt to the CTAs in contiguous runs, so a run can start or end inside a tile; such
 //     pieces are written to a scratch buffer (the first piece as a running sum, later pieces contribution by
 //     contribution) and the CTA that finishes a tile's last piece adds them in k order. The result therefore does not
 //     depend on how many CTAs or rows there are: a row shard of a weight gives bitwise the outputs of the whole weight.
-// Everything up to the float conversion is exact; x keeps 22 bits relative to the largest magnitude of its super-block.
+// The products are exact; a super-block's 256 of them per digit are summed in FP32 by the tensor core. x keeps 22 bits
+// relative to the largest magnitude of its super-block.
 //
 // Every wait (mbarrier phases) is bounded: a wait that runs out records 64 + its role in a status word, raises the
 // CTA's abort flag, all roles fall through to the common exit and tensor memory is released. No CTA waits for another.
@@ -74,10 +75,11 @@ namespace {
 
 constexpr int ROWS = 128;        // weight rows per unit (MMA M)
 constexpr int SP = 4;            // stages of the row-parameter ring
-constexpr int P_BYTES = 2 * ROWS * 16;
+constexpr int P_BYTES = ROWS * 16;
 constexpr int MAX_SX = 8;        // stages of the image ring: enough of them in flight to cover the latency of a copy from L2
 constexpr int MAX_SW = 12;       // stages of the weight ring (as many as fit)
 constexpr size_t SMEM_MAX = 227 * 1024;
+constexpr int UMMA_AUTO_MIN_ROWS = 11;  // rows of x from which the kernel is chosen without being asked for
 constexpr size_t RESIDENT_MAX = 96 * 1024;  // largest activation image that stays in shared memory for the whole kernel
 
 template <int TYPE>
@@ -86,7 +88,7 @@ template <>
 struct UFmt<JQ_TYPE_Q4_K> {
     static constexpr int BYTES = 144;
     static constexpr int QS = 16;             // offset of the nibbles
-    static constexpr bool IN_PLACE = true;    // high nibbles stay where they are (16 q): the even sub-blocks' scales carry a factor 16 instead
+    static constexpr bool IN_PLACE = true;    // high nibbles stay where they are (16 q): the odd sub-blocks' scales are divided by 16 instead
 };
 template <>
 struct UFmt<JQ_TYPE_Q5_K> {
@@ -160,17 +162,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// D[128 x N] (tensor memory, s32) = A[128 x 32] (tensor memory, u8) . B[32 x N] (shared memory, s8)
-__device__ __forceinline__ void umma_i8_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+// D[128 x N] (tensor memory, f32) (+)= A[128 x 16] (tensor memory, f16) . B[16 x N] (shared memory, f16)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d), "r"(tmem_a),
-        "l"(bdesc), "r"(idesc), "r"(0u)
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d), "r"(tmem_a),
+        "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
-// Instruction descriptor of kind::i8: D = S32 (bits 4-5 = 2), A = unsigned 8 bit (bits 7-9 = 0), B = signed 8 bit (bits 10-12 = 1),
-// both K-major, N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-constexpr uint32_t idesc_of(int n_cols) { return (2u << 4) | (1u << 10) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24); }
+// Instruction descriptor of kind::f16: D = F32 (bits 4-5 = 1), A and B half precision (bits 7-9 and 10-12 = 0), both K-major,
+// N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t idesc_of(int n_cols) { return (1u << 4) | ((uint32_t)(n_cols >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24); }
 
 // Shared-memory descriptor of a K-major operand without swizzle: 8 rows x 16 bytes per core matrix, `lbo` bytes between the
 // core matrices of consecutive 16-byte steps of k, `sbo` bytes between those of consecutive groups of 8 rows; descriptor version 1.
@@ -202,13 +204,6 @@ __device__ __forceinline__ bool warp_wait_phases(const Phase& p0, const Phase& p
     int ok = 1;
     if (lane == 0) {
         ok = wait_phases(p0, p1, p2, use2, abort_flag, code, limit) ? 1 : 0;
-    }
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
-}
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit, int lane) {
-    int ok = 1;
-    if (lane == 0) {
-        ok = tc::mbar_wait(bar, parity, abort_flag, &g_umma_status, code, limit) ? 1 : 0;
     }
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
@@ -274,6 +269,9 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
 
 __device__ __forceinline__ void epilogue_barrier(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
+__device__ __forceinline__ __half2 u32_as_half2(uint32_t v) { return *reinterpret_cast<const __half2*>(&v); }
+__device__ __forceinline__ uint32_t half2_as_u32(__half2 v) { return *reinterpret_cast<const uint32_t*>(&v); }
+
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -291,9 +289,9 @@ __global__ void __launch_bounds__(128) umma_activation_image_kernel(const float*
     }
 }
 
-// MR = rows of x the kernel computes (1, 2, 5, 8, 10 or 16; a call with fewer rows leaves the others unused). From eight rows on
-// two sets of epilogue warps share the rows of x (the scale fold is 24 integer multiply-adds per weight row, super-block
-// and row of x). RES: the image of the whole k is built by this kernel into shared memory and stays there (small k x rows).
+// MR = rows of x the kernel computes (4, 8 or 16; a call with fewer rows leaves the others unused). From eight rows on two
+// sets of epilogue warps share the rows of x. RES: the image of the whole k is built by this kernel into shared memory and
+// stays there (small k x rows).
 template <int MR>
 struct Roles {
     static constexpr int ES = MR >= 8 ? 2 : 1;     // sets of four epilogue warps
@@ -308,19 +306,19 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
     using F = UFmt<TYPE>;
     constexpr int ES = Roles<MR>::ES, HM = Roles<MR>::HM;
     constexpr int MMA2_WARP = 6 + 4 * ES;       // the second MMA issuer
-    constexpr int SG = N <= 16 ? 8 : 4;         // sub-blocks per accumulator stage
-    constexpr int NGROUPS = 8 / SG;
-    constexpr int D_COLS = SG * N;              // tensor-memory columns of an accumulator stage
-    constexpr int A_COLS = 64;                  // of an A stage: 8 sub-blocks x 32 bytes
-    constexpr int NA = N == 48 ? 2 : 3;         // A stages
-    constexpr int ND = N == 8 ? 4 : 2;          // accumulator stages
+    constexpr int NGROUPS = 1;                  // one accumulator per unit: the scales are in the A operand
+    constexpr int D_COLS = N;                   // tensor-memory columns of an accumulator stage
+    constexpr int A_COLS = 128;                 // of an A stage: 256 half-precision values of k per row
+    constexpr int NA = 3;                       // A stages
+    constexpr int ND = 4;                       // accumulator stages
     constexpr int D_BASE = NA * A_COLS;
     constexpr uint32_t TMEM_COLS = 512u;
     static_assert(D_BASE + ND * D_COLS <= 512, "tensor memory has 512 columns");
     constexpr int WB = ROWS * F::BYTES;
     constexpr int XB = (IC::BYTES + 127) & ~127;
     constexpr uint32_t IDESC = idesc_of(N);
-    constexpr int LDW = 3 * HM <= 4 ? 4 : (3 * HM <= 8 ? 8 : (3 * HM <= 16 ? 16 : 24));  // accumulator columns an epilogue thread reads per sub-block
+    constexpr int LDW = 2 * HM;  // accumulator columns an epilogue thread reads per unit: two digits per row of x
+    static_assert(LDW == 8 || LDW == 16, "tcgen05.ld shapes of the epilogue");
 
     extern __shared__ uint8_t smem_unaligned[];
     uint8_t* smem = smem_unaligned + ((128u - (tc::smem_u32(smem_unaligned) & 127u)) & 127u);
@@ -500,7 +498,7 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
         }
     } else if (warp == 1 || warp == MMA2_WARP) {
         // ---- MMA issue: one thread of warp 1 takes the even units of the run, one thread of the last warp the odd ones. An
-        // MMA of this shape keeps the tensor core busy for 60 to 75 clocks whatever N is, and issuing stalls while the
+        // MMA of this shape keeps the tensor core busy for about a hundred clocks whatever N is, and issuing stalls while the
         // tensor core's queue is full; with two issuers one waits for its unit's inputs (a poll of an mbarrier takes a few
         // hundred clocks to come back) while the other's MMAs run.
         if (lane == 0) {
@@ -564,26 +562,15 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
                 if (i == 0) CT(3);
                 const uint64_t xdesc = desc0 + (uint64_t)((uint32_t)((RES ? wk.b : xr.s) * XB) >> 4);
                 const uint32_t abase = tmem + (uint32_t)(ar.s * A_COLS);
+                const uint32_t dbase = tmem + (uint32_t)D_BASE + (uint32_t)(dr.s * D_COLS);
+                // sixteen steps of 16 values of k: 8 tensor-memory columns of A and one 16-row slab of the image each
 #pragma unroll
-                for (int g = 0; g < NGROUPS; g++) {
-                    if (g > 0) {
-                        ok = my_turn(dr.s, filling[dr.s]) && tc::mbar_wait(empty_d(dr.s), dr.ph ^ 1u, abort_flag, &g_umma_status, 64 + 2, limit);
-                        if (!ok) {
-                            break;
-                        }
-                        d_issued[dr.s] = filling[dr.s] + 1;
-                        tc::fence_after_sync();
-                    }
-                    const uint32_t dbase = tmem + (uint32_t)D_BASE + (uint32_t)(dr.s * D_COLS);
-#pragma unroll
-                    for (int sg = 0; sg < SG; sg++) {
-                        const int s = g * SG + sg;
-                        umma_i8_ts(dbase + (uint32_t)(sg * N), abase + (uint32_t)(s * 8), xdesc + (uint64_t)((s * IC::SUB_BYTES) >> 4), IDESC);
-                    }
-                    tc::umma_commit(full_d(dr.s));
-                    TR(1, i, 1 + (g & 1));
-                    dr.next(ND);
+                for (int st = 0; st < IC::STEPS; st++) {
+                    umma_f16_ts(dbase, abase + (uint32_t)(st * 8), xdesc + (uint64_t)((st * IC::SUB_BYTES) >> 4), IDESC, st > 0 ? 1u : 0u);
                 }
+                tc::umma_commit(full_d(dr.s));
+                TR(1, i, 1);
+                dr.next(ND);
                 if (!ok) {
                     break;
                 }
@@ -627,15 +614,8 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
             const uint4 h = *reinterpret_cast<const uint4*>(wrow);  // fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins
             const uint32_t sca = h.y & 0x3f3f3f3fu, scb = and_or(h.y >> 2, 0x30303030u, h.w & 0x0f0f0f0fu);            // scales 0..3, 4..7
             const uint32_t mna = h.z & 0x3f3f3f3fu, mnb = and_or(h.z >> 2, 0x30303030u, (h.w >> 4) & 0x0f0f0f0fu);     // mins 0..3, 4..7
-            uint32_t sc16[4];  // the scales of sub-blocks 2j and 2j + 1 as 16-bit halves
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint32_t pair = __byte_perm(j < 2 ? sca : scb, 0u, 0x4140u + (uint32_t)(2 * (j & 1)) * 0x0101u);  // bytes (e, 0, o, 0)
-                sc16[j] = F::IN_PLACE ? pair + (pair & 0xffffu) * 15u : pair;
-            }
             uint4* prow = reinterpret_cast<uint4*>(p_ring + ps * P_BYTES) + r;
-            prow[0] = make_uint4(sc16[0], sc16[1], sc16[2], sc16[3]);
-            prow[ROWS] = make_uint4(mna, mnb, h.x, 0u);
+            prow[0] = make_uint4(mna, mnb, h.x, 0u);
             warp_arrive(full_p(ps), lane);
             if (warp == 2) TR(2, i, 1);
             uint4 qh0 = make_uint4(0u, 0u, 0u, 0u), qh1 = qh0;
@@ -644,26 +624,42 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
                 qh1 = *reinterpret_cast<const uint4*>(wrow + 32);
             }
             const uint32_t hw[8] = {qh0.x, qh0.y, qh0.z, qh0.w, qh1.x, qh1.y, qh1.z, qh1.w};
+            // A byte b under the exponent byte 0x64 is the half-precision number 1024 + b. The operand is quant x scale, an
+            // integer below 2048 and therefore exact in half precision: (1024 + q) sc - 1024 sc in one fused multiply-add per
+            // pair. Q4_K's high nibbles stay where they are: (1024 + 16 q) (sc / 16) - 64 sc.
+            const __half2 k1024 = u32_as_half2(0x64006400u);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const uint4 qa = *reinterpret_cast<const uint4*>(wrow + F::QS + 32 * j);
                 const uint4 qb = *reinterpret_cast<const uint4*>(wrow + F::QS + 32 * j + 16);
                 const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-                uint32_t av[16];  // sub-block 2j: bytes 0..31, then sub-block 2j + 1
+                const uint32_t scw = j < 2 ? sca : scb;
+                const __half2 sce = __hsub2(u32_as_half2(__byte_perm(scw, 0x64646464u, 0x4040u + (uint32_t)(2 * (j & 1)) * 0x0101u)), k1024);
+                const __half2 sco = __hsub2(u32_as_half2(__byte_perm(scw, 0x64646464u, 0x4141u + (uint32_t)(2 * (j & 1)) * 0x0101u)), k1024);
+                const __half2 mule = sce, adde = __hmul2(sce, u32_as_half2(0xe400e400u));                                   // -1024 sc
+                const __half2 mulo = F::IN_PLACE ? __hmul2(sco, u32_as_half2(0x2c002c00u)) : sco;                           // sc / 16
+                const __half2 addo = __hmul2(sco, F::IN_PLACE ? u32_as_half2(0xd400d400u) : u32_as_half2(0xe400e400u));    // -64 sc
+                uint32_t lo[16], hi[16];  // sub-block 2j and sub-block 2j + 1: 32 values each, two to a register
 #pragma unroll
                 for (int c = 0; c < 8; c++) {
+                    uint32_t te, to;
                     if constexpr (TYPE == JQ_TYPE_Q5_K) {
                         // bit 2j (2j + 1) of the fifth-bit bytes goes to bit 4 of the low (high) nibbles' bytes
                         const uint32_t e = 2 * j <= 4 ? hw[c] << (4 - 2 * j) : hw[c] >> (2 * j - 4);
                         const uint32_t o = 2 * j + 1 <= 4 ? hw[c] << (3 - 2 * j) : hw[c] >> (2 * j - 3);
-                        av[c] = and_or(e, 0x10101010u, w[c] & 0x0f0f0f0fu);
-                        av[8 + c] = and_or(o, 0x10101010u, (w[c] >> 4) & 0x0f0f0f0fu);
+                        te = and_or(e, 0x10101010u, w[c] & 0x0f0f0f0fu);
+                        to = and_or(o, 0x10101010u, (w[c] >> 4) & 0x0f0f0f0fu);
                     } else {
-                        av[c] = w[c] & 0x0f0f0f0fu;
-                        av[8 + c] = w[c] & 0xf0f0f0f0u;
+                        te = w[c] & 0x0f0f0f0fu;
+                        to = w[c] & 0xf0f0f0f0u;
                     }
+                    lo[2 * c] = half2_as_u32(__hfma2(u32_as_half2(__byte_perm(te, 0x64646464u, 0x4140u)), mule, adde));
+                    lo[2 * c + 1] = half2_as_u32(__hfma2(u32_as_half2(__byte_perm(te, 0x64646464u, 0x4342u)), mule, adde));
+                    hi[2 * c] = half2_as_u32(__hfma2(u32_as_half2(__byte_perm(to, 0x64646464u, 0x4140u)), mulo, addo));
+                    hi[2 * c + 1] = half2_as_u32(__hfma2(u32_as_half2(__byte_perm(to, 0x64646464u, 0x4342u)), mulo, addo));
                 }
-                tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 16 * j), av);
+                tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 32 * j), lo);
+                tmem_st16(tmem + lane_base + (uint32_t)(as * A_COLS + 32 * j + 16), hi);
             }
             tmem_st_wait();
             if (warp == 2) TR(2, i, 2);
@@ -832,73 +828,22 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
             }
             tc::fence_after_sync();
             if (warp == 6) TR(3, i, 0);
-            const uint4* prow = reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r;
-            const uint4 pa = prow[0], pb = prow[ROWS];
+            const uint4 pb = *(reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r);
             warp_arrive(empty_p(ps), lane);
-            const uint32_t sc16[4] = {pa.x, pa.y, pa.z, pa.w};
-            int I[HM][3];
-#pragma unroll
-            for (int m = 0; m < HM; m++) {
-                I[m][0] = I[m][1] = I[m][2] = 0;
-            }
-#pragma unroll
-            for (int g = 0; g < NGROUPS; g++) {
+            // the accumulators of this thread's rows of x: for row m the sum over the super-block of quant x scale x high digit, then x low digit
+            uint32_t dv[LDW];
+            {
                 const uint32_t ds = (uint32_t)dr.s;
-                if (g > 0) {
-                    ok = warp_wait(full_d(ds), dr.ph, abort_flag, 64 + 4, limit, lane);
-                    if (!ok) {
-                        break;
-                    }
-                    tc::fence_after_sync();
-                }
-                const uint32_t dbase = tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS + 3 * m0);
-                constexpr int CS = (64 / LDW) < SG ? (64 / LDW) : SG;  // sub-blocks whose accumulators are in registers at a time
-#pragma unroll
-                for (int c0 = 0; c0 < SG; c0 += CS) {
-                    uint32_t dv[CS][LDW];
-#pragma unroll
-                    for (int c = 0; c < CS; c++) {
-                        if constexpr (LDW == 24) {
-                            uint32_t lo[16], hi[8];
-                            tmem_ld<16>(lo, dbase + (uint32_t)((c0 + c) * N));
-                            tmem_ld<8>(hi, dbase + (uint32_t)((c0 + c) * N + 16));
-#pragma unroll
-                            for (int q = 0; q < 16; q++) {
-                                dv[c][q] = lo[q];
-                            }
-#pragma unroll
-                            for (int q = 0; q < 8; q++) {
-                                dv[c][16 + q] = hi[q];
-                            }
-                        } else {
-                            tmem_ld<LDW>(dv[c], dbase + (uint32_t)((c0 + c) * N));
-                        }
-                    }
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < CS; c++) {
-                        const int s = g * SG + c0 + c;
-                        const int scale = (int)((s & 1) ? sc16[s >> 1] >> 16 : sc16[s >> 1] & 0xffffu);
-#pragma unroll
-                        for (int m = 0; m < HM; m++) {
-#pragma unroll
-                            for (int dg = 0; dg < 3; dg++) {
-                                I[m][dg] += scale * (int)dv[c][3 * m + dg];
-                            }
-                        }
-                    }
-                }
+                tmem_ld<LDW>(dv, tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS + 2 * m0));
+                tmem_ld_wait();
                 tc::fence_before_sync();
                 warp_arrive(empty_d(ds), lane);
-                if (warp == 6) TR(3, i, 1 + (g & 1));
+                if (warp == 6) TR(3, i, 1);
                 dr.next(ND);
             }
-            if (!ok) {
-                break;
-            }
-            // ---- this super-block's contribution: d (sum over digits of weight x integer) - dmin (sum over sub-blocks of min x sum of x) ----
+            // ---- this super-block's contribution: d (sum over the two digits of weight x accumulator) - dmin (sum over sub-blocks of min x sum of x) ----
             const float* aux = reinterpret_cast<const float*>(x_ring + (size_t)(RES ? b : xs) * XB + IC::XD) + m0;
-            const float d = half_bits_to_float(pb.z) * (F::IN_PLACE ? 0.0625f : 1.0f), dmin = half_bits_to_float(pb.z >> 16);
+            const float d = half_bits_to_float(pb.z), dmin = half_bits_to_float(pb.z >> 16);
             float msum[HM];
 #pragma unroll
             for (int m = 0; m < HM; m++) {
@@ -916,7 +861,7 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
 #pragma unroll
             for (int m = 0; m < HM; m++) {
                 const float w0 = aux[8 * IC::MPAD + m];
-                const float q = fmaf(w0 * 65536.0f, (float)I[m][2], fmaf(w0 * 256.0f, (float)I[m][1], w0 * (float)I[m][0]));
+                const float q = fmaf(w0 * 2048.0f, __uint_as_float(dv[2 * m]), w0 * __uint_as_float(dv[2 * m + 1]));
                 c[m] = fmaf(d, q, -(dmin * msum[m]));
             }
             if constexpr (!RES) {
@@ -1073,18 +1018,11 @@ int launch_typed(const UArgs& a, int grid, size_t smem, cudaStream_t s) {
 template <int TYPE, bool PEER>
 int by_rows(int mr, bool resident, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     if (resident) {
-        switch (mr) {
-            case 1: return launch_typed<TYPE, 1, PEER, true>(a, grid, smem, s);
-            case 2: return launch_typed<TYPE, 2, PEER, true>(a, grid, smem, s);
-            default: return launch_typed<TYPE, 5, PEER, true>(a, grid, smem, s);
-        }
+        return mr == 4 ? launch_typed<TYPE, 4, PEER, true>(a, grid, smem, s) : launch_typed<TYPE, 8, PEER, true>(a, grid, smem, s);
     }
     switch (mr) {
-        case 1: return launch_typed<TYPE, 1, PEER, false>(a, grid, smem, s);
-        case 2: return launch_typed<TYPE, 2, PEER, false>(a, grid, smem, s);
-        case 5: return launch_typed<TYPE, 5, PEER, false>(a, grid, smem, s);
+        case 4: return launch_typed<TYPE, 4, PEER, false>(a, grid, smem, s);
         case 8: return launch_typed<TYPE, 8, PEER, false>(a, grid, smem, s);
-        case 10: return launch_typed<TYPE, 10, PEER, false>(a, grid, smem, s);
         default: return launch_typed<TYPE, 16, PEER, false>(a, grid, smem, s);
     }
 }
@@ -1105,7 +1043,7 @@ int launch_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream
     return JQ_OK;
 }
 
-int rows_bucket(int rows) { return rows <= 2 ? rows : (rows <= 5 ? 5 : (rows <= 8 ? 8 : (rows <= 10 ? 10 : 16))); }
+int rows_bucket(int rows) { return rows <= 4 ? 4 : (rows <= 8 ? 8 : 16); }
 
 }  // namespace
 
@@ -1120,8 +1058,22 @@ static bool shape_ok(int type, int64_t k, int rows) {
     return (type == JQ_TYPE_Q4_K || type == JQ_TYPE_Q5_K) && rows >= 1 && rows <= 16 && k > 0 && k % 256 == 0;
 }
 
-bool gemv_umma_takes(int type, int64_t k, int rows) {
-    return shape_ok(type, k, rows) && g_opt_gemv_umma.load(std::memory_order_relaxed) != 0 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0;
+// Option gemv_tcgen05 = 1: every shape the kernel takes. 0 (the default): where it is measured faster than the mma.sync kernel's
+// two passes, which is 11 or more rows of x on a weight with at least one 128-row tile per SM (a CTA's run then spans whole
+// tiles and only running sums change hands). 2: never. n = 0: the caller does not know the weight's rows (only option 1 counts).
+bool gemv_umma_takes(int type, int64_t k, int rows, int64_t n) {
+    if (!shape_ok(type, k, rows) || g_opt_gemv_generic.load(std::memory_order_relaxed) != 0) {
+        return false;
+    }
+    const int64_t opt = g_opt_gemv_umma.load(std::memory_order_relaxed);
+    if (opt != 0) {
+        return opt == 1;
+    }
+    return rows >= UMMA_AUTO_MIN_ROWS && (n + ROWS - 1) / ROWS >= sm_count_of_current_device();
+}
+
+bool gemv_umma_fallback(int type, int64_t k, int rows) {
+    return shape_ok(type, k, rows) && g_opt_gemv_umma.load(std::memory_order_relaxed) != 2 && g_opt_gemv_generic.load(std::memory_order_relaxed) == 0;
 }
 
 // Writes the activation image of x [rows, k] for gemv_umma (rows in [1, 16]) into `image` (gemv_umma_image_bytes bytes).
@@ -1129,8 +1081,7 @@ int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, 
     switch (umma::columns_for_rows(rows_bucket(rows))) {
         case 8: return launch_image<8>(x, rows, k, image, s);
         case 16: return launch_image<16>(x, rows, k, image, s);
-        case 32: return launch_image<32>(x, rows, k, image, s);
-        default: return launch_image<48>(x, rows, k, image, s);
+        default: return launch_image<32>(x, rows, k, image, s);
     }
 }
 
@@ -1173,7 +1124,7 @@ int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* ima
         a.max_pieces = 1;
     }
     const size_t xb = (umma::image_block_bytes(ncols) + 127) & ~(size_t)127;
-    a.SX = ncols <= 16 ? 8 : (ncols == 32 ? 6 : 5);
+    a.SX = ncols == 8 ? 8 : (ncols == 16 ? 6 : 4);
     // Few rows of x and a k whose whole image fits beside the weight ring: the kernel builds the image itself in shared memory
     // (no image kernel, no trip of the image through global memory).
     const bool resident = x != nullptr && ncols <= 16 && (size_t)a.KB * xb <= RESIDENT_MAX;

@@ -1,8 +1,8 @@
 """The tcgen05 decode GEMV (option "gemv_tcgen05"; Q4_K and Q5_K, 1 to 16 rows of x in one pass over the weights) against the
 CPU oracle (ops/Gguf.java:187-205 semantics) and against the default kernel.
 
-The kernel is not the default (the mma.sync kernel is faster on every measured shape), so these tests switch it on. They cover
-what is particular to it: every column count of the MMA (rows 1, 2, 5, 8, 10, 16), tiles shared by several thread blocks
+The kernel is not the default (the mma.sync kernel is faster on nearly every measured shape), so these tests switch it on. They
+cover what is particular to it: every column count of the MMA (up to 4, 8 and 16 rows), tiles shared by several thread blocks
 (few output rows), tiles split between two (many output rows), the activation image built inside the kernel (small k) and
 streamed from a scratch buffer (large k or many rows), the pair of weights in one launch is covered by the decoder tests of
 the default kernel only. Tolerance: max |diff| <= 1e-3 max |expect| (FP32 accumulation) and the reference's 2e-4 bound.
@@ -81,3 +81,29 @@ def test_non_finite_activations_give_nan():
     got = Gguf.linear(x, w, None)
     assert np.isnan(got[0]).all() and np.isnan(got[2]).all()
     close_like_reference(oracle.linear("Q4_K", raw, x[1:2]), got[1:2], "finite row")
+
+
+@pytest.mark.parametrize("t,n,k,m", [("Q4_K", 32000, 4096, 12), ("Q5_K", 20480, 5120, 16), ("Q4_K", 32000, 4096, 27), ("Q5_K", 49152, 8192, 8)])
+def test_shapes_that_reach_the_kernel_without_the_option(t, n, k, m):
+    """With the option at its default the kernel takes 11 to 16 rows of x on weights of at least one 128-row tile per SM (27 rows:
+    16 through it, 11 more through it), and stands in where the mma.sync kernel declines (Q5_K, k = 8192, 3 to 8 rows of x and
+    more 16-row tiles per thread block than that kernel can carry sums for)."""
+    L = jitnn_b200.load()
+    L.jq_set_option(b"gemv_tcgen05", 0)
+    rows = np.unique(np.concatenate([np.arange(130), np.arange(n - 130, n), np.random.default_rng(n).integers(0, n, 48)]))
+    got = check(t, n, k, m, seed=n + m, rows=rows)
+    L.jq_set_option(b"gemv_tcgen05", 2)  # never: the same call through the mma.sync kernel (or, where that declines, the CUDA-core one)
+    raw = synth.random_valid_blocks(t, n, k, seed=n + m).numpy()
+    x = np.random.default_rng(n + m + 1).standard_normal((m, k)).astype(np.float32)
+    bias = np.random.default_rng(n + m + 2).standard_normal(n).astype(np.float32)
+    w = Tensor.quantized(t, raw, n, k)
+    other = Gguf.linear(torch.from_numpy(x).cuda(), w, torch.from_numpy(bias).cuda()).cpu().numpy()
+    w.release()
+    assert float(np.abs(other - got).max() / np.abs(other).max()) <= 1e-5
+
+
+def test_option_values():
+    L = jitnn_b200.load()
+    assert L.jq_set_option(b"gemv_tcgen05", 3) != 0
+    assert L.jq_set_option(b"gemv_tcgen05", 2) == 0
+    assert L.jq_set_option(b"gemv_tcgen05", 0) == 0
