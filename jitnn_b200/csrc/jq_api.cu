@@ -225,6 +225,35 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
     return JQ_OK;
 }
 
+// Up to three linears on the same x [m, k] (the decoder's wq / wk / wv, and w1 / w3). Weights of one K-quant type and k whose
+// rows together are a shape the tcgen05 kernel is chosen for go through it in one launch, sharing one activation image;
+// anything else is one linear after the other.
+int linear_device_multi(const jq_weight* const* ws, int count, const float* x, int64_t m, float* const* ys, cudaStream_t s) {
+    const int64_t min_rows = g_prefill_min_rows.load();
+    bool together = count >= 2 && count <= 3 && m >= 1 && m <= 16 && !(min_rows > 0 && m >= min_rows);
+    int64_t n_all = 0;
+    for (int i = 0; i < count && together; i++) {
+        together = ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->n > 0;
+        n_all += ws[i]->n;
+    }
+    if (together && gemv_umma_takes(ws[0]->type, ws[0]->k, (int)m, n_all)) {
+        View vs[3];
+        for (int i = 0; i < count; i++) {
+            vs[i] = view_of(ws[i]);
+        }
+        uint8_t* image = nullptr;
+        int rc = scratch_for(s, gemv_umma_image_bytes(ws[0]->k, (int)m), &image);
+        return rc == JQ_OK ? launch_gemv_umma_multi(vs, count, x, image, (int)m, nullptr, ys, s) : rc;
+    }
+    for (int i = 0; i < count; i++) {
+        int rc = linear_device(ws[i], x, m, nullptr, ys[i], s, false);
+        if (rc != JQ_OK) {
+            return rc;
+        }
+    }
+    return JQ_OK;
+}
+
 }  // namespace jq
 
 using namespace jq;

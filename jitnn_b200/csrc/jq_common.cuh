@@ -186,6 +186,8 @@ inline size_t gemv_umma_image_bytes_one_row(int64_t k) { return gemv_umma_image_
 int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s);
 int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
                      const PeerOut* peer = nullptr, bool no_scratch = false);
+int launch_gemv_umma_multi(const View* vs, int count, const float* x, uint8_t* image, int rows, const float* bias, float* const* ys, cudaStream_t s,
+                           const PeerOut* peer = nullptr, bool no_scratch = false);
 int gemv_umma_status(int* status);
 // Option "gemv_tcgen05": 1 sends Q4_K and Q5_K decode (1 to 16 rows) to the tcgen05 kernel instead of the mma.sync one, 2 never,
 // 0 where it is faster (many rows of x, many rows of the weight).

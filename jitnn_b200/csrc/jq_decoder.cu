@@ -20,6 +20,7 @@
 namespace jq {
 
 int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bias, float* y, cudaStream_t s, bool x_remote = false);
+int linear_device_multi(const jq_weight* const* ws, int count, const float* x, int64_t m, float* const* ys, cudaStream_t s);
 
 namespace {
 
@@ -89,13 +90,36 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const float* __rest
 }
 
 // If delta != nullptr: x += delta (the residual add). Then out = x * rsqrt(mean(x^2) + eps) * w (RMSNorm).
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w, float eps,
-                                   float* __restrict__ out, int dim) {
+// One CTA of NORM_THREADS threads per row: with few rows the kernel is bound by the latency of its loads, so every thread has
+// all of its row's values in flight at once (128-bit loads) and keeps up to 16 of them in registers for the second pass.
+constexpr int NORM_THREADS = 1024;
+__global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
+                                                                   float eps, float* __restrict__ out, int dim) {
     __shared__ float scratch[32];
     float* xr = x + (int64_t)blockIdx.x * dim;
     const float* dr = delta != nullptr ? delta + (int64_t)blockIdx.x * dim : nullptr;
+    float* o = out + (int64_t)blockIdx.x * dim;
+    constexpr int HOLD = 4;
+    const int nv = (dim & 3) == 0 ? dim >> 2 : 0;  // 128-bit pieces; a dim that is no multiple of 4 takes the scalar loops below
+    float4 held[HOLD];
     float sq = 0.0f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+#pragma unroll
+    for (int h = 0; h < HOLD; h++) {
+        const int i = threadIdx.x + h * NORM_THREADS;
+        held[h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < nv) {
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            if (dr != nullptr) {
+                const float4 dv = reinterpret_cast<const float4*>(dr)[i];
+                v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                reinterpret_cast<float4*>(xr)[i] = v;
+            }
+            held[h] = v;
+            sq = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, sq))));
+        }
+    }
+    const int rest = nv > 0 ? (nv > HOLD * NORM_THREADS ? 4 * HOLD * NORM_THREADS : dim) : 0;  // first element the loops below handle
+    for (int i = rest + threadIdx.x; i < dim; i += NORM_THREADS) {
         float v = xr[i];
         if (dr != nullptr) {
             v += dr[i];
@@ -105,8 +129,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     }
     const float total = block_sum(sq, scratch);
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
-    float* o = out + (int64_t)blockIdx.x * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+#pragma unroll
+    for (int h = 0; h < HOLD; h++) {
+        const int i = threadIdx.x + h * NORM_THREADS;
+        if (i < nv) {
+            const float4 wv = reinterpret_cast<const float4*>(w)[i];
+            reinterpret_cast<float4*>(o)[i] = make_float4(held[h].x * inv * wv.x, held[h].y * inv * wv.y, held[h].z * inv * wv.z, held[h].w * inv * wv.w);
+        }
+    }
+    for (int i = rest + threadIdx.x; i < dim; i += NORM_THREADS) {
         o[i] = xr[i] * inv * w[i];
     }
 }
@@ -1456,11 +1487,12 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         // attention block; the residual add of the previous block's feed-forward output is fused into this norm
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
-        LIN(L[0], d->xn, d->q);
-        LIN(L[1], d->xn, d->k);
-        LIN(L[2], d->xn, d->v);
+        {
+            float* const qkv[3] = {d->q, d->k, d->v};
+            if (rc == JQ_OK) rc = linear_device_multi(L, 3, d->xn, T, qkv, s);
+        }
         if (rc != JQ_OK) break;
         rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd, pos_step, tok_stride);
         LAUNCHED("rope_store_kernel");
@@ -1474,10 +1506,12 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         LIN(L[3], d->att, d->proj);
         if (rc != JQ_OK) break;
         // feed-forward block
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
-        LIN(L[4], d->xn, d->gate);
-        LIN(L[5], d->xn, d->up);
+        {
+            float* const gu[2] = {d->gate, d->up};
+            if (rc == JQ_OK) rc = linear_device_multi(L + 4, 2, d->xn, T, gu, s);
+        }
         if (rc != JQ_OK) break;
         const int64_t cnt = (int64_t)T * d->hidden;
         swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
@@ -1485,7 +1519,7 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         LIN(L[6], d->act, d->proj);
     }
     if (rc == JQ_OK) {
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         LIN(d->output, d->xn, d->logits);
     }
@@ -1617,7 +1651,7 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             GEMV_IMAGED(L[0], d->q, L[1], d->k);
             GEMV_IMAGED(L[2], d->v, nullptr, nullptr);
         } else {
-            add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+            add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
             LIN(L[0], d->xn, d->q);
             LIN(L[1], d->xn, d->k);
@@ -1656,7 +1690,7 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
             NORM_IMAGE(B, d->norms + (size_t)(2 * l + 1) * dim, {L[4], L[5]});
             GEMV_IMAGED(L[4], d->gate, L[5], d->up);
         } else {
-            add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+            add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
             LIN(L[4], d->xn, d->gate);
             LIN(L[5], d->xn, d->up);
@@ -1680,7 +1714,7 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         }
     }
     if (rc == JQ_OK) {
-        add_rmsnorm_kernel<<<T, 256, 0, s>>>(d->x, D, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, D, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         PEER_LIN(d->output, d->xn, d->vocab, vocab_l, 4);
     }
@@ -1959,7 +1993,7 @@ JQ_API int jq_decoder_prompt(jq_decoder* d, int seq, const int32_t* tokens_host,
             const jq_weight* const* L = &d->lin[(size_t)l * 7];
             float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
             float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
-            add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, l == 0 ? nullptr : proj, d->norms + (size_t)(2 * l) * dim, d->eps, xn, dim);
+            add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(x, l == 0 ? nullptr : proj, d->norms + (size_t)(2 * l) * dim, d->eps, xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
             LIN(L[0], xn, q, true);
             LIN(L[1], xn, k, false);
@@ -1976,7 +2010,7 @@ JQ_API int jq_decoder_prompt(jq_decoder* d, int seq, const int32_t* tokens_host,
             LAUNCHED("attention_prompt_kernel");
             LIN(L[3], att, proj, true);
             if (rc != JQ_OK) break;
-            add_rmsnorm_kernel<<<T, 256, 0, s>>>(x, proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, xn, dim);
+            add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(x, proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
             LIN(L[4], xn, gate, true);
             LIN(L[5], xn, up, false);
@@ -1989,7 +2023,7 @@ JQ_API int jq_decoder_prompt(jq_decoder* d, int seq, const int32_t* tokens_host,
         if (rc == JQ_OK) {
             // the last token alone goes on: final residual add and norm, output projection (FP32 path), first index of the maximum
             const size_t last = (size_t)(T - 1) * dim;
-            add_rmsnorm_kernel<<<1, 256, 0, s>>>(x + last, proj + last, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+            add_rmsnorm_kernel<<<1, NORM_THREADS, 0, s>>>(x + last, proj + last, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
             if (rc == JQ_OK) rc = linear_device(d->output, d->xn, 1, nullptr, d->logits, s);
         }

@@ -98,16 +98,17 @@ struct UFmt<JQ_TYPE_Q5_K> {
 };
 
 struct UArgs {
-    const uint8_t* q0;      // blocks of the first weight, row after row
-    const uint8_t* q1;      // of the second weight, if there is one
+    const uint8_t* q[3];    // blocks of up to three weights of one type and k (unused entries: those of the first)
     const uint8_t* image;   // [KB][image block], unless the kernel builds the image itself ...
     const float* x;         // ... from x [rows, k]
     const float* bias;
-    float* y0;
-    float* y1;
-    int64_t n0, n1;         // rows of the first and of the second weight (n1 = 0: none)
-    int KB;                 // super-blocks per weight row
-    int tiles0, tiles;      // 128-row tiles of the first weight, of both
+    float* y[3];
+    int64_t n[3];           // rows of the weights (0: none)
+    int64_t col0[3], n_sum; // NC > 1: where a weight's rows start in a row of `parts`, and the length of such a row
+    int KB;                 // super-blocks per tile: those of a weight row, or (NC > 1) of one of the NC equal ranges a row's k is cut into
+    int NC;                 // ranges of k: each (tile, range) is a tile of its own whose sums go to `parts` instead of y
+    float* parts;           // NC > 1: [NC][rows][n_sum] sums per range, added in range order by umma_parts_sum_kernel
+    int tile_end[3], tiles; // 128-row tiles (times NC) up to and including each weight; of all
     int rows;               // rows of x
     int SW;                 // stages of the weight ring
     int SX;                 // stages of the image ring
@@ -289,6 +290,38 @@ __global__ void __launch_bounds__(128) umma_activation_image_kernel(const float*
     }
 }
 
+// Where the outputs of up to three weights go: weight w owns columns [col0[w], col0[w] + n[w]) of a row of `parts`.
+struct PartsOut {
+    float* y[3];
+    int64_t n[3], col0[3];
+    int64_t n_sum;
+};
+// y_w [rows, n_w] = (bias +) the sums of the NC ranges of k, added in range order (one thread per output).
+__global__ void __launch_bounds__(256) umma_parts_sum_kernel(const float* __restrict__ parts, int nc, int rows, PartsOut po, const float* __restrict__ bias) {
+    const int64_t outputs = (int64_t)rows * po.n_sum;
+    const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i < outputs) {
+        float v[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            v[c] = c < nc ? __ldcg(parts + (size_t)c * outputs + i) : 0.0f;
+        }
+        float sum = v[0];
+#pragma unroll
+        for (int c = 1; c < 8; c++) {
+            if (c < nc) {
+                sum += v[c];
+            }
+        }
+        const int64_t m = i / po.n_sum, col = i - m * po.n_sum;
+        const int wi = col < po.col0[1] ? 0 : (col < po.col0[2] ? 1 : 2);
+        const int64_t row = col - (wi == 0 ? 0 : (wi == 1 ? po.col0[1] : po.col0[2]));
+        const int64_t n = wi == 0 ? po.n[0] : (wi == 1 ? po.n[1] : po.n[2]);
+        float* y = wi == 0 ? po.y[0] : (wi == 1 ? po.y[1] : po.y[2]);
+        y[m * n + row] = sum + ((bias != nullptr && wi == 0) ? bias[row] : 0.0f);
+    }
+}
+
 // MR = rows of x the kernel computes (4, 8 or 16; a call with fewer rows leaves the others unused). From eight rows on two
 // sets of epilogue warps share the rows of x. RES: the image of the whole k is built by this kernel into shared memory and
 // stays there (small k x rows).
@@ -392,8 +425,9 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
 
     // Weights depend on nothing that runs before this kernel: the first ring-full of them is requested at once.
     auto issue_w = [&](int i, int s, int t, int b) {
-        const bool first = t < a.tiles0;
-        const uint8_t* src = (first ? a.q0 : a.q1) + ((int64_t)(first ? t : t - a.tiles0) * KB + b) * WB;
+        const int wi = t < a.tile_end[0] ? 0 : (t < a.tile_end[1] ? 1 : 2);
+        const int t_in = t - (wi == 0 ? 0 : (wi == 1 ? a.tile_end[0] : a.tile_end[1]));
+        const uint8_t* src = (wi == 0 ? a.q[0] : (wi == 1 ? a.q[1] : a.q[2])) + ((int64_t)t_in * KB + b) * WB;
         tc::mbar_expect_tx(full_w(s), WB);
         tc::bulk_load(tc::smem_u32(w_ring + (size_t)s * WB), src, WB, full_w(s));
         TR(0, i, 0);
@@ -440,7 +474,8 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
     if (warp == 0) {
         // ---- copies: one thread asks the copy engine for a unit's weights (one contiguous run of the tiled layout) and, unless
         // the image is resident, for its super-block's image, which is complete only when the kernel before this one has finished.
-        auto issue_x = [&](int i, int s, int b) {
+        auto issue_x = [&](int i, int s, int t, int b_in_tile) {
+            const int b = a.NC > 1 ? (t % a.NC) * KB + b_in_tile : b_in_tile;  // the range's first super-block of k + the position in it
             tc::mbar_expect_tx(full_x(s), IC::BYTES);
             tc::bulk_load(tc::smem_u32(x_ring + s * XB), a.image + (size_t)b * IC::BYTES, IC::BYTES, full_x(s));
             TR(0, i, 1);
@@ -461,7 +496,7 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
             wx.start(u0, u1, KB);
             if constexpr (!RES) {
                 for (int i = 0; i < ix; i++) {
-                    issue_x(i, i, wx.b);
+                    issue_x(i, i, wx.t, wx.b);
                     wx.next();
                 }
             }
@@ -479,7 +514,7 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
                     wr.next(SW);
                 }
                 if (xfree) {
-                    issue_x(ix++, xr.s, wx.b);
+                    issue_x(ix++, xr.s, wx.t, wx.b);
                     wx.next();
                     xr.next(SX);
                 }
@@ -703,10 +738,27 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
         epilogue_barrier(1 + eset);
         // y (or every rank's y) for this thread's row of tile `tile`
         auto write_tile = [&](int tile, const float (&sum)[HM]) {
-            const bool second = tile >= a.tiles0;
-            const int64_t n = second ? a.n1 : a.n0;
-            const int64_t row = (int64_t)(second ? tile - a.tiles0 : tile) * ROWS + r;
-            float* const yo = second ? a.y1 : a.y0;
+            const int wi = tile < a.tile_end[0] ? 0 : (tile < a.tile_end[1] ? 1 : 2);
+            const int t_in = tile - (wi == 0 ? 0 : (wi == 1 ? a.tile_end[0] : a.tile_end[1]));
+            const int64_t n = wi == 0 ? a.n[0] : (wi == 1 ? a.n[1] : a.n[2]);
+            if (a.NC > 1) {
+                // a range of k of tile `t_in / NC` of its weight: its sums wait in `parts` for the kernel that adds the ranges in order
+                const int t = t_in / a.NC, c = t_in - t * a.NC;
+                const int64_t row = (int64_t)t * ROWS + r;
+                if (row < n) {
+                    float* dst = a.parts + ((size_t)c * a.rows + m0) * a.n_sum + (wi == 0 ? a.col0[0] : (wi == 1 ? a.col0[1] : a.col0[2])) + row;
+#pragma unroll
+                    for (int m = 0; m < HM; m++) {
+                        if (m0 + m < a.rows) {
+                            dst[(size_t)m * a.n_sum] = sum[m];
+                        }
+                    }
+                }
+                return;
+            }
+            const bool second = wi != 0;
+            const int64_t row = (int64_t)t_in * ROWS + r;
+            float* const yo = wi == 0 ? a.y[0] : (wi == 1 ? a.y[1] : a.y[2]);
             if (row < n) {
                 const float bv = (a.bias != nullptr && !second) ? a.bias[row] : 0.0f;
 #pragma unroll
@@ -1061,6 +1113,24 @@ static bool shape_ok(int type, int64_t k, int rows) {
 // Option gemv_tcgen05 = 1: every shape the kernel takes. 0 (the default): where it is measured faster than the mma.sync kernel's
 // two passes, which is 11 or more rows of x on a weight with at least one 128-row tile per SM (a CTA's run then spans whole
 // tiles and only running sums change hands). 2: never. n = 0: the caller does not know the weight's rows (only option 1 counts).
+// Into how many equal ranges the k of a weight with few tiles is cut so that every CTA's run spans at least one (tile, range):
+// such a pair is then shared by at most two CTAs and only running sums change hands. 1: no cut needed; 0: no cut of at most 8
+// ranges of at least 4 super-blocks does it.
+static int ranges_of_k(int type, int kb, int64_t tiles, int sms) {
+    if (tiles >= sms) {
+        return 1;
+    }
+    if (type == JQ_TYPE_Q5_K && tiles * kb < 12 * (int64_t)sms) {
+        return 0;  // measured: with fewer than 12 units per CTA the Q5_K kernel does not make up for its start and the extra launch
+    }
+    for (int nc = 2; nc <= 8; nc++) {
+        if (kb % nc == 0 && kb / nc >= 4 && tiles * nc >= sms) {
+            return nc;
+        }
+    }
+    return 0;
+}
+
 bool gemv_umma_takes(int type, int64_t k, int rows, int64_t n) {
     if (!shape_ok(type, k, rows) || g_opt_gemv_generic.load(std::memory_order_relaxed) != 0) {
         return false;
@@ -1069,7 +1139,7 @@ bool gemv_umma_takes(int type, int64_t k, int rows, int64_t n) {
     if (opt != 0) {
         return opt == 1;
     }
-    return rows >= UMMA_AUTO_MIN_ROWS && (n + ROWS - 1) / ROWS >= sm_count_of_current_device();
+    return rows >= UMMA_AUTO_MIN_ROWS && n > 0 && ranges_of_k(type, (int)(k / 256), (n + ROWS - 1) / ROWS, sm_count_of_current_device()) > 0;
 }
 
 bool gemv_umma_fallback(int type, int64_t k, int rows) {
@@ -1085,16 +1155,23 @@ int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, 
     }
 }
 
-// y [rows, n] = x . W^T (+ bias) for a Q4_K or Q5_K weight and 1 to 16 rows of x. Either x is given (FP32 [rows, k]; `image`
-// is then scratch of gemv_umma_image_bytes(k, rows) bytes that is used unless the kernel can keep the whole image in shared
-// memory), or x is nullptr and `image` already holds the activation image, written earlier in the stream.
-// With v2 != nullptr the rows of a second weight of the same type and k follow in the same launch (results in y2, no
-// bias). `peer`: the outputs go into every rank's y of a row-sharded linear instead.
+// y_w [rows, n_w] = x . W_w^T (+ bias for the first) for one to three Q4_K or Q5_K weights of one type and k, and 1 to 16 rows of x:
+// the rows of the weights follow one another in the same launch. Either x is given (FP32 [rows, k]; `image` is then scratch of
+// gemv_umma_image_bytes(k, rows) bytes that is used unless the kernel can keep the whole image in shared memory), or x is
+// nullptr and `image` already holds the activation image, written earlier in the stream.
+// `peer` (one weight only): the outputs go into every rank's y of a row-sharded linear instead.
 // no_scratch: deal whole tiles to the CTAs, which needs no scratch buffers (and balances the load worse).
-int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
-                     const PeerOut* peer, bool no_scratch) {
-    if (!shape_ok(v.type, v.k, rows) || v.n <= 0 || (x == nullptr && image == nullptr) ||
-        (v2 != nullptr && (v2->type != v.type || v2->k != v.k || v2->n <= 0 || peer != nullptr))) {
+int launch_gemv_umma_multi(const View* vs, int count, const float* x, uint8_t* image, int rows, const float* bias, float* const* ys, cudaStream_t s,
+                           const PeerOut* peer, bool no_scratch) {
+    if (count < 1 || count > 3 || vs == nullptr || ys == nullptr) {
+        return fail(JQ_ERR_INVALID, "decode GEMV: %d weights in one launch (1 to 3)", count);
+    }
+    const View& v = vs[0];
+    bool ok = shape_ok(v.type, v.k, rows) && (x != nullptr || image != nullptr) && (count == 1 || peer == nullptr);
+    for (int i = 0; i < count && ok; i++) {
+        ok = vs[i].type == v.type && vs[i].k == v.k && vs[i].n > 0;
+    }
+    if (!ok) {
         return fail(JQ_ERR_UNSUPPORTED, "decode GEMV: type %d, k = %lld, %d rows is outside what the tcgen05 kernel takes", v.type, (long long)v.k, rows);
     }
     const int bb = v.type == JQ_TYPE_Q4_K ? 144 : 176;
@@ -1102,20 +1179,41 @@ int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* ima
     const int ncols = umma::columns_for_rows(mr);
     int rc = JQ_OK;
     UArgs a = {};
-    a.q0 = v.q;
-    a.q1 = v2 != nullptr ? v2->q : v.q;
     a.image = image;
     a.bias = bias;
-    a.y0 = y;
-    a.y1 = y2;
-    a.n0 = v.n;
-    a.n1 = v2 != nullptr ? v2->n : 0;
-    a.KB = (int)(v.k / 256);
-    a.tiles0 = (int)((v.n + ROWS - 1) / ROWS);
-    a.tiles = a.tiles0 + (v2 != nullptr ? (int)((v2->n + ROWS - 1) / ROWS) : 0);
+    const int sms = sm_count_of_current_device();
+    int64_t tiles_all = 0;
+    for (int i = 0; i < count; i++) {
+        tiles_all += (vs[i].n + ROWS - 1) / ROWS;
+    }
+    // Chosen by the default rule for many rows of x on weights of few tiles: the k of every tile in NC ranges (see ranges_of_k).
+    // The results then depend on NC, that is on the number of weight rows; asked for by the option, the kernel never cuts k.
+    int nc = 1;
+    if (g_opt_gemv_umma.load(std::memory_order_relaxed) == 0 && rows >= UMMA_AUTO_MIN_ROWS && peer == nullptr && !no_scratch) {
+        nc = ranges_of_k(v.type, (int)(v.k / 256), tiles_all, sms);
+        nc = nc < 1 ? 1 : nc;
+    }
+    a.NC = nc;
+    a.KB = (int)(v.k / 256) / nc;
+    PartsOut po = {};
+    int tile_end = 0;
+    int64_t col = 0;
+    for (int i = 0; i < 3; i++) {
+        const bool live = i < count;
+        a.q[i] = live ? vs[i].q : v.q;
+        a.y[i] = po.y[i] = live ? ys[i] : ys[0];
+        a.n[i] = po.n[i] = live ? vs[i].n : 0;
+        a.col0[i] = po.col0[i] = col;  // a weight that is not there starts where the rows end: no column is its
+        if (live) {
+            tile_end += (int)((vs[i].n + ROWS - 1) / ROWS) * nc;
+            col += vs[i].n;
+        }
+        a.tile_end[i] = tile_end;
+    }
+    a.n_sum = po.n_sum = col;
+    a.tiles = tile_end;
     a.rows = rows;
     const int64_t U = no_scratch ? a.tiles : (int64_t)a.tiles * a.KB;
-    const int sms = sm_count_of_current_device();
     const int grid = (int)(U < sms ? U : sms);
     a.whole_tiles = no_scratch ? 1 : 0;
     const int64_t per_cta = (U + grid - 1) / grid;
@@ -1127,7 +1225,7 @@ int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* ima
     a.SX = ncols == 8 ? 8 : (ncols == 16 ? 6 : 4);
     // Few rows of x and a k whose whole image fits beside the weight ring: the kernel builds the image itself in shared memory
     // (no image kernel, no trip of the image through global memory).
-    const bool resident = x != nullptr && ncols <= 16 && (size_t)a.KB * xb <= RESIDENT_MAX;
+    const bool resident = x != nullptr && nc == 1 && ncols <= 16 && (size_t)a.KB * xb <= RESIDENT_MAX;
     if (x != nullptr && !resident) {
         if (image == nullptr) {
             return fail(JQ_ERR_INVALID, "decode GEMV: no scratch for the activation image");
@@ -1156,10 +1254,33 @@ int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* ima
     }
     a.partial = reinterpret_cast<unsigned long long*>(partial);
     a.aside = reinterpret_cast<float*>(a.partial + (size_t)grid * a.max_pieces * rows * ROWS);
-    if (v.type == JQ_TYPE_Q4_K) {
-        return peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, resident, a, grid, smem, s);
+    if (nc > 1) {
+        uint8_t* parts = nullptr;
+        rc = scratch_for_slot(s, 4, (size_t)nc * rows * a.n_sum * sizeof(float), &parts);
+        if (rc != JQ_OK) {
+            return rc;
+        }
+        a.parts = reinterpret_cast<float*>(parts);
     }
-    return peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, resident, a, grid, smem, s);
+    if (v.type == JQ_TYPE_Q4_K) {
+        rc = peer != nullptr ? by_rows<JQ_TYPE_Q4_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q4_K, false>(mr, resident, a, grid, smem, s);
+    } else {
+        rc = peer != nullptr ? by_rows<JQ_TYPE_Q5_K, true>(mr, resident, a, grid, smem, s) : by_rows<JQ_TYPE_Q5_K, false>(mr, resident, a, grid, smem, s);
+    }
+    if (rc == JQ_OK && nc > 1) {
+        const int64_t outputs = (int64_t)rows * a.n_sum;
+        umma_parts_sum_kernel<<<(unsigned)((outputs + 255) / 256), 256, 0, s>>>(a.parts, nc, rows, po, bias);
+        count_launch();
+        rc = check_launch("umma_parts_sum_kernel");
+    }
+    return rc;
+}
+
+int launch_gemv_umma(const View& v, const View* v2, const float* x, uint8_t* image, int rows, const float* bias, float* y, float* y2, cudaStream_t s,
+                     const PeerOut* peer, bool no_scratch) {
+    const View vs[2] = {v, v2 != nullptr ? *v2 : v};
+    float* const ys[2] = {y, y2};
+    return launch_gemv_umma_multi(vs, v2 != nullptr ? 2 : 1, x, image, rows, bias, ys, s, peer, no_scratch);
 }
 
 #ifdef JQ_UMMA_TRACE

@@ -191,3 +191,27 @@ def test_full_width_decoder(layers, dim, heads, kv_heads, hidden, formats, fused
         dec.close()
     finally:
         jitnn_b200.load().jq_set_option(b"decoder_fused", 1)
+
+
+@pytest.mark.parametrize("layers,dim,heads,kv_heads,hidden", [(2, 4096, 32, 32, 11008), (1, 8192, 64, 8, 28672)])
+def test_full_width_decoder_twelve_tokens_per_call(layers, dim, heads, kv_heads, hidden):
+    """Twelve tokens in one call at the benchmark's widths, all Q4_K: from eleven rows on the linears whose weights have enough rows
+    go through the tcgen05 GEMV in one pass, wq / wk / wv and w1 / w3 as one launch each on one activation image, weights of few
+    128-row tiles with k cut into ranges; the others through the mma.sync kernel in two passes. Against the oracle, token by token."""
+    all_q4k = {"wv": "Q4_K", "w2": "Q4_K", "output": "Q4_K"}
+    cfg = llama_oracle.Config(layers=layers, dim=dim, heads=heads, kv_heads=kv_heads, hidden=hidden, vocab=32000, max_seq=16)
+    weights = llama_oracle.random_model(cfg, seed=dim // 32, formats=all_q4k)
+    dec = LlamaDecoder(cfg.layers, cfg.dim, cfg.heads, cfg.kv_heads, cfg.hidden, cfg.vocab, cfg.max_seq, cfg.eps, cfg.rope_base)
+    dec.load(weights)
+    ref = llama_oracle.Decoder(cfg, weights, threads=8)
+    prompt = np.random.default_rng(dim + 1).integers(0, cfg.vocab, 12).astype(np.int32)
+    ref_logits = np.stack([ref.forward(int(t), i) for i, t in enumerate(prompt)])
+    got, nxt = dec.forward(prompt, 0)
+    scale = np.abs(ref_logits).max()
+    assert np.abs(got - ref_logits).max() <= 2e-4 * scale, float(np.abs(got - ref_logits).max() / scale)
+    assert np.array_equal(nxt, np.argmax(got, axis=1))
+    # the same tokens in groups of at most eight (mma.sync kernels only): the two routes agree far inside the tolerance
+    dec.forward(prompt[:8], 0)
+    tail, _ = dec.forward(prompt[8:], 8)
+    assert np.abs(tail - got[8:]).max() <= 2e-5 * scale
+    dec.close()

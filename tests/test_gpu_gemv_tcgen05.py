@@ -83,11 +83,13 @@ def test_non_finite_activations_give_nan():
     close_like_reference(oracle.linear("Q4_K", raw, x[1:2]), got[1:2], "finite row")
 
 
-@pytest.mark.parametrize("t,n,k,m", [("Q4_K", 32000, 4096, 12), ("Q5_K", 20480, 5120, 16), ("Q4_K", 32000, 4096, 27), ("Q5_K", 49152, 8192, 8)])
+@pytest.mark.parametrize("t,n,k,m", [("Q4_K", 32000, 4096, 12), ("Q5_K", 20480, 5120, 16), ("Q4_K", 32000, 4096, 27), ("Q5_K", 49152, 8192, 8),
+                                     ("Q4_K", 8192, 8192, 16), ("Q4_K", 5120, 5120, 11), ("Q5_K", 8192, 28672, 13)])
 def test_shapes_that_reach_the_kernel_without_the_option(t, n, k, m):
     """With the option at its default the kernel takes 11 to 16 rows of x on weights of at least one 128-row tile per SM (27 rows:
-    16 through it, 11 more through it), and stands in where the mma.sync kernel declines (Q5_K, k = 8192, 3 to 8 rows of x and
-    more 16-row tiles per thread block than that kernel can carry sums for)."""
+    16 through it, 11 more through it), on weights of fewer tiles with k cut into 2 to 8 equal ranges whose sums a second kernel
+    adds in order (the last three cases: 4, 4 and 4 ranges), and stands in where the mma.sync kernel declines (Q5_K, k = 8192, 3 to
+    8 rows of x and more 16-row tiles per thread block than that kernel can carry sums for)."""
     L = jitnn_b200.load()
     L.jq_set_option(b"gemv_tcgen05", 0)
     rows = np.unique(np.concatenate([np.arange(130), np.arange(n - 130, n), np.random.default_rng(n).integers(0, n, 48)]))
