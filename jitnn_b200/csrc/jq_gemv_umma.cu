@@ -339,11 +339,14 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
     using F = UFmt<TYPE>;
     constexpr int ES = Roles<MR>::ES, HM = Roles<MR>::HM;
     constexpr int MMA2_WARP = 6 + 4 * ES;       // the second MMA issuer
-    constexpr int NGROUPS = 1;                  // one accumulator per unit: the scales are in the A operand
-    constexpr int D_COLS = N;                   // tensor-memory columns of an accumulator stage
+    constexpr int NGROUPS = 1;                  // one accumulator stage per unit: the scales are in the A operand
+    // (A unit's MMAs taking turns on two accumulators, so that none waits for the one before it, measured no faster: the
+    // sixteen MMAs of a unit take 1500 (N = 8) to 2100 (N = 32) clocks to issue either way.)
+    constexpr int ACC = 1;
+    constexpr int D_COLS = ACC * N;             // tensor-memory columns of an accumulator stage
     constexpr int A_COLS = 128;                 // of an A stage: 256 half-precision values of k per row
     constexpr int NA = 3;                       // A stages
-    constexpr int ND = 4;                       // accumulator stages
+    constexpr int ND = 128 / D_COLS < 4 ? 128 / D_COLS : 4;  // accumulator stages
     constexpr int D_BASE = NA * A_COLS;
     constexpr uint32_t TMEM_COLS = 512u;
     static_assert(D_BASE + ND * D_COLS <= 512, "tensor memory has 512 columns");
@@ -601,7 +604,8 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
                 // sixteen steps of 16 values of k: 8 tensor-memory columns of A and one 16-row slab of the image each
 #pragma unroll
                 for (int st = 0; st < IC::STEPS; st++) {
-                    umma_f16_ts(dbase, abase + (uint32_t)(st * 8), xdesc + (uint64_t)((st * IC::SUB_BYTES) >> 4), IDESC, st > 0 ? 1u : 0u);
+                    umma_f16_ts(dbase + (uint32_t)((st % ACC) * N), abase + (uint32_t)(st * 8), xdesc + (uint64_t)((st * IC::SUB_BYTES) >> 4), IDESC,
+                                st >= ACC ? 1u : 0u);
                 }
                 tc::umma_commit(full_d(dr.s));
                 TR(1, i, 1);
@@ -883,10 +887,13 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
             const uint4 pb = *(reinterpret_cast<const uint4*>(p_ring + ps * P_BYTES) + r);
             warp_arrive(empty_p(ps), lane);
             // the accumulators of this thread's rows of x: for row m the sum over the super-block of quant x scale x high digit, then x low digit
-            uint32_t dv[LDW];
+            uint32_t dv[ACC][LDW];
             {
                 const uint32_t ds = (uint32_t)dr.s;
-                tmem_ld<LDW>(dv, tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS + 2 * m0));
+#pragma unroll
+                for (int j = 0; j < ACC; j++) {
+                    tmem_ld<LDW>(dv[j], tmem + lane_base + (uint32_t)(D_BASE + ds * D_COLS + j * N + 2 * m0));
+                }
                 tmem_ld_wait();
                 tc::fence_before_sync();
                 warp_arrive(empty_d(ds), lane);
@@ -913,7 +920,13 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
 #pragma unroll
             for (int m = 0; m < HM; m++) {
                 const float w0 = aux[8 * IC::MPAD + m];
-                const float q = fmaf(w0 * 2048.0f, __uint_as_float(dv[2 * m]), w0 * __uint_as_float(dv[2 * m + 1]));
+                float dh = __uint_as_float(dv[0][2 * m]), dl = __uint_as_float(dv[0][2 * m + 1]);
+#pragma unroll
+                for (int j = 1; j < ACC; j++) {
+                    dh += __uint_as_float(dv[j][2 * m]);
+                    dl += __uint_as_float(dv[j][2 * m + 1]);
+                }
+                const float q = fmaf(w0 * 2048.0f, dh, w0 * dl);
                 c[m] = fmaf(d, q, -(dmin * msum[m]));
             }
             if constexpr (!RES) {
