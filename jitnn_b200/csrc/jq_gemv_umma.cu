@@ -13,7 +13,7 @@
 //         2048, exact in half precision: one byte permute per two quants and one fused multiply-add per pair) and store
 //         them into tensor memory as the A operand (tcgen05.st); the row's mins, d and dmin go into a small
 //         shared-memory ring;
-//       - one thread issues sixteen tcgen05.mma.cta_group::1.kind::f16 (M = 128 rows, N = 8..32 digit columns, K = 16,
+//       - one thread issues sixteen tcgen05.mma.cta_group::1.kind::f16 (M = 128 rows, N = 16 or 32 digit columns, K = 16,
 //         A from tensor memory, B = the image in shared memory) that accumulate the whole super-block into one FP32
 //         accumulator: the scales are already in the operand;
 //       - 128 "epilogue" threads, one per weight row, read the accumulators (tcgen05.ld), weigh the two digits, and
@@ -322,8 +322,8 @@ __global__ void __launch_bounds__(256) umma_parts_sum_kernel(const float* __rest
     }
 }
 
-// MR = rows of x the kernel computes (4, 8 or 16; a call with fewer rows leaves the others unused). From eight rows on two
-// sets of epilogue warps share the rows of x. RES: the image of the whole k is built by this kernel into shared memory and
+// MR = rows of x the kernel computes (8 or 16; a call with fewer rows leaves the others unused). Two sets of epilogue warps
+// share the rows of x. RES: the image of the whole k is built by this kernel into shared memory and
 // stays there (small k x rows).
 template <int MR>
 struct Roles {
@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(Roles<MR>::THREADS, 1) gemv_umma_kernel(const 
     constexpr int MMA2_WARP = 6 + 4 * ES;       // the second MMA issuer
     constexpr int NGROUPS = 1;                  // one accumulator stage per unit: the scales are in the A operand
     // (A unit's MMAs taking turns on two accumulators, so that none waits for the one before it, measured no faster: the
-    // sixteen MMAs of a unit take 1500 (N = 8) to 2100 (N = 32) clocks to issue either way.)
+    // sixteen MMAs of a unit take 1500 (N = 16) to 2100 (N = 32) clocks to issue either way.)
     constexpr int ACC = 1;
     constexpr int D_COLS = ACC * N;             // tensor-memory columns of an accumulator stage
     constexpr int A_COLS = 128;                 // of an A stage: 256 half-precision values of k per row
@@ -1083,13 +1083,9 @@ int launch_typed(const UArgs& a, int grid, size_t smem, cudaStream_t s) {
 template <int TYPE, bool PEER>
 int by_rows(int mr, bool resident, const UArgs& a, int grid, size_t smem, cudaStream_t s) {
     if (resident) {
-        return mr == 4 ? launch_typed<TYPE, 4, PEER, true>(a, grid, smem, s) : launch_typed<TYPE, 8, PEER, true>(a, grid, smem, s);
+        return launch_typed<TYPE, 8, PEER, true>(a, grid, smem, s);
     }
-    switch (mr) {
-        case 4: return launch_typed<TYPE, 4, PEER, false>(a, grid, smem, s);
-        case 8: return launch_typed<TYPE, 8, PEER, false>(a, grid, smem, s);
-        default: return launch_typed<TYPE, 16, PEER, false>(a, grid, smem, s);
-    }
+    return mr == 8 ? launch_typed<TYPE, 8, PEER, false>(a, grid, smem, s) : launch_typed<TYPE, 16, PEER, false>(a, grid, smem, s);
 }
 
 template <int N>
@@ -1108,7 +1104,7 @@ int launch_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream
     return JQ_OK;
 }
 
-int rows_bucket(int rows) { return rows <= 4 ? 4 : (rows <= 8 ? 8 : 16); }
+int rows_bucket(int rows) { return rows <= 8 ? 8 : 16; }
 
 }  // namespace
 
@@ -1162,7 +1158,6 @@ bool gemv_umma_fallback(int type, int64_t k, int rows) {
 // Writes the activation image of x [rows, k] for gemv_umma (rows in [1, 16]) into `image` (gemv_umma_image_bytes bytes).
 int launch_gemv_umma_image(const float* x, int rows, int64_t k, uint8_t* image, cudaStream_t s) {
     switch (umma::columns_for_rows(rows_bucket(rows))) {
-        case 8: return launch_image<8>(x, rows, k, image, s);
         case 16: return launch_image<16>(x, rows, k, image, s);
         default: return launch_image<32>(x, rows, k, image, s);
     }
@@ -1235,7 +1230,7 @@ int launch_gemv_umma_multi(const View* vs, int count, const float* x, uint8_t* i
         a.max_pieces = 1;
     }
     const size_t xb = (umma::image_block_bytes(ncols) + 127) & ~(size_t)127;
-    a.SX = ncols == 8 ? 8 : (ncols == 16 ? 6 : 4);
+    a.SX = ncols == 16 ? 6 : 4;
     // Few rows of x and a k whose whole image fits beside the weight ring: the kernel builds the image itself in shared memory
     // (no image kernel, no trip of the image through global memory).
     const bool resident = x != nullptr && nc == 1 && ncols <= 16 && (size_t)a.KB * xb <= RESIDENT_MAX;

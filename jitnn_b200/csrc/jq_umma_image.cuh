@@ -21,10 +21,10 @@
 namespace jq {
 namespace umma {
 
-// N = MMA columns: 8, 16 or 32 hold up to 4, 8, 16 rows of x.
+// N = MMA columns: 16 or 32 hold up to 8 or 16 rows of x (an MMA of 128 rows takes multiples of 16 columns).
 template <int N>
 struct ImageCfg {
-    static_assert(N == 8 || N == 16 || N == 32, "column counts of the decode GEMV");
+    static_assert(N == 16 || N == 32, "column counts of the decode GEMV");
     static constexpr int MAX_ROWS = N / 2;
     static constexpr int MPAD = N / 2;                       // floats per aux row (16-byte multiples)
     static constexpr int STEPS = 16;                         // MMA instructions per super-block
@@ -36,9 +36,9 @@ struct ImageCfg {
     static_assert(BYTES % 16 == 0, "the image is copied in 16-byte pieces");
 };
 
-__host__ __device__ constexpr int columns_for_rows(int rows) { return rows <= 4 ? 8 : (rows <= 8 ? 16 : 32); }
+__host__ __device__ constexpr int columns_for_rows(int rows) { return rows <= 8 ? 16 : 32; }
 __host__ __device__ constexpr size_t image_block_bytes(int n_cols) {
-    return n_cols == 8 ? ImageCfg<8>::BYTES : (n_cols == 16 ? ImageCfg<16>::BYTES : ImageCfg<32>::BYTES);
+    return n_cols == 16 ? ImageCfg<16>::BYTES : ImageCfg<32>::BYTES;
 }
 
 // This lane's eight values of the super-block at xb: lane = 4 sub + tt holds elements 8 tt .. 8 tt + 7 of sub-block `sub`.
