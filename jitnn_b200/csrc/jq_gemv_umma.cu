@@ -1252,16 +1252,23 @@ int launch_gemv_umma_multi(const View* vs, int count, const float* x, uint8_t* i
     a.lbo = (uint32_t)(ncols / 8) * 128u;
     a.sbo = 128u;
     a.peer = peer != nullptr ? peer->table : nullptr;
+    // Two scratch areas. The hand-off words are all zero between launches (every word a CTA writes is cleared by the CTA that
+    // reads it), whatever the launches' shapes; the floats a CTA keeps aside for itself are never cleared, so they live in an
+    // area of their own, where no launch looks for marks.
     uint8_t* partial = nullptr;
+    uint8_t* aside = nullptr;
     if (!no_scratch) {
         const size_t words = (size_t)grid * a.max_pieces * rows * ROWS;
-        rc = scratch_zeroed_for_slot(s, 2, words * (sizeof(unsigned long long) + sizeof(float)), &partial);
+        rc = scratch_zeroed_for_slot(s, 2, words * sizeof(unsigned long long), &partial);
+        if (rc == JQ_OK) {
+            rc = scratch_for_slot(s, 5, words * sizeof(float), &aside);
+        }
         if (rc != JQ_OK) {
             return rc;
         }
     }
     a.partial = reinterpret_cast<unsigned long long*>(partial);
-    a.aside = reinterpret_cast<float*>(a.partial + (size_t)grid * a.max_pieces * rows * ROWS);
+    a.aside = reinterpret_cast<float*>(aside);
     if (nc > 1) {
         uint8_t* parts = nullptr;
         rc = scratch_for_slot(s, 4, (size_t)nc * rows * a.n_sum * sizeof(float), &parts);

@@ -109,3 +109,15 @@ def test_option_values():
     assert L.jq_set_option(b"gemv_tcgen05", 3) != 0
     assert L.jq_set_option(b"gemv_tcgen05", 2) == 0
     assert L.jq_set_option(b"gemv_tcgen05", 0) == 0
+
+
+def test_launches_of_different_shapes_share_the_scratch():
+    """The hand-off words between thread blocks must be all zero when a launch starts, whatever ran before it: a launch with few rows
+    of x whose thread blocks keep floats aside (a tile shared by three or more of them) between two launches with many rows, whose
+    hand-off words cover more of the scratch buffer."""
+    rows = np.unique(np.concatenate([np.arange(130), np.arange(11008 - 130, 11008)]))
+    check("Q4_K", 11008, 4096, 16, seed=1, rows=rows)
+    check("Q4_K", 4096, 11008, 2, seed=2, rows=rows[:130])
+    check("Q4_K", 11008, 4096, 16, seed=3, rows=rows)
+    check("Q5_K", 4096, 11008, 5, seed=4, rows=rows[:130])
+    check("Q4_K", 11008, 4096, 9, seed=5, rows=rows)
