@@ -801,7 +801,7 @@ def sharded_decoder_check(torch, device, rank, world):
     """Before the timed run at N > 1: a two-layer decoder of the 70B layer shape (d 8192, 64 / 8 heads, FFN 28672, vocab 32000,
     all Q4_K, seeded) split over the ranks against the same decoder on this rank's GPU alone, on the general kernels
     (option decoder_fused = 0), where both do the same arithmetic per output row: logits and greedy tokens of a prompt of 12
-    tokens and of 3 single-token steps must be bitwise equal on every rank."""
+    tokens must agree within 2e-5, those of the same tokens in calls of at most eight and of 3 single-token steps bitwise, on every rank."""
     import numpy as np
     import torch.distributed as dist
     import jitnn_b200
@@ -826,9 +826,16 @@ def sharded_decoder_check(torch, device, rank, world):
     for d in (whole, split):
         d.load({"output": ("Q4_K", raw, vocab, dim), "norm": ones, "tok_embeddings": table})
     prompt = np.random.default_rng(3).integers(0, vocab, 12).astype(np.int32)
+    # twelve tokens in one call: from eleven rows on the kernel of a linear is chosen by its number of weight rows (the tcgen05
+    # GEMV where they are many), so a shard may sum in another order than the whole weight: equal within 2e-5 of the largest logit
     a, na = whole.forward(prompt, 0)
     b, nb = split.forward(prompt, 0)
-    ok = bool(np.array_equal(a, b) and np.array_equal(na, nb))
+    ok = bool(np.abs(a - b).max() <= 2e-5 * np.abs(a).max())
+    # the same tokens in calls of at most eight (one kernel whatever the rows): bitwise
+    for lo, hi in ((0, 8), (8, 12)):
+        a, na = whole.forward(prompt[lo:hi], lo)
+        b, nb = split.forward(prompt[lo:hi], lo)
+        ok = ok and bool(np.array_equal(a, b) and np.array_equal(na, nb))
     tok, pos = int(na[-1]), 12
     for _ in range(3):
         a, na = whole.forward([tok], pos)
@@ -843,7 +850,7 @@ def sharded_decoder_check(torch, device, rank, world):
     all_ok = bool(int(t.item()))
     assert all_ok, "the row-sharded decoder differs from the single-GPU decoder"
     return {"against": "the same 2-layer 70B-shape decoder on one GPU, general kernels", "bitwise_equal": all_ok, "ranks_checked": world,
-            "tokens": 12 + 3}
+            "tokens": 12 + 3, "note": "bitwise: the 12 tokens in calls of 8 and 4, and 3 single-token steps; the 12 tokens in one call within 2e-5"}
 
 
 def decode_leg(torch, device, shape=None):
