@@ -1653,9 +1653,8 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         } else {
             add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
-            LIN(L[0], d->xn, d->q);
-            LIN(L[1], d->xn, d->k);
-            LIN(L[2], d->xn, d->v);
+            float* const qkv[3] = {d->q, d->k, d->v};
+            if (rc == JQ_OK) rc = linear_device_multi(L, 3, d->xn, T, qkv, s);
         }
         if (rc != JQ_OK) break;
         const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
@@ -1692,8 +1691,8 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         } else {
             add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, B, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");
-            LIN(L[4], d->xn, d->gate);
-            LIN(L[5], d->xn, d->up);
+            float* const gu[2] = {d->gate, d->up};
+            if (rc == JQ_OK) rc = linear_device_multi(L + 4, 2, d->xn, T, gu, s);
         }
         if (rc != JQ_OK) break;
         if (fused_in && hidden_l % 256 == 0 && L[6]->type == JQ_TYPE_Q4_K) {
