@@ -146,7 +146,7 @@ size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
 // second Q4_K weight with the same k can ride in the same launch.
 size_t q4k_image_bytes_one_row(int64_t k);
 int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
-                              const PeerOut* peer = nullptr);
+                              const PeerOut* peer = nullptr, const View* v3 = nullptr, float* y3 = nullptr);
 // Status word of the waits a GEMV makes itself for a peer exchange (peer_wait_inline): 0 or 32 + rank, cleared by the call.
 int gemv_peer_status(int* status);
 int gemv_q6k_status(int* status);  // the same for the Q6_K kernel's weight-ring waits (0 or 25)

@@ -1321,6 +1321,23 @@ static Images decoder_images_for(const jq_decoder* d, std::initializer_list<cons
 }
 
 // y = W x (and y2 = W2 x in the same launch when both are Q4_K), x being the image written just before
+static int decoder_gemv_imaged(jq_decoder* d, const jq_weight* w, float* y, const jq_weight* w2, float* y2, cudaStream_t gs);
+
+// The same for three weights (wq, wk, wv): one launch when all are Q4_K, else the first two together and the third alone.
+static int decoder_gemv_imaged3(jq_decoder* d, const jq_weight* w, float* y, const jq_weight* w2, float* y2, const jq_weight* w3, float* y3,
+                                cudaStream_t gs) {
+    if (w->type == JQ_TYPE_Q4_K && w2->type == JQ_TYPE_Q4_K && w3->type == JQ_TYPE_Q4_K) {
+        const View v{w->q, w->aux, w->n, w->k, w->type}, v2{w2->q, w2->aux, w2->n, w2->k, w2->type}, v3{w3->q, w3->aux, w3->n, w3->k, w3->type};
+        bool handled = false;
+        int rc = launch_gemv_q4k_i8_imaged(v, &v2, d->img_q4k, nullptr, y, y2, gs, &handled, nullptr, &v3, y3);
+        if (rc != JQ_OK || handled) {
+            return rc;
+        }
+    }
+    int rc = decoder_gemv_imaged(d, w, y, w2, y2, gs);
+    return rc == JQ_OK ? decoder_gemv_imaged(d, w3, y3, nullptr, nullptr, gs) : rc;
+}
+
 static int decoder_gemv_imaged(jq_decoder* d, const jq_weight* w, float* y, const jq_weight* w2, float* y2, cudaStream_t gs) {
     int rc = JQ_OK;
     for (int pass = 0; pass < 2 && rc == JQ_OK; pass++) {
@@ -1405,8 +1422,9 @@ static int enqueue_forward_fused(jq_decoder* d, int max_keys, const TokenArgs* t
         CKL(launch_cluster_pdl(norm_image_kernel, norm_ctas, norm_block, norm_smem, s, l > 0 || first_programmatic, d->x, l == 0 ? nullptr : d->proj,
                        l == 0 ? d->embed : nullptr, d->tokens, d->vocab, d->norms + (size_t)(2 * l) * dim, d->eps, dim, images_for({L[0], L[1], L[2]}), (const uint32_t*)nullptr, 0),
             "norm_image_kernel");
-        GEMV(L[0], d->q, L[1], d->k, s);
-        GEMV(L[2], d->v, nullptr, nullptr, s);
+        if (rc == JQ_OK) {
+            rc = decoder_gemv_imaged3(d, L[0], d->q, L[1], d->k, L[2], d->v, s);
+        }
         if (rc != JQ_OK) break;
         CKL(launch_pdl(attention_image_kernel<false>, dim3(d->heads, splits_now), dim3(ATTF_THREADS), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos,
                        d->heads, d->kv_heads, d->splits, scale, d->att_part, d->counters, images_for({L[3]}), PeerImage{}),
@@ -1648,8 +1666,9 @@ static int enqueue_forward_sharded(jq_decoder* d, int T, int max_keys, const Tok
         float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         if (fused_in) {
             NORM_IMAGE(l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, {L[0], L[1], L[2]});
-            GEMV_IMAGED(L[0], d->q, L[1], d->k);
-            GEMV_IMAGED(L[2], d->v, nullptr, nullptr);
+            if (rc == JQ_OK) {
+                rc = decoder_gemv_imaged3(d, L[0], d->q, L[1], d->k, L[2], d->v, s);
+            }
         } else {
             add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, l == 0 ? nullptr : D, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
             LAUNCHED("add_rmsnorm_kernel");

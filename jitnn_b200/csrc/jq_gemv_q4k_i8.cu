@@ -125,12 +125,16 @@ __device__ __forceinline__ long long gtime() {
 #endif
 
 // ---- the GEMV ---------------------------------------------------------------------------------------------------
-// A second weight with the same k that is multiplied with the same x in the same launch (q = nullptr: none).
+// A second and a third weight with the same k that are multiplied with the same x in the same launch (q = nullptr: none).
 struct Second {
     const uint8_t* q;
     int64_t n;
     float* y;
-    int first_tiles;  // tiles of the first weight
+    int first_tiles;   // tiles of the first weight
+    const uint8_t* q3;
+    int64_t n3;
+    float* y3;
+    int second_tiles;  // tiles of the first and the second weight
 };
 
 // PEER: the outputs go into every rank's y of a row-sharded linear (jq_peer.cu) instead of y. A template flag, not a
@@ -196,8 +200,8 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
     // the slot of tile number ti of the CTA, first block of this warp in slice sl
     auto step_ptr = [&](int ti, int sl) {
         const int tile = (int)blockIdx.x + ti * (int)gridDim.x;
-        const int local = tile < w2.first_tiles ? tile : tile - w2.first_tiles;
-        const uint8_t* base = tile < w2.first_tiles ? v.q : w2.q;
+        const int local = tile < w2.first_tiles ? tile : (tile < w2.second_tiles ? tile - w2.first_tiles : tile - w2.second_tiles);
+        const uint8_t* base = tile < w2.first_tiles ? v.q : (tile < w2.second_tiles ? w2.q : w2.q3);
         return base + ((int64_t)(local >> 3) * KB + (sl * KS + warp)) * UNIT + (local & 7) * 16 * B::BYTES;
     };
     const uint8_t* gp = step_ptr(0, 0);
@@ -515,12 +519,12 @@ __global__ void __launch_bounds__(NW * 32, OCC) gemv_q4k_i8_kernel(View v, Secon
             }
             __syncthreads();
             // ---- the warps' partial sums in a fixed order, added to what earlier slices left ---------------------------------
-            const bool second = my_tile >= w2.first_tiles;
-            const int64_t n = second ? w2.n : v.n;
-            float* const yo = second ? w2.y : y;
+            const bool second = my_tile >= w2.first_tiles, third = my_tile >= w2.second_tiles;
+            const int64_t n = third ? w2.n3 : (second ? w2.n : v.n);
+            float* const yo = third ? w2.y3 : (second ? w2.y : y);
             for (int o = tid; o < 16 * MT; o += THREADS) {
                 const int r = o / MT, m = o % MT;
-                const int64_t row = (int64_t)(second ? my_tile - w2.first_tiles : my_tile) * 16 + r;
+                const int64_t row = (int64_t)(third ? my_tile - w2.second_tiles : (second ? my_tile - w2.first_tiles : my_tile)) * 16 + r;
                 const float* p = rd + o;
                 constexpr int W = 16 * MT;  // floats per warp
                 float sum = ((p[0] + p[W]) + (p[2 * W] + p[3 * W])) + ((p[4 * W] + p[5 * W]) + (p[6 * W] + p[7 * W]));
@@ -586,7 +590,7 @@ int launch(const View& v, const Second& w2, const PeerOut& peer, const uint8_t* 
         JQ_CUDA(cudaFuncSetAttribute(gemv_q4k_i8_kernel<MT, STAGES, NW, OCC, Q5, PEER, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX));
         configured.fetch_or((uint64_t)1 << (dev & 63));
     }
-    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0) + (w2.q3 != nullptr ? (int)((w2.n3 + 15) / 16) : 0);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(NW * 32);
@@ -623,7 +627,7 @@ int run(const View& v, const Second& w2, const PeerOut& peer, const float* x, in
         bool* handled, bool may_fuse) {
     // x == nullptr: the image is already in `image` (written by a kernel earlier in the stream)
     const int KB = (int)(v.k / 256);
-    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0);
+    const int tiles = (int)((v.n + 15) / 16) + (w2.q != nullptr ? (int)((w2.n + 15) / 16) : 0) + (w2.q3 != nullptr ? (int)((w2.n3 + 15) / 16) : 0);
     // Candidates, best first. Many rows of x make the image large: one CTA of 16 warps per SM shares one copy of it.
     constexpr bool WIDE = MT > 2;
     // (Three CTAs of 8 warps per SM, which 80 registers per thread allow, measured no faster than two on any shape and
@@ -735,7 +739,7 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
         v.k / 256 >= (1 << 20)) {
         return JQ_OK;
     }
-    const Second none{nullptr, 0, nullptr, 0x7fffffff};
+    const Second none{nullptr, 0, nullptr, 0x7fffffff, nullptr, 0, nullptr, 0x7fffffff};
     PeerOut local{};  // world = 0: results go to y
     const PeerOut& po = peer != nullptr ? *peer : local;
     if (v.type == JQ_TYPE_Q5_K) {
@@ -767,15 +771,19 @@ size_t q4k_image_bytes_one_row(int64_t k) { return (size_t)(k / 256) * Cfg<1>::P
 
 // One row of x whose image (q4k::build_image<1> per super-block) a kernel earlier in the stream has written to `image`;
 // that kernel should execute griddepcontrol.launch_dependents so that this one can request weights meanwhile. With
-// v2 != nullptr the rows of a second Q4_K weight with the same k follow in the same launch, results in y2.
+// v2 != nullptr the rows of a second Q4_K weight with the same k follow in the same launch, results in y2, and with
+// v3 != nullptr (only together with v2) those of a third, results in y3.
 int launch_gemv_q4k_i8_imaged(const View& v, const View* v2, const uint8_t* image, const float* bias, float* y, float* y2, cudaStream_t s, bool* handled,
-                              const PeerOut* peer) {
+                              const PeerOut* peer, const View* v3, float* y3) {
     *handled = false;
     if (v.type != JQ_TYPE_Q4_K || v.n == 0 || v.k == 0 || image == nullptr || v.k / 256 >= (1 << 20) ||
-        (v2 != nullptr && (v2->type != JQ_TYPE_Q4_K || v2->k != v.k || v2->n == 0 || y2 == nullptr))) {
+        (v2 != nullptr && (v2->type != JQ_TYPE_Q4_K || v2->k != v.k || v2->n == 0 || y2 == nullptr)) ||
+        (v3 != nullptr && (v2 == nullptr || v3->type != JQ_TYPE_Q4_K || v3->k != v.k || v3->n == 0 || y3 == nullptr))) {
         return JQ_OK;
     }
-    const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? (int)((v.n + 15) / 16) : 0x7fffffff};
+    const int t1 = (int)((v.n + 15) / 16), t2 = v2 != nullptr ? t1 + (int)((v2->n + 15) / 16) : 0x7fffffff;
+    const Second w2{v2 != nullptr ? v2->q : nullptr, v2 != nullptr ? v2->n : 0, y2, v2 != nullptr ? t1 : 0x7fffffff,
+                    v3 != nullptr ? v3->q : nullptr, v3 != nullptr ? v3->n : 0, y3, v3 != nullptr ? t2 : 0x7fffffff};
     const PeerOut local{};  // world = 0: results go to y (and y2)
     if (peer != nullptr && v2 != nullptr) {
         return JQ_OK;  // a second weight has no place in a peer's y
