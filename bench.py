@@ -790,7 +790,7 @@ def decode_70b_leg(torch, device, rank, world, shape=None):
                         "frac": round((weight_bytes + kv16) / world / dt16 / 1e9 / peak, 4)},
             "prompt_tokens_per_s": round(seqs * prompt_len / t_prompt, 1), "weight_bytes_per_token": int(weight_bytes), "peak_source": "of " + which,
             "config": "70B shape, %d layers, all Q4_K, rows split over %d GPU(s), 16 prompts of %d tokens in groups of 16, %d timed greedy steps "
-                      "per batch size, fp32 KV cache; batch 1: the fused single-token step (9 launches per layer; with several GPUs the attention and "
+                      "per batch size, fp32 KV cache; batch 1: the fused single-token step (8 launches per layer; with several GPUs the attention and "
                       "SwiGLU kernels store the next linear's activation image into every rank, wo / w2 store their rows into every rank's "
                       "vector, the consumers wait for the flags themselves); batch 16: general kernels, the linears of enough weight rows on the tcgen05 "
                       "GEMV (16 rows of x in one pass), the others in two passes of 8; both replayed as CUDA graphs" % (layers, world, prompt_len, gen - 2),
