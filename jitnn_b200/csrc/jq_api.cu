@@ -229,13 +229,35 @@ int linear_device(const jq_weight* w, const float* x, int64_t m, const float* bi
 // rows together are a shape the tcgen05 kernel is chosen for go through it in one launch, sharing one activation image;
 // anything else is one linear after the other.
 int linear_device_multi(const jq_weight* const* ws, int count, const float* x, int64_t m, float* const* ys, cudaStream_t s) {
+    if (count <= 0) {
+        return JQ_OK;
+    }
     const int64_t min_rows = g_prefill_min_rows.load();
-    bool together = count >= 2 && count <= 3 && m >= 1 && m <= 16 && !(min_rows > 0 && m >= min_rows);
+    bool same = count >= 1;
     int64_t n_all = 0;
-    for (int i = 0; i < count && together; i++) {
-        together = ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->n > 0;
+    for (int i = 0; i < count && same; i++) {
+        same = ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->n > 0;
         n_all += ws[i]->n;
     }
+    if (!same && count >= 2 && count <= 3) {
+        // mixed formats (a Q6_K wv beside Q4_K wq and wk): those like the first go together, the others alone
+        const jq_weight* like[3];
+        float* like_y[3];
+        int n_like = 0;
+        for (int i = 0; i < count; i++) {
+            if (ws[i]->type == ws[0]->type && ws[i]->k == ws[0]->k && ws[i]->n > 0) {
+                like[n_like] = ws[i];
+                like_y[n_like++] = ys[i];
+            } else {
+                int rc = linear_device(ws[i], x, m, nullptr, ys[i], s, false);
+                if (rc != JQ_OK) {
+                    return rc;
+                }
+            }
+        }
+        return n_like > 0 ? linear_device_multi(like, n_like, x, m, like_y, s) : JQ_OK;
+    }
+    const bool together = same && count >= 2 && count <= 3 && m >= 1 && m <= 16 && !(min_rows > 0 && m >= min_rows);
     if (together && gemv_umma_takes(ws[0]->type, ws[0]->k, (int)m, n_all)) {
         View vs[3];
         for (int i = 0; i < count; i++) {
@@ -244,6 +266,35 @@ int linear_device_multi(const jq_weight* const* ws, int count, const float* x, i
         uint8_t* image = nullptr;
         int rc = scratch_for(s, gemv_umma_image_bytes(ws[0]->k, (int)m), &image);
         return rc == JQ_OK ? launch_gemv_umma_multi(vs, count, x, image, (int)m, nullptr, ys, s) : rc;
+    }
+    const bool k_quant = ws[0]->type == JQ_TYPE_Q4_K || ws[0]->type == JQ_TYPE_Q5_K;
+    if (count >= 2 && count <= 3 && same && k_quant && g_opt_gemv_generic.load() == 0 && !(min_rows > 0 && m >= min_rows)) {
+        // the mma.sync kernel: up to 8 rows of x per pass, the weights' rows one after the other in one launch on one image
+        View vs[3];
+        for (int i = 0; i < count; i++) {
+            vs[i] = view_of(ws[i]);
+        }
+        bool all = true;
+        for (int64_t m0 = 0; m0 < m && all; m0 += 8) {
+            const int rows = (int)(m - m0 < 8 ? m - m0 : 8);
+            float* out[3];
+            for (int i = 0; i < count; i++) {
+                out[i] = ys[i] + m0 * ws[i]->n;
+            }
+            uint8_t* image = nullptr;
+            bool handled = false;
+            int rc = scratch_for(s, gemv_q4k_i8_scratch_bytes(ws[0]->k, rows), &image);
+            if (rc == JQ_OK) {
+                rc = launch_gemv_q4k_i8_multi(vs, count, x + m0 * ws[0]->k, rows, out, s, image, &handled);
+            }
+            if (rc != JQ_OK) {
+                return rc;
+            }
+            all = handled;  // a shape that kernel declines (nothing has been launched for this group): one linear after the other
+        }
+        if (all) {
+            return JQ_OK;
+        }
     }
     for (int i = 0; i < count; i++) {
         int rc = linear_device(ws[i], x, m, nullptr, ys[i], s, false);

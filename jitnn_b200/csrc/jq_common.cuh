@@ -142,6 +142,7 @@ struct PeerOut {
 int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bias, float* y, cudaStream_t s, uint8_t* image, bool* handled,
                        const PeerOut* peer = nullptr, bool x_remote = false);
 size_t gemv_q4k_i8_scratch_bytes(int64_t k, int rows);
+int launch_gemv_q4k_i8_multi(const View* vs, int count, const float* x, int rows, float* const* ys, cudaStream_t s, uint8_t* image, bool* handled);
 // The same for one row of x whose activation image (jq_q4k_image.cuh) a kernel earlier in the stream has already written; a
 // second Q4_K weight with the same k can ride in the same launch.
 size_t q4k_image_bytes_one_row(int64_t k);

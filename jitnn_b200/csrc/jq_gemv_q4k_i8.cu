@@ -752,6 +752,34 @@ int launch_gemv_q4k_i8(const View& v, const float* x, int rows, const float* bia
     return run<8, false>(v, none, po, x, rows, bias, y, s, image, handled, !x_remote);
 }
 
+// The same for two or three weights of one type and k on the same x: their rows follow one another in one launch, on one
+// activation image (results in ys[i], [rows, n_i]; no bias).
+int launch_gemv_q4k_i8_multi(const View* vs, int count, const float* x, int rows, float* const* ys, cudaStream_t s, uint8_t* image, bool* handled) {
+    *handled = false;
+    if (count < 2 || count > 3 || rows < 1 || rows > 8 || image == nullptr) {
+        return JQ_OK;
+    }
+    const View& v = vs[0];
+    for (int i = 0; i < count; i++) {
+        if ((vs[i].type != JQ_TYPE_Q4_K && vs[i].type != JQ_TYPE_Q5_K) || vs[i].type != v.type || vs[i].k != v.k || vs[i].n == 0 || v.k == 0 ||
+            v.k / 256 >= (1 << 20) || ys[i] == nullptr) {
+            return JQ_OK;
+        }
+    }
+    const int t1 = (int)((v.n + 15) / 16), t2 = t1 + (int)((vs[1].n + 15) / 16);
+    const Second w2{vs[1].q, vs[1].n, ys[1], t1, count == 3 ? vs[2].q : nullptr, count == 3 ? vs[2].n : 0, count == 3 ? ys[2] : nullptr,
+                    count == 3 ? t2 : 0x7fffffff};
+    const PeerOut local{};
+    if (v.type == JQ_TYPE_Q5_K) {
+        if (rows == 1) return run<1, true>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+        if (rows == 2) return run<2, true>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+        return run<8, true>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+    }
+    if (rows == 1) return run<1, false>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+    if (rows == 2) return run<2, false>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+    return run<8, false>(v, w2, local, x, rows, nullptr, ys[0], s, image, handled, true);
+}
+
 #ifdef JQ_Q4K_TRACE
 }  // namespace jq
 extern "C" JQ_API int jq_debug_q4k_trace(long long* out, int* tickets) {
