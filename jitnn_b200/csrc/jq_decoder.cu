@@ -80,6 +80,8 @@ __global__ void set_tokens_kernel(TokenArgs a, int* __restrict__ tokens, int* __
 
 // x[t, :] = table[token[t], :]
 __global__ void embed_kernel(const int* __restrict__ tokens, const float* __restrict__ table, float* __restrict__ x, int dim, int vocab) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     int tok = tokens[blockIdx.x];
     tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
     const float4* src = reinterpret_cast<const float4*>(table + (int64_t)tok * dim);
@@ -95,6 +97,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const float* __rest
 constexpr int NORM_THREADS = 1024;
 __global__ void __launch_bounds__(NORM_THREADS) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ w,
                                                                    float eps, float* __restrict__ out, int dim) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     __shared__ float scratch[32];
     float* xr = x + (int64_t)blockIdx.x * dim;
     const float* dr = delta != nullptr ? delta + (int64_t)blockIdx.x * dim : nullptr;
@@ -155,6 +159,8 @@ __global__ void add_kernel(float* __restrict__ x, const float* __restrict__ delt
 __global__ void rope_store_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ k_cache,
                                   float* __restrict__ v_cache, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                   const int* __restrict__ pos0, int heads, int kv_heads, int head_dim, int pos_step, int64_t tok_stride) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     // consecutive tokens of one sequence: pos_step 1, tok_stride 0; one token each of several sequences at the same
     // position: pos_step 0, tok_stride = elements between two sequences' caches
     const int t = blockIdx.x, h = blockIdx.y, p = threadIdx.x, half = head_dim / 2;
@@ -196,6 +202,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_partial_kernel(const fl
                                                                         const float* __restrict__ v_cache, float* __restrict__ part,
                                                                         const int* __restrict__ pos0, int heads, int kv_heads, int head_dim,
                                                                         int splits, float scale, int pos_step, int64_t tok_stride) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     __shared__ float qs[256];
     __shared__ float sc[ATT_CHUNK];
     __shared__ float scratch[32];
@@ -280,6 +288,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_partial_kernel(const fl
 // out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s over the splits of (t, h), in split order.
 __global__ void attention_combine_kernel(const float* __restrict__ part, float* __restrict__ out, int heads, int head_dim, int stride_splits,
                                          int splits) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     // stride_splits = chunks the partial buffer was laid out for, splits = chunks written by this call
     const int h = blockIdx.x, t = blockIdx.y;
     const float* p = part + ((int64_t)t * heads + h) * stride_splits * (head_dim + 2);
@@ -446,6 +456,8 @@ __global__ void set_pos_kernel(int pos0, int* __restrict__ pos) { *pos = pos0; }
 
 // act = silu(gate) * up
 __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ act, int64_t count) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) {
         const float g = gate[i];
@@ -455,6 +467,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __res
 
 // First index of the maximum of each row (ops/Reduce.java:201). grid = rows, 1024 threads.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
+    asm volatile("griddepcontrol.launch_dependents;");  // launched programmatically, the kernel behind this one may be scheduled now ...
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // ... and this one touches memory only when the kernel before it has finished
     __shared__ float bv[32];
     __shared__ int bi[32];
     const float* row = logits + (int64_t)blockIdx.x * vocab;
@@ -1473,8 +1487,13 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
             rc = linear_device(w, in, T, nullptr, out_, s);
         }
     };
+    cudaError_t pdl_err = cudaSuccess;  // what the latest programmatic launch returned
     auto LAUNCHED = [&](const char* name) {
         count_launch(1);
+        if (rc == JQ_OK && pdl_err != cudaSuccess) {
+            rc = cuda_fail(pdl_err, name);
+        }
+        pdl_err = cudaSuccess;
         if (rc == JQ_OK) {
             rc = check_launch(name);
         }
@@ -1492,7 +1511,7 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         }
     }
     if (rc == JQ_OK) {
-        embed_kernel<<<T, 256, 0, s>>>(d->tokens, d->embed, d->x, dim, d->vocab);
+        if (rc == JQ_OK) pdl_err = launch_pdl(embed_kernel, dim3(T), dim3(256), 0, s, true, d->tokens, d->embed, d->x, dim, d->vocab);
         LAUNCHED("embed_kernel");
     }
     const float scale = (float)(1.0 / std::sqrt((double)hd));
@@ -1505,26 +1524,26 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         float* kc = d->k_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         float* vc = d->v_cache + seq_base + (size_t)l * d->max_seq * kv_dim;
         // attention block; the residual add of the previous block's feed-forward output is fused into this norm
-        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
+        if (rc == JQ_OK) pdl_err = launch_pdl(add_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), 0, s, true, d->x, l == 0 ? nullptr : d->proj, d->norms + (size_t)(2 * l) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         {
             float* const qkv[3] = {d->q, d->k, d->v};
             if (rc == JQ_OK) rc = linear_device_multi(L, 3, d->xn, T, qkv, s);
         }
         if (rc != JQ_OK) break;
-        rope_store_kernel<<<dim3(T, d->heads + 2 * d->kv_heads), hd / 2, 0, s>>>(d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd, pos_step, tok_stride);
+        if (rc == JQ_OK) pdl_err = launch_pdl(rope_store_kernel, dim3(T, d->heads + 2 * d->kv_heads), dim3(hd / 2), 0, s, true, d->q, d->k, d->v, kc, vc, d->cos_t, d->sin_t, d->pos, d->heads, d->kv_heads, hd, pos_step, tok_stride);
         LAUNCHED("rope_store_kernel");
         // only the key chunks that can hold a position of this call are launched (all of them inside the captured graph)
         const int splits_now = (max_keys + ATT_CHUNK - 1) / ATT_CHUNK;
-        attention_partial_kernel<<<dim3(d->heads, splits_now, T), ATT_THREADS, 0, s>>>(d->q, kc, vc, d->att_part, d->pos, d->heads, d->kv_heads, hd,
+        if (rc == JQ_OK) pdl_err = launch_pdl(attention_partial_kernel, dim3(d->heads, splits_now, T), dim3(ATT_THREADS), 0, s, true, d->q, kc, vc, d->att_part, d->pos, d->heads, d->kv_heads, hd,
                                                                                  d->splits, scale, pos_step, tok_stride);
         LAUNCHED("attention_partial_kernel");
-        attention_combine_kernel<<<dim3(d->heads, T), hd < 128 ? hd : 128, 0, s>>>(d->att_part, d->att, d->heads, hd, d->splits, splits_now);
+        if (rc == JQ_OK) pdl_err = launch_pdl(attention_combine_kernel, dim3(d->heads, T), dim3(hd < 128 ? hd : 128), 0, s, true, d->att_part, d->att, d->heads, hd, d->splits, splits_now);
         LAUNCHED("attention_combine_kernel");
         LIN(L[3], d->att, d->proj);
         if (rc != JQ_OK) break;
         // feed-forward block
-        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
+        if (rc == JQ_OK) pdl_err = launch_pdl(add_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), 0, s, true, d->x, d->proj, d->norms + (size_t)(2 * l + 1) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         {
             float* const gu[2] = {d->gate, d->up};
@@ -1532,17 +1551,17 @@ static int enqueue_forward(jq_decoder* d, int T, int max_keys, const TokenArgs* 
         }
         if (rc != JQ_OK) break;
         const int64_t cnt = (int64_t)T * d->hidden;
-        swiglu_kernel<<<(unsigned)((cnt + 255) / 256), 256, 0, s>>>(d->gate, d->up, d->act, cnt);
+        if (rc == JQ_OK) pdl_err = launch_pdl(swiglu_kernel, dim3((unsigned)((cnt + 255) / 256)), dim3(256), 0, s, true, d->gate, d->up, d->act, cnt);
         LAUNCHED("swiglu_kernel");
         LIN(L[6], d->act, d->proj);
     }
     if (rc == JQ_OK) {
-        add_rmsnorm_kernel<<<T, NORM_THREADS, 0, s>>>(d->x, d->proj, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
+        if (rc == JQ_OK) pdl_err = launch_pdl(add_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), 0, s, true, d->x, d->proj, d->norms + (size_t)(2 * d->layers) * dim, d->eps, d->xn, dim);
         LAUNCHED("add_rmsnorm_kernel");
         LIN(d->output, d->xn, d->logits);
     }
     if (rc == JQ_OK) {
-        argmax_kernel<<<T, 1024, 0, s>>>(d->logits, d->argmax, d->vocab);
+        if (rc == JQ_OK) pdl_err = launch_pdl(argmax_kernel, dim3(T), dim3(1024), 0, s, true, d->logits, d->argmax, d->vocab);
         LAUNCHED("argmax_kernel");
     }
     return rc;
